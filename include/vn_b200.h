@@ -1,0 +1,179 @@
+/*
+ * vn_b200.h -- C ABI of the B200 (sm_100a) speculative-decoding library.
+ *
+ * The reference (CUI-hyg/VerseNext) has no C FFI for this path: its only
+ * native binding is the PyO3 module `verse_rs` (packages/verse_torch/src/lib.rs:51-65),
+ * which is not on the decode path.  These entry points are what a ctypes /
+ * cffi stub inside the reference's Python packages binds instead of the
+ * NumPy / torch calls cited beside each group.
+ *
+ * Conventions
+ *  - every function returns an int32 status (VN_OK == 0); nothing throws or
+ *    aborts across this boundary; vn_last_error() gives the message.
+ *  - pointers named *_dev are device pointers obtained from vn_alloc();
+ *    all other pointers are host memory owned by the caller.
+ *  - one vn_ctx per GPU; all work of a context is issued on its one stream.
+ *  - matrices are row-major; weights are (out_features, in_features) as in
+ *    the reference's Linear (verse_torch/vnnn.py:394-430).
+ */
+#ifndef VN_B200_H
+#define VN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum vn_status {
+  VN_OK = 0,
+  VN_ERR_INVALID = 1,     /* bad argument            -> ValueError   */
+  VN_ERR_OOM = 2,         /* device allocation failed -> MemoryError */
+  VN_ERR_OVERFLOW = 3,    /* KV cache capacity        -> RuntimeError (kv_cache_parallel.py:152-159) */
+  VN_ERR_TIMEOUT = 4,     /* a bounded device wait ran out */
+  VN_ERR_CUDA = 5,        /* CUDA runtime error       -> RuntimeError */
+  VN_ERR_NCCL = 6,
+  VN_ERR_INDEX = 7,       /* layer / sequence index   -> IndexError (kv_cache_parallel.py:136-139) */
+  VN_ERR_UNSUPPORTED = 8
+};
+
+enum vn_dtype { VN_F32 = 0, VN_BF16 = 1, VN_I8 = 2, VN_I4 = 3, VN_I64 = 4, VN_I32 = 5, VN_U8 = 6 };
+
+typedef struct vn_ctx vn_ctx;
+typedef struct vn_model vn_model;
+typedef struct vn_kv vn_kv;
+
+/* ---- lifecycle ------------------------------------------------------- */
+int32_t vn_version(void);
+int32_t vn_ctx_create(int32_t device, vn_ctx** out);
+int32_t vn_ctx_destroy(vn_ctx* ctx);
+const char* vn_last_error(vn_ctx* ctx);       /* ctx may be NULL: last error of the calling thread */
+int32_t vn_sync(vn_ctx* ctx);
+/* number of kernels this context has launched since creation */
+int32_t vn_launch_count(vn_ctx* ctx, uint64_t* out);
+/* opaque handle of the context's CUDA stream (cudaStream_t) */
+int32_t vn_stream(vn_ctx* ctx, void** out);
+
+/* ---- memory (replaces Tensor.to(device): verse_torch/tensor.py:394) --- */
+int32_t vn_alloc(vn_ctx* ctx, size_t bytes, void** out_dev);
+int32_t vn_free(vn_ctx* ctx, void* dev);
+int32_t vn_memset(vn_ctx* ctx, void* dev, int32_t byte, size_t bytes);
+int32_t vn_h2d(vn_ctx* ctx, void* dst_dev, const void* src, size_t bytes);   /* synchronous */
+int32_t vn_d2h(vn_ctx* ctx, void* dst, const void* src_dev, size_t bytes);   /* synchronous */
+int32_t vn_d2d(vn_ctx* ctx, void* dst_dev, const void* src_dev, size_t bytes);
+int32_t vn_host_alloc(vn_ctx* ctx, size_t bytes, void** out);                /* pinned */
+int32_t vn_host_free(vn_ctx* ctx, void* p);
+int32_t vn_h2d_async(vn_ctx* ctx, void* dst_dev, const void* src_pinned, size_t bytes);
+int32_t vn_d2h_async(vn_ctx* ctx, void* dst_pinned, const void* src_dev, size_t bytes);
+int32_t vn_mem_info(vn_ctx* ctx, size_t* free_bytes, size_t* total_bytes);
+
+/* ---- device timing on the context's stream --------------------------- */
+int32_t vn_event_create(vn_ctx* ctx, void** out_event);
+int32_t vn_event_destroy(vn_ctx* ctx, void* event);
+int32_t vn_event_record(vn_ctx* ctx, void* event);
+int32_t vn_event_elapsed_ms(vn_ctx* ctx, void* start, void* stop, float* out_ms); /* synchronises on stop */
+/* Per-kernel timing: while enabled, every launch of this context is bracketed by CUDA events on
+ * its stream.  vn_profile(ctx, 1) clears and starts, vn_profile(ctx, 0) clears and stops;
+ * vn_profile_report writes {"kernel": {"launches": n, "ms": total}, ...} as JSON text. */
+int32_t vn_profile(vn_ctx* ctx, int32_t enable);
+int32_t vn_profile_report(vn_ctx* ctx, char* buf, size_t buf_bytes);
+/* overwrite a scratch buffer twice the size of L2 (bench hygiene) */
+int32_t vn_flush_l2(vn_ctx* ctx);
+
+/* ---- DeviceBackend ops, fp32 (verse_torch/device.py:219-270, :285-335) - */
+/* c[b] = a[b] @ b[b]; a: batch x M x K, b: (batch | 1) x K x N */
+int32_t vn_matmul(vn_ctx* ctx, const float* a_dev, const float* b_dev, float* c_dev,
+                  int64_t batch, int64_t M, int64_t N, int64_t K, int32_t b_broadcast);
+/* y = x @ w.T + bias; x: M x K, w: N x K */
+int32_t vn_linear(vn_ctx* ctx, const float* x_dev, const float* w_dev, const float* bias_dev,
+                  float* y_dev, int64_t M, int64_t N, int64_t K);
+/* softmax over the middle axis of an (outer, n, inner) view; inner == 1 for the last axis */
+int32_t vn_softmax(vn_ctx* ctx, const float* x_dev, float* y_dev, int64_t outer, int64_t n, int64_t inner);
+int32_t vn_layernorm(vn_ctx* ctx, const float* x_dev, const float* w_dev, const float* b_dev,
+                     float* y_dev, int64_t rows, int64_t cols, float eps);
+int32_t vn_rmsnorm(vn_ctx* ctx, const float* x_dev, const float* w_dev, float* y_dev,
+                   int64_t rows, int64_t cols, float eps);
+/* NeoX half-split rotation; x: outer x T x D, cos/sin: T x half (D/2) */
+int32_t vn_rope(vn_ctx* ctx, const float* x_dev, const float* cos_dev, const float* sin_dev,
+                float* y_dev, int64_t outer, int64_t T, int64_t D);
+/* softmax(q k^T / sqrt(D) + mask) v; q: BH x Tq x D, k,v: BH x Tk x D, mask: Tq x Tk additive or NULL */
+int32_t vn_attention(vn_ctx* ctx, const float* q_dev, const float* k_dev, const float* v_dev,
+                     const float* mask_dev, float* out_dev, int64_t BH, int64_t Tq, int64_t Tk, int64_t D);
+
+/* ---- acceptance / rejection sampling ---------------------------------- */
+/* Replaces the argmax compare + accept loop of SpeculativeDecoder
+ * (verse_nex/speculative.py:218-223, :280-287) and the softmax / top-k /
+ * rng.choice sampling of cometspark.py:892-911.
+ *   p_logits_dev  [B, k+1, V] fp32 target logits (row k is used only when bonus != 0;
+ *                  with bonus == 0 it may hold k rows)
+ *   q_logits_dev  [B, k, V] fp32 draft logits, or NULL: proposals were deterministic
+ *   draft_dev     [B, k] int64
+ *   u_accept_dev  [B, k] fp32 / u_sample_dev [B, k+1] fp32 injected uniforms, or both NULL:
+ *                  Philox4x32-10, key = seed, counter = (position, row, purpose, offset)
+ *   temperature <= 0 selects the greedy rule; top_k <= 0 disables top-k
+ *   out_len_dev   [B] int32 number of accepted draft tokens
+ *   out_tokens_dev[B, k+1] int64 committed tokens, padded with -1
+ * k may be 0 (plain sampling of one token per row from p). */
+int32_t vn_accept(vn_ctx* ctx, const float* p_logits_dev, const float* q_logits_dev,
+                  const int64_t* draft_dev, const float* u_accept_dev, const float* u_sample_dev,
+                  uint64_t seed, uint32_t offset, float temperature, int32_t top_k, int32_t bonus,
+                  int32_t B, int32_t k, int32_t V, int32_t* out_len_dev, int64_t* out_tokens_dev);
+/* Same rule on rows that are not contiguous: row (b, i) of p starts at
+ * p_logits_dev + b * p_stride_b + i * p_stride_i (strides in elements), likewise q.
+ * Lets the logits of [context, draft] (speculative.py:202-213) be used in place. */
+int32_t vn_accept_strided(vn_ctx* ctx, const float* p_logits_dev, int64_t p_stride_b, int64_t p_stride_i,
+                          const float* q_logits_dev, int64_t q_stride_b, int64_t q_stride_i,
+                          const int64_t* draft_dev, const float* u_accept_dev, const float* u_sample_dev,
+                          uint64_t seed, uint32_t offset, float temperature, int32_t top_k, int32_t bonus,
+                          int32_t B, int32_t k, int32_t V, int32_t* out_len_dev, int64_t* out_tokens_dev);
+/* Philox uniforms exactly as vn_accept draws them (for tests) */
+int32_t vn_philox_uniform(vn_ctx* ctx, uint64_t seed, uint32_t offset, int32_t B, int32_t n,
+                          int32_t purpose, float* out_dev);
+
+/* ---- target / draft model (verse_nex/cometspark.py:294-698) ------------ */
+/* config_json: the keyword arguments of CometSparkNexLM.__init__ (cometspark.py:334-364)
+ * plus "embedding_scale" (spark/src/base_model.py:161) and "dtype": "f32" | "bf16". */
+int32_t vn_model_create(vn_ctx* ctx, const char* config_json, vn_model** out);
+int32_t vn_model_destroy(vn_model* m);
+/* name: dotted state_dict name (verse_torch/vnnn.py:235-252); data: host fp32, C order */
+int32_t vn_model_load_tensor(vn_model* m, const char* name, const float* data,
+                             int32_t ndim, const int64_t* shape);
+/* checks that every tensor arrived, precomputes sink K/V and the RoPE table */
+int32_t vn_model_finalize(vn_model* m);
+/* weight-only quantisation of every Linear: "int8" (per output channel,
+ * quantize.py:187-214), "int4" (per output channel, :231-258), "int4g128" */
+int32_t vn_model_quantize(vn_model* m, const char* scheme);
+int32_t vn_model_param_bytes(vn_model* m, uint64_t* out);
+
+/* KV cache: per layer K and V of shape [max_batch, max_seq, n_kv_head, head_dim]
+ * with per-sequence lengths (verse_nex/kv_cache_parallel.py:42-283). */
+int32_t vn_kv_create(vn_model* m, int32_t max_batch, int32_t max_seq, vn_kv** out);
+int32_t vn_kv_destroy(vn_kv* kv);
+int32_t vn_kv_reset_seq(vn_kv* kv, int32_t seq);          /* seq < 0: all */
+int32_t vn_kv_lengths(vn_kv* kv, int32_t* out_host);      /* [max_batch] */
+int32_t vn_kv_set_lengths(vn_kv* kv, const int32_t* lens_host);
+/* Commit / roll back the entries appended by the last forward of `n_new`
+ * positions: sequence b keeps slots keep_idx[b*stride .. +n_keep[b]) (slot
+ * numbers 0..n_new-1, ascending), compacted in place behind its committed
+ * prefix; everything else appended is dropped.  keep_idx_dev == NULL keeps
+ * the first n_keep[b] slots (chain proposals). */
+int32_t vn_kv_commit(vn_kv* kv, int32_t n_new, const int32_t* keep_idx_dev, int32_t stride,
+                     const int32_t* n_keep_dev);
+int32_t vn_kv_read(vn_kv* kv, int32_t layer, int32_t seq, int32_t which /*0=k 1=v*/, float* out_host,
+                   int32_t n_positions);
+
+/* One forward over T new positions per sequence on top of the cache.
+ *   tokens_dev [B, T] int64; parents_host [T] int32 tree parents (-1 = child of the last
+ *   committed token) or NULL for a chain.  Appends K/V at slots len[b] .. len[b]+T-1
+ *   and advances nothing: call vn_kv_commit to make them permanent.
+ *   out_hidden_dev [B, T, dim] fp32 or NULL; out_logits_dev [B, T, V] fp32 or NULL;
+ *   last_only != 0: logits / hidden of the last position only ([B, 1, ...]). */
+int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int32_t B, int32_t T,
+                         const int32_t* parents_host, float* out_hidden_dev, float* out_logits_dev,
+                         int32_t last_only);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VN_B200_H */

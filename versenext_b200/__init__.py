@@ -1,0 +1,21 @@
+"""B200 (sm_100a) implementation of VerseNext's speculative-decoding path.
+
+Public surface (names follow the reference):
+  SpeculativeDecoder                      verse_nex/speculative.py:55
+  get_backend / clear_backend_cache,
+  DeviceBackend, B200Backend              verse_torch/device.py:219-389
+  Context, DeviceArray                    device memory (plays torch.Tensor's role, tensor.py:394)
+  sampling.accept / sample / argmax       acceptance and sampling kernels
+
+Everything computes in libvn_b200.so; importing this package does not need a
+GPU, calling it does.
+"""
+
+from . import _lib
+from .device import Context, DeviceArray, as_device
+from .backend import DeviceBackend, B200Backend, get_backend, clear_backend_cache
+from .speculative import SpeculativeDecoder, Tensor
+from . import sampling
+
+__all__ = ["Context", "DeviceArray", "as_device", "DeviceBackend", "B200Backend", "get_backend",
+           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "sampling"]

@@ -1,0 +1,716 @@
+// Acceptance / rejection sampling over the vocabulary (HBM-streaming kernels).
+//
+// Full-vocabulary path (top_k <= 0), four launches on the context's stream:
+//   accept_stats_kernel     every logit read once: per (row, 4096-float chunk) max / argmax /
+//                           sum exp(x - chunk max)                     [the HBM-bound kernel]
+//   accept_decide_kernel    per sequence: combine chunks, test u*q(x) < p(x), find the first
+//                           rejected position
+//   accept_residual_kernel  per (sequence, chunk): mass of max(0, p - q) of the ONE row pair
+//                           that has to be resampled (or of p_k for the bonus token)
+//   accept_pick_kernel      per sequence: inverse CDF over chunk masses, then inside one chunk
+// Element-wise exponentials are float32; every sum, normalisation and CDF is float64, so a
+// different summation order cannot move a decision relative to the CPU restatement.
+//
+// Top-k path: accept_topk_kernel reduces every row to its (token, scaled logit) list of the
+// entries >= the k-th largest value (radix select on order-preserving keys), then
+// accept_topk_decide_kernel applies the same rule on those short lists.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+constexpr int CHUNK = 4096;
+constexpr int STATS_THREADS = 256;
+constexpr int MAX_K = 16;            // draft positions per call
+constexpr int KEEP_MAX = 1024;       // kept entries per row on the top-k path
+constexpr int CAND_MAX = 1024;       // candidates gathered before the in-shared-memory select
+
+struct RowSet {
+  const float* p;
+  const float* q;
+  long long p_sb, p_si, q_sb, q_si;  // strides in elements
+  int np, nq;                        // rows per sequence taken from p / q
+  int V;
+};
+
+__device__ __forceinline__ const float* row_ptr(const RowSet& rs, int b, int j) {
+  return j < rs.np ? rs.p + (long long)b * rs.p_sb + (long long)j * rs.p_si
+                   : rs.q + (long long)b * rs.q_sb + (long long)(j - rs.np) * rs.q_si;
+}
+
+struct Partial {
+  float m;
+  int arg;
+  double s;
+};
+
+struct Decision {
+  int n_acc;     // accepted draft tokens
+  int mode;      // 0 nothing to sample, 1 residual of (p_n, q_n), 2 plain p_n (bonus / fallback), 3 p_n with draft token removed
+  int pos;       // row index n of the distribution to sample
+  int x;         // draft token at pos (mode 3)
+  float m_p, m_q;
+  double inv_sp, inv_sq;
+  float u;       // uniform for the inverse CDF
+};
+
+// ---- Philox4x32-10 -------------------------------------------------------
+__device__ __forceinline__ uint32_t philox_word0(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                                 uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return c0;
+}
+
+__device__ __forceinline__ float philox_uniform(uint64_t seed, uint32_t offset, uint32_t row,
+                                                uint32_t position, uint32_t purpose) {
+  uint32_t w = philox_word0(position, row, purpose, offset, (uint32_t)seed, (uint32_t)(seed >> 32));
+  return (float)(w >> 8) * 5.9604644775390625e-08f;  // 2^-24
+}
+
+__global__ void philox_uniform_kernel(uint64_t seed, uint32_t offset, int B, int n, int purpose, float* out) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < B * n) out[i] = philox_uniform(seed, offset, i / n, i % n, purpose);
+}
+
+// ---- block reductions -----------------------------------------------------
+__device__ __forceinline__ void warp_argmax(float& m, int& a) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float om = __shfl_xor_sync(0xffffffffu, m, o);
+    int oa = __shfl_xor_sync(0xffffffffu, a, o);
+    if (om > m || (om == m && oa < a)) { m = om; a = oa; }
+  }
+}
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---- kernel A: streaming statistics ---------------------------------------
+// One work item = 4096 consecutive logits of one row; 256 threads x 4 x float4.
+template <bool VEC4>
+__global__ void __launch_bounds__(STATS_THREADS)
+accept_stats_kernel(RowSet rs, int B, int nchunks, float temp, int greedy, Partial* __restrict__ out) {
+  __shared__ float sm_m[STATS_THREADS / 32];
+  __shared__ int sm_a[STATS_THREADS / 32];
+  __shared__ double sm_s[STATS_THREADS / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rows_per_seq = rs.np + rs.nq;
+  const long long nitems = (long long)B * rows_per_seq * nchunks;
+  const bool scale = (temp != 1.0f) && !greedy;
+  for (long long item = blockIdx.x; item < nitems; item += gridDim.x) {
+    const int c = (int)(item % nchunks);
+    const int r = (int)(item / nchunks);
+    const float* row = row_ptr(rs, r / rows_per_seq, r % rows_per_seq);
+    const int start = c * CHUNK;
+    float x[16];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = start + u * (STATS_THREADS * 4) + tid * 4;
+      if (VEC4 && idx + 3 < rs.V) {
+        float4 v = __ldcs(reinterpret_cast<const float4*>(row + idx));
+        x[u * 4 + 0] = v.x; x[u * 4 + 1] = v.y; x[u * 4 + 2] = v.z; x[u * 4 + 3] = v.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[u * 4 + e] = (idx + e < rs.V) ? __ldcs(row + idx + e) : -CUDART_INF_F;
+      }
+    }
+    if (scale) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) x[e] = __fdiv_rn(x[e], temp);
+    }
+    float m = -CUDART_INF_F;
+    int a = 0x7fffffff;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int idx = start + u * (STATS_THREADS * 4) + tid * 4 + e;
+        if (x[u * 4 + e] > m) { m = x[u * 4 + e]; a = idx; }
+      }
+    warp_argmax(m, a);
+    if (lane == 0) { sm_m[warp] = m; sm_a[warp] = a; }
+    __syncthreads();
+    m = sm_m[0]; a = sm_a[0];
+#pragma unroll
+    for (int w = 1; w < STATS_THREADS / 32; ++w) {
+      float om = sm_m[w]; int oa = sm_a[w];
+      if (om > m || (om == m && oa < a)) { m = om; a = oa; }
+    }
+    double s = 0.0;
+    if (!greedy) {
+      float sf = 0.f;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) sf += expf(x[e] - m);
+      s = warp_sum((double)sf);
+      if (lane == 0) sm_s[warp] = s;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      double tot = 0.0;
+      if (!greedy)
+#pragma unroll
+        for (int w = 0; w < STATS_THREADS / 32; ++w) tot += sm_s[w];
+      Partial p; p.m = m; p.arg = a; p.s = tot;
+      out[item] = p;
+    }
+  }
+}
+
+// ---- kernel B: per-sequence decision --------------------------------------
+__device__ __forceinline__ float scaled(float x, float temp) { return temp != 1.0f ? __fdiv_rn(x, temp) : x; }
+
+__global__ void accept_decide_kernel(RowSet rs, int B, int k, int nchunks, const Partial* __restrict__ part,
+                                     const long long* __restrict__ draft, const float* __restrict__ u_acc,
+                                     const float* __restrict__ u_smp, uint64_t seed, uint32_t offset,
+                                     float temp, int greedy, int bonus, Decision* __restrict__ dec,
+                                     int* __restrict__ out_len, long long* __restrict__ out_tok) {
+  const int b = blockIdx.x;
+  const int rows_per_seq = rs.np + rs.nq;
+  __shared__ float r_m[2 * MAX_K + 1];
+  __shared__ int r_a[2 * MAX_K + 1];
+  __shared__ double r_s[2 * MAX_K + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int j = warp; j < rows_per_seq; j += nwarps) {
+    const Partial* pp = part + ((long long)b * rows_per_seq + j) * nchunks;
+    float m = -CUDART_INF_F; int a = 0x7fffffff;
+    for (int c = lane; c < nchunks; c += 32) {
+      Partial p = pp[c];
+      if (p.m > m || (p.m == m && p.arg < a)) { m = p.m; a = p.arg; }
+    }
+    warp_argmax(m, a);
+    double s = 0.0;
+    if (!greedy)
+      for (int c = lane; c < nchunks; c += 32) {
+        Partial p = pp[c];
+        s += p.s * exp((double)(p.m - m));
+      }
+    s = warp_sum(s);
+    if (lane == 0) { r_m[j] = m; r_a[j] = a; r_s[j] = s; }
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  Decision d;
+  d.mode = 0; d.pos = 0; d.x = -1; d.m_p = d.m_q = 0.f; d.inv_sp = d.inv_sq = 0.0; d.u = 0.f;
+  long long* tok = out_tok + (long long)b * (k + 1);
+  for (int i = 0; i <= k; ++i) tok[i] = -1;
+  int n = 0;
+  if (greedy) {
+    while (n < k && draft[(long long)b * k + n] == (long long)r_a[n]) { tok[n] = r_a[n]; ++n; }
+    if (n < k) tok[n] = r_a[n];
+    else if (bonus) tok[k] = r_a[k];
+    d.n_acc = n;
+    out_len[b] = n;
+    dec[b] = d;
+    return;
+  }
+  bool rejected = false;
+  for (; n < k; ++n) {
+    const long long x = draft[(long long)b * k + n];
+    const bool x_ok = x >= 0 && x < rs.V;
+    const float lp = x_ok ? scaled(row_ptr(rs, b, n)[x], temp) : -CUDART_INF_F;
+    const double p = (double)expf(lp - r_m[n]) / r_s[n];
+    double q = 1.0;
+    if (rs.nq) {
+      const float lq = x_ok ? scaled(row_ptr(rs, b, rs.np + n)[x], temp) : -CUDART_INF_F;
+      q = (double)expf(lq - r_m[rs.np + n]) / r_s[rs.np + n];
+    }
+    const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, n, 0);
+    if ((double)u * q < p) { tok[n] = x; continue; }
+    rejected = true;
+    d.mode = rs.nq ? 1 : 3;
+    d.pos = n;
+    d.x = (int)x;
+    d.m_p = r_m[n]; d.inv_sp = 1.0 / r_s[n];
+    if (rs.nq) { d.m_q = r_m[rs.np + n]; d.inv_sq = 1.0 / r_s[rs.np + n]; }
+    break;
+  }
+  if (!rejected && bonus) {
+    d.mode = 2; d.pos = k; d.m_p = r_m[k]; d.inv_sp = 1.0 / r_s[k];
+  }
+  if (d.mode) d.u = u_smp ? u_smp[(long long)b * (k + 1) + d.pos] : philox_uniform(seed, offset, b, d.pos, 1);
+  d.n_acc = n;
+  out_len[b] = n;
+  dec[b] = d;
+}
+
+// residual weight of one token under decision d (double)
+__device__ __forceinline__ double residual_weight(const Decision& d, float xp, float xq, int token, bool plain) {
+  double p = (double)expf(xp - d.m_p) * d.inv_sp;
+  if (plain || d.mode == 2) return p;
+  if (d.mode == 3) return token == d.x ? 0.0 : p;
+  double q = (double)expf(xq - d.m_q) * d.inv_sq;
+  double r = p - q;
+  return r > 0.0 ? r : 0.0;
+}
+
+// ---- kernel C: residual mass per (sequence, chunk) ------------------------
+// mass[b][c][0] = sum of max(0, p - q), mass[b][c][1] = sum of p (fallback when the residual vanishes)
+template <bool VEC4>
+__global__ void __launch_bounds__(STATS_THREADS)
+accept_residual_kernel(RowSet rs, int nchunks, float temp, const Decision* __restrict__ dec,
+                       double* __restrict__ mass) {
+  const int b = blockIdx.y, c = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const Decision d = dec[b];
+  if (d.mode == 0) return;
+  __shared__ double sm[2][STATS_THREADS / 32];
+  const float* rp = row_ptr(rs, b, d.pos);
+  const float* rq = d.mode == 1 ? row_ptr(rs, b, rs.np + d.pos) : nullptr;
+  const bool scale = temp != 1.0f;
+  double acc_r = 0.0, acc_p = 0.0;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int idx = c * CHUNK + u * (STATS_THREADS * 4) + tid * 4;
+    float xp[4], xq[4] = {0.f, 0.f, 0.f, 0.f};
+    if (VEC4 && idx + 3 < rs.V) {
+      float4 v = *reinterpret_cast<const float4*>(rp + idx);
+      xp[0] = v.x; xp[1] = v.y; xp[2] = v.z; xp[3] = v.w;
+      if (rq) { float4 w = *reinterpret_cast<const float4*>(rq + idx); xq[0] = w.x; xq[1] = w.y; xq[2] = w.z; xq[3] = w.w; }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        xp[e] = idx + e < rs.V ? rp[idx + e] : -CUDART_INF_F;
+        if (rq) xq[e] = idx + e < rs.V ? rq[idx + e] : -CUDART_INF_F;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (idx + e >= rs.V) continue;
+      const float a = scale ? __fdiv_rn(xp[e], temp) : xp[e];
+      const double p = (double)expf(a - d.m_p) * d.inv_sp;
+      double r = p;
+      if (d.mode == 1) {
+        const float qs = scale ? __fdiv_rn(xq[e], temp) : xq[e];
+        r = p - (double)expf(qs - d.m_q) * d.inv_sq;
+        r = r > 0.0 ? r : 0.0;
+      } else if (d.mode == 3 && idx + e == d.x) {
+        r = 0.0;
+      }
+      acc_r += r;
+      acc_p += p;
+    }
+  }
+  acc_r = warp_sum(acc_r);
+  acc_p = warp_sum(acc_p);
+  if (lane == 0) { sm[0][warp] = acc_r; sm[1][warp] = acc_p; }
+  __syncthreads();
+  if (tid == 0) {
+    double r = 0.0, p = 0.0;
+#pragma unroll
+    for (int w = 0; w < STATS_THREADS / 32; ++w) { r += sm[0][w]; p += sm[1][w]; }
+    mass[((long long)b * nchunks + c) * 2 + 0] = r;
+    mass[((long long)b * nchunks + c) * 2 + 1] = p;
+  }
+}
+
+// ---- kernel D: inverse CDF ------------------------------------------------
+__global__ void __launch_bounds__(STATS_THREADS)
+accept_pick_kernel(RowSet rs, int k, int nchunks, float temp, const Decision* __restrict__ dec,
+                   const double* __restrict__ mass, long long* __restrict__ out_tok) {
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const Decision d = dec[b];
+  if (d.mode == 0) return;
+  __shared__ int s_chunk, s_plain, s_thread;
+  __shared__ double s_before, s_target;
+  __shared__ double s_part[STATS_THREADS];
+  const double* mb = mass + (long long)b * nchunks * 2;
+  if (tid == 0) {
+    double Z = 0.0;
+    for (int c = 0; c < nchunks; ++c) Z += mb[c * 2];
+    int plain = 0;
+    if (!(Z > 0.0)) {  // residual vanished: fall back to p itself
+      plain = 1; Z = 0.0;
+      for (int c = 0; c < nchunks; ++c) Z += mb[c * 2 + 1];
+    }
+    const double target = (double)d.u * Z;
+    double cum = 0.0; int chosen = -1; double before = 0.0; int last_nz = 0;
+    for (int c = 0; c < nchunks; ++c) {
+      const double w = mb[c * 2 + plain];
+      if (w > 0.0) last_nz = c;
+      if (chosen < 0 && cum + w > target) { chosen = c; before = cum; }
+      cum += w;
+    }
+    if (chosen < 0) {  // rounding pushed the target past the total: last token that has weight
+      chosen = last_nz; before = 0.0;
+      for (int c = 0; c < last_nz; ++c) before += mb[c * 2 + plain];
+    }
+    s_chunk = chosen; s_plain = plain; s_before = before; s_target = target;
+  }
+  __syncthreads();
+  const int c = s_chunk; const bool plain = s_plain != 0;
+  const float* rp = row_ptr(rs, b, d.pos);
+  const float* rq = d.mode == 1 ? row_ptr(rs, b, rs.np + d.pos) : nullptr;
+  const bool scale = temp != 1.0f;
+  // thread t owns 16 consecutive tokens so that the scan order is ascending token id
+  double w[16];
+  double local = 0.0;
+  const int base = c * CHUNK + tid * 16;
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const int t = base + e;
+    double v = 0.0;
+    if (t < rs.V) {
+      float a = scale ? __fdiv_rn(rp[t], temp) : rp[t];
+      float q = rq ? (scale ? __fdiv_rn(rq[t], temp) : rq[t]) : 0.f;
+      v = residual_weight(d, a, q, t, plain);
+    }
+    w[e] = v;
+    local += v;
+  }
+  s_part[tid] = local;
+  __syncthreads();
+  if (tid == 0) {
+    double cum = s_before; int chosen = -1; int last_nz = -1;
+    for (int t = 0; t < STATS_THREADS; ++t) {
+      if (s_part[t] > 0.0) last_nz = t;
+      if (chosen < 0 && cum + s_part[t] > s_target) { chosen = t; s_before = cum; }
+      cum += s_part[t];
+    }
+    if (chosen < 0) { chosen = last_nz < 0 ? 0 : last_nz; s_before = -1.0; }
+    s_thread = chosen;
+  }
+  __syncthreads();
+  if (tid == s_thread) {
+    int pick = -1, last_nz = -1;
+    if (s_before >= 0.0) {
+      double cum = s_before;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        if (w[e] > 0.0) last_nz = e;
+        if (pick < 0 && cum + w[e] > s_target) pick = e;
+        cum += w[e];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) if (w[e] > 0.0) last_nz = e;
+    }
+    if (pick < 0) pick = last_nz < 0 ? 0 : last_nz;
+    out_tok[(long long)b * (k + 1) + d.n_acc] = base + pick;
+  }
+}
+
+// ---- top-k path -----------------------------------------------------------
+__device__ __forceinline__ uint32_t order_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+struct TopkRow {
+  int n;                 // kept entries
+  int overflow;          // 1 when ties at the threshold did not fit
+  int tok[KEEP_MAX];     // ascending token id
+  float val[KEEP_MAX];   // scaled logit
+};
+
+// One CTA per row.  Radix select (11 + 11 + 10 bits) of the k-th largest key.  After each level
+// the number of keys that can still be kept is known from the histogram; as soon as they fit in
+// shared memory they are gathered (one more read of the row) and the select finishes there.
+__global__ void __launch_bounds__(1024)
+accept_topk_kernel(RowSet rs, int top_k, float temp, TopkRow* __restrict__ out) {
+  const int rows_per_seq = rs.np + rs.nq;
+  const int r = blockIdx.x;
+  const float* row = row_ptr(rs, r / rows_per_seq, r % rows_per_seq);
+  const int V = rs.V, tid = threadIdx.x, nt = blockDim.x;
+  const bool scale = temp != 1.0f;
+  const int want = top_k < V ? top_k : V;
+  __shared__ uint32_t hist[2048];
+  __shared__ uint32_t c_key[CAND_MAX];
+  __shared__ int c_tok[CAND_MAX];
+  __shared__ int wcount[32];
+  __shared__ uint32_t s_prefix, s_mask, s_kth;
+  __shared__ int s_need, s_ncand, s_done, s_nout, s_base;
+  if (tid == 0) { s_prefix = 0; s_mask = 0; s_need = want; s_ncand = 0; s_done = 0; s_nout = 0; s_base = 0; s_kth = 0; }
+  __syncthreads();
+  for (int level = 0; level < 3; ++level) {
+    const int sh = level == 0 ? 21 : (level == 1 ? 10 : 0);
+    const uint32_t nb = level == 2 ? 1024u : 2048u;
+    for (int i = tid; i < 2048; i += nt) hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix, mask = s_mask;
+    for (int i = tid; i < V; i += nt) {
+      float x = row[i];
+      if (scale) x = __fdiv_rn(x, temp);
+      const uint32_t key = order_key(x);
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> sh) & (nb - 1)], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const int need = s_need;  // how many of the largest keys of this prefix class are kept
+      uint32_t digit = 0; int above = 0;
+      for (int d = (int)nb - 1; d >= 0; --d) {
+        if (above + (int)hist[d] >= need) { digit = (uint32_t)d; break; }
+        above += hist[d];
+      }
+      s_need = need - above;                 // still needed from inside the digit class
+      s_prefix = prefix | (digit << sh);
+      s_mask = mask | ((nb - 1) << sh);
+      const int ncand = want - s_need + (int)hist[digit];  // keys >= the smallest key of the class
+      s_ncand = ncand;
+      s_done = ncand <= CAND_MAX ? 2 : (level == 2 ? 1 : 0);
+    }
+    __syncthreads();
+    if (s_done) break;
+  }
+  TopkRow* o = out + r;
+  if (s_done == 2) {
+    const uint32_t lo = s_prefix;
+    __syncthreads();
+    if (tid == 0) s_ncand = 0;
+    __syncthreads();
+    for (int i = tid; i < V; i += nt) {
+      float x = row[i];
+      if (scale) x = __fdiv_rn(x, temp);
+      const uint32_t key = order_key(x);
+      if (key >= lo) {
+        int slot = atomicAdd(&s_ncand, 1);
+        if (slot < CAND_MAX) { c_key[slot] = key; c_tok[slot] = i; }
+      }
+    }
+    __syncthreads();
+    const int nc = min(s_ncand, CAND_MAX);
+    // exact k-th largest among the candidates by rank counting (nc is small)
+    for (int i = tid; i < nc; i += nt) {
+      const uint32_t ki = c_key[i];
+      int greater = 0, geq = 0;
+      for (int j = 0; j < nc; ++j) { greater += c_key[j] > ki; geq += c_key[j] >= ki; }
+      if (greater < want && geq >= want) s_kth = ki;  // every writer holds the same key
+    }
+    __syncthreads();
+    const uint32_t kth = s_kth;
+    for (int i = tid; i < nc; i += nt)
+      if (c_key[i] >= kth) {
+        int pos = 0;  // kept candidates with a smaller token id: output is ascending in id
+        for (int j = 0; j < nc; ++j) pos += (c_key[j] >= kth) && (c_tok[j] < c_tok[i]);
+        if (pos < KEEP_MAX) { o->tok[pos] = c_tok[i]; o->val[pos] = key_value(c_key[i]); }
+        atomicAdd(&s_nout, 1);
+      }
+    __syncthreads();
+    if (tid == 0) { o->n = min(s_nout, KEEP_MAX); o->overflow = s_nout > KEEP_MAX; }
+  } else {
+    // every bit resolved and still too many ties at the threshold: stream the kept entries
+    // out in id order, truncated to KEEP_MAX (overflow flag set)
+    const uint32_t kth = s_prefix;
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int start = 0; start < V; start += nt) {
+      const int i = start + tid;
+      bool keep = false; uint32_t key = 0;
+      if (i < V) {
+        float x = row[i];
+        if (scale) x = __fdiv_rn(x, temp);
+        key = order_key(x);
+        keep = key >= kth;
+      }
+      const unsigned bal = __ballot_sync(0xffffffffu, keep);
+      if (lane == 0) wcount[warp] = __popc(bal);
+      __syncthreads();
+      int off = s_base;
+      for (int w = 0; w < warp; ++w) off += wcount[w];
+      off += __popc(bal & ((1u << lane) - 1));
+      if (keep && off < KEEP_MAX) { o->tok[off] = i; o->val[off] = key_value(key); }
+      __syncthreads();
+      if (tid == 0) { int tot = 0; for (int w = 0; w < (nt >> 5); ++w) tot += wcount[w]; s_base += tot; }
+      __syncthreads();
+    }
+    if (tid == 0) { o->n = min(s_base, KEEP_MAX); o->overflow = s_base > KEEP_MAX; }
+  }
+}
+
+__device__ int list_find(const TopkRow& r, int token) {
+  int lo = 0, hi = r.n - 1;
+  while (lo <= hi) {
+    int mid = (lo + hi) >> 1;
+    if (r.tok[mid] == token) return mid;
+    if (r.tok[mid] < token) lo = mid + 1; else hi = mid - 1;
+  }
+  return -1;
+}
+
+// One CTA per sequence, the work is a few hundred operations: thread 0 walks the lists.
+__global__ void accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restrict__ rows,
+                                          const long long* __restrict__ draft, const float* __restrict__ u_acc,
+                                          const float* __restrict__ u_smp, uint64_t seed, uint32_t offset,
+                                          int bonus, int* __restrict__ out_len, long long* __restrict__ out_tok) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const int rows_per_seq = np + nq;
+  const TopkRow* rb = rows + (long long)b * rows_per_seq;
+  long long* tok = out_tok + (long long)b * (k + 1);
+  for (int i = 0; i <= k; ++i) tok[i] = -1;
+  auto stats = [](const TopkRow& r, float& m, double& s) {
+    m = -CUDART_INF_F;
+    for (int i = 0; i < r.n; ++i) m = fmaxf(m, r.val[i]);
+    s = 0.0;
+    for (int i = 0; i < r.n; ++i) s += (double)expf(r.val[i] - m);
+  };
+  int n = 0;
+  int sample_row = -1, q_row = -1, removed = -1;
+  for (; n < k; ++n) {
+    const int x = (int)draft[(long long)b * k + n];
+    const TopkRow& P = rb[n];
+    float mp; double sp; stats(P, mp, sp);
+    int ip = list_find(P, x);
+    double p = ip >= 0 ? (double)expf(P.val[ip] - mp) / sp : 0.0;
+    double q = 1.0;
+    if (nq) {
+      const TopkRow& Q = rb[np + n];
+      float mq; double sq; stats(Q, mq, sq);
+      int iq = list_find(Q, x);
+      q = iq >= 0 ? (double)expf(Q.val[iq] - mq) / sq : 0.0;
+    }
+    const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, n, 0);
+    if ((double)u * q < p) { tok[n] = x; continue; }
+    sample_row = n;
+    if (nq) q_row = np + n; else removed = x;
+    break;
+  }
+  out_len[b] = n;
+  if (sample_row < 0) {
+    if (!bonus) return;
+    sample_row = k;
+  }
+  const TopkRow& P = rb[sample_row];
+  float mp; double sp; stats(P, mp, sp);
+  float mq = 0.f; double sq = 1.0;
+  if (q_row >= 0) stats(rb[q_row], mq, sq);
+  const float u = u_smp ? u_smp[(long long)b * (k + 1) + sample_row] : philox_uniform(seed, offset, b, sample_row, 1);
+  for (int pass = 0; pass < 2; ++pass) {
+    // pass 0: residual; pass 1 (only when it vanished): p itself
+    double Z = 0.0;
+    auto weight = [&](int i) {
+      double p = (double)expf(P.val[i] - mp) / sp;
+      if (pass == 1) return p;
+      if (q_row >= 0) {
+        int iq = list_find(rb[q_row], P.tok[i]);
+        double q = iq >= 0 ? (double)expf(rb[q_row].val[iq] - mq) / sq : 0.0;
+        double r = p - q;
+        return r > 0.0 ? r : 0.0;
+      }
+      return P.tok[i] == removed ? 0.0 : p;
+    };
+    for (int i = 0; i < P.n; ++i) Z += weight(i);
+    if (!(Z > 0.0)) continue;
+    const double target = (double)u * Z;
+    double cum = 0.0; int pick = -1, last_nz = -1;
+    for (int i = 0; i < P.n; ++i) {
+      double w = weight(i);
+      if (w > 0.0) last_nz = i;
+      cum += w;
+      if (cum > target) { pick = i; break; }
+    }
+    if (pick < 0) pick = last_nz;
+    tok[n] = P.tok[pick];
+    return;
+  }
+}
+
+}  // namespace
+
+static int32_t accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_si,
+                           const float* q, long long q_sb, long long q_si, const int64_t* draft,
+                           const float* u_acc, const float* u_smp, uint64_t seed, uint32_t offset,
+                           float temperature, int32_t top_k, int32_t bonus, int32_t B, int32_t k, int32_t V,
+                           int32_t* out_len, int64_t* out_tok) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, B >= 0 && k >= 0 && k <= MAX_K && V >= 1, "bad sizes B=%d k=%d V=%d (k <= %d)", B, k, V, MAX_K);
+  VN_REQUIRE(ctx, p && out_len && out_tok, "null pointer");
+  VN_REQUIRE(ctx, k == 0 || draft, "draft tokens missing");
+  VN_REQUIRE(ctx, (u_acc == nullptr) == (u_smp == nullptr) || k == 0, "inject both uniform arrays or neither");
+  VN_REQUIRE(ctx, bonus || k > 0, "nothing to do: k == 0 without a bonus token");
+  if (B == 0) return VN_OK;
+  const bool greedy = temperature <= 0.f;
+  const float temp = greedy ? 1.0f : fmaxf(temperature, 1e-8f);
+  RowSet rs;
+  rs.p = p; rs.q = greedy ? nullptr : q;
+  rs.p_sb = p_sb; rs.p_si = p_si; rs.q_sb = q_sb; rs.q_si = q_si;
+  rs.np = bonus ? k + 1 : k;
+  rs.nq = (rs.q && k > 0) ? k : 0;
+  rs.V = V;
+  const int rows_per_seq = rs.np + rs.nq;
+  const long long* d64 = reinterpret_cast<const long long*>(draft);
+  long long* o64 = reinterpret_cast<long long*>(out_tok);
+
+  if (!greedy && top_k > 0 && top_k < V) {
+    VN_REQUIRE(ctx, top_k <= KEEP_MAX, "top_k %d above the supported maximum %d", top_k, KEEP_MAX);
+    void* ws;
+    int32_t st = vn_workspace(ctx, sizeof(TopkRow) * (size_t)B * rows_per_seq, &ws);
+    if (st) return st;
+    TopkRow* rows = (TopkRow*)ws;
+    VN_LAUNCH(ctx, accept_topk_kernel, B * rows_per_seq, 1024, 0, rs, top_k, temp, rows);
+    VN_LAUNCH(ctx, accept_topk_decide_kernel, ceil_div(B, 32), 32, 0, B, k, rs.np, rs.nq, rows, d64, u_acc, u_smp,
+              seed, offset, bonus, out_len, o64);
+    return VN_OK;
+  }
+
+  const int nchunks = ceil_div(V, CHUNK);
+  const size_t n_part = (size_t)B * rows_per_seq * nchunks;
+  const size_t off_dec = (n_part * sizeof(Partial) + 255) & ~(size_t)255;
+  const size_t off_mass = (off_dec + (size_t)B * sizeof(Decision) + 255) & ~(size_t)255;
+  const size_t total = off_mass + (size_t)B * nchunks * 2 * sizeof(double);
+  void* ws;
+  int32_t st = vn_workspace(ctx, total, &ws);
+  if (st) return st;
+  Partial* part = (Partial*)ws;
+  Decision* dec = (Decision*)((char*)ws + off_dec);
+  double* mass = (double*)((char*)ws + off_mass);
+
+  auto aligned16 = [](const void* ptr) { return ((uintptr_t)ptr & 15) == 0; };
+  const bool vec = (V % 4 == 0) && aligned16(p) && (p_sb % 4 == 0) && (p_si % 4 == 0) &&
+                   (!rs.nq || (aligned16(q) && (q_sb % 4 == 0) && (q_si % 4 == 0)));
+  const long long nitems = (long long)n_part;
+  const int grid = (int)std::min<long long>(nitems, (long long)ctx->sm_count * 8);
+  if (vec) VN_LAUNCH(ctx, accept_stats_kernel<true>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
+  else     VN_LAUNCH(ctx, accept_stats_kernel<false>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
+  VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_acc, u_smp, seed, offset, temp,
+            (int)greedy, bonus, dec, out_len, o64);
+  if (!greedy) {
+    dim3 g(nchunks, B);
+    if (vec) VN_LAUNCH(ctx, accept_residual_kernel<true>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);
+    else     VN_LAUNCH(ctx, accept_residual_kernel<false>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);
+    VN_LAUNCH(ctx, accept_pick_kernel, B, STATS_THREADS, 0, rs, k, nchunks, temp, dec, mass, o64);
+  }
+  return VN_OK;
+}
+
+extern "C" {
+
+int32_t vn_accept(vn_ctx* ctx, const float* p_logits_dev, const float* q_logits_dev, const int64_t* draft_dev,
+                  const float* u_accept_dev, const float* u_sample_dev, uint64_t seed, uint32_t offset,
+                  float temperature, int32_t top_k, int32_t bonus, int32_t B, int32_t k, int32_t V,
+                  int32_t* out_len_dev, int64_t* out_tokens_dev) {
+  const long long np = bonus ? k + 1 : k;
+  return accept_impl(ctx, p_logits_dev, np * V, V, q_logits_dev, (long long)k * V, V, draft_dev, u_accept_dev,
+                     u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev, out_tokens_dev);
+}
+
+int32_t vn_accept_strided(vn_ctx* ctx, const float* p_logits_dev, int64_t p_stride_b, int64_t p_stride_i,
+                          const float* q_logits_dev, int64_t q_stride_b, int64_t q_stride_i,
+                          const int64_t* draft_dev, const float* u_accept_dev, const float* u_sample_dev,
+                          uint64_t seed, uint32_t offset, float temperature, int32_t top_k, int32_t bonus,
+                          int32_t B, int32_t k, int32_t V, int32_t* out_len_dev, int64_t* out_tokens_dev) {
+  return accept_impl(ctx, p_logits_dev, p_stride_b, p_stride_i, q_logits_dev, q_stride_b, q_stride_i, draft_dev,
+                     u_accept_dev, u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev,
+                     out_tokens_dev);
+}
+
+int32_t vn_philox_uniform(vn_ctx* ctx, uint64_t seed, uint32_t offset, int32_t B, int32_t n, int32_t purpose,
+                          float* out_dev) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, B >= 0 && n >= 0 && out_dev, "bad arguments");
+  if (B * n == 0) return VN_OK;
+  VN_LAUNCH(ctx, philox_uniform_kernel, ceil_div(B * n, 256), 256, 0, seed, offset, B, n, purpose, out_dev);
+  return VN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,84 @@
+// Shared host-side plumbing of the library: context, error reporting, launch accounting.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <string>
+#include <vector>
+#include <map>
+#include <mutex>
+
+#include "../../include/vn_b200.h"
+
+struct vn_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  uint64_t launches = 0;
+  // scratch owned by the context, grown on demand (never shrinks)
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  void* flush = nullptr;
+  size_t flush_bytes = 0;
+  int sm_count = 148;
+  // optional per-kernel timing: CUDA events around every launch, summed per kernel name
+  bool profiling = false;
+  struct ProfRec { const char* name; cudaEvent_t a, b; };
+  std::vector<ProfRec> prof;
+};
+
+void vn_prof_begin(vn_ctx* ctx, const char* name);
+void vn_prof_end(vn_ctx* ctx);
+
+extern thread_local std::string g_vn_thread_error;
+
+inline int32_t vn_fail(vn_ctx* ctx, int32_t code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_vn_thread_error = buf;
+  if (ctx) ctx->err = buf;
+  return code;
+}
+
+#define VN_CUDA(ctx, expr)                                                            \
+  do {                                                                                \
+    cudaError_t _e = (expr);                                                          \
+    if (_e != cudaSuccess)                                                            \
+      return vn_fail((ctx), _e == cudaErrorMemoryAllocation ? VN_ERR_OOM : VN_ERR_CUDA, \
+                     "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+  } while (0)
+
+#define VN_CHECK_CTX(ctx)                                             \
+  do {                                                                \
+    if (!(ctx)) return vn_fail(nullptr, VN_ERR_INVALID, "null context"); \
+    cudaError_t _e = cudaSetDevice((ctx)->device);                    \
+    if (_e != cudaSuccess) return vn_fail((ctx), VN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(_e)); \
+  } while (0)
+
+#define VN_REQUIRE(ctx, cond, ...)                                  \
+  do {                                                              \
+    if (!(cond)) return vn_fail((ctx), VN_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+// every kernel launch goes through this so that the context can report how many ran
+#define VN_LAUNCH(ctx, kernel, grid, block, smem, ...)                                  \
+  do {                                                                                  \
+    if ((ctx)->profiling) vn_prof_begin((ctx), #kernel);                                \
+    kernel<<<(grid), (block), (smem), (ctx)->stream>>>(__VA_ARGS__);                    \
+    if ((ctx)->profiling) vn_prof_end((ctx));                                           \
+    (ctx)->launches++;                                                                  \
+    cudaError_t _e = cudaGetLastError();                                                \
+    if (_e != cudaSuccess)                                                              \
+      return vn_fail((ctx), VN_ERR_CUDA, "launch of %s failed: %s", #kernel, cudaGetErrorString(_e)); \
+  } while (0)
+
+int32_t vn_workspace(vn_ctx* ctx, size_t bytes, void** out);
+
+template <typename T>
+static inline T ceil_div(T a, T b) { return (a + b - 1) / b; }
