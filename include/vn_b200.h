@@ -127,6 +127,12 @@ int32_t vn_accept_strided(vn_ctx* ctx, const float* p_logits_dev, int64_t p_stri
                           const int64_t* draft_dev, const float* u_accept_dev, const float* u_sample_dev,
                           uint64_t seed, uint32_t offset, float temperature, int32_t top_k, int32_t bonus,
                           int32_t B, int32_t k, int32_t V, int32_t* out_len_dev, int64_t* out_tokens_dev);
+/* One token per row of logits (row r at logits_dev + r * row_stride): argmax when temperature <= 0,
+ * else inverse-CDF draw from softmax(logits / T) restricted to the top-k (cometspark.py:892-911).
+ * uniforms_dev [R] or NULL: Philox counter (position, row, purpose, offset). */
+int32_t vn_sample(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, float temperature,
+                  int32_t top_k, const float* uniforms_dev, uint64_t seed, uint32_t offset, uint32_t position,
+                  uint32_t purpose, int64_t* out_tokens_dev);
 /* Philox uniforms exactly as vn_accept draws them (for tests) */
 int32_t vn_philox_uniform(vn_ctx* ctx, uint64_t seed, uint32_t offset, int32_t B, int32_t n,
                           int32_t purpose, float* out_dev);
@@ -159,7 +165,7 @@ int32_t vn_kv_set_lengths(vn_kv* kv, const int32_t* lens_host);
  * prefix; everything else appended is dropped.  keep_idx_dev == NULL keeps
  * the first n_keep[b] slots (chain proposals). */
 int32_t vn_kv_commit(vn_kv* kv, int32_t n_new, const int32_t* keep_idx_dev, int32_t stride,
-                     const int32_t* n_keep_dev);
+                     const int32_t* n_keep_dev, int32_t keep_add /* kept = n_keep[b] + keep_add */);
 int32_t vn_kv_read(vn_kv* kv, int32_t layer, int32_t seq, int32_t which /*0=k 1=v*/, float* out_host,
                    int32_t n_positions);
 
@@ -168,10 +174,23 @@ int32_t vn_kv_read(vn_kv* kv, int32_t layer, int32_t seq, int32_t which /*0=k 1=
  *   committed token) or NULL for a chain.  Appends K/V at slots len[b] .. len[b]+T-1
  *   and advances nothing: call vn_kv_commit to make them permanent.
  *   out_hidden_dev [B, T, dim] fp32 or NULL; out_logits_dev [B, T, V] fp32 or NULL;
- *   last_only != 0: logits / hidden of the last position only ([B, 1, ...]). */
+ *   last_only != 0: logits / hidden of the last position only ([B, 1, ...]).
+ *   slot_offset: the new positions start behind `slot_offset` entries that earlier forwards
+ *   appended and that are not committed yet (a draft model proposing token by token). */
 int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int32_t B, int32_t T,
                          const int32_t* parents_host, float* out_hidden_dev, float* out_logits_dev,
-                         int32_t last_only);
+                         int32_t last_only, int32_t slot_offset);
+
+/* ---- round bookkeeping on the device (no counterpart in the reference: its loop is host code,
+ *      speculative.py:280-293) -------------------------------------------------------------------- */
+/* step_tokens_dev [k, B] proposals per draft step, pair_dev [B, 2] last two committed tokens ->
+ * draft_dev [B, k] and verify_dev [B, n_verify] = (last committed, d_0, .., d_{n_verify-2}) */
+int32_t vn_spec_gather(vn_ctx* ctx, const int64_t* step_tokens_dev, const int64_t* pair_dev, int32_t B, int32_t k,
+                       int32_t n_verify, int64_t* draft_dev, int64_t* verify_dev);
+/* fold one round's committed tokens (out_tokens_dev [B, k+1], -1 padded) into pair_dev, the per-request
+ * history_dev [B, cap] / count_dev [B], and n_commit_dev [B] = tokens committed this round */
+int32_t vn_spec_advance(vn_ctx* ctx, const int64_t* out_tokens_dev, int32_t B, int32_t k, int64_t* pair_dev,
+                        int64_t* history_dev, int32_t cap, int32_t* count_dev, int32_t* n_commit_dev);
 
 #ifdef __cplusplus
 }

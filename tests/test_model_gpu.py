@@ -1,0 +1,229 @@
+"""VerseNexLM forward, KV cache, tree verification and the speculative engine on the device,
+against fixtures recorded from the reference and against the CPU oracle."""
+
+import numpy as np
+import pytest
+
+from oracle import model as OM
+from oracle import spec as OS
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b):
+    return float(np.max(np.abs(np.asarray(a, np.float64) - b)) / max(np.max(np.abs(b)), 1e-30))
+
+
+def build(cfg: OM.Config, sd, dtype="f32"):
+    import versenext_b200 as vn
+    kw = cfg.to_dict()
+    kw.pop("init_std")
+    m = vn.VerseNexLM(dtype=dtype, **kw)
+    m.load_state_dict(sd)
+    return m
+
+
+def _sd(g, prefix):
+    return {n[len(prefix):]: g[n] for n in g.files if n.startswith(prefix)}
+
+
+def variant_b():
+    t_cfg = OM.small_config(tie_weights=False, init_std=0.2)
+    d_cfg = OM.small_config(n_layer=1, tie_weights=False, init_std=0.2)
+    t_sd = OM.init_state_dict(t_cfg, seed=101, gate_std=1.0)
+    d_sd = OM.init_state_dict(d_cfg, seed=102, gate_std=1.0)
+    d_sd["tok_emb.weight"], d_sd["head.weight"] = t_sd["tok_emb.weight"], t_sd["head.weight"]
+    for n in list(d_sd):
+        if n.startswith("blocks.0.") and not n.endswith("norm1.weight") and not n.endswith("norm2.weight"):
+            d_sd[n] = (t_sd[n] + 0.15 * d_sd[n]).astype(np.float32)
+    return t_cfg, t_sd, d_cfg, d_sd
+
+
+def mini_cfg(**over):
+    kw = dict(vocab_size=512, dim=64, n_layer=4, n_head=4, n_kv_head=2, window_size=16,
+              num_global_tokens=8, max_seq_len=128, init_std=0.1)
+    kw.update(over)
+    return OM.mate_config(**kw)
+
+
+def test_small_config_logits_and_greedy_stream(golden):
+    """BASELINE config 1 with the reference's own initial weights: logits 1e-3, greedy stream bit-exact."""
+    g = golden("model_small.npz")
+    cfg = OM.small_config()
+    m = build(cfg, _sd(g, "a_t."))
+    lg = m(g["prompt"]).data.numpy()
+    assert rel_err(lg, g["a_logits"]) < 1e-3
+    out = m.generate(g["prompt"], max_new_tokens=128)
+    np.testing.assert_array_equal(out, g["a_greedy"])
+
+
+def test_small_config_speculative_streams(golden):
+    import versenext_b200 as vn
+    g = golden("model_small.npz")
+    t = build(OM.small_config(), _sd(g, "a_t."))
+    d = build(OM.small_config(n_layer=1), _sd(g, "a_d."))
+    eng = vn.SpecEngine(t, d, max_batch=1, max_seq=256, k=4, temperature=0.0, bonus=False, max_new_tokens=160)
+    toks, st = eng.generate(g["prompt"], 128)
+    np.testing.assert_array_equal(toks, g["a_spec"])
+    assert st["rounds"] == int(g["a_rounds"])
+
+
+def test_nondegenerate_variant_matches_reference_streams(golden):
+    """Seeded weights with many rejections: logits, greedy stream, speculative stream, round and accept counts."""
+    import versenext_b200 as vn
+    g = golden("model_small.npz")
+    t_cfg, t_sd, d_cfg, d_sd = variant_b()
+    t, d = build(t_cfg, t_sd), build(d_cfg, d_sd)
+    assert rel_err(t(g["prompt"]).data.numpy(), g["b_logits"]) < 1e-3
+    np.testing.assert_array_equal(t.generate(g["prompt"], max_new_tokens=96), g["b_greedy"])
+    eng = vn.SpecEngine(t, d, max_batch=1, max_seq=256, k=4, temperature=0.0, bonus=False, max_new_tokens=128)
+    eng.prefill(g["prompt"])
+    rounds = accepted = 0
+    while int(eng.counts()[0]) < 96:
+        eng.step()
+        rounds += 1
+        n = int(eng.accept_len.numpy()[0])
+        accepted += n
+    np.testing.assert_array_equal(eng.tokens(96), g["b_spec"][:, 32:])
+    assert rounds == int(g["b_rounds"]) and accepted == int(g["b_accepted"])
+    # with the bonus token the stream is still the greedy stream, in fewer rounds
+    eng2 = vn.SpecEngine(t, d, max_batch=1, max_seq=256, k=4, temperature=0.0, bonus=True, max_new_tokens=128)
+    toks, st = eng2.generate(g["prompt"], 96)
+    np.testing.assert_array_equal(toks, g["b_greedy"])
+    assert st["rounds"] <= rounds
+
+
+@pytest.mark.parametrize("dtype,tol", [("f32", 1e-3), ("bf16", 2e-2)])
+def test_mini_mate_model_against_reference(golden, dtype, tol):
+    """MoD + TriSparse, RoPE, GQA, tied head, embedding scale; batch 2, beyond two windows."""
+    g = golden("model_mini.npz")
+    cfg = mini_cfg()
+    sd = OM.init_state_dict(cfg, seed=7, gate_std=1.0)
+    ref = g["logits"]
+    if dtype == "bf16":  # the reference run with the same bf16-rounded weights
+        sd = {n: OM.bf16_round(v) for n, v in sd.items()}
+        ref = OM.forward(sd, cfg, g["tokens"])[0]
+    m = build(cfg, sd, dtype)
+    lg = m(g["tokens"]).data.numpy()
+    assert rel_err(lg, ref) < tol
+    if dtype == "f32":
+        m2 = build(mini_cfg(embedding_scale=False, use_alibi=True), sd)
+        assert rel_err(m2(g["tokens"][:1]).data.numpy(), g["logits_alibi_rope"]) < tol
+    # cached continuation: prefill 30 then 10 more positions
+    cache = m.new_cache(2, 64)
+    m.forward_cached(g["tokens"][:, :30], cache, want_logits=False, want_hidden=True, last_only=True)
+    cache.commit(30, np.full(2, 30, np.int32))
+    np.testing.assert_array_equal(cache.per_seq_lens, [30, 30])
+    lg2 = m.forward_cached(g["tokens"][:, 30:], cache).numpy()
+    want = g["logits_incremental"] if dtype == "f32" else ref[:, 30:]
+    assert rel_err(lg2, want) < tol
+
+
+def test_ragged_batch_lengths_and_reset():
+    cfg = mini_cfg(n_layer=2)
+    sd = OM.init_state_dict(cfg, seed=3, gate_std=0.5)
+    m = build(cfg, sd)
+    rng = np.random.default_rng(1)
+    a, b = rng.integers(0, 512, (1, 21)), rng.integers(0, 512, (1, 9))
+    cache = m.new_cache(2, 64)
+    # sequence 0 holds 21 tokens, sequence 1 holds 9: feed them separately via set_lengths
+    both = np.concatenate([a[:, :9], b], axis=0)
+    m.forward_cached(both, cache, want_logits=False, want_hidden=True, last_only=True)
+    cache.commit(9, np.array([9, 9], np.int32))
+    pad = np.concatenate([a[:, 9:], np.zeros((1, 12), np.int64)], axis=0)
+    m.forward_cached(pad, cache, want_logits=False, want_hidden=True, last_only=True)
+    cache.commit(12, np.array([12, 0], np.int32))          # sequence 1 rolls back all 12
+    np.testing.assert_array_equal(cache.per_seq_lens, [21, 9])
+    nxt = rng.integers(0, 512, (2, 3))
+    lg = m.forward_cached(nxt, cache).numpy()
+    wa = OM.forward(sd, cfg, np.concatenate([a, nxt[:1]], axis=1))[0][:, -3:]
+    wb = OM.forward(sd, cfg, np.concatenate([b, nxt[1:]], axis=1))[0][:, -3:]
+    assert rel_err(lg[0], wa[0]) < 1e-3 and rel_err(lg[1], wb[0]) < 1e-3
+    cache.reset_seq(1)
+    np.testing.assert_array_equal(cache.per_seq_lens, [21, 0])
+    k0, v0 = cache.get(0, 0)
+    _, oc = OM.forward(sd, cfg, a)
+    np.testing.assert_allclose(k0, oc[0]["k"][0], rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(v0, oc[0]["v"][0], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype,tol", [("f32", 1e-3), ("bf16", 2e-2)])
+def test_tree_verification_equals_per_path_forward(dtype, tol):
+    """16-node tree (4 roots, 2 children under the first two, 2 grandchildren under each child)."""
+    cfg = mini_cfg(n_layer=3, window_size=12)
+    sd = OM.init_state_dict(cfg, seed=9, gate_std=1.0)
+    if dtype == "bf16":
+        sd = {n: OM.bf16_round(v) for n, v in sd.items()}
+    m = build(cfg, sd, dtype)
+    rng = np.random.default_rng(2)
+    B = 2
+    ctx_tok = rng.integers(0, 512, (B, 20))
+    parents = [-1, -1, -1, -1, 0, 0, 1, 1, 4, 4, 5, 5, 6, 6, 7, 7]
+    nodes = rng.integers(0, 512, (B, 16))
+    cache = m.new_cache(B, 64)
+    m.forward_cached(ctx_tok, cache, want_logits=False, want_hidden=True, last_only=True)
+    cache.commit(20, np.full(B, 20, np.int32))
+    lg = m.forward_cached(nodes, cache, parents=parents).numpy()
+    _, oc = OM.forward(sd, cfg, ctx_tok)
+    want, _ = OM.forward(sd, cfg, nodes, cache=oc, parents=parents)
+    assert rel_err(lg, want) < tol
+    # commit the path 1 -> 6 -> 13 of sequence 0 and 0 -> 5 of sequence 1, then continue
+    keep = np.array([[1, 6, 13], [0, 5, 0]], np.int32)
+    cache.commit(16, np.array([3, 2], np.int32), keep_idx=keep)
+    np.testing.assert_array_equal(cache.per_seq_lens, [23, 22])
+    nxt = rng.integers(0, 512, (B, 2))
+    lg2 = m.forward_cached(nxt, cache).numpy()
+    s0 = np.concatenate([ctx_tok[:1], nodes[:1, [1, 6, 13]], nxt[:1]], axis=1)
+    s1 = np.concatenate([ctx_tok[1:], nodes[1:, [0, 5]], nxt[1:]], axis=1)
+    assert rel_err(lg2[0], OM.forward(sd, cfg, s0)[0][0, -2:]) < tol
+    assert rel_err(lg2[1], OM.forward(sd, cfg, s1)[0][0, -2:]) < tol
+
+
+def test_batched_stochastic_engine_matches_oracle():
+    """temperature 0.8, top-k 20, batch 3: tokens identical to the CPU restatement with the same Philox streams."""
+    import versenext_b200 as vn
+    t_cfg, t_sd, d_cfg, d_sd = variant_b()
+    t, d = build(t_cfg, t_sd), build(d_cfg, d_sd)
+    prompts = np.random.default_rng(5).integers(0, 256, (3, 12)).astype(np.int64)
+    eng = vn.SpecEngine(t, d, max_batch=3, max_seq=128, k=3, temperature=0.8, top_k=20, seed=77, bonus=True,
+                        max_new_tokens=64)
+    toks, st = eng.generate(prompts, 24)
+    want = OS.generate(t_sd, t_cfg, d_sd, d_cfg, prompts, 3, 24, temperature=0.8, top_k=20, seed=77, bonus=True)
+    np.testing.assert_array_equal(toks, want["tokens"])
+
+
+def test_generate_api_sampling_and_eos():
+    cfg = OM.small_config()
+    sd = OM.init_state_dict(cfg, seed=4)
+    m = build(cfg, sd)
+    p = np.array([[1, 2, 3, 4]], np.int64)
+    out = m.generate(p, max_new_tokens=5, temperature=0.9, top_k=10, seed=3)
+    assert out.shape == (1, 9) and out.dtype == np.int64 and np.all((out >= 0) & (out < 256))
+    np.testing.assert_array_equal(out, m.generate(p, max_new_tokens=5, temperature=0.9, top_k=10, seed=3))
+    out = m.generate(p[0], max_new_tokens=3, eos_id=255)
+    assert out.shape[0] == 1 and out[0, -1] == 255
+
+
+def test_errors():
+    import versenext_b200 as vn
+    with pytest.raises(ValueError):
+        vn.VerseNexLM(vocab_size=16, dim=16, n_layer=2, n_head=2, layer_pattern=["trisparse"])
+    with pytest.raises(ValueError):
+        vn.VerseNexLM(vocab_size=16, dim=16, n_layer=1, n_head=2, layer_pattern=["rwkv"])
+    cfg = OM.small_config()
+    sd = OM.init_state_dict(cfg, seed=4)
+    m = build(cfg, sd)
+    cache = m.new_cache(1, 8)
+    with pytest.raises(RuntimeError):
+        m.forward_cached(np.zeros((1, 9), np.int64), cache)           # capacity
+    with pytest.raises(IndexError):
+        cache.get(7, 0, 1)
+    with pytest.raises(IndexError):
+        cache.reset_seq(3)
+    with pytest.raises(ValueError):
+        m.forward_cached(np.zeros((2, 2), np.int64), cache)           # batch larger than the cache
+    m2 = vn.VerseNexLM(vocab_size=16, dim=16, n_layer=1, n_head=2)
+    with pytest.raises(ValueError):
+        m2.finalize()                                                 # tensors missing
+    with pytest.raises(ValueError):
+        m2.load_tensor("blocks.0.attn.wq.weight", np.zeros((3, 3), np.float32))

@@ -2,6 +2,8 @@
 
 Public surface (names follow the reference):
   SpeculativeDecoder                      verse_nex/speculative.py:55
+  VerseNexLM (= CometSparkNexLM), KVCache verse_nex/cometspark.py:294, kv_cache_parallel.py:42
+  SpecEngine                              batched draft -> verify -> accept -> commit loop
   get_backend / clear_backend_cache,
   DeviceBackend, B200Backend              verse_torch/device.py:219-389
   Context, DeviceArray                    device memory (plays torch.Tensor's role, tensor.py:394)
@@ -15,7 +17,9 @@ from . import _lib
 from .device import Context, DeviceArray, as_device
 from .backend import DeviceBackend, B200Backend, get_backend, clear_backend_cache
 from .speculative import SpeculativeDecoder, Tensor
+from .model import VerseNexLM, CometSparkNexLM, KVCache
+from .engine import SpecEngine
 from . import sampling
 
 __all__ = ["Context", "DeviceArray", "as_device", "DeviceBackend", "B200Backend", "get_backend",
-           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "sampling"]
+           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "sampling", "VerseNexLM", "CometSparkNexLM", "KVCache", "SpecEngine"]

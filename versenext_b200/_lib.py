@@ -75,6 +75,9 @@ PROTOTYPES = {
     "vn_accept_strided": [_p, _p, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _u64, _u32, _f32, _i32, _i32,
                           _i32, _i32, _i32, _p, _p],
     "vn_philox_uniform": [_p, _u64, _u32, _i32, _i32, _i32, _p],
+    "vn_sample": [_p, _p, _i64, _i32, _i32, _f32, _i32, _p, _u64, _u32, _u32, _u32, _p],
+    "vn_spec_gather": [_p, _p, _p, _i32, _i32, _i32, _p, _p],
+    "vn_spec_advance": [_p, _p, _i32, _i32, _p, _p, _i32, _p, _p],
     "vn_model_create": [_p, C.c_char_p, C.POINTER(_p)],
     "vn_model_destroy": [_p],
     "vn_model_load_tensor": [_p, C.c_char_p, _p, _i32, C.POINTER(_i64)],
@@ -86,9 +89,9 @@ PROTOTYPES = {
     "vn_kv_reset_seq": [_p, _i32],
     "vn_kv_lengths": [_p, _p],
     "vn_kv_set_lengths": [_p, _p],
-    "vn_kv_commit": [_p, _i32, _p, _i32, _p],
+    "vn_kv_commit": [_p, _i32, _p, _i32, _p, _i32],
     "vn_kv_read": [_p, _i32, _i32, _i32, _p, _i32],
-    "vn_model_forward": [_p, _p, _p, _i32, _i32, _p, _p, _p, _i32],
+    "vn_model_forward": [_p, _p, _p, _i32, _i32, _p, _p, _p, _i32, _i32],
 }
 _RESTYPE = {"vn_last_error": C.c_char_p}
 

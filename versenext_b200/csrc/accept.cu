@@ -172,8 +172,9 @@ __device__ __forceinline__ float scaled(float x, float temp) { return temp != 1.
 __global__ void accept_decide_kernel(RowSet rs, int B, int k, int nchunks, const Partial* __restrict__ part,
                                      const long long* __restrict__ draft, const float* __restrict__ u_acc,
                                      const float* __restrict__ u_smp, uint64_t seed, uint32_t offset,
-                                     float temp, int greedy, int bonus, Decision* __restrict__ dec,
-                                     int* __restrict__ out_len, long long* __restrict__ out_tok) {
+                                     float temp, int greedy, int bonus, int smp_purpose, int pos_base,
+                                     Decision* __restrict__ dec, int* __restrict__ out_len,
+                                     long long* __restrict__ out_tok) {
   const int b = blockIdx.x;
   const int rows_per_seq = rs.np + rs.nq;
   __shared__ float r_m[2 * MAX_K + 1];
@@ -209,7 +210,7 @@ __global__ void accept_decide_kernel(RowSet rs, int B, int k, int nchunks, const
     if (n < k) tok[n] = r_a[n];
     else if (bonus) tok[k] = r_a[k];
     d.n_acc = n;
-    out_len[b] = n;
+    if (out_len) out_len[b] = n;
     dec[b] = d;
     return;
   }
@@ -224,7 +225,7 @@ __global__ void accept_decide_kernel(RowSet rs, int B, int k, int nchunks, const
       const float lq = x_ok ? scaled(row_ptr(rs, b, rs.np + n)[x], temp) : -CUDART_INF_F;
       q = (double)expf(lq - r_m[rs.np + n]) / r_s[rs.np + n];
     }
-    const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, n, 0);
+    const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, pos_base + n, 0);
     if ((double)u * q < p) { tok[n] = x; continue; }
     rejected = true;
     d.mode = rs.nq ? 1 : 3;
@@ -237,9 +238,9 @@ __global__ void accept_decide_kernel(RowSet rs, int B, int k, int nchunks, const
   if (!rejected && bonus) {
     d.mode = 2; d.pos = k; d.m_p = r_m[k]; d.inv_sp = 1.0 / r_s[k];
   }
-  if (d.mode) d.u = u_smp ? u_smp[(long long)b * (k + 1) + d.pos] : philox_uniform(seed, offset, b, d.pos, 1);
+  if (d.mode) d.u = u_smp ? u_smp[(long long)b * (k + 1) + d.pos] : philox_uniform(seed, offset, b, pos_base + d.pos, smp_purpose);
   d.n_acc = n;
-  out_len[b] = n;
+  if (out_len) out_len[b] = n;
   dec[b] = d;
 }
 
@@ -541,7 +542,8 @@ __device__ int list_find(const TopkRow& r, int token) {
 __global__ void accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restrict__ rows,
                                           const long long* __restrict__ draft, const float* __restrict__ u_acc,
                                           const float* __restrict__ u_smp, uint64_t seed, uint32_t offset,
-                                          int bonus, int* __restrict__ out_len, long long* __restrict__ out_tok) {
+                                          int bonus, int smp_purpose, int pos_base, int* __restrict__ out_len,
+                                          long long* __restrict__ out_tok) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   const int rows_per_seq = np + nq;
@@ -569,13 +571,13 @@ __global__ void accept_topk_decide_kernel(int B, int k, int np, int nq, const To
       int iq = list_find(Q, x);
       q = iq >= 0 ? (double)expf(Q.val[iq] - mq) / sq : 0.0;
     }
-    const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, n, 0);
+    const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, pos_base + n, 0);
     if ((double)u * q < p) { tok[n] = x; continue; }
     sample_row = n;
     if (nq) q_row = np + n; else removed = x;
     break;
   }
-  out_len[b] = n;
+  if (out_len) out_len[b] = n;
   if (sample_row < 0) {
     if (!bonus) return;
     sample_row = k;
@@ -584,7 +586,8 @@ __global__ void accept_topk_decide_kernel(int B, int k, int np, int nq, const To
   float mp; double sp; stats(P, mp, sp);
   float mq = 0.f; double sq = 1.0;
   if (q_row >= 0) stats(rb[q_row], mq, sq);
-  const float u = u_smp ? u_smp[(long long)b * (k + 1) + sample_row] : philox_uniform(seed, offset, b, sample_row, 1);
+  const float u = u_smp ? u_smp[(long long)b * (k + 1) + sample_row]
+                        : philox_uniform(seed, offset, b, pos_base + sample_row, smp_purpose);
   for (int pass = 0; pass < 2; ++pass) {
     // pass 0: residual; pass 1 (only when it vanished): p itself
     double Z = 0.0;
@@ -617,14 +620,14 @@ __global__ void accept_topk_decide_kernel(int B, int k, int np, int nq, const To
 
 }  // namespace
 
-static int32_t accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_si,
+int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_si,
                            const float* q, long long q_sb, long long q_si, const int64_t* draft,
                            const float* u_acc, const float* u_smp, uint64_t seed, uint32_t offset,
                            float temperature, int32_t top_k, int32_t bonus, int32_t B, int32_t k, int32_t V,
-                           int32_t* out_len, int64_t* out_tok) {
+                           int32_t* out_len, int64_t* out_tok, int32_t smp_purpose, int32_t pos_base) {
   VN_CHECK_CTX(ctx);
   VN_REQUIRE(ctx, B >= 0 && k >= 0 && k <= MAX_K && V >= 1, "bad sizes B=%d k=%d V=%d (k <= %d)", B, k, V, MAX_K);
-  VN_REQUIRE(ctx, p && out_len && out_tok, "null pointer");
+  VN_REQUIRE(ctx, p && out_tok, "null pointer");
   VN_REQUIRE(ctx, k == 0 || draft, "draft tokens missing");
   VN_REQUIRE(ctx, (u_acc == nullptr) == (u_smp == nullptr) || k == 0, "inject both uniform arrays or neither");
   VN_REQUIRE(ctx, bonus || k > 0, "nothing to do: k == 0 without a bonus token");
@@ -649,7 +652,7 @@ static int32_t accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long lon
     TopkRow* rows = (TopkRow*)ws;
     VN_LAUNCH(ctx, accept_topk_kernel, B * rows_per_seq, 1024, 0, rs, top_k, temp, rows);
     VN_LAUNCH(ctx, accept_topk_decide_kernel, ceil_div(B, 32), 32, 0, B, k, rs.np, rs.nq, rows, d64, u_acc, u_smp,
-              seed, offset, bonus, out_len, o64);
+              seed, offset, bonus, smp_purpose, pos_base, out_len, o64);
     return VN_OK;
   }
 
@@ -673,7 +676,7 @@ static int32_t accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long lon
   if (vec) VN_LAUNCH(ctx, accept_stats_kernel<true>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
   else     VN_LAUNCH(ctx, accept_stats_kernel<false>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
   VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_acc, u_smp, seed, offset, temp,
-            (int)greedy, bonus, dec, out_len, o64);
+            (int)greedy, bonus, smp_purpose, pos_base, dec, out_len, o64);
   if (!greedy) {
     dim3 g(nchunks, B);
     if (vec) VN_LAUNCH(ctx, accept_residual_kernel<true>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);
@@ -690,8 +693,8 @@ int32_t vn_accept(vn_ctx* ctx, const float* p_logits_dev, const float* q_logits_
                   float temperature, int32_t top_k, int32_t bonus, int32_t B, int32_t k, int32_t V,
                   int32_t* out_len_dev, int64_t* out_tokens_dev) {
   const long long np = bonus ? k + 1 : k;
-  return accept_impl(ctx, p_logits_dev, np * V, V, q_logits_dev, (long long)k * V, V, draft_dev, u_accept_dev,
-                     u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev, out_tokens_dev);
+  return vn_accept_impl(ctx, p_logits_dev, np * V, V, q_logits_dev, (long long)k * V, V, draft_dev, u_accept_dev,
+                        u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev, out_tokens_dev, 1, 0);
 }
 
 int32_t vn_accept_strided(vn_ctx* ctx, const float* p_logits_dev, int64_t p_stride_b, int64_t p_stride_i,
@@ -699,9 +702,21 @@ int32_t vn_accept_strided(vn_ctx* ctx, const float* p_logits_dev, int64_t p_stri
                           const int64_t* draft_dev, const float* u_accept_dev, const float* u_sample_dev,
                           uint64_t seed, uint32_t offset, float temperature, int32_t top_k, int32_t bonus,
                           int32_t B, int32_t k, int32_t V, int32_t* out_len_dev, int64_t* out_tokens_dev) {
-  return accept_impl(ctx, p_logits_dev, p_stride_b, p_stride_i, q_logits_dev, q_stride_b, q_stride_i, draft_dev,
-                     u_accept_dev, u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev,
-                     out_tokens_dev);
+  return vn_accept_impl(ctx, p_logits_dev, p_stride_b, p_stride_i, q_logits_dev, q_stride_b, q_stride_i, draft_dev,
+                        u_accept_dev, u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev,
+                        out_tokens_dev, 1, 0);
+}
+
+int32_t vn_sample(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, float temperature,
+                  int32_t top_k, const float* uniforms_dev, uint64_t seed, uint32_t offset, uint32_t position,
+                  uint32_t purpose, int64_t* out_tokens_dev) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, R >= 0 && out_tokens_dev, "bad arguments");
+  if (R == 0) return VN_OK;
+  int32_t st = vn_accept_impl(ctx, logits_dev, row_stride, 0, nullptr, 0, 0, nullptr, uniforms_dev, uniforms_dev, seed,
+                              offset, temperature, top_k, 1, R, 0, V, nullptr, out_tokens_dev, (int32_t)purpose,
+                              (int32_t)position);
+  return st;
 }
 
 int32_t vn_philox_uniform(vn_ctx* ctx, uint64_t seed, uint32_t offset, int32_t B, int32_t n, int32_t purpose,

@@ -1,19 +1,754 @@
-// placeholder until the model forward lands
+// VerseNexLM on the device: weights, KV cache, one forward over new positions (chain or tree).
+// Mirrors CometSparkNexLM.forward (verse_nex/cometspark.py:670-698) block by block, with the KV cache that
+// TriSparseAttention.forward accepts (tri_sparse_attn.py:559-575) kept resident and updated in place.
 #include "common.cuh"
-extern "C" {
-#define STUB(ctxexpr) return vn_fail(ctxexpr, VN_ERR_UNSUPPORTED, "model path not built yet")
-int32_t vn_model_create(vn_ctx* ctx, const char*, vn_model**) { STUB(ctx); }
-int32_t vn_model_destroy(vn_model*) { return VN_OK; }
-int32_t vn_model_load_tensor(vn_model*, const char*, const float*, int32_t, const int64_t*) { STUB(nullptr); }
-int32_t vn_model_finalize(vn_model*) { STUB(nullptr); }
-int32_t vn_model_quantize(vn_model*, const char*) { STUB(nullptr); }
-int32_t vn_model_param_bytes(vn_model*, uint64_t*) { STUB(nullptr); }
-int32_t vn_kv_create(vn_model*, int32_t, int32_t, vn_kv**) { STUB(nullptr); }
-int32_t vn_kv_destroy(vn_kv*) { return VN_OK; }
-int32_t vn_kv_reset_seq(vn_kv*, int32_t) { STUB(nullptr); }
-int32_t vn_kv_lengths(vn_kv*, int32_t*) { STUB(nullptr); }
-int32_t vn_kv_set_lengths(vn_kv*, const int32_t*) { STUB(nullptr); }
-int32_t vn_kv_commit(vn_kv*, int32_t, const int32_t*, int32_t, const int32_t*) { STUB(nullptr); }
-int32_t vn_kv_read(vn_kv*, int32_t, int32_t, int32_t, float*, int32_t) { STUB(nullptr); }
-int32_t vn_model_forward(vn_model*, vn_kv*, const int64_t*, int32_t, int32_t, const int32_t*, float*, float*, int32_t) { STUB(nullptr); }
+#include "gemm.cuh"
+#include "gemm_mma.cuh"
+#include "model_kernels.cuh"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#include <set>
+
+namespace {
+
+struct Config {
+  int vocab = 0, dim = 0, n_layer = 0, n_head = 0, n_kv = 0, hd = 0;
+  int window = 512, n_sink = 64, use_alibi = 1, use_rope = 0, max_seq_len = 2048;
+  double rope_theta = 10000.0;
+  int P = 5, E = 8, top_k = 3, expert_hidden = 0, mlp_hidden = 0, mlp_mult = 4;
+  int tie = 1, emb_scale = 0;
+  int bf16 = 0;
+  std::vector<int> kind;  // 0 trisparse, 1 mod
+};
+
+// ---- minimal JSON field access (flat object, as json.dumps of the constructor kwargs yields) -------------
+bool json_find(const std::string& s, const char* key, size_t* pos) {
+  std::string k = std::string("\"") + key + "\"";
+  size_t p = s.find(k);
+  if (p == std::string::npos) return false;
+  p = s.find(':', p + k.size());
+  if (p == std::string::npos) return false;
+  ++p;
+  while (p < s.size() && isspace((unsigned char)s[p])) ++p;
+  *pos = p;
+  return true;
 }
+bool json_num(const std::string& s, const char* key, double* out) {
+  size_t p;
+  if (!json_find(s, key, &p)) return false;
+  if (s.compare(p, 4, "null") == 0) return false;
+  if (s.compare(p, 4, "true") == 0) { *out = 1; return true; }
+  if (s.compare(p, 5, "false") == 0) { *out = 0; return true; }
+  char* end = nullptr;
+  double v = strtod(s.c_str() + p, &end);
+  if (end == s.c_str() + p) return false;
+  *out = v;
+  return true;
+}
+bool json_str(const std::string& s, const char* key, std::string* out) {
+  size_t p;
+  if (!json_find(s, key, &p) || s[p] != '"') return false;
+  size_t e = s.find('"', p + 1);
+  if (e == std::string::npos) return false;
+  *out = s.substr(p + 1, e - p - 1);
+  return true;
+}
+bool json_str_list(const std::string& s, const char* key, std::vector<std::string>* out) {
+  size_t p;
+  if (!json_find(s, key, &p) || s[p] != '[') return false;
+  size_t e = s.find(']', p);
+  if (e == std::string::npos) return false;
+  size_t i = p + 1;
+  while (i < e) {
+    size_t a = s.find('"', i);
+    if (a == std::string::npos || a > e) break;
+    size_t b = s.find('"', a + 1);
+    out->push_back(s.substr(a + 1, b - a - 1));
+    i = b + 1;
+  }
+  return true;
+}
+
+struct Layer {
+  int kind = 0;
+  float* norm1 = nullptr;
+  float* norm2 = nullptr;
+  float gate_logits[3] = {0.f, 0.f, 0.f};
+  void* wqkv = nullptr;     // [(H + 2 n_kv) hd, D]
+  void* wproj = nullptr;    // [D, H hd]
+  void* sink = nullptr;     // [n_sink, D]   global_tokens.weight
+  void* sink_kv = nullptr;  // [n_sink, 2 n_kv hd] computed by finalize: sink @ [wk; wv]^T
+  void* sink_k = nullptr;   // [n_sink, n_kv hd] (compacted from sink_kv)
+  void* sink_v = nullptr;
+  void* w_gateup = nullptr; // trisparse: [2 hidden, D], rows interleaved gate_j, up_j
+  void* w_down = nullptr;   // [D, hidden]
+  float* router = nullptr;  // mod: [(P + P E), D] fp32
+  void* e_gateup = nullptr; // mod: [P E][2 eh, D]
+  void* e_down = nullptr;   // mod: [P E][D, eh]
+};
+
+}  // namespace
+
+struct vn_model {
+  vn_ctx* ctx = nullptr;
+  Config cfg;
+  size_t esz = 4;           // bytes per stored weight / activation element
+  void* emb = nullptr;      // [V, D]
+  void* head = nullptr;     // [V, D] (== emb when tied)
+  float* norm_f = nullptr;
+  std::vector<Layer> layers;
+  float* rope_cos = nullptr;  // [rope_rows, hd/2]
+  float* rope_sin = nullptr;
+  int rope_rows = 0;
+  std::set<std::string> loaded;
+  bool finalized = false;
+  uint64_t param_bytes = 0;
+  int* status = nullptr;    // device word: 1 = a token id was out of range
+  // activations, grown on demand
+  int cap_rows = 0;
+  float* x = nullptr;       // [M, D] residual stream
+  void* h = nullptr;        // [M, D] normalised, storage dtype
+  float* h32 = nullptr;     // [M, D] fp32 copy for the routers
+  float* qkv = nullptr;     // [M, (H + 2 n_kv) hd]
+  void* attn = nullptr;     // [M, D]
+  void* act = nullptr;      // [M * slots, max(hidden, eh)]
+  float* y = nullptr;       // [M * slots, D]
+  int* slot_expert = nullptr; float* slot_w = nullptr; float* part_w = nullptr;
+  int* expert_count = nullptr; int* expert_off = nullptr; int* expert_cur = nullptr;
+  int* sorted_row = nullptr; int* slot_pos = nullptr;
+  int* depth_dev = nullptr; unsigned long long* anc_dev = nullptr; int* rows_dev = nullptr;
+  float* stage = nullptr; size_t stage_elems = 0;
+};
+
+struct vn_kv {
+  vn_model* m = nullptr;
+  int max_batch = 0, max_seq = 0;
+  std::vector<void*> k, v;   // per layer [max_batch, max_seq, n_kv, hd]
+  void** planes_dev = nullptr;  // [2 * n_layer] device array of plane pointers (k0, v0, k1, v1, ...)
+  int* lens = nullptr;       // device [max_batch]
+  std::vector<int> len_ub;   // host upper bound of every length
+};
+
+namespace {
+
+template <typename T>
+int32_t upload_rows(vn_model* m, const float* host, void* dst, long long rows, long long cols, long long dst_ld,
+                    long long row_mul, long long row_off) {
+  vn_ctx* ctx = m->ctx;
+  const size_t n = (size_t)rows * cols;
+  if (n == 0) return VN_OK;
+  if (n > m->stage_elems) {
+    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (m->stage) VN_CUDA(ctx, cudaFree(m->stage));
+    m->stage = nullptr; m->stage_elems = 0;
+    VN_CUDA(ctx, cudaMalloc(&m->stage, n * sizeof(float)));
+    m->stage_elems = n;
+  }
+  VN_CUDA(ctx, cudaMemcpyAsync(m->stage, host, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  VN_LAUNCH(ctx, convert_rows_kernel<T>, (unsigned)ceil_div((long long)n, 256ll), 256, 0, m->stage, (T*)dst, rows, cols,
+            dst_ld, row_mul, row_off);
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the host buffer may be reused by the caller
+  return VN_OK;
+}
+
+int32_t upload(vn_model* m, const float* host, void* dst, long long rows, long long cols, long long dst_ld,
+               long long row_mul = 1, long long row_off = 0, bool force_f32 = false) {
+  if (m->cfg.bf16 && !force_f32)
+    return upload_rows<__nv_bfloat16>(m, host, dst, rows, cols, dst_ld, row_mul, row_off);
+  return upload_rows<float>(m, host, dst, rows, cols, dst_ld, row_mul, row_off);
+}
+
+int32_t dev_alloc(vn_ctx* ctx, void** p, size_t bytes) {
+  VN_CUDA(ctx, cudaMalloc(p, bytes ? bytes : 16));
+  return VN_OK;
+}
+
+#define TRY(expr) do { int32_t _s = (expr); if (_s != VN_OK) return _s; } while (0)
+
+int32_t alloc_weights(vn_model* m) {
+  vn_ctx* ctx = m->ctx;
+  const Config& c = m->cfg;
+  const size_t e = m->esz;
+  const size_t D = c.dim, qkv_rows = (size_t)(c.n_head + 2 * c.n_kv) * c.hd;
+  uint64_t bytes = 0;
+  auto A = [&](void** p, size_t n) -> int32_t { bytes += n; return dev_alloc(ctx, p, n); };
+  TRY(A(&m->emb, (size_t)c.vocab * D * e));
+  if (c.tie) m->head = m->emb; else TRY(A(&m->head, (size_t)c.vocab * D * e));
+  TRY(A((void**)&m->norm_f, D * 4));
+  TRY(dev_alloc(ctx, (void**)&m->status, 4));
+  VN_CUDA(ctx, cudaMemsetAsync(m->status, 0, 4, ctx->stream));
+  m->layers.resize(c.n_layer);
+  for (int i = 0; i < c.n_layer; ++i) {
+    Layer& L = m->layers[i];
+    L.kind = c.kind[i];
+    TRY(A((void**)&L.norm1, D * 4));
+    TRY(A((void**)&L.norm2, D * 4));
+    TRY(A(&L.wqkv, qkv_rows * D * e));
+    TRY(A(&L.wproj, D * (size_t)c.n_head * c.hd * e));
+    TRY(A(&L.sink, (size_t)c.n_sink * D * e));
+    TRY(dev_alloc(ctx, &L.sink_k, (size_t)c.n_sink * c.n_kv * c.hd * e));
+    TRY(dev_alloc(ctx, &L.sink_v, (size_t)c.n_sink * c.n_kv * c.hd * e));
+    if (L.kind == 0) {
+      TRY(A(&L.w_gateup, (size_t)2 * c.mlp_hidden * D * e));
+      TRY(A(&L.w_down, D * (size_t)c.mlp_hidden * e));
+    } else {
+      const size_t ne = (size_t)c.P * c.E;
+      TRY(A((void**)&L.router, (size_t)(c.P + ne) * D * 4));
+      TRY(A(&L.e_gateup, ne * 2 * c.expert_hidden * D * e));
+      TRY(A(&L.e_down, ne * D * c.expert_hidden * e));
+    }
+  }
+  m->param_bytes = bytes;
+  return VN_OK;
+}
+
+int32_t ensure_rows(vn_model* m, int M) {
+  if (M <= m->cap_rows) return VN_OK;
+  vn_ctx* ctx = m->ctx;
+  const Config& c = m->cfg;
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  void** bufs[] = {(void**)&m->x, &m->h, (void**)&m->h32, (void**)&m->qkv, &m->attn, &m->act, (void**)&m->y,
+                   (void**)&m->slot_expert, (void**)&m->slot_w, (void**)&m->part_w, (void**)&m->sorted_row,
+                   (void**)&m->slot_pos, (void**)&m->rows_dev};
+  for (void** b : bufs) { if (*b) cudaFree(*b); *b = nullptr; }
+  const size_t e = m->esz, D = c.dim, R = (size_t)M + (M >> 2) + 8;
+  bool has_mod = false;
+  for (int k : c.kind) has_mod |= (k == 1);
+  const size_t S = has_mod ? (size_t)c.P * c.top_k : 1;
+  const size_t hid = std::max((size_t)c.mlp_hidden, has_mod ? (size_t)c.expert_hidden : 0);
+  TRY(dev_alloc(ctx, (void**)&m->x, R * D * 4));
+  TRY(dev_alloc(ctx, &m->h, R * D * e));
+  TRY(dev_alloc(ctx, (void**)&m->h32, R * D * 4));
+  TRY(dev_alloc(ctx, (void**)&m->qkv, R * (size_t)(c.n_head + 2 * c.n_kv) * c.hd * 4));
+  TRY(dev_alloc(ctx, &m->attn, R * D * e));
+  TRY(dev_alloc(ctx, &m->act, R * S * hid * e));
+  TRY(dev_alloc(ctx, (void**)&m->rows_dev, R * 4));
+  if (has_mod) {
+    TRY(dev_alloc(ctx, (void**)&m->y, R * S * D * 4));
+    TRY(dev_alloc(ctx, (void**)&m->slot_expert, R * S * 4));
+    TRY(dev_alloc(ctx, (void**)&m->slot_w, R * S * 4));
+    TRY(dev_alloc(ctx, (void**)&m->part_w, R * c.P * 4));
+    TRY(dev_alloc(ctx, (void**)&m->sorted_row, R * S * 4));
+    TRY(dev_alloc(ctx, (void**)&m->slot_pos, R * S * 4));
+    if (!m->expert_count) {
+      const size_t ne = (size_t)c.P * c.E;
+      TRY(dev_alloc(ctx, (void**)&m->expert_count, ne * 4));
+      TRY(dev_alloc(ctx, (void**)&m->expert_off, ne * 4));
+      TRY(dev_alloc(ctx, (void**)&m->expert_cur, ne * 4));
+    }
+  }
+  m->cap_rows = (int)R;
+  return VN_OK;
+}
+
+// one Linear: C = A @ W^T with the epilogue, dispatching on the storage dtype
+int32_t linear(vn_model* m, GemmArgs g) {
+  vn_ctx* ctx = m->ctx;
+  if (m->cfg.bf16) {
+    if (gemm_mma_supported(g)) return launch_gemm_mma(ctx, g);
+    return launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g);
+  }
+  return launch_gemm_simt<float, float>(ctx, g);
+}
+
+template <typename T>
+int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, bool tree, float* out_hidden,
+                  float* out_logits, int last_only, int slot_offset) {
+  vn_ctx* ctx = m->ctx;
+  const Config& c = m->cfg;
+  const int M = B * Tn, D = c.dim, H = c.n_head, hd = c.hd, n_kv = c.n_kv;
+  const int qkv_ld = (H + 2 * n_kv) * hd;
+  const float emb_scale = c.emb_scale ? sqrtf((float)D) : 1.0f;
+  VN_LAUNCH(ctx, embed_kernel<T>, M, 128, 0, (const long long*)tokens, (const T*)m->emb, m->x, D, c.vocab, emb_scale,
+            m->status);
+  for (int li = 0; li < c.n_layer; ++li) {
+    Layer& L = m->layers[li];
+    VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm1, (T*)m->h, (float*)nullptr, (const int*)nullptr, D, 1e-6f);
+    GemmArgs g;
+    g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.C = m->qkv; g.ldc = qkv_ld; g.M = M; g.N = qkv_ld; g.K = D;
+    TRY(linear(m, g));
+    VN_LAUNCH(ctx, rope_append_kernel<T>, M, 128, 0, m->qkv, m->rope_cos, m->rope_sin, kv->lens,
+              tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq,
+              c.use_rope, m->rope_rows, slot_offset);
+    AttnArgs a;
+    a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[li]; a.vc = kv->v[li]; a.sink_k = L.sink_k; a.sink_v = L.sink_v;
+    a.out = m->attn; a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
+    a.Tn = Tn; a.H = H; a.n_kv = n_kv; a.hd = hd; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink;
+    a.use_alibi = c.use_alibi; a.alibi_max = 1024; a.slot_offset = slot_offset;
+    a.g_a = 1.f / (1.f + expf(-L.gate_logits[0]));
+    a.g_b = 1.f / (1.f + expf(-L.gate_logits[1]));
+    a.g_c = 1.f / (1.f + expf(-L.gate_logits[2]));
+    a.scale = 1.0f / sqrtf((float)hd);
+    {
+      dim3 grid(ceil_div(H, 8), M);
+      VN_LAUNCH(ctx, trisparse_attn_kernel<T>, grid, 256, 0, a);
+    }
+    g = GemmArgs();
+    g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.C = m->x; g.ldc = D; g.M = M; g.N = D; g.K = H * hd;
+    g.epi = EPI_ADD;
+    TRY(linear(m, g));
+    const bool mod = L.kind == 1;
+    VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm2, (T*)m->h, mod ? m->h32 : (float*)nullptr,
+              (const int*)nullptr, D, 1e-6f);
+    if (!mod) {
+      g = GemmArgs();
+      g.A = m->h; g.lda = D; g.W = L.w_gateup; g.ldw = D; g.C = m->act; g.ldc = c.mlp_hidden; g.M = M;
+      g.N = 2 * c.mlp_hidden; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = c.bf16;
+      TRY(linear(m, g));
+      g = GemmArgs();
+      g.A = m->act; g.lda = c.mlp_hidden; g.W = L.w_down; g.ldw = c.mlp_hidden; g.C = m->x; g.ldc = D; g.M = M; g.N = D;
+      g.K = c.mlp_hidden; g.epi = EPI_ADD;
+      TRY(linear(m, g));
+    } else {
+      const int ne = c.P * c.E, S = c.P * c.top_k, eh = c.expert_hidden;
+      VN_CUDA(ctx, cudaMemsetAsync(m->expert_count, 0, ne * 4, ctx->stream));
+      RouteArgs r;
+      r.h = m->h32; r.gates = L.router; r.slot_expert = m->slot_expert; r.slot_w = m->slot_w; r.part_w = m->part_w;
+      r.expert_count = m->expert_count; r.M = M; r.D = D; r.P = c.P; r.E = c.E; r.top_k = c.top_k;
+      VN_LAUNCH(ctx, mod_route_kernel, ceil_div(M, 4), 128, 0, r);
+      VN_LAUNCH(ctx, mod_offsets_kernel, 1, 32, 0, m->expert_count, m->expert_off, m->expert_cur, ne);
+      VN_LAUNCH(ctx, mod_scatter_kernel, ceil_div(M * S, 256), 256, 0, m->slot_expert, m->expert_off, m->expert_cur,
+                m->sorted_row, m->slot_pos, M * S, S);
+      g = GemmArgs();
+      g.A = m->h; g.lda = D; g.a_rows = m->sorted_row; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
+      g.C = m->act; g.ldc = eh; g.M = M; g.N = 2 * eh; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = c.bf16;
+      g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne;
+      TRY(linear(m, g));
+      g = GemmArgs();
+      g.A = m->act; g.lda = eh; g.W = L.e_down; g.ldw = eh; g.w_stride = (long long)D * eh; g.C = m->y; g.ldc = D;
+      g.M = M; g.N = D; g.K = eh; g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne;
+      TRY(linear(m, g));
+      VN_LAUNCH(ctx, mod_combine_kernel, M, 256, 0, m->x, m->y, m->slot_pos, m->slot_w, m->part_w, D, c.P, c.top_k);
+    }
+  }
+  // final norm + head on every row, or on the last position of every sequence
+  int rows_out = M;
+  const int* row_sel = nullptr;
+  if (last_only) {
+    rows_out = B;
+    std::vector<int> sel(B);
+    for (int b = 0; b < B; ++b) sel[b] = b * Tn + Tn - 1;
+    VN_CUDA(ctx, cudaMemcpyAsync(m->rows_dev, sel.data(), B * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `sel` is a stack-owned host buffer
+    row_sel = m->rows_dev;
+  }
+  VN_LAUNCH(ctx, rmsnorm_kernel<T>, rows_out, 256, 0, m->x, m->norm_f, (T*)m->h, out_hidden, row_sel, D, 1e-6f);
+  if (out_logits) {
+    GemmArgs g;
+    g.A = m->h; g.lda = D; g.W = m->head; g.ldw = D; g.C = out_logits; g.ldc = c.vocab; g.M = rows_out; g.N = c.vocab;
+    g.K = D;
+    TRY(linear(m, g));
+  }
+  return VN_OK;
+}
+
+struct NameRoute { int layer; std::string rest; };
+
+}  // namespace
+
+extern "C" {
+
+int32_t vn_model_create(vn_ctx* ctx, const char* config_json, vn_model** out) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, config_json && out, "null argument");
+  *out = nullptr;
+  const std::string s(config_json);
+  Config c;
+  double v;
+  auto need = [&](const char* key, int* dst) -> bool { if (!json_num(s, key, &v)) return false; *dst = (int)v; return true; };
+  VN_REQUIRE(ctx, need("vocab_size", &c.vocab) && need("dim", &c.dim) && need("n_layer", &c.n_layer) &&
+             need("n_head", &c.n_head), "config needs vocab_size, dim, n_layer, n_head");
+  c.n_kv = c.n_head;
+  need("n_kv_head", &c.n_kv);
+  need("window_size", &c.window); need("num_global_tokens", &c.n_sink); need("use_alibi", &c.use_alibi);
+  need("use_rope", &c.use_rope); need("max_seq_len", &c.max_seq_len);
+  if (json_num(s, "rope_theta", &v)) c.rope_theta = v;
+  need("num_dense_parts", &c.P); need("num_experts_per_part", &c.E); need("top_k", &c.top_k);
+  need("expert_hidden", &c.expert_hidden); need("mlp_hidden_multiple", &c.mlp_mult);
+  need("tie_weights", &c.tie); need("embedding_scale", &c.emb_scale);
+  std::string dt;
+  if (json_str(s, "dtype", &dt)) {
+    VN_REQUIRE(ctx, dt == "f32" || dt == "bf16", "dtype must be \"f32\" or \"bf16\", got %s", dt.c_str());
+    c.bf16 = dt == "bf16";
+  }
+  VN_REQUIRE(ctx, c.vocab > 0 && c.dim > 0 && c.n_layer > 0 && c.n_head > 0 && c.n_kv > 0, "non-positive size");
+  VN_REQUIRE(ctx, c.dim % c.n_head == 0, "dim(%d) must be divisible by n_head(%d)", c.dim, c.n_head);
+  VN_REQUIRE(ctx, c.n_head % c.n_kv == 0, "n_head(%d) must be divisible by n_kv_head(%d)", c.n_head, c.n_kv);
+  c.hd = c.dim / c.n_head;
+  VN_REQUIRE(ctx, c.hd % 8 == 0 && c.hd <= 64, "head_dim %d unsupported (multiple of 8, at most 64)", c.hd);
+  VN_REQUIRE(ctx, c.window >= 1 && c.n_sink >= 1, "window_size and num_global_tokens must be positive");
+  std::vector<std::string> pat;
+  if (json_str_list(s, "layer_pattern", &pat)) {
+    VN_REQUIRE(ctx, (int)pat.size() == c.n_layer, "layer_pattern length (%zu) must equal n_layer (%d)", pat.size(), c.n_layer);
+    for (auto& k : pat) {
+      VN_REQUIRE(ctx, k == "trisparse" || k == "mod", "layer kind %s is not built (trisparse | mod)", k.c_str());
+      c.kind.push_back(k == "mod");
+    }
+  } else {
+    c.kind.assign(c.n_layer, 0);
+  }
+  if (c.expert_hidden <= 0) c.expert_hidden = std::max((int)(c.dim * 8.0 / 3.0 / 64.0) * 64, 64);  // mod.py:687-688
+  c.mlp_hidden = (int)((long long)((c.mlp_mult * c.dim * 2.0 / 3.0 + 63) / 64)) * 64;              // vnnn.py:794
+  VN_REQUIRE(ctx, c.top_k >= 1 && c.top_k <= c.E && c.top_k <= 8 && c.E <= 60 && c.P >= 1 &&
+             c.P + c.P * c.E <= 64, "MoD shape unsupported (P=%d E=%d top_k=%d)", c.P, c.E, c.top_k);
+  vn_model* m = new vn_model();
+  m->ctx = ctx; m->cfg = c; m->esz = c.bf16 ? 2 : 4;
+  int32_t st = alloc_weights(m);
+  if (st != VN_OK) { vn_model_destroy(m); return st; }
+  *out = m;
+  return VN_OK;
+}
+
+int32_t vn_model_destroy(vn_model* m) {
+  if (!m) return VN_OK;
+  cudaSetDevice(m->ctx->device);
+  cudaStreamSynchronize(m->ctx->stream);
+  auto F = [](void* p) { if (p) cudaFree(p); };
+  F(m->emb); if (m->head != m->emb) F(m->head); F(m->norm_f); F(m->rope_cos); F(m->rope_sin); F(m->status);
+  for (auto& L : m->layers) {
+    F(L.norm1); F(L.norm2); F(L.wqkv); F(L.wproj); F(L.sink); F(L.sink_kv); F(L.sink_k); F(L.sink_v); F(L.w_gateup);
+    F(L.w_down); F(L.router); F(L.e_gateup); F(L.e_down);
+  }
+  F(m->x); F(m->h); F(m->h32); F(m->qkv); F(m->attn); F(m->act); F(m->y); F(m->slot_expert); F(m->slot_w); F(m->part_w);
+  F(m->expert_count); F(m->expert_off); F(m->expert_cur); F(m->sorted_row); F(m->slot_pos); F(m->depth_dev);
+  F(m->anc_dev); F(m->rows_dev); F(m->stage);
+  delete m;
+  return VN_OK;
+}
+
+int32_t vn_model_load_tensor(vn_model* m, const char* name, const float* data, int32_t ndim, const int64_t* shape) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, name && data && shape && ndim >= 1 && ndim <= 2, "bad tensor argument");
+  const Config& c = m->cfg;
+  const std::string n(name);
+  const long long r = shape[0], cl = ndim == 2 ? shape[1] : 1;
+  const long long D = c.dim;
+  auto expect = [&](long long er, long long ec) -> bool { return r == er && cl == ec; };
+#define SHAPE(er, ec) VN_REQUIRE(ctx, expect((er), (ec)), "%s: shape (%lld, %lld) expected (%lld, %lld)", name, r, cl, (long long)(er), (long long)(ec))
+  if (n == "rope.cos" || n == "rope.sin") {
+    // optional override of the RoPE table with one computed by the caller (rows x head_dim/2, float32)
+    VN_REQUIRE(ctx, cl == c.hd / 2 && r >= 1, "%s: shape (%lld, %lld) expected (rows, %d)", name, r, cl, c.hd / 2);
+    float** dst = n == "rope.cos" ? &m->rope_cos : &m->rope_sin;
+    VN_REQUIRE(ctx, m->rope_rows == 0 || m->rope_rows == r || *dst == nullptr, "rope tables must have equal row counts");
+    if (*dst) { VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); VN_CUDA(ctx, cudaFree(*dst)); *dst = nullptr; }
+    TRY(dev_alloc(ctx, (void**)dst, (size_t)r * cl * 4));
+    VN_CUDA(ctx, cudaMemcpy(*dst, data, (size_t)r * cl * 4, cudaMemcpyHostToDevice));
+    m->rope_rows = (int)r;
+    return VN_OK;
+  }
+  else if (n == "tok_emb.weight") { SHAPE(c.vocab, D); TRY(upload(m, data, m->emb, r, cl, D)); }
+  else if (n == "head.weight") { SHAPE(c.vocab, D); if (!c.tie) TRY(upload(m, data, m->head, r, cl, D)); }
+  else if (n == "norm.weight") { SHAPE(D, 1); TRY(upload(m, data, m->norm_f, 1, D, D, 1, 0, true)); }
+  else if (n.rfind("blocks.", 0) == 0) {
+    const size_t dot = n.find('.', 7);
+    VN_REQUIRE(ctx, dot != std::string::npos, "bad tensor name %s", name);
+    const int li = atoi(n.substr(7, dot - 7).c_str());
+    if (li < 0 || li >= c.n_layer) return vn_fail(ctx, VN_ERR_INDEX, "%s: layer %d out of range", name, li);
+    Layer& L = m->layers[li];
+    const std::string rest = n.substr(dot + 1);
+    const long long qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
+    if (rest == "norm1.weight") { SHAPE(D, 1); TRY(upload(m, data, L.norm1, 1, D, D, 1, 0, true)); }
+    else if (rest == "norm2.weight") { SHAPE(D, 1); TRY(upload(m, data, L.norm2, 1, D, D, 1, 0, true)); }
+    else if (rest == "attn.gate_logits") { SHAPE(3, 1); memcpy(L.gate_logits, data, 12); }
+    else if (rest == "attn.wq.weight") { SHAPE(qd, D); TRY(upload(m, data, L.wqkv, r, cl, D, 1, 0)); }
+    else if (rest == "attn.wk.weight") { SHAPE(kvd, D); TRY(upload(m, data, L.wqkv, r, cl, D, 1, qd)); }
+    else if (rest == "attn.wv.weight") { SHAPE(kvd, D); TRY(upload(m, data, L.wqkv, r, cl, D, 1, qd + kvd)); }
+    else if (rest == "attn.proj.weight") { SHAPE(D, qd); TRY(upload(m, data, L.wproj, r, cl, qd)); }
+    else if (rest == "attn.global_tokens.weight") { SHAPE(c.n_sink, D); TRY(upload(m, data, L.sink, r, cl, D)); }
+    else if (L.kind == 0 && rest == "ffn.w_gate.weight") { SHAPE(c.mlp_hidden, D); TRY(upload(m, data, L.w_gateup, r, cl, D, 2, 0)); }
+    else if (L.kind == 0 && rest == "ffn.w_up.weight") { SHAPE(c.mlp_hidden, D); TRY(upload(m, data, L.w_gateup, r, cl, D, 2, 1)); }
+    else if (L.kind == 0 && rest == "ffn.w_down.weight") { SHAPE(D, c.mlp_hidden); TRY(upload(m, data, L.w_down, r, cl, c.mlp_hidden)); }
+    else if (L.kind == 1 && rest == "ffn.part_router.gate.weight") { SHAPE(c.P, D); TRY(upload(m, data, L.router, r, cl, D, 1, 0, true)); }
+    else if (L.kind == 1 && rest.rfind("ffn.parts.", 0) == 0) {
+      const size_t d2 = rest.find('.', 10);
+      VN_REQUIRE(ctx, d2 != std::string::npos, "bad tensor name %s", name);
+      const int p = atoi(rest.substr(10, d2 - 10).c_str());
+      if (p < 0 || p >= c.P) return vn_fail(ctx, VN_ERR_INDEX, "%s: part %d out of range", name, p);
+      const std::string r2 = rest.substr(d2 + 1);
+      const long long eh = c.expert_hidden;
+      if (r2 == "router.gate.weight") { SHAPE(c.E, D); TRY(upload(m, data, L.router, r, cl, D, 1, c.P + (long long)p * c.E, true)); }
+      else if (r2.rfind("experts.", 0) == 0) {
+        const size_t d3 = r2.find('.', 8);
+        VN_REQUIRE(ctx, d3 != std::string::npos, "bad tensor name %s", name);
+        const int ex = atoi(r2.substr(8, d3 - 8).c_str());
+        if (ex < 0 || ex >= c.E) return vn_fail(ctx, VN_ERR_INDEX, "%s: expert %d out of range", name, ex);
+        const std::string r3 = r2.substr(d3 + 1);
+        const long long ge = (long long)p * c.E + ex;
+        char* gu = (char*)L.e_gateup + (size_t)ge * 2 * eh * D * m->esz;
+        char* dn = (char*)L.e_down + (size_t)ge * D * eh * m->esz;
+        if (r3 == "w_gate.weight") { SHAPE(eh, D); TRY(upload(m, data, gu, r, cl, D, 2, 0)); }
+        else if (r3 == "w_up.weight") { SHAPE(eh, D); TRY(upload(m, data, gu, r, cl, D, 2, 1)); }
+        else if (r3 == "w_down.weight") { SHAPE(D, eh); TRY(upload(m, data, dn, r, cl, eh)); }
+        else return vn_fail(ctx, VN_ERR_INVALID, "unexpected tensor %s", name);
+      } else return vn_fail(ctx, VN_ERR_INVALID, "unexpected tensor %s", name);
+    } else return vn_fail(ctx, VN_ERR_INVALID, "unexpected tensor %s", name);
+  } else return vn_fail(ctx, VN_ERR_INVALID, "unexpected tensor %s", name);
+#undef SHAPE
+  m->loaded.insert(n);
+  m->finalized = false;
+  return VN_OK;
+}
+
+int32_t vn_model_finalize(vn_model* m) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  const Config& c = m->cfg;
+  // every tensor of the reference's state_dict must have arrived (head.weight may be omitted when tied)
+  std::vector<std::string> want = {"tok_emb.weight", "norm.weight"};
+  if (!c.tie) want.push_back("head.weight");
+  for (int i = 0; i < c.n_layer; ++i) {
+    const std::string p = "blocks." + std::to_string(i) + ".";
+    for (const char* s : {"norm1.weight", "norm2.weight", "attn.gate_logits", "attn.wq.weight", "attn.wk.weight",
+                          "attn.wv.weight", "attn.proj.weight", "attn.global_tokens.weight"})
+      want.push_back(p + s);
+    if (c.kind[i] == 0) {
+      for (const char* s : {"ffn.w_gate.weight", "ffn.w_up.weight", "ffn.w_down.weight"}) want.push_back(p + s);
+    } else {
+      want.push_back(p + "ffn.part_router.gate.weight");
+      for (int q = 0; q < c.P; ++q) {
+        const std::string pp = p + "ffn.parts." + std::to_string(q) + ".";
+        want.push_back(pp + "router.gate.weight");
+        for (int e = 0; e < c.E; ++e)
+          for (const char* s : {"w_gate.weight", "w_up.weight", "w_down.weight"})
+            want.push_back(pp + "experts." + std::to_string(e) + "." + s);
+      }
+    }
+  }
+  for (auto& w : want)
+    if (!m->loaded.count(w)) return vn_fail(ctx, VN_ERR_INVALID, "missing tensor %s", w.c_str());
+  // RoPE table, built on the host in float32 exactly as the reference does (tri_sparse_attn.py:169-180)
+  if (c.use_rope && (!m->rope_cos || !m->rope_sin)) {
+    if (m->rope_cos) { cudaFree(m->rope_cos); m->rope_cos = nullptr; }
+    if (m->rope_sin) { cudaFree(m->rope_sin); m->rope_sin = nullptr; }
+    const int half = c.hd / 2, rows = std::max(c.max_seq_len, 16) * 2;
+    std::vector<float> cs((size_t)rows * half), sn((size_t)rows * half);
+    for (int j = 0; j < half; ++j) {
+      // float32 throughout, as NumPy evaluates 1.0 / (theta ** (2.0 * i / head_dim)) on a float32 arange
+      const float ex = (2.0f * (float)j) / (float)c.hd;
+      const float inv = 1.0f / powf((float)c.rope_theta, ex);
+      for (int p = 0; p < rows; ++p) {
+        const float ang = (float)p * inv;  // np.outer of two float32 arrays
+        cs[(size_t)p * half + j] = cosf(ang);
+        sn[(size_t)p * half + j] = sinf(ang);
+      }
+    }
+    TRY(dev_alloc(ctx, (void**)&m->rope_cos, cs.size() * 4));
+    TRY(dev_alloc(ctx, (void**)&m->rope_sin, sn.size() * 4));
+    VN_CUDA(ctx, cudaMemcpy(m->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+    VN_CUDA(ctx, cudaMemcpy(m->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+    m->rope_rows = rows;
+  }
+  // sink K / V = wk(global_tokens), wv(global_tokens): fixed per layer (tri_sparse_attn.py:223-242)
+  const long long D = c.dim, qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
+  for (auto& L : m->layers) {
+    for (int which = 0; which < 2; ++which) {
+      GemmArgs g;
+      g.A = L.sink; g.lda = D;
+      g.W = (char*)L.wqkv + (size_t)(qd + which * kvd) * D * m->esz; g.ldw = D;
+      g.C = which ? L.sink_v : L.sink_k; g.ldc = kvd; g.M = c.n_sink; g.N = (int)kvd; g.K = (int)D; g.c_bf16 = c.bf16;
+      if (c.bf16) TRY((launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g)));
+      else TRY((launch_gemm_simt<float, float>(ctx, g)));
+    }
+  }
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  m->finalized = true;
+  return VN_OK;
+}
+
+int32_t vn_model_quantize(vn_model* m, const char* scheme) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
+  return vn_fail(m->ctx, VN_ERR_UNSUPPORTED, "quantisation scheme %s is not built yet", scheme ? scheme : "(null)");
+}
+
+int32_t vn_model_param_bytes(vn_model* m, uint64_t* out) {
+  if (!m || !out) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  *out = m->param_bytes;
+  return VN_OK;
+}
+
+int32_t vn_kv_create(vn_model* m, int32_t max_batch, int32_t max_seq, vn_kv** out) {
+  if (!m || !out) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, max_batch >= 1 && max_seq >= 1, "max_batch and max_seq must be positive");
+  vn_kv* kv = new vn_kv();
+  kv->m = m; kv->max_batch = max_batch; kv->max_seq = max_seq;
+  const size_t plane = (size_t)max_batch * max_seq * m->cfg.n_kv * m->cfg.hd * m->esz;
+  std::vector<void*> planes;
+  for (int i = 0; i < m->cfg.n_layer; ++i) {
+    void *k = nullptr, *v = nullptr;
+    if (cudaMalloc(&k, plane) != cudaSuccess || cudaMalloc(&v, plane) != cudaSuccess) {
+      if (k) cudaFree(k);
+      vn_kv_destroy(kv);
+      return vn_fail(ctx, VN_ERR_OOM, "KV cache allocation of %zu bytes per plane failed", plane);
+    }
+    kv->k.push_back(k); kv->v.push_back(v);
+    planes.push_back(k); planes.push_back(v);
+  }
+  TRY(dev_alloc(ctx, (void**)&kv->planes_dev, planes.size() * sizeof(void*)));
+  VN_CUDA(ctx, cudaMemcpy(kv->planes_dev, planes.data(), planes.size() * sizeof(void*), cudaMemcpyHostToDevice));
+  TRY(dev_alloc(ctx, (void**)&kv->lens, (size_t)max_batch * 4));
+  VN_CUDA(ctx, cudaMemset(kv->lens, 0, (size_t)max_batch * 4));
+  kv->len_ub.assign(max_batch, 0);
+  *out = kv;
+  return VN_OK;
+}
+
+int32_t vn_kv_destroy(vn_kv* kv) {
+  if (!kv) return VN_OK;
+  cudaSetDevice(kv->m->ctx->device);
+  cudaStreamSynchronize(kv->m->ctx->stream);
+  for (void* p : kv->k) cudaFree(p);
+  for (void* p : kv->v) cudaFree(p);
+  if (kv->planes_dev) cudaFree(kv->planes_dev);
+  if (kv->lens) cudaFree(kv->lens);
+  delete kv;
+  return VN_OK;
+}
+
+int32_t vn_kv_lengths(vn_kv* kv, int32_t* out_host) {
+  if (!kv || !out_host) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_ctx* ctx = kv->m->ctx;
+  VN_CHECK_CTX(ctx);
+  VN_CUDA(ctx, cudaMemcpyAsync(out_host, kv->lens, (size_t)kv->max_batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (int b = 0; b < kv->max_batch; ++b) kv->len_ub[b] = out_host[b];
+  return VN_OK;
+}
+
+int32_t vn_kv_set_lengths(vn_kv* kv, const int32_t* lens_host) {
+  if (!kv || !lens_host) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_ctx* ctx = kv->m->ctx;
+  VN_CHECK_CTX(ctx);
+  for (int b = 0; b < kv->max_batch; ++b)
+    if (lens_host[b] < 0 || lens_host[b] > kv->max_seq)
+      return vn_fail(ctx, VN_ERR_OVERFLOW, "length %d of sequence %d outside [0, %d]", lens_host[b], b, kv->max_seq);
+  VN_CUDA(ctx, cudaMemcpyAsync(kv->lens, lens_host, (size_t)kv->max_batch * 4, cudaMemcpyHostToDevice, ctx->stream));
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (int b = 0; b < kv->max_batch; ++b) kv->len_ub[b] = lens_host[b];
+  return VN_OK;
+}
+
+int32_t vn_kv_reset_seq(vn_kv* kv, int32_t seq) {
+  if (!kv) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_ctx* ctx = kv->m->ctx;
+  VN_CHECK_CTX(ctx);
+  if (seq >= kv->max_batch) return vn_fail(ctx, VN_ERR_INDEX, "sequence %d out of range (%d)", seq, kv->max_batch);
+  if (seq < 0) {
+    VN_CUDA(ctx, cudaMemsetAsync(kv->lens, 0, (size_t)kv->max_batch * 4, ctx->stream));
+    std::fill(kv->len_ub.begin(), kv->len_ub.end(), 0);
+  } else {
+    VN_CUDA(ctx, cudaMemsetAsync(kv->lens + seq, 0, 4, ctx->stream));
+    kv->len_ub[seq] = 0;
+  }
+  return VN_OK;
+}
+
+int32_t vn_kv_commit(vn_kv* kv, int32_t n_new, const int32_t* keep_idx_dev, int32_t stride, const int32_t* n_keep_dev,
+                     int32_t keep_add) {
+  if (!kv || !n_keep_dev) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_model* m = kv->m;
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, n_new >= 0 && n_new <= 4096, "n_new out of range");
+  const int B = kv->max_batch;
+  if (n_new == 0) return VN_OK;
+  if (keep_idx_dev) {
+    VN_REQUIRE(ctx, stride >= 1, "stride must be positive");
+    const int row_elems = m->cfg.n_kv * m->cfg.hd;
+    const size_t smem = (size_t)n_new * row_elems * m->esz;
+    VN_REQUIRE(ctx, smem <= 200 * 1024, "tree of %d nodes too large to compact in shared memory", n_new);
+    dim3 grid(B, 2 * m->cfg.n_layer);
+    if (m->cfg.bf16) {
+      if (smem > 48 * 1024)
+        VN_CUDA(ctx, cudaFuncSetAttribute(kv_commit_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      VN_LAUNCH(ctx, kv_commit_kernel<__nv_bfloat16>, grid, 256, smem, (__nv_bfloat16* const*)kv->planes_dev, kv->lens,
+                keep_idx_dev, stride, n_keep_dev, keep_add, n_new, kv->max_seq, row_elems);
+    } else {
+      if (smem > 48 * 1024)
+        VN_CUDA(ctx, cudaFuncSetAttribute(kv_commit_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      VN_LAUNCH(ctx, kv_commit_kernel<float>, grid, 256, smem, (float* const*)kv->planes_dev, kv->lens, keep_idx_dev, stride,
+                n_keep_dev, keep_add, n_new, kv->max_seq, row_elems);
+    }
+  }
+  VN_LAUNCH(ctx, kv_advance_kernel, ceil_div(B, 128), 128, 0, kv->lens, n_keep_dev, keep_add, n_new, kv->max_seq, B);
+  for (int b = 0; b < B; ++b) kv->len_ub[b] = std::min(kv->len_ub[b] + n_new, kv->max_seq);
+  return VN_OK;
+}
+
+int32_t vn_kv_read(vn_kv* kv, int32_t layer, int32_t seq, int32_t which, float* out_host, int32_t n_positions) {
+  if (!kv || !out_host) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_model* m = kv->m;
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  if (layer < 0 || layer >= m->cfg.n_layer) return vn_fail(ctx, VN_ERR_INDEX, "layer %d out of range (%d)", layer, m->cfg.n_layer);
+  if (seq < 0 || seq >= kv->max_batch) return vn_fail(ctx, VN_ERR_INDEX, "sequence %d out of range (%d)", seq, kv->max_batch);
+  VN_REQUIRE(ctx, n_positions >= 0 && n_positions <= kv->max_seq, "n_positions out of range");
+  const size_t row = (size_t)m->cfg.n_kv * m->cfg.hd, n = row * n_positions;
+  const char* src = (const char*)(which ? kv->v[layer] : kv->k[layer]) + (size_t)seq * kv->max_seq * row * m->esz;
+  if (!m->cfg.bf16) {
+    VN_CUDA(ctx, cudaMemcpyAsync(out_host, src, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  } else {
+    std::vector<uint16_t> tmp(n);
+    VN_CUDA(ctx, cudaMemcpyAsync(tmp.data(), src, n * 2, cudaMemcpyDeviceToHost, ctx->stream));
+    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (size_t i = 0; i < n; ++i) { uint32_t u = (uint32_t)tmp[i] << 16; memcpy(out_host + i, &u, 4); }
+  }
+  return VN_OK;
+}
+
+int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int32_t B, int32_t T,
+                         const int32_t* parents_host, float* out_hidden_dev, float* out_logits_dev, int32_t last_only,
+                         int32_t slot_offset) {
+  if (!m || !kv) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, m->finalized, "vn_model_finalize has not been called");
+  VN_REQUIRE(ctx, kv->m == m, "KV cache belongs to another model");
+  VN_REQUIRE(ctx, tokens_dev && B >= 1 && T >= 1, "bad arguments");
+  VN_REQUIRE(ctx, B <= kv->max_batch, "batch %d exceeds the cache's max_batch %d", B, kv->max_batch);
+  VN_REQUIRE(ctx, (long long)B * T < (1ll << 24), "too many rows");
+  VN_REQUIRE(ctx, slot_offset >= 0, "slot_offset must be non-negative");
+  // capacity: conservative host bound first, exact lengths only when that trips
+  const int limit = m->cfg.use_rope ? std::min(kv->max_seq, m->rope_rows) : kv->max_seq;
+  bool over = false;
+  for (int b = 0; b < B; ++b) over |= kv->len_ub[b] + slot_offset + T > limit;
+  if (over) {
+    std::vector<int32_t> lens(kv->max_batch);
+    TRY(vn_kv_lengths(kv, lens.data()));
+    for (int b = 0; b < B; ++b)
+      if (lens[b] + slot_offset + T > limit)
+        return vn_fail(ctx, VN_ERR_OVERFLOW, "KV cache overflow: sequence %d holds %d, +%d exceeds the capacity %d", b,
+                       lens[b] + slot_offset, T, limit);
+  }
+  const bool tree = parents_host != nullptr;
+  if (tree) {
+    VN_REQUIRE(ctx, T <= 64, "a tree may have at most 64 nodes, got %d", T);
+    std::vector<int> depth(T);
+    std::vector<unsigned long long> anc(T);
+    for (int i = 0; i < T; ++i) {
+      const int p = parents_host[i];
+      VN_REQUIRE(ctx, p >= -1 && p < i, "parents[%d] = %d is not an earlier node", i, p);
+      depth[i] = p < 0 ? 0 : depth[p] + 1;
+      anc[i] = (1ull << i) | (p < 0 ? 0ull : anc[p]);
+    }
+    if (!m->depth_dev) {
+      TRY(dev_alloc(ctx, (void**)&m->depth_dev, 64 * 4));
+      TRY(dev_alloc(ctx, (void**)&m->anc_dev, 64 * 8));
+    }
+    VN_CUDA(ctx, cudaMemcpyAsync(m->depth_dev, depth.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
+    VN_CUDA(ctx, cudaMemcpyAsync(m->anc_dev, anc.data(), T * 8, cudaMemcpyHostToDevice, ctx->stream));
+    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  }
+  TRY(ensure_rows(m, B * T));
+  if (m->cfg.bf16) return forward_t<__nv_bfloat16>(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
+  return forward_t<float>(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
+}
+
+}  // extern "C"

@@ -1,0 +1,450 @@
+// Device kernels of the VerseNexLM forward other than the GEMMs: embedding, RMSNorm, RoPE + KV append,
+// TriSparse attention over the KV cache (window / sinks / ALiBi paths, tree ancestor mask), MoD routing,
+// expert combine, KV commit.
+#pragma once
+#include "common.cuh"
+#include "gemm.cuh"
+#include <math_constants.h>
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- weight staging: fp32 host rows -> storage dtype, with a row map (dst_row = src_row * mul + off)
+template <typename T>
+__global__ void convert_rows_kernel(const float* __restrict__ src, T* __restrict__ dst, long long rows,
+                                    long long cols, long long dst_ld, long long row_mul, long long row_off) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * cols) return;
+  const long long r = i / cols, c = i % cols;
+  dst[(r * row_mul + row_off) * dst_ld + c] = from_f<T>(src[i]);
+}
+
+// ---- embedding gather (verse_torch/vnnn.py:453-460) + optional sqrt(dim) scale (base_model.py:201-203)
+template <typename T>
+__global__ void embed_kernel(const long long* __restrict__ tokens, const T* __restrict__ emb, float* __restrict__ x,
+                             int D, int V, float scale, int* __restrict__ status) {
+  const int row = blockIdx.x;
+  long long tok = tokens[row];
+  if (tok < 0 || tok >= V) {  // record and clamp: never read outside the table
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    tok = tok < 0 ? 0 : V - 1;
+  }
+  const T* e = emb + tok * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) x[(long long)row * D + d] = to_f<T>(e[d]) * scale;
+}
+
+// ---- RMSNorm: y = x / sqrt(mean(x^2) + eps) * w (vnnn.py:501-505).  Optional row gather, optional fp32 copy.
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                      T* __restrict__ y, float* __restrict__ y32,
+                                                      const int* __restrict__ rows, int D, float eps) {
+  __shared__ float sm[8];
+  const long long src = rows ? rows[blockIdx.x] : blockIdx.x;
+  const float* xr = x + src * D;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += 256) ss += xr[d] * xr[d];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += sm[i];
+  const float r = sqrtf(tot / (float)D + eps);
+  for (int d = threadIdx.x; d < D; d += 256) {
+    const float v = xr[d] / r * w[d];
+    if (y) y[(long long)blockIdx.x * D + d] = from_f<T>(v);
+    if (y32) y32[(long long)blockIdx.x * D + d] = v;
+  }
+}
+
+// ---- RoPE on q and k (tri_sparse_attn.py:182-206: x*cos + rotate_half(x)*sin, table built on the host in
+// float32 exactly as :169-180) and append of k, v to the cache at slot len[b] + t.
+// qkv: [M, (H + 2*n_kv) * hd] fp32 (q | k | v); q is rotated in place.
+template <typename T>
+__global__ void rope_append_kernel(float* __restrict__ qkv, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, const int* __restrict__ lens,
+                                   const int* __restrict__ depth, T* __restrict__ kc, T* __restrict__ vc, int Tn,
+                                   int H, int n_kv, int hd, int max_seq, int use_rope, int rope_rows, int slot_offset) {
+  const int row = blockIdx.x, b = row / Tn, t = row % Tn;
+  const int len = lens[b] + slot_offset;
+  const int pos = len + (depth ? depth[t] : t);
+  const int slot = len + t;
+  const int half = hd / 2;
+  const int ld = (H + 2 * n_kv) * hd;
+  float* r = qkv + (long long)row * ld;
+  const int p = pos < rope_rows ? pos : rope_rows - 1;
+  // q and k heads: pairs (j, j + half)
+  const int n_rot = (H + n_kv) * half;
+  for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
+    const int head = i / half, j = i % half;
+    float x1 = r[head * hd + j], x2 = r[head * hd + half + j];
+    float o1 = x1, o2 = x2;
+    if (use_rope) {
+      const float c = cos_t[(long long)p * half + j], s = sin_t[(long long)p * half + j];
+      o1 = x1 * c + (-x2) * s;
+      o2 = x2 * c + x1 * s;
+    }
+    if (head < H) {
+      r[head * hd + j] = o1;
+      r[head * hd + half + j] = o2;
+    } else if (slot < max_seq) {
+      const int kh = head - H;
+      T* dst = kc + (((long long)b * max_seq + slot) * n_kv + kh) * hd;
+      dst[j] = from_f<T>(o1);
+      dst[half + j] = from_f<T>(o2);
+    }
+  }
+  if (slot < max_seq) {
+    const float* v = r + (H + n_kv) * hd;
+    T* dst = vc + ((long long)b * max_seq + slot) * n_kv * hd;
+    for (int i = threadIdx.x; i < n_kv * hd; i += blockDim.x) dst[i] = from_f<T>(v[i]);
+  }
+}
+
+// ---- TriSparse attention (tri_sparse_attn.py:536-613) on top of the cache -------------------------------
+struct AttnArgs {
+  const float* q;        // [M, ld_q] fp32, head h at offset h*hd
+  int ld_q;
+  const void* kc;        // [B, max_seq, n_kv, hd]
+  const void* vc;
+  const void* sink_k;    // [n_sink, n_kv, hd]
+  const void* sink_v;
+  void* out;             // [M, H*hd] storage dtype
+  const int* lens;       // [B] committed length per sequence
+  const int* depth;      // [T] or null (chain: depth = t)
+  const unsigned long long* anc;  // [T] ancestor-or-self bit mask over new slots, or null (chain: causal)
+  int Tn, H, n_kv, hd, max_seq, window, n_sink, slot_offset;
+  int use_alibi, alibi_max;
+  float g_a, g_b, g_c;   // sigmoid(gate_logits)
+  float scale;
+};
+
+// online-softmax state of one 8-lane group: running max, running sum, 8 output dims per lane
+struct GroupAcc {
+  float m, l, o[8];
+  __device__ __forceinline__ void init() {
+    m = -CUDART_INF_F; l = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = 0.f;
+  }
+  __device__ __forceinline__ void push(float s, const float* v) {
+    const float nm = fmaxf(m, s);
+    const float c = expf(m - nm), e = expf(s - nm);
+    l = l * c + e;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = o[i] * c + e * v[i];
+    m = nm;
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float* out);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* out) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* out) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
+}
+
+// merge the 4 groups of a warp (lanes g*8 + i own dims i*? .. see below) and return the normalised output of the
+// calling lane's dims; all lanes participate
+__device__ __forceinline__ void merge_groups(GroupAcc& a) {
+#pragma unroll
+  for (int o = 8; o <= 16; o <<= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, a.m, o);
+    const float ol = __shfl_xor_sync(0xffffffffu, a.l, o);
+    const float nm = fmaxf(a.m, om);
+    const float c1 = (a.m == -CUDART_INF_F) ? 0.f : expf(a.m - nm);
+    const float c2 = (om == -CUDART_INF_F) ? 0.f : expf(om - nm);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float oo = __shfl_xor_sync(0xffffffffu, a.o[i], o);
+      a.o[i] = a.o[i] * c1 + oo * c2;
+    }
+    a.l = a.l * c1 + ol * c2;
+    a.m = nm;
+  }
+}
+
+// One warp per (query row, head).  The warp is 4 groups of 8 lanes; a group scores one key at a time, each
+// lane owning head dims [8*li, 8*li+8) with li = lane % 8 (head_dim 64) -- keys are strided over the groups.
+// head_dim must be 64 (8 lanes x 8) or 32 (only 4 lanes of a group active) ... generalised by HD8 = hd / 8 <= 8.
+template <typename T>
+__global__ void __launch_bounds__(256) trisparse_attn_kernel(AttnArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane >> 3, li = lane & 7;
+  const int wid = blockIdx.x * 8 + warp;           // (row, head) index
+  const int M = gridDim.y;                          // unused; rows come from blockIdx.y
+  (void)M;
+  const int row = blockIdx.y;
+  const int h = wid;
+  if (h >= a.H) return;
+  const int b = row / a.Tn, t = row % a.Tn;
+  const int hd = a.hd;
+  const int hd8 = hd >> 3;                          // lanes of a group that carry dims
+  const bool active = li < hd8;
+  const int len = a.lens[b] + a.slot_offset;
+  const int my_depth = a.depth ? a.depth[t] : t;
+  const int pos = len + my_depth;
+  const int kvh = h / (a.H / a.n_kv);
+  const T* kc = reinterpret_cast<const T*>(a.kc) + ((long long)b * a.max_seq * a.n_kv + kvh) * hd;
+  const T* vc = reinterpret_cast<const T*>(a.vc) + ((long long)b * a.max_seq * a.n_kv + kvh) * hd;
+  const long long kstride = (long long)a.n_kv * hd;
+  float q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = active ? a.q[(long long)row * a.ld_q + h * hd + li * 8 + i] : 0.f;
+  const unsigned long long anc = a.anc ? a.anc[t] : 0ull;
+
+  auto score = [&](const T* kr) {
+    float kv[8];
+    float s = 0.f;
+    if (active) {
+      load8<T>(kr + li * 8, kv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s = fmaf(q[i], kv[i], s);
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    return s * a.scale;
+  };
+  auto value = [&](const T* vr, float* v) {
+    if (active) load8<T>(vr + li * 8, v);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+  };
+
+  float out[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out[i] = 0.f;
+
+  // total keys this query may see through paths A / C: cached [0, len) and new slots
+  const int n_new = a.Tn;
+  // ---- path A: sliding window, causal (tri_sparse_attn.py:341-346) ---------------------------------
+  {
+    GroupAcc acc; acc.init();
+    const int lo = max(0, pos - a.window + 1);
+    for (int j = lo + grp; j < len; j += 4) {        // cached keys: position == slot
+      const float s = score(kc + (long long)j * kstride);
+      float v[8]; value(vc + (long long)j * kstride, v);
+      acc.push(s, v);
+    }
+    for (int n = grp; n < n_new; n += 4) {           // keys appended by this call
+      const bool vis = a.anc ? ((anc >> n) & 1ull) : (n <= t);
+      const int pn = len + (a.depth ? a.depth[n] : n);
+      if (!vis || pos - pn >= a.window || pn > pos) continue;
+      const float s = score(kc + (long long)(len + n) * kstride);
+      float v[8]; value(vc + (long long)(len + n) * kstride, v);
+      acc.push(s, v);
+    }
+    merge_groups(acc);
+    const float inv = acc.l > 0.f ? a.g_a / acc.l : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] += acc.o[i] * inv;
+  }
+  // ---- path B: global sink tokens, no mask, keys never rotated (:461-483, :223-242) -----------------
+  {
+    GroupAcc acc; acc.init();
+    const T* sk = reinterpret_cast<const T*>(a.sink_k) + (long long)kvh * hd;
+    const T* sv = reinterpret_cast<const T*>(a.sink_v) + (long long)kvh * hd;
+    for (int j = grp; j < a.n_sink; j += 4) {
+      const float s = score(sk + (long long)j * kstride);
+      float v[8]; value(sv + (long long)j * kstride, v);
+      acc.push(s, v);
+    }
+    merge_groups(acc);
+    const float inv = acc.l > 0.f ? a.g_b / acc.l : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] += acc.o[i] * inv;
+  }
+  // ---- path C: full causal + ALiBi bias -slope_h * (i - j), only while T_k <= 1024 (:489-530, :600) --
+  const int tk_eff = a.anc ? (pos + 1) : (len + n_new);
+  if (a.use_alibi && tk_eff <= a.alibi_max) {
+    GroupAcc acc; acc.init();
+    const float slope = 1.0f / exp2f((float)(h + 1) / (float)a.H);
+    for (int j = grp; j < len; j += 4) {
+      const float s = score(kc + (long long)j * kstride) - slope * (float)(pos - j);
+      float v[8]; value(vc + (long long)j * kstride, v);
+      acc.push(s, v);
+    }
+    for (int n = grp; n < n_new; n += 4) {
+      const bool vis = a.anc ? ((anc >> n) & 1ull) : (n <= t);
+      const int pn = len + (a.depth ? a.depth[n] : n);
+      if (!vis || pn > pos) continue;
+      const float s = score(kc + (long long)(len + n) * kstride) - slope * (float)(pos - pn);
+      float v[8]; value(vc + (long long)(len + n) * kstride, v);
+      acc.push(s, v);
+    }
+    merge_groups(acc);
+    const float inv = acc.l > 0.f ? a.g_c / acc.l : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] += acc.o[i] * inv;
+  }
+  if (grp == 0 && active) {
+    T* o = reinterpret_cast<T*>(a.out) + (long long)row * a.H * hd + h * hd + li * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = from_f<T>(out[i]);
+  }
+}
+
+// ---- MoD routing (mod.py:340-387, :748-770) ----------------------------------------------------------
+// One warp per token.  Part router: softmax over all P part logits.  Expert router of every part: top-k on the
+// logits (ties -> lower index first), softmax over the kept logits.  Slot s = p*top_k + j of a token holds
+// (global expert id, weight of that expert, weight of the part), with the experts of a part in ascending id.
+struct RouteArgs {
+  const float* h;        // [M, D] fp32 normalised activations
+  const float* gates;    // [(P + P*E), D] fp32: part router rows, then E rows per part
+  int* slot_expert;      // [M, P*top_k]
+  float* slot_w;         // [M, P*top_k] expert weight
+  float* part_w;         // [M, P]
+  int* expert_count;     // [P*E], zeroed before the launch
+  int M, D, P, E, top_k;
+};
+
+__global__ void __launch_bounds__(128) mod_route_kernel(RouteArgs r) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + warp;
+  if (row >= r.M) return;
+  const int n_logit = r.P + r.P * r.E;       // <= 64 supported
+  const float* x = r.h + (long long)row * r.D;
+  float lg[64];
+  for (int g = 0; g < n_logit; ++g) {
+    const float* w = r.gates + (long long)g * r.D;
+    float s = 0.f;
+    for (int d = lane; d < r.D; d += 32) s = fmaf(x[d], w[d], s);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    lg[g] = s;
+  }
+  if (lane != 0) return;
+  // part weights: softmax over all parts
+  float m = -CUDART_INF_F;
+  for (int p = 0; p < r.P; ++p) m = fmaxf(m, lg[p]);
+  float den = 0.f;
+  for (int p = 0; p < r.P; ++p) den += expf(lg[p] - m);
+  for (int p = 0; p < r.P; ++p) r.part_w[(long long)row * r.P + p] = expf(lg[p] - m) / den;
+  for (int p = 0; p < r.P; ++p) {
+    const float* el = lg + r.P + p * r.E;
+    int sel[8]; float sl[8];
+    unsigned long long used = 0ull;
+    for (int j = 0; j < r.top_k; ++j) {        // repeated argmax, lowest index on ties
+      int best = -1; float bv = -CUDART_INF_F;
+      for (int e = 0; e < r.E; ++e)
+        if (!((used >> e) & 1ull) && (best < 0 || el[e] > bv)) { best = e; bv = el[e]; }
+      used |= 1ull << best;
+      sel[j] = best; sl[j] = bv;
+    }
+    float em = sl[0];
+    float ed = 0.f;
+    for (int j = 0; j < r.top_k; ++j) ed += expf(sl[j] - em);
+    // ascending expert id inside the part
+    for (int i = 1; i < r.top_k; ++i)
+      for (int j = i; j > 0 && sel[j - 1] > sel[j]; --j) {
+        const int ti = sel[j]; sel[j] = sel[j - 1]; sel[j - 1] = ti;
+        const float tf = sl[j]; sl[j] = sl[j - 1]; sl[j - 1] = tf;
+      }
+    for (int j = 0; j < r.top_k; ++j) {
+      const long long s = (long long)row * r.P * r.top_k + p * r.top_k + j;
+      const int ge = p * r.E + sel[j];
+      r.slot_expert[s] = ge;
+      r.slot_w[s] = expf(sl[j] - em) / ed;
+      atomicAdd(&r.expert_count[ge], 1);
+    }
+  }
+}
+
+// exclusive prefix over the expert counts; resets the fill cursors
+__global__ void mod_offsets_kernel(const int* __restrict__ count, int* __restrict__ offset, int* __restrict__ cursor,
+                                   int n_expert) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < n_expert; ++e) { offset[e] = acc; acc += count[e]; cursor[e] = 0; }
+  }
+}
+
+// place every (token, slot) in its expert's segment; sorted_row[pos] = token row, slot_pos[token, slot] = pos
+__global__ void mod_scatter_kernel(const int* __restrict__ slot_expert, const int* __restrict__ offset,
+                                   int* __restrict__ cursor, int* __restrict__ sorted_row, int* __restrict__ slot_pos,
+                                   int n_slots_total, int S) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_slots_total) return;
+  const int e = slot_expert[i];
+  const int pos = offset[e] + atomicAdd(&cursor[e], 1);
+  sorted_row[pos] = i / S;
+  slot_pos[i] = pos;
+}
+
+// x[row] += sum_p part_w[p] * (sum_j slot_w[p, j] * y[slot_pos[p, j]])   (mod.py:196-211, :604-605, :779-781)
+__global__ void mod_combine_kernel(float* __restrict__ x, const float* __restrict__ y, const int* __restrict__ slot_pos,
+                                   const float* __restrict__ slot_w, const float* __restrict__ part_w, int D, int P,
+                                   int top_k) {
+  const int row = blockIdx.x;
+  const int S = P * top_k;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float out = 0.f;
+    for (int p = 0; p < P; ++p) {
+      float comb = 0.f;
+      for (int j = 0; j < top_k; ++j) {
+        const long long s = (long long)row * S + p * top_k + j;
+        comb += y[(long long)slot_pos[s] * D + d] * slot_w[s];
+      }
+      out += comb * part_w[(long long)row * P + p];
+    }
+    x[(long long)row * D + d] += out;
+  }
+}
+
+// ---- KV commit / rollback: compact the kept slots of the last forward behind the committed prefix ---------
+// grid (B, layers*2): one CTA moves the kept rows of one sequence in one K or V plane through shared memory.
+template <typename T>
+__global__ void kv_commit_kernel(T* const* __restrict__ planes, const int* __restrict__ lens,
+                                 const int* __restrict__ keep_idx, int stride, const int* __restrict__ n_keep, int keep_add,
+                                 int n_new, int max_seq, int row_elems) {
+  extern __shared__ unsigned char smem_raw[];
+  T* sm = reinterpret_cast<T*>(smem_raw);
+  const int b = blockIdx.x;
+  T* plane = planes[blockIdx.y] + (long long)b * max_seq * row_elems;
+  const int len = lens[b];
+  int nk = n_keep[b] + keep_add;
+  nk = nk < 0 ? 0 : (nk > n_new ? n_new : nk);
+  for (int i = 0; i < nk; ++i) {
+    int src = keep_idx[b * stride + i];
+    src = src < 0 ? 0 : (src >= n_new ? n_new - 1 : src);
+    const T* s = plane + (long long)(len + src) * row_elems;
+    for (int e = threadIdx.x; e < row_elems; e += blockDim.x) sm[i * row_elems + e] = s[e];
+  }
+  __syncthreads();
+  for (int i = 0; i < nk; ++i) {
+    T* d = plane + (long long)(len + i) * row_elems;
+    for (int e = threadIdx.x; e < row_elems; e += blockDim.x) d[e] = sm[i * row_elems + e];
+  }
+}
+
+__global__ void kv_advance_kernel(int* __restrict__ lens, const int* __restrict__ n_keep, int keep_add, int n_new, int max_seq, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  int nk = n_keep[b] + keep_add;
+  nk = nk < 0 ? 0 : (nk > n_new ? n_new : nk);
+  const int nl = lens[b] + nk;
+  lens[b] = nl > max_seq ? max_seq : nl;
+}
+
+// gather rows of a [rows, D] fp32 matrix
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows, float* __restrict__ dst,
+                                   int D) {
+  const long long s = rows[blockIdx.x];
+  for (int d = threadIdx.x; d < D; d += blockDim.x) dst[(long long)blockIdx.x * D + d] = src[s * D + d];
+}

@@ -1,0 +1,154 @@
+"""Batched speculative decoding with a draft MODEL: draft -> verify -> accept -> commit.
+
+The reference composes this loop on the host from `VerseNexLM.forward` and
+`SpeculativeDecoder.verify_then_commit` (verse_nex/speculative.py:230-310),
+re-running the whole context every round and serving batch row 0 only.
+Here both models keep KV caches on the device, every request of the batch
+advances each round, and a round issues no host synchronisation: proposals,
+acceptance results, the last committed tokens and the cache lengths all stay
+in device memory (`vn_spec_gather`, `vn_accept`, `vn_spec_advance`,
+`vn_kv_commit`).
+
+Cache protocol.  With s the committed tokens of a request, at the start of a
+round the target cache holds s[:-1] and the draft cache s[:-2].  The draft
+first consumes (s[-2], s[-1]) in one forward, then its own proposals one at a
+time; the target scores (s[-1], d_0 .. d_{k-1}) in one forward.  If n tokens
+are committed, both caches keep the first n entries they appended this round
+and drop the rest.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+
+from .device import DeviceArray
+from .model import VerseNexLM, _ptr
+
+PURPOSE_DRAFT = 2  # Philox purpose of the draft model's own sampling (0 / 1: accept test / resample)
+
+
+class SpecEngine:
+    def __init__(self, target: VerseNexLM, draft: VerseNexLM, max_batch: int, max_seq: int, k: int = 4,
+                 temperature: float = 0.0, top_k: int = 0, seed: int = 0, bonus: bool = True,
+                 max_new_tokens: int = 4096):
+        if target.vocab_size != draft.vocab_size:
+            raise ValueError("target and draft must share the vocabulary")
+        if target.ctx is not draft.ctx:
+            raise ValueError("target and draft must live on the same device")
+        if k < 1 or k > 16:
+            raise ValueError("k must be in [1, 16]")
+        self.target, self.draft, self.ctx = target, draft, target.ctx
+        self.B, self.k, self.V = int(max_batch), int(k), target.vocab_size
+        self.temperature, self.top_k, self.seed, self.bonus = float(temperature), int(top_k or 0), int(seed), bool(bonus)
+        self.n_verify = self.k + 1 if self.bonus else self.k
+        self.t_cache = target.new_cache(self.B, max_seq)
+        self.d_cache = draft.new_cache(self.B, max_seq)
+        ctx, B, k, V = self.ctx, self.B, self.k, self.V
+        self.cap = int(max_new_tokens) + k + 1
+        self.pair = ctx.zeros((B, 2), np.int64)
+        self.step_tokens = ctx.zeros((k, B), np.int64)
+        self.draft_tokens = ctx.zeros((B, k), np.int64)
+        self.verify_tokens = ctx.zeros((B, self.n_verify), np.int64)
+        self.q_logits = ctx.empty((k, B, V), np.float32)          # step-major: row (b, i) at (i*B + b) * V
+        self.p_logits = ctx.empty((B, self.n_verify, V), np.float32)
+        self.accept_len = ctx.zeros((B,), np.int32)
+        self.out_tokens = ctx.zeros((B, k + 1), np.int64)
+        self.history = ctx.zeros((B, self.cap), np.int64)
+        self.count = ctx.zeros((B,), np.int32)
+        self.n_commit = ctx.zeros((B,), np.int32)
+        self.round = 0
+        self.rounds_run = 0
+
+    # -- prefill -------------------------------------------------------------------
+    def prefill(self, prompts):
+        """prompts (B, T) int64 with T >= 2.  Fills both caches and the (s[-2], s[-1]) pair."""
+        prompts = np.ascontiguousarray(prompts, dtype=np.int64)
+        B, T = prompts.shape
+        if B != self.B:
+            raise ValueError(f"engine was built for batch {self.B}, got {B}")
+        if T < 2:
+            raise ValueError("prompts need at least two tokens")
+        self.t_cache.reset()
+        self.d_cache.reset()
+        tok = self.ctx.from_numpy(prompts)
+        # chunk the prompt so that activation buffers stay bounded for long prompts
+        chunk = max(1, 8192 // B)
+        for cache, model, upto in ((self.t_cache, self.target, T - 1), (self.d_cache, self.draft, T - 2)):
+            done = 0
+            while done < upto:
+                n = min(chunk, upto - done)
+                part = self.ctx.from_numpy(prompts[:, done:done + n])
+                model.forward_cached(part, cache, want_logits=False, want_hidden=True, last_only=True)
+                cache.commit(n, np.full(B, n, np.int32))
+                done += n
+        self.pair.copy_from_host(prompts[:, -2:])
+        self.ctx._check(self.ctx.lib.vn_memset(self.ctx.handle, _ptr(self.count), 0, self.count.nbytes))
+        self.round = 0
+        self.rounds_run = 0
+        del tok
+
+    # -- one round -----------------------------------------------------------------
+    def step(self):
+        ctx, lib, B, k, V = self.ctx, self.ctx.lib, self.B, self.k, self.V
+        greedy = self.temperature <= 0
+        # draft: k proposals; the first forward consumes the last two committed tokens
+        for i in range(k):
+            q_i = self.q_logits[i]
+            if i == 0:
+                self.draft.forward_cached(self.pair, self.d_cache, last_only=True, out_logits=q_i, slot_offset=0)
+            else:
+                self.draft.forward_cached(self.step_tokens[i - 1].reshape(B, 1), self.d_cache, last_only=True,
+                                          out_logits=q_i, slot_offset=i + 1)
+            ctx._check(lib.vn_sample(ctx.handle, _ptr(q_i), V, B, V, self.temperature, self.top_k, None,
+                                     self.seed, self.round, i, PURPOSE_DRAFT, _ptr(self.step_tokens[i])))
+        ctx._check(lib.vn_spec_gather(ctx.handle, _ptr(self.step_tokens), _ptr(self.pair), B, k, self.n_verify,
+                                      _ptr(self.draft_tokens), _ptr(self.verify_tokens)))
+        # target: one forward over (last committed, d_0 .. d_{n_verify-2})
+        self.target.forward_cached(self.verify_tokens, self.t_cache, out_logits=self.p_logits)
+        # acceptance
+        ctx._check(lib.vn_accept_strided(
+            ctx.handle, _ptr(self.p_logits), self.n_verify * V, V,
+            None if greedy else _ptr(self.q_logits), V, B * V,
+            _ptr(self.draft_tokens), None, None, self.seed, self.round, self.temperature, self.top_k,
+            int(self.bonus), B, k, V, _ptr(self.accept_len), _ptr(self.out_tokens)))
+        ctx._check(lib.vn_spec_advance(ctx.handle, _ptr(self.out_tokens), B, k, _ptr(self.pair), _ptr(self.history),
+                                       self.cap, _ptr(self.count), _ptr(self.n_commit)))
+        # both caches keep the first n_commit entries appended this round
+        ctx._check(lib.vn_kv_commit(self.t_cache.handle, self.n_verify, None, 0, _ptr(self.n_commit), 0))
+        ctx._check(lib.vn_kv_commit(self.d_cache.handle, k + 1, None, 0, _ptr(self.n_commit), 0))
+        self.round += 1
+        self.rounds_run += 1
+
+    # -- results --------------------------------------------------------------------
+    def counts(self) -> np.ndarray:
+        return self.count.numpy()
+
+    def tokens(self, n_new: Optional[int] = None) -> np.ndarray:
+        """Generated tokens per request, (B, n_new) (requests must have produced at least n_new)."""
+        c = self.counts()
+        n = int(c.min()) if n_new is None else int(n_new)
+        if n > c.min():
+            raise ValueError(f"only {int(c.min())} tokens available")
+        return self.history.numpy()[:, :n]
+
+    def generate(self, prompts, max_new_tokens: int):
+        """Run rounds until every request has `max_new_tokens` tokens.  Returns (tokens (B, T + new), stats)."""
+        prompts = np.ascontiguousarray(prompts, dtype=np.int64)
+        if max_new_tokens + self.k + 1 > self.cap:
+            raise ValueError("max_new_tokens exceeds the engine's history capacity")
+        self.prefill(prompts)
+        accepted = 0
+        while True:
+            # a request gains at least one token per round: poll the counters only now and then
+            need = max_new_tokens - int(self.counts().min())
+            if need <= 0:
+                break
+            for _ in range(max(1, need // (self.k + 1))):
+                self.step()
+        new = self.tokens(max_new_tokens)
+        stats = dict(rounds=self.rounds_run, proposed=self.rounds_run * self.k * self.B,
+                     committed=int(self.counts().sum()))
+        return np.concatenate([prompts, new], axis=1), stats

@@ -1,0 +1,289 @@
+"""`VerseNexLM` (= CometSparkNexLM) resident on the device.
+
+Constructor keywords, attributes, `state_dict` names and the `forward` /
+`__call__` / `generate` signatures follow verse_nex/cometspark.py:294-449,
+:670-698 and :773-830.  `embedding_scale=True` adds the `tok_emb * sqrt(dim)`
+of the CometSparkV05LM wrapper (spark/src/base_model.py:199-206).
+
+Differences that the device path brings (all additive):
+  * `dtype="f32" | "bf16"` selects the storage type of weights, GEMM inputs
+    and the KV cache (accumulation, residual stream, softmax and logits stay
+    float32);
+  * `new_cache()` returns a `KVCache`; `forward_cached` runs T new positions
+    (a chain, or a tree given `parents`) on top of it, which is what
+    `SpeculativeDecoder.verify` re-computes from scratch in the reference
+    (speculative.py:202-213).
+Weights are not initialised here: load them with `load_state_dict` from a
+reference `state_dict()` (name -> float32 ndarray, vnnn.py:235-285).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import json
+from typing import List, Optional
+
+import numpy as np
+
+from . import sampling
+from .device import Context, DeviceArray, as_device
+
+VALID_KINDS = ("trisparse", "mod")
+
+
+def _ptr(a):
+    return C.c_void_p(a.ptr) if a is not None else C.c_void_p(None)
+
+
+class KVCache:
+    """Per-layer K / V of shape (max_batch, max_seq, n_kv_head, head_dim) with per-sequence lengths.
+
+    Same role and vocabulary as ParallelKVCache (verse_nex/kv_cache_parallel.py:42-283):
+    `per_seq_lens`, `reset_seq`, `get`; overflow raises RuntimeError, a bad layer index IndexError.
+    `commit` is new: it keeps a chosen subset of the entries appended by the last forward
+    (accepted path) and drops the rest (rejected suffix) by compacting in place.
+    """
+
+    def __init__(self, model: "VerseNexLM", max_batch: int, max_seq: int):
+        self.model = model
+        self.ctx = model.ctx
+        self.max_batch, self.max_seq = int(max_batch), int(max_seq)
+        h = C.c_void_p()
+        self.ctx._check(self.ctx.lib.vn_kv_create(model.handle, self.max_batch, self.max_seq, C.byref(h)))
+        self.handle = h
+
+    @property
+    def per_seq_lens(self) -> np.ndarray:
+        out = np.zeros(self.max_batch, dtype=np.int32)
+        self.ctx._check(self.ctx.lib.vn_kv_lengths(self.handle, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def set_lengths(self, lens):
+        lens = np.ascontiguousarray(lens, dtype=np.int32)
+        if lens.shape != (self.max_batch,):
+            raise ValueError(f"lens must have shape ({self.max_batch},)")
+        self.ctx._check(self.ctx.lib.vn_kv_set_lengths(self.handle, lens.ctypes.data_as(C.c_void_p)))
+
+    def reset_seq(self, seq_idx: Optional[int] = None):
+        self.ctx._check(self.ctx.lib.vn_kv_reset_seq(self.handle, -1 if seq_idx is None else int(seq_idx)))
+
+    def reset(self):
+        self.reset_seq(None)
+
+    def commit(self, n_new: int, n_keep, keep_idx=None, keep_add: int = 0):
+        """Keep `n_keep[b] + keep_add` of the `n_new` entries the last forward(s) appended to sequence b:
+        the first ones (chain), or the slots listed in `keep_idx[b]` (tree path, ascending)."""
+        nk = as_device(self.ctx, n_keep, np.int32)
+        ki = as_device(self.ctx, keep_idx, np.int32) if keep_idx is not None else None
+        stride = ki.shape[-1] if ki is not None else 0
+        self.ctx._check(self.ctx.lib.vn_kv_commit(self.handle, int(n_new), _ptr(ki), stride, _ptr(nk), int(keep_add)))
+
+    def get(self, layer_idx: int, seq_idx: int = 0, n_positions: Optional[int] = None):
+        """(k, v) float32 ndarrays of shape (n_positions, n_kv_head, head_dim) for one sequence."""
+        if n_positions is None:
+            n_positions = int(self.per_seq_lens[seq_idx])
+        m = self.model
+        out = []
+        for which in (0, 1):
+            a = np.empty((n_positions, m.n_kv_head, m.head_dim), dtype=np.float32)
+            self.ctx._check(self.ctx.lib.vn_kv_read(self.handle, int(layer_idx), int(seq_idx), which,
+                                                    a.ctypes.data_as(C.c_void_p), int(n_positions)))
+            out.append(a)
+        return tuple(out)
+
+    def __del__(self):
+        try:
+            if self.handle:
+                self.ctx.lib.vn_kv_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+
+class VerseNexLM:
+    def __init__(self, vocab_size: int, dim: int, n_layer: int, n_head: int, n_kv_head: Optional[int] = None,
+                 layer_pattern: Optional[List[str]] = None, window_size: int = 512, num_global_tokens: int = 64,
+                 anchor_interval: int = 128, latent_dim=None, use_alibi: bool = True, use_rope: bool = False,
+                 max_seq_len: int = 2048, dropout: float = 0.0, rope_theta: float = 10000.0,
+                 num_dense_parts: int = 5, num_experts_per_part: int = 8, top_k: int = 3,
+                 expert_hidden: Optional[int] = None, aux_loss_weight: float = 0.01, dense_part_names=None,
+                 tie_weights: bool = True, mlp_hidden_multiple: int = 4, init_std: float = 0.02,
+                 residual_scale=None, embedding_scale: bool = False, dtype: str = "f32", device: str = "cuda"):
+        if layer_pattern is None:
+            layer_pattern = ["trisparse"] * n_layer
+        if len(layer_pattern) != n_layer:
+            raise ValueError(f"layer_pattern length ({len(layer_pattern)}) must equal n_layer ({n_layer})")
+        for i, k in enumerate(layer_pattern):
+            if k not in VALID_KINDS:
+                raise ValueError(f"layer_pattern[{i}]={k!r} is not available on this backend {VALID_KINDS}")
+        if dtype not in ("f32", "bf16"):
+            raise ValueError("dtype must be 'f32' or 'bf16'")
+        self.vocab_size, self.dim, self.n_layer, self.n_head = int(vocab_size), int(dim), int(n_layer), int(n_head)
+        self.n_kv_head = int(n_kv_head) if n_kv_head is not None else int(n_head)
+        self.head_dim = self.dim // self.n_head
+        self.layer_pattern = list(layer_pattern)
+        self.tie_weights = bool(tie_weights)
+        self.max_seq_len = int(max_seq_len)
+        self.window_size = int(window_size)
+        self.use_rope, self.use_alibi = bool(use_rope), bool(use_alibi)
+        self.rope_theta = float(rope_theta)
+        self.embedding_scale = bool(embedding_scale)
+        self.dtype = dtype
+        self.aux_loss_weight = aux_loss_weight
+        self._config = dict(vocab_size=self.vocab_size, dim=self.dim, n_layer=self.n_layer, n_head=self.n_head,
+                            n_kv_head=self.n_kv_head, layer_pattern=self.layer_pattern, window_size=int(window_size),
+                            num_global_tokens=int(num_global_tokens), use_alibi=self.use_alibi, use_rope=self.use_rope,
+                            max_seq_len=self.max_seq_len, rope_theta=self.rope_theta,
+                            num_dense_parts=int(num_dense_parts), num_experts_per_part=int(num_experts_per_part),
+                            top_k=int(top_k), expert_hidden=expert_hidden, tie_weights=self.tie_weights,
+                            mlp_hidden_multiple=int(mlp_hidden_multiple), embedding_scale=self.embedding_scale,
+                            dtype=dtype)
+        from .backend import _parse_index
+        self.ctx = Context.get(_parse_index(device))
+        h = C.c_void_p()
+        self.ctx._check(self.ctx.lib.vn_model_create(self.ctx.handle, json.dumps(self._config).encode(), C.byref(h)))
+        self.handle = h
+        self._finalized = False
+        self._scratch_cache: Optional[KVCache] = None
+
+    # -- reference-compatible helpers -----------------------------------------
+    def get_config(self) -> dict:
+        return dict(self._config)
+
+    def eval(self):
+        return self
+
+    def param_bytes(self) -> int:
+        n = C.c_uint64()
+        self.ctx._check(self.ctx.lib.vn_model_param_bytes(self.handle, C.byref(n)))
+        return int(n.value)
+
+    def load_tensor(self, name: str, array):
+        a = np.ascontiguousarray(np.asarray(array), dtype=np.float32)
+        shape = (C.c_int64 * max(a.ndim, 1))(*(a.shape if a.ndim else (1,)))
+        self.ctx._check(self.ctx.lib.vn_model_load_tensor(self.handle, name.encode(), a.ctypes.data_as(C.c_void_p),
+                                                          max(a.ndim, 1), shape))
+        self._finalized = False
+
+    def load_state_dict(self, sd: dict, strict: bool = True):
+        for name, value in sd.items():
+            if name == "head.weight" and self.tie_weights:
+                continue
+            self.load_tensor(name, getattr(value, "data", value))
+        self.finalize()
+
+    def finalize(self):
+        if self.use_rope:
+            # RoPE table with the reference's own NumPy expression (tri_sparse_attn.py:169-180)
+            half = self.head_dim // 2
+            rows = max(self.max_seq_len, 16) * 2
+            i = np.arange(half, dtype=np.float32)
+            inv_freq = 1.0 / (self.rope_theta ** (2.0 * i / self.head_dim))
+            ang = np.outer(np.arange(rows, dtype=np.float32), inv_freq)
+            self.load_tensor("rope.cos", np.cos(ang).astype(np.float32))
+            self.load_tensor("rope.sin", np.sin(ang).astype(np.float32))
+        self.ctx._check(self.ctx.lib.vn_model_finalize(self.handle))
+        self._finalized = True
+
+    def new_cache(self, max_batch: int, max_seq: Optional[int] = None) -> KVCache:
+        return KVCache(self, max_batch, max_seq if max_seq is not None else self.max_seq_len)
+
+    # -- forward -----------------------------------------------------------------
+    def forward_cached(self, tokens, cache: KVCache, parents=None, last_only: bool = False,
+                       want_logits: bool = True, want_hidden: bool = False, slot_offset: int = 0,
+                       out_logits: Optional[DeviceArray] = None):
+        """T new positions per sequence on top of `cache` (appended, not yet committed).
+
+        tokens (B, T) int64 host or device; parents: list of T tree parents (-1 = child of the last
+        committed token) or None for a chain.  Returns logits (B, T | 1, V) and / or hidden."""
+        if not self._finalized:
+            self.finalize()
+        tok = as_device(self.ctx, tokens, np.int64)
+        B, T = tok.shape
+        rows = 1 if last_only else T
+        logits = hidden = None
+        if want_logits:
+            logits = out_logits if out_logits is not None else self.ctx.empty((B, rows, self.vocab_size), np.float32)
+        if want_hidden:
+            hidden = self.ctx.empty((B, rows, self.dim), np.float32)
+        par = None
+        if parents is not None:
+            par = np.ascontiguousarray(parents, dtype=np.int32)
+            if par.shape != (T,):
+                raise ValueError("parents must list one parent per new position")
+        self.ctx._check(self.ctx.lib.vn_model_forward(
+            self.handle, cache.handle, _ptr(tok), B, T,
+            par.ctypes.data_as(C.c_void_p) if par is not None else None, _ptr(hidden), _ptr(logits),
+            int(bool(last_only)), int(slot_offset)))
+        if want_logits and want_hidden:
+            return logits, hidden
+        return logits if want_logits else hidden
+
+    def forward(self, idx):
+        """Whole-sequence forward from position 0, logits (B, T, V) -- CometSparkNexLM.forward."""
+        from .speculative import Tensor, _unwrap
+        ids = _unwrap(idx)
+        ids = ids if isinstance(ids, DeviceArray) else np.asarray(ids, dtype=np.int64)
+        if ids.ndim == 1:
+            ids = ids.reshape(1, -1)
+        B, T = ids.shape
+        c = self._scratch_cache
+        if c is None or c.max_batch < B or c.max_seq < T:
+            self._scratch_cache = c = self.new_cache(max(B, 1), max(T, self.max_seq_len))
+        c.reset()
+        return Tensor(self.forward_cached(ids, c))
+
+    __call__ = forward
+
+    # -- generate (cometspark.py:773-830) -------------------------------------------
+    def generate(self, idx, max_new_tokens: Optional[int] = None, temperature: float = 1.0,
+                 top_k: Optional[int] = None, eos_id: Optional[int] = None, max_safe_limit: int = 100_000,
+                 seed: int = 0) -> np.ndarray:
+        """Autoregressive generation with the KV cache.  As in the reference, `temperature == 1.0 and
+        top_k is None` means GREEDY decoding (cometspark.py:817-818); any other setting samples from
+        softmax(logits / T) over the top-k.  Uniforms come from Philox(seed)."""
+        from .speculative import _unwrap
+        ids = np.asarray(_unwrap(idx))
+        if ids.ndim == 1:
+            ids = ids[None, :]
+        ids = ids.astype(np.int64)
+        limit = max_safe_limit if max_new_tokens is None else int(max_new_tokens)
+        greedy = (temperature == 1.0 and top_k is None) or temperature <= 0
+        B, T0 = ids.shape
+        cap = T0 + min(limit, 1 << 20) + 1
+        if self.use_rope:
+            cap = min(cap, 2 * max(self.max_seq_len, 16))   # rows of the RoPE table
+        cache = self.new_cache(B, cap)
+        logits = self.forward_cached(ids, cache, last_only=True)
+        cache.commit(T0, np.full(B, T0, np.int32))
+        out = [ids]
+        for step in range(limit):
+            lg = logits.reshape(B, self.vocab_size)
+            if greedy:
+                nxt = sampling.argmax(self.ctx, lg)
+            else:
+                nxt = sampling.sample(self.ctx, lg, temperature=temperature, top_k=top_k or 0, seed=seed, offset=step)
+            host = nxt.numpy()
+            out.append(host[:, None])
+            if eos_id is not None and np.all(host == eos_id):
+                break
+            if step + 1 == limit:
+                break
+            logits = self.forward_cached(nxt.reshape(B, 1), cache, last_only=True)
+            cache.commit(1, np.ones(B, np.int32))
+        res = np.concatenate(out, axis=1)
+        if eos_id is not None and res.shape[1] > 0 and not np.all(res[:, -1] == eos_id):
+            res = np.concatenate([res, np.full((B, 1), eos_id, dtype=res.dtype)], axis=1)
+        return res
+
+    def __del__(self):
+        try:
+            self._scratch_cache = None
+            if self.handle:
+                self.ctx.lib.vn_model_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+
+CometSparkNexLM = VerseNexLM
