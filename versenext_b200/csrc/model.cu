@@ -436,7 +436,8 @@ int32_t vn_model_load_tensor(vn_model* m, const char* name, const float* data, i
     VN_REQUIRE(ctx, m->rope_rows == 0 || m->rope_rows == r || *dst == nullptr, "rope tables must have equal row counts");
     if (*dst) { VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); VN_CUDA(ctx, cudaFree(*dst)); *dst = nullptr; }
     TRY(dev_alloc(ctx, (void**)dst, (size_t)r * cl * 4));
-    VN_CUDA(ctx, cudaMemcpy(*dst, data, (size_t)r * cl * 4, cudaMemcpyHostToDevice));
+    VN_CUDA(ctx, cudaMemcpyAsync(*dst, data, (size_t)r * cl * 4, cudaMemcpyHostToDevice, ctx->stream));
+    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     m->rope_rows = (int)r;
     return VN_OK;
   }
@@ -539,8 +540,9 @@ int32_t vn_model_finalize(vn_model* m) {
     }
     TRY(dev_alloc(ctx, (void**)&m->rope_cos, cs.size() * 4));
     TRY(dev_alloc(ctx, (void**)&m->rope_sin, sn.size() * 4));
-    VN_CUDA(ctx, cudaMemcpy(m->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
-    VN_CUDA(ctx, cudaMemcpy(m->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+    VN_CUDA(ctx, cudaMemcpyAsync(m->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    VN_CUDA(ctx, cudaMemcpyAsync(m->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     m->rope_rows = rows;
   }
   // sink K / V = wk(global_tokens), wv(global_tokens): fixed per layer (tri_sparse_attn.py:223-242)
@@ -591,9 +593,11 @@ int32_t vn_kv_create(vn_model* m, int32_t max_batch, int32_t max_seq, vn_kv** ou
     planes.push_back(k); planes.push_back(v);
   }
   TRY(dev_alloc(ctx, (void**)&kv->planes_dev, planes.size() * sizeof(void*)));
-  VN_CUDA(ctx, cudaMemcpy(kv->planes_dev, planes.data(), planes.size() * sizeof(void*), cudaMemcpyHostToDevice));
+  VN_CUDA(ctx, cudaMemcpyAsync(kv->planes_dev, planes.data(), planes.size() * sizeof(void*), cudaMemcpyHostToDevice,
+                               ctx->stream));
   TRY(dev_alloc(ctx, (void**)&kv->lens, (size_t)max_batch * 4));
-  VN_CUDA(ctx, cudaMemset(kv->lens, 0, (size_t)max_batch * 4));
+  VN_CUDA(ctx, cudaMemsetAsync(kv->lens, 0, (size_t)max_batch * 4, ctx->stream));
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   kv->len_ub.assign(max_batch, 0);
   *out = kv;
   return VN_OK;

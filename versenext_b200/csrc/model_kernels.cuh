@@ -160,6 +160,7 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, flo
 // merge the 4 groups of a warp (lanes g*8 + i own dims i*? .. see below) and return the normalised output of the
 // calling lane's dims; all lanes participate
 __device__ __forceinline__ void merge_groups(GroupAcc& a) {
+  __syncwarp();
 #pragma unroll
   for (int o = 8; o <= 16; o <<= 1) {
     const float om = __shfl_xor_sync(0xffffffffu, a.m, o);
@@ -205,6 +206,7 @@ __global__ void __launch_bounds__(256) trisparse_attn_kernel(AttnArgs a) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) q[i] = active ? a.q[(long long)row * a.ld_q + h * hd + li * 8 + i] : 0.f;
   const unsigned long long anc = a.anc ? a.anc[t] : 0ull;
+  const unsigned gmask = 0xFFu << (grp * 8);
 
   auto score = [&](const T* kr) {
     float kv[8];
@@ -214,9 +216,10 @@ __global__ void __launch_bounds__(256) trisparse_attn_kernel(AttnArgs a) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) s = fmaf(q[i], kv[i], s);
     }
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    // the 8 lanes of a group always take the same branches; other groups may be elsewhere in their loops
+    s += __shfl_xor_sync(gmask, s, 1);
+    s += __shfl_xor_sync(gmask, s, 2);
+    s += __shfl_xor_sync(gmask, s, 4);
     return s * a.scale;
   };
   auto value = [&](const T* vr, float* v) {
