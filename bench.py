@@ -1,9 +1,16 @@
 #!/usr/bin/env python
 """Benchmark of the speculative-decoding hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload accept]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload spec|accept]
 
 Prints ONE JSON line (rank 0).  Workloads:
+
+  spec     (default) full speculative decode: mate-shaped VerseNexLM target (dim 1024, 20 layers =
+           5 MoD + 15 TriSparse, vocab 248320, bf16, tied head, seeded N(0, 0.02) weights) with a
+           2-layer dim-256 draft over the same vocabulary, k=4, temperature 0.8, top-k 50, 32
+           requests per GPU with 512-token uniform-random prompts.  A step is one round
+           (draft 4 tokens -> verify 5 positions -> accept -> commit) over the whole batch;
+           metric = accepted tok/s = tokens committed / time.  Prefill is outside the timed region.
 
   accept   isolated acceptance-sampling op: B=64 sequences, k=4 draft positions,
            vocab 248320, fp32 target logits [B,k+1,V] and draft logits [B,k,V]
@@ -169,6 +176,227 @@ def cpu_accept_sample(n_seq, repeats=1):
     return accept_bytes(n_seq, k, V) / best / 1e9, best
 
 
+# ---------------------------------------------------------------------------
+# speculative decode workload
+# ---------------------------------------------------------------------------
+
+SPEC = dict(B=32, prompt=512, k=4, temperature=0.8, top_k=50, seed=4, new_tokens=256)
+SPEC_WORKLOAD = ("spec: mate target (D=1024, L=20: 5 MoD + 15 TriSparse, V=248320, bf16) + 2-layer D=256 draft, "
+                 "k=4, T=0.8, top-k 50, 32 requests/GPU, 512-token prompts")
+MATE_PARAMS = 1107375164
+
+
+def spec_step_bytes(B, ctx_len, dtype_bytes=2):
+    """Algorithmic bytes of one verify+sample step: every unique target weight once, plus the K/V window
+    (20 layers x B x min(ctx, 1024) positions x (2 x 512) values)."""
+    return MATE_PARAMS * dtype_bytes + 20 * B * min(ctx_len, 1024) * 2 * 512 * dtype_bytes
+
+
+def spec_prompts(B, T, seed, rank=0):
+    return np.random.default_rng([seed, rank]).integers(0, 248320, (B, T)).astype(np.int64)
+
+
+def build_spec_models(scale=1.0):
+    import versenext_b200 as vn
+    from versenext_b200 import synthetic as S
+    tk, dk = S.mate_kwargs(), S.draft_kwargs()
+    target = vn.VerseNexLM(dtype="bf16", **tk)
+    S.load_random(target, tk, seed=0)
+    draft = vn.VerseNexLM(dtype="bf16", **dk)
+    S.load_random(draft, dk, seed=1)
+    return target, draft
+
+
+def cpu_spec_sample(max_seconds=25.0, rounds=2):
+    """Reference algorithm on the host (NumPy restatement, BLAS threads = all cores): one request of the
+    workload, full re-forward of [context, draft] every round as the reference does.  Returns
+    (tok/s, seconds, rounds run)."""
+    from oracle import model as OM
+    from oracle import spec as OS
+    from versenext_b200 import synthetic as S
+    tk, dk = S.mate_kwargs(), S.draft_kwargs()
+    t_cfg = OM.mate_config()
+    d_cfg = OM.Config(**{k: v for k, v in dk.items()})
+    t_sd = dict(S.random_tensors(tk, seed=0))
+    t_sd["head.weight"] = t_sd["tok_emb.weight"]
+    d_sd = dict(S.random_tensors(dk, seed=1))
+    d_sd["head.weight"] = d_sd["tok_emb.weight"]
+    prompt = spec_prompts(1, SPEC["prompt"], SPEC["seed"])
+    t0 = time.perf_counter()
+    done = committed = 0
+    seq = prompt
+    while done < rounds and time.perf_counter() - t0 < max_seconds:
+        st = OS.generate(t_sd, t_cfg, d_sd, d_cfg, seq, SPEC["k"], 10 ** 6, temperature=SPEC["temperature"],
+                         top_k=SPEC["top_k"], seed=SPEC["seed"], bonus=True, max_rounds=1)
+        new_seq = st["tokens"][0]
+        committed += new_seq.shape[1] - seq.shape[1]
+        seq = new_seq
+        done += 1
+    dt = time.perf_counter() - t0
+    return committed / dt, dt, done
+
+
+def run_spec(args):
+    import versenext_b200 as vn
+    world, rank, local, dist = dist_setup(args.gpus)
+    ctx = vn.Context.get(local)
+    B, k, T0 = SPEC["B"], SPEC["k"], SPEC["prompt"]
+    t_build = time.perf_counter()
+    target, draft = build_spec_models()
+    t_build = time.perf_counter() - t_build
+    warm = max(args.warmup, 3)
+    max_seq = T0 + (warm + 3 * args.steps + 16) * (k + 1) + 64
+    eng = vn.SpecEngine(target, draft, max_batch=B, max_seq=max_seq, k=k, temperature=SPEC["temperature"],
+                        top_k=SPEC["top_k"], seed=SPEC["seed"], bonus=True,
+                        max_new_tokens=(warm + 3 * args.steps + 16) * (k + 1))
+    prompts = spec_prompts(B, T0, SPEC["seed"], rank)
+    ctx.sync()
+    t_pre = time.perf_counter()
+    eng.prefill(prompts)
+    ctx.sync()
+    t_pre = time.perf_counter() - t_pre
+    for _ in range(warm):
+        eng.step()
+    c0 = eng.counts().sum()
+    # ---- timed region: K rounds, state resident on the device, no host synchronisation inside
+    clocks = ClockSampler(local).start() if rank == 0 else None
+    barrier_sync(dist, ctx)
+    l0 = ctx.launch_count()
+    e0, e1 = ctx.event(), ctx.event()
+    e0.record()
+    for _ in range(args.steps):
+        eng.step()
+    e1.record()
+    ms = e0.elapsed_ms(e1)
+    barrier_sync(dist, ctx)
+    launches = ctx.launch_count() - l0
+    clk = clocks.stop() if clocks else None
+    c1 = eng.counts().sum()
+    ms = max_over_ranks(dist, ms, local)
+    committed = float(c1 - c0)
+    if dist is not None:
+        import torch
+        t = torch.tensor([committed], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t)
+        committed = float(t.item())
+    value = committed / (ms * 1e-3)
+    accept_rate = float(eng.accept_len.numpy().mean() / k)
+    ctx_len = int(eng.t_cache.per_seq_lens.mean())
+
+    # ---- end to end through the host-facing call: pinned host tokens in, committed tokens out, every round
+    h_pair = ctx.pinned((B, 2), np.int64)
+    h_len, h_tok = ctx.pinned((B,), np.int32), ctx.pinned((B, k + 1), np.int64)
+    eng.pair.copy_to_pinned_async(h_pair)
+    ctx.sync()
+
+    def e2e_step():
+        eng.pair.copy_from_pinned_async(h_pair)     # the caller supplies the last committed tokens
+        eng.step()
+        eng.accept_len.copy_to_pinned_async(h_len)
+        eng.out_tokens.copy_to_pinned_async(h_tok)
+        eng.pair.copy_to_pinned_async(h_pair)
+        ctx.sync()
+        return int((h_tok >= 0).sum())
+
+    e2e_step()
+    n_e2e = args.steps
+    barrier_sync(dist, ctx)
+    t0 = time.perf_counter()
+    got = 0
+    for _ in range(n_e2e):
+        got += e2e_step()
+    barrier_sync(dist, ctx)
+    e2e_s = max_over_ranks(dist, time.perf_counter() - t0, local)
+    e2e = {"value": got * world / e2e_s, "unit": "tok/s", "steps": n_e2e,
+           "h2d_bytes_per_step": int(h_pair.nbytes),
+           "d2h_bytes_per_step": int(h_len.nbytes + h_tok.nbytes + h_pair.nbytes)}
+
+    # ---- per-kernel durations of the verify + sample part of a round (CUDA events around each launch)
+    ctx.profile(True)
+    n_prof = min(args.steps, 10)
+    for _ in range(n_prof):
+        eng.verify_accept_only()
+    rep = ctx.profile_report()
+    ctx.profile(False)
+    step_ms = sum(v["ms"] for v in rep.values()) / n_prof
+    gemm_ms = sum(v["ms"] for n, v in rep.items() if n.startswith("gemm_")) / n_prof
+    nbytes = spec_step_bytes(B, ctx_len)
+    peak, peak_kind = peaks()
+    achieved = nbytes / (step_ms * 1e-3) / 1e9
+    top = sorted(rep.items(), key=lambda kv: -kv[1]["ms"])
+    roofline = {"bound": "hbm", "kernel": "verify+sample step (all kernels of the target forward and acceptance)",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_kind": f"of {peak_kind}", "traffic": None, "step_ms": step_ms, "algorithmic_bytes": nbytes,
+                "gemm_ms": gemm_ms, "gemm_weight_gbs": MATE_PARAMS * 2 / (gemm_ms * 1e-3) / 1e9,
+                "kernel_ms_per_step": {n: v["ms"] / n_prof for n, v in top},
+                "kernel_launches_per_step": {n: v["launches"] / n_prof for n, v in top}}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        import os as _os
+        tps, secs, rounds = cpu_spec_sample()
+        cpu = {"value": tps, "unit": "tok/s", "cores": _os.cpu_count(), "kind": "port",
+               "sample": f"1 of 32 requests, {rounds} rounds ({secs:.1f} s), full re-forward per round as the "
+                         "reference does; NumPy restatement (oracle/), fp32, BLAS threads = all cores"}
+    sampler = None
+    if rank == 0 and world == 1 and not args.no_sampler:
+        del eng
+        sampler = accept_quick(ctx)
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "accepted tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": SPEC_WORKLOAD, "per_gpu_requests": B, "context_tokens": ctx_len,
+                       "l2": "weights (2.2 GB) larger than L2, no flush", "step": "one speculative round"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clk,
+            "accept_rate": accept_rate, "tokens_per_round_per_request": committed / world / B / args.steps,
+            "prefill_s": t_pre, "weights_build_s": t_build, "sampler": sampler,
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def accept_quick(ctx, steps=20):
+    """sampler GB/s of the isolated acceptance op (second half of the headline metric)."""
+    from versenext_b200 import sampling
+    B, k, V = ACCEPT["B"], ACCEPT["k"], ACCEPT["V"]
+    p, q, draft = make_accept_inputs(B, k, V, ACCEPT["seed"])
+    pd, qd, dd = ctx.from_numpy(p), ctx.from_numpy(q), ctx.from_numpy(draft)
+    out = (ctx.empty((B,), np.int32), ctx.empty((B, k + 1), np.int64))
+    for i in range(3):
+        sampling.accept(ctx, pd, qd, dd, seed=1234, offset=i, temperature=1.0, out=out)
+    e0, e1 = ctx.event(), ctx.event()
+    e0.record()
+    for i in range(steps):
+        sampling.accept(ctx, pd, qd, dd, seed=1234, offset=i, temperature=1.0, out=out)
+    e1.record()
+    ms = e0.elapsed_ms(e1) / steps
+    peak, kind = peaks()
+    gbs = accept_bytes(B, k, V) / (ms * 1e-3) / 1e9
+    return {"metric": "sampler GB/s", "value": gbs, "unit": "GB/s", "ms_per_call": ms, "frac_of_hbm_peak": gbs / peak,
+            "workload": "B=64 k=4 V=248320 fp32 logits, T=1.0"}
+
+
+def run_reference_spec(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    budget = 150.0
+    tps, secs, rounds = cpu_spec_sample(max_seconds=budget, rounds=max(1, args.steps))
+    sample = (f"1 of 32 requests per step, {rounds} rounds run inside a {budget:.0f} s budget; full re-forward per "
+              "round as the reference does; NumPy restatement (oracle/), fp32, BLAS threads = all cores")
+    print(json.dumps({
+        "impl": "reference", "metric": "accepted tok/s", "value": tps, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": rounds, "warmup": 0, "ms_per_step": secs / max(rounds, 1) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": SPEC_WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
 def run_reference(args):
     world, rank, local, _ = 1, int(os.environ.get("RANK", "0")), 0, None
     if rank != 0:
@@ -306,16 +534,17 @@ def run_accept(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="accept", choices=["accept"])
+    ap.add_argument("--workload", default="spec", choices=["spec", "accept"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-sampler", action="store_true", help="spec workload: skip the sampler GB/s measurement")
     args = ap.parse_args()
     if args.impl == "reference":
-        run_reference(args)
+        (run_reference_spec if args.workload == "spec" else run_reference)(args)
     else:
-        run_accept(args)
+        (run_spec if args.workload == "spec" else run_accept)(args)
 
 
 if __name__ == "__main__":

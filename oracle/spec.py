@@ -74,7 +74,7 @@ def greedy_generate(sd, cfg, prompt, n_new):
 
 
 def generate(t_sd, t_cfg, d_sd, d_cfg, prompt, k, n_new, temperature=0.0, top_k=0,
-             seed=0, bonus=False, use_cache=True):
+             seed=0, bonus=False, max_rounds=None):
     """Speculative decoding with a draft MODEL, one request at a time.
 
     Returns dict(tokens [B, T+n_new], rounds, proposed, accepted).
@@ -92,7 +92,7 @@ def generate(t_sd, t_cfg, d_sd, d_cfg, prompt, k, n_new, temperature=0.0, top_k=
         seq = prompt[b:b + 1].copy()
         target_len = prompt.shape[1] + n_new
         rnd = 0
-        while seq.shape[1] < target_len:
+        while seq.shape[1] < target_len and (max_rounds is None or rnd < max_rounds):
             # --- draft k tokens
             d_seq = seq.copy()
             q_rows = []
@@ -126,5 +126,5 @@ def generate(t_sd, t_cfg, d_sd, d_cfg, prompt, k, n_new, temperature=0.0, top_k=
             stats["accepted"] += int(acc[0])
             rnd += 1
         out.append(seq[:, :target_len])
-    stats["tokens"] = np.concatenate(out, axis=0)
+    stats["tokens"] = np.concatenate(out, axis=0) if max_rounds is None else out
     return stats

@@ -122,6 +122,22 @@ class SpecEngine:
         self.round += 1
         self.rounds_run += 1
 
+    def verify_accept_only(self):
+        """The verify + sample half of a round on the current proposals (for per-kernel timing): target
+        forward, acceptance, bookkeeping and the target cache commit; the draft cache is left alone."""
+        ctx, lib, B, k, V = self.ctx, self.ctx.lib, self.B, self.k, self.V
+        greedy = self.temperature <= 0
+        self.target.forward_cached(self.verify_tokens, self.t_cache, out_logits=self.p_logits)
+        ctx._check(lib.vn_accept_strided(
+            ctx.handle, _ptr(self.p_logits), self.n_verify * V, V,
+            None if greedy else _ptr(self.q_logits), V, B * V,
+            _ptr(self.draft_tokens), None, None, self.seed, self.round, self.temperature, self.top_k,
+            int(self.bonus), B, k, V, _ptr(self.accept_len), _ptr(self.out_tokens)))
+        ctx._check(lib.vn_spec_advance(ctx.handle, _ptr(self.out_tokens), B, k, _ptr(self.pair), _ptr(self.history),
+                                       self.cap, _ptr(self.count), _ptr(self.n_commit)))
+        ctx._check(lib.vn_kv_commit(self.t_cache.handle, self.n_verify, None, 0, _ptr(self.n_commit), 0))
+        self.round += 1
+
     # -- results --------------------------------------------------------------------
     def counts(self) -> np.ndarray:
         return self.count.numpy()
