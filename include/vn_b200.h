@@ -127,6 +127,27 @@ int32_t vn_accept_strided(vn_ctx* ctx, const float* p_logits_dev, int64_t p_stri
                           const int64_t* draft_dev, const float* u_accept_dev, const float* u_sample_dev,
                           uint64_t seed, uint32_t offset, float temperature, int32_t top_k, int32_t bonus,
                           int32_t B, int32_t k, int32_t V, int32_t* out_len_dev, int64_t* out_tokens_dev);
+/* vn_accept for callers that must not allocate.  It has no counterpart in the reference.
+ * Some hosts drive this library from places where device allocation is forbidden or fails: inside a
+ * serving loop whose memory pool already owns the whole GPU, under a framework that traps cudaMalloc
+ * after start-up, or in a latency-critical thread where an allocation's implicit device
+ * synchronisation is not acceptable.  vn_accept grows a scratch buffer on demand; this variant keeps
+ * its scratch (chunk statistics, decisions, residual masses) in a fixed 2 MiB array that is part of
+ * the library image on every GPU that loads it, and calls no cudaMalloc / cudaFree or any other
+ * allocating routine.
+ *   - full-vocabulary rule and greedy rule only (no top-k argument); contiguous [B, k+1, V] /
+ *     [B, k, V] inputs as for vn_accept; the caller still owns inputs and outputs;
+ *   - sizes whose scratch exceeds the array (B * (2k+1) * ceil(V/4096) * 16 bytes plus about
+ *     1 KB per sequence must stay below 2 MiB: e.g. B=128, k=4, V=248320 fits, B=256 does not)
+ *     are rejected with VN_ERR_INVALID and a message that names both numbers;
+ *   - the first call on a device looks up the array's device address; make that first call
+ *     before any stream capture is begun;
+ *   - all calls share the one array: two calls that overlap on the GPU (different contexts /
+ *     streams of the same device) race; calls on one context are ordered by its stream. */
+int32_t vn_accept_noalloc(vn_ctx* ctx, const float* p_logits_dev, const float* q_logits_dev,
+                          const int64_t* draft_dev, const float* u_accept_dev, const float* u_sample_dev,
+                          uint64_t seed, uint32_t offset, float temperature, int32_t bonus,
+                          int32_t B, int32_t k, int32_t V, int32_t* out_len_dev, int64_t* out_tokens_dev);
 /* One token per row of logits (row r at logits_dev + r * row_stride): argmax when temperature <= 0,
  * else inverse-CDF draw from softmax(logits / T) restricted to the top-k (cometspark.py:892-911).
  * uniforms_dev [R] or NULL: Philox counter (position, row, purpose, offset). */

@@ -719,6 +719,91 @@ int32_t vn_sample(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int3
   return st;
 }
 
+}  // extern "C"
+
+// ---- acceptance without any allocation ---------------------------------------------------------------
+// Scratch of the full-vocabulary path (chunk statistics, per-sequence decisions, residual masses) held in a
+// fixed array inside the library image instead of the context's growable workspace.  Every GPU that loads the
+// library carries these 2 MiB until the process exits.
+namespace {
+constexpr size_t NOALLOC_SCRATCH_BYTES = 2u << 20;
+static __device__ __align__(256) unsigned char g_accept_scratch[NOALLOC_SCRATCH_BYTES];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void* g_accept_scratch_ptr[NOALLOC_MAX_DEVICES] = {nullptr};  // device address of the array, per device
+std::mutex g_accept_scratch_mutex;
+}  // namespace
+
+extern "C" {
+
+int32_t vn_accept_noalloc(vn_ctx* ctx, const float* p_logits_dev, const float* q_logits_dev, const int64_t* draft_dev,
+                          const float* u_accept_dev, const float* u_sample_dev, uint64_t seed, uint32_t offset,
+                          float temperature, int32_t bonus, int32_t B, int32_t k, int32_t V, int32_t* out_len_dev,
+                          int64_t* out_tokens_dev) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, B >= 0 && k >= 0 && k <= MAX_K && V >= 1, "bad sizes B=%d k=%d V=%d (k <= %d)", B, k, V, MAX_K);
+  VN_REQUIRE(ctx, p_logits_dev && out_len_dev && out_tokens_dev, "null pointer");
+  VN_REQUIRE(ctx, k == 0 || draft_dev, "draft tokens missing");
+  VN_REQUIRE(ctx, (u_accept_dev == nullptr) == (u_sample_dev == nullptr) || k == 0,
+             "inject both uniform arrays or neither");
+  VN_REQUIRE(ctx, bonus || k > 0, "nothing to do: k == 0 without a bonus token");
+  VN_REQUIRE(ctx, ctx->device >= 0 && ctx->device < NOALLOC_MAX_DEVICES, "device index %d not supported here", ctx->device);
+  if (B == 0) return VN_OK;
+  const bool greedy = temperature <= 0.f;
+  const float temp = greedy ? 1.0f : fmaxf(temperature, 1e-8f);
+  RowSet rs;
+  rs.p = p_logits_dev; rs.q = greedy ? nullptr : q_logits_dev;
+  rs.np = bonus ? k + 1 : k;
+  rs.nq = (rs.q && k > 0) ? k : 0;
+  rs.p_sb = (long long)rs.np * V; rs.p_si = V; rs.q_sb = (long long)k * V; rs.q_si = V;
+  rs.V = V;
+  const int rows_per_seq = rs.np + rs.nq;
+  const int nchunks = ceil_div(V, CHUNK);
+  const size_t n_part = (size_t)B * rows_per_seq * nchunks;
+  const size_t off_dec = (n_part * sizeof(Partial) + 255) & ~(size_t)255;
+  const size_t off_mass = (off_dec + (size_t)B * sizeof(Decision) + 255) & ~(size_t)255;
+  const size_t total = off_mass + (size_t)B * nchunks * 2 * sizeof(double);
+  if (total > NOALLOC_SCRATCH_BYTES)
+    return vn_fail(ctx, VN_ERR_INVALID,
+                   "vn_accept_noalloc: B=%d k=%d V=%d needs %zu bytes of scratch, the built-in array holds %zu "
+                   "(use vn_accept for larger problems)", B, k, V, total, NOALLOC_SCRATCH_BYTES);
+  // One-time set-up per device, with that device current (VN_CHECK_CTX selected it): in host code the array's
+  // name is only a stand-in for the symbol, so its device address has to be asked for.
+  void* ws = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_accept_scratch_mutex);
+    if (!g_accept_scratch_ptr[ctx->device]) {
+      void* addr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&addr, g_accept_scratch);
+      if (e != cudaSuccess || !addr)
+        return vn_fail(ctx, VN_ERR_CUDA, "cudaGetSymbolAddress(g_accept_scratch) failed: %s", cudaGetErrorString(e));
+      g_accept_scratch_ptr[ctx->device] = addr;
+    }
+    ws = g_accept_scratch_ptr[ctx->device];
+  }
+  Partial* part = (Partial*)ws;
+  Decision* dec = (Decision*)((char*)ws + off_dec);
+  double* mass = (double*)((char*)ws + off_mass);
+  const long long* d64 = reinterpret_cast<const long long*>(draft_dev);
+  long long* o64 = reinterpret_cast<long long*>(out_tokens_dev);
+  auto aligned16 = [](const void* ptr) { return ((uintptr_t)ptr & 15) == 0; };
+  const bool vec = (V % 4 == 0) && aligned16(rs.p) && (!rs.nq || aligned16(rs.q));
+  // every kernel below overwrites the part of the scratch it owns before anything reads it (each chunk
+  // statistic, decision and mass entry that is read was written earlier in this same call), so nothing left
+  // over from the previous call has to be cleared
+  const int grid = (int)std::min<long long>((long long)n_part, (long long)ctx->sm_count * 8);
+  if (vec) VN_LAUNCH(ctx, accept_stats_kernel<true>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
+  else     VN_LAUNCH(ctx, accept_stats_kernel<false>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
+  VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_accept_dev, u_sample_dev, seed, offset,
+            temp, (int)greedy, bonus, 1, 0, dec, out_len_dev, o64);
+  if (!greedy) {
+    dim3 g(nchunks, B);
+    if (vec) VN_LAUNCH(ctx, accept_residual_kernel<true>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);
+    else     VN_LAUNCH(ctx, accept_residual_kernel<false>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);
+    VN_LAUNCH(ctx, accept_pick_kernel, B, STATS_THREADS, 0, rs, k, nchunks, temp, dec, mass, o64);
+  }
+  return VN_OK;
+}
+
 int32_t vn_philox_uniform(vn_ctx* ctx, uint64_t seed, uint32_t offset, int32_t B, int32_t n, int32_t purpose,
                           float* out_dev) {
   VN_CHECK_CTX(ctx);
