@@ -227,3 +227,39 @@ def test_errors():
         m2.finalize()                                                 # tensors missing
     with pytest.raises(ValueError):
         m2.load_tensor("blocks.0.attn.wq.weight", np.zeros((3, 3), np.float32))
+
+
+def hd64_cfg(**over):
+    kw = dict(vocab_size=384, dim=256, n_layer=2, n_head=4, n_kv_head=2, window_size=24, num_global_tokens=20,
+              max_seq_len=256, init_std=0.05, num_dense_parts=2, num_experts_per_part=2, top_k=1)
+    kw.update(over)
+    return OM.mate_config(**kw)
+
+
+@pytest.mark.parametrize("variant", ["rope_window", "alibi_norope", "tree"])
+def test_tensor_core_attention_head_dim_64(variant):
+    """bf16, head_dim 64 takes the tensor-core attention kernel: window edge, sinks, ALiBi path, GQA, trees."""
+    over = {}
+    if variant == "alibi_norope":
+        over = dict(use_alibi=True, use_rope=False, embedding_scale=False)
+    cfg = hd64_cfg(**over)
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=21, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    rng = np.random.default_rng(6)
+    B = 3
+    ctx_tok = rng.integers(0, 384, (B, 61))          # > 2 windows, not a multiple of 16
+    cache = m.new_cache(B, 128)
+    lg0 = m.forward_cached(ctx_tok, cache).numpy()   # prefill through the same kernel (many row tiles)
+    want0, oc = OM.forward(sd, cfg, ctx_tok)
+    assert rel_err(lg0, want0) < 2e-2
+    cache.commit(61, np.full(B, 61, np.int32))
+    if variant == "tree":
+        parents = [-1, -1, -1, -1, 0, 0, 1, 1, 4, 4, 5, 5, 6, 6, 7, 7]
+        nodes = rng.integers(0, 384, (B, 16))
+        lg = m.forward_cached(nodes, cache, parents=parents).numpy()
+        want, _ = OM.forward(sd, cfg, nodes, cache=oc, parents=parents)
+    else:
+        nxt = rng.integers(0, 384, (B, 5))
+        lg = m.forward_cached(nxt, cache).numpy()
+        want, _ = OM.forward(sd, cfg, nxt, cache=oc)
+    assert rel_err(lg, want) < 2e-2

@@ -1,0 +1,285 @@
+// TriSparse attention on tensor cores for bf16 caches with head_dim 64 (tri_sparse_attn.py:536-613).
+//
+// One CTA per (sequence, kv head, tile of 16 query rows); the rows of a tile are (query head of the GQA
+// group) x (new position), so every K / V row fetched from the cache serves all of them.  The 8 warps of the
+// CTA take 16-key blocks round-robin, each with its own online-softmax state, and are merged through shared
+// memory.  The three paths of the reference (window, sinks, ALiBi) keep their own softmax and are mixed by the
+// sigmoid gates afterwards.
+//
+// mma.sync.m16n8k16 fragments are filled straight from global memory without a transposing stage by using the
+// freedom to permute the contraction index (same permutation on both operands) and the output columns:
+//   S = Q K^T : thread (g, t) of the warp loads dims [16t, 16t+16) of key row g     (32 contiguous bytes)
+//   O = P V   : thread (g, t) loads dims [8g, 8g+8) of key rows 2t, 2t+1, 2t+8, 2t+9 (16 contiguous bytes each)
+//               and pairs the rows with byte permutes; accumulator column n of tile j is output dim 8n + j.
+#pragma once
+#include "model_kernels.cuh"
+#include "gemm_mma.cuh"
+
+namespace attn_detail {
+
+constexpr int AW = 8;  // warps per CTA
+
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct RowInfo {
+  bool valid;
+  int tq, pos;
+  float slope;
+  unsigned long long anc;
+};
+
+// mode 0: window path (cached keys within the window, appended keys by ancestry), 1: sinks, 2: ALiBi path
+template <int MODE>
+__device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* __restrict__ Kb,
+                                       const __nv_bfloat16* __restrict__ Vb, long long ks, int lo, int hi, int len,
+                                       const RowInfo (&row)[2], const unsigned (&qf)[4][4], const int* s_depth,
+                                       int warp, int lane, float (&o)[8][4], float (&m)[2], float (&l)[2]) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  m[0] = m[1] = -CUDART_INF_F;
+  l[0] = l[1] = 0.f;
+  const int nblk = hi > lo ? (hi - lo + 15) >> 4 : 0;
+  for (int blk = warp; blk < nblk; blk += AW) {
+    const int j0 = lo + blk * 16;
+    // ---- K: rows j0 + 8i + g, dims 16t .. 16t+15
+    unsigned kr[2][8];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      int key = j0 + 8 * i + g;
+      key = key < hi ? key : hi - 1;
+      const uint4* p = reinterpret_cast<const uint4*>(Kb + (long long)key * ks + 16 * t);
+      const uint4 u0 = p[0], u1 = p[1];
+      kr[i][0] = u0.x; kr[i][1] = u0.y; kr[i][2] = u0.z; kr[i][3] = u0.w;
+      kr[i][4] = u1.x; kr[i][5] = u1.y; kr[i][6] = u1.z; kr[i][7] = u1.w;
+    }
+    // ---- V: rows j0 + {2t, 2t+1, 2t+8, 2t+9}, dims 8g .. 8g+7
+    unsigned vr[4][4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      int key = j0 + 2 * t + (x & 1) + ((x >> 1) << 3);
+      key = key < hi ? key : hi - 1;
+      const uint4 u = *reinterpret_cast<const uint4*>(Vb + (long long)key * ks + 8 * g);
+      vr[x][0] = u.x; vr[x][1] = u.y; vr[x][2] = u.z; vr[x][3] = u.w;
+    }
+    // ---- S = Q K^T for two tiles of 8 keys
+    float c[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const unsigned bfrag[2] = {kr[i][2 * s], kr[i][2 * s + 1]};
+        mma_detail::mma_bf16(c[i], qf[s], bfrag);
+      }
+    }
+    // ---- scale, bias, mask
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = j0 + 8 * i + 2 * t + (e & 1);
+        const RowInfo& r = row[e >> 1];
+        bool vis = r.valid && key < hi;
+        float sc = c[i][e] * a.scale;
+        if (MODE == 0 || MODE == 2) {
+          int kpos = key;
+          if (key >= len) {
+            const int n = key - len;
+            kpos = len + (s_depth ? s_depth[n < 64 ? n : 63] : n);
+            vis = vis && (a.anc ? ((r.anc >> n) & 1ull) != 0 : n <= r.tq) && kpos <= r.pos;
+          }
+          if (MODE == 0) vis = vis && (r.pos - kpos) < a.window;
+          else sc -= r.slope * (float)(r.pos - kpos);
+        }
+        c[i][e] = vis ? sc : -CUDART_INF_F;
+      }
+    // ---- online softmax (rows g and g+8; a row lives in the 4 lanes of a quad)
+    float pr[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float mx = fmaxf(fmaxf(c[0][2 * h], c[0][2 * h + 1]), fmaxf(c[1][2 * h], c[1][2 * h + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float mn = fmaxf(m[h], mx);
+      float corr = 1.f;
+      if (mn == -CUDART_INF_F) {
+        pr[0][2 * h] = pr[0][2 * h + 1] = pr[1][2 * h] = pr[1][2 * h + 1] = 0.f;
+      } else {
+        corr = __expf(m[h] - mn);
+        pr[0][2 * h] = __expf(c[0][2 * h] - mn);
+        pr[0][2 * h + 1] = __expf(c[0][2 * h + 1] - mn);
+        pr[1][2 * h] = __expf(c[1][2 * h] - mn);
+        pr[1][2 * h + 1] = __expf(c[1][2 * h + 1] - mn);
+      }
+      l[h] = l[h] * corr + pr[0][2 * h] + pr[0][2 * h + 1] + pr[1][2 * h] + pr[1][2 * h + 1];
+      m[h] = mn;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { o[j][2 * h] *= corr; o[j][2 * h + 1] *= corr; }
+    }
+    // ---- O += P V
+    const unsigned pa[4] = {pack_bf16(pr[0][0], pr[0][1]), pack_bf16(pr[0][2], pr[0][3]),
+                            pack_bf16(pr[1][0], pr[1][1]), pack_bf16(pr[1][2], pr[1][3])};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
+      const unsigned bfrag[2] = {__byte_perm(vr[0][j >> 1], vr[1][j >> 1], sel),
+                                 __byte_perm(vr[2][j >> 1], vr[3][j >> 1], sel)};
+      mma_detail::mma_bf16(o[j], pa, bfrag);
+    }
+  }
+  // row sums live spread over the quad
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+}
+
+__global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a) {
+  __shared__ float sO[AW][16][64];
+  __shared__ float sM[AW][16], sL[AW][16];
+  __shared__ int s_depth[64];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
+  const int n_rep = a.H / a.n_kv;
+  const int R = a.Tn * n_rep;
+  const int tile0 = blockIdx.y * 16;
+  const int len = a.lens[b] + a.slot_offset;
+  if (a.depth) {
+    if (tid < 64) s_depth[tid] = tid < a.Tn ? a.depth[tid] : 0;
+    __syncthreads();
+  }
+  const int* depth = a.depth ? s_depth : nullptr;
+
+  RowInfo row[2];
+  int tq_min = 1 << 30, tq_max = -1, pos_min = 1 << 30;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = tile0 + g + 8 * h;
+    row[h].valid = r < R;
+    const int rr = row[h].valid ? r : 0;
+    row[h].tq = rr % a.Tn;
+    const int hrep = rr / a.Tn;
+    row[h].pos = len + (depth ? depth[row[h].tq] : row[h].tq);
+    row[h].slope = 1.0f / exp2f((float)(kvh * n_rep + hrep + 1) / (float)a.H);
+    row[h].anc = a.anc ? a.anc[row[h].tq] : 0ull;
+  }
+  // tile-wide key range (all threads compute the same numbers from the tile's rows)
+  for (int r = tile0; r < tile0 + 16 && r < R; ++r) {
+    const int tq = r % a.Tn;
+    const int p = len + (depth ? depth[tq] : tq);
+    tq_min = min(tq_min, tq); tq_max = max(tq_max, tq); pos_min = min(pos_min, p);
+  }
+  const int hi_new = a.anc ? len + a.Tn : len + tq_max + 1;  // appended slots this tile can see
+
+  // Q fragments, dims permuted as described at the top of the file
+  unsigned qf[4][4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = tile0 + g + 8 * h;
+    const int rr = r < R ? r : 0;
+    const int tq = rr % a.Tn, hrep = rr / a.Tn;
+    const float* q = a.q + (long long)(b * a.Tn + tq) * a.ld_q + (kvh * n_rep + hrep) * 64 + 16 * t;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(q + 4 * s);
+      qf[s][h] = r < R ? pack_bf16(v.x, v.y) : 0u;
+      qf[s][2 + h] = r < R ? pack_bf16(v.z, v.w) : 0u;
+    }
+  }
+
+  const long long ks = (long long)a.n_kv * 64;
+  const __nv_bfloat16* Kc = reinterpret_cast<const __nv_bfloat16*>(a.kc) + ((long long)b * a.max_seq * a.n_kv + kvh) * 64;
+  const __nv_bfloat16* Vc = reinterpret_cast<const __nv_bfloat16*>(a.vc) + ((long long)b * a.max_seq * a.n_kv + kvh) * 64;
+  const __nv_bfloat16* Ks = reinterpret_cast<const __nv_bfloat16*>(a.sink_k) + (long long)kvh * 64;
+  const __nv_bfloat16* Vs = reinterpret_cast<const __nv_bfloat16*>(a.sink_v) + (long long)kvh * 64;
+
+  // final output of this thread after the cross-warp merge: row = tid / 16, dims 4 * (tid % 16) .. +3
+  float fin[4] = {0.f, 0.f, 0.f, 0.f};
+  const int mrow = tid >> 4, mcol = (tid & 15) * 4;
+  const bool use_c = a.use_alibi && (a.anc ? true : (len + a.Tn) <= a.alibi_max);
+
+  for (int path = 0; path < 3; ++path) {
+    if (path == 2 && !use_c) break;
+    float o[8][4], m[2], l[2];
+    if (path == 0) {
+      const int lo = max(0, pos_min - a.window + 1);
+      attend<0>(a, Kc, Vc, ks, lo, hi_new, len, row, qf, depth, warp, lane, o, m, l);
+    } else if (path == 1) {
+      attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf, depth, warp, lane, o, m, l);
+    } else {
+      attend<2>(a, Kc, Vc, ks, 0, hi_new, len, row, qf, depth, warp, lane, o, m, l);
+    }
+    // each warp parks its partial result; column n of tile j is output dim 8n + j
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      sO[warp][g][16 * t + j] = o[j][0];
+      sO[warp][g][16 * t + 8 + j] = o[j][1];
+      sO[warp][g + 8][16 * t + j] = o[j][2];
+      sO[warp][g + 8][16 * t + 8 + j] = o[j][3];
+    }
+    if (t == 0) {
+      sM[warp][g] = m[0]; sL[warp][g] = l[0];
+      sM[warp][g + 8] = m[1]; sL[warp][g + 8] = l[1];
+    }
+    __syncthreads();
+    {
+      float M = -CUDART_INF_F;
+#pragma unroll
+      for (int w = 0; w < AW; ++w) M = fmaxf(M, sM[w][mrow]);
+      float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (M != -CUDART_INF_F) {
+#pragma unroll
+        for (int w = 0; w < AW; ++w) {
+          const float mw = sM[w][mrow];
+          if (mw == -CUDART_INF_F) continue;
+          const float cw = __expf(mw - M);
+          L += sL[w][mrow] * cw;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[e] += sO[w][mrow][mcol + e] * cw;
+        }
+      }
+      // ALiBi path of a tree node is gated by its own T_k (position + 1 <= 1024)
+      float gate = path == 0 ? a.g_a : (path == 1 ? a.g_b : a.g_c);
+      if (path == 2 && a.anc) {
+        const int r = tile0 + mrow;
+        const int tq = r < R ? r % a.Tn : 0;
+        if (len + (depth ? depth[tq] : tq) + 1 > a.alibi_max) gate = 0.f;
+      }
+      if (L > 0.f) {
+        const float inv = gate / L;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) fin[e] += acc[e] * inv;
+      }
+    }
+    __syncthreads();
+  }
+  const int r = tile0 + mrow;
+  if (r < R) {
+    const int tq = r % a.Tn, hrep = r / a.Tn;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out) + (long long)(b * a.Tn + tq) * a.H * 64 +
+                         (kvh * n_rep + hrep) * 64 + mcol;
+    __nv_bfloat162 v0 = __floats2bfloat162_rn(fin[0], fin[1]), v1 = __floats2bfloat162_rn(fin[2], fin[3]);
+    reinterpret_cast<__nv_bfloat162*>(out)[0] = v0;
+    reinterpret_cast<__nv_bfloat162*>(out)[1] = v1;
+  }
+}
+
+}  // namespace attn_detail
+
+inline bool attn_mma_supported(const AttnArgs& a, bool bf16) {
+  return bf16 && a.hd == 64 && a.Tn <= (a.anc ? 64 : (1 << 20)) && (a.ld_q % 4) == 0;
+}
+
+inline int32_t launch_attn_mma(vn_ctx* ctx, const AttnArgs& a, int B) {
+  const int n_rep = a.H / a.n_kv;
+  dim3 grid(B * a.n_kv, ceil_div(a.Tn * n_rep, 16));
+  VN_LAUNCH(ctx, attn_detail::trisparse_attn_mma_kernel, grid, attn_detail::AW * 32, 0, a);
+  return VN_OK;
+}

@@ -78,6 +78,18 @@ inline int32_t vn_fail(vn_ctx* ctx, int32_t code, const char* fmt, ...) {
       return vn_fail((ctx), VN_ERR_CUDA, "launch of %s failed: %s", #kernel, cudaGetErrorString(_e)); \
   } while (0)
 
+// same, with an explicit name for the per-kernel timing report (call sites of one kernel told apart)
+#define VN_LAUNCH_NAMED(ctx, name, kernel, grid, block, smem, ...)                      \
+  do {                                                                                  \
+    if ((ctx)->profiling) vn_prof_begin((ctx), (name));                                 \
+    kernel<<<(grid), (block), (smem), (ctx)->stream>>>(__VA_ARGS__);                    \
+    if ((ctx)->profiling) vn_prof_end((ctx));                                           \
+    (ctx)->launches++;                                                                  \
+    cudaError_t _e = cudaGetLastError();                                                \
+    if (_e != cudaSuccess)                                                              \
+      return vn_fail((ctx), VN_ERR_CUDA, "launch of %s failed: %s", (name), cudaGetErrorString(_e)); \
+  } while (0)
+
 int32_t vn_workspace(vn_ctx* ctx, size_t bytes, void** out);
 
 template <typename T>

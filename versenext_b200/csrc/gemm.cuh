@@ -25,6 +25,7 @@ struct GemmArgs {
   int nseg = 1;
   int epi = EPI_STORE;
   int c_bf16 = 0;
+  const char* tag = nullptr;      // name of the call site in the per-kernel timing report (string literal)
 };
 
 __device__ __forceinline__ float ld_f(const float* p) { return *p; }

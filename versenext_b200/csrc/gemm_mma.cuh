@@ -174,7 +174,7 @@ inline int32_t launch_gemm_mma(vn_ctx* ctx, const GemmArgs& g) {
     attr_set |= 1ull << (ctx->device & 63);
   }
   dim3 grid(ceil_div(g.M, BM), ceil_div(g.N, BN), g.nseg);
-  if (big) VN_LAUNCH(ctx, gemm_mma_kernel<128>, grid, 256, smem, g);
-  else VN_LAUNCH(ctx, gemm_mma_kernel<64>, grid, 128, smem, g);
+  if (big) VN_LAUNCH_NAMED(ctx, g.tag ? g.tag : "gemm_mma_kernel<128>", gemm_mma_kernel<128>, grid, 256, smem, g);
+  else VN_LAUNCH_NAMED(ctx, g.tag ? g.tag : "gemm_mma_kernel<64>", gemm_mma_kernel<64>, grid, 128, smem, g);
   return VN_OK;
 }

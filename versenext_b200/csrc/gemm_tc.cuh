@@ -1,0 +1,328 @@
+// Weight-streaming skinny GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
+//
+//   C[m, n] = sum_k X[m, k] * W[n, k]        X: tokens x K (bf16), W: features x K (bf16), few tokens (<= 256)
+//
+// The roles are swapped with respect to the usual layout: the WEIGHT tile is the UMMA "A" operand (M = 128
+// output features -> 128 TMEM lanes) and the token block is the "B" operand (N = tokens, 16 .. 256), so one
+// CTA streams a 128 x K slab of the weight matrix exactly once while the small activation block is re-read
+// from L2.  D[feature, token] accumulates in TMEM (fp32), is read back with tcgen05.ld by four epilogue
+// warps (lane = feature), and is written so that consecutive lanes hit consecutive features of one token.
+//
+// CTA = 6 warps: warp 0 issues TMA loads (one elected thread), warp 1 allocates TMEM and issues tcgen05.mma
+// (one thread), warps 2..5 run the epilogue.  A ring of STAGES shared-memory stages (weight tile 128 x 64 +
+// token tile NTOK x 64, both 128-byte swizzled, K-major) is handed over with mbarriers.  Every wait is
+// bounded: when it runs out the kernel raises a flag in global memory, stops issuing work, and still frees
+// its TMEM before returning.
+//
+// Split-K: blockIdx.y selects a K range; partial tiles go to a workspace [split][rows][N] and are reduced by
+// the caller's finalize kernel (deterministic order).
+#pragma once
+#include <cuda.h>
+#include "gemm.cuh"
+
+namespace tc_detail {
+
+constexpr int BF = 128;        // features per CTA (UMMA M)
+constexpr int BK = 64;         // K elements per stage = one 128-byte swizzle row
+constexpr int TC_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;  // ~1 s
+
+struct TcArgs {
+  void* C;                 // see epi
+  const float* bias;
+  long long ldc;
+  int M, N, K;             // tokens (per segment: upper bound), features, reduction
+  int ntok;                // UMMA N: tokens rounded up to 16
+  int stages;
+  int kb_per_split;        // k blocks (of 64) per blockIdx.y
+  int epi, c_bf16;
+  const int* seg_off;      // segmented mode (blockIdx.z = segment)
+  const int* seg_cnt;
+  long long w_rows_per_seg;  // rows of W between consecutive segments
+  float* partial;          // split-K workspace [gridDim.y][rows_total][N] or null
+  long long partial_stride;  // rows_total * N
+  int* error_flag;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded wait; false when the limit ran out
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try(bar, parity)) {
+    if ((unsigned long long)(clock64() - t0) > WAIT_LIMIT_CYCLES) return false;
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, unsigned long long* bar, int c0,
+                                            int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// K-major, 128-byte swizzle: 8-row groups of 1024 bytes (SBO = 1024 B -> 64), LBO unused (= 1), version 1
+__device__ __forceinline__ unsigned long long umma_desc(const void* smem_tile) {
+  const unsigned addr = smem_u32(smem_tile);
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)1 << 16;
+  d |= (unsigned long long)64 << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
+                                          unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs g) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ unsigned long long bar_full[8], bar_empty[8], bar_acc;
+  __shared__ unsigned tmem_base_slot;
+  __shared__ int s_error;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int z = blockIdx.z;
+  int row0 = 0, cnt = g.M;
+  if (g.seg_cnt) { row0 = g.seg_off[z]; cnt = g.seg_cnt[z]; }
+  if (cnt > g.ntok) cnt = g.ntok;
+  const int n0 = blockIdx.x * BF;
+  const int nkb_total = (g.K + BK - 1) / BK;
+  const int kb0 = blockIdx.y * g.kb_per_split;
+  int nkb = nkb_total - kb0;
+  if (nkb > g.kb_per_split) nkb = g.kb_per_split;
+  // nothing to do for this CTA: uniform exit before any barrier or TMEM allocation
+  if (cnt <= 0 || nkb <= 0) return;
+
+  // stage buffers: 1024-byte aligned (swizzle atom), weight tile then token tile
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const unsigned w_bytes = BF * BK * 2, x_bytes = (unsigned)g.ntok * BK * 2;
+  const unsigned stage_bytes = w_bytes + x_bytes;
+  const int S = g.stages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
+    mbar_init(&bar_acc, 1);
+    s_error = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  // TMEM: power of two >= ntok rounded to 32 columns
+  unsigned ncols = 32;
+  while (ncols < (unsigned)((g.ntok + 31) & ~31)) ncols <<= 1;
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int w_row = (int)((long long)z * g.w_rows_per_seg) + n0;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % S;
+        if (!mbar_wait(&bar_empty[s], ((kb / S) & 1) ^ 1)) { s_error = 1; break; }
+        unsigned char* st = base + (size_t)s * stage_bytes;
+        mbar_expect_tx(&bar_full[s], stage_bytes);
+        const int kx = (kb0 + kb) * BK;
+        tma_load_2d(st, &tm_w, &bar_full[s], kx, w_row);
+        tma_load_2d(st + w_bytes, &tm_x, &bar_full[s], kx, row0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // instruction descriptor: D fp32, A and B bf16, both K-major, N = ntok, M = 128
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(g.ntok >> 3) << 17) | ((unsigned)(BF >> 4) << 24);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % S;
+        if (!mbar_wait(&bar_full[s], (kb / S) & 1)) { s_error = 1; ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned char* st = base + (size_t)s * stage_bytes;
+        const unsigned long long da = umma_desc(st), db = umma_desc(st + w_bytes);
+#pragma unroll
+        for (int k4 = 0; k4 < BK / 16; ++k4)   // +32 bytes along K inside the swizzle row: +2 in the address field
+          umma_bf16(tmem_base, da + 2ull * k4, db + 2ull * k4, idesc, (kb | k4) != 0);
+        umma_commit(&bar_empty[s]);            // frees the stage when these MMAs have read it
+      }
+      umma_commit(&bar_acc);                   // accumulator complete (or abandoned)
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
+    const int q = warp & 3;
+    const int f = q * 32 + lane;               // feature within the tile
+    const int n = n0 + f;
+    const bool acc_ok = mbar_wait(&bar_acc, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!acc_ok) s_error = 1;
+    // one decision per warp: the TMEM loads below are warp-collective
+    const int go = __shfl_sync(0xffffffffu, (acc_ok && *(volatile int*)&s_error == 0) ? 1 : 0, 0);
+    if (go) {
+      const int nchunk = (cnt + 31) >> 5;
+      for (int ch = 0; ch < nchunk; ++ch) {
+        unsigned r[32];
+        tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(ch * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int m = ch * 32 + i;
+          float v = __uint_as_float(r[i]);
+          const long long crow = (long long)(row0 + m);
+          if (g.partial) {
+            if (m < cnt && n < g.N) g.partial[(long long)blockIdx.y * g.partial_stride + crow * g.N + n] = v;
+          } else if (g.epi == EPI_SWIGLU) {
+            const float other = __shfl_xor_sync(0xffffffffu, v, 1);   // (gate, up) sit in adjacent lanes
+            if (m < cnt && !(lane & 1) && n + 1 < g.N)
+              store_out<float>(g.C, crow * g.ldc + (n >> 1), silu_ref(v) * other, g.c_bf16);
+          } else if (m < cnt && n < g.N) {
+            if (g.epi == EPI_ADD) reinterpret_cast<float*>(g.C)[crow * g.ldc + n] += v;
+            else store_out<float>(g.C, crow * g.ldc + n, v + (g.bias ? g.bias[n] : 0.f), g.c_bf16);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (s_error) {
+    // give copies and MMAs that may still be in flight time to land before shared memory and TMEM are released
+    if (threadIdx.x == 0 && g.error_flag) atomicExch(g.error_flag, 1);
+    const long long t0 = clock64();
+    while ((unsigned long long)(clock64() - t0) < 200000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, K] with row pitch ld (elements); box = 64 x box_rows, 128-byte swizzle, zero fill
+inline bool make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace tc_detail
+
+struct TcPlan {
+  int splits = 1;
+  bool force_partial = false;    // write to the workspace even when one K range is enough
+  int splits_used = 1;           // out: number of partial slices written
+  float* partial = nullptr;      // caller-provided workspace for split-K partials
+  long long rows_total = 0;      // rows addressed in C (all segments)
+  int* error_flag = nullptr;
+};
+
+// Supported: bf16 operands, K-major, 16-byte aligned rows, tokens <= 256, A rows contiguous (no gather).
+inline bool gemm_tc_supported(const GemmArgs& g) {
+  return g.M >= 1 && g.M <= 256 && g.a_rows == nullptr && g.ldw_k == 1 && g.K % 8 == 0 && g.lda % 8 == 0 &&
+         g.ldw % 8 == 0 && ((uintptr_t)g.A & 15) == 0 && ((uintptr_t)g.W & 15) == 0 &&
+         (g.seg_cnt != nullptr || g.nseg == 1) && tc_detail::encode_fn() != nullptr;
+}
+
+// a_rows_total: number of valid rows behind g.A (rows beyond are zero-filled by TMA)
+inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_total, TcPlan& plan) {
+  using namespace tc_detail;
+  if (g.M <= 0 || g.N <= 0) return VN_OK;
+  const int ntok = (g.M + 15) & ~15;
+  CUtensorMap tm_w, tm_x;
+  const long long w_rows = g.seg_cnt ? (long long)(g.nseg - 1) * (g.w_stride / g.ldw) + g.N : g.N;
+  if (!make_map(&tm_w, g.W, w_rows, g.K, g.ldw, BF) || !make_map(&tm_x, g.A, a_rows_total, g.K, g.lda, ntok))
+    return vn_fail(ctx, VN_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  TcArgs a;
+  a.C = g.C; a.bias = g.bias; a.ldc = g.ldc; a.M = g.M; a.N = g.N; a.K = g.K; a.ntok = ntok;
+  const size_t stage_bytes = (size_t)BF * BK * 2 + (size_t)ntok * BK * 2;
+  const int nkb = (g.K + BK - 1) / BK;
+  const int splits = std::max(1, std::min(plan.splits, nkb));
+  a.kb_per_split = (nkb + splits - 1) / splits;
+  int stages = (int)std::min<size_t>(8, (200 * 1024) / stage_bytes);
+  stages = std::max(2, std::min(stages, std::max(2, a.kb_per_split)));
+  a.stages = stages;
+  a.epi = g.epi; a.c_bf16 = g.c_bf16;
+  a.seg_off = g.seg_off; a.seg_cnt = g.seg_cnt;
+  a.w_rows_per_seg = g.seg_cnt ? g.w_stride / g.ldw : 0;
+  const int gy = ceil_div(nkb, a.kb_per_split);
+  plan.splits_used = gy;
+  a.partial = (gy > 1 || plan.force_partial) ? plan.partial : nullptr;
+  a.partial_stride = plan.rows_total * (long long)g.N;
+  a.error_flag = plan.error_flag;
+  if ((gy > 1 || plan.force_partial) && !plan.partial) return vn_fail(ctx, VN_ERR_INVALID, "split-K needs a workspace");
+  const size_t smem = stage_bytes * stages + 1024;
+  static unsigned long long attr_set = 0;
+  if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    attr_set |= 1ull << (ctx->device & 63);
+  }
+  dim3 grid(ceil_div(g.N, BF), gy, g.nseg);
+  VN_LAUNCH_NAMED(ctx, g.tag ? g.tag : "gemm_tc_kernel", gemm_tc_kernel, grid, TC_THREADS, smem, tm_w, tm_x, a);
+  return VN_OK;
+}

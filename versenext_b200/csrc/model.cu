@@ -5,6 +5,8 @@
 #include "gemm.cuh"
 #include "gemm_mma.cuh"
 #include "model_kernels.cuh"
+#include "attn_mma.cuh"
+#include "gemm_tc.cuh"
 
 #include <math.h>
 #include <stdlib.h>
@@ -120,6 +122,12 @@ struct vn_model {
   int* sorted_row = nullptr; int* slot_pos = nullptr;
   int* depth_dev = nullptr; unsigned long long* anc_dev = nullptr; int* rows_dev = nullptr;
   float* stage = nullptr; size_t stage_elems = 0;
+  void* hs = nullptr;            // [M * slots, D] routed activations in expert order (tcgen05 path)
+  float* partial = nullptr;      // split-K workspace of the tcgen05 path
+  size_t partial_bytes = 0;
+  int* tc_error = nullptr;       // device word raised by a bounded wait that ran out
+  bool use_tc = true;            // VN_GEMM_TC=0 in the environment: keep the mma.sync GEMMs
+  bool force_simt_attn = false;  // VN_ATTN_SIMT=1 in the environment: keep the SIMT attention kernel (A/B checks)
 };
 
 struct vn_kv {
@@ -211,9 +219,9 @@ int32_t ensure_rows(vn_model* m, int M) {
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   void** bufs[] = {(void**)&m->x, &m->h, (void**)&m->h32, (void**)&m->qkv, &m->attn, &m->act, (void**)&m->y,
                    (void**)&m->slot_expert, (void**)&m->slot_w, (void**)&m->part_w, (void**)&m->sorted_row,
-                   (void**)&m->slot_pos, (void**)&m->rows_dev};
+                   (void**)&m->slot_pos, (void**)&m->rows_dev, &m->hs};
   for (void** b : bufs) { if (*b) cudaFree(*b); *b = nullptr; }
-  const size_t e = m->esz, D = c.dim, R = (size_t)M + (M >> 2) + 8;
+  const size_t e = m->esz, D = c.dim, R = (size_t)M + (M >> 2) + 32;
   bool has_mod = false;
   for (int k : c.kind) has_mod |= (k == 1);
   const size_t S = has_mod ? (size_t)c.P * c.top_k : 1;
@@ -227,6 +235,7 @@ int32_t ensure_rows(vn_model* m, int M) {
   TRY(dev_alloc(ctx, (void**)&m->rows_dev, R * 4));
   if (has_mod) {
     TRY(dev_alloc(ctx, (void**)&m->y, R * S * D * 4));
+    if (c.bf16) TRY(dev_alloc(ctx, &m->hs, R * S * D * e));
     TRY(dev_alloc(ctx, (void**)&m->slot_expert, R * S * 4));
     TRY(dev_alloc(ctx, (void**)&m->slot_w, R * S * 4));
     TRY(dev_alloc(ctx, (void**)&m->part_w, R * c.P * 4));
@@ -265,9 +274,10 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
             m->status);
   for (int li = 0; li < c.n_layer; ++li) {
     Layer& L = m->layers[li];
-    VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm1, (T*)m->h, (float*)nullptr, (const int*)nullptr, D, 1e-6f);
+    VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm1, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.C = m->qkv; g.ldc = qkv_ld; g.M = M; g.N = qkv_ld; g.K = D;
+    g.tag = "gemm_qkv";
     TRY(linear(m, g));
     VN_LAUNCH(ctx, rope_append_kernel<T>, M, 128, 0, m->qkv, m->rope_cos, m->rope_sin, kv->lens,
               tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq,
@@ -281,25 +291,27 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
     a.g_b = 1.f / (1.f + expf(-L.gate_logits[1]));
     a.g_c = 1.f / (1.f + expf(-L.gate_logits[2]));
     a.scale = 1.0f / sqrtf((float)hd);
-    {
+    if (attn_mma_supported(a, c.bf16 != 0) && !m->force_simt_attn) {
+      TRY(launch_attn_mma(ctx, a, B));
+    } else {
       dim3 grid(ceil_div(H, 8), M);
       VN_LAUNCH(ctx, trisparse_attn_kernel<T>, grid, 256, 0, a);
     }
     g = GemmArgs();
     g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.C = m->x; g.ldc = D; g.M = M; g.N = D; g.K = H * hd;
-    g.epi = EPI_ADD;
+    g.epi = EPI_ADD; g.tag = "gemm_proj";
     TRY(linear(m, g));
     const bool mod = L.kind == 1;
     VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm2, (T*)m->h, mod ? m->h32 : (float*)nullptr,
-              (const int*)nullptr, D, 1e-6f);
+              1, 0, D, 1e-6f);
     if (!mod) {
       g = GemmArgs();
       g.A = m->h; g.lda = D; g.W = L.w_gateup; g.ldw = D; g.C = m->act; g.ldc = c.mlp_hidden; g.M = M;
-      g.N = 2 * c.mlp_hidden; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = c.bf16;
+      g.N = 2 * c.mlp_hidden; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = c.bf16; g.tag = "gemm_gateup";
       TRY(linear(m, g));
       g = GemmArgs();
       g.A = m->act; g.lda = c.mlp_hidden; g.W = L.w_down; g.ldw = c.mlp_hidden; g.C = m->x; g.ldc = D; g.M = M; g.N = D;
-      g.K = c.mlp_hidden; g.epi = EPI_ADD;
+      g.K = c.mlp_hidden; g.epi = EPI_ADD; g.tag = "gemm_down";
       TRY(linear(m, g));
     } else {
       const int ne = c.P * c.E, S = c.P * c.top_k, eh = c.expert_hidden;
@@ -314,32 +326,177 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
       g = GemmArgs();
       g.A = m->h; g.lda = D; g.a_rows = m->sorted_row; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
       g.C = m->act; g.ldc = eh; g.M = M; g.N = 2 * eh; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = c.bf16;
-      g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne;
+      g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne; g.tag = "gemm_expert_gateup";
       TRY(linear(m, g));
       g = GemmArgs();
       g.A = m->act; g.lda = eh; g.W = L.e_down; g.ldw = eh; g.w_stride = (long long)D * eh; g.C = m->y; g.ldc = D;
       g.M = M; g.N = D; g.K = eh; g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne;
+      g.tag = "gemm_expert_down";
       TRY(linear(m, g));
       VN_LAUNCH(ctx, mod_combine_kernel, M, 256, 0, m->x, m->y, m->slot_pos, m->slot_w, m->part_w, D, c.P, c.top_k);
     }
   }
   // final norm + head on every row, or on the last position of every sequence
-  int rows_out = M;
-  const int* row_sel = nullptr;
-  if (last_only) {
-    rows_out = B;
-    std::vector<int> sel(B);
-    for (int b = 0; b < B; ++b) sel[b] = b * Tn + Tn - 1;
-    VN_CUDA(ctx, cudaMemcpyAsync(m->rows_dev, sel.data(), B * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
-    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `sel` is a stack-owned host buffer
-    row_sel = m->rows_dev;
-  }
-  VN_LAUNCH(ctx, rmsnorm_kernel<T>, rows_out, 256, 0, m->x, m->norm_f, (T*)m->h, out_hidden, row_sel, D, 1e-6f);
+  const int rows_out = last_only ? B : M;
+  const int row_mul = last_only ? Tn : 1, row_add = last_only ? Tn - 1 : 0;
+  VN_LAUNCH(ctx, rmsnorm_kernel<T>, rows_out, 256, 0, m->x, m->norm_f, (T*)m->h, out_hidden, row_mul, row_add, D, 1e-6f);
   if (out_logits) {
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = m->head; g.ldw = D; g.C = out_logits; g.ldc = c.vocab; g.M = rows_out; g.N = c.vocab;
-    g.K = D;
+    g.K = D; g.tag = "gemm_head";
     TRY(linear(m, g));
+  }
+  return VN_OK;
+}
+
+// ---- decode / verify forward on the tcgen05 weight-streaming GEMM (bf16, at most 256 rows) ----------------
+// Same arithmetic as forward_t<bf16>; the differences are scheduling: small-N GEMMs are split along K so that
+// about two CTAs per SM stream weights, their partials are reduced by a finalize kernel that also applies the
+// residual add and the next RMSNorm, and routed tokens are gathered into expert order so that TMA can load them.
+int32_t ensure_partial(vn_model* m, size_t bytes) {
+  vn_ctx* ctx = m->ctx;
+  if (!m->tc_error) {
+    TRY(dev_alloc(ctx, (void**)&m->tc_error, 4));
+    VN_CUDA(ctx, cudaMemsetAsync(m->tc_error, 0, 4, ctx->stream));
+  }
+  if (bytes <= m->partial_bytes) return VN_OK;
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (m->partial) VN_CUDA(ctx, cudaFree(m->partial));
+  m->partial = nullptr; m->partial_bytes = 0;
+  const size_t want = bytes + (bytes >> 2);
+  TRY(dev_alloc(ctx, (void**)&m->partial, want));
+  m->partial_bytes = want;
+  return VN_OK;
+}
+
+// choose a split count so that tiles * splits covers the GPU about twice, never more than the k blocks
+int tc_splits(const vn_ctx* ctx, int N, int K, int nseg) {
+  const int tiles = ceil_div(N, tc_detail::BF) * nseg;
+  const int nkb = ceil_div(K, tc_detail::BK);
+  int s = ceil_div(2 * ctx->sm_count, tiles);
+  s = std::max(1, std::min(s, nkb));
+  const int per = ceil_div(nkb, s);
+  return ceil_div(nkb, per);   // effective number of K ranges
+}
+
+// launches the GEMM into the split-K workspace; returns the number of partial slices through *splits_out
+int32_t tc_partial(vn_model* m, GemmArgs g, long long a_rows, long long c_rows, int* splits_out) {
+  vn_ctx* ctx = m->ctx;
+  const int splits = tc_splits(ctx, g.N, g.K, g.nseg);
+  TRY(ensure_partial(m, (size_t)splits * c_rows * g.N * 4));
+  TcPlan plan;
+  plan.splits = splits; plan.force_partial = true;
+  plan.partial = m->partial; plan.rows_total = c_rows; plan.error_flag = m->tc_error;
+  TRY(launch_gemm_tc(ctx, g, a_rows, plan));
+  *splits_out = plan.splits_used;
+  return VN_OK;
+}
+
+int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, bool tree, float* out_hidden,
+                   float* out_logits, int last_only, int slot_offset) {
+  typedef __nv_bfloat16 T;
+  vn_ctx* ctx = m->ctx;
+  const Config& c = m->cfg;
+  const int M = B * Tn, D = c.dim, H = c.n_head, hd = c.hd, n_kv = c.n_kv;
+  const int qkv_ld = (H + 2 * n_kv) * hd;
+  const long long cap = m->cap_rows;
+  const float emb_scale = c.emb_scale ? sqrtf((float)D) : 1.0f;
+  TcPlan direct;
+  TRY(ensure_partial(m, 1024));
+  direct.error_flag = m->tc_error;
+  VN_LAUNCH(ctx, embed_kernel<T>, M, 128, 0, (const long long*)tokens, (const T*)m->emb, m->x, D, c.vocab, emb_scale,
+            m->status);
+  VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, m->layers[0].norm1, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
+  for (int li = 0; li < c.n_layer; ++li) {
+    Layer& L = m->layers[li];
+    const bool mod = L.kind == 1;
+    const bool last = li + 1 == c.n_layer;
+    int sp = 1;
+    GemmArgs g;
+    // ---- attention block
+    g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.M = M; g.N = qkv_ld; g.K = D; g.tag = "gemm_qkv";
+    TRY(tc_partial(m, g, cap, M, &sp));
+    {
+      const long long total = (long long)M * qkv_ld;
+      VN_LAUNCH(ctx, splitk_store_kernel, (unsigned)ceil_div(total, 256ll), 256, 0, m->partial, sp, total, m->qkv,
+                (long long)qkv_ld, qkv_ld, total);
+    }
+    VN_LAUNCH(ctx, rope_append_kernel<T>, M, 128, 0, m->qkv, m->rope_cos, m->rope_sin, kv->lens,
+              tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq,
+              c.use_rope, m->rope_rows, slot_offset);
+    AttnArgs a;
+    a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[li]; a.vc = kv->v[li]; a.sink_k = L.sink_k; a.sink_v = L.sink_v;
+    a.out = m->attn; a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
+    a.Tn = Tn; a.H = H; a.n_kv = n_kv; a.hd = hd; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink;
+    a.use_alibi = c.use_alibi; a.alibi_max = 1024; a.slot_offset = slot_offset;
+    a.g_a = 1.f / (1.f + expf(-L.gate_logits[0]));
+    a.g_b = 1.f / (1.f + expf(-L.gate_logits[1]));
+    a.g_c = 1.f / (1.f + expf(-L.gate_logits[2]));
+    a.scale = 1.0f / sqrtf((float)hd);
+    if (attn_mma_supported(a, true) && !m->force_simt_attn) {
+      TRY(launch_attn_mma(ctx, a, B));
+    } else {
+      dim3 grid(ceil_div(H, 8), M);
+      VN_LAUNCH(ctx, trisparse_attn_kernel<T>, grid, 256, 0, a);
+    }
+    g = GemmArgs();
+    g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.M = M; g.N = D; g.K = H * hd; g.tag = "gemm_proj";
+    TRY(tc_partial(m, g, cap, M, &sp));
+    VN_LAUNCH(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, L.norm2, (T*)m->h,
+              mod ? m->h32 : (float*)nullptr, D, 1e-6f);
+    // ---- feed-forward block
+    const float* next_norm = last ? nullptr : m->layers[li + 1].norm1;
+    if (!mod) {
+      g = GemmArgs();
+      g.A = m->h; g.lda = D; g.W = L.w_gateup; g.ldw = D; g.M = M; g.N = 2 * c.mlp_hidden; g.K = D;
+      g.tag = "gemm_gateup";
+      TRY(tc_partial(m, g, cap, M, &sp));
+      {
+        const long long pairs = (long long)M * c.mlp_hidden;
+        VN_LAUNCH(ctx, splitk_swiglu_kernel<T>, (unsigned)ceil_div(pairs, 256ll), 256, 0, m->partial, sp,
+                  (long long)M * 2 * c.mlp_hidden, (T*)m->act, 2 * c.mlp_hidden, pairs);
+      }
+      g = GemmArgs();
+      g.A = m->act; g.lda = c.mlp_hidden; g.W = L.w_down; g.ldw = c.mlp_hidden; g.M = M; g.N = D; g.K = c.mlp_hidden;
+      g.tag = "gemm_down";
+      TRY(tc_partial(m, g, cap, M, &sp));
+      VN_LAUNCH(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm, (T*)m->h,
+                (float*)nullptr, D, 1e-6f);
+    } else {
+      const int ne = c.P * c.E, S = c.P * c.top_k, eh = c.expert_hidden;
+      VN_CUDA(ctx, cudaMemsetAsync(m->expert_count, 0, ne * 4, ctx->stream));
+      RouteArgs r;
+      r.h = m->h32; r.gates = L.router; r.slot_expert = m->slot_expert; r.slot_w = m->slot_w; r.part_w = m->part_w;
+      r.expert_count = m->expert_count; r.M = M; r.D = D; r.P = c.P; r.E = c.E; r.top_k = c.top_k;
+      VN_LAUNCH(ctx, mod_route_kernel, ceil_div(M, 4), 128, 0, r);
+      VN_LAUNCH(ctx, mod_offsets_kernel, 1, 32, 0, m->expert_count, m->expert_off, m->expert_cur, ne);
+      VN_LAUNCH(ctx, mod_scatter_kernel, ceil_div(M * S, 256), 256, 0, m->slot_expert, m->expert_off, m->expert_cur,
+                m->sorted_row, m->slot_pos, M * S, S);
+      VN_LAUNCH(ctx, gather_sorted_kernel<T>, M * S, 128, 0, (const T*)m->h, m->sorted_row, (T*)m->hs, D);
+      g = GemmArgs();
+      g.A = m->hs; g.lda = D; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
+      g.C = m->act; g.ldc = eh; g.M = M; g.N = 2 * eh; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = 1;
+      g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne; g.tag = "gemm_expert_gateup";
+      TRY(launch_gemm_tc(ctx, g, (long long)M * S, direct));
+      g = GemmArgs();
+      g.A = m->act; g.lda = eh; g.W = L.e_down; g.ldw = eh; g.w_stride = (long long)D * eh;
+      g.M = M; g.N = D; g.K = eh; g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne;
+      g.tag = "gemm_expert_down";
+      TRY(tc_partial(m, g, (long long)M * S, (long long)M * S, &sp));
+      VN_LAUNCH(ctx, mod_combine_split_kernel, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
+                m->slot_w, m->part_w, D, c.P, c.top_k);
+      if (next_norm)
+        VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
+    }
+  }
+  const int rows_out = last_only ? B : M;
+  const int row_mul = last_only ? Tn : 1, row_add = last_only ? Tn - 1 : 0;
+  VN_LAUNCH(ctx, rmsnorm_kernel<T>, rows_out, 256, 0, m->x, m->norm_f, (T*)m->h, out_hidden, row_mul, row_add, D, 1e-6f);
+  if (out_logits) {
+    GemmArgs g;
+    g.A = m->h; g.lda = D; g.W = m->head; g.ldw = D; g.C = out_logits; g.ldc = c.vocab; g.M = rows_out; g.N = c.vocab;
+    g.K = D; g.tag = "gemm_head";
+    TRY(launch_gemm_tc(ctx, g, cap, direct));
   }
   return VN_OK;
 }
@@ -395,6 +552,8 @@ int32_t vn_model_create(vn_ctx* ctx, const char* config_json, vn_model** out) {
              c.P + c.P * c.E <= 64, "MoD shape unsupported (P=%d E=%d top_k=%d)", c.P, c.E, c.top_k);
   vn_model* m = new vn_model();
   m->ctx = ctx; m->cfg = c; m->esz = c.bf16 ? 2 : 4;
+  { const char* e = getenv("VN_ATTN_SIMT"); m->force_simt_attn = e && e[0] == '1'; }
+  { const char* e = getenv("VN_GEMM_TC"); m->use_tc = !(e && e[0] == '0'); }
   int32_t st = alloc_weights(m);
   if (st != VN_OK) { vn_model_destroy(m); return st; }
   *out = m;
@@ -413,7 +572,7 @@ int32_t vn_model_destroy(vn_model* m) {
   }
   F(m->x); F(m->h); F(m->h32); F(m->qkv); F(m->attn); F(m->act); F(m->y); F(m->slot_expert); F(m->slot_w); F(m->part_w);
   F(m->expert_count); F(m->expert_off); F(m->expert_cur); F(m->sorted_row); F(m->slot_pos); F(m->depth_dev);
-  F(m->anc_dev); F(m->rows_dev); F(m->stage);
+  F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error);
   delete m;
   return VN_OK;
 }
@@ -751,6 +910,9 @@ int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
     VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   }
   TRY(ensure_rows(m, B * T));
+  if (m->cfg.bf16 && m->use_tc && B * T <= 256 && m->cfg.dim % 8 == 0 && m->cfg.dim <= 2048 &&
+      tc_detail::encode_fn() != nullptr)
+    return forward_tc(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
   if (m->cfg.bf16) return forward_t<__nv_bfloat16>(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
   return forward_t<float>(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
 }

@@ -37,13 +37,13 @@ __global__ void embed_kernel(const long long* __restrict__ tokens, const T* __re
   for (int d = threadIdx.x; d < D; d += blockDim.x) x[(long long)row * D + d] = to_f<T>(e[d]) * scale;
 }
 
-// ---- RMSNorm: y = x / sqrt(mean(x^2) + eps) * w (vnnn.py:501-505).  Optional row gather, optional fp32 copy.
+// ---- RMSNorm: y = x / sqrt(mean(x^2) + eps) * w (vnnn.py:501-505).  Source row = i * row_mul + row_add; optional fp32 copy.
 template <typename T>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                       T* __restrict__ y, float* __restrict__ y32,
-                                                      const int* __restrict__ rows, int D, float eps) {
+                                                      int row_mul, int row_add, int D, float eps) {
   __shared__ float sm[8];
-  const long long src = rows ? rows[blockIdx.x] : blockIdx.x;
+  const long long src = (long long)blockIdx.x * row_mul + row_add;   // e.g. the last position of every sequence
   const float* xr = x + src * D;
   float ss = 0.f;
   for (int d = threadIdx.x; d < D; d += 256) ss += xr[d] * xr[d];
@@ -318,43 +318,48 @@ struct RouteArgs {
 };
 
 __global__ void __launch_bounds__(128) mod_route_kernel(RouteArgs r) {
+  __shared__ float s_lg[4][64];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + warp;
   if (row >= r.M) return;
-  const int n_logit = r.P + r.P * r.E;       // <= 64 supported
+  const int n_logit = r.P + r.P * r.E;       // <= 64
   const float* x = r.h + (long long)row * r.D;
-  float lg[64];
   for (int g = 0; g < n_logit; ++g) {
     const float* w = r.gates + (long long)g * r.D;
     float s = 0.f;
     for (int d = lane; d < r.D; d += 32) s = fmaf(x[d], w[d], s);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    lg[g] = s;
+    if (lane == 0) s_lg[warp][g] = s;
   }
-  if (lane != 0) return;
-  // part weights: softmax over all parts
-  float m = -CUDART_INF_F;
-  for (int p = 0; p < r.P; ++p) m = fmaxf(m, lg[p]);
-  float den = 0.f;
-  for (int p = 0; p < r.P; ++p) den += expf(lg[p] - m);
-  for (int p = 0; p < r.P; ++p) r.part_w[(long long)row * r.P + p] = expf(lg[p] - m) / den;
-  for (int p = 0; p < r.P; ++p) {
+  __syncwarp();
+  const float* lg = s_lg[warp];
+  if (lane == 31 || r.P > 31) {
+    // part weights: softmax over all parts (one lane; P is tiny)
+    if (lane == 31 || lane == 0) {
+      float m = -CUDART_INF_F;
+      for (int p = 0; p < r.P; ++p) m = fmaxf(m, lg[p]);
+      float den = 0.f;
+      for (int p = 0; p < r.P; ++p) den += expf(lg[p] - m);
+      for (int p = 0; p < r.P; ++p) r.part_w[(long long)row * r.P + p] = expf(lg[p] - m) / den;
+    }
+  }
+  // one lane per part: top-k of its expert logits (lowest index wins ties), softmax over the kept logits
+  for (int p = lane; p < r.P; p += 32) {
     const float* el = lg + r.P + p * r.E;
     int sel[8]; float sl[8];
     unsigned long long used = 0ull;
-    for (int j = 0; j < r.top_k; ++j) {        // repeated argmax, lowest index on ties
+    for (int j = 0; j < r.top_k; ++j) {
       int best = -1; float bv = -CUDART_INF_F;
       for (int e = 0; e < r.E; ++e)
         if (!((used >> e) & 1ull) && (best < 0 || el[e] > bv)) { best = e; bv = el[e]; }
       used |= 1ull << best;
       sel[j] = best; sl[j] = bv;
     }
-    float em = sl[0];
+    const float em = sl[0];
     float ed = 0.f;
     for (int j = 0; j < r.top_k; ++j) ed += expf(sl[j] - em);
-    // ascending expert id inside the part
-    for (int i = 1; i < r.top_k; ++i)
+    for (int i = 1; i < r.top_k; ++i)      // ascending expert id inside the part
       for (int j = i; j > 0 && sel[j - 1] > sel[j]; --j) {
         const int ti = sel[j]; sel[j] = sel[j - 1]; sel[j - 1] = ti;
         const float tf = sl[j]; sl[j] = sl[j - 1]; sl[j - 1] = tf;
@@ -450,4 +455,112 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __r
                                    int D) {
   const long long s = rows[blockIdx.x];
   for (int d = threadIdx.x; d < D; d += blockDim.x) dst[(long long)blockIdx.x * D + d] = src[s * D + d];
+}
+
+// ---- split-K finalize kernels (partials [splits][rows][N] fp32, summed in split order: deterministic) -----
+// x[row] += sum_s partial[s][row]; then, if norm_w, y = RMSNorm(x) * norm_w in the storage dtype (+ fp32 copy).
+// One CTA per row; D <= 256 * 8.
+template <typename T>
+__global__ void __launch_bounds__(256) splitk_add_norm_kernel(const float* __restrict__ partial, int splits,
+                                                              long long pstride, float* __restrict__ x,
+                                                              const float* __restrict__ norm_w, T* __restrict__ y,
+                                                              float* __restrict__ y32, int D, float eps) {
+  __shared__ float sm[8];
+  const long long row = blockIdx.x;
+  float v[8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = threadIdx.x + i * 256;
+    v[i] = 0.f;
+    if (d < D) {
+      float acc = 0.f;
+      for (int s = 0; s < splits; ++s) acc += partial[(long long)s * pstride + row * D + d];
+      v[i] = x[row * D + d] + acc;
+      x[row * D + d] = v[i];
+      ss += v[i] * v[i];
+    }
+  }
+  if (!norm_w) return;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += sm[i];
+  const float r = sqrtf(tot / (float)D + eps);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = threadIdx.x + i * 256;
+    if (d < D) {
+      const float o = v[i] / r * norm_w[d];
+      if (y) y[row * D + d] = from_f<T>(o);
+      if (y32) y32[row * D + d] = o;
+    }
+  }
+}
+
+// out[row, n] = sum_s partial[s][row][n]
+__global__ void splitk_store_kernel(const float* __restrict__ partial, int splits, long long pstride,
+                                    float* __restrict__ out, long long ld, int N, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long row = i / N;
+  const int n = (int)(i % N);
+  float acc = 0.f;
+  for (int s = 0; s < splits; ++s) acc += partial[(long long)s * pstride + i];
+  out[row * ld + n] = acc;
+}
+
+// act[row, j] = silu(sum_s partial[.., 2j]) * sum_s partial[.., 2j+1]
+template <typename T>
+__global__ void splitk_swiglu_kernel(const float* __restrict__ partial, int splits, long long pstride,
+                                     T* __restrict__ act, int N, long long total_pairs) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total_pairs) return;
+  const int half = N / 2;
+  const long long row = i / half;
+  const int j = (int)(i % half);
+  float g = 0.f, u = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float2 p = *reinterpret_cast<const float2*>(partial + (long long)s * pstride + row * N + 2 * j);
+    g += p.x; u += p.y;
+  }
+  act[row * half + j] = from_f<T>(silu_ref(g) * u);
+}
+
+// copy the routed tokens' normalised activations into expert order: dst[pos] = src[sorted_row[pos]]
+template <typename T>
+__global__ void gather_sorted_kernel(const T* __restrict__ src, const int* __restrict__ sorted_row, T* __restrict__ dst,
+                                     int D) {
+  const long long s = sorted_row[blockIdx.x];
+  const uint4* a = reinterpret_cast<const uint4*>(src + s * D);
+  uint4* b = reinterpret_cast<uint4*>(dst + (long long)blockIdx.x * D);
+  const int n16 = D * (int)sizeof(T) / 16;
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) b[i] = a[i];
+}
+
+// combine with split-K partials of the expert outputs: y = sum_s ypart[s]
+__global__ void mod_combine_split_kernel(float* __restrict__ x, const float* __restrict__ ypart, int splits,
+                                         long long pstride, const int* __restrict__ slot_pos,
+                                         const float* __restrict__ slot_w, const float* __restrict__ part_w, int D, int P,
+                                         int top_k) {
+  const int row = blockIdx.x;
+  const int S = P * top_k;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float out = 0.f;
+    for (int p = 0; p < P; ++p) {
+      float comb = 0.f;
+      for (int j = 0; j < top_k; ++j) {
+        const long long s = (long long)row * S + p * top_k + j;
+        const long long at = (long long)slot_pos[s] * D + d;
+        float yv = 0.f;
+        for (int q = 0; q < splits; ++q) yv += ypart[(long long)q * pstride + at];
+        comb += yv * slot_w[s];
+      }
+      out += comb * part_w[(long long)row * P + p];
+    }
+    x[(long long)row * D + d] += out;
+  }
 }
