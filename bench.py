@@ -245,10 +245,10 @@ def run_spec(args):
     target, draft = build_spec_models()
     t_build = time.perf_counter() - t_build
     warm = max(args.warmup, 3)
-    max_seq = T0 + (warm + 3 * args.steps + 16) * (k + 1) + 64
+    max_seq = T0 + (warm + 4 * args.steps + 40) * (k + 1) + 64
     eng = vn.SpecEngine(target, draft, max_batch=B, max_seq=max_seq, k=k, temperature=SPEC["temperature"],
                         top_k=SPEC["top_k"], seed=SPEC["seed"], bonus=True,
-                        max_new_tokens=(warm + 3 * args.steps + 16) * (k + 1))
+                        max_new_tokens=(warm + 4 * args.steps + 40) * (k + 1))
     prompts = spec_prompts(B, T0, SPEC["seed"], rank)
     ctx.sync()
     t_pre = time.perf_counter()
@@ -311,15 +311,25 @@ def run_spec(args):
            "h2d_bytes_per_step": int(h_pair.nbytes),
            "d2h_bytes_per_step": int(h_len.nbytes + h_tok.nbytes + h_pair.nbytes)}
 
-    # ---- per-kernel durations of the verify + sample part of a round (CUDA events around each launch)
+    # ---- verify + sample part of a round: (a) timed as a replayed graph with CUDA events, (b) per-kernel
+    # durations with CUDA events around every launch (eager; each pair of events adds a few microseconds,
+    # so these give the SHARES, the graph timing gives the step time)
+    n_prof = min(args.steps, 16)
+    eng.verify_accept_only(graph=False)
+    eng.verify_accept_only(graph=True)
+    v0, v1 = ctx.event(), ctx.event()
+    v0.record()
+    for _ in range(n_prof):
+        eng.verify_accept_only(graph=True)
+    v1.record()
+    step_ms = v0.elapsed_ms(v1) / n_prof
     ctx.profile(True)
-    n_prof = min(args.steps, 10)
     for _ in range(n_prof):
         eng.verify_accept_only()
     rep = ctx.profile_report()
     ctx.profile(False)
-    step_ms = sum(v["ms"] for v in rep.values()) / n_prof
-    gemm_ms = sum(v["ms"] for n, v in rep.items() if n.startswith("gemm_")) / n_prof
+    prof_ms = sum(v["ms"] for v in rep.values()) / n_prof
+    gemm_ms = sum(v["ms"] for n, v in rep.items() if n.startswith("gemm_")) / n_prof * (step_ms / prof_ms)
     nbytes = spec_step_bytes(B, ctx_len)
     peak, peak_kind = peaks()
     achieved = nbytes / (step_ms * 1e-3) / 1e9
@@ -328,6 +338,7 @@ def run_spec(args):
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_kind": f"of {peak_kind}", "traffic": None, "step_ms": step_ms, "algorithmic_bytes": nbytes,
                 "gemm_ms": gemm_ms, "gemm_weight_gbs": MATE_PARAMS * 2 / (gemm_ms * 1e-3) / 1e9,
+                "kernel_share": {n: v["ms"] / n_prof / prof_ms for n, v in top},
                 "kernel_ms_per_step": {n: v["ms"] / n_prof for n, v in top},
                 "kernel_launches_per_step": {n: v["launches"] / n_prof for n, v in top}}
 

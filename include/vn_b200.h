@@ -213,6 +213,17 @@ int32_t vn_spec_gather(vn_ctx* ctx, const int64_t* step_tokens_dev, const int64_
 int32_t vn_spec_advance(vn_ctx* ctx, const int64_t* out_tokens_dev, int32_t B, int32_t k, int64_t* pair_dev,
                         int64_t* history_dev, int32_t cap, int32_t* count_dev, int32_t* n_commit_dev);
 
+/* Device-side round counter: while set, every Philox offset passed to vn_accept* / vn_sample is
+ * incremented by *counter_dev, and vn_spec_advance adds one to it at the end of a round. */
+int32_t vn_set_offset_source(vn_ctx* ctx, const uint32_t* counter_dev);
+/* CUDA-graph capture of everything issued on the context's stream between begin and end (one decode
+ * round has a fixed launch sequence: lengths, tokens and the round counter all live on the device).
+ * Nothing inside may allocate or synchronise: run the sequence once un-captured first. */
+int32_t vn_graph_begin(vn_ctx* ctx);
+int32_t vn_graph_end(vn_ctx* ctx, void** out_exec);
+int32_t vn_graph_launch(vn_ctx* ctx, void* exec);
+int32_t vn_graph_destroy(vn_ctx* ctx, void* exec);
+
 #ifdef __cplusplus
 }
 #endif

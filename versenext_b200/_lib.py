@@ -79,6 +79,11 @@ PROTOTYPES = {
     "vn_sample": [_p, _p, _i64, _i32, _i32, _f32, _i32, _p, _u64, _u32, _u32, _u32, _p],
     "vn_spec_gather": [_p, _p, _p, _i32, _i32, _i32, _p, _p],
     "vn_spec_advance": [_p, _p, _i32, _i32, _p, _p, _i32, _p, _p],
+    "vn_set_offset_source": [_p, _p],
+    "vn_graph_begin": [_p],
+    "vn_graph_end": [_p, C.POINTER(_p)],
+    "vn_graph_launch": [_p, _p],
+    "vn_graph_destroy": [_p, _p],
     "vn_model_create": [_p, C.c_char_p, C.POINTER(_p)],
     "vn_model_destroy": [_p],
     "vn_model_load_tensor": [_p, C.c_char_p, _p, _i32, C.POINTER(_i64)],

@@ -171,11 +171,13 @@ __device__ __forceinline__ float scaled(float x, float temp) { return temp != 1.
 
 __global__ void accept_decide_kernel(RowSet rs, int B, int k, int nchunks, const Partial* __restrict__ part,
                                      const long long* __restrict__ draft, const float* __restrict__ u_acc,
-                                     const float* __restrict__ u_smp, uint64_t seed, uint32_t offset,
+                                     const float* __restrict__ u_smp, uint64_t seed, uint32_t offset_host,
+                                     const unsigned* __restrict__ offset_dev,
                                      float temp, int greedy, int bonus, int smp_purpose, int pos_base,
                                      Decision* __restrict__ dec, int* __restrict__ out_len,
                                      long long* __restrict__ out_tok) {
   const int b = blockIdx.x;
+  const uint32_t offset = offset_host + (offset_dev ? *offset_dev : 0u);  // device-side round counter, if any
   const int rows_per_seq = rs.np + rs.nq;
   __shared__ float r_m[2 * MAX_K + 1];
   __shared__ int r_a[2 * MAX_K + 1];
@@ -419,11 +421,15 @@ struct TopkRow {
 // the number of keys that can still be kept is known from the histogram; as soon as they fit in
 // shared memory they are gathered (one more read of the row) and the select finishes there.
 __global__ void __launch_bounds__(1024)
-accept_topk_kernel(RowSet rs, int top_k, float temp, TopkRow* __restrict__ out) {
+accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* __restrict__ out) {
+  // blockIdx.x = row * chunks + chunk: every CTA selects inside its own slice of the row; the slices'
+  // lists are merged by accept_topk_merge_kernel (the row's k largest are among the slices' k largest)
   const int rows_per_seq = rs.np + rs.nq;
-  const int r = blockIdx.x;
-  const float* row = row_ptr(rs, r / rows_per_seq, r % rows_per_seq);
-  const int V = rs.V, tid = threadIdx.x, nt = blockDim.x;
+  const int r = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
+  const int slice = (((rs.V + chunks - 1) / chunks) + 3) & ~3;
+  const int base0 = chunk * slice;
+  const float* row = row_ptr(rs, r / rows_per_seq, r % rows_per_seq) + base0;
+  const int V = max(0, min(slice, rs.V - base0)), tid = threadIdx.x, nt = blockDim.x;
   const bool scale = temp != 1.0f;
   const int want = top_k < V ? top_k : V;
   __shared__ uint32_t hist[2048];
@@ -464,7 +470,7 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, TopkRow* __restrict__ out) 
     __syncthreads();
     if (s_done) break;
   }
-  TopkRow* o = out + r;
+  TopkRow* o = out + blockIdx.x;
   if (s_done == 2) {
     const uint32_t lo = s_prefix;
     __syncthreads();
@@ -476,7 +482,7 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, TopkRow* __restrict__ out) 
       const uint32_t key = order_key(x);
       if (key >= lo) {
         int slot = atomicAdd(&s_ncand, 1);
-        if (slot < CAND_MAX) { c_key[slot] = key; c_tok[slot] = i; }
+        if (slot < CAND_MAX) { c_key[slot] = key; c_tok[slot] = base0 + i; }
       }
     }
     __syncthreads();
@@ -519,7 +525,7 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, TopkRow* __restrict__ out) 
       int off = s_base;
       for (int w = 0; w < warp; ++w) off += wcount[w];
       off += __popc(bal & ((1u << lane) - 1));
-      if (keep && off < KEEP_MAX) { o->tok[off] = i; o->val[off] = key_value(key); }
+      if (keep && off < KEEP_MAX) { o->tok[off] = base0 + i; o->val[off] = key_value(key); }
       __syncthreads();
       if (tid == 0) { int tot = 0; for (int w = 0; w < (nt >> 5); ++w) tot += wcount[w]; s_base += tot; }
       __syncthreads();
@@ -528,92 +534,203 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, TopkRow* __restrict__ out) 
   }
 }
 
-__device__ int list_find(const TopkRow& r, int token) {
-  int lo = 0, hi = r.n - 1;
-  while (lo <= hi) {
-    int mid = (lo + hi) >> 1;
-    if (r.tok[mid] == token) return mid;
-    if (r.tok[mid] < token) lo = mid + 1; else hi = mid - 1;
+// Merge the slices' lists of one row: the global k-th largest value is found among the candidates by rank
+// counting, everything >= it is kept; slices are in ascending token order, so the output is too.
+__global__ void __launch_bounds__(256)
+accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_k, TopkRow* __restrict__ out) {
+  constexpr int MERGE_MAX = 4096;
+  __shared__ float s_val[MERGE_MAX];
+  __shared__ int s_tok[MERGE_MAX];
+  __shared__ int s_off[65];
+  __shared__ float s_kth;
+  __shared__ int s_cnt;
+  const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+  const TopkRow* pr = parts + (long long)r * chunks;
+  if (tid == 0) {
+    int acc = 0;
+    for (int c = 0; c < chunks; ++c) { s_off[c] = acc; acc += pr[c].n; }
+    s_off[chunks] = acc < MERGE_MAX ? acc : MERGE_MAX;
+    s_kth = -CUDART_INF_F;
+    s_cnt = 0;
   }
-  return -1;
+  __syncthreads();
+  const int n = s_off[chunks];
+  for (int c = 0; c < chunks; ++c)
+    for (int i = tid; i < pr[c].n; i += nt) {
+      const int at = s_off[c] + i;
+      if (at < MERGE_MAX) { s_val[at] = pr[c].val[i]; s_tok[at] = pr[c].tok[i]; }
+    }
+  __syncthreads();
+  const int want = top_k < n ? top_k : n;
+  for (int i = tid; i < n; i += nt) {
+    const float vi = s_val[i];
+    int greater = 0, geq = 0;
+    for (int j = 0; j < n; ++j) { greater += s_val[j] > vi; geq += s_val[j] >= vi; }
+    if (greater < want && geq >= want) s_kth = vi;   // every writer holds the same value
+  }
+  __syncthreads();
+  const float kth = s_kth;
+  TopkRow* o = out + r;
+  for (int i = tid; i < n; i += nt)
+    if (s_val[i] >= kth) {
+      int pos = 0;
+      for (int j = 0; j < i; ++j) pos += s_val[j] >= kth;
+      if (pos < KEEP_MAX) { o->tok[pos] = s_tok[i]; o->val[pos] = s_val[i]; }
+      atomicAdd(&s_cnt, 1);
+    }
+  __syncthreads();
+  if (tid == 0) { o->n = min(s_cnt, KEEP_MAX); o->overflow = s_cnt > KEEP_MAX; }
 }
 
-// One CTA per sequence, the work is a few hundred operations: thread 0 walks the lists.
-__global__ void accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restrict__ rows,
-                                          const long long* __restrict__ draft, const float* __restrict__ u_acc,
-                                          const float* __restrict__ u_smp, uint64_t seed, uint32_t offset,
-                                          int bonus, int smp_purpose, int pos_base, int* __restrict__ out_len,
-                                          long long* __restrict__ out_tok) {
-  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+// ---- warp-cooperative helpers on a kept list ------------------------------------------------------------
+__device__ __forceinline__ void list_stats(const TopkRow& r, int lane, float& m, double& s) {
+  m = -CUDART_INF_F;
+  for (int i = lane; i < r.n; i += 32) m = fmaxf(m, r.val[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  double acc = 0.0;
+  for (int i = lane; i < r.n; i += 32) acc += (double)expf(r.val[i] - m);
+  s = warp_sum(acc);
+}
+
+// value of `token` in the list, or -inf when it is not kept (all lanes get the result)
+__device__ __forceinline__ float list_value(const TopkRow& r, int lane, int token) {
+  float v = -CUDART_INF_F;
+  for (int i = lane; i < r.n; i += 32)
+    if (r.tok[i] == token) v = r.val[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// One warp per sequence: acceptance tests, then the inverse CDF over the kept list of the row to sample.
+__global__ void __launch_bounds__(128)
+accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restrict__ rows,
+                          const long long* __restrict__ draft, const float* __restrict__ u_acc,
+                          const float* __restrict__ u_smp, uint64_t seed, uint32_t offset_host,
+                          const unsigned* __restrict__ offset_dev, int bonus, int smp_purpose, int pos_base,
+                          int* __restrict__ out_len, long long* __restrict__ out_tok) {
+  const int lane = threadIdx.x & 31;
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (b >= B) return;
+  const uint32_t offset = offset_host + (offset_dev ? *offset_dev : 0u);
   const int rows_per_seq = np + nq;
   const TopkRow* rb = rows + (long long)b * rows_per_seq;
   long long* tok = out_tok + (long long)b * (k + 1);
-  for (int i = 0; i <= k; ++i) tok[i] = -1;
-  auto stats = [](const TopkRow& r, float& m, double& s) {
-    m = -CUDART_INF_F;
-    for (int i = 0; i < r.n; ++i) m = fmaxf(m, r.val[i]);
-    s = 0.0;
-    for (int i = 0; i < r.n; ++i) s += (double)expf(r.val[i] - m);
-  };
+  for (int i = lane; i <= k; i += 32) tok[i] = -1;
+  __syncwarp();
   int n = 0;
   int sample_row = -1, q_row = -1, removed = -1;
   for (; n < k; ++n) {
     const int x = (int)draft[(long long)b * k + n];
-    const TopkRow& P = rb[n];
-    float mp; double sp; stats(P, mp, sp);
-    int ip = list_find(P, x);
-    double p = ip >= 0 ? (double)expf(P.val[ip] - mp) / sp : 0.0;
+    float mp; double sp;
+    list_stats(rb[n], lane, mp, sp);
+    const float vp = list_value(rb[n], lane, x);
+    const double p = vp == -CUDART_INF_F ? 0.0 : (double)expf(vp - mp) / sp;
     double q = 1.0;
     if (nq) {
-      const TopkRow& Q = rb[np + n];
-      float mq; double sq; stats(Q, mq, sq);
-      int iq = list_find(Q, x);
-      q = iq >= 0 ? (double)expf(Q.val[iq] - mq) / sq : 0.0;
+      float mq; double sq;
+      list_stats(rb[np + n], lane, mq, sq);
+      const float vq = list_value(rb[np + n], lane, x);
+      q = vq == -CUDART_INF_F ? 0.0 : (double)expf(vq - mq) / sq;
     }
     const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, pos_base + n, 0);
-    if ((double)u * q < p) { tok[n] = x; continue; }
+    if ((double)u * q < p) { if (lane == 0) tok[n] = x; continue; }
     sample_row = n;
     if (nq) q_row = np + n; else removed = x;
     break;
   }
-  if (out_len) out_len[b] = n;
+  if (lane == 0 && out_len) out_len[b] = n;
   if (sample_row < 0) {
     if (!bonus) return;
     sample_row = k;
   }
   const TopkRow& P = rb[sample_row];
-  float mp; double sp; stats(P, mp, sp);
+  float mp; double sp;
+  list_stats(P, lane, mp, sp);
   float mq = 0.f; double sq = 1.0;
-  if (q_row >= 0) stats(rb[q_row], mq, sq);
+  if (q_row >= 0) list_stats(rb[q_row], lane, mq, sq);
   const float u = u_smp ? u_smp[(long long)b * (k + 1) + sample_row]
                         : philox_uniform(seed, offset, b, pos_base + sample_row, smp_purpose);
   for (int pass = 0; pass < 2; ++pass) {
-    // pass 0: residual; pass 1 (only when it vanished): p itself
-    double Z = 0.0;
-    auto weight = [&](int i) {
-      double p = (double)expf(P.val[i] - mp) / sp;
+    // pass 0: residual max(0, p - q) (or p without the rejected token); pass 1, only when that vanished: p itself
+    auto weight = [&](int i) -> double {
+      const double p = (double)expf(P.val[i] - mp) / sp;
       if (pass == 1) return p;
       if (q_row >= 0) {
-        int iq = list_find(rb[q_row], P.tok[i]);
-        double q = iq >= 0 ? (double)expf(rb[q_row].val[iq] - mq) / sq : 0.0;
-        double r = p - q;
-        return r > 0.0 ? r : 0.0;
+        // q's value for this token: all lanes of the warp look it up together
+        return p;  // placeholder, replaced below (needs a warp-wide lookup)
       }
       return P.tok[i] == removed ? 0.0 : p;
     };
-    for (int i = 0; i < P.n; ++i) Z += weight(i);
+    // weights of the entries this lane owns, in chunks of 32 consecutive entries (ascending token id)
+    double Z = 0.0;
+    const int nchunk = (P.n + 31) >> 5;
+    // first sweep: total mass
+    for (int c = 0; c < nchunk; ++c) {
+      const int i = c * 32 + lane;
+      double w = 0.0;
+      const int tk = i < P.n ? P.tok[i] : -1;
+      if (pass == 0 && q_row >= 0) {
+        // every lane needs q(tk) for its own token: loop over the 32 tokens of the chunk
+        double mine = 0.0;
+        for (int src = 0; src < 32; ++src) {
+          const int t2 = __shfl_sync(0xffffffffu, tk, src);
+          if (t2 < 0) continue;
+          const float vq = list_value(rb[q_row], lane, t2);
+          if (src == lane) {
+            const double pp = (double)expf(P.val[i] - mp) / sp;
+            const double qq = vq == -CUDART_INF_F ? 0.0 : (double)expf(vq - mq) / sq;
+            mine = pp - qq > 0.0 ? pp - qq : 0.0;
+          }
+        }
+        w = mine;
+      } else if (i < P.n) {
+        w = weight(i);
+      }
+      Z += w;
+    }
+    Z = warp_sum(Z);
     if (!(Z > 0.0)) continue;
     const double target = (double)u * Z;
-    double cum = 0.0; int pick = -1, last_nz = -1;
-    for (int i = 0; i < P.n; ++i) {
-      double w = weight(i);
-      if (w > 0.0) last_nz = i;
-      cum += w;
-      if (cum > target) { pick = i; break; }
+    double run = 0.0;
+    int pick = -1, last_nz = -1;
+    for (int c = 0; c < nchunk && pick < 0; ++c) {
+      const int i = c * 32 + lane;
+      double w = 0.0;
+      const int tk = i < P.n ? P.tok[i] : -1;
+      if (pass == 0 && q_row >= 0) {
+        double mine = 0.0;
+        for (int src = 0; src < 32; ++src) {
+          const int t2 = __shfl_sync(0xffffffffu, tk, src);
+          if (t2 < 0) continue;
+          const float vq = list_value(rb[q_row], lane, t2);
+          if (src == lane) {
+            const double pp = (double)expf(P.val[i] - mp) / sp;
+            const double qq = vq == -CUDART_INF_F ? 0.0 : (double)expf(vq - mq) / sq;
+            mine = pp - qq > 0.0 ? pp - qq : 0.0;
+          }
+        }
+        w = mine;
+      } else if (i < P.n) {
+        w = weight(i);
+      }
+      // inclusive scan of the chunk in entry order
+      double cum = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, cum, o);
+        if (lane >= o) cum += up;
+      }
+      cum += run;
+      const unsigned hit = __ballot_sync(0xffffffffu, i < P.n && cum > target);
+      const unsigned nz = __ballot_sync(0xffffffffu, i < P.n && w > 0.0);
+      if (nz) last_nz = c * 32 + (31 - __clz(nz));
+      if (hit) pick = c * 32 + (__ffs(hit) - 1);
+      run = __shfl_sync(0xffffffffu, cum, 31);
     }
     if (pick < 0) pick = last_nz;
-    tok[n] = P.tok[pick];
+    if (lane == 0 && pick >= 0) tok[n] = P.tok[pick];
     return;
   }
 }
@@ -646,13 +763,19 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
 
   if (!greedy && top_k > 0 && top_k < V) {
     VN_REQUIRE(ctx, top_k <= KEEP_MAX, "top_k %d above the supported maximum %d", top_k, KEEP_MAX);
+    // slices per row: enough CTAs to fill the GPU, at least 8192 logits each
+    const int n_rows = B * rows_per_seq;
+    int chunks = std::min(std::min(16, std::max(1, V / 8192)), std::max(1, ceil_div(2 * ctx->sm_count, n_rows)));
+    chunks = std::max(1, std::min(chunks, 2048 / std::max(top_k, 1)));
     void* ws;
-    int32_t st = vn_workspace(ctx, sizeof(TopkRow) * (size_t)B * rows_per_seq, &ws);
+    int32_t st = vn_workspace(ctx, sizeof(TopkRow) * (size_t)n_rows * (chunks + 1), &ws);
     if (st) return st;
-    TopkRow* rows = (TopkRow*)ws;
-    VN_LAUNCH(ctx, accept_topk_kernel, B * rows_per_seq, 1024, 0, rs, top_k, temp, rows);
-    VN_LAUNCH(ctx, accept_topk_decide_kernel, ceil_div(B, 32), 32, 0, B, k, rs.np, rs.nq, rows, d64, u_acc, u_smp,
-              seed, offset, bonus, smp_purpose, pos_base, out_len, o64);
+    TopkRow* rows = (TopkRow*)ws;                 // merged lists [n_rows]
+    TopkRow* parts = rows + n_rows;               // per-slice lists [n_rows * chunks]
+    VN_LAUNCH(ctx, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, chunks > 1 ? parts : rows);
+    if (chunks > 1) VN_LAUNCH(ctx, accept_topk_merge_kernel, n_rows, 256, 0, parts, chunks, top_k, rows);
+    VN_LAUNCH(ctx, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, B, k, rs.np, rs.nq, rows, d64, u_acc, u_smp,
+              seed, offset, ctx->offset_src, bonus, smp_purpose, pos_base, out_len, o64);
     return VN_OK;
   }
 
@@ -675,8 +798,8 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
   const int grid = (int)std::min<long long>(nitems, (long long)ctx->sm_count * 8);
   if (vec) VN_LAUNCH(ctx, accept_stats_kernel<true>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
   else     VN_LAUNCH(ctx, accept_stats_kernel<false>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
-  VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_acc, u_smp, seed, offset, temp,
-            (int)greedy, bonus, smp_purpose, pos_base, dec, out_len, o64);
+  VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_acc, u_smp, seed, offset,
+            ctx->offset_src, temp, (int)greedy, bonus, smp_purpose, pos_base, dec, out_len, o64);
   if (!greedy) {
     dim3 g(nchunks, B);
     if (vec) VN_LAUNCH(ctx, accept_residual_kernel<true>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);
@@ -794,7 +917,7 @@ int32_t vn_accept_noalloc(vn_ctx* ctx, const float* p_logits_dev, const float* q
   if (vec) VN_LAUNCH(ctx, accept_stats_kernel<true>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
   else     VN_LAUNCH(ctx, accept_stats_kernel<false>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
   VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_accept_dev, u_sample_dev, seed, offset,
-            temp, (int)greedy, bonus, 1, 0, dec, out_len_dev, o64);
+            (const unsigned*)nullptr, temp, (int)greedy, bonus, 1, 0, dec, out_len_dev, o64);
   if (!greedy) {
     dim3 g(nchunks, B);
     if (vec) VN_LAUNCH(ctx, accept_residual_kernel<true>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);

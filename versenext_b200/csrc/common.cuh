@@ -24,6 +24,9 @@ struct vn_ctx {
   void* flush = nullptr;
   size_t flush_bytes = 0;
   int sm_count = 148;
+  // when set, every Philox offset of the acceptance / sampling kernels is incremented by *offset_src
+  // (a round counter that lives on the device, so that a captured graph draws fresh numbers on every replay)
+  const unsigned* offset_src = nullptr;
   // optional per-kernel timing: CUDA events around every launch, summed per kernel name
   bool profiling = false;
   struct ProfRec { const char* name; cudaEvent_t a, b; };

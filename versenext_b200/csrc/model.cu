@@ -319,7 +319,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
       RouteArgs r;
       r.h = m->h32; r.gates = L.router; r.slot_expert = m->slot_expert; r.slot_w = m->slot_w; r.part_w = m->part_w;
       r.expert_count = m->expert_count; r.M = M; r.D = D; r.P = c.P; r.E = c.E; r.top_k = c.top_k;
-      VN_LAUNCH(ctx, mod_route_kernel, ceil_div(M, 4), 128, 0, r);
+      VN_LAUNCH(ctx, mod_route_kernel, M, 128, 0, r);
       VN_LAUNCH(ctx, mod_offsets_kernel, 1, 32, 0, m->expert_count, m->expert_off, m->expert_cur, ne);
       VN_LAUNCH(ctx, mod_scatter_kernel, ceil_div(M * S, 256), 256, 0, m->slot_expert, m->expert_off, m->expert_cur,
                 m->sorted_row, m->slot_pos, M * S, S);
@@ -373,8 +373,11 @@ int32_t ensure_partial(vn_model* m, size_t bytes) {
 int tc_splits(const vn_ctx* ctx, int N, int K, int nseg) {
   const int tiles = ceil_div(N, tc_detail::BF) * nseg;
   const int nkb = ceil_div(K, tc_detail::BK);
-  int s = ceil_div(2 * ctx->sm_count, tiles);
-  s = std::max(1, std::min(s, nkb));
+  // every slice costs a partial tile written and read back (rows x 128 x 4 bytes), so split only until the
+  // GPU is covered about once, and never below VN_TC_MIN_KB k blocks per CTA
+  static const int min_kb = [] { const char* e = getenv("VN_TC_MIN_KB"); return e ? std::max(1, atoi(e)) : 4; }();
+  int s = ceil_div(ctx->sm_count, tiles);
+  s = std::max(1, std::min(s, std::max(1, nkb / min_kb)));
   const int per = ceil_div(nkb, s);
   return ceil_div(nkb, per);   // effective number of K ranges
 }
@@ -416,14 +419,9 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     // ---- attention block
     g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.M = M; g.N = qkv_ld; g.K = D; g.tag = "gemm_qkv";
     TRY(tc_partial(m, g, cap, M, &sp));
-    {
-      const long long total = (long long)M * qkv_ld;
-      VN_LAUNCH(ctx, splitk_store_kernel, (unsigned)ceil_div(total, 256ll), 256, 0, m->partial, sp, total, m->qkv,
-                (long long)qkv_ld, qkv_ld, total);
-    }
-    VN_LAUNCH(ctx, rope_append_kernel<T>, M, 128, 0, m->qkv, m->rope_cos, m->rope_sin, kv->lens,
-              tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq,
-              c.use_rope, m->rope_rows, slot_offset);
+    VN_LAUNCH(ctx, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld, m->qkv,
+              m->rope_cos, m->rope_sin, kv->lens, tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[li],
+              (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
     AttnArgs a;
     a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[li]; a.vc = kv->v[li]; a.sink_k = L.sink_k; a.sink_v = L.sink_v;
     a.out = m->attn; a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
@@ -468,7 +466,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       RouteArgs r;
       r.h = m->h32; r.gates = L.router; r.slot_expert = m->slot_expert; r.slot_w = m->slot_w; r.part_w = m->part_w;
       r.expert_count = m->expert_count; r.M = M; r.D = D; r.P = c.P; r.E = c.E; r.top_k = c.top_k;
-      VN_LAUNCH(ctx, mod_route_kernel, ceil_div(M, 4), 128, 0, r);
+      VN_LAUNCH(ctx, mod_route_kernel, M, 128, 0, r);
       VN_LAUNCH(ctx, mod_offsets_kernel, 1, 32, 0, m->expert_count, m->expert_off, m->expert_cur, ne);
       VN_LAUNCH(ctx, mod_scatter_kernel, ceil_div(M * S, 256), 256, 0, m->slot_expert, m->expert_off, m->expert_cur,
                 m->sorted_row, m->slot_pos, M * S, S);

@@ -318,34 +318,46 @@ struct RouteArgs {
 };
 
 __global__ void __launch_bounds__(128) mod_route_kernel(RouteArgs r) {
-  __shared__ float s_lg[4][64];
+  // one CTA per token: the 4 warps split the gate rows, warp 0 then selects
+  __shared__ float lg[64];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 4 + warp;
-  if (row >= r.M) return;
+  const int row = blockIdx.x;
   const int n_logit = r.P + r.P * r.E;       // <= 64
   const float* x = r.h + (long long)row * r.D;
-  for (int g = 0; g < n_logit; ++g) {
-    const float* w = r.gates + (long long)g * r.D;
-    float s = 0.f;
-    for (int d = lane; d < r.D; d += 32) s = fmaf(x[d], w[d], s);
+  const int n4 = r.D >> 7;                   // float4 chunks per lane (D multiple of 128), <= 16
+  float4 xr[16];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) s_lg[warp][g] = s;
+  for (int i = 0; i < 16; ++i)
+    xr[i] = i < n4 ? *reinterpret_cast<const float4*>(x + i * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int g = warp; g < n_logit; g += 4) {
+    const float* w = r.gates + (long long)g * r.D;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < n4) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + i * 128 + lane * 4);
+        s0 = fmaf(xr[i].x, wv.x, s0); s1 = fmaf(xr[i].y, wv.y, s1);
+        s2 = fmaf(xr[i].z, wv.z, s2); s3 = fmaf(xr[i].w, wv.w, s3);
+      }
+    float sum = (s0 + s1) + (s2 + s3);
+    for (int d = (n4 << 7) + lane; d < r.D; d += 32) sum = fmaf(x[d], w[d], sum);   // tail when D % 128 != 0
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) lg[g] = sum;
   }
-  __syncwarp();
-  const float* lg = s_lg[warp];
-  if (lane == 31 || r.P > 31) {
-    // part weights: softmax over all parts (one lane; P is tiny)
-    if (lane == 31 || lane == 0) {
-      float m = -CUDART_INF_F;
-      for (int p = 0; p < r.P; ++p) m = fmaxf(m, lg[p]);
-      float den = 0.f;
-      for (int p = 0; p < r.P; ++p) den += expf(lg[p] - m);
-      for (int p = 0; p < r.P; ++p) r.part_w[(long long)row * r.P + p] = expf(lg[p] - m) / den;
-    }
+  __syncthreads();
+  if (warp != 0) return;
+  if (lane == 31) {
+    // part weights: softmax over all parts
+    float m = -CUDART_INF_F;
+    for (int p = 0; p < r.P; ++p) m = fmaxf(m, lg[p]);
+    float den = 0.f;
+    for (int p = 0; p < r.P; ++p) den += expf(lg[p] - m);
+    for (int p = 0; p < r.P; ++p) r.part_w[(long long)row * r.P + p] = expf(lg[p] - m) / den;
   }
   // one lane per part: top-k of its expert logits (lowest index wins ties), softmax over the kept logits
-  for (int p = lane; p < r.P; p += 32) {
+  for (int p = lane; p < r.P; p += 31) {
+    if (lane == 31) break;
     const float* el = lg + r.P + p * r.E;
     int sel[8]; float sl[8];
     unsigned long long used = 0ull;
@@ -467,18 +479,24 @@ __global__ void __launch_bounds__(256) splitk_add_norm_kernel(const float* __res
                                                               float* __restrict__ y32, int D, float eps) {
   __shared__ float sm[8];
   const long long row = blockIdx.x;
-  float v[8];
+  float4 v[2];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int d = threadIdx.x + i * 256;
-    v[i] = 0.f;
+  for (int i = 0; i < 2; ++i) {
+    const int d = (threadIdx.x + i * 256) * 4;
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (d < D) {
-      float acc = 0.f;
-      for (int s = 0; s < splits; ++s) acc += partial[(long long)s * pstride + row * D + d];
-      v[i] = x[row * D + d] + acc;
-      x[row * D + d] = v[i];
-      ss += v[i] * v[i];
+      const float* p = partial + row * D + d;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+      for (int s = 0; s < splits; ++s) {   // independent loads, summed in split order
+        const float4 t = *reinterpret_cast<const float4*>(p + (long long)s * pstride);
+        acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+      }
+      const float4 xv = *reinterpret_cast<const float4*>(x + row * D + d);
+      v[i] = make_float4(xv.x + acc.x, xv.y + acc.y, xv.z + acc.z, xv.w + acc.w);
+      *reinterpret_cast<float4*>(x + row * D + d) = v[i];
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
     }
   }
   if (!norm_w) return;
@@ -491,12 +509,13 @@ __global__ void __launch_bounds__(256) splitk_add_norm_kernel(const float* __res
   for (int i = 0; i < 8; ++i) tot += sm[i];
   const float r = sqrtf(tot / (float)D + eps);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int d = threadIdx.x + i * 256;
+  for (int i = 0; i < 2; ++i) {
+    const int d = (threadIdx.x + i * 256) * 4;
     if (d < D) {
-      const float o = v[i] / r * norm_w[d];
-      if (y) y[row * D + d] = from_f<T>(o);
-      if (y32) y32[row * D + d] = o;
+      const float4 w = *reinterpret_cast<const float4*>(norm_w + d);
+      const float o0 = v[i].x / r * w.x, o1 = v[i].y / r * w.y, o2 = v[i].z / r * w.z, o3 = v[i].w / r * w.w;
+      if (y) { y[row * D + d] = from_f<T>(o0); y[row * D + d + 1] = from_f<T>(o1); y[row * D + d + 2] = from_f<T>(o2); y[row * D + d + 3] = from_f<T>(o3); }
+      if (y32) *reinterpret_cast<float4*>(y32 + row * D + d) = make_float4(o0, o1, o2, o3);
     }
   }
 }
@@ -542,25 +561,102 @@ __global__ void gather_sorted_kernel(const T* __restrict__ src, const int* __res
 }
 
 // combine with split-K partials of the expert outputs: y = sum_s ypart[s]
-__global__ void mod_combine_split_kernel(float* __restrict__ x, const float* __restrict__ ypart, int splits,
-                                         long long pstride, const int* __restrict__ slot_pos,
-                                         const float* __restrict__ slot_w, const float* __restrict__ part_w, int D, int P,
-                                         int top_k) {
+__global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restrict__ x, const float* __restrict__ ypart,
+                                                                int splits, long long pstride,
+                                                                const int* __restrict__ slot_pos,
+                                                                const float* __restrict__ slot_w,
+                                                                const float* __restrict__ part_w, int D, int P,
+                                                                int top_k) {
+  __shared__ long long s_at[64];
+  __shared__ float s_w[64];
   const int row = blockIdx.x;
-  const int S = P * top_k;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float out = 0.f;
+  const int S = P * top_k;   // <= 64
+  if (threadIdx.x < S) {
+    const long long s = (long long)row * S + threadIdx.x;
+    s_at[threadIdx.x] = (long long)slot_pos[s] * D;
+    s_w[threadIdx.x] = slot_w[s];
+  }
+  __syncthreads();
+  for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+    float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < P; ++p) {
-      float comb = 0.f;
+      float4 comb = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int j = 0; j < top_k; ++j) {
-        const long long s = (long long)row * S + p * top_k + j;
-        const long long at = (long long)slot_pos[s] * D + d;
-        float yv = 0.f;
-        for (int q = 0; q < splits; ++q) yv += ypart[(long long)q * pstride + at];
-        comb += yv * slot_w[s];
+        const int sl = p * top_k + j;
+        float4 yv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int q = 0; q < splits; ++q) {
+          const float4 t = *reinterpret_cast<const float4*>(ypart + (long long)q * pstride + s_at[sl] + d);
+          yv.x += t.x; yv.y += t.y; yv.z += t.z; yv.w += t.w;
+        }
+        const float w = s_w[sl];
+        comb.x += yv.x * w; comb.y += yv.y * w; comb.z += yv.z * w; comb.w += yv.w * w;
       }
-      out += comb * part_w[(long long)row * P + p];
+      const float pw = part_w[(long long)row * P + p];
+      out.x += comb.x * pw; out.y += comb.y * pw; out.z += comb.z * pw; out.w += comb.w * pw;
     }
-    x[(long long)row * D + d] += out;
+    float4* xp = reinterpret_cast<float4*>(x + (long long)row * D + d);
+    float4 xv = *xp;
+    xv.x += out.x; xv.y += out.y; xv.z += out.z; xv.w += out.w;
+    *xp = xv;
+  }
+}
+
+// ---- split-K finalize of the q|k|v projection fused with RoPE and the cache append ------------------------
+// One CTA per new position: sums the partial slices of its row into shared memory, then does what
+// rope_append_kernel does (q rotated and written to the fp32 q buffer, k rotated and v copied into the cache).
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_finalize_kernel(const float* __restrict__ partial, int splits,
+                                                           long long pstride, float* __restrict__ qkv,
+                                                           const float* __restrict__ cos_t,
+                                                           const float* __restrict__ sin_t,
+                                                           const int* __restrict__ lens, const int* __restrict__ depth,
+                                                           T* __restrict__ kc, T* __restrict__ vc, int Tn, int H,
+                                                           int n_kv, int hd, int max_seq, int use_rope, int rope_rows,
+                                                           int slot_offset) {
+  extern __shared__ float s_row[];   // (H + 2 n_kv) * hd floats
+  const int row = blockIdx.x, b = row / Tn, t = row % Tn;
+  const int ld = (H + 2 * n_kv) * hd;
+  for (int i = threadIdx.x * 4; i < ld; i += blockDim.x * 4) {
+    const float* p = partial + (long long)row * ld + i;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(p + (long long)s * pstride);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(s_row + i) = acc;
+  }
+  __syncthreads();
+  const int len = lens[b] + slot_offset;
+  const int pos = len + (depth ? depth[t] : t);
+  const int slot = len + t;
+  const int half = hd / 2;
+  float* r = qkv + (long long)row * ld;
+  const int p = pos < rope_rows ? pos : rope_rows - 1;
+  const int n_rot = (H + n_kv) * half;
+  for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
+    const int head = i / half, j = i % half;
+    const float x1 = s_row[head * hd + j], x2 = s_row[head * hd + half + j];
+    float o1 = x1, o2 = x2;
+    if (use_rope) {
+      const float c = cos_t[(long long)p * half + j], s = sin_t[(long long)p * half + j];
+      o1 = x1 * c + (-x2) * s;
+      o2 = x2 * c + x1 * s;
+    }
+    if (head < H) {
+      r[head * hd + j] = o1;
+      r[head * hd + half + j] = o2;
+    } else if (slot < max_seq) {
+      const int kh = head - H;
+      T* dst = kc + (((long long)b * max_seq + slot) * n_kv + kh) * hd;
+      dst[j] = from_f<T>(o1);
+      dst[half + j] = from_f<T>(o2);
+    }
+  }
+  if (slot < max_seq) {
+    const float* v = s_row + (H + n_kv) * hd;
+    T* dst = vc + ((long long)b * max_seq + slot) * n_kv * hd;
+    for (int i = threadIdx.x; i < n_kv * hd; i += blockDim.x) dst[i] = from_f<T>(v[i]);
   }
 }

@@ -5,9 +5,11 @@ The reference composes this loop on the host from `VerseNexLM.forward` and
 re-running the whole context every round and serving batch row 0 only.
 Here both models keep KV caches on the device, every request of the batch
 advances each round, and a round issues no host synchronisation: proposals,
-acceptance results, the last committed tokens and the cache lengths all stay
-in device memory (`vn_spec_gather`, `vn_accept`, `vn_spec_advance`,
-`vn_kv_commit`).
+acceptance results, the last committed tokens, the cache lengths and the
+round counter that offsets the Philox streams all stay in device memory
+(`vn_spec_gather`, `vn_accept`, `vn_spec_advance`, `vn_kv_commit`).  Because
+the launch sequence of a round is then fixed, it is captured once into a CUDA
+graph and replayed (`graph=True`).
 
 Cache protocol.  With s the committed tokens of a request, at the start of a
 round the target cache holds s[:-1] and the draft cache s[:-2].  The draft
@@ -24,7 +26,6 @@ from typing import Optional
 
 import numpy as np
 
-from .device import DeviceArray
 from .model import VerseNexLM, _ptr
 
 PURPOSE_DRAFT = 2  # Philox purpose of the draft model's own sampling (0 / 1: accept test / resample)
@@ -33,7 +34,7 @@ PURPOSE_DRAFT = 2  # Philox purpose of the draft model's own sampling (0 / 1: ac
 class SpecEngine:
     def __init__(self, target: VerseNexLM, draft: VerseNexLM, max_batch: int, max_seq: int, k: int = 4,
                  temperature: float = 0.0, top_k: int = 0, seed: int = 0, bonus: bool = True,
-                 max_new_tokens: int = 4096):
+                 max_new_tokens: int = 4096, graph: bool = True):
         if target.vocab_size != draft.vocab_size:
             raise ValueError("target and draft must share the vocabulary")
         if target.ctx is not draft.ctx:
@@ -44,6 +45,7 @@ class SpecEngine:
         self.B, self.k, self.V = int(max_batch), int(k), target.vocab_size
         self.temperature, self.top_k, self.seed, self.bonus = float(temperature), int(top_k or 0), int(seed), bool(bonus)
         self.n_verify = self.k + 1 if self.bonus else self.k
+        self.max_seq = int(max_seq)
         self.t_cache = target.new_cache(self.B, max_seq)
         self.d_cache = draft.new_cache(self.B, max_seq)
         ctx, B, k, V = self.ctx, self.B, self.k, self.V
@@ -59,8 +61,13 @@ class SpecEngine:
         self.history = ctx.zeros((B, self.cap), np.int64)
         self.count = ctx.zeros((B,), np.int32)
         self.n_commit = ctx.zeros((B,), np.int32)
-        self.round = 0
+        self.round_dev = ctx.zeros((1,), np.uint32)               # rounds completed; offsets the Philox streams
         self.rounds_run = 0
+        self.use_graph = bool(graph)
+        self._graph = None
+        self._graph_verify = None
+        self._eager_rounds = 0
+        self._len_bound = 0        # host upper bound of the longest target-cache length
 
     # -- prefill -------------------------------------------------------------------
     def prefill(self, prompts):
@@ -73,7 +80,6 @@ class SpecEngine:
             raise ValueError("prompts need at least two tokens")
         self.t_cache.reset()
         self.d_cache.reset()
-        tok = self.ctx.from_numpy(prompts)
         # chunk the prompt so that activation buffers stay bounded for long prompts
         chunk = max(1, 8192 // B)
         for cache, model, upto in ((self.t_cache, self.target, T - 1), (self.d_cache, self.draft, T - 2)):
@@ -85,58 +91,94 @@ class SpecEngine:
                 cache.commit(n, np.full(B, n, np.int32))
                 done += n
         self.pair.copy_from_host(prompts[:, -2:])
-        self.ctx._check(self.ctx.lib.vn_memset(self.ctx.handle, _ptr(self.count), 0, self.count.nbytes))
-        self.round = 0
+        for buf in (self.count, self.round_dev):
+            self.ctx._check(self.ctx.lib.vn_memset(self.ctx.handle, _ptr(buf), 0, buf.nbytes))
         self.rounds_run = 0
-        del tok
+        self._len_bound = T - 1
 
     # -- one round -----------------------------------------------------------------
-    def step(self):
+    def _issue_round(self, draft_part: bool = True):
+        """Enqueue the kernels of one round on the context's stream (no synchronisation, no allocation)."""
         ctx, lib, B, k, V = self.ctx, self.ctx.lib, self.B, self.k, self.V
         greedy = self.temperature <= 0
-        # draft: k proposals; the first forward consumes the last two committed tokens
-        for i in range(k):
-            q_i = self.q_logits[i]
-            if i == 0:
-                self.draft.forward_cached(self.pair, self.d_cache, last_only=True, out_logits=q_i, slot_offset=0)
-            else:
-                self.draft.forward_cached(self.step_tokens[i - 1].reshape(B, 1), self.d_cache, last_only=True,
-                                          out_logits=q_i, slot_offset=i + 1)
-            ctx._check(lib.vn_sample(ctx.handle, _ptr(q_i), V, B, V, self.temperature, self.top_k, None,
-                                     self.seed, self.round, i, PURPOSE_DRAFT, _ptr(self.step_tokens[i])))
-        ctx._check(lib.vn_spec_gather(ctx.handle, _ptr(self.step_tokens), _ptr(self.pair), B, k, self.n_verify,
-                                      _ptr(self.draft_tokens), _ptr(self.verify_tokens)))
-        # target: one forward over (last committed, d_0 .. d_{n_verify-2})
-        self.target.forward_cached(self.verify_tokens, self.t_cache, out_logits=self.p_logits)
-        # acceptance
-        ctx._check(lib.vn_accept_strided(
-            ctx.handle, _ptr(self.p_logits), self.n_verify * V, V,
-            None if greedy else _ptr(self.q_logits), V, B * V,
-            _ptr(self.draft_tokens), None, None, self.seed, self.round, self.temperature, self.top_k,
-            int(self.bonus), B, k, V, _ptr(self.accept_len), _ptr(self.out_tokens)))
-        ctx._check(lib.vn_spec_advance(ctx.handle, _ptr(self.out_tokens), B, k, _ptr(self.pair), _ptr(self.history),
-                                       self.cap, _ptr(self.count), _ptr(self.n_commit)))
-        # both caches keep the first n_commit entries appended this round
-        ctx._check(lib.vn_kv_commit(self.t_cache.handle, self.n_verify, None, 0, _ptr(self.n_commit), 0))
-        ctx._check(lib.vn_kv_commit(self.d_cache.handle, k + 1, None, 0, _ptr(self.n_commit), 0))
-        self.round += 1
+        ctx._check(lib.vn_set_offset_source(ctx.handle, _ptr(self.round_dev)))
+        try:
+            if draft_part:
+                # draft: k proposals; the first forward consumes the last two committed tokens
+                for i in range(k):
+                    q_i = self.q_logits[i]
+                    if i == 0:
+                        self.draft.forward_cached(self.pair, self.d_cache, last_only=True, out_logits=q_i,
+                                                  slot_offset=0)
+                    else:
+                        self.draft.forward_cached(self.step_tokens[i - 1].reshape(B, 1), self.d_cache,
+                                                  last_only=True, out_logits=q_i, slot_offset=i + 1)
+                    ctx._check(lib.vn_sample(ctx.handle, _ptr(q_i), V, B, V, self.temperature, self.top_k, None,
+                                             self.seed, 0, i, PURPOSE_DRAFT, _ptr(self.step_tokens[i])))
+                ctx._check(lib.vn_spec_gather(ctx.handle, _ptr(self.step_tokens), _ptr(self.pair), B, k,
+                                              self.n_verify, _ptr(self.draft_tokens), _ptr(self.verify_tokens)))
+            # target: one forward over (last committed, d_0 .. d_{n_verify-2})
+            self.target.forward_cached(self.verify_tokens, self.t_cache, out_logits=self.p_logits)
+            ctx._check(lib.vn_accept_strided(
+                ctx.handle, _ptr(self.p_logits), self.n_verify * V, V,
+                None if greedy else _ptr(self.q_logits), V, B * V,
+                _ptr(self.draft_tokens), None, None, self.seed, 0, self.temperature, self.top_k,
+                int(self.bonus), B, k, V, _ptr(self.accept_len), _ptr(self.out_tokens)))
+            ctx._check(lib.vn_spec_advance(ctx.handle, _ptr(self.out_tokens), B, k, _ptr(self.pair),
+                                           _ptr(self.history), self.cap, _ptr(self.count), _ptr(self.n_commit)))
+            # both caches keep the first n_commit entries appended this round
+            ctx._check(lib.vn_kv_commit(self.t_cache.handle, self.n_verify, None, 0, _ptr(self.n_commit), 0))
+            if draft_part:
+                ctx._check(lib.vn_kv_commit(self.d_cache.handle, k + 1, None, 0, _ptr(self.n_commit), 0))
+        finally:
+            ctx._check(lib.vn_set_offset_source(ctx.handle, None))
+
+    def _check_capacity(self):
+        # the device kernels trust the cache capacity; every round appends at most n_verify entries
+        if self._len_bound + self.n_verify + 1 > self.max_seq:
+            lens = self.t_cache.per_seq_lens
+            self._len_bound = int(lens.max())
+            if self._len_bound + self.n_verify + 1 > self.max_seq:
+                raise RuntimeError(f"KV cache overflow: a sequence holds {self._len_bound} of {self.max_seq} positions")
+
+    def step(self):
+        """One speculative round for the whole batch."""
+        self._check_capacity()
+        ctx, lib = self.ctx, self.ctx.lib
+        if self.use_graph and self._eager_rounds >= 1:
+            if self._graph is None:
+                ctx._check(lib.vn_graph_begin(ctx.handle))
+                try:
+                    self._issue_round()
+                finally:
+                    g = C.c_void_p()
+                    ctx._check(lib.vn_graph_end(ctx.handle, C.byref(g)))
+                self._graph = g
+            ctx._check(lib.vn_graph_launch(ctx.handle, self._graph))
+        else:
+            self._issue_round()          # the first round runs eagerly: buffers grow, attributes get set
+            self._eager_rounds += 1
+        self._len_bound += self.n_verify
         self.rounds_run += 1
 
-    def verify_accept_only(self):
-        """The verify + sample half of a round on the current proposals (for per-kernel timing): target
-        forward, acceptance, bookkeeping and the target cache commit; the draft cache is left alone."""
-        ctx, lib, B, k, V = self.ctx, self.ctx.lib, self.B, self.k, self.V
-        greedy = self.temperature <= 0
-        self.target.forward_cached(self.verify_tokens, self.t_cache, out_logits=self.p_logits)
-        ctx._check(lib.vn_accept_strided(
-            ctx.handle, _ptr(self.p_logits), self.n_verify * V, V,
-            None if greedy else _ptr(self.q_logits), V, B * V,
-            _ptr(self.draft_tokens), None, None, self.seed, self.round, self.temperature, self.top_k,
-            int(self.bonus), B, k, V, _ptr(self.accept_len), _ptr(self.out_tokens)))
-        ctx._check(lib.vn_spec_advance(ctx.handle, _ptr(self.out_tokens), B, k, _ptr(self.pair), _ptr(self.history),
-                                       self.cap, _ptr(self.count), _ptr(self.n_commit)))
-        ctx._check(lib.vn_kv_commit(self.t_cache.handle, self.n_verify, None, 0, _ptr(self.n_commit), 0))
-        self.round += 1
+    def verify_accept_only(self, graph: bool = False):
+        """The verify + sample half of a round on the current proposals (for timing): target forward,
+        acceptance, bookkeeping and the target cache commit; the draft cache is left alone."""
+        self._check_capacity()
+        ctx, lib = self.ctx, self.ctx.lib
+        if graph:
+            if self._graph_verify is None:
+                ctx._check(lib.vn_graph_begin(ctx.handle))
+                try:
+                    self._issue_round(draft_part=False)
+                finally:
+                    g = C.c_void_p()
+                    ctx._check(lib.vn_graph_end(ctx.handle, C.byref(g)))
+                self._graph_verify = g
+            ctx._check(lib.vn_graph_launch(ctx.handle, self._graph_verify))
+        else:
+            self._issue_round(draft_part=False)
+        self._len_bound += self.n_verify
 
     # -- results --------------------------------------------------------------------
     def counts(self) -> np.ndarray:
@@ -156,7 +198,6 @@ class SpecEngine:
         if max_new_tokens + self.k + 1 > self.cap:
             raise ValueError("max_new_tokens exceeds the engine's history capacity")
         self.prefill(prompts)
-        accepted = 0
         while True:
             # a request gains at least one token per round: poll the counters only now and then
             need = max_new_tokens - int(self.counts().min())
@@ -168,3 +209,13 @@ class SpecEngine:
         stats = dict(rounds=self.rounds_run, proposed=self.rounds_run * self.k * self.B,
                      committed=int(self.counts().sum()))
         return np.concatenate([prompts, new], axis=1), stats
+
+    def __del__(self):
+        try:
+            for name in ("_graph", "_graph_verify"):
+                g = getattr(self, name, None)
+                if g is not None:
+                    self.ctx.lib.vn_graph_destroy(self.ctx.handle, g)
+                    setattr(self, name, None)
+        except Exception:
+            pass
