@@ -453,19 +453,37 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* __rest
       if ((key & mask) == prefix) atomicAdd(&hist[(key >> sh) & (nb - 1)], 1u);
     }
     __syncthreads();
-    if (tid == 0) {
+    {
+      // digit of the threshold: the largest d with (keys in digits > d) < need <= (keys in digits >= d).
+      // Block-wide suffix sums over the histogram; thread t owns digits 2t and 2t+1 (launched with 1024 threads).
       const int need = s_need;  // how many of the largest keys of this prefix class are kept
-      uint32_t digit = 0; int above = 0;
-      for (int d = (int)nb - 1; d >= 0; --d) {
-        if (above + (int)hist[d] >= need) { digit = (uint32_t)d; break; }
-        above += hist[d];
+      const int lane = tid & 31, warp = tid >> 5;
+      const int h0 = (2 * tid < (int)nb) ? (int)hist[2 * tid] : 0;
+      const int h1 = (2 * tid + 1 < (int)nb) ? (int)hist[2 * tid + 1] : 0;
+      const int local = h0 + h1;
+      int incl = local;       // inclusive suffix sum inside the warp (lanes above me)
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_down_sync(0xffffffffu, incl, o);
+        if (lane + o < 32) incl += v;
       }
-      s_need = need - above;                 // still needed from inside the digit class
-      s_prefix = prefix | (digit << sh);
-      s_mask = mask | ((nb - 1) << sh);
-      const int ncand = want - s_need + (int)hist[digit];  // keys >= the smallest key of the class
-      s_ncand = ncand;
-      s_done = ncand <= CAND_MAX ? 2 : (level == 2 ? 1 : 0);
+      if (lane == 0) wcount[warp] = incl;   // warp total
+      __syncthreads();
+      int above_warps = 0;
+      for (int w = warp + 1; w < (nt >> 5); ++w) above_warps += wcount[w];
+      const int above_me = above_warps + incl - local;   // keys in digits owned by threads after me
+      if (need > 0 && above_me < need && need <= above_me + local) {
+        uint32_t digit; int above;
+        if (above_me + h1 >= need) { digit = 2 * tid + 1; above = above_me; }
+        else { digit = 2 * tid; above = above_me + h1; }
+        s_need = need - above;                 // still needed from inside the digit class
+        s_prefix = prefix | (digit << sh);
+        s_mask = mask | ((nb - 1) << sh);
+        const int ncand = want - (need - above) + (int)hist[digit];  // keys >= the smallest key of the class
+        s_ncand = ncand;
+        s_done = ncand <= CAND_MAX ? 2 : (level == 2 ? 1 : 0);
+      }
+      if (need <= 0 && tid == 0) { s_ncand = 0; s_done = 2; s_prefix = 0xFFFFFFFFu; }   // empty slice
     }
     __syncthreads();
     if (s_done) break;

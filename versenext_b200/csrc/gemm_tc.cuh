@@ -113,7 +113,7 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
       : "r"(taddr));
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs g) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ unsigned long long bar_full[8], bar_empty[8], bar_acc;
@@ -125,6 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   int row0 = 0, cnt = g.M;
   if (g.seg_cnt) { row0 = g.seg_off[z]; cnt = g.seg_cnt[z]; }
   if (cnt > g.ntok) cnt = g.ntok;
+  const int cnt16 = (cnt + 15) & ~15;      // UMMA N and token rows loaded by this CTA
   const int n0 = blockIdx.x * BF;
   const int nkb_total = (g.K + BK - 1) / BK;
   const int kb0 = blockIdx.y * g.kb_per_split;
@@ -166,17 +167,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const int s = kb % S;
         if (!mbar_wait(&bar_empty[s], ((kb / S) & 1) ^ 1)) { s_error = 1; break; }
         unsigned char* st = base + (size_t)s * stage_bytes;
-        mbar_expect_tx(&bar_full[s], stage_bytes);
+        mbar_expect_tx(&bar_full[s], w_bytes + (unsigned)cnt16 * BK * 2);
         const int kx = (kb0 + kb) * BK;
         tma_load_2d(st, &tm_w, &bar_full[s], kx, w_row);
-        tma_load_2d(st + w_bytes, &tm_x, &bar_full[s], kx, row0);
+        // tokens in boxes of 16 rows (two swizzle atoms each): only the rows this segment has
+        for (int r16 = 0; r16 < cnt16; r16 += 16)
+          tma_load_2d(st + w_bytes + (size_t)r16 * BK * 2, &tm_x, &bar_full[s], kx, row0 + r16);
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       // instruction descriptor: D fp32, A and B bf16, both K-major, N = ntok, M = 128
-      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(g.ntok >> 3) << 17) | ((unsigned)(BF >> 4) << 24);
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(cnt16 >> 3) << 17) | ((unsigned)(BF >> 4) << 24);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % S;
@@ -296,7 +299,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   const int ntok = (g.M + 15) & ~15;
   CUtensorMap tm_w, tm_x;
   const long long w_rows = g.seg_cnt ? (long long)(g.nseg - 1) * (g.w_stride / g.ldw) + g.N : g.N;
-  if (!make_map(&tm_w, g.W, w_rows, g.K, g.ldw, BF) || !make_map(&tm_x, g.A, a_rows_total, g.K, g.lda, ntok))
+  if (!make_map(&tm_w, g.W, w_rows, g.K, g.ldw, BF) || !make_map(&tm_x, g.A, a_rows_total, g.K, g.lda, 16))
     return vn_fail(ctx, VN_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   TcArgs a;
   a.C = g.C; a.bias = g.bias; a.ldc = g.ldc; a.M = g.M; a.N = g.N; a.K = g.K; a.ntok = ntok;
@@ -304,7 +307,9 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   const int nkb = (g.K + BK - 1) / BK;
   const int splits = std::max(1, std::min(plan.splits, nkb));
   a.kb_per_split = (nkb + splits - 1) / splits;
-  int stages = (int)std::min<size_t>(8, (200 * 1024) / stage_bytes);
+  // at most ~108 KB of stages per CTA so that two CTAs share an SM: one drains its accumulator while the
+  // other streams
+  int stages = (int)std::min<size_t>(6, (108 * 1024) / stage_bytes);
   stages = std::max(2, std::min(stages, std::max(2, a.kb_per_split)));
   a.stages = stages;
   a.epi = g.epi; a.c_bf16 = g.c_bf16;
