@@ -131,6 +131,9 @@ def dist_setup(n_gpus):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     dist = None
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         import torch
         import torch.distributed as dist_mod
         torch.cuda.set_device(local)
@@ -196,13 +199,13 @@ def spec_prompts(B, T, seed, rank=0):
     return np.random.default_rng([seed, rank]).integers(0, 248320, (B, T)).astype(np.int64)
 
 
-def build_spec_models(scale=1.0):
+def build_spec_models(device="cuda"):
     import versenext_b200 as vn
     from versenext_b200 import synthetic as S
     tk, dk = S.mate_kwargs(), S.draft_kwargs()
-    target = vn.VerseNexLM(dtype="bf16", **tk)
+    target = vn.VerseNexLM(dtype="bf16", device=device, **tk)
     S.load_random(target, tk, seed=0)
-    draft = vn.VerseNexLM(dtype="bf16", **dk)
+    draft = vn.VerseNexLM(dtype="bf16", device=device, **dk)
     S.load_random(draft, dk, seed=1)
     return target, draft
 
@@ -242,7 +245,7 @@ def run_spec(args):
     ctx = vn.Context.get(local)
     B, k, T0 = SPEC["B"], SPEC["k"], SPEC["prompt"]
     t_build = time.perf_counter()
-    target, draft = build_spec_models()
+    target, draft = build_spec_models(f"cuda:{local}")
     t_build = time.perf_counter() - t_build
     warm = max(args.warmup, 3)
     max_seq = T0 + (warm + 4 * args.steps + 40) * (k + 1) + 64
@@ -328,7 +331,7 @@ def run_spec(args):
         eng.verify_accept_only()
     rep = ctx.profile_report()
     ctx.profile(False)
-    prof_ms = sum(v["ms"] for v in rep.values()) / n_prof
+    prof_ms = max(sum(v["ms"] for v in rep.values()) / n_prof, 1e-9)
     gemm_ms = sum(v["ms"] for n, v in rep.items() if n.startswith("gemm_")) / n_prof * (step_ms / prof_ms)
     nbytes = spec_step_bytes(B, ctx_len)
     peak, peak_kind = peaks()
