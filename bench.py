@@ -131,9 +131,9 @@ def dist_setup(n_gpus):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     dist = None
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # NCCL writes its version banner and debug lines to stdout: send them to stderr so that
+        # stdout carries the one JSON line only.
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import torch
         import torch.distributed as dist_mod
         torch.cuda.set_device(local)

@@ -263,3 +263,64 @@ def test_tensor_core_attention_head_dim_64(variant):
         lg = m.forward_cached(nxt, cache).numpy()
         want, _ = OM.forward(sd, cfg, nxt, cache=oc)
     assert rel_err(lg, want) < 2e-2
+
+
+def _dequantise(w, scheme):
+    from oracle import quant as OQ
+    if scheme == "int8":
+        q, s = OQ.quantize_int8(w)
+        return OQ.dequant_int8(q, s)
+    if scheme == "int4":
+        p, s = OQ.quantize_int4(w)
+        return OQ.dequant_int4(p, s, w.shape[1])
+    p, s = OQ.quantize_int4_g128(w)
+    return OQ.dequant_int4_g128(p, s, w.shape[1])
+
+
+def _dequantised_state_dict(sd, cfg, scheme):
+    """What the quantised device model computes with, as float32 weights for the oracle."""
+    out = {}
+    for n, w in sd.items():
+        linear = w.ndim == 2 and n.endswith(".weight") and "global_tokens" not in n and "router" not in n \
+            and n != "tok_emb.weight"
+        out[n] = _dequantise(w, scheme) if linear else w
+    if cfg.tie_weights:   # the head is quantised on its own copy, the embedding stays dense
+        out["head.weight"] = _dequantise(sd["tok_emb.weight"], scheme)
+    return out
+
+
+@pytest.mark.parametrize("scheme", ["int8", "int4", "int4g128"])
+def test_weight_only_quantised_model(scheme):
+    """INT8 / INT4 per output channel (reference schemes) and INT4 group-128: the device model against the
+    reference forward run on the dequantised weights; MoD + TriSparse, chain then cached continuation."""
+    cfg = OM.mate_config(vocab_size=320, dim=128, n_layer=2, n_head=4, n_kv_head=2, window_size=16,
+                         num_global_tokens=8, max_seq_len=128, init_std=0.08, num_dense_parts=2,
+                         num_experts_per_part=2, top_k=1, expert_hidden=128, mlp_hidden_multiple=3)
+    assert cfg.mlp_hidden % 128 == 0 and cfg.expert_hidden % 128 == 0
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=31, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    m.quantize(scheme)
+    sd_q = _dequantised_state_dict(sd, cfg, scheme)
+    oracle_cfg = OM.Config(**{**cfg.to_dict(), "tie_weights": False})
+    toks = np.random.default_rng(8).integers(0, 320, (2, 30))
+    cache = m.new_cache(2, 64)
+    lg = m.forward_cached(toks[:, :24], cache).numpy()
+    want, oc = OM.forward(sd_q, oracle_cfg, toks[:, :24])
+    assert rel_err(lg, want) < 2e-2
+    cache.commit(24, np.full(2, 24, np.int32))
+    lg2 = m.forward_cached(toks[:, 24:], cache).numpy()
+    want2, _ = OM.forward(sd_q, oracle_cfg, toks[:, 24:], cache=oc)
+    assert rel_err(lg2, want2) < 2e-2
+    with pytest.raises(ValueError):
+        m.load_tensor("norm.weight", np.ones(128, np.float32))
+    with pytest.raises(ValueError):
+        m.quantize("int8")
+
+
+def test_quantise_needs_bf16_and_known_scheme():
+    cfg = OM.small_config()
+    m = build(cfg, OM.init_state_dict(cfg, seed=4))
+    with pytest.raises(NotImplementedError):
+        m.quantize("int8")
+    with pytest.raises(ValueError):
+        m.quantize("fp3")

@@ -26,6 +26,10 @@ struct GemmArgs {
   int epi = EPI_STORE;
   int c_bf16 = 0;
   const char* tag = nullptr;      // name of the call site in the per-kernel timing report (string literal)
+  // weight-only quantisation: W points at INT8 / packed INT4 bytes, ldw and w_stride stay in ELEMENTS
+  int wq = 0;                     // 0 dense, 1 int8, 2 int4 per output row, 3 int4 with one scale per 128 inputs
+  const float* w_scale = nullptr; // [N] (wq 1, 2) or [N, K/128] (wq 3)
+  long long ws_stride = 0;        // scales between consecutive segments
 };
 
 __device__ __forceinline__ float ld_f(const float* p) { return *p; }

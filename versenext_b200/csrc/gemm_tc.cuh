@@ -33,6 +33,7 @@ struct TcArgs {
   long long ldc;
   int M, N, K;             // tokens (per segment: upper bound), features, reduction
   int ntok;                // UMMA N: tokens rounded up to 16
+  int x_box;               // token rows per TMA box: ntok (one box) for a dense block, 16 in segmented mode
   int stages;
   int kb_per_split;        // k blocks (of 64) per blockIdx.y
   int epi, c_bf16;
@@ -171,7 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const int kx = (kb0 + kb) * BK;
         tma_load_2d(st, &tm_w, &bar_full[s], kx, w_row);
         // tokens in boxes of 16 rows (two swizzle atoms each): only the rows this segment has
-        for (int r16 = 0; r16 < cnt16; r16 += 16)
+        for (int r16 = 0; r16 < cnt16; r16 += g.x_box)
           tma_load_2d(st + w_bytes + (size_t)r16 * BK * 2, &tm_x, &bar_full[s], kx, row0 + r16);
       }
     }
@@ -299,10 +300,11 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   const int ntok = (g.M + 15) & ~15;
   CUtensorMap tm_w, tm_x;
   const long long w_rows = g.seg_cnt ? (long long)(g.nseg - 1) * (g.w_stride / g.ldw) + g.N : g.N;
-  if (!make_map(&tm_w, g.W, w_rows, g.K, g.ldw, BF) || !make_map(&tm_x, g.A, a_rows_total, g.K, g.lda, 16))
+  if (!make_map(&tm_w, g.W, w_rows, g.K, g.ldw, BF) || !make_map(&tm_x, g.A, a_rows_total, g.K, g.lda, g.seg_cnt ? 16 : ntok))
     return vn_fail(ctx, VN_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   TcArgs a;
   a.C = g.C; a.bias = g.bias; a.ldc = g.ldc; a.M = g.M; a.N = g.N; a.K = g.K; a.ntok = ntok;
+  a.x_box = g.seg_cnt ? 16 : ntok;
   const size_t stage_bytes = (size_t)BF * BK * 2 + (size_t)ntok * BK * 2;
   const int nkb = (g.K + BK - 1) / BK;
   const int splits = std::max(1, std::min(plan.splits, nkb));

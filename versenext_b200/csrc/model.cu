@@ -7,6 +7,7 @@
 #include "model_kernels.cuh"
 #include "attn_mma.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_mma_q.cuh"
 
 #include <math.h>
 #include <stdlib.h>
@@ -89,6 +90,10 @@ struct Layer {
   float* router = nullptr;  // mod: [(P + P E), D] fp32
   void* e_gateup = nullptr; // mod: [P E][2 eh, D]
   void* e_down = nullptr;   // mod: [P E][D, eh]
+  // weight-only quantised copies (dense buffers are freed once these exist): 0 qkv, 1 proj, 2 gate|up, 3 down,
+  // 4 expert gate|up, 5 expert down
+  void* q[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  float* qs[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 }  // namespace
@@ -122,6 +127,9 @@ struct vn_model {
   int* sorted_row = nullptr; int* slot_pos = nullptr;
   int* depth_dev = nullptr; unsigned long long* anc_dev = nullptr; int* rows_dev = nullptr;
   float* stage = nullptr; size_t stage_elems = 0;
+  int qmode = 0;                 // 0 dense, 1 int8, 2 int4 per channel, 3 int4 group-128 (vn_model_quantize)
+  void* head_q = nullptr;        // quantised LM head (its own copy: the embedding table stays dense)
+  float* head_qs = nullptr;
   void* hs = nullptr;            // [M * slots, D] routed activations in expert order (tcgen05 path)
   float* partial = nullptr;      // split-K workspace of the tcgen05 path
   size_t partial_bytes = 0;
@@ -255,6 +263,10 @@ int32_t ensure_rows(vn_model* m, int M) {
 // one Linear: C = A @ W^T with the epilogue, dispatching on the storage dtype
 int32_t linear(vn_model* m, GemmArgs g) {
   vn_ctx* ctx = m->ctx;
+  if (g.wq) {
+    if (!gemm_mma_q_supported(g)) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised GEMM shape K=%d unsupported", g.K);
+    return launch_gemm_mma_q(ctx, g);
+  }
   if (m->cfg.bf16) {
     if (gemm_mma_supported(g)) return launch_gemm_mma(ctx, g);
     return launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g);
@@ -270,6 +282,15 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
   const int M = B * Tn, D = c.dim, H = c.n_head, hd = c.hd, n_kv = c.n_kv;
   const int qkv_ld = (H + 2 * n_kv) * hd;
   const float emb_scale = c.emb_scale ? sqrtf((float)D) : 1.0f;
+  // dense weight, or its quantised copy with the scales (rows_per_seg: output rows of one expert)
+  auto pick = [&](GemmArgs& g, void* dense, void* q, float* qs, long long rows_per_seg) {
+    if (m->qmode) {
+      g.W = q; g.w_scale = qs; g.wq = m->qmode;
+      g.ws_stride = rows_per_seg * (m->qmode == 3 ? g.K / 128 : 1);
+    } else {
+      g.W = dense;
+    }
+  };
   VN_LAUNCH(ctx, embed_kernel<T>, M, 128, 0, (const long long*)tokens, (const T*)m->emb, m->x, D, c.vocab, emb_scale,
             m->status);
   for (int li = 0; li < c.n_layer; ++li) {
@@ -278,6 +299,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.C = m->qkv; g.ldc = qkv_ld; g.M = M; g.N = qkv_ld; g.K = D;
     g.tag = "gemm_qkv";
+    pick(g, L.wqkv, L.q[0], L.qs[0], 0);
     TRY(linear(m, g));
     VN_LAUNCH(ctx, rope_append_kernel<T>, M, 128, 0, m->qkv, m->rope_cos, m->rope_sin, kv->lens,
               tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq,
@@ -300,6 +322,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
     g = GemmArgs();
     g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.C = m->x; g.ldc = D; g.M = M; g.N = D; g.K = H * hd;
     g.epi = EPI_ADD; g.tag = "gemm_proj";
+    pick(g, L.wproj, L.q[1], L.qs[1], 0);
     TRY(linear(m, g));
     const bool mod = L.kind == 1;
     VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm2, (T*)m->h, mod ? m->h32 : (float*)nullptr,
@@ -308,10 +331,12 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
       g = GemmArgs();
       g.A = m->h; g.lda = D; g.W = L.w_gateup; g.ldw = D; g.C = m->act; g.ldc = c.mlp_hidden; g.M = M;
       g.N = 2 * c.mlp_hidden; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = c.bf16; g.tag = "gemm_gateup";
+      pick(g, L.w_gateup, L.q[2], L.qs[2], 0);
       TRY(linear(m, g));
       g = GemmArgs();
       g.A = m->act; g.lda = c.mlp_hidden; g.W = L.w_down; g.ldw = c.mlp_hidden; g.C = m->x; g.ldc = D; g.M = M; g.N = D;
       g.K = c.mlp_hidden; g.epi = EPI_ADD; g.tag = "gemm_down";
+      pick(g, L.w_down, L.q[3], L.qs[3], 0);
       TRY(linear(m, g));
     } else {
       const int ne = c.P * c.E, S = c.P * c.top_k, eh = c.expert_hidden;
@@ -327,11 +352,13 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
       g.A = m->h; g.lda = D; g.a_rows = m->sorted_row; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
       g.C = m->act; g.ldc = eh; g.M = M; g.N = 2 * eh; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = c.bf16;
       g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne; g.tag = "gemm_expert_gateup";
+      pick(g, L.e_gateup, L.q[4], L.qs[4], 2 * eh);
       TRY(linear(m, g));
       g = GemmArgs();
       g.A = m->act; g.lda = eh; g.W = L.e_down; g.ldw = eh; g.w_stride = (long long)D * eh; g.C = m->y; g.ldc = D;
       g.M = M; g.N = D; g.K = eh; g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne;
       g.tag = "gemm_expert_down";
+      pick(g, L.e_down, L.q[5], L.qs[5], D);
       TRY(linear(m, g));
       VN_LAUNCH(ctx, mod_combine_kernel, M, 256, 0, m->x, m->y, m->slot_pos, m->slot_w, m->part_w, D, c.P, c.top_k);
     }
@@ -344,6 +371,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = m->head; g.ldw = D; g.C = out_logits; g.ldc = c.vocab; g.M = rows_out; g.N = c.vocab;
     g.K = D; g.tag = "gemm_head";
+    pick(g, m->head, m->head_q, m->head_qs, 0);
     TRY(linear(m, g));
   }
   return VN_OK;
@@ -570,7 +598,8 @@ int32_t vn_model_destroy(vn_model* m) {
   }
   F(m->x); F(m->h); F(m->h32); F(m->qkv); F(m->attn); F(m->act); F(m->y); F(m->slot_expert); F(m->slot_w); F(m->part_w);
   F(m->expert_count); F(m->expert_off); F(m->expert_cur); F(m->sorted_row); F(m->slot_pos); F(m->depth_dev);
-  F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error);
+  F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->head_q); F(m->head_qs);
+  for (auto& L : m->layers) for (int i = 0; i < 6; ++i) { F(L.q[i]); F(L.qs[i]); }
   delete m;
   return VN_OK;
 }
@@ -580,6 +609,7 @@ int32_t vn_model_load_tensor(vn_model* m, const char* name, const float* data, i
   vn_ctx* ctx = m->ctx;
   VN_CHECK_CTX(ctx);
   VN_REQUIRE(ctx, name && data && shape && ndim >= 1 && ndim <= 2, "bad tensor argument");
+  VN_REQUIRE(ctx, m->qmode == 0, "the model is quantised: its dense weights are gone, create a new model to reload");
   const Config& c = m->cfg;
   const std::string n(name);
   const long long r = shape[0], cl = ndim == 2 ? shape[1] : 1;
@@ -655,6 +685,7 @@ int32_t vn_model_finalize(vn_model* m) {
   if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
   vn_ctx* ctx = m->ctx;
   VN_CHECK_CTX(ctx);
+  if (m->qmode) return VN_OK;   // nothing left to derive once the weights are quantised
   const Config& c = m->cfg;
   // every tensor of the reference's state_dict must have arrived (head.weight may be omitted when tied)
   std::vector<std::string> want = {"tok_emb.weight", "norm.weight"};
@@ -719,9 +750,74 @@ int32_t vn_model_finalize(vn_model* m) {
   return VN_OK;
 }
 
+// quantise one dense bf16 matrix [rows, K]; the dense buffer is released afterwards when `release` is set
+static int32_t quantize_matrix(vn_model* m, void** dense, long long rows, int K, int mode, void** q, float** qs,
+                               bool release, uint64_t* bytes) {
+  vn_ctx* ctx = m->ctx;
+  VN_REQUIRE(ctx, K % 64 == 0 && (mode != 3 || K % 128 == 0), "in_features %d not supported by the quantised kernels", K);
+  const size_t qbytes = (size_t)rows * (mode == 1 ? K : K / 2);
+  const size_t nscale = (size_t)rows * (mode == 3 ? K / 128 : 1);
+  TRY(dev_alloc(ctx, q, qbytes));
+  TRY(dev_alloc(ctx, (void**)qs, nscale * 4));
+  const __nv_bfloat16* w = (const __nv_bfloat16*)*dense;
+  if (mode == 1) VN_LAUNCH(ctx, mmaq_detail::quantize_rows_kernel<1>, (unsigned)rows, 256, 0, w, K, (unsigned char*)*q, *qs);
+  else if (mode == 2) VN_LAUNCH(ctx, mmaq_detail::quantize_rows_kernel<2>, (unsigned)rows, 256, 0, w, K, (unsigned char*)*q, *qs);
+  else {
+    VN_REQUIRE(ctx, rows < (1ll << 31) && K / 128 < 65536, "matrix too large");
+    dim3 grid((unsigned)rows, K / 128);
+    VN_LAUNCH(ctx, mmaq_detail::quantize_g128_kernel, grid, 128, 0, w, K, (unsigned char*)*q, *qs);
+  }
+  *bytes += qbytes + nscale * 4;
+  if (release) {
+    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    VN_CUDA(ctx, cudaFree(*dense));
+    *dense = nullptr;
+  }
+  return VN_OK;
+}
+
 int32_t vn_model_quantize(vn_model* m, const char* scheme) {
   if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
-  return vn_fail(m->ctx, VN_ERR_UNSUPPORTED, "quantisation scheme %s is not built yet", scheme ? scheme : "(null)");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, scheme, "scheme is null");
+  const std::string s(scheme);
+  const int mode = s == "int8" ? 1 : (s == "int4" ? 2 : (s == "int4g128" ? 3 : 0));
+  VN_REQUIRE(ctx, mode != 0, "unknown quantisation scheme %s (int8 | int4 | int4g128)", scheme);
+  VN_REQUIRE(ctx, m->finalized, "quantise after vn_model_finalize");
+  VN_REQUIRE(ctx, m->qmode == 0, "model is already quantised");
+  if (!m->cfg.bf16) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "weight-only quantisation needs a bf16 model");
+  const Config& c = m->cfg;
+  const long long D = c.dim, qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
+  uint64_t bytes = 0;
+  // every Linear of the blocks and the LM head (verse_torch/compress.py:807-822 swaps every Linear and gives
+  // the tied head its own quantised copy); the router gates and the embedding table stay dense
+  for (auto& L : m->layers) {
+    TRY(quantize_matrix(m, &L.wqkv, qd + 2 * kvd, (int)D, mode, &L.q[0], &L.qs[0], true, &bytes));
+    TRY(quantize_matrix(m, &L.wproj, D, (int)qd, mode, &L.q[1], &L.qs[1], true, &bytes));
+    if (L.kind == 0) {
+      TRY(quantize_matrix(m, &L.w_gateup, 2ll * c.mlp_hidden, (int)D, mode, &L.q[2], &L.qs[2], true, &bytes));
+      TRY(quantize_matrix(m, &L.w_down, D, c.mlp_hidden, mode, &L.q[3], &L.qs[3], true, &bytes));
+    } else {
+      const long long ne = (long long)c.P * c.E;
+      TRY(quantize_matrix(m, &L.e_gateup, ne * 2 * c.expert_hidden, (int)D, mode, &L.q[4], &L.qs[4], true, &bytes));
+      TRY(quantize_matrix(m, &L.e_down, ne * D, c.expert_hidden, mode, &L.q[5], &L.qs[5], true, &bytes));
+    }
+  }
+  void* head = m->head;
+  TRY(quantize_matrix(m, &head, c.vocab, (int)D, mode, &m->head_q, &m->head_qs, false, &bytes));
+  if (!c.tie && m->head) { VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); VN_CUDA(ctx, cudaFree(m->head)); m->head = nullptr; }
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  m->qmode = mode;
+  m->use_tc = false;
+  // embedding + norms + routers + sinks stay as they were
+  uint64_t keep = (uint64_t)c.vocab * D * m->esz + (uint64_t)D * 4;
+  for (auto& L : m->layers) {
+    keep += 2ull * D * 4 + (uint64_t)c.n_sink * D * m->esz;
+    if (L.kind == 1) keep += (uint64_t)(c.P + c.P * c.E) * D * 4;
+  }
+  m->param_bytes = keep + bytes;
+  return VN_OK;
 }
 
 int32_t vn_model_param_bytes(vn_model* m, uint64_t* out) {

@@ -185,6 +185,20 @@ class VerseNexLM:
         self.ctx._check(self.ctx.lib.vn_model_finalize(self.handle))
         self._finalized = True
 
+    def quantize(self, scheme: str = "int8"):
+        """Weight-only quantisation of every Linear of the blocks and of the LM head, on the device.
+
+        "int8" and "int4" are the reference's per-output-channel schemes (verse_torch/quantize.py:187-258:
+        scale = max|w| / 127 or / 7, round-half-even, INT4 packed two per byte with the even index in the low
+        nibble); "int4g128" keeps one bf16 scale per 128 input features.  The LM head gets its own quantised
+        copy (as compress.py:817-822 un-ties it); the embedding table and the router gates stay dense.
+        bf16 models only.  The dense weights are released: the model cannot be reloaded afterwards."""
+        if not self._finalized:
+            self.finalize()
+        self.ctx._check(self.ctx.lib.vn_model_quantize(self.handle, scheme.encode()))
+        self.quantized = scheme
+        return self
+
     def new_cache(self, max_batch: int, max_seq: Optional[int] = None) -> KVCache:
         return KVCache(self, max_batch, max_seq if max_seq is not None else self.max_seq_len)
 
