@@ -422,6 +422,8 @@ struct TopkRow {
 // shared memory they are gathered (one more read of the row) and the select finishes there.
 __global__ void __launch_bounds__(1024)
 accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   // blockIdx.x = row * chunks + chunk: every CTA selects inside its own slice of the row; the slices'
   // lists are merged by accept_topk_merge_kernel (the row's k largest are among the slices' k largest)
   const int rows_per_seq = rs.np + rs.nq;
@@ -556,6 +558,8 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* __rest
 // counting, everything >= it is kept; slices are in ascending token order, so the output is too.
 __global__ void __launch_bounds__(256)
 accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_k, TopkRow* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int MERGE_MAX = 4096;
   __shared__ float s_val[MERGE_MAX];
   __shared__ int s_tok[MERGE_MAX];
@@ -628,6 +632,8 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
                           const float* __restrict__ u_smp, uint64_t seed, uint32_t offset_host,
                           const unsigned* __restrict__ offset_dev, int bonus, int smp_purpose, int pos_base,
                           int* __restrict__ out_len, long long* __restrict__ out_tok) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (b >= B) return;
@@ -790,9 +796,9 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
     if (st) return st;
     TopkRow* rows = (TopkRow*)ws;                 // merged lists [n_rows]
     TopkRow* parts = rows + n_rows;               // per-slice lists [n_rows * chunks]
-    VN_LAUNCH(ctx, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, chunks > 1 ? parts : rows);
-    if (chunks > 1) VN_LAUNCH(ctx, accept_topk_merge_kernel, n_rows, 256, 0, parts, chunks, top_k, rows);
-    VN_LAUNCH(ctx, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, B, k, rs.np, rs.nq, rows, d64, u_acc, u_smp,
+    VN_LAUNCH_PDL(ctx, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, chunks > 1 ? parts : rows);
+    if (chunks > 1) VN_LAUNCH_PDL(ctx, accept_topk_merge_kernel, n_rows, 256, 0, parts, chunks, top_k, rows);
+    VN_LAUNCH_PDL(ctx, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, B, k, rs.np, rs.nq, rows, d64, u_acc, u_smp,
               seed, offset, ctx->offset_src, bonus, smp_purpose, pos_base, out_len, o64);
     return VN_OK;
   }

@@ -150,6 +150,8 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
   const int n_rep = a.H / a.n_kv;
   const int R = a.Tn * n_rep;
   const int tile0 = blockIdx.y * 16;
+  pdl_trigger();
+  pdl_wait();
   const int len = a.lens[b] + a.slot_offset;
   if (a.depth) {
     if (tid < 64) s_depth[tid] = tid < a.Tn ? a.depth[tid] : 0;
@@ -280,6 +282,6 @@ inline bool attn_mma_supported(const AttnArgs& a, bool bf16) {
 inline int32_t launch_attn_mma(vn_ctx* ctx, const AttnArgs& a, int B) {
   const int n_rep = a.H / a.n_kv;
   dim3 grid(B * a.n_kv, ceil_div(a.Tn * n_rep, 16));
-  VN_LAUNCH(ctx, attn_detail::trisparse_attn_mma_kernel, grid, attn_detail::AW * 32, 0, a);
+  VN_LAUNCH_PDL(ctx, attn_detail::trisparse_attn_mma_kernel, grid, attn_detail::AW * 32, 0, a);
   return VN_OK;
 }

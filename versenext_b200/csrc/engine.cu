@@ -9,6 +9,8 @@ namespace {
 // tokens) -> draft [B, k] and the target's verify input [B, n_verify] = (last committed, d_0, d_1, ...)
 __global__ void spec_gather_kernel(const long long* __restrict__ step_tokens, const long long* __restrict__ pair, int B,
                                    int k, int n_verify, long long* __restrict__ draft, long long* __restrict__ verify) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   verify[(long long)b * n_verify] = pair[b * 2 + 1];
@@ -23,6 +25,8 @@ __global__ void spec_gather_kernel(const long long* __restrict__ step_tokens, co
 __global__ void spec_advance_kernel(const long long* __restrict__ out_tokens, int B, int k, long long* __restrict__ pair,
                                     long long* __restrict__ history, int cap, int* __restrict__ count,
                                     int* __restrict__ n_commit, unsigned* __restrict__ round_counter) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b == 0 && round_counter) *round_counter += 1u;   // read by this round's kernels earlier in the stream
   if (b >= B) return;
@@ -49,7 +53,7 @@ int32_t vn_spec_gather(vn_ctx* ctx, const int64_t* step_tokens_dev, const int64_
   VN_CHECK_CTX(ctx);
   VN_REQUIRE(ctx, step_tokens_dev && pair_dev && draft_dev && verify_dev && B >= 1 && k >= 1 && n_verify >= 1 &&
              n_verify <= k + 1, "bad arguments");
-  VN_LAUNCH(ctx, spec_gather_kernel, ceil_div(B, 128), 128, 0, (const long long*)step_tokens_dev,
+  VN_LAUNCH_PDL(ctx, spec_gather_kernel, ceil_div(B, 128), 128, 0, (const long long*)step_tokens_dev,
             (const long long*)pair_dev, B, k, n_verify, (long long*)draft_dev, (long long*)verify_dev);
   return VN_OK;
 }
@@ -59,7 +63,7 @@ int32_t vn_spec_advance(vn_ctx* ctx, const int64_t* out_tokens_dev, int32_t B, i
   VN_CHECK_CTX(ctx);
   VN_REQUIRE(ctx, out_tokens_dev && pair_dev && history_dev && count_dev && n_commit_dev && B >= 1 && k >= 0 && cap >= 0,
              "bad arguments");
-  VN_LAUNCH(ctx, spec_advance_kernel, ceil_div(B, 128), 128, 0, (const long long*)out_tokens_dev, B, k,
+  VN_LAUNCH_PDL(ctx, spec_advance_kernel, ceil_div(B, 128), 128, 0, (const long long*)out_tokens_dev, B, k,
             (long long*)pair_dev, (long long*)history_dev, cap, count_dev, n_commit_dev,
             const_cast<unsigned*>(ctx->offset_src));
   return VN_OK;

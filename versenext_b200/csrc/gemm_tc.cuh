@@ -43,8 +43,15 @@ struct TcArgs {
   float* partial;          // split-K workspace [gridDim.y][rows_total][N] or null
   long long partial_stride;  // rows_total * N
   int* error_flag;
+  long long* trace;        // optional [CTAs][8] clock64 stamps of the kernel's phases (null: no tracing)
 };
 
+// SM cycle counter, ordered with the surrounding memory operations (for the optional phase stamps)
+__device__ __forceinline__ long long clock_now() {
+  long long c;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(c) :: "memory");
+  return c;
+}
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
@@ -52,6 +59,10 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// adds to the transaction count of the current phase without arriving
+__device__ __forceinline__ void mbar_expect_tx_only(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(unsigned long long* bar, unsigned parity) {
   unsigned ok;
@@ -114,6 +125,9 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
       : "r"(taddr));
 }
 
+enum { TC_PARTIAL = 0, TC_STORE = 1, TC_SWIGLU = 2, TC_ADD = 3 };
+
+template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs g) {
   extern __shared__ unsigned char smem_raw[];
@@ -124,7 +138,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int z = blockIdx.z;
   int row0 = 0, cnt = g.M;
-  if (g.seg_cnt) { row0 = g.seg_off[z]; cnt = g.seg_cnt[z]; }
+  long long* tr = g.trace ? g.trace + 8ll * (blockIdx.x + gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z)) : nullptr;
+  if (tr && threadIdx.x == 0) {
+    tr[0] = clock_now();
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    tr[6] = (long long)ns;
+  }
+  pdl_trigger();
+  // segment sizes are written by the routing kernels that precede this one; a dense block only waits
+  // once its first weight tiles are on their way (weights never change)
+  if (g.seg_cnt) { pdl_wait(); row0 = g.seg_off[z]; cnt = g.seg_cnt[z]; }
   if (cnt > g.ntok) cnt = g.ntok;
   const int cnt16 = (cnt + 15) & ~15;      // UMMA N and token rows loaded by this CTA
   const int n0 = blockIdx.x * BF;
@@ -159,12 +183,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = tmem_base_slot;
+  if (tr && threadIdx.x == 0) tr[1] = clock_now();          // barriers initialised, TMEM allocated
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const int w_row = (int)((long long)z * g.w_rows_per_seg) + n0;
-      for (int kb = 0; kb < nkb; ++kb) {
+      int kb_first = 0;
+      if (!g.seg_cnt) {
+        const int npre = nkb < S ? nkb : S;
+        for (int kb = 0; kb < npre; ++kb) {
+          mbar_expect_tx_only(&bar_full[kb], w_bytes);
+          tma_load_2d(base + (size_t)kb * stage_bytes, &tm_w, &bar_full[kb], (kb0 + kb) * BK, w_row);
+        }
+        pdl_wait();
+        for (int kb = 0; kb < npre; ++kb) {
+          mbar_expect_tx(&bar_full[kb], (unsigned)cnt16 * BK * 2);
+          for (int r16 = 0; r16 < cnt16; r16 += g.x_box)
+            tma_load_2d(base + (size_t)kb * stage_bytes + w_bytes + (size_t)r16 * BK * 2, &tm_x, &bar_full[kb],
+                        (kb0 + kb) * BK, row0 + r16);
+        }
+        kb_first = npre;
+      }
+      for (int kb = kb_first; kb < nkb; ++kb) {
         const int s = kb % S;
         if (!mbar_wait(&bar_empty[s], ((kb / S) & 1) ^ 1)) { s_error = 1; break; }
         unsigned char* st = base + (size_t)s * stage_bytes;
@@ -185,6 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % S;
         if (!mbar_wait(&bar_full[s], (kb / S) & 1)) { s_error = 1; ok = false; break; }
+        if (tr && kb == 0) tr[2] = clock_now();             // first stage landed
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         unsigned char* st = base + (size_t)s * stage_bytes;
         const unsigned long long da = umma_desc(st), db = umma_desc(st + w_bytes);
@@ -194,44 +236,115 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         umma_commit(&bar_empty[s]);            // frees the stage when these MMAs have read it
       }
       umma_commit(&bar_acc);                   // accumulator complete (or abandoned)
+      if (tr) tr[3] = clock_now();                          // last MMA issued
     }
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
     const int q = warp & 3;
     const int f = q * 32 + lane;               // feature within the tile
     const int n = n0 + f;
+    pdl_wait();
     const bool acc_ok = mbar_wait(&bar_acc, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (!acc_ok) s_error = 1;
-    // one decision per warp: the TMEM loads below are warp-collective
-    const int go = __shfl_sync(0xffffffffu, (acc_ok && *(volatile int*)&s_error == 0) ? 1 : 0, 0);
+    if (tr && threadIdx.x == 64) tr[4] = clock_now();       // accumulator complete
+    // one decision for the four epilogue warps (named barrier 1 with an AND reduction): the TMEM loads are
+    // warp-collective and the staged stores below synchronise the four warps with each other
+    int go;
+    {
+      const int mine = (acc_ok && *(volatile int*)&s_error == 0) ? 1 : 0;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.b32 q, %1, 0;\n\t"
+          "bar.red.and.pred p, 1, 128, q;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(go) : "r"(mine) : "memory");
+    }
     if (go) {
+      // One instantiation per epilogue kind keeps this unrolled loop small: with all kinds in one body the
+      // loop outgrew the instruction cache and the epilogue took 9 us for 160 tokens instead of about 1.
       const int nchunk = (cnt + 31) >> 5;
+      // float4 rows need 16-byte alignment of every row start (uniform over the CTA)
+      const bool vec_ok = MODE == TC_PARTIAL
+                              ? (g.N % 4 == 0 && ((uintptr_t)g.partial & 15) == 0)
+                              : (g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 15) == 0);
       for (int ch = 0; ch < nchunk; ++ch) {
         unsigned r[32];
         tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int m0 = ch * 32;
+        const int mrem = cnt - m0;               // tokens left from this chunk on (>= 1)
+        if (MODE == TC_PARTIAL || (MODE == TC_STORE && !g.c_bf16)) {
+          // fp32 rows of the output: staged through shared memory (the pipeline stages are free once the
+          // accumulator is complete) so that one instruction stores 512 contiguous bytes of a token row
+          float* out; long long ld;
+          if (MODE == TC_PARTIAL) { out = g.partial + (long long)blockIdx.y * g.partial_stride; ld = g.N; }
+          else { out = reinterpret_cast<float*>(g.C); ld = g.ldc; }
+          out += (long long)(row0 + m0) * ld + n0;
+          const float bias = (MODE == TC_STORE && g.bias && n < g.N) ? g.bias[n] : 0.f;
+          if (vec_ok) {
+            float* tile = reinterpret_cast<float*>(base) + (ch & 1) * (32 * BF);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int m = ch * 32 + i;
-          float v = __uint_as_float(r[i]);
-          const long long crow = (long long)(row0 + m);
-          if (g.partial) {
-            if (m < cnt && n < g.N) g.partial[(long long)blockIdx.y * g.partial_stride + crow * g.N + n] = v;
-          } else if (g.epi == EPI_SWIGLU) {
+            for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]) + bias;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int c4 = lane * 4;
+            if (n0 + c4 < g.N) {                 // N % 4 == 0: a float4 is inside or outside as a whole
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int row = q * 8 + j;
+                if (row < mrem)
+                  *reinterpret_cast<float4*>(out + (long long)row * ld + c4) =
+                      *reinterpret_cast<const float4*>(tile + row * BF + c4);
+              }
+            }
+          } else if (n < g.N) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < mrem) out[(long long)i * ld + f] = __uint_as_float(r[i]) + bias;
+          }
+        } else if (MODE == TC_SWIGLU) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __uint_as_float(r[i]);
             const float other = __shfl_xor_sync(0xffffffffu, v, 1);   // (gate, up) sit in adjacent lanes
-            if (m < cnt && !(lane & 1) && n + 1 < g.N)
-              store_out<float>(g.C, crow * g.ldc + (n >> 1), silu_ref(v) * other, g.c_bf16);
-          } else if (m < cnt && n < g.N) {
-            if (g.epi == EPI_ADD) reinterpret_cast<float*>(g.C)[crow * g.ldc + n] += v;
-            else store_out<float>(g.C, crow * g.ldc + n, v + (g.bias ? g.bias[n] : 0.f), g.c_bf16);
+            if (i < mrem && !(lane & 1) && n + 1 < g.N)
+              store_out<float>(g.C, (long long)(row0 + m0 + i) * g.ldc + (n >> 1), silu_ref(v) * other, g.c_bf16);
+          }
+        } else if (MODE == TC_ADD) {
+          if (n < g.N) {
+            float* dst = reinterpret_cast<float*>(g.C) + (long long)(row0 + m0) * g.ldc + n;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < mrem) dst[(long long)i * g.ldc] += __uint_as_float(r[i]);
+          }
+        } else {
+          if (n < g.N) {
+            const float bias = g.bias ? g.bias[n] : 0.f;
+            const long long at = (long long)(row0 + m0) * g.ldc + n;
+            if (g.c_bf16) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C) + at;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < mrem) dst[(long long)i * g.ldc] = __float2bfloat16_rn(__uint_as_float(r[i]) + bias);
+            } else {
+              float* dst = reinterpret_cast<float*>(g.C) + at;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < mrem) dst[(long long)i * g.ldc] = __uint_as_float(r[i]) + bias;
+            }
           }
         }
       }
     }
+    if (tr && threadIdx.x == 64) tr[5] = clock_now();     // this warp's stores issued
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (tr && threadIdx.x == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    tr[7] = (long long)ns;
+  }
   if (s_error) {
     // give copies and MMAs that may still be in flight time to land before shared memory and TMEM are released
     if (threadIdx.x == 0 && g.error_flag) atomicExch(g.error_flag, 1);
@@ -284,6 +397,7 @@ struct TcPlan {
   float* partial = nullptr;      // caller-provided workspace for split-K partials
   long long rows_total = 0;      // rows addressed in C (all segments)
   int* error_flag = nullptr;
+  long long* trace = nullptr;    // device buffer [CTAs][8] for phase stamps, or null
 };
 
 // Supported: bf16 operands, K-major, 16-byte aligned rows, tokens <= 256, A rows contiguous (no gather).
@@ -322,14 +436,25 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   a.partial = (gy > 1 || plan.force_partial) ? plan.partial : nullptr;
   a.partial_stride = plan.rows_total * (long long)g.N;
   a.error_flag = plan.error_flag;
+  a.trace = plan.trace;
   if ((gy > 1 || plan.force_partial) && !plan.partial) return vn_fail(ctx, VN_ERR_INVALID, "split-K needs a workspace");
   const size_t smem = stage_bytes * stages + 1024;
+  const int mode = a.partial ? TC_PARTIAL : g.epi == EPI_SWIGLU ? TC_SWIGLU : g.epi == EPI_ADD ? TC_ADD : TC_STORE;
   static unsigned long long attr_set = 0;
   if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
-    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_PARTIAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
     attr_set |= 1ull << (ctx->device & 63);
   }
   dim3 grid(ceil_div(g.N, BF), gy, g.nseg);
-  VN_LAUNCH_NAMED(ctx, g.tag ? g.tag : "gemm_tc_kernel", gemm_tc_kernel, grid, TC_THREADS, smem, tm_w, tm_x, a);
+  const char* name = g.tag ? g.tag : "gemm_tc_kernel";
+  switch (mode) {
+    case TC_PARTIAL: VN_LAUNCH_PDL_NAMED(ctx, name, gemm_tc_kernel<TC_PARTIAL>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_SWIGLU:  VN_LAUNCH_PDL_NAMED(ctx, name, gemm_tc_kernel<TC_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_ADD:     VN_LAUNCH_PDL_NAMED(ctx, name, gemm_tc_kernel<TC_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    default:         VN_LAUNCH_PDL_NAMED(ctx, name, gemm_tc_kernel<TC_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+  }
   return VN_OK;
 }

@@ -252,6 +252,7 @@ int32_t ensure_rows(vn_model* m, int M) {
     if (!m->expert_count) {
       const size_t ne = (size_t)c.P * c.E;
       TRY(dev_alloc(ctx, (void**)&m->expert_count, ne * 4));
+      VN_CUDA(ctx, cudaMemsetAsync(m->expert_count, 0, ne * 4, ctx->stream));
       TRY(dev_alloc(ctx, (void**)&m->expert_off, ne * 4));
       TRY(dev_alloc(ctx, (void**)&m->expert_cur, ne * 4));
     }
@@ -361,6 +362,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
       pick(g, L.e_down, L.q[5], L.qs[5], D);
       TRY(linear(m, g));
       VN_LAUNCH(ctx, mod_combine_kernel, M, 256, 0, m->x, m->y, m->slot_pos, m->slot_w, m->part_w, D, c.P, c.top_k);
+      VN_CUDA(ctx, cudaMemsetAsync(m->expert_count, 0, ne * 4, ctx->stream));   // zero between forwards
     }
   }
   // final norm + head on every row, or on the last position of every sequence
@@ -435,9 +437,10 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
   TcPlan direct;
   TRY(ensure_partial(m, 1024));
   direct.error_flag = m->tc_error;
-  VN_LAUNCH(ctx, embed_kernel<T>, M, 128, 0, (const long long*)tokens, (const T*)m->emb, m->x, D, c.vocab, emb_scale,
+  // expert_count is zero between forwards: the combine kernel of every MoD layer leaves it so
+  VN_LAUNCH_PDL(ctx, embed_kernel<T>, M, 128, 0, (const long long*)tokens, (const T*)m->emb, m->x, D, c.vocab, emb_scale,
             m->status);
-  VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, m->layers[0].norm1, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
+  VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, m->layers[0].norm1, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
   for (int li = 0; li < c.n_layer; ++li) {
     Layer& L = m->layers[li];
     const bool mod = L.kind == 1;
@@ -447,7 +450,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     // ---- attention block
     g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.M = M; g.N = qkv_ld; g.K = D; g.tag = "gemm_qkv";
     TRY(tc_partial(m, g, cap, M, &sp));
-    VN_LAUNCH(ctx, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld, m->qkv,
+    VN_LAUNCH_PDL(ctx, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld, m->qkv,
               m->rope_cos, m->rope_sin, kv->lens, tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[li],
               (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
     AttnArgs a;
@@ -468,7 +471,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     g = GemmArgs();
     g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.M = M; g.N = D; g.K = H * hd; g.tag = "gemm_proj";
     TRY(tc_partial(m, g, cap, M, &sp));
-    VN_LAUNCH(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, L.norm2, (T*)m->h,
+    VN_LAUNCH_PDL(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, L.norm2, (T*)m->h,
               mod ? m->h32 : (float*)nullptr, D, 1e-6f);
     // ---- feed-forward block
     const float* next_norm = last ? nullptr : m->layers[li + 1].norm1;
@@ -479,26 +482,25 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       TRY(tc_partial(m, g, cap, M, &sp));
       {
         const long long pairs = (long long)M * c.mlp_hidden;
-        VN_LAUNCH(ctx, splitk_swiglu_kernel<T>, (unsigned)ceil_div(pairs, 256ll), 256, 0, m->partial, sp,
+        VN_LAUNCH_PDL(ctx, splitk_swiglu_kernel<T>, (unsigned)ceil_div(pairs, 256ll), 256, 0, m->partial, sp,
                   (long long)M * 2 * c.mlp_hidden, (T*)m->act, 2 * c.mlp_hidden, pairs);
       }
       g = GemmArgs();
       g.A = m->act; g.lda = c.mlp_hidden; g.W = L.w_down; g.ldw = c.mlp_hidden; g.M = M; g.N = D; g.K = c.mlp_hidden;
       g.tag = "gemm_down";
       TRY(tc_partial(m, g, cap, M, &sp));
-      VN_LAUNCH(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm, (T*)m->h,
+      VN_LAUNCH_PDL(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm, (T*)m->h,
                 (float*)nullptr, D, 1e-6f);
     } else {
       const int ne = c.P * c.E, S = c.P * c.top_k, eh = c.expert_hidden;
-      VN_CUDA(ctx, cudaMemsetAsync(m->expert_count, 0, ne * 4, ctx->stream));
       RouteArgs r;
       r.h = m->h32; r.gates = L.router; r.slot_expert = m->slot_expert; r.slot_w = m->slot_w; r.part_w = m->part_w;
       r.expert_count = m->expert_count; r.M = M; r.D = D; r.P = c.P; r.E = c.E; r.top_k = c.top_k;
-      VN_LAUNCH(ctx, mod_route_kernel, M, 128, 0, r);
-      VN_LAUNCH(ctx, mod_offsets_kernel, 1, 32, 0, m->expert_count, m->expert_off, m->expert_cur, ne);
-      VN_LAUNCH(ctx, mod_scatter_kernel, ceil_div(M * S, 256), 256, 0, m->slot_expert, m->expert_off, m->expert_cur,
+      VN_LAUNCH_PDL(ctx, mod_route_kernel, M, 128, 0, r);
+      VN_LAUNCH_PDL(ctx, mod_offsets_kernel, 1, 32, 0, m->expert_count, m->expert_off, m->expert_cur, ne);
+      VN_LAUNCH_PDL(ctx, mod_scatter_kernel, ceil_div(M * S, 256), 256, 0, m->slot_expert, m->expert_off, m->expert_cur,
                 m->sorted_row, m->slot_pos, M * S, S);
-      VN_LAUNCH(ctx, gather_sorted_kernel<T>, M * S, 128, 0, (const T*)m->h, m->sorted_row, (T*)m->hs, D);
+      VN_LAUNCH_PDL(ctx, gather_sorted_kernel<T>, M * S, 128, 0, (const T*)m->h, m->sorted_row, (T*)m->hs, D);
       g = GemmArgs();
       g.A = m->hs; g.lda = D; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
       g.C = m->act; g.ldc = eh; g.M = M; g.N = 2 * eh; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = 1;
@@ -509,15 +511,15 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.M = M; g.N = D; g.K = eh; g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne;
       g.tag = "gemm_expert_down";
       TRY(tc_partial(m, g, (long long)M * S, (long long)M * S, &sp));
-      VN_LAUNCH(ctx, mod_combine_split_kernel, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
-                m->slot_w, m->part_w, D, c.P, c.top_k);
+      VN_LAUNCH_PDL(ctx, mod_combine_split_kernel, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
+                m->slot_w, m->part_w, D, c.P, c.top_k, m->expert_count, ne);
       if (next_norm)
-        VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
+        VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
     }
   }
   const int rows_out = last_only ? B : M;
   const int row_mul = last_only ? Tn : 1, row_add = last_only ? Tn - 1 : 0;
-  VN_LAUNCH(ctx, rmsnorm_kernel<T>, rows_out, 256, 0, m->x, m->norm_f, (T*)m->h, out_hidden, row_mul, row_add, D, 1e-6f);
+  VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, rows_out, 256, 0, m->x, m->norm_f, (T*)m->h, out_hidden, row_mul, row_add, D, 1e-6f);
   if (out_logits) {
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = m->head; g.ldw = D; g.C = out_logits; g.ldc = c.vocab; g.M = rows_out; g.N = c.vocab;
@@ -933,7 +935,7 @@ int32_t vn_kv_commit(vn_kv* kv, int32_t n_new, const int32_t* keep_idx_dev, int3
                 n_keep_dev, keep_add, n_new, kv->max_seq, row_elems);
     }
   }
-  VN_LAUNCH(ctx, kv_advance_kernel, ceil_div(B, 128), 128, 0, kv->lens, n_keep_dev, keep_add, n_new, kv->max_seq, B);
+  VN_LAUNCH_PDL(ctx, kv_advance_kernel, ceil_div(B, 128), 128, 0, kv->lens, n_keep_dev, keep_add, n_new, kv->max_seq, B);
   for (int b = 0; b < B; ++b) kv->len_ub[b] = std::min(kv->len_ub[b] + n_new, kv->max_seq);
   return VN_OK;
 }

@@ -27,6 +27,8 @@ __global__ void convert_rows_kernel(const float* __restrict__ src, T* __restrict
 template <typename T>
 __global__ void embed_kernel(const long long* __restrict__ tokens, const T* __restrict__ emb, float* __restrict__ x,
                              int D, int V, float scale, int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   long long tok = tokens[row];
   if (tok < 0 || tok >= V) {  // record and clamp: never read outside the table
@@ -42,6 +44,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                       T* __restrict__ y, float* __restrict__ y32,
                                                       int row_mul, int row_add, int D, float eps) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sm[8];
   const long long src = (long long)blockIdx.x * row_mul + row_add;   // e.g. the last position of every sequence
   const float* xr = x + src * D;
@@ -318,6 +322,8 @@ struct RouteArgs {
 };
 
 __global__ void __launch_bounds__(128) mod_route_kernel(RouteArgs r) {
+  pdl_trigger();
+  pdl_wait();
   // one CTA per token: the 4 warps split the gate rows, warp 0 then selects
   __shared__ float lg[64];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -389,6 +395,8 @@ __global__ void __launch_bounds__(128) mod_route_kernel(RouteArgs r) {
 // exclusive prefix over the expert counts; resets the fill cursors
 __global__ void mod_offsets_kernel(const int* __restrict__ count, int* __restrict__ offset, int* __restrict__ cursor,
                                    int n_expert) {
+  pdl_trigger();
+  pdl_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     int acc = 0;
     for (int e = 0; e < n_expert; ++e) { offset[e] = acc; acc += count[e]; cursor[e] = 0; }
@@ -399,6 +407,8 @@ __global__ void mod_offsets_kernel(const int* __restrict__ count, int* __restric
 __global__ void mod_scatter_kernel(const int* __restrict__ slot_expert, const int* __restrict__ offset,
                                    int* __restrict__ cursor, int* __restrict__ sorted_row, int* __restrict__ slot_pos,
                                    int n_slots_total, int S) {
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_slots_total) return;
   const int e = slot_expert[i];
@@ -454,6 +464,8 @@ __global__ void kv_commit_kernel(T* const* __restrict__ planes, const int* __res
 }
 
 __global__ void kv_advance_kernel(int* __restrict__ lens, const int* __restrict__ n_keep, int keep_add, int n_new, int max_seq, int B) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   int nk = n_keep[b] + keep_add;
@@ -477,6 +489,8 @@ __global__ void __launch_bounds__(256) splitk_add_norm_kernel(const float* __res
                                                               long long pstride, float* __restrict__ x,
                                                               const float* __restrict__ norm_w, T* __restrict__ y,
                                                               float* __restrict__ y32, int D, float eps) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sm[8];
   const long long row = blockIdx.x;
   float4 v[2];
@@ -536,6 +550,8 @@ __global__ void splitk_store_kernel(const float* __restrict__ partial, int split
 template <typename T>
 __global__ void splitk_swiglu_kernel(const float* __restrict__ partial, int splits, long long pstride,
                                      T* __restrict__ act, int N, long long total_pairs) {
+  pdl_trigger();
+  pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total_pairs) return;
   const int half = N / 2;
@@ -553,6 +569,8 @@ __global__ void splitk_swiglu_kernel(const float* __restrict__ partial, int spli
 template <typename T>
 __global__ void gather_sorted_kernel(const T* __restrict__ src, const int* __restrict__ sorted_row, T* __restrict__ dst,
                                      int D) {
+  pdl_trigger();
+  pdl_wait();
   const long long s = sorted_row[blockIdx.x];
   const uint4* a = reinterpret_cast<const uint4*>(src + s * D);
   uint4* b = reinterpret_cast<uint4*>(dst + (long long)blockIdx.x * D);
@@ -566,7 +584,13 @@ __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restric
                                                                 const int* __restrict__ slot_pos,
                                                                 const float* __restrict__ slot_w,
                                                                 const float* __restrict__ part_w, int D, int P,
-                                                                int top_k) {
+                                                                int top_k, int* __restrict__ zero_counts,
+                                                                int n_zero) {
+  pdl_trigger();
+  pdl_wait();
+  // the expert GEMMs were the last readers of the per-expert counts: leave them at zero for the next router
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero_counts[i] = 0;
   __shared__ long long s_at[64];
   __shared__ float s_w[64];
   const int row = blockIdx.x;
@@ -614,6 +638,8 @@ __global__ void __launch_bounds__(256) qkv_finalize_kernel(const float* __restri
                                                            T* __restrict__ kc, T* __restrict__ vc, int Tn, int H,
                                                            int n_kv, int hd, int max_seq, int use_rope, int rope_rows,
                                                            int slot_offset) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float s_row[];   // (H + 2 n_kv) * hd floats
   const int row = blockIdx.x, b = row / Tn, t = row % Tn;
   const int ld = (H + 2 * n_kv) * hd;
