@@ -442,70 +442,138 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* __rest
   __shared__ int s_need, s_ncand, s_done, s_nout, s_base;
   if (tid == 0) { s_prefix = 0; s_mask = 0; s_need = want; s_ncand = 0; s_done = 0; s_nout = 0; s_base = 0; s_kth = 0; }
   __syncthreads();
-  for (int level = 0; level < 3; ++level) {
-    const int sh = level == 0 ? 21 : (level == 1 ? 10 : 0);
-    const uint32_t nb = level == 2 ? 1024u : 2048u;
-    for (int i = tid; i < 2048; i += nt) hist[i] = 0;
+  // ---- bound pass.  Groups of four threads take the maximum of the entries they read; the want-th largest
+  // of the 256 group maxima is a lower bound of the want-th largest entry (those maxima are want distinct
+  // entries), so everything kept lies at or above it.  On logits this leaves a few more than want candidates
+  // after one read of the slice and no histogram; adversarial orders or heavy ties overflow the candidate
+  // buffer and take the radix select below.
+  __shared__ uint32_t s_bmax[256];
+  __shared__ uint32_t s_lo;
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+  const int V4 = vec ? (V >> 2) : 0;
+  const float4* row4 = reinterpret_cast<const float4*>(row);
+  {
+    float tmax = -CUDART_INF_F;
+    int i = tid;
+    for (; i + 3 * nt < V4; i += 4 * nt) {
+      const float4 a0 = __ldg(row4 + i), a1 = __ldg(row4 + i + nt), a2 = __ldg(row4 + i + 2 * nt),
+                   a3 = __ldg(row4 + i + 3 * nt);
+      tmax = fmaxf(tmax, fmaxf(fmaxf(fmaxf(a0.x, a0.y), fmaxf(a0.z, a0.w)), fmaxf(fmaxf(a1.x, a1.y), fmaxf(a1.z, a1.w))));
+      tmax = fmaxf(tmax, fmaxf(fmaxf(fmaxf(a2.x, a2.y), fmaxf(a2.z, a2.w)), fmaxf(fmaxf(a3.x, a3.y), fmaxf(a3.z, a3.w))));
+    }
+    for (; i < V4; i += nt) {
+      const float4 a0 = __ldg(row4 + i);
+      tmax = fmaxf(tmax, fmaxf(fmaxf(a0.x, a0.y), fmaxf(a0.z, a0.w)));
+    }
+    for (int j = (V4 << 2) + tid; j < V; j += nt) tmax = fmaxf(tmax, row[j]);
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    if (tid == 0) s_lo = 0u;
+    if ((tid & 3) == 0 && (tid >> 2) < 256) s_bmax[tid >> 2] = order_key(scale ? __fdiv_rn(tmax, temp) : tmax);
     __syncthreads();
-    const uint32_t prefix = s_prefix, mask = s_mask;
-    for (int i = tid; i < V; i += nt) {
-      float x = row[i];
-      if (scale) x = __fdiv_rn(x, temp);
-      const uint32_t key = order_key(x);
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> sh) & (nb - 1)], 1u);
+    const int nb = min(nt >> 2, 256);
+    if (tid < nb) {
+      const uint32_t mine = s_bmax[tid];
+      int greater = 0, geq = 0;
+      for (int j = 0; j < nb; ++j) { const uint32_t o = s_bmax[j]; greater += o > mine; geq += o >= mine; }
+      if (greater < want && geq >= want) s_lo = mine;   // every writer holds the same key
     }
     __syncthreads();
-    {
-      // digit of the threshold: the largest d with (keys in digits > d) < need <= (keys in digits >= d).
-      // Block-wide suffix sums over the histogram; thread t owns digits 2t and 2t+1 (launched with 1024 threads).
-      const int need = s_need;  // how many of the largest keys of this prefix class are kept
-      const int lane = tid & 31, warp = tid >> 5;
-      const int h0 = (2 * tid < (int)nb) ? (int)hist[2 * tid] : 0;
-      const int h1 = (2 * tid + 1 < (int)nb) ? (int)hist[2 * tid + 1] : 0;
-      const int local = h0 + h1;
-      int incl = local;       // inclusive suffix sum inside the warp (lanes above me)
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_down_sync(0xffffffffu, incl, o);
-        if (lane + o < 32) incl += v;
-      }
-      if (lane == 0) wcount[warp] = incl;   // warp total
-      __syncthreads();
-      int above_warps = 0;
-      for (int w = warp + 1; w < (nt >> 5); ++w) above_warps += wcount[w];
-      const int above_me = above_warps + incl - local;   // keys in digits owned by threads after me
-      if (need > 0 && above_me < need && need <= above_me + local) {
-        uint32_t digit; int above;
-        if (above_me + h1 >= need) { digit = 2 * tid + 1; above = above_me; }
-        else { digit = 2 * tid; above = above_me + h1; }
-        s_need = need - above;                 // still needed from inside the digit class
-        s_prefix = prefix | (digit << sh);
-        s_mask = mask | ((nb - 1) << sh);
-        const int ncand = want - (need - above) + (int)hist[digit];  // keys >= the smallest key of the class
-        s_ncand = ncand;
-        s_done = ncand <= CAND_MAX ? 2 : (level == 2 ? 1 : 0);
-      }
-      if (need <= 0 && tid == 0) { s_ncand = 0; s_done = 2; s_prefix = 0xFFFFFFFFu; }   // empty slice
-    }
-    __syncthreads();
-    if (s_done) break;
   }
-  TopkRow* o = out + blockIdx.x;
-  if (s_done == 2) {
-    const uint32_t lo = s_prefix;
+  // candidates: every entry with key >= lo (slot order is arbitrary, the select below ranks them)
+  auto gather = [&](uint32_t lo) {
+    int i = tid;
+    for (; i < V4; i += nt) {
+      const float4 a = __ldg(row4 + i);
+      const float xs[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t key = order_key(scale ? __fdiv_rn(xs[e], temp) : xs[e]);
+        if (key >= lo) {
+          const int slot = atomicAdd(&s_ncand, 1);
+          if (slot < CAND_MAX) { c_key[slot] = key; c_tok[slot] = base0 + 4 * i + e; }
+        }
+      }
+    }
+    for (int j = (V4 << 2) + tid; j < V; j += nt) {
+      const float x = row[j];
+      const uint32_t key = order_key(scale ? __fdiv_rn(x, temp) : x);
+      if (key >= lo) {
+        const int slot = atomicAdd(&s_ncand, 1);
+        if (slot < CAND_MAX) { c_key[slot] = key; c_tok[slot] = base0 + j; }
+      }
+    }
+  };
+  bool have = false;
+  if (want > 0) {
+    gather(s_lo);
     __syncthreads();
+    have = s_ncand <= CAND_MAX;
+    __syncthreads();
+  }
+  if (!have) {
     if (tid == 0) s_ncand = 0;
     __syncthreads();
-    for (int i = tid; i < V; i += nt) {
-      float x = row[i];
-      if (scale) x = __fdiv_rn(x, temp);
-      const uint32_t key = order_key(x);
-      if (key >= lo) {
-        int slot = atomicAdd(&s_ncand, 1);
-        if (slot < CAND_MAX) { c_key[slot] = key; c_tok[slot] = base0 + i; }
+    for (int level = 0; level < 3; ++level) {
+      const int sh = level == 0 ? 21 : (level == 1 ? 10 : 0);
+      const uint32_t nb = level == 2 ? 1024u : 2048u;
+      for (int i = tid; i < 2048; i += nt) hist[i] = 0;
+      __syncthreads();
+      const uint32_t prefix = s_prefix, mask = s_mask;
+      for (int i = tid; i < V; i += nt) {
+        float x = row[i];
+        if (scale) x = __fdiv_rn(x, temp);
+        const uint32_t key = order_key(x);
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> sh) & (nb - 1)], 1u);
       }
+      __syncthreads();
+      {
+        // digit of the threshold: the largest d with (keys in digits > d) < need <= (keys in digits >= d).
+        // Block-wide suffix sums over the histogram; thread t owns digits 2t and 2t+1 (launched with 1024 threads).
+        const int need = s_need;  // how many of the largest keys of this prefix class are kept
+        const int lane = tid & 31, warp = tid >> 5;
+        const int h0 = (2 * tid < (int)nb) ? (int)hist[2 * tid] : 0;
+        const int h1 = (2 * tid + 1 < (int)nb) ? (int)hist[2 * tid + 1] : 0;
+        const int local = h0 + h1;
+        int incl = local;       // inclusive suffix sum inside the warp (lanes above me)
+  #pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_down_sync(0xffffffffu, incl, o);
+          if (lane + o < 32) incl += v;
+        }
+        if (lane == 0) wcount[warp] = incl;   // warp total
+        __syncthreads();
+        int above_warps = 0;
+        for (int w = warp + 1; w < (nt >> 5); ++w) above_warps += wcount[w];
+        const int above_me = above_warps + incl - local;   // keys in digits owned by threads after me
+        if (need > 0 && above_me < need && need <= above_me + local) {
+          uint32_t digit; int above;
+          if (above_me + h1 >= need) { digit = 2 * tid + 1; above = above_me; }
+          else { digit = 2 * tid; above = above_me + h1; }
+          s_need = need - above;                 // still needed from inside the digit class
+          s_prefix = prefix | (digit << sh);
+          s_mask = mask | ((nb - 1) << sh);
+          const int ncand = want - (need - above) + (int)hist[digit];  // keys >= the smallest key of the class
+          s_ncand = ncand;
+          s_done = ncand <= CAND_MAX ? 2 : (level == 2 ? 1 : 0);
+        }
+        if (need <= 0 && tid == 0) { s_ncand = 0; s_done = 2; s_prefix = 0xFFFFFFFFu; }   // empty slice
+      }
+      __syncthreads();
+      if (s_done) break;
     }
-    __syncthreads();
+    if (s_done == 2) {
+      const uint32_t lo = s_prefix;
+      __syncthreads();
+      if (tid == 0) s_ncand = 0;
+      __syncthreads();
+      gather(lo);
+      __syncthreads();
+      have = true;
+    }
+  }
+  TopkRow* o = out + blockIdx.x;
+  if (have) {
     const int nc = min(s_ncand, CAND_MAX);
     // exact k-th largest among the candidates by rank counting (nc is small)
     for (int i = tid; i < nc; i += nt) {

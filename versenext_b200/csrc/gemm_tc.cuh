@@ -34,7 +34,7 @@ struct TcArgs {
   int M, N, K;             // tokens (per segment: upper bound), features, reduction
   int ntok;                // UMMA N: tokens rounded up to 16
   int x_box;               // token rows per TMA box: ntok (one box) for a dense block, 16 in segmented mode
-  int stages;
+  unsigned smem_budget;    // bytes of stage memory behind the 1024-byte aligned base
   int kb_per_split;        // k blocks (of 64) per blockIdx.y
   int epi, c_bf16;
   const int* seg_off;      // segmented mode (blockIdx.z = segment)
@@ -161,9 +161,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 
   // stage buffers: 1024-byte aligned (swizzle atom), weight tile then token tile
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const unsigned w_bytes = BF * BK * 2, x_bytes = (unsigned)g.ntok * BK * 2;
+  // a stage holds the weight tile and the token rows this CTA really has, so a short segment gets more
+  // stages out of the same shared memory
+  const unsigned w_bytes = BF * BK * 2, x_bytes = (unsigned)cnt16 * BK * 2;
   const unsigned stage_bytes = w_bytes + x_bytes;
-  const int S = g.stages;
+  int S = (int)(g.smem_budget / stage_bytes);
+  S = S > 8 ? 8 : S;
+  S = S > nkb ? (nkb < 2 ? 2 : nkb) : S;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
@@ -268,6 +272,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const bool vec_ok = MODE == TC_PARTIAL
                               ? (g.N % 4 == 0 && ((uintptr_t)g.partial & 15) == 0)
                               : (g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 15) == 0);
+      // paired outputs: rows of C start on an 8-byte boundary and N covers whole groups of four columns
+      const bool swi_ok = MODE == TC_SWIGLU && g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 7) == 0;
       for (int ch = 0; ch < nchunk; ++ch) {
         unsigned r[32];
         tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(ch * 32), r);
@@ -303,12 +309,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               if (i < mrem) out[(long long)i * ld + f] = __uint_as_float(r[i]) + bias;
           }
         } else if (MODE == TC_SWIGLU) {
+          // (gate, up) sit in adjacent columns: stage the fp32 tile, then every lane turns two pairs of a token
+          // row into two outputs, so that a warp stores 64 contiguous outputs of a row at once
+          if (swi_ok) {
+            float* tile = reinterpret_cast<float*>(base) + (ch & 1) * (32 * BF);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = __uint_as_float(r[i]);
-            const float other = __shfl_xor_sync(0xffffffffu, v, 1);   // (gate, up) sit in adjacent lanes
-            if (i < mrem && !(lane & 1) && n + 1 < g.N)
-              store_out<float>(g.C, (long long)(row0 + m0 + i) * g.ldc + (n >> 1), silu_ref(v) * other, g.c_bf16);
+            for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int c4 = lane * 4;
+            if (n0 + c4 + 3 < g.N) {
+#pragma unroll 2
+              for (int j = 0; j < 8; ++j) {
+                const int row = q * 8 + j;
+                if (row < mrem) {
+                  const float4 v = *reinterpret_cast<const float4*>(tile + row * BF + c4);
+                  const float o0 = silu_ref(v.x) * v.y, o1 = silu_ref(v.z) * v.w;
+                  const long long at = (long long)(row0 + m0 + row) * g.ldc + ((n0 + c4) >> 1);
+                  if (g.c_bf16)
+                    *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(g.C) + at) =
+                        __floats2bfloat162_rn(o0, o1);
+                  else
+                    *reinterpret_cast<float2*>(reinterpret_cast<float*>(g.C) + at) = make_float2(o0, o1);
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float v = __uint_as_float(r[i]);
+              const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+              if (i < mrem && !(lane & 1) && n + 1 < g.N)
+                store_out<float>(g.C, (long long)(row0 + m0 + i) * g.ldc + (n >> 1), silu_ref(v) * other, g.c_bf16);
+            }
           }
         } else if (MODE == TC_ADD) {
           if (n < g.N) {
@@ -423,11 +455,12 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   const int nkb = (g.K + BK - 1) / BK;
   const int splits = std::max(1, std::min(plan.splits, nkb));
   a.kb_per_split = (nkb + splits - 1) / splits;
-  // at most ~108 KB of stages per CTA so that two CTAs share an SM: one drains its accumulator while the
-  // other streams
-  int stages = (int)std::min<size_t>(6, (108 * 1024) / stage_bytes);
-  stages = std::max(2, std::min(stages, std::max(2, a.kb_per_split)));
-  a.stages = stages;
+  // about 108 KB of stages per CTA so that two CTAs share an SM (one drains its accumulator while the other
+  // streams); at least two stages of the largest token block, and no more than the k range needs
+  size_t budget = std::min<size_t>(108 * 1024, stage_bytes * 8);
+  budget = std::min(budget, std::max<size_t>(2, a.kb_per_split) * stage_bytes);
+  budget = std::max(budget, 2 * stage_bytes);
+  a.smem_budget = (unsigned)budget;
   a.epi = g.epi; a.c_bf16 = g.c_bf16;
   a.seg_off = g.seg_off; a.seg_cnt = g.seg_cnt;
   a.w_rows_per_seg = g.seg_cnt ? g.w_stride / g.ldw : 0;
@@ -438,7 +471,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   a.error_flag = plan.error_flag;
   a.trace = plan.trace;
   if ((gy > 1 || plan.force_partial) && !plan.partial) return vn_fail(ctx, VN_ERR_INVALID, "split-K needs a workspace");
-  const size_t smem = stage_bytes * stages + 1024;
+  const size_t smem = budget + 1024;
   const int mode = a.partial ? TC_PARTIAL : g.epi == EPI_SWIGLU ? TC_SWIGLU : g.epi == EPI_ADD ? TC_ADD : TC_STORE;
   static unsigned long long attr_set = 0;
   if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
