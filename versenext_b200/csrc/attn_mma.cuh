@@ -17,11 +17,18 @@
 
 namespace attn_detail {
 
-constexpr int AW = 8;  // warps per CTA
+constexpr int AW = 8;    // warps per CTA
+constexpr int RING = 3;  // key blocks per warp in shared memory (4 KB each)
 
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
+}
+
+__device__ __forceinline__ long long clock_stamp() {
+  long long c;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(c) :: "memory");
+  return c;
 }
 
 struct RowInfo {
@@ -36,7 +43,8 @@ template <int MODE>
 __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* __restrict__ Kb,
                                        const __nv_bfloat16* __restrict__ Vb, long long ks, int lo, int hi, int len,
                                        const RowInfo (&row)[2], const unsigned (&qf)[4][4], const int* s_depth,
-                                       int warp, int lane, float (&o)[8][4], float (&m)[2], float (&l)[2]) {
+                                       int warp, int lane, unsigned char* ring, float (&o)[8][4], float (&m)[2],
+                                       float (&l)[2]) {
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int j = 0; j < 8; ++j)
@@ -45,26 +53,55 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
   m[0] = m[1] = -CUDART_INF_F;
   l[0] = l[1] = 0.f;
   const int nblk = hi > lo ? (hi - lo + 15) >> 4 : 0;
-  for (int blk = warp; blk < nblk; blk += AW) {
-    const int j0 = lo + blk * 16;
-    // ---- K: rows j0 + 8i + g, dims 16t .. 16t+15
+  int pos_max = max(row[0].pos, row[1].pos);     // latest query position of the tile
+#pragma unroll
+  for (int o_ = 16; o_ > 0; o_ >>= 1) pos_max = max(pos_max, __shfl_xor_sync(0xffffffffu, pos_max, o_));
+  // This warp's blocks (warp, warp + AW, ...) stream through its own ring of RING stages in shared memory:
+  // 16 key rows of 128 bytes for K, then the same for V, 16-byte chunks XOR-swizzled with the row so that the
+  // fragment loads below are free of bank conflicts.  cp.async keeps RING - 1 blocks in flight per warp.
+  const int n_my = nblk > warp ? (nblk - warp + AW - 1) / AW : 0;
+  auto issue = [&](int it) {
+    const int j0 = lo + (warp + it * AW) * 16;
+    unsigned char* st = ring + (it % RING) * 4096;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int ci = i * 32 + lane;
+      const int r = ci >> 3, c = ci & 7;
+      int key = j0 + r;
+      key = key < hi ? key : hi - 1;
+      const int soff = r * 128 + ((c ^ (r & 7)) << 4);
+      mma_detail::cp_async16(st + soff, Kb + (long long)key * ks + c * 8, true);
+      mma_detail::cp_async16(st + 2048 + soff, Vb + (long long)key * ks + c * 8, true);
+    }
+  };
+#pragma unroll
+  for (int s = 0; s < RING - 1; ++s) {
+    if (s < n_my) issue(s);
+    mma_detail::cp_async_commit();
+  }
+  for (int it = 0; it < n_my; ++it) {
+    const int j0 = lo + (warp + it * AW) * 16;
+    mma_detail::cp_async_wait<RING - 2>();
+    __syncwarp();                                  // block `it` has landed; everyone is done with block it - 1
+    if (it + RING - 1 < n_my) issue(it + RING - 1);
+    mma_detail::cp_async_commit();
+    const unsigned char* st = ring + (it % RING) * 4096;
+    // ---- K: rows 8i + g, dims 16t .. 16t+15 (chunks 2t, 2t+1)
     unsigned kr[2][8];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      int key = j0 + 8 * i + g;
-      key = key < hi ? key : hi - 1;
-      const uint4* p = reinterpret_cast<const uint4*>(Kb + (long long)key * ks + 16 * t);
-      const uint4 u0 = p[0], u1 = p[1];
+      const unsigned char* rp = st + (8 * i + g) * 128;
+      const uint4 u0 = *reinterpret_cast<const uint4*>(rp + (((2 * t) ^ g) << 4));
+      const uint4 u1 = *reinterpret_cast<const uint4*>(rp + (((2 * t + 1) ^ g) << 4));
       kr[i][0] = u0.x; kr[i][1] = u0.y; kr[i][2] = u0.z; kr[i][3] = u0.w;
       kr[i][4] = u1.x; kr[i][5] = u1.y; kr[i][6] = u1.z; kr[i][7] = u1.w;
     }
-    // ---- V: rows j0 + {2t, 2t+1, 2t+8, 2t+9}, dims 8g .. 8g+7
+    // ---- V: rows {2t, 2t+1, 2t+8, 2t+9}, dims 8g .. 8g+7 (chunk g)
     unsigned vr[4][4];
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
-      int key = j0 + 2 * t + (x & 1) + ((x >> 1) << 3);
-      key = key < hi ? key : hi - 1;
-      const uint4 u = *reinterpret_cast<const uint4*>(Vb + (long long)key * ks + 8 * g);
+      const int r = 2 * t + (x & 1) + ((x >> 1) << 3);
+      const uint4 u = *reinterpret_cast<const uint4*>(st + 2048 + r * 128 + ((g ^ (r & 7)) << 4));
       vr[x][0] = u.x; vr[x][1] = u.y; vr[x][2] = u.z; vr[x][3] = u.w;
     }
     // ---- S = Q K^T for two tiles of 8 keys
@@ -78,27 +115,36 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
         mma_detail::mma_bf16(c[i], qf[s], bfrag);
       }
     }
-    // ---- scale, bias, mask
+    // ---- scale, bias, mask.  A block of committed keys that every row of the tile sees needs no mask
+    // (rows beyond R compute on real keys too; their result is never stored)
+    const bool plain = j0 + 16 <= hi && (MODE == 1 || (MODE == 0 && j0 + 16 <= len && pos_max - j0 < a.window));
+    if (plain) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < 2; ++i)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = j0 + 8 * i + 2 * t + (e & 1);
-        const RowInfo& r = row[e >> 1];
-        bool vis = r.valid && key < hi;
-        float sc = c[i][e] * a.scale;
-        if (MODE == 0 || MODE == 2) {
-          int kpos = key;
-          if (key >= len) {
-            const int n = key - len;
-            kpos = len + (s_depth ? s_depth[n < 64 ? n : 63] : n);
-            vis = vis && (a.anc ? ((r.anc >> n) & 1ull) != 0 : n <= r.tq) && kpos <= r.pos;
+        for (int e = 0; e < 4; ++e) c[i][e] *= a.scale;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = j0 + 8 * i + 2 * t + (e & 1);
+          const RowInfo& r = row[e >> 1];
+          bool vis = r.valid && key < hi;
+          float sc = c[i][e] * a.scale;
+          if (MODE == 0 || MODE == 2) {
+            int kpos = key;
+            if (key >= len) {
+              const int n = key - len;
+              kpos = len + (s_depth ? s_depth[n < 64 ? n : 63] : n);
+              vis = vis && (a.anc ? ((r.anc >> n) & 1ull) != 0 : n <= r.tq) && kpos <= r.pos;
+            }
+            if (MODE == 0) vis = vis && (r.pos - kpos) < a.window;
+            else sc -= r.slope * (float)(r.pos - kpos);
           }
-          if (MODE == 0) vis = vis && (r.pos - kpos) < a.window;
-          else sc -= r.slope * (float)(r.pos - kpos);
+          c[i][e] = vis ? sc : -CUDART_INF_F;
         }
-        c[i][e] = vis ? sc : -CUDART_INF_F;
-      }
+    }
     // ---- online softmax (rows g and g+8; a row lives in the 4 lanes of a quad)
     float pr[2][4];
 #pragma unroll
@@ -119,8 +165,10 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
       }
       l[h] = l[h] * corr + pr[0][2 * h] + pr[0][2 * h + 1] + pr[1][2 * h] + pr[1][2 * h + 1];
       m[h] = mn;
+      if (corr != 1.f) {   // the running maximum moved: rare after the first blocks
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { o[j][2 * h] *= corr; o[j][2 * h + 1] *= corr; }
+        for (int j = 0; j < 8; ++j) { o[j][2 * h] *= corr; o[j][2 * h + 1] *= corr; }
+      }
     }
     // ---- O += P V
     const unsigned pa[4] = {pack_bf16(pr[0][0], pr[0][1]), pack_bf16(pr[0][2], pr[0][3]),
@@ -133,6 +181,7 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
       mma_detail::mma_bf16(o[j], pa, bfrag);
     }
   }
+  __syncwarp();   // the ring is reused by the caller
   // row sums live spread over the quad
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -142,7 +191,9 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
 }
 
 __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a) {
-  __shared__ float sO[AW][16][64];
+  // per warp: a ring of RING key blocks; after a path's keys the first 4 KB of the warp's ring hold its
+  // partial output (16 rows x 64 dims fp32, 16-byte chunks swizzled) for the merge across warps
+  extern __shared__ __align__(128) unsigned char attn_smem[];
   __shared__ float sM[AW][16], sL[AW][16];
   __shared__ int s_depth[64];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -150,6 +201,8 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
   const int n_rep = a.H / a.n_kv;
   const int R = a.Tn * n_rep;
   const int tile0 = blockIdx.y * 16;
+  long long* tr = a.trace ? a.trace + 8ll * (blockIdx.x + (long long)gridDim.x * blockIdx.y) : nullptr;
+  if (tr && tid == 0) tr[0] = clock_stamp();
   pdl_trigger();
   pdl_wait();
   const int len = a.lens[b] + a.slot_offset;
@@ -206,25 +259,35 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
   float fin[4] = {0.f, 0.f, 0.f, 0.f};
   const int mrow = tid >> 4, mcol = (tid & 15) * 4;
   const bool use_c = a.use_alibi && (a.anc ? true : (len + a.Tn) <= a.alibi_max);
+  unsigned char* ring = attn_smem + warp * (RING * 4096);
 
+  if (tr && tid == 0) tr[1] = clock_stamp();     // row setup and Q fragments done
   for (int path = 0; path < 3; ++path) {
     if (path == 2 && !use_c) break;
     float o[8][4], m[2], l[2];
     if (path == 0) {
       const int lo = max(0, pos_min - a.window + 1);
-      attend<0>(a, Kc, Vc, ks, lo, hi_new, len, row, qf, depth, warp, lane, o, m, l);
+      attend<0>(a, Kc, Vc, ks, lo, hi_new, len, row, qf, depth, warp, lane, ring, o, m, l);
     } else if (path == 1) {
-      attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf, depth, warp, lane, o, m, l);
+      attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf, depth, warp, lane, ring, o, m, l);
     } else {
-      attend<2>(a, Kc, Vc, ks, 0, hi_new, len, row, qf, depth, warp, lane, o, m, l);
+      attend<2>(a, Kc, Vc, ks, 0, hi_new, len, row, qf, depth, warp, lane, ring, o, m, l);
     }
-    // each warp parks its partial result; column n of tile j is output dim 8n + j
+    if (tr && tid == 0 && path < 3) tr[2 + 2 * path] = clock_stamp();   // this warp's keys done
+    // each warp parks its partial result.  Column n of tile j is output dim 8n + j, so thread (g, t) holds dims
+    // 16t .. 16t+15 of rows g and g + 8: four 16-byte chunks per row, chunk c stored at c ^ bit3(c) ^ 2*(row & 1),
+    // which spreads the eight lanes of a quarter warp over all banks for the stores here and the loads below
+    {
+      float4* mine = reinterpret_cast<float4*>(ring);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      sO[warp][g][16 * t + j] = o[j][0];
-      sO[warp][g][16 * t + 8 + j] = o[j][1];
-      sO[warp][g + 8][16 * t + j] = o[j][2];
-      sO[warp][g + 8][16 * t + 8 + j] = o[j][3];
+      for (int h = 0; h < 2; ++h) {
+        const int r = g + 8 * h;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = 4 * t + k, e = 2 * h + (k >> 1), j = (k & 1) * 4;
+          mine[r * 16 + (c ^ ((c >> 3) & 1) ^ ((r & 1) << 1))] = make_float4(o[j][e], o[j + 1][e], o[j + 2][e], o[j + 3][e]);
+        }
+      }
     }
     if (t == 0) {
       sM[warp][g] = m[0]; sL[warp][g] = l[0];
@@ -243,8 +306,10 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
           if (mw == -CUDART_INF_F) continue;
           const float cw = __expf(mw - M);
           L += sL[w][mrow] * cw;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) acc[e] += sO[w][mrow][mcol + e] * cw;
+          const int c = tid & 15;
+          const float4 v = reinterpret_cast<const float4*>(attn_smem + w * (RING * 4096))[
+              mrow * 16 + (c ^ ((c >> 3) & 1) ^ ((mrow & 1) << 1))];
+          acc[0] += v.x * cw; acc[1] += v.y * cw; acc[2] += v.z * cw; acc[3] += v.w * cw;
         }
       }
       // ALiBi path of a tree node is gated by its own T_k (position + 1 <= 1024)
@@ -261,6 +326,7 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
       }
     }
     __syncthreads();
+    if (tr && tid == 0 && path < 2) tr[3 + 2 * path] = clock_stamp();   // merge of this path done
   }
   const int r = tile0 + mrow;
   if (r < R) {
@@ -282,6 +348,13 @@ inline bool attn_mma_supported(const AttnArgs& a, bool bf16) {
 inline int32_t launch_attn_mma(vn_ctx* ctx, const AttnArgs& a, int B) {
   const int n_rep = a.H / a.n_kv;
   dim3 grid(B * a.n_kv, ceil_div(a.Tn * n_rep, 16));
-  VN_LAUNCH_PDL(ctx, attn_detail::trisparse_attn_mma_kernel, grid, attn_detail::AW * 32, 0, a);
+  const size_t smem = (size_t)attn_detail::AW * attn_detail::RING * 4096;
+  static unsigned long long attr_set = 0;
+  if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
+    VN_CUDA(ctx, cudaFuncSetAttribute(attn_detail::trisparse_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+    attr_set |= 1ull << (ctx->device & 63);
+  }
+  VN_LAUNCH_PDL(ctx, attn_detail::trisparse_attn_mma_kernel, grid, attn_detail::AW * 32, smem, a);
   return VN_OK;
 }

@@ -126,6 +126,7 @@ struct AttnArgs {
   int use_alibi, alibi_max;
   float g_a, g_b, g_c;   // sigmoid(gate_logits)
   float scale;
+  long long* trace = nullptr;   // optional [CTAs][8] cycle stamps of the tensor-core kernel's phases
 };
 
 // online-softmax state of one 8-lane group: running max, running sum, 8 output dims per lane
