@@ -492,10 +492,12 @@ def run_accept(args):
                 "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
                 "kernel_ms": dom_ms, "algorithmic_bytes": nbytes,
                 "kernel_shares": {n: v["ms"] / total_k for n, v in rep.items()}}
-    tpath = os.path.join(ROOT, "profiles", "accept_traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            roofline["traffic"] = json.load(f).get("dram_bytes_per_launch")
+    # DRAM bytes of one launch of the dominant kernel, from the ncu capture summarised in
+    # profiles/accept_stats_kernel_ncu_full.txt (dram__bytes_read.sum + dram__bytes_write.sum); it scales with
+    # the rows processed, so it is only quoted for the configuration that was captured
+    if (B, k, V) == (64, 4, 248320):
+        roofline["traffic"] = 572150784 + 4005120
+        roofline["traffic_source"] = "profiles/accept_stats_kernel_ncu_full.txt"
 
     # ---- end to end: pinned host logits -> device -> op -> host result, every step
     hp, hq, hd = ctx.pinned(p.shape, np.float32), ctx.pinned(q.shape, np.float32), ctx.pinned(draft.shape, np.int64)
