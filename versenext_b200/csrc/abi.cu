@@ -26,7 +26,7 @@ int32_t vn_ctx_create(int32_t device, vn_ctx** out) {
     return vn_fail(nullptr, VN_ERR_CUDA, "context setup: %s", cudaGetErrorString(e));
   }
   cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
-  if (const char* e = getenv("VN_PDL")) ctx->pdl = atoi(e) != 0;
+  if (const char* e = getenv("VN_PDL")) ctx->pdl = atoi(e);
   *out = ctx;
   return VN_OK;
 }

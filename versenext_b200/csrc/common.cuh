@@ -31,8 +31,10 @@ struct vn_ctx {
   bool profiling = false;
   // programmatic dependent launch: kernels launched through VN_LAUNCH_PDL may start while their predecessor
   // in the stream drains; each of them waits (pdl_wait) before it touches anything a predecessor wrote.
-  // Off unless VN_PDL=1: measured on B200 inside a captured round it was 5 % slower than plain edges.
-  bool pdl = false;
+  // Level 0 (VN_PDL=0): plain stream order.  1 (default): only the weight-streaming GEMMs, which prefetch
+  // weight tiles before they wait (+4 % rounds per second on B200).  2: every kernel that supports it (measured
+  // no better than 0: waiting CTAs of the small kernels only take up SM slots).
+  int pdl = 1;
   struct ProfRec { const char* name; cudaEvent_t a, b; };
   std::vector<ProfRec> prof;
 };
@@ -108,31 +110,33 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 #endif
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t vn_launch_pdl(vn_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                 Args&&... args) {
+inline cudaError_t vn_launch_pdl(vn_ctx* ctx, int level, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                 size_t smem, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = (ctx->pdl && !ctx->profiling) ? 1 : 0;
+  cfg.numAttrs = (ctx->pdl >= level && !ctx->profiling) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 // only for kernels that call pdl_wait() as described above
-#define VN_LAUNCH_PDL_NAMED(ctx, name, kernel, grid, block, smem, ...)                  \
+#define VN_LAUNCH_PDL_LEVEL(ctx, level, name, kernel, grid, block, smem, ...)           \
   do {                                                                                  \
     if ((ctx)->profiling) vn_prof_begin((ctx), (name));                                 \
-    cudaError_t _e = vn_launch_pdl((ctx), kernel, dim3(grid), dim3(block), (smem), __VA_ARGS__); \
+    cudaError_t _e = vn_launch_pdl((ctx), (level), kernel, dim3(grid), dim3(block), (smem), __VA_ARGS__); \
     if ((ctx)->profiling) vn_prof_end((ctx));                                           \
     (ctx)->launches++;                                                                  \
     if (_e == cudaSuccess) _e = cudaGetLastError();                                     \
     if (_e != cudaSuccess)                                                              \
       return vn_fail((ctx), VN_ERR_CUDA, "launch of %s failed: %s", (name), cudaGetErrorString(_e)); \
   } while (0)
+#define VN_LAUNCH_PDL_NAMED(ctx, name, kernel, grid, block, smem, ...) \
+  VN_LAUNCH_PDL_LEVEL(ctx, 2, name, kernel, grid, block, smem, __VA_ARGS__)
 #define VN_LAUNCH_PDL(ctx, kernel, grid, block, smem, ...) \
-  VN_LAUNCH_PDL_NAMED(ctx, #kernel, kernel, grid, block, smem, __VA_ARGS__)
+  VN_LAUNCH_PDL_LEVEL(ctx, 2, #kernel, kernel, grid, block, smem, __VA_ARGS__)
 
 int32_t vn_workspace(vn_ctx* ctx, size_t bytes, void** out);
 

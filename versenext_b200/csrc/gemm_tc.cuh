@@ -484,10 +484,10 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   dim3 grid(ceil_div(g.N, BF), gy, g.nseg);
   const char* name = g.tag ? g.tag : "gemm_tc_kernel";
   switch (mode) {
-    case TC_PARTIAL: VN_LAUNCH_PDL_NAMED(ctx, name, gemm_tc_kernel<TC_PARTIAL>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    case TC_SWIGLU:  VN_LAUNCH_PDL_NAMED(ctx, name, gemm_tc_kernel<TC_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    case TC_ADD:     VN_LAUNCH_PDL_NAMED(ctx, name, gemm_tc_kernel<TC_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    default:         VN_LAUNCH_PDL_NAMED(ctx, name, gemm_tc_kernel<TC_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_PARTIAL: VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_PARTIAL>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_SWIGLU:  VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_ADD:     VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    default:         VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
   }
   return VN_OK;
 }
