@@ -636,20 +636,25 @@ accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_
   __shared__ int s_cnt;
   const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
   const TopkRow* pr = parts + (long long)r * chunks;
+  // list lengths in one round trip (chunks <= 64), exclusive offsets by one warp
+  __shared__ int s_n[64];
+  if (tid < 64) s_n[tid] = tid < chunks ? pr[tid].n : 0;
+  if (tid == 0) { s_kth = -CUDART_INF_F; s_cnt = 0; }
+  __syncthreads();
   if (tid == 0) {
     int acc = 0;
-    for (int c = 0; c < chunks; ++c) { s_off[c] = acc; acc += pr[c].n; }
+    for (int c = 0; c < chunks; ++c) { s_off[c] = acc; acc += s_n[c]; }
     s_off[chunks] = acc < MERGE_MAX ? acc : MERGE_MAX;
-    s_kth = -CUDART_INF_F;
-    s_cnt = 0;
   }
   __syncthreads();
   const int n = s_off[chunks];
-  for (int c = 0; c < chunks; ++c)
-    for (int i = tid; i < pr[c].n; i += nt) {
-      const int at = s_off[c] + i;
-      if (at < MERGE_MAX) { s_val[at] = pr[c].val[i]; s_tok[at] = pr[c].tok[i]; }
-    }
+  for (int at = tid; at < n; at += nt) {
+    int c = 0;
+    while (c + 1 < chunks && s_off[c + 1] <= at) ++c;
+    const int i = at - s_off[c];
+    s_val[at] = pr[c].val[i];
+    s_tok[at] = pr[c].tok[i];
+  }
   __syncthreads();
   const int want = top_k < n ? top_k : n;
   for (int i = tid; i < n; i += nt) {

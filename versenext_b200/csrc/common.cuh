@@ -110,16 +110,30 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 #endif
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t vn_launch_pdl(vn_ctx* ctx, int level, void (*kernel)(KArgs...), dim3 grid, dim3 block,
-                                 size_t smem, Args&&... args) {
+inline cudaError_t vn_launch_cluster(vn_ctx* ctx, int level, int cluster_y, void (*kernel)(KArgs...), dim3 grid,
+                                     dim3 block, size_t smem, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute at[2];
+  int n = 0;
+  if (cluster_y > 1) {     // thread-block cluster along y (grid.y must be a multiple of it)
+    at[n].id = cudaLaunchAttributeClusterDimension;
+    at[n].val.clusterDim.x = 1; at[n].val.clusterDim.y = (unsigned)cluster_y; at[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (ctx->pdl >= level && !ctx->profiling) {
+    at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
   cfg.attrs = at;
-  cfg.numAttrs = (ctx->pdl >= level && !ctx->profiling) ? 1 : 0;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t vn_launch_pdl(vn_ctx* ctx, int level, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                 size_t smem, Args&&... args) {
+  return vn_launch_cluster(ctx, level, 1, kernel, grid, block, smem, static_cast<Args&&>(args)...);
 }
 
 // only for kernels that call pdl_wait() as described above
@@ -127,6 +141,17 @@ inline cudaError_t vn_launch_pdl(vn_ctx* ctx, int level, void (*kernel)(KArgs...
   do {                                                                                  \
     if ((ctx)->profiling) vn_prof_begin((ctx), (name));                                 \
     cudaError_t _e = vn_launch_pdl((ctx), (level), kernel, dim3(grid), dim3(block), (smem), __VA_ARGS__); \
+    if ((ctx)->profiling) vn_prof_end((ctx));                                           \
+    (ctx)->launches++;                                                                  \
+    if (_e == cudaSuccess) _e = cudaGetLastError();                                     \
+    if (_e != cudaSuccess)                                                              \
+      return vn_fail((ctx), VN_ERR_CUDA, "launch of %s failed: %s", (name), cudaGetErrorString(_e)); \
+  } while (0)
+// the same with a thread-block cluster of cluster_y CTAs along y
+#define VN_LAUNCH_CLUSTER(ctx, level, cluster_y, name, kernel, grid, block, smem, ...)  \
+  do {                                                                                  \
+    if ((ctx)->profiling) vn_prof_begin((ctx), (name));                                 \
+    cudaError_t _e = vn_launch_cluster((ctx), (level), (cluster_y), kernel, dim3(grid), dim3(block), (smem), __VA_ARGS__); \
     if ((ctx)->profiling) vn_prof_end((ctx));                                           \
     (ctx)->launches++;                                                                  \
     if (_e == cudaSuccess) _e = cudaGetLastError();                                     \

@@ -27,6 +27,16 @@ constexpr int BK = 64;         // K elements per stage = one 128-byte swizzle ro
 constexpr int TC_THREADS = 192;
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;  // ~1 s
 
+// RoPE + KV-cache append applied to the q | k | v projection (same meaning as in rope_append_kernel)
+struct TcRope {
+  const float* cos_t; const float* sin_t;
+  const int* lens; const int* depth;
+  void* kc; void* vc;      // bf16 caches [B, max_seq, n_kv, hd]
+  float* q_out;            // fp32 [rows, ldq]: q heads rotated (k and v columns are not written)
+  long long ldq;
+  int Tn, H, n_kv, hd, max_seq, use_rope, rope_rows, slot_offset;
+};
+
 struct TcArgs {
   void* C;                 // see epi
   const float* bias;
@@ -44,6 +54,10 @@ struct TcArgs {
   long long partial_stride;  // rows_total * N
   int* error_flag;
   long long* trace;        // optional [CTAs][8] clock64 stamps of the kernel's phases (null: no tracing)
+  // cluster modes: the CTAs of one feature tile (blockIdx.y = K range) form a thread-block cluster and reduce
+  // their partial tiles through distributed shared memory; the epilogue below runs on the reduced rows
+  float* resid;            // TC_CL_ADD: resid[row, n] += value (fp32, pitch ldc)
+  TcRope rope;             // TC_CL_QKV
 };
 
 // SM cycle counter, ordered with the surrounding memory operations (for the optional phase stamps)
@@ -125,7 +139,23 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
       : "r"(taddr));
 }
 
-enum { TC_PARTIAL = 0, TC_STORE = 1, TC_SWIGLU = 2, TC_ADD = 3 };
+enum { TC_PARTIAL = 0, TC_STORE = 1, TC_SWIGLU = 2, TC_ADD = 3,
+       TC_CL_STORE = 4, TC_CL_SWIGLU = 5, TC_CL_ADD = 6, TC_CL_QKV = 7 };   // >= TC_CL_STORE: cluster split-K
+
+__device__ __forceinline__ unsigned cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned cluster_size() { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+// every thread of every CTA of the cluster; release / acquire so that shared-memory writes before it are
+// visible to distributed-shared-memory reads after it
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(unsigned local_addr, unsigned rank) {
+  unsigned ra; float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra));
+  return v;
+}
 
 template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS)
@@ -280,7 +310,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int m0 = ch * 32;
         const int mrem = cnt - m0;               // tokens left from this chunk on (>= 1)
-        if (MODE == TC_PARTIAL || (MODE == TC_STORE && !g.c_bf16)) {
+        if (MODE >= TC_CL_STORE) {
+          // whole partial tile [token][feature] in this CTA's shared memory; reduced after the cluster barrier
+          float* tile = reinterpret_cast<float*>(base);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile[(m0 + i) * BF + f] = __uint_as_float(r[i]);
+        } else if (MODE == TC_PARTIAL || (MODE == TC_STORE && !g.c_bf16)) {
           // fp32 rows of the output: staged through shared memory (the pipeline stages are free once the
           // accumulator is complete) so that one instruction stores 512 contiguous bytes of a token row
           float* out; long long ld;
@@ -370,6 +405,104 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
     if (tr && threadIdx.x == 64) tr[5] = clock_now();     // this warp's stores issued
   }
+  if (MODE >= TC_CL_STORE) {
+    __syncwarp();            // the single-lane roles above rejoin their warps before the aligned barriers
+    cluster_sync_all();
+    if (warp >= 2 && *(volatile int*)&s_error == 0) {
+      const int q = warp & 3;
+      const unsigned rank = cluster_rank(), S = cluster_size();
+      const unsigned tile_addr = smem_u32(base);
+      const int c4 = lane * 4, n = n0 + c4;
+      // rows rank, rank + S, ... of the tile belong to this CTA; its four epilogue warps take them in turn
+      // (all peers' loads of a row are issued before the first add)
+      auto reduce_row = [&](int m, float4 (&pv)[8]) {
+        const unsigned at = tile_addr + (unsigned)((m * BF + c4) * 4);
+#pragma unroll
+        for (unsigned pr = 0; pr < 8; ++pr)
+          if (pr < S) pv[pr] = ld_dsmem_f4(at, pr);
+      };
+      auto sum_row = [&](const float4 (&pv)[8]) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (unsigned pr = 0; pr < 8; ++pr)        // fixed order: the sum does not depend on scheduling
+          if (pr < S) { acc.x += pv[pr].x; acc.y += pv[pr].y; acc.z += pv[pr].z; acc.w += pv[pr].w; }
+        return acc;
+      };
+      auto finish = [&](int m, float4 acc) {
+        const long long row = row0 + m;
+        if (MODE == TC_CL_ADD) {
+          if (n < g.N) {
+            float4* dst = reinterpret_cast<float4*>(g.resid + row * g.ldc + n);
+            float4 x = *dst;
+            x.x += acc.x; x.y += acc.y; x.z += acc.z; x.w += acc.w;
+            *dst = x;
+          }
+        } else if (MODE == TC_CL_SWIGLU) {
+          if (n < g.N) {
+            const float o0 = silu_ref(acc.x) * acc.y, o1 = silu_ref(acc.z) * acc.w;
+            const long long o_at = row * g.ldc + (n >> 1);
+            if (g.c_bf16)
+              *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(g.C) + o_at) = __floats2bfloat162_rn(o0, o1);
+            else
+              *reinterpret_cast<float2*>(reinterpret_cast<float*>(g.C) + o_at) = make_float2(o0, o1);
+          }
+        } else if (MODE == TC_CL_QKV) {
+          const TcRope& rp = g.rope;
+          const int b = (int)(row / rp.Tn), t = (int)(row % rp.Tn);
+          const int len = rp.lens[b] + rp.slot_offset;
+          const int pos = len + (rp.depth ? rp.depth[t] : t);
+          const int slot = len + t;
+          const int half = rp.hd >> 1;
+          const int head = n / rp.hd, j = n % rp.hd;       // the four features of a lane share head and half
+          float v[4] = {acc.x, acc.y, acc.z, acc.w};
+          const bool rot = rp.use_rope && head < rp.H + rp.n_kv;
+          {
+            const int pp = pos < rp.rope_rows ? pos : rp.rope_rows - 1;
+            const int jj = j < half ? j : j - half;
+            const int part = half >> 2;                    // lanes between a feature and its rotation partner
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float other = __shfl_xor_sync(0xffffffffu, v[e], part);
+              if (rot && n < g.N) {
+                const float c = rp.cos_t[(long long)pp * half + jj + e], sn = rp.sin_t[(long long)pp * half + jj + e];
+                v[e] = j < half ? v[e] * c + (-other) * sn : v[e] * c + other * sn;
+              }
+            }
+          }
+          if (n < g.N) {
+            if (head < rp.H) {
+              *reinterpret_cast<float4*>(rp.q_out + row * rp.ldq + n) = make_float4(v[0], v[1], v[2], v[3]);
+            } else if (slot < rp.max_seq) {
+              const bool is_k = head < rp.H + rp.n_kv;
+              const int kh = is_k ? head - rp.H : head - rp.H - rp.n_kv;
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(is_k ? rp.kc : rp.vc) +
+                                   (((long long)b * rp.max_seq + slot) * rp.n_kv + kh) * rp.hd + j;
+              reinterpret_cast<__nv_bfloat162*>(dst)[0] = __floats2bfloat162_rn(v[0], v[1]);
+              reinterpret_cast<__nv_bfloat162*>(dst)[1] = __floats2bfloat162_rn(v[2], v[3]);
+            }
+          }
+        } else {
+          if (n < g.N) {
+            if (g.bias) { acc.x += g.bias[n]; acc.y += g.bias[n + 1]; acc.z += g.bias[n + 2]; acc.w += g.bias[n + 3]; }
+            if (g.c_bf16) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C) + row * g.ldc + n;
+              reinterpret_cast<__nv_bfloat162*>(dst)[0] = __floats2bfloat162_rn(acc.x, acc.y);
+              reinterpret_cast<__nv_bfloat162*>(dst)[1] = __floats2bfloat162_rn(acc.z, acc.w);
+            } else {
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(g.C) + row * g.ldc + n) = acc;
+            }
+          }
+        }
+      };
+      for (int m = (int)rank + (int)S * q; m < cnt; m += (int)S * 4) {
+        float4 pa[8];
+        reduce_row(m, pa);
+        finish(m, sum_row(pa));
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();      // nobody leaves while a peer may still read its tile
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tr && threadIdx.x == 0) {
@@ -430,7 +563,23 @@ struct TcPlan {
   long long rows_total = 0;      // rows addressed in C (all segments)
   int* error_flag = nullptr;
   long long* trace = nullptr;    // device buffer [CTAs][8] for phase stamps, or null
+  // cluster split-K: the K ranges of a feature tile run as one thread-block cluster (at most 8 CTAs) that
+  // reduces its partial tiles through distributed shared memory and applies the epilogue itself
+  int cluster_mode = 0;          // 0: off, else tc_detail::TC_CL_STORE / TC_CL_SWIGLU / TC_CL_ADD / TC_CL_QKV
+  float* resid = nullptr;        // TC_CL_ADD target (pitch g.ldc)
+  tc_detail::TcRope rope = {};   // TC_CL_QKV
 };
+
+// cluster split-K needs whole float4 groups per lane and, for the RoPE epilogue, heads that tile the 128 features
+inline bool gemm_tc_cluster_supported(const GemmArgs& g, int mode, const tc_detail::TcRope* rope) {
+  if (g.seg_cnt || g.nseg != 1 || g.N % 4 != 0) return false;
+  if (mode == tc_detail::TC_CL_QKV) {
+    if (!rope) return false;
+    const int hd = rope->hd;
+    return (hd == 32 || hd == 64 || hd == 128) && rope->ldq % 4 == 0;
+  }
+  return g.ldc % 4 == 0;
+}
 
 // Supported: bf16 operands, K-major, 16-byte aligned rows, tokens <= 256, A rows contiguous (no gather).
 inline bool gemm_tc_supported(const GemmArgs& g) {
@@ -470,15 +619,29 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   a.partial_stride = plan.rows_total * (long long)g.N;
   a.error_flag = plan.error_flag;
   a.trace = plan.trace;
-  if ((gy > 1 || plan.force_partial) && !plan.partial) return vn_fail(ctx, VN_ERR_INVALID, "split-K needs a workspace");
+  a.resid = plan.resid;
+  a.rope = plan.rope;
+  if (plan.cluster_mode) {
+    if (gy > 8 || g.seg_cnt) return vn_fail(ctx, VN_ERR_INVALID, "cluster split-K: at most 8 K ranges, dense rows only");
+    a.partial = nullptr;
+    budget = std::max(budget, (size_t)((g.M + 31) / 32) * 32 * BF * 4);   // the whole partial tile is staged
+    a.smem_budget = (unsigned)budget;
+  }
+  if (!plan.cluster_mode && (gy > 1 || plan.force_partial) && !plan.partial)
+    return vn_fail(ctx, VN_ERR_INVALID, "split-K needs a workspace");
   const size_t smem = budget + 1024;
-  const int mode = a.partial ? TC_PARTIAL : g.epi == EPI_SWIGLU ? TC_SWIGLU : g.epi == EPI_ADD ? TC_ADD : TC_STORE;
+  const int mode = plan.cluster_mode ? plan.cluster_mode
+                   : a.partial ? TC_PARTIAL : g.epi == EPI_SWIGLU ? TC_SWIGLU : g.epi == EPI_ADD ? TC_ADD : TC_STORE;
   static unsigned long long attr_set = 0;
   if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
     VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_PARTIAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
     VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
     VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
     VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_CL_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_CL_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_CL_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_CL_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
     attr_set |= 1ull << (ctx->device & 63);
   }
   dim3 grid(ceil_div(g.N, BF), gy, g.nseg);
@@ -487,6 +650,10 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
     case TC_PARTIAL: VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_PARTIAL>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
     case TC_SWIGLU:  VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
     case TC_ADD:     VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_CL_STORE:  VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_CL_SWIGLU: VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_CL_ADD:    VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_CL_QKV:    VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_QKV>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
     default:         VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
   }
   return VN_OK;

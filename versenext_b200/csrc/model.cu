@@ -134,6 +134,10 @@ struct vn_model {
   float* partial = nullptr;      // split-K workspace of the tcgen05 path
   size_t partial_bytes = 0;
   int* tc_error = nullptr;       // device word raised by a bounded wait that ran out
+  // Split-K reduced inside thread-block clusters through distributed shared memory, epilogue in the GEMM
+  // (VN_TC_CLUSTER=1: q|k|v and gate|up, 2: also the residual projections).  Off by default: on B200 the
+  // cluster launch plus the reduce cost 3.5-5 us per GEMM, as much as the finalize kernel it removes.
+  int use_cluster = 0;
   bool use_tc = true;            // VN_GEMM_TC=0 in the environment: keep the mma.sync GEMMs
   bool force_simt_attn = false;  // VN_ATTN_SIMT=1 in the environment: keep the SIMT attention kernel (A/B checks)
 };
@@ -425,6 +429,20 @@ int32_t tc_partial(vn_model* m, GemmArgs g, long long a_rows, long long c_rows, 
   return VN_OK;
 }
 
+// split-K inside thread-block clusters: the K ranges of a feature tile reduce through distributed shared
+// memory and the epilogue (residual add, SwiGLU, RoPE + cache append) runs in the GEMM itself
+int32_t tc_cluster(vn_model* m, const GemmArgs& g, long long a_rows, int mode, float* resid,
+                   const tc_detail::TcRope* rope) {
+  vn_ctx* ctx = m->ctx;
+  TcPlan plan;
+  plan.splits = std::min(8, tc_splits(ctx, g.N, g.K, 1));
+  plan.error_flag = m->tc_error;
+  plan.cluster_mode = mode;
+  plan.resid = resid;
+  if (rope) plan.rope = *rope;
+  return launch_gemm_tc(ctx, g, a_rows, plan);
+}
+
 int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, bool tree, float* out_hidden,
                    float* out_logits, int last_only, int slot_offset) {
   typedef __nv_bfloat16 T;
@@ -449,10 +467,20 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     GemmArgs g;
     // ---- attention block
     g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.M = M; g.N = qkv_ld; g.K = D; g.tag = "gemm_qkv";
-    TRY(tc_partial(m, g, cap, M, &sp));
-    VN_LAUNCH_PDL(ctx, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld, m->qkv,
-              m->rope_cos, m->rope_sin, kv->lens, tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[li],
-              (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
+    tc_detail::TcRope rope;
+    rope.cos_t = m->rope_cos; rope.sin_t = m->rope_sin; rope.lens = kv->lens;
+    rope.depth = tree ? m->depth_dev : (const int*)nullptr;
+    rope.kc = kv->k[li]; rope.vc = kv->v[li]; rope.q_out = m->qkv; rope.ldq = qkv_ld;
+    rope.Tn = Tn; rope.H = H; rope.n_kv = n_kv; rope.hd = hd; rope.max_seq = kv->max_seq;
+    rope.use_rope = c.use_rope; rope.rope_rows = m->rope_rows; rope.slot_offset = slot_offset;
+    if (m->use_cluster && gemm_tc_cluster_supported(g, tc_detail::TC_CL_QKV, &rope)) {
+      TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_QKV, nullptr, &rope));
+    } else {
+      TRY(tc_partial(m, g, cap, M, &sp));
+      VN_LAUNCH_PDL(ctx, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld,
+                    m->qkv, m->rope_cos, m->rope_sin, kv->lens, tree ? m->depth_dev : (const int*)nullptr,
+                    (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
+    }
     AttnArgs a;
     a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[li]; a.vc = kv->v[li]; a.sink_k = L.sink_k; a.sink_v = L.sink_v;
     a.out = m->attn; a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
@@ -470,17 +498,29 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     }
     g = GemmArgs();
     g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.M = M; g.N = D; g.K = H * hd; g.tag = "gemm_proj";
-    TRY(tc_partial(m, g, cap, M, &sp));
-    VN_LAUNCH_PDL(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, L.norm2, (T*)m->h,
-              mod ? m->h32 : (float*)nullptr, D, 1e-6f);
+    g.ldc = D;
+    // the residual add needs a norm kernel behind it either way, so the cluster reduce only pays for the
+    // projections whose finalize kernel disappears (q|k|v, gate|up); VN_TC_CLUSTER=2 forces it here too
+    if (m->use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
+      TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_ADD, m->x, nullptr));
+      VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm2, (T*)m->h, mod ? m->h32 : (float*)nullptr, 1, 0, D,
+                    1e-6f);
+    } else {
+      TRY(tc_partial(m, g, cap, M, &sp));
+      VN_LAUNCH_PDL(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, L.norm2,
+                    (T*)m->h, mod ? m->h32 : (float*)nullptr, D, 1e-6f);
+    }
     // ---- feed-forward block
     const float* next_norm = last ? nullptr : m->layers[li + 1].norm1;
     if (!mod) {
       g = GemmArgs();
       g.A = m->h; g.lda = D; g.W = L.w_gateup; g.ldw = D; g.M = M; g.N = 2 * c.mlp_hidden; g.K = D;
       g.tag = "gemm_gateup";
-      TRY(tc_partial(m, g, cap, M, &sp));
-      {
+      g.C = m->act; g.ldc = c.mlp_hidden; g.c_bf16 = 1;
+      if (m->use_cluster && gemm_tc_cluster_supported(g, tc_detail::TC_CL_SWIGLU, nullptr)) {
+        TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_SWIGLU, nullptr, nullptr));
+      } else {
+        TRY(tc_partial(m, g, cap, M, &sp));
         const long long pairs = (long long)M * c.mlp_hidden;
         VN_LAUNCH_PDL(ctx, splitk_swiglu_kernel<T>, (unsigned)ceil_div(pairs, 256ll), 256, 0, m->partial, sp,
                   (long long)M * 2 * c.mlp_hidden, (T*)m->act, 2 * c.mlp_hidden, pairs);
@@ -488,9 +528,16 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g = GemmArgs();
       g.A = m->act; g.lda = c.mlp_hidden; g.W = L.w_down; g.ldw = c.mlp_hidden; g.M = M; g.N = D; g.K = c.mlp_hidden;
       g.tag = "gemm_down";
-      TRY(tc_partial(m, g, cap, M, &sp));
-      VN_LAUNCH_PDL(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm, (T*)m->h,
-                (float*)nullptr, D, 1e-6f);
+      g.ldc = D;
+      if (m->use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
+        TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_ADD, m->x, nullptr));
+        if (next_norm)
+          VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
+      } else {
+        TRY(tc_partial(m, g, cap, M, &sp));
+        VN_LAUNCH_PDL(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm,
+                      (T*)m->h, (float*)nullptr, D, 1e-6f);
+      }
     } else {
       const int ne = c.P * c.E, S = c.P * c.top_k, eh = c.expert_hidden;
       RouteArgs r;
@@ -582,6 +629,7 @@ int32_t vn_model_create(vn_ctx* ctx, const char* config_json, vn_model** out) {
   m->ctx = ctx; m->cfg = c; m->esz = c.bf16 ? 2 : 4;
   { const char* e = getenv("VN_ATTN_SIMT"); m->force_simt_attn = e && e[0] == '1'; }
   { const char* e = getenv("VN_GEMM_TC"); m->use_tc = !(e && e[0] == '0'); }
+  { const char* e = getenv("VN_TC_CLUSTER"); m->use_cluster = e ? atoi(e) : 0; }
   int32_t st = alloc_weights(m);
   if (st != VN_OK) { vn_model_destroy(m); return st; }
   *out = m;
