@@ -678,7 +678,14 @@ accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_
 }
 
 // ---- warp-cooperative helpers on a kept list ------------------------------------------------------------
-__device__ __forceinline__ void list_stats(const TopkRow& r, int lane, float& m, double& s) {
+// a kept list where it currently lives: the row in global memory, or the warp's copy in shared memory
+struct ListView {
+  const int* tok;
+  const float* val;
+  int n;
+};
+
+__device__ __forceinline__ void list_stats(const ListView& r, int lane, float& m, double& s) {
   m = -CUDART_INF_F;
   for (int i = lane; i < r.n; i += 32) m = fmaxf(m, r.val[i]);
 #pragma unroll
@@ -689,7 +696,7 @@ __device__ __forceinline__ void list_stats(const TopkRow& r, int lane, float& m,
 }
 
 // value of `token` in the list, or -inf when it is not kept (all lanes get the result)
-__device__ __forceinline__ float list_value(const TopkRow& r, int lane, int token) {
+__device__ __forceinline__ float list_value(const ListView& r, int lane, int token) {
   float v = -CUDART_INF_F;
   for (int i = lane; i < r.n; i += 32)
     if (r.tok[i] == token) v = r.val[i];
@@ -713,6 +720,36 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
   const uint32_t offset = offset_host + (offset_dev ? *offset_dev : 0u);
   const int rows_per_seq = np + nq;
   const TopkRow* rb = rows + (long long)b * rows_per_seq;
+  // The lists of this sequence are read many times below, each read a dependent round trip to L2: copy them
+  // into shared memory first when they fit (at most DEC_ROWS rows of DEC_ENT entries, the usual case).
+  constexpr int DEC_ROWS = 16, DEC_ENT = 64;
+  __shared__ int s_tok[4][DEC_ROWS][DEC_ENT];
+  __shared__ float s_val[4][DEC_ROWS][DEC_ENT];
+  __shared__ int s_n[4][DEC_ROWS];
+  const int wslot = threadIdx.x >> 5;
+  bool staged = rows_per_seq <= DEC_ROWS;
+  if (staged) {
+    int nmax = 0;
+    for (int r = lane; r < rows_per_seq; r += 32) { const int nr = rb[r].n; s_n[wslot][r] = nr; nmax = max(nmax, nr); }
+    __syncwarp();
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
+    staged = nmax <= DEC_ENT;
+  }
+  if (staged) {
+    for (int idx = lane; idx < rows_per_seq * DEC_ENT; idx += 32) {
+      const int r = idx / DEC_ENT, i = idx % DEC_ENT;
+      if (i < s_n[wslot][r]) { s_tok[wslot][r][i] = rb[r].tok[i]; s_val[wslot][r][i] = rb[r].val[i]; }
+    }
+    __syncwarp();
+  }
+  auto view = [&](int r) {
+    ListView v;
+    v.n = staged ? s_n[wslot][r] : rb[r].n;
+    v.tok = staged ? s_tok[wslot][r] : rb[r].tok;
+    v.val = staged ? s_val[wslot][r] : rb[r].val;
+    return v;
+  };
   long long* tok = out_tok + (long long)b * (k + 1);
   for (int i = lane; i <= k; i += 32) tok[i] = -1;
   __syncwarp();
@@ -721,14 +758,14 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
   for (; n < k; ++n) {
     const int x = (int)draft[(long long)b * k + n];
     float mp; double sp;
-    list_stats(rb[n], lane, mp, sp);
-    const float vp = list_value(rb[n], lane, x);
+    list_stats(view(n), lane, mp, sp);
+    const float vp = list_value(view(n), lane, x);
     const double p = vp == -CUDART_INF_F ? 0.0 : (double)expf(vp - mp) / sp;
     double q = 1.0;
     if (nq) {
       float mq; double sq;
-      list_stats(rb[np + n], lane, mq, sq);
-      const float vq = list_value(rb[np + n], lane, x);
+      list_stats(view(np + n), lane, mq, sq);
+      const float vq = list_value(view(np + n), lane, x);
       q = vq == -CUDART_INF_F ? 0.0 : (double)expf(vq - mq) / sq;
     }
     const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, pos_base + n, 0);
@@ -742,11 +779,12 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
     if (!bonus) return;
     sample_row = k;
   }
-  const TopkRow& P = rb[sample_row];
+  const ListView P = view(sample_row);
   float mp; double sp;
   list_stats(P, lane, mp, sp);
   float mq = 0.f; double sq = 1.0;
-  if (q_row >= 0) list_stats(rb[q_row], lane, mq, sq);
+  const ListView Q = view(q_row >= 0 ? q_row : 0);
+  if (q_row >= 0) list_stats(Q, lane, mq, sq);
   const float u = u_smp ? u_smp[(long long)b * (k + 1) + sample_row]
                         : philox_uniform(seed, offset, b, pos_base + sample_row, smp_purpose);
   for (int pass = 0; pass < 2; ++pass) {
@@ -774,7 +812,7 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
         for (int src = 0; src < 32; ++src) {
           const int t2 = __shfl_sync(0xffffffffu, tk, src);
           if (t2 < 0) continue;
-          const float vq = list_value(rb[q_row], lane, t2);
+          const float vq = list_value(Q, lane, t2);
           if (src == lane) {
             const double pp = (double)expf(P.val[i] - mp) / sp;
             const double qq = vq == -CUDART_INF_F ? 0.0 : (double)expf(vq - mq) / sq;
@@ -801,7 +839,7 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
         for (int src = 0; src < 32; ++src) {
           const int t2 = __shfl_sync(0xffffffffu, tk, src);
           if (t2 < 0) continue;
-          const float vq = list_value(rb[q_row], lane, t2);
+          const float vq = list_value(Q, lane, t2);
           if (src == lane) {
             const double pp = (double)expf(P.val[i] - mp) / sp;
             const double qq = vq == -CUDART_INF_F ? 0.0 : (double)expf(vq - mq) / sq;
