@@ -705,6 +705,16 @@ __device__ __forceinline__ float list_value(const ListView& r, int lane, int tok
   return v;
 }
 
+// per-lane lookup: binary search of `token` in the list (ascending token ids); -inf when it is not kept
+__device__ __forceinline__ float list_find(const ListView& r, int token) {
+  int lo = 0, hi = r.n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (r.tok[mid] < token) lo = mid + 1; else hi = mid;
+  }
+  return (lo < r.n && r.tok[lo] == token) ? r.val[lo] : -CUDART_INF_F;
+}
+
 // One warp per sequence: acceptance tests, then the inverse CDF over the kept list of the row to sample.
 __global__ void __launch_bounds__(128)
 accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restrict__ rows,
@@ -808,18 +818,12 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
       const int tk = i < P.n ? P.tok[i] : -1;
       if (pass == 0 && q_row >= 0) {
         // every lane needs q(tk) for its own token: loop over the 32 tokens of the chunk
-        double mine = 0.0;
-        for (int src = 0; src < 32; ++src) {
-          const int t2 = __shfl_sync(0xffffffffu, tk, src);
-          if (t2 < 0) continue;
-          const float vq = list_value(Q, lane, t2);
-          if (src == lane) {
-            const double pp = (double)expf(P.val[i] - mp) / sp;
-            const double qq = vq == -CUDART_INF_F ? 0.0 : (double)expf(vq - mq) / sq;
-            mine = pp - qq > 0.0 ? pp - qq : 0.0;
-          }
+        if (i < P.n) {   // every lane looks up q for its own token
+          const float my_vq = list_find(Q, tk);
+          const double pp = (double)expf(P.val[i] - mp) / sp;
+          const double qq = my_vq == -CUDART_INF_F ? 0.0 : (double)expf(my_vq - mq) / sq;
+          w = pp - qq > 0.0 ? pp - qq : 0.0;
         }
-        w = mine;
       } else if (i < P.n) {
         w = weight(i);
       }
@@ -835,18 +839,12 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
       double w = 0.0;
       const int tk = i < P.n ? P.tok[i] : -1;
       if (pass == 0 && q_row >= 0) {
-        double mine = 0.0;
-        for (int src = 0; src < 32; ++src) {
-          const int t2 = __shfl_sync(0xffffffffu, tk, src);
-          if (t2 < 0) continue;
-          const float vq = list_value(Q, lane, t2);
-          if (src == lane) {
-            const double pp = (double)expf(P.val[i] - mp) / sp;
-            const double qq = vq == -CUDART_INF_F ? 0.0 : (double)expf(vq - mq) / sq;
-            mine = pp - qq > 0.0 ? pp - qq : 0.0;
-          }
+        if (i < P.n) {   // every lane looks up q for its own token
+          const float my_vq = list_find(Q, tk);
+          const double pp = (double)expf(P.val[i] - mp) / sp;
+          const double qq = my_vq == -CUDART_INF_F ? 0.0 : (double)expf(my_vq - mq) / sq;
+          w = pp - qq > 0.0 ? pp - qq : 0.0;
         }
-        w = mine;
       } else if (i < P.n) {
         w = weight(i);
       }

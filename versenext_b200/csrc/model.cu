@@ -259,6 +259,7 @@ int32_t ensure_rows(vn_model* m, int M) {
       VN_CUDA(ctx, cudaMemsetAsync(m->expert_count, 0, ne * 4, ctx->stream));
       TRY(dev_alloc(ctx, (void**)&m->expert_off, ne * 4));
       TRY(dev_alloc(ctx, (void**)&m->expert_cur, ne * 4));
+      VN_CUDA(ctx, cudaMemsetAsync(m->expert_cur, 0, ne * 4, ctx->stream));
     }
   }
   m->cap_rows = (int)R;
@@ -367,6 +368,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
       TRY(linear(m, g));
       VN_LAUNCH(ctx, mod_combine_kernel, M, 256, 0, m->x, m->y, m->slot_pos, m->slot_w, m->part_w, D, c.P, c.top_k);
       VN_CUDA(ctx, cudaMemsetAsync(m->expert_count, 0, ne * 4, ctx->stream));   // zero between forwards
+      VN_CUDA(ctx, cudaMemsetAsync(m->expert_cur, 0, ne * 4, ctx->stream));
     }
   }
   // final norm + head on every row, or on the last position of every sequence
@@ -544,10 +546,8 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       r.h = m->h32; r.gates = L.router; r.slot_expert = m->slot_expert; r.slot_w = m->slot_w; r.part_w = m->part_w;
       r.expert_count = m->expert_count; r.M = M; r.D = D; r.P = c.P; r.E = c.E; r.top_k = c.top_k;
       VN_LAUNCH_PDL(ctx, mod_route_kernel, M, 128, 0, r);
-      VN_LAUNCH_PDL(ctx, mod_offsets_kernel, 1, 32, 0, m->expert_count, m->expert_off, m->expert_cur, ne);
-      VN_LAUNCH_PDL(ctx, mod_scatter_kernel, ceil_div(M * S, 256), 256, 0, m->slot_expert, m->expert_off, m->expert_cur,
-                m->sorted_row, m->slot_pos, M * S, S);
-      VN_LAUNCH_PDL(ctx, gather_sorted_kernel<T>, M * S, 128, 0, (const T*)m->h, m->sorted_row, (T*)m->hs, D);
+      VN_LAUNCH_PDL(ctx, mod_dispatch_kernel<T>, M * S, 128, 0, (const T*)m->h, m->slot_expert, m->expert_count,
+                    m->expert_off, m->expert_cur, m->slot_pos, (T*)m->hs, ne, S, D);
       g = GemmArgs();
       g.A = m->hs; g.lda = D; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
       g.C = m->act; g.ldc = eh; g.M = M; g.N = 2 * eh; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = 1;
@@ -559,7 +559,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.tag = "gemm_expert_down";
       TRY(tc_partial(m, g, (long long)M * S, (long long)M * S, &sp));
       VN_LAUNCH_PDL(ctx, mod_combine_split_kernel, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
-                m->slot_w, m->part_w, D, c.P, c.top_k, m->expert_count, ne);
+                m->slot_w, m->part_w, D, c.P, c.top_k, m->expert_count, m->expert_cur, ne);
       if (next_norm)
         VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
     }

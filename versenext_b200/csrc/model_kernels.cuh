@@ -567,6 +567,36 @@ __global__ void splitk_swiglu_kernel(const float* __restrict__ partial, int spli
 }
 
 // copy the routed tokens' normalised activations into expert order: dst[pos] = src[sorted_row[pos]]
+// ---- MoD dispatch in one launch: segment offsets, a place for every routed (token, slot) pair inside its
+// expert's segment, and the copy of the token's normalised row to that place (the expert GEMMs load their rows
+// contiguously with TMA).  One CTA per pair.  `cursor` must be zero on entry (the combine kernel leaves it so).
+template <typename T>
+__global__ void mod_dispatch_kernel(const T* __restrict__ src, const int* __restrict__ slot_expert,
+                                    const int* __restrict__ count, int* __restrict__ offset, int* __restrict__ cursor,
+                                    int* __restrict__ slot_pos, T* __restrict__ dst, int n_expert, int S, int D) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ int s_pos;
+  const int i = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const int e = slot_expert[i];
+    int acc = 0, mine = 0;
+    for (int x = 0; x < n_expert; ++x) {
+      if (x == e) mine = acc;
+      if (i == 0) offset[x] = acc;          // the GEMMs read the segment starts from here
+      acc += count[x];
+    }
+    const int pos = mine + atomicAdd(&cursor[e], 1);
+    slot_pos[i] = pos;
+    s_pos = pos;
+  }
+  __syncthreads();
+  const uint4* a = reinterpret_cast<const uint4*>(src + (long long)(i / S) * D);
+  uint4* b = reinterpret_cast<uint4*>(dst + (long long)s_pos * D);
+  const int n16 = D * (int)sizeof(T) / 16;
+  for (int j = threadIdx.x; j < n16; j += blockDim.x) b[j] = a[j];
+}
+
 template <typename T>
 __global__ void gather_sorted_kernel(const T* __restrict__ src, const int* __restrict__ sorted_row, T* __restrict__ dst,
                                      int D) {
@@ -586,12 +616,12 @@ __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restric
                                                                 const float* __restrict__ slot_w,
                                                                 const float* __restrict__ part_w, int D, int P,
                                                                 int top_k, int* __restrict__ zero_counts,
-                                                                int n_zero) {
+                                                                int* __restrict__ zero_cursor, int n_zero) {
   pdl_trigger();
   pdl_wait();
   // the expert GEMMs were the last readers of the per-expert counts: leave them at zero for the next router
   if (blockIdx.x == 0)
-    for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero_counts[i] = 0;
+    for (int i = threadIdx.x; i < n_zero; i += blockDim.x) { zero_counts[i] = 0; if (zero_cursor) zero_cursor[i] = 0; }
   __shared__ long long s_at[64];
   __shared__ float s_w[64];
   const int row = blockIdx.x;
