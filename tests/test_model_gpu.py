@@ -293,6 +293,29 @@ def test_cluster_split_k_reduce(level, monkeypatch):
     assert rel_err(lg, want) < 2e-2
 
 
+def test_persistent_gemm_variant(monkeypatch):
+    """Opt-in persistent tile-loop GEMM (one CTA per SM, double-buffered TMEM accumulator), forced onto the small
+    shapes of this model: dense store, split-K partial and per-expert SwiGLU tiles give the same logits."""
+    monkeypatch.setenv("VN_TC_PERSIST", "2")       # read at every GEMM launch
+    cfg = hd64_cfg()
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=27, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    rng = np.random.default_rng(10)
+    B = 4
+    ctx_tok = rng.integers(0, 384, (B, 37))
+    cache = m.new_cache(B, 128)
+    lg0 = m.forward_cached(ctx_tok, cache).numpy()
+    want0, oc = OM.forward(sd, cfg, ctx_tok)
+    assert rel_err(lg0, want0) < 2e-2
+    cache.commit(37, np.full(B, 37, np.int32))
+    for _ in range(2):
+        nxt = rng.integers(0, 384, (B, 5))
+        lg = m.forward_cached(nxt, cache).numpy()
+        want, oc = OM.forward(sd, cfg, nxt, cache=oc)
+        assert rel_err(lg, want) < 2e-2
+        cache.commit(5, np.full(B, 5, np.int32))
+
+
 def _dequantise(w, scheme):
     from oracle import quant as OQ
     if scheme == "int8":

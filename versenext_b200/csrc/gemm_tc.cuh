@@ -18,6 +18,7 @@
 // the caller's finalize kernel (deterministic order).
 #pragma once
 #include <cuda.h>
+#include <stdlib.h>
 #include "gemm.cuh"
 
 namespace tc_detail {
@@ -73,6 +74,9 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // adds to the transaction count of the current phase without arriving
 __device__ __forceinline__ void mbar_expect_tx_only(unsigned long long* bar, unsigned bytes) {
@@ -155,6 +159,109 @@ __device__ __forceinline__ float4 ld_dsmem_f4(unsigned local_addr, unsigned rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra));
   return v;
+}
+
+// Epilogue of one 32-token chunk of the accumulator (r[i] = feature f of token m0 + i for this thread).
+// `base` points at 32 KB of shared memory for two staging tiles (`buf` selects one; callers alternate so that a
+// tile is not rewritten while another warp still reads it).  split_y selects the slice of the split-K workspace.
+template <int MODE>
+__device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigned (&r)[32], unsigned char* base,
+                                                  int ch, int buf, int q, int lane, int n0, int row0, int cnt,
+                                                  int split_y, bool vec_ok, bool swi_ok) {
+  const int f = q * 32 + lane, n = n0 + f;
+  const int m0 = ch * 32;
+  const int mrem = cnt - m0;               // tokens left from this chunk on (>= 1)
+    if (MODE >= TC_CL_STORE) {
+      // whole partial tile [token][feature] in this CTA's shared memory; reduced after the cluster barrier
+      float* tile = reinterpret_cast<float*>(base);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) tile[(m0 + i) * BF + f] = __uint_as_float(r[i]);
+    } else if (MODE == TC_PARTIAL || (MODE == TC_STORE && !g.c_bf16)) {
+      // fp32 rows of the output: staged through shared memory (the pipeline stages are free once the
+      // accumulator is complete) so that one instruction stores 512 contiguous bytes of a token row
+      float* out; long long ld;
+      if (MODE == TC_PARTIAL) { out = g.partial + (long long)split_y * g.partial_stride; ld = g.N; }
+      else { out = reinterpret_cast<float*>(g.C); ld = g.ldc; }
+      out += (long long)(row0 + m0) * ld + n0;
+      const float bias = (MODE == TC_STORE && g.bias && n < g.N) ? g.bias[n] : 0.f;
+      if (vec_ok) {
+        float* tile = reinterpret_cast<float*>(base) + buf * (32 * BF);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]) + bias;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int c4 = lane * 4;
+        if (n0 + c4 < g.N) {                 // N % 4 == 0: a float4 is inside or outside as a whole
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int row = q * 8 + j;
+            if (row < mrem)
+              *reinterpret_cast<float4*>(out + (long long)row * ld + c4) =
+                  *reinterpret_cast<const float4*>(tile + row * BF + c4);
+          }
+        }
+      } else if (n < g.N) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < mrem) out[(long long)i * ld + f] = __uint_as_float(r[i]) + bias;
+      }
+    } else if (MODE == TC_SWIGLU) {
+      // (gate, up) sit in adjacent columns: stage the fp32 tile, then every lane turns two pairs of a token
+      // row into two outputs, so that a warp stores 64 contiguous outputs of a row at once
+      if (swi_ok) {
+        float* tile = reinterpret_cast<float*>(base) + buf * (32 * BF);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int c4 = lane * 4;
+        if (n0 + c4 + 3 < g.N) {
+#pragma unroll 2
+          for (int j = 0; j < 8; ++j) {
+            const int row = q * 8 + j;
+            if (row < mrem) {
+              const float4 v = *reinterpret_cast<const float4*>(tile + row * BF + c4);
+              const float o0 = silu_ref(v.x) * v.y, o1 = silu_ref(v.z) * v.w;
+              const long long at = (long long)(row0 + m0 + row) * g.ldc + ((n0 + c4) >> 1);
+              if (g.c_bf16)
+                *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(g.C) + at) =
+                    __floats2bfloat162_rn(o0, o1);
+              else
+                *reinterpret_cast<float2*>(reinterpret_cast<float*>(g.C) + at) = make_float2(o0, o1);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float v = __uint_as_float(r[i]);
+          const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+          if (i < mrem && !(lane & 1) && n + 1 < g.N)
+            store_out<float>(g.C, (long long)(row0 + m0 + i) * g.ldc + (n >> 1), silu_ref(v) * other, g.c_bf16);
+        }
+      }
+    } else if (MODE == TC_ADD) {
+      if (n < g.N) {
+        float* dst = reinterpret_cast<float*>(g.C) + (long long)(row0 + m0) * g.ldc + n;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < mrem) dst[(long long)i * g.ldc] += __uint_as_float(r[i]);
+      }
+    } else {
+      if (n < g.N) {
+        const float bias = g.bias ? g.bias[n] : 0.f;
+        const long long at = (long long)(row0 + m0) * g.ldc + n;
+        if (g.c_bf16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C) + at;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < mrem) dst[(long long)i * g.ldc] = __float2bfloat16_rn(__uint_as_float(r[i]) + bias);
+        } else {
+          float* dst = reinterpret_cast<float*>(g.C) + at;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < mrem) dst[(long long)i * g.ldc] = __uint_as_float(r[i]) + bias;
+        }
+      }
+    }
 }
 
 template <int MODE>
@@ -308,99 +415,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         unsigned r[32];
         tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int m0 = ch * 32;
-        const int mrem = cnt - m0;               // tokens left from this chunk on (>= 1)
-        if (MODE >= TC_CL_STORE) {
-          // whole partial tile [token][feature] in this CTA's shared memory; reduced after the cluster barrier
-          float* tile = reinterpret_cast<float*>(base);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) tile[(m0 + i) * BF + f] = __uint_as_float(r[i]);
-        } else if (MODE == TC_PARTIAL || (MODE == TC_STORE && !g.c_bf16)) {
-          // fp32 rows of the output: staged through shared memory (the pipeline stages are free once the
-          // accumulator is complete) so that one instruction stores 512 contiguous bytes of a token row
-          float* out; long long ld;
-          if (MODE == TC_PARTIAL) { out = g.partial + (long long)blockIdx.y * g.partial_stride; ld = g.N; }
-          else { out = reinterpret_cast<float*>(g.C); ld = g.ldc; }
-          out += (long long)(row0 + m0) * ld + n0;
-          const float bias = (MODE == TC_STORE && g.bias && n < g.N) ? g.bias[n] : 0.f;
-          if (vec_ok) {
-            float* tile = reinterpret_cast<float*>(base) + (ch & 1) * (32 * BF);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]) + bias;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            const int c4 = lane * 4;
-            if (n0 + c4 < g.N) {                 // N % 4 == 0: a float4 is inside or outside as a whole
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int row = q * 8 + j;
-                if (row < mrem)
-                  *reinterpret_cast<float4*>(out + (long long)row * ld + c4) =
-                      *reinterpret_cast<const float4*>(tile + row * BF + c4);
-              }
-            }
-          } else if (n < g.N) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < mrem) out[(long long)i * ld + f] = __uint_as_float(r[i]) + bias;
-          }
-        } else if (MODE == TC_SWIGLU) {
-          // (gate, up) sit in adjacent columns: stage the fp32 tile, then every lane turns two pairs of a token
-          // row into two outputs, so that a warp stores 64 contiguous outputs of a row at once
-          if (swi_ok) {
-            float* tile = reinterpret_cast<float*>(base) + (ch & 1) * (32 * BF);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]);
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            const int c4 = lane * 4;
-            if (n0 + c4 + 3 < g.N) {
-#pragma unroll 2
-              for (int j = 0; j < 8; ++j) {
-                const int row = q * 8 + j;
-                if (row < mrem) {
-                  const float4 v = *reinterpret_cast<const float4*>(tile + row * BF + c4);
-                  const float o0 = silu_ref(v.x) * v.y, o1 = silu_ref(v.z) * v.w;
-                  const long long at = (long long)(row0 + m0 + row) * g.ldc + ((n0 + c4) >> 1);
-                  if (g.c_bf16)
-                    *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(g.C) + at) =
-                        __floats2bfloat162_rn(o0, o1);
-                  else
-                    *reinterpret_cast<float2*>(reinterpret_cast<float*>(g.C) + at) = make_float2(o0, o1);
-                }
-              }
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float v = __uint_as_float(r[i]);
-              const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-              if (i < mrem && !(lane & 1) && n + 1 < g.N)
-                store_out<float>(g.C, (long long)(row0 + m0 + i) * g.ldc + (n >> 1), silu_ref(v) * other, g.c_bf16);
-            }
-          }
-        } else if (MODE == TC_ADD) {
-          if (n < g.N) {
-            float* dst = reinterpret_cast<float*>(g.C) + (long long)(row0 + m0) * g.ldc + n;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < mrem) dst[(long long)i * g.ldc] += __uint_as_float(r[i]);
-          }
-        } else {
-          if (n < g.N) {
-            const float bias = g.bias ? g.bias[n] : 0.f;
-            const long long at = (long long)(row0 + m0) * g.ldc + n;
-            if (g.c_bf16) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C) + at;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < mrem) dst[(long long)i * g.ldc] = __float2bfloat16_rn(__uint_as_float(r[i]) + bias);
-            } else {
-              float* dst = reinterpret_cast<float*>(g.C) + at;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < mrem) dst[(long long)i * g.ldc] = __uint_as_float(r[i]) + bias;
-            }
-          }
-        }
+        tc_epilogue_chunk<MODE>(g, r, base, ch, ch & 1, q, lane, n0, row0, cnt, (int)blockIdx.y, vec_ok, swi_ok);
       }
     }
     if (tr && threadIdx.x == 64) tr[5] = clock_now();     // this warp's stores issued
@@ -522,6 +537,195 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   }
 }
 
+// ---- persistent variant: one CTA per SM walks a list of tiles -------------------------------------------
+// For GEMMs with many more tiles than SM slots (LM head: 1940 tiles, expert gate|up: 672).  The roles are the
+// same, but the stage ring keeps running across tiles and the accumulator is double buffered in TMEM, so the
+// weight stream of tile t + 1 flows while the epilogue warps drain tile t, and there is no partial last wave.
+// Tile id -> (segment z, K range y, feature tile x), x fastest, so that CTAs that run at the same time share a
+// segment's token rows in L2.  Tiles of empty segments are skipped by every role alike.
+constexpr int PERSIST_STAGING = 32 * 1024;   // two staging tiles for the epilogue, in front of the stages
+
+template <int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs g,
+                       int tiles_x, int tiles_y, int tiles_total) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ unsigned long long bar_full[8], bar_empty[8], acc_full[2], acc_empty[2];
+  __shared__ unsigned tmem_base_slot;
+  __shared__ int s_error;
+  __shared__ int s_maxcnt;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();
+  // the longest segment fixes the stage size for the whole launch (uniform over the CTA)
+  int maxcnt = g.M;
+  if (g.seg_cnt) {
+    if (threadIdx.x == 0) {
+      int mx = 0;
+      const int nseg = tiles_total / (tiles_x * tiles_y);
+      for (int z = 0; z < nseg; ++z) mx = max(mx, g.seg_cnt[z]);
+      s_maxcnt = mx;
+    }
+    __syncthreads();
+    maxcnt = s_maxcnt;
+  }
+  if (maxcnt > g.ntok) maxcnt = g.ntok;
+  if (maxcnt <= 0 || (int)blockIdx.x >= tiles_total) return;     // uniform: nothing allocated yet
+  const int max16 = (maxcnt + 15) & ~15;
+
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* stages = base + PERSIST_STAGING;
+  const unsigned w_bytes = BF * BK * 2;
+  const unsigned stage_bytes = w_bytes + (unsigned)max16 * BK * 2;
+  int S = (int)((g.smem_budget - PERSIST_STAGING) / stage_bytes);
+  S = S > 8 ? 8 : S;
+  const int nkb_total = (g.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
+    mbar_init(&acc_full[0], 1); mbar_init(&acc_full[1], 1);
+    mbar_init(&acc_empty[0], 4); mbar_init(&acc_empty[1], 4);     // one arrival per epilogue warp
+    s_error = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  unsigned ncols_buf = 32;
+  while (ncols_buf < (unsigned)((g.ntok + 31) & ~31)) ncols_buf <<= 1;
+  const unsigned ncols = ncols_buf * 2;
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = tmem_base_slot;
+
+  // every role walks the same tile list and derives the same per-tile numbers
+  auto tile_info = [&](int id, int& z, int& y, int& n0, int& row0, int& cnt, int& kb0, int& nkb) {
+    const int per_seg = tiles_x * tiles_y;
+    z = id / per_seg;
+    const int rem = id - z * per_seg;
+    y = rem / tiles_x;
+    n0 = (rem - y * tiles_x) * BF;
+    row0 = 0; cnt = g.M;
+    if (g.seg_cnt) { row0 = g.seg_off[z]; cnt = g.seg_cnt[z]; }
+    if (cnt > g.ntok) cnt = g.ntok;
+    kb0 = y * g.kb_per_split;
+    nkb = nkb_total - kb0;
+    if (nkb > g.kb_per_split) nkb = g.kb_per_split;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int id = blockIdx.x; id < tiles_total && ok; id += gridDim.x) {
+        int z, y, n0, row0, cnt, kb0, nkb;
+        tile_info(id, z, y, n0, row0, cnt, kb0, nkb);
+        if (cnt <= 0 || nkb <= 0) continue;
+        const int cnt16 = (cnt + 15) & ~15;
+        const int w_row = (int)((long long)z * g.w_rows_per_seg) + n0;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(&bar_empty[s], ((it / S) & 1) ^ 1)) { s_error = 1; ok = false; break; }
+          unsigned char* st = stages + (size_t)s * stage_bytes;
+          mbar_expect_tx(&bar_full[s], w_bytes + (unsigned)cnt16 * BK * 2);
+          const int kx = (kb0 + kb) * BK;
+          tma_load_2d(st, &tm_w, &bar_full[s], kx, w_row);
+          for (int r16 = 0; r16 < cnt16; r16 += g.x_box)
+            tma_load_2d(st + w_bytes + (size_t)r16 * BK * 2, &tm_x, &bar_full[s], kx, row0 + r16);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int it = 0, t = 0;
+      bool ok = true;
+      for (int id = blockIdx.x; id < tiles_total && ok; id += gridDim.x) {
+        int z, y, n0, row0, cnt, kb0, nkb;
+        tile_info(id, z, y, n0, row0, cnt, kb0, nkb);
+        if (cnt <= 0 || nkb <= 0) continue;
+        const int cnt16 = (cnt + 15) & ~15;
+        const int buf = t & 1;
+        // the epilogue warps must have drained this accumulator (two tiles ago)
+        if (!mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1)) { s_error = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(cnt16 >> 3) << 17) | ((unsigned)(BF >> 4) << 24);
+        const unsigned acc = tmem_base + (unsigned)buf * ncols_buf;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(&bar_full[s], (it / S) & 1)) { s_error = 1; ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          unsigned char* st = stages + (size_t)s * stage_bytes;
+          const unsigned long long da = umma_desc(st), db = umma_desc(st + w_bytes);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4)
+            umma_bf16(acc, da + 2ull * k4, db + 2ull * k4, idesc, (kb | k4) != 0);
+          umma_commit(&bar_empty[s]);
+        }
+        umma_commit(&acc_full[buf]);
+        ++t;
+      }
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5 ----------------
+    const int q = warp & 3;
+    const bool vec_ok = MODE == TC_PARTIAL
+                            ? (g.N % 4 == 0 && ((uintptr_t)g.partial & 15) == 0)
+                            : (g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 15) == 0);
+    const bool swi_ok = MODE == TC_SWIGLU && g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 7) == 0;
+    int t = 0, chunk_no = 0;
+    for (int id = blockIdx.x; id < tiles_total; id += gridDim.x) {
+      int z, y, n0, row0, cnt, kb0, nkb;
+      tile_info(id, z, y, n0, row0, cnt, kb0, nkb);
+      if (cnt <= 0 || nkb <= 0) continue;
+      const int buf = t & 1;
+      const bool acc_ok = mbar_wait(&acc_full[buf], (t >> 1) & 1);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (!acc_ok) s_error = 1;
+      int go;
+      {
+        const int mine = (acc_ok && *(volatile int*)&s_error == 0) ? 1 : 0;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.b32 q, %1, 0;\n\t"
+            "bar.red.and.pred p, 1, 128, q;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(go) : "r"(mine) : "memory");
+      }
+      if (!go) break;                    // uniform over the four warps
+      const int nchunk = (cnt + 31) >> 5;
+      for (int ch = 0; ch < nchunk; ++ch, ++chunk_no) {
+        unsigned r[32];
+        tmem_ld32(tmem_base + (unsigned)buf * ncols_buf + ((unsigned)(q * 32) << 16) + (unsigned)(ch * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (ch == nchunk - 1) {          // accumulator read out: hand the buffer back before the stores
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+        tc_epilogue_chunk<MODE>(g, r, base, ch, chunk_no & 1, q, lane, n0, row0, cnt, y, vec_ok, swi_ok);
+      }
+      ++t;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (s_error) {
+    if (threadIdx.x == 0 && g.error_flag) atomicExch(g.error_flag, 1);
+    const long long t0 = clock64();
+    while ((unsigned long long)(clock64() - t0) < 200000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -580,6 +784,9 @@ inline bool gemm_tc_cluster_supported(const GemmArgs& g, int mode, const tc_deta
   }
   return g.ldc % 4 == 0;
 }
+
+// read on every launch so that a test can switch it
+inline int persist_level_env() { const char* e = getenv("VN_TC_PERSIST"); return e ? atoi(e) : 0; }
 
 // Supported: bf16 operands, K-major, 16-byte aligned rows, tokens <= 256, A rows contiguous (no gather).
 inline bool gemm_tc_supported(const GemmArgs& g) {
@@ -646,6 +853,37 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   }
   dim3 grid(ceil_div(g.N, BF), gy, g.nseg);
   const char* name = g.tag ? g.tag : "gemm_tc_kernel";
+  // Persistent variant (one CTA per SM walks the tiles, accumulator double buffered), opt-in: VN_TC_PERSIST=1 for
+  // GEMMs with more tiles than two per SM, =2 for every GEMM it supports.  Measured on B200 it matches the
+  // one-tile-per-CTA kernel within 3 % on the LM head and the expert GEMMs (their limit is the rate at which TMA
+  // delivers weight plus re-fetched token tiles, about 7.3 TB/s over all SMs), so it is not the default.
+  const int persist_level = persist_level_env();
+  const long long tiles_total = (long long)grid.x * grid.y * grid.z;
+  if (persist_level > 0 && (mode == TC_STORE || mode == TC_SWIGLU || mode == TC_PARTIAL) &&
+      (persist_level >= 2 || tiles_total > 2ll * ctx->sm_count) && tiles_total < (1ll << 30)) {
+    const size_t stages_max = (216 * 1024 - PERSIST_STAGING) / stage_bytes;
+    if (stages_max >= 2) {
+      const size_t pbudget = PERSIST_STAGING + std::min<size_t>(8, stages_max) * stage_bytes;
+      a.smem_budget = (unsigned)pbudget;
+      const size_t psmem = pbudget + 1024;
+      static unsigned long long pattr_set = 0;
+      if (!((pattr_set >> (ctx->device & 63)) & 1ull)) {
+        VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_persist_kernel<TC_PARTIAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_persist_kernel<TC_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_persist_kernel<TC_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        pattr_set |= 1ull << (ctx->device & 63);
+      }
+      const int pgrid = (int)std::min<long long>(tiles_total, ctx->sm_count);
+      const int tx = (int)grid.x, ty = (int)grid.y, tt = (int)tiles_total;
+      if (mode == TC_STORE)
+        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_STORE>, pgrid, TC_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
+      else if (mode == TC_SWIGLU)
+        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_SWIGLU>, pgrid, TC_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
+      else
+        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_PARTIAL>, pgrid, TC_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
+      return VN_OK;
+    }
+  }
   switch (mode) {
     case TC_PARTIAL: VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_PARTIAL>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
     case TC_SWIGLU:  VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;

@@ -545,7 +545,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       RouteArgs r;
       r.h = m->h32; r.gates = L.router; r.slot_expert = m->slot_expert; r.slot_w = m->slot_w; r.part_w = m->part_w;
       r.expert_count = m->expert_count; r.M = M; r.D = D; r.P = c.P; r.E = c.E; r.top_k = c.top_k;
-      VN_LAUNCH_PDL(ctx, mod_route_kernel, M, 128, 0, r);
+      VN_LAUNCH_PDL(ctx, mod_route_kernel, M, 512, 0, r);
       VN_LAUNCH_PDL(ctx, mod_dispatch_kernel<T>, M * S, 128, 0, (const T*)m->h, m->slot_expert, m->expert_count,
                     m->expert_off, m->expert_cur, m->slot_pos, (T*)m->hs, ne, S, D);
       g = GemmArgs();

@@ -322,10 +322,10 @@ struct RouteArgs {
   int M, D, P, E, top_k;
 };
 
-__global__ void __launch_bounds__(128) mod_route_kernel(RouteArgs r) {
+__global__ void __launch_bounds__(512) mod_route_kernel(RouteArgs r) {
   pdl_trigger();
   pdl_wait();
-  // one CTA per token: the 4 warps split the gate rows, warp 0 then selects
+  // one CTA per token: the warps split the gate rows (one or two each), warp 0 then selects
   __shared__ float lg[64];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(128) mod_route_kernel(RouteArgs r) {
 #pragma unroll
   for (int i = 0; i < 16; ++i)
     xr[i] = i < n4 ? *reinterpret_cast<const float4*>(x + i * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int g = warp; g < n_logit; g += 4) {
+  for (int g = warp; g < n_logit; g += (int)(blockDim.x >> 5)) {
     const float* w = r.gates + (long long)g * r.D;
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
