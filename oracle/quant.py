@@ -58,16 +58,18 @@ def quantize_int4(w):
 
 
 def quantize_int4_g128(w, group=128):
-    """Returns (packed uint8 [out, in/2], scales float32 (bf16-representable) [out, in/group])."""
+    """Returns (packed uint8 [out, in/2], scales float32 (bf16-representable) [out, ceil(in/group)]).
+    A last group shorter than `group` (the SwiGLU hidden 2752 = 21.5 groups) takes its scale from the
+    features it has."""
     w = np.asarray(w, dtype=F32)
     out_dim, in_dim = w.shape
-    if in_dim % group:
-        raise ValueError("in_features must be a multiple of the group size")
-    g = w.reshape(out_dim, in_dim // group, group)
+    pad = (-in_dim) % group
+    wp = np.pad(w, ((0, 0), (0, pad))) if pad else w
+    g = wp.reshape(out_dim, -1, group)
     max_abs = np.max(np.abs(g), axis=-1, keepdims=True)
     scale = bf16_round((np.where(max_abs > 0, max_abs, 1.0) / 7.0).astype(F32))
-    q = np.round(g / scale).clip(-8, 7).astype(np.int8).reshape(out_dim, in_dim)
-    return pack_int4(q), scale[..., 0]
+    q = np.round(g / scale).clip(-8, 7).astype(np.int8).reshape(out_dim, in_dim + pad)[:, :in_dim]
+    return pack_int4(np.ascontiguousarray(q)), scale[..., 0]
 
 
 def dequant_int8(q, scale):
@@ -80,7 +82,10 @@ def dequant_int4(packed, scale, in_dim):
 
 def dequant_int4_g128(packed, scales, in_dim, group=128):
     q = unpack_int4(packed, in_dim).astype(F32)
-    return (q.reshape(q.shape[0], -1, group) * scales[..., None]).reshape(q.shape[0], in_dim)
+    pad = (-in_dim) % group
+    if pad:
+        q = np.pad(q, ((0, 0), (0, pad)))
+    return (q.reshape(q.shape[0], -1, group) * scales[..., None]).reshape(q.shape[0], in_dim + pad)[:, :in_dim]
 
 
 def linear_int8(x, q, scale):

@@ -346,8 +346,8 @@ def test_weight_only_quantised_model(scheme):
     reference forward run on the dequantised weights; MoD + TriSparse, chain then cached continuation."""
     cfg = OM.mate_config(vocab_size=320, dim=128, n_layer=2, n_head=4, n_kv_head=2, window_size=16,
                          num_global_tokens=8, max_seq_len=128, init_std=0.08, num_dense_parts=2,
-                         num_experts_per_part=2, top_k=1, expert_hidden=128, mlp_hidden_multiple=3)
-    assert cfg.mlp_hidden % 128 == 0 and cfg.expert_hidden % 128 == 0
+                         num_experts_per_part=2, top_k=1, expert_hidden=192, mlp_hidden_multiple=3)
+    assert cfg.mlp_hidden % 128 == 0 and cfg.expert_hidden % 128 == 64    # expert w_down: a half last group
     sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=31, gate_std=1.0).items()}
     m = build(cfg, sd, "bf16")
     m.quantize(scheme)

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(BM * 2) gemm_mma_q_kernel(GemmArgs g) {
   const __nv_bfloat16* A = reinterpret_cast<const __nv_bfloat16*>(g.A);
   const unsigned char* W = reinterpret_cast<const unsigned char*>(g.W) +
                            (long long)z * (QMODE == 1 ? g.w_stride : g.w_stride / 2);
-  const int groups = QMODE == 3 ? g.K / 128 : 1;
+  const int groups = QMODE == 3 ? (g.K + 127) / 128 : 1;   // the last group may be half a group (K % 128 == 64)
   const float* scale = g.w_scale + (long long)z * g.ws_stride;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wm = warp / WARPS_N, wn = warp % WARPS_N;
@@ -224,8 +224,9 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
 __global__ void __launch_bounds__(128) quantize_g128_kernel(const __nv_bfloat16* __restrict__ w, int K,
                                                             unsigned char* __restrict__ q, float* __restrict__ scale) {
   const long long row = blockIdx.x;
-  const int grp = blockIdx.y, groups = K / 128;
-  const float v = __bfloat162float(w[row * K + grp * 128 + threadIdx.x]);
+  const int grp = blockIdx.y, groups = (K + 127) / 128;
+  const int col = grp * 128 + (int)threadIdx.x;            // a last group shorter than 128 is padded with zeros
+  const float v = col < K ? __bfloat162float(w[row * K + col]) : 0.f;
   float mx = fabsf(v);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -238,7 +239,7 @@ __global__ void __launch_bounds__(128) quantize_g128_kernel(const __nv_bfloat16*
   if (threadIdx.x == 0) scale[row * groups + grp] = sc;
   s_q[threadIdx.x] = fminf(fmaxf(rintf(__fdiv_rn(v, sc)), -8.f), 7.f);
   __syncthreads();
-  if (threadIdx.x < 64) {
+  if (threadIdx.x < 64 && grp * 128 + 2 * (int)threadIdx.x < K) {
     const int a = (int)s_q[2 * threadIdx.x], b = (int)s_q[2 * threadIdx.x + 1];
     q[row * (K / 2) + grp * 64 + threadIdx.x] = (unsigned char)((a & 0xf) | ((b & 0xf) << 4));
   }
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(128) quantize_g128_kernel(const __nv_bfloat16*
 
 inline bool gemm_mma_q_supported(const GemmArgs& g) {
   return g.wq >= 1 && g.wq <= 3 && g.K % 64 == 0 && g.lda % 8 == 0 && g.ldw % 32 == 0 && g.ldw_k == 1 &&
-         ((uintptr_t)g.A & 15) == 0 && ((uintptr_t)g.W & 15) == 0 && (g.wq != 3 || g.K % 128 == 0) &&
+         ((uintptr_t)g.A & 15) == 0 && ((uintptr_t)g.W & 15) == 0 &&
          (g.seg_cnt != nullptr || g.nseg == 1);
 }
 

@@ -292,7 +292,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
   auto pick = [&](GemmArgs& g, void* dense, void* q, float* qs, long long rows_per_seg) {
     if (m->qmode) {
       g.W = q; g.w_scale = qs; g.wq = m->qmode;
-      g.ws_stride = rows_per_seg * (m->qmode == 3 ? g.K / 128 : 1);
+      g.ws_stride = rows_per_seg * (m->qmode == 3 ? (g.K + 127) / 128 : 1);
     } else {
       g.W = dense;
     }
@@ -804,17 +804,17 @@ int32_t vn_model_finalize(vn_model* m) {
 static int32_t quantize_matrix(vn_model* m, void** dense, long long rows, int K, int mode, void** q, float** qs,
                                bool release, uint64_t* bytes) {
   vn_ctx* ctx = m->ctx;
-  VN_REQUIRE(ctx, K % 64 == 0 && (mode != 3 || K % 128 == 0), "in_features %d not supported by the quantised kernels", K);
+  VN_REQUIRE(ctx, K % 64 == 0, "in_features %d not supported by the quantised kernels (multiple of 64 needed)", K);
   const size_t qbytes = (size_t)rows * (mode == 1 ? K : K / 2);
-  const size_t nscale = (size_t)rows * (mode == 3 ? K / 128 : 1);
+  const size_t nscale = (size_t)rows * (mode == 3 ? (K + 127) / 128 : 1);
   TRY(dev_alloc(ctx, q, qbytes));
   TRY(dev_alloc(ctx, (void**)qs, nscale * 4));
   const __nv_bfloat16* w = (const __nv_bfloat16*)*dense;
   if (mode == 1) VN_LAUNCH(ctx, mmaq_detail::quantize_rows_kernel<1>, (unsigned)rows, 256, 0, w, K, (unsigned char*)*q, *qs);
   else if (mode == 2) VN_LAUNCH(ctx, mmaq_detail::quantize_rows_kernel<2>, (unsigned)rows, 256, 0, w, K, (unsigned char*)*q, *qs);
   else {
-    VN_REQUIRE(ctx, rows < (1ll << 31) && K / 128 < 65536, "matrix too large");
-    dim3 grid((unsigned)rows, K / 128);
+    VN_REQUIRE(ctx, rows < (1ll << 31) && (K + 127) / 128 < 65536, "matrix too large");
+    dim3 grid((unsigned)rows, (K + 127) / 128);
     VN_LAUNCH(ctx, mmaq_detail::quantize_g128_kernel, grid, 128, 0, w, K, (unsigned char*)*q, *qs);
   }
   *bytes += qbytes + nscale * 4;
