@@ -172,6 +172,12 @@ int32_t vn_model_finalize(vn_model* m);
  * quantize.py:187-214), "int4" (per output channel, :231-258), "int4g128" */
 int32_t vn_model_quantize(vn_model* m, const char* scheme);
 int32_t vn_model_param_bytes(vn_model* m, uint64_t* out);
+/* Device-side conditions raised by forwards since the last call, read after a stream synchronisation and
+ * cleared: *bad_token != 0 when a token id outside [0, vocab) was met (the kernels clamp it instead of reading
+ * outside the embedding table; the reference raises IndexError from NumPy fancy indexing, vnnn.py:453-460);
+ * *wait_timeout != 0 when a bounded wait inside a kernel ran out (the affected logits are undefined).
+ * Returns VN_OK when both are clear, VN_ERR_INDEX for a bad token, VN_ERR_TIMEOUT for a timeout. */
+int32_t vn_model_status(vn_model* m, int32_t* bad_token, int32_t* wait_timeout);
 
 /* KV cache: per layer K and V of shape [max_batch, max_seq, n_kv_head, head_dim]
  * with per-sequence lengths (verse_nex/kv_cache_parallel.py:42-283). */

@@ -222,6 +222,9 @@ def test_errors():
         cache.reset_seq(3)
     with pytest.raises(ValueError):
         m.forward_cached(np.zeros((2, 2), np.int64), cache)           # batch larger than the cache
+    with pytest.raises(IndexError):                                   # token id outside the vocabulary
+        m(np.array([[1, 2, 10 ** 6]], np.int64))
+    m.check()                                                         # the flag was cleared by the raise
     m2 = vn.VerseNexLM(vocab_size=16, dim=16, n_layer=1, n_head=2)
     with pytest.raises(ValueError):
         m2.finalize()                                                 # tensors missing

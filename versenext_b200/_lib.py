@@ -30,6 +30,7 @@ _EXC = {
     VN_ERR_INVALID: ValueError,        # speculative.py:188-196 rank / batch mismatch
     VN_ERR_OOM: MemoryError,
     VN_ERR_OVERFLOW: RuntimeError,     # kv_cache_parallel.py:152-159
+    VN_ERR_TIMEOUT: RuntimeError,      # a bounded wait inside a kernel ran out
     VN_ERR_INDEX: IndexError,          # kv_cache_parallel.py:136-139
     VN_ERR_UNSUPPORTED: NotImplementedError,
 }
@@ -90,6 +91,7 @@ PROTOTYPES = {
     "vn_model_finalize": [_p],
     "vn_model_quantize": [_p, C.c_char_p],
     "vn_model_param_bytes": [_p, C.POINTER(_u64)],
+    "vn_model_status": [_p, C.POINTER(_i32), C.POINTER(_i32)],
     "vn_kv_create": [_p, _i32, _i32, C.POINTER(_p)],
     "vn_kv_destroy": [_p],
     "vn_kv_reset_seq": [_p, _i32],

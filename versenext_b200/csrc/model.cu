@@ -876,6 +876,28 @@ int32_t vn_model_param_bytes(vn_model* m, uint64_t* out) {
   return VN_OK;
 }
 
+int32_t vn_model_status(vn_model* m, int32_t* bad_token, int32_t* wait_timeout) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  int tok = 0, to = 0;
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (m->status) {
+    VN_CUDA(ctx, cudaMemcpyAsync(&tok, m->status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VN_CUDA(ctx, cudaMemsetAsync(m->status, 0, 4, ctx->stream));
+  }
+  if (m->tc_error) {
+    VN_CUDA(ctx, cudaMemcpyAsync(&to, m->tc_error, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VN_CUDA(ctx, cudaMemsetAsync(m->tc_error, 0, 4, ctx->stream));
+  }
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (bad_token) *bad_token = tok;
+  if (wait_timeout) *wait_timeout = to;
+  if (to) return vn_fail(ctx, VN_ERR_TIMEOUT, "a bounded wait inside a GEMM kernel ran out: results of the last forwards are undefined");
+  if (tok) return vn_fail(ctx, VN_ERR_INDEX, "token id outside [0, %d) met by a forward (clamped on the device)", m->cfg.vocab);
+  return VN_OK;
+}
+
 int32_t vn_kv_create(vn_model* m, int32_t max_batch, int32_t max_seq, vn_kv** out) {
   if (!m || !out) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
   vn_ctx* ctx = m->ctx;

@@ -205,6 +205,8 @@ class SpecEngine:
                 break
             for _ in range(max(1, need // (self.k + 1))):
                 self.step()
+        self.target.check()          # token ids in range, no kernel wait ran out
+        self.draft.check()
         new = self.tokens(max_new_tokens)
         stats = dict(rounds=self.rounds_run, proposed=self.rounds_run * self.k * self.B,
                      committed=int(self.counts().sum()))

@@ -158,6 +158,12 @@ class VerseNexLM:
         self.ctx._check(self.ctx.lib.vn_model_param_bytes(self.handle, C.byref(n)))
         return int(n.value)
 
+    def check(self):
+        """Raise what the forwards since the last check ran into on the device: IndexError for a token id outside
+        the vocabulary (as NumPy indexing does in the reference, vnnn.py:453-460), RuntimeError for a kernel
+        wait that ran out.  Synchronises the stream."""
+        self.ctx._check(self.ctx.lib.vn_model_status(self.handle, None, None))
+
     def load_tensor(self, name: str, array):
         a = np.ascontiguousarray(np.asarray(array), dtype=np.float32)
         shape = (C.c_int64 * max(a.ndim, 1))(*(a.shape if a.ndim else (1,)))
@@ -245,7 +251,9 @@ class VerseNexLM:
         if c is None or c.max_batch < B or c.max_seq < T:
             self._scratch_cache = c = self.new_cache(max(B, 1), max(T, self.max_seq_len))
         c.reset()
-        return Tensor(self.forward_cached(ids, c))
+        out = Tensor(self.forward_cached(ids, c))
+        self.check()
+        return out
 
     __call__ = forward
 
@@ -285,6 +293,7 @@ class VerseNexLM:
                 break
             logits = self.forward_cached(nxt.reshape(B, 1), cache, last_only=True)
             cache.commit(1, np.ones(B, np.int32))
+        self.check()
         res = np.concatenate(out, axis=1)
         if eos_id is not None and res.shape[1] > 0 and not np.all(res[:, -1] == eos_id):
             res = np.concatenate([res, np.full((B, 1), eos_id, dtype=res.dtype)], axis=1)
