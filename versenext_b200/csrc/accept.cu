@@ -96,74 +96,127 @@ __device__ __forceinline__ double warp_sum(double v) {
 }
 
 // ---- kernel A: streaming statistics ---------------------------------------
-// One work item = 4096 consecutive logits of one row; 256 threads x 4 x float4.
-template <bool VEC4>
+// One chunk = 4096 consecutive logits of one row (256 threads x 4 x float4); a work item is a PAIR of
+// neighbouring chunks, so that the two block-wide reductions (max, then sum of exp) and their barriers are paid
+// once per 8192 logits and every thread has eight 16-byte loads in flight.  Each chunk still gets its own
+// (max, argmax, sum) record, computed exactly as if it were alone.  The arg-max index is only tracked for the
+// greedy rule and exp only for the stochastic one.
+template <bool VEC4, bool GREEDY>
 __global__ void __launch_bounds__(STATS_THREADS)
-accept_stats_kernel(RowSet rs, int B, int nchunks, float temp, int greedy, Partial* __restrict__ out) {
-  __shared__ float sm_m[STATS_THREADS / 32];
-  __shared__ int sm_a[STATS_THREADS / 32];
-  __shared__ double sm_s[STATS_THREADS / 32];
+accept_stats_kernel(RowSet rs, int B, int nchunks, float temp, Partial* __restrict__ out) {
+  __shared__ float sm_m[2][STATS_THREADS / 32];
+  __shared__ int sm_a[2][STATS_THREADS / 32];
+  __shared__ double sm_s[2][STATS_THREADS / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rows_per_seq = rs.np + rs.nq;
-  const long long nitems = (long long)B * rows_per_seq * nchunks;
-  const bool scale = (temp != 1.0f) && !greedy;
+  const int npairs = (nchunks + 1) >> 1;
+  const long long nitems = (long long)B * rows_per_seq * npairs;
+  const bool scale = (temp != 1.0f) && !GREEDY;
   for (long long item = blockIdx.x; item < nitems; item += gridDim.x) {
-    const int c = (int)(item % nchunks);
-    const int r = (int)(item / nchunks);
+    const int pi = (int)(item % npairs);
+    const int r = (int)(item / npairs);
     const float* row = row_ptr(rs, r / rows_per_seq, r % rows_per_seq);
-    const int start = c * CHUNK;
-    float x[16];
+    const bool two = 2 * pi + 1 < nchunks;            // uniform over the CTA
+    float x[2][16];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int idx = start + u * (STATS_THREADS * 4) + tid * 4;
-      if (VEC4 && idx + 3 < rs.V) {
-        float4 v = __ldcs(reinterpret_cast<const float4*>(row + idx));
-        x[u * 4 + 0] = v.x; x[u * 4 + 1] = v.y; x[u * 4 + 2] = v.z; x[u * 4 + 3] = v.w;
-      } else {
+    for (int h = 0; h < 2; ++h) {
+      const int start = (2 * pi + h) * CHUNK;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) x[u * 4 + e] = (idx + e < rs.V) ? __ldcs(row + idx + e) : -CUDART_INF_F;
+      for (int u = 0; u < 4; ++u) {
+        const int idx = start + u * (STATS_THREADS * 4) + tid * 4;
+        if (VEC4 && idx + 3 < rs.V && (h == 0 || two)) {
+          float4 v = __ldcs(reinterpret_cast<const float4*>(row + idx));
+          x[h][u * 4 + 0] = v.x; x[h][u * 4 + 1] = v.y; x[h][u * 4 + 2] = v.z; x[h][u * 4 + 3] = v.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            x[h][u * 4 + e] = (idx + e < rs.V && (h == 0 || two)) ? __ldcs(row + idx + e) : -CUDART_INF_F;
+        }
       }
     }
     if (scale) {
 #pragma unroll
-      for (int e = 0; e < 16; ++e) x[e] = __fdiv_rn(x[e], temp);
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) x[h][e] = __fdiv_rn(x[h][e], temp);
     }
-    float m = -CUDART_INF_F;
-    int a = 0x7fffffff;
+    float m[2];
+    int a[2];
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
+    for (int h = 0; h < 2; ++h) {
+      m[h] = -CUDART_INF_F;
+      a[h] = 0x7fffffff;
+      const int start = (2 * pi + h) * CHUNK;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int idx = start + u * (STATS_THREADS * 4) + tid * 4 + e;
-        if (x[u * 4 + e] > m) { m = x[u * 4 + e]; a = idx; }
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (GREEDY) {
+            const int idx = start + u * (STATS_THREADS * 4) + tid * 4 + e;
+            if (x[h][u * 4 + e] > m[h]) { m[h] = x[h][u * 4 + e]; a[h] = idx; }
+          } else {
+            m[h] = fmaxf(m[h], x[h][u * 4 + e]);
+          }
+        }
+    }
+    if (GREEDY) {
+      warp_argmax(m[0], a[0]);
+      warp_argmax(m[1], a[1]);
+    } else {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        m[0] = fmaxf(m[0], __shfl_xor_sync(0xffffffffu, m[0], o));
+        m[1] = fmaxf(m[1], __shfl_xor_sync(0xffffffffu, m[1], o));
       }
-    warp_argmax(m, a);
-    if (lane == 0) { sm_m[warp] = m; sm_a[warp] = a; }
-    __syncthreads();
-    m = sm_m[0]; a = sm_a[0];
-#pragma unroll
-    for (int w = 1; w < STATS_THREADS / 32; ++w) {
-      float om = sm_m[w]; int oa = sm_a[w];
-      if (om > m || (om == m && oa < a)) { m = om; a = oa; }
     }
-    double s = 0.0;
-    if (!greedy) {
-      float sf = 0.f;
+    if (lane == 0) { sm_m[0][warp] = m[0]; sm_m[1][warp] = m[1]; if (GREEDY) { sm_a[0][warp] = a[0]; sm_a[1][warp] = a[1]; } }
+    __syncthreads();
 #pragma unroll
-      for (int e = 0; e < 16; ++e) sf += expf(x[e] - m);
-      s = warp_sum((double)sf);
-      if (lane == 0) sm_s[warp] = s;
+    for (int h = 0; h < 2; ++h) {
+      m[h] = sm_m[h][0];
+      if (GREEDY) a[h] = sm_a[h][0];
+#pragma unroll
+      for (int w = 1; w < STATS_THREADS / 32; ++w) {
+        const float om = sm_m[h][w];
+        if (GREEDY) {
+          const int oa = sm_a[h][w];
+          if (om > m[h] || (om == m[h] && oa < a[h])) { m[h] = om; a[h] = oa; }
+        } else {
+          m[h] = fmaxf(m[h], om);
+        }
+      }
+    }
+    if (!GREEDY) {
+      float sf0 = 0.f, sf1 = 0.f;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) sf0 += expf(x[0][e] - m[0]);
+      if (two) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) sf1 += expf(x[1][e] - m[1]);
+      }
+      const double s0 = warp_sum((double)sf0), s1 = warp_sum((double)sf1);
+      if (lane == 0) { sm_s[0][warp] = s0; sm_s[1][warp] = s1; }
     }
     __syncthreads();
-    if (tid == 0) {
+    if (tid < 2 && (tid == 0 || two)) {
       double tot = 0.0;
-      if (!greedy)
+      if (!GREEDY)
 #pragma unroll
-        for (int w = 0; w < STATS_THREADS / 32; ++w) tot += sm_s[w];
-      Partial p; p.m = m; p.arg = a; p.s = tot;
-      out[item] = p;
+        for (int w = 0; w < STATS_THREADS / 32; ++w) tot += sm_s[tid][w];
+      Partial p; p.m = tid == 0 ? m[0] : m[1]; p.arg = GREEDY ? (tid == 0 ? a[0] : a[1]) : 0; p.s = tot;
+      out[(long long)r * nchunks + 2 * pi + tid] = p;
     }
   }
+}
+
+// the four instantiations behind one call
+static int32_t launch_accept_stats(vn_ctx* ctx, bool vec, bool greedy, int grid, const RowSet& rs, int B, int nchunks,
+                                   float temp, Partial* part) {
+  if (vec && greedy) VN_LAUNCH(ctx, (accept_stats_kernel<true, true>), grid, STATS_THREADS, 0, rs, B, nchunks, temp, part);
+  else if (vec) VN_LAUNCH(ctx, (accept_stats_kernel<true, false>), grid, STATS_THREADS, 0, rs, B, nchunks, temp, part);
+  else if (greedy) VN_LAUNCH(ctx, (accept_stats_kernel<false, true>), grid, STATS_THREADS, 0, rs, B, nchunks, temp, part);
+  else VN_LAUNCH(ctx, (accept_stats_kernel<false, false>), grid, STATS_THREADS, 0, rs, B, nchunks, temp, part);
+  return VN_OK;
 }
 
 // ---- kernel B: per-sequence decision --------------------------------------
@@ -929,8 +982,7 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
                    (!rs.nq || (aligned16(q) && (q_sb % 4 == 0) && (q_si % 4 == 0)));
   const long long nitems = (long long)n_part;
   const int grid = (int)std::min<long long>(nitems, (long long)ctx->sm_count * 8);
-  if (vec) VN_LAUNCH(ctx, accept_stats_kernel<true>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
-  else     VN_LAUNCH(ctx, accept_stats_kernel<false>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
+  { const int32_t st_ = launch_accept_stats(ctx, vec, greedy, grid, rs, B, nchunks, temp, part); if (st_) return st_; }
   VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_acc, u_smp, seed, offset,
             ctx->offset_src, temp, (int)greedy, bonus, smp_purpose, pos_base, dec, out_len, o64);
   if (!greedy) {
@@ -1047,8 +1099,7 @@ int32_t vn_accept_noalloc(vn_ctx* ctx, const float* p_logits_dev, const float* q
   // statistic, decision and mass entry that is read was written earlier in this same call), so nothing left
   // over from the previous call has to be cleared
   const int grid = (int)std::min<long long>((long long)n_part, (long long)ctx->sm_count * 8);
-  if (vec) VN_LAUNCH(ctx, accept_stats_kernel<true>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
-  else     VN_LAUNCH(ctx, accept_stats_kernel<false>, grid, STATS_THREADS, 0, rs, B, nchunks, temp, (int)greedy, part);
+  { const int32_t st_ = launch_accept_stats(ctx, vec, greedy, grid, rs, B, nchunks, temp, part); if (st_) return st_; }
   VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_accept_dev, u_sample_dev, seed, offset,
             (const unsigned*)nullptr, temp, (int)greedy, bonus, 1, 0, dec, out_len_dev, o64);
   if (!greedy) {
