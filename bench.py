@@ -43,6 +43,12 @@ sys.path.insert(0, ROOT)
 ACCEPT = dict(B=64, k=4, V=248320, seed=1234, temperature=1.0)
 
 
+# DRAM bytes of one verify + accept step of the default workload, summed over its kernels from the ncu capture
+# summarised in profiles/spec_step_dram_traffic.txt (B=32, ctx about 550).  ncu flushes the caches before every
+# kernel, so partial tiles and logits that the real run finds in L2 count as DRAM here: an upper bound.
+SPEC_STEP_TRAFFIC = 4264900000
+
+
 def accept_bytes(B, k, V):
     return B * (k + 1) * V * 4 + B * k * V * 4
 
@@ -339,7 +345,7 @@ def run_spec(args):
     top = sorted(rep.items(), key=lambda kv: -kv[1]["ms"])
     roofline = {"bound": "hbm", "kernel": "verify+sample step (all kernels of the target forward and acceptance)",
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": f"of {peak_kind}", "traffic": None, "step_ms": step_ms, "algorithmic_bytes": nbytes,
+                "peak_kind": f"of {peak_kind}", "traffic": SPEC_STEP_TRAFFIC, "step_ms": step_ms, "algorithmic_bytes": nbytes,
                 "gemm_ms": gemm_ms, "gemm_weight_gbs": MATE_PARAMS * 2 / (gemm_ms * 1e-3) / 1e9,
                 "kernel_share": {n: v["ms"] / n_prof / prof_ms for n, v in top},
                 "kernel_ms_per_step": {n: v["ms"] / n_prof for n, v in top},
@@ -496,7 +502,7 @@ def run_accept(args):
     # profiles/accept_stats_kernel_ncu_full.txt (dram__bytes_read.sum + dram__bytes_write.sum); it scales with
     # the rows processed, so it is only quoted for the configuration that was captured
     if (B, k, V) == (64, 4, 248320):
-        roofline["traffic"] = 572150784 + 4005120
+        roofline["traffic"] = 572177920 + 4024064
         roofline["traffic_source"] = "profiles/accept_stats_kernel_ncu_full.txt"
 
     # ---- end to end: pinned host logits -> device -> op -> host result, every step

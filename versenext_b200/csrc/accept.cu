@@ -677,7 +677,7 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* __rest
 
 // Merge the slices' lists of one row: the global k-th largest value is found among the candidates by rank
 // counting, everything >= it is kept; slices are in ascending token order, so the output is too.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_k, TopkRow* __restrict__ out) {
   pdl_trigger();
   pdl_wait();
@@ -959,7 +959,7 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
     TopkRow* rows = (TopkRow*)ws;                 // merged lists [n_rows]
     TopkRow* parts = rows + n_rows;               // per-slice lists [n_rows * chunks]
     VN_LAUNCH_PDL(ctx, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, chunks > 1 ? parts : rows);
-    if (chunks > 1) VN_LAUNCH_PDL(ctx, accept_topk_merge_kernel, n_rows, 256, 0, parts, chunks, top_k, rows);
+    if (chunks > 1) VN_LAUNCH_PDL(ctx, accept_topk_merge_kernel, n_rows, 1024, 0, parts, chunks, top_k, rows);
     VN_LAUNCH_PDL(ctx, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, B, k, rs.np, rs.nq, rows, d64, u_acc, u_smp,
               seed, offset, ctx->offset_src, bonus, smp_purpose, pos_base, out_len, o64);
     return VN_OK;
