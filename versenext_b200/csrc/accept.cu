@@ -14,6 +14,7 @@
 // Top-k path: accept_topk_kernel reduces every row to its (token, scaled logit) list of the
 // entries >= the k-th largest value (radix select on order-preserving keys), then
 // accept_topk_decide_kernel applies the same rule on those short lists.
+#include <stdlib.h>
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -949,9 +950,11 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
 
   if (!greedy && top_k > 0 && top_k < V) {
     VN_REQUIRE(ctx, top_k <= KEEP_MAX, "top_k %d above the supported maximum %d", top_k, KEEP_MAX);
-    // slices per row: enough CTAs to fill the GPU, at least 8192 logits each
+    // slices per row: about one CTA per SM (measured best on B200: fewer, longer slices and a smaller merge beat
+    // two or four CTAs per SM), at least 8192 logits each
     const int n_rows = B * rows_per_seq;
-    int chunks = std::min(std::min(16, std::max(1, V / 8192)), std::max(1, ceil_div(2 * ctx->sm_count, n_rows)));
+    static const int topk_ctas_per_sm = [] { const char* e = getenv("VN_TOPK_CTAS_PER_SM"); return e ? std::max(1, atoi(e)) : 1; }();
+    int chunks = std::min(std::min(16, std::max(1, V / 8192)), std::max(1, ceil_div(topk_ctas_per_sm * ctx->sm_count, n_rows)));
     chunks = std::max(1, std::min(chunks, 2048 / std::max(top_k, 1)));
     void* ws;
     int32_t st = vn_workspace(ctx, sizeof(TopkRow) * (size_t)n_rows * (chunks + 1), &ws);
