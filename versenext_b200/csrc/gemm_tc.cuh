@@ -25,7 +25,8 @@ namespace tc_detail {
 
 constexpr int BF = 128;        // features per CTA (UMMA M)
 constexpr int BK = 64;         // K elements per stage = one 128-byte swizzle row
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;      // TMA warp, MMA warp, two groups of four epilogue warps
+constexpr int PERSIST_THREADS = 192; // persistent variant: one epilogue group
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;  // ~1 s
 
 // RoPE + KV-cache append applied to the q | k | v projection (same meaning as in rope_append_kernel)
@@ -163,11 +164,12 @@ __device__ __forceinline__ float4 ld_dsmem_f4(unsigned local_addr, unsigned rank
 
 // Epilogue of one 32-token chunk of the accumulator (r[i] = feature f of token m0 + i for this thread).
 // `base` points at 32 KB of shared memory for two staging tiles (`buf` selects one; callers alternate so that a
-// tile is not rewritten while another warp still reads it).  split_y selects the slice of the split-K workspace.
+// tile is not rewritten while another warp still reads it) shared by the four warps that meet at named barrier
+// `bar_id`.  split_y selects the slice of the split-K workspace.
 template <int MODE>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigned (&r)[32], unsigned char* base,
-                                                  int ch, int buf, int q, int lane, int n0, int row0, int cnt,
-                                                  int split_y, bool vec_ok, bool swi_ok) {
+                                                  int ch, int buf, int bar_id, int q, int lane, int n0, int row0,
+                                                  int cnt, int split_y, bool vec_ok, bool swi_ok) {
   const int f = q * 32 + lane, n = n0 + f;
   const int m0 = ch * 32;
   const int mrem = cnt - m0;               // tokens left from this chunk on (>= 1)
@@ -188,7 +190,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
         float* tile = reinterpret_cast<float*>(base) + buf * (32 * BF);
 #pragma unroll
         for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]) + bias;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
         const int c4 = lane * 4;
         if (n0 + c4 < g.N) {                 // N % 4 == 0: a float4 is inside or outside as a whole
 #pragma unroll
@@ -211,7 +213,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
         float* tile = reinterpret_cast<float*>(base) + buf * (32 * BF);
 #pragma unroll
         for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
         const int c4 = lane * 4;
         if (n0 + c4 + 3 < g.N) {
 #pragma unroll 2
@@ -380,8 +382,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       if (tr) tr[3] = clock_now();                          // last MMA issued
     }
   } else {
-    // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
+    // ---------------- epilogue: warps 2..9 in two groups of four (TMEM lane quarter = warp % 4); the groups take
+    // the 32-token chunks of the accumulator alternately, each with its own staging tiles and named barrier
     const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;
     const int f = q * 32 + lane;               // feature within the tile
     const int n = n0 + f;
     pdl_wait();
@@ -397,7 +401,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       asm volatile(
           "{\n\t.reg .pred p, q;\n\t"
           "setp.ne.b32 q, %1, 0;\n\t"
-          "bar.red.and.pred p, 1, 128, q;\n\t"
+          "bar.red.and.pred p, 1, 256, q;\n\t"
           "selp.u32 %0, 1, 0, p;\n\t}"
           : "=r"(go) : "r"(mine) : "memory");
     }
@@ -411,11 +415,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
                               : (g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 15) == 0);
       // paired outputs: rows of C start on an 8-byte boundary and N covers whole groups of four columns
       const bool swi_ok = MODE == TC_SWIGLU && g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 7) == 0;
-      for (int ch = 0; ch < nchunk; ++ch) {
+      for (int ch = grp; ch < nchunk; ch += 2) {
         unsigned r[32];
         tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        tc_epilogue_chunk<MODE>(g, r, base, ch, ch & 1, q, lane, n0, row0, cnt, (int)blockIdx.y, vec_ok, swi_ok);
+        tc_epilogue_chunk<MODE>(g, r, MODE >= TC_CL_STORE ? base : base + grp * (32 * 1024), ch, (ch >> 1) & 1, 2 + grp, q,
+                                lane, n0, row0, cnt, (int)blockIdx.y, vec_ok, swi_ok);
       }
     }
     if (tr && threadIdx.x == 64) tr[5] = clock_now();     // this warp's stores issued
@@ -424,7 +429,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     __syncwarp();            // the single-lane roles above rejoin their warps before the aligned barriers
     cluster_sync_all();
     if (warp >= 2 && *(volatile int*)&s_error == 0) {
-      const int q = warp & 3;
+      const int q = warp - 2;                       // eight warps share the rows
       const unsigned rank = cluster_rank(), S = cluster_size();
       const unsigned tile_addr = smem_u32(base);
       const int c4 = lane * 4, n = n0 + c4;
@@ -509,7 +514,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
         }
       };
-      for (int m = (int)rank + (int)S * q; m < cnt; m += (int)S * 4) {
+      for (int m = (int)rank + (int)S * q; m < cnt; m += (int)S * 8) {
         float4 pa[8];
         reduce_row(m, pa);
         finish(m, sum_row(pa));
@@ -546,7 +551,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 constexpr int PERSIST_STAGING = 32 * 1024;   // two staging tiles for the epilogue, in front of the stages
 
 template <int MODE>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(PERSIST_THREADS, 1)
 gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs g,
                        int tiles_x, int tiles_y, int tiles_total) {
   extern __shared__ unsigned char smem_raw[];
@@ -708,7 +713,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
-        tc_epilogue_chunk<MODE>(g, r, base, ch, chunk_no & 1, q, lane, n0, row0, cnt, y, vec_ok, swi_ok);
+        tc_epilogue_chunk<MODE>(g, r, base, ch, chunk_no & 1, 2, q, lane, n0, row0, cnt, y, vec_ok, swi_ok);
       }
       ++t;
     }
@@ -816,6 +821,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   size_t budget = std::min<size_t>(108 * 1024, stage_bytes * 8);
   budget = std::min(budget, std::max<size_t>(2, a.kb_per_split) * stage_bytes);
   budget = std::max(budget, 2 * stage_bytes);
+  budget = std::max<size_t>(budget, 64 * 1024);       // the epilogue stages four 16 KB tiles in the freed stage memory
   a.smem_budget = (unsigned)budget;
   a.epi = g.epi; a.c_bf16 = g.c_bf16;
   a.seg_off = g.seg_off; a.seg_cnt = g.seg_cnt;
@@ -876,11 +882,11 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
       const int pgrid = (int)std::min<long long>(tiles_total, ctx->sm_count);
       const int tx = (int)grid.x, ty = (int)grid.y, tt = (int)tiles_total;
       if (mode == TC_STORE)
-        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_STORE>, pgrid, TC_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
+        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_STORE>, pgrid, PERSIST_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
       else if (mode == TC_SWIGLU)
-        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_SWIGLU>, pgrid, TC_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
+        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_SWIGLU>, pgrid, PERSIST_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
       else
-        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_PARTIAL>, pgrid, TC_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
+        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_PARTIAL>, pgrid, PERSIST_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
       return VN_OK;
     }
   }
