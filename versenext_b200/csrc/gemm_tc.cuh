@@ -47,6 +47,8 @@ struct TcArgs {
   int ntok;                // UMMA N: tokens rounded up to 16
   int x_box;               // token rows per TMA box: ntok (one box) for a dense block, 16 in segmented mode
   unsigned smem_budget;    // bytes of stage memory behind the 1024-byte aligned base
+  int tma_out;             // fp32 output rows leave through TMA stores (dense PARTIAL / STORE only)
+  int out_bufs;            // 16 KB staging tiles per epilogue group for that
   int kb_per_split;        // k blocks (of 64) per blockIdx.y
   int epi, c_bf16;
   const int* seg_off;      // segmented mode (blockIdx.z = segment)
@@ -107,6 +109,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// one 32-token x 128-feature fp32 tile from shared memory to the output tensor (x = feature, y = row, z = slice);
+// rows and columns beyond the tensor are clipped by the hardware
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z) : "memory");
 }
 
 // K-major, 128-byte swizzle: 8-row groups of 1024 bytes (SBO = 1024 B -> 64), LBO unused (= 1), version 1
@@ -268,7 +277,8 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
 
 template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs g) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+               const __grid_constant__ CUtensorMap tm_out, TcArgs g) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ unsigned long long bar_full[8], bar_empty[8], bar_acc;
   __shared__ unsigned tmem_base_slot;
@@ -415,13 +425,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
                               : (g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 15) == 0);
       // paired outputs: rows of C start on an 8-byte boundary and N covers whole groups of four columns
       const bool swi_ok = MODE == TC_SWIGLU && g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 7) == 0;
+      const bool tma_out = (MODE == TC_PARTIAL || MODE == TC_STORE) && g.tma_out;   // uniform over the CTA
+      const bool issuer = ((warp - 2) & 3) == 0 && lane == 0;                        // one thread per group
       for (int ch = grp; ch < nchunk; ch += 2) {
         unsigned r[32];
         tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        tc_epilogue_chunk<MODE>(g, r, MODE >= TC_CL_STORE ? base : base + grp * (32 * 1024), ch, (ch >> 1) & 1, 2 + grp, q,
-                                lane, n0, row0, cnt, (int)blockIdx.y, vec_ok, swi_ok);
+        if (tma_out) {
+          // registers -> shared memory once, then the tile leaves asynchronously: the load/store units move every
+          // byte one time instead of three (staging store, staging load, global store)
+          const int jb = ch >> 1;
+          float* tile = reinterpret_cast<float*>(base + ((size_t)grp * g.out_bufs + (jb % g.out_bufs)) * (32 * BF * 4));
+          if (jb >= g.out_bufs) {           // the tile is being reused: its earlier store must have read it
+            if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+          }
+          const int f = q * 32 + lane;
+          const float bias = (MODE == TC_STORE && g.bias && n0 + f < g.N) ? g.bias[n0 + f] : 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]) + bias;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+          if (issuer) {
+            tma_store_3d(&tm_out, tile, n0, row0 + ch * 32, MODE == TC_PARTIAL ? (int)blockIdx.y : 0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        } else {
+          tc_epilogue_chunk<MODE>(g, r, MODE >= TC_CL_STORE ? base : base + grp * (32 * 1024), ch, (ch >> 1) & 1, 2 + grp,
+                                  q, lane, n0, row0, cnt, (int)blockIdx.y, vec_ok, swi_ok);
+        }
       }
+      if (tma_out && issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before exit
     }
     if (tr && threadIdx.x == 64) tr[5] = clock_now();     // this warp's stores issued
   }
@@ -749,6 +783,20 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// fp32 output [slices][rows][N] (row pitch ld, slice pitch slice_stride, in elements): box = 128 x 32 x 1, no swizzle
+inline bool make_out_map(CUtensorMap* out, const void* ptr, long long N, long long rows, long long slices, long long ld,
+                         long long slice_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)rows, (cuuint64_t)slices};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)slice_stride * 4};
+  cuuint32_t box[3] = {(cuuint32_t)BF, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // 2-D bf16 tensor [rows, K] with row pitch ld (elements); box = 64 x box_rows, 128-byte swizzle, zero fill
 inline bool make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
@@ -842,9 +890,28 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   }
   if (!plan.cluster_mode && (gy > 1 || plan.force_partial) && !plan.partial)
     return vn_fail(ctx, VN_ERR_INVALID, "split-K needs a workspace");
-  const size_t smem = budget + 1024;
   const int mode = plan.cluster_mode ? plan.cluster_mode
                    : a.partial ? TC_PARTIAL : g.epi == EPI_SWIGLU ? TC_SWIGLU : g.epi == EPI_ADD ? TC_ADD : TC_STORE;
+  // dense fp32 outputs leave through TMA stores (VN_TC_TMA_STORE=0: staged float4 stores instead)
+  static const bool tma_store_on = [] { const char* e = getenv("VN_TC_TMA_STORE"); return !(e && e[0] == '0'); }();
+  CUtensorMap tm_out = tm_x;      // placeholder when unused
+  a.tma_out = 0; a.out_bufs = 1;
+  if (tma_store_on && !g.seg_cnt && g.N >= BF && g.N % 4 == 0 && (mode == TC_PARTIAL || (mode == TC_STORE && !g.c_bf16))) {
+    const bool part = mode == TC_PARTIAL;
+    const float* optr = part ? a.partial : reinterpret_cast<const float*>(g.C);
+    const long long old_ = part ? g.N : g.ldc;
+    const long long slice = part ? a.partial_stride : (long long)g.M * old_;
+    const long long rows = part ? plan.rows_total : g.M;
+    if (((uintptr_t)optr & 15) == 0 && old_ % 4 == 0 && slice % 4 == 0 &&
+        make_out_map(&tm_out, optr, g.N, rows, part ? gy : 1, old_, slice)) {
+      const int per_group = (((g.M + 31) / 32) + 1) / 2;               // chunks the busier epilogue group drains
+      budget = std::max<size_t>(budget, (size_t)std::min(per_group, 3) * 2 * 32 * BF * 4);
+      a.smem_budget = (unsigned)budget;
+      a.out_bufs = (int)std::min<size_t>(per_group, budget / (2 * 32 * BF * 4));
+      a.tma_out = a.out_bufs >= 1 ? 1 : 0;
+    }
+  }
+  const size_t smem = budget + 1024;
   static unsigned long long attr_set = 0;
   if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
     VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_PARTIAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
@@ -891,14 +958,14 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
     }
   }
   switch (mode) {
-    case TC_PARTIAL: VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_PARTIAL>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    case TC_SWIGLU:  VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    case TC_ADD:     VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    case TC_CL_STORE:  VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    case TC_CL_SWIGLU: VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    case TC_CL_ADD:    VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    case TC_CL_QKV:    VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_QKV>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
-    default:         VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, a); break;
+    case TC_PARTIAL: VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_PARTIAL>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
+    case TC_SWIGLU:  VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
+    case TC_ADD:     VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
+    case TC_CL_STORE:  VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
+    case TC_CL_SWIGLU: VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
+    case TC_CL_ADD:    VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
+    case TC_CL_QKV:    VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_QKV>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
+    default:         VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
   }
   return VN_OK;
 }
