@@ -96,7 +96,7 @@ def mate_config(**over) -> Config:
 
 
 def small_config(**over) -> Config:
-    """BASELINE config 1: all-trisparse, alibi, no rope, dim 64, vocab 256."""
+    """The CPU-runnable small configuration: all-trisparse, alibi, no rope, dim 64, vocab 256."""
     kw = dict(vocab_size=256, dim=64, n_layer=2, n_head=4, n_kv_head=2,
               window_size=32, num_global_tokens=4, use_alibi=True, use_rope=False,
               max_seq_len=256, tie_weights=True)

@@ -18,7 +18,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("VERSENEXT_REFERENCE", "reference")
 sys.path[:0] = [os.path.join(REF, "packages", "verse_torch"),
                 os.path.join(REF, "packages", "verse_nex"), REPO]
 

@@ -47,7 +47,7 @@ def mini_cfg(**over):
 
 
 def test_small_config_logits_and_greedy_stream(golden):
-    """BASELINE config 1 with the reference's own initial weights: logits 1e-3, greedy stream bit-exact."""
+    """The small CPU-runnable configuration with the reference's own initial weights: logits 1e-3, greedy stream bit-exact."""
     g = golden("model_small.npz")
     cfg = OM.small_config()
     m = build(cfg, _sd(g, "a_t."))
