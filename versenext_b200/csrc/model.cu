@@ -458,9 +458,8 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
   TRY(ensure_partial(m, 1024));
   direct.error_flag = m->tc_error;
   // expert_count is zero between forwards: the combine kernel of every MoD layer leaves it so
-  VN_LAUNCH_PDL(ctx, embed_kernel<T>, M, 128, 0, (const long long*)tokens, (const T*)m->emb, m->x, D, c.vocab, emb_scale,
-            m->status);
-  VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, m->layers[0].norm1, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
+  VN_LAUNCH_PDL(ctx, embed_norm_kernel<T>, M, 256, 0, (const long long*)tokens, (const T*)m->emb, m->x,
+                m->layers[0].norm1, (T*)m->h, D, c.vocab, emb_scale, 1e-6f, m->status);
   for (int li = 0; li < c.n_layer; ++li) {
     Layer& L = m->layers[li];
     const bool mod = L.kind == 1;

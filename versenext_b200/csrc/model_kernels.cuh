@@ -39,6 +39,40 @@ __global__ void embed_kernel(const long long* __restrict__ tokens, const T* __re
   for (int d = threadIdx.x; d < D; d += blockDim.x) x[(long long)row * D + d] = to_f<T>(e[d]) * scale;
 }
 
+// ---- embedding gather + scale fused with the first block's RMSNorm (decode / verify path: one launch less)
+template <typename T>
+__global__ void __launch_bounds__(256) embed_norm_kernel(const long long* __restrict__ tokens, const T* __restrict__ emb,
+                                                         float* __restrict__ x, const float* __restrict__ w,
+                                                         T* __restrict__ y, int D, int V, float scale, float eps,
+                                                         int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float sm[8];
+  const int row = blockIdx.x;
+  long long tok = tokens[row];
+  if (tok < 0 || tok >= V) {  // record and clamp: never read outside the table
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    tok = tok < 0 ? 0 : V - 1;
+  }
+  const T* e = emb + tok * D;
+  float* xr = x + (long long)row * D;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += 256) {
+    const float v = to_f<T>(e[d]) * scale;
+    xr[d] = v;
+    ss += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += sm[i];
+  const float r = sqrtf(tot / (float)D + eps);
+  for (int d = threadIdx.x; d < D; d += 256) y[(long long)row * D + d] = from_f<T>(xr[d] / r * w[d]);
+}
+
 // ---- RMSNorm: y = x / sqrt(mean(x^2) + eps) * w (vnnn.py:501-505).  Source row = i * row_mul + row_add; optional fp32 copy.
 template <typename T>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
