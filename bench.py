@@ -137,13 +137,25 @@ def dist_setup(n_gpus):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     dist = None
     if world > 1:
-        # NCCL writes its version banner and debug lines to stdout: send them to stderr so that
-        # stdout carries the one JSON line only.
+        # NCCL prints its version banner (and, at higher debug levels, more) to file descriptor 1 when the first
+        # communicator comes up.  Stdout must carry the one JSON line only, so descriptor 1 points at stderr while
+        # the process group and its first collective are set up.
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import torch
         import torch.distributed as dist_mod
         torch.cuda.set_device(local)
-        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+            t = torch.zeros(1, device=f"cuda:{local}")
+            dist_mod.all_reduce(t)
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
         dist = dist_mod
     return world, rank, local, dist
 
