@@ -254,6 +254,19 @@ __global__ void accept_decide_kernel(RowSet rs, int B, int k, int nchunks, const
     s = warp_sum(s);
     if (lane == 0) { r_m[j] = m; r_a[j] = a; r_s[j] = s; }
   }
+  // the draft tokens' logits and the acceptance uniforms of all k positions in one round trip: the serial
+  // accept loop below then runs on shared memory
+  __shared__ long long s_x[MAX_K];
+  __shared__ float s_lp[MAX_K], s_lq[MAX_K], s_u[MAX_K];
+  if (!greedy && (int)threadIdx.x < k) {
+    const int n = threadIdx.x;
+    const long long x = draft[(long long)b * k + n];
+    const bool x_ok = x >= 0 && x < rs.V;
+    s_x[n] = x;
+    s_lp[n] = x_ok ? scaled(row_ptr(rs, b, n)[x], temp) : -CUDART_INF_F;
+    s_lq[n] = (rs.nq && x_ok) ? scaled(row_ptr(rs, b, rs.np + n)[x], temp) : -CUDART_INF_F;
+    s_u[n] = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, pos_base + n, 0);
+  }
   __syncthreads();
   if (threadIdx.x != 0) return;
   Decision d;
@@ -272,16 +285,11 @@ __global__ void accept_decide_kernel(RowSet rs, int B, int k, int nchunks, const
   }
   bool rejected = false;
   for (; n < k; ++n) {
-    const long long x = draft[(long long)b * k + n];
-    const bool x_ok = x >= 0 && x < rs.V;
-    const float lp = x_ok ? scaled(row_ptr(rs, b, n)[x], temp) : -CUDART_INF_F;
-    const double p = (double)expf(lp - r_m[n]) / r_s[n];
+    const long long x = s_x[n];
+    const double p = (double)expf(s_lp[n] - r_m[n]) / r_s[n];
     double q = 1.0;
-    if (rs.nq) {
-      const float lq = x_ok ? scaled(row_ptr(rs, b, rs.np + n)[x], temp) : -CUDART_INF_F;
-      q = (double)expf(lq - r_m[rs.np + n]) / r_s[rs.np + n];
-    }
-    const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, pos_base + n, 0);
+    if (rs.nq) q = (double)expf(s_lq[n] - r_m[rs.np + n]) / r_s[rs.np + n];
+    const float u = s_u[n];
     if ((double)u * q < p) { tok[n] = x; continue; }
     rejected = true;
     d.mode = rs.nq ? 1 : 3;
@@ -379,7 +387,15 @@ accept_pick_kernel(RowSet rs, int k, int nchunks, float temp, const Decision* __
   __shared__ int s_chunk, s_plain, s_thread;
   __shared__ double s_before, s_target;
   __shared__ double s_part[STATS_THREADS];
-  const double* mb = mass + (long long)b * nchunks * 2;
+  // chunk masses of this sequence in shared memory (one round trip instead of dependent loads in thread 0)
+  constexpr int PICK_MAX = 512;
+  __shared__ double s_mass[2 * PICK_MAX];
+  const double* mg = mass + (long long)b * nchunks * 2;
+  const bool staged = nchunks <= PICK_MAX;
+  if (staged)
+    for (int i = tid; i < 2 * nchunks; i += STATS_THREADS) s_mass[i] = mg[i];
+  __syncthreads();
+  const double* mb = staged ? s_mass : mg;
   if (tid == 0) {
     double Z = 0.0;
     for (int c = 0; c < nchunks; ++c) Z += mb[c * 2];
