@@ -70,6 +70,63 @@ def test_two_ranks_gloo():
         np.testing.assert_allclose(got[r]["gs"], s, rtol=1e-12)
 
 
+def _accept_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import torch.distributed as dist
+    from versenext_b200 import dist as vd
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        res = {}
+        for name, (p, q, draft, ua, us, T) in _accept_cases().items():
+            V = p.shape[-1]
+            lo, hi = vd.vocab_shard(V, world, rank, align=8)
+            qs = None if q is None else q[..., lo:hi]
+            res[name] = vd.sharded_accept(p[..., lo:hi], qs, draft, ua, us, lo, T)
+        out.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+def _accept_cases():
+    rng = np.random.default_rng(11)
+    B, k, V = 7, 4, 1003
+    q = rng.normal(0, 2, (B, k, V)).astype(np.float32)
+    p = np.concatenate([q + rng.normal(0, 0.5, (B, k, V)).astype(np.float32),
+                        rng.normal(0, 2, (B, 1, V)).astype(np.float32)], axis=1)
+    draft = np.argmax(q + rng.gumbel(size=q.shape), -1).astype(np.int64)
+    ua = rng.random((B, k)).astype(np.float32)
+    us = rng.random((B, k + 1)).astype(np.float32)
+    small = (p[:, :, :20].copy(), q[:, :, :20].copy(), draft % 20, ua, us, 1.0)   # 20 columns: an empty last shard
+    return {"t1": (p, q, draft, ua, us, 1.0), "t07": (p, q, draft, ua, us, 0.7), "greedy": (p, q, draft, ua, us, 0.0),
+            "point_mass": (p, None, draft, ua, us, 1.0), "tiny": small}
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_vocabulary_sharded_acceptance_matches_unsharded_rule(world):
+    """The exchange protocol of the sharded LM head + acceptance (stats and token logits, residual masses, picked
+    token) on gloo ranks: every rank returns the decisions and tokens of the unsharded rule."""
+    import torch.multiprocessing as mp
+    from oracle import accept as OA
+    ctx = mp.get_context("spawn")
+    qout = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_accept_worker, args=(r, world, port, qout)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(qout.get(timeout=180) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for name, (pl, ql, draft, ua, us, T) in _accept_cases().items():
+        want_n, want_t = OA.accept(pl, ql, draft, ua, us, T, 0)
+        for r in range(world):
+            n, t = got[r][name]
+            np.testing.assert_array_equal(n, want_n, err_msg=f"{name} rank {r}")
+            np.testing.assert_array_equal(t, want_t, err_msg=f"{name} rank {r}")
+
+
 def test_shard_helpers_single_process():
     from versenext_b200 import dist as vd
     for total in (0, 1, 7, 32, 33):
