@@ -101,6 +101,28 @@ int32_t vn_rope(vn_ctx* ctx, const float* x_dev, const float* cos_dev, const flo
 int32_t vn_attention(vn_ctx* ctx, const float* q_dev, const float* k_dev, const float* v_dev,
                      const float* mask_dev, float* out_dev, int64_t BH, int64_t Tq, int64_t Tk, int64_t D);
 
+/* Row-level pieces of the acceptance rule for a vocabulary split across GPUs (no counterpart in the reference, which
+ * has no sharded head; they are the kernels of vn_accept driven with softmax statistics supplied by the caller).
+ * A rank holds V consecutive columns of R logit rows (row pitch in elements).  All pointers are device pointers.
+ *   vn_row_stats:    per row max and sum exp(x - max) of logits / temperature over these columns (float32 exp,
+ *                    float64 sum), and the scaled logit at column tokens[r] (-inf when the token is not one of these
+ *                    columns, i.e. outside [0, V); pass ids relative to the first column).
+ *   vn_row_residual: out_mass[r] = { sum max(0, p - q), sum p } over these columns, with p = exp(x - m_p) / s_p from
+ *                    the GLOBAL statistics m_p, s_p (and m_q, s_q).  mode[r]: 0 skip, 1 residual of (p, q), 2 plain p,
+ *                    3 p with column removed[r] zeroed (deterministic proposals).
+ *   vn_row_pick:     inverse CDF over ascending columns of the same weights: the smallest column whose running
+ *                    weight exceeds u[r] times this block's weight total; out_token[r] is relative to the first
+ *                    column; rows with mode 0 are left untouched. */
+int32_t vn_row_stats(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, float temperature,
+                     const int64_t* tokens_dev, float* out_max_dev, double* out_sum_dev, float* out_logit_dev);
+int32_t vn_row_residual(vn_ctx* ctx, const float* p_dev, int64_t p_stride, const float* q_dev, int64_t q_stride, int32_t R,
+                        int32_t V, float temperature, const int32_t* mode_dev, const float* m_p_dev, const double* s_p_dev,
+                        const float* m_q_dev, const double* s_q_dev, const int64_t* removed_dev, double* out_mass_dev);
+int32_t vn_row_pick(vn_ctx* ctx, const float* p_dev, int64_t p_stride, const float* q_dev, int64_t q_stride, int32_t R,
+                    int32_t V, float temperature, const int32_t* mode_dev, const float* m_p_dev, const double* s_p_dev,
+                    const float* m_q_dev, const double* s_q_dev, const int64_t* removed_dev, const float* u_dev,
+                    int64_t* out_token_dev);
+
 /* ---- acceptance / rejection sampling ---------------------------------- */
 /* Replaces the argmax compare + accept loop of SpeculativeDecoder
  * (verse_nex/speculative.py:218-223, :280-287) and the softmax / top-k /

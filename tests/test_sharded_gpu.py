@@ -1,0 +1,66 @@
+"""Vocabulary-sharded acceptance with the per-shard arithmetic on the device (`vn_row_stats`, `vn_row_residual`,
+`vn_row_pick`): one GPU stands in for the ranks, every shard's logits live in their own device buffers, and the
+three exchanges of the protocol are done by stacking the shards' small result arrays.  The outcome must equal the
+unsharded rule of the CPU oracle on the concatenated logits."""
+
+import numpy as np
+import pytest
+
+from oracle import accept as OA
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(B, k, V, seed):
+    rng = np.random.default_rng(seed)
+    q = rng.normal(0, 2, (B, k, V)).astype(np.float32)
+    p = np.concatenate([q + rng.normal(0, 0.5, (B, k, V)).astype(np.float32),
+                        rng.normal(0, 2, (B, 1, V)).astype(np.float32)], axis=1)
+    draft = np.argmax(q + rng.gumbel(size=q.shape), -1).astype(np.int64)
+    return p, q, draft, rng.random((B, k)).astype(np.float32), rng.random((B, k + 1)).astype(np.float32)
+
+
+@pytest.mark.parametrize("world,V,T,with_q", [(3, 1003, 1.0, True), (2, 9000, 0.7, True), (4, 40000, 1.0, False),
+                                              (3, 1003, 0.0, True), (8, 248320, 1.0, True)])
+def test_device_shards_match_unsharded_oracle(world, V, T, with_q):
+    import versenext_b200 as vn
+    from versenext_b200 import dist as vd
+    from versenext_b200.sharded import DeviceShardOps, ShardedAccept, run_emulated
+    ctx = vn.Context.get(0)
+    B, k = (4, 4) if V > 100000 else (7, 4)
+    p, q, draft, ua, us = _inputs(B, k, V, seed=V + world)
+    parts = []
+    for r in range(world):
+        lo, hi = vd.vocab_shard(V, world, r, align=128 if V > 100000 else 8)
+        pd = ctx.from_numpy(np.ascontiguousarray(p[..., lo:hi]))
+        qd = ctx.from_numpy(np.ascontiguousarray(q[..., lo:hi])) if with_q else None
+        parts.append(ShardedAccept(DeviceShardOps(ctx, pd, qd, T), draft, ua, us, lo, r, T))
+    want_n, want_t = OA.accept(p, q if with_q else None, draft, ua, us, T, 0)
+    for n, t in run_emulated(parts):
+        np.testing.assert_array_equal(n, want_n)
+        np.testing.assert_array_equal(t, want_t)
+
+
+def test_row_stats_against_numpy():
+    import ctypes as C
+    import versenext_b200 as vn
+    ctx = vn.Context.get(0)
+    rng = np.random.default_rng(2)
+    R, V = 11, 12345
+    x = rng.normal(0, 3, (R, V)).astype(np.float32)
+    x[3, :] = -np.inf                                  # a fully masked row
+    tok = rng.integers(-1, V + 1, R).astype(np.int64)
+    xd, td = ctx.from_numpy(x), ctx.from_numpy(tok)
+    m, s, lx = ctx.empty((R,), np.float32), ctx.empty((R,), np.float64), ctx.empty((R,), np.float32)
+    ptr = lambda a: C.c_void_p(a.ptr)
+    ctx._check(ctx.lib.vn_row_stats(ctx.handle, ptr(xd), V, R, V, 0.5, ptr(td), ptr(m), ptr(s), ptr(lx)))
+    xs = (x / np.float32(0.5)).astype(np.float32)
+    wm = xs.max(axis=1)
+    with np.errstate(invalid="ignore"):
+        ws = np.where(np.isneginf(wm), 0.0, np.exp(xs - wm[:, None]).astype(np.float32).sum(axis=1, dtype=np.float64))
+    np.testing.assert_array_equal(m.numpy(), wm)
+    # 16 exponentials are added in float32 per thread before the float64 sums, chunk maxima are rescaled afterwards
+    np.testing.assert_allclose(s.numpy(), ws, rtol=1e-6)
+    inside = (tok >= 0) & (tok < V)
+    wl = np.where(inside, xs[np.arange(R), np.clip(tok, 0, V - 1)], -np.inf)
+    np.testing.assert_array_equal(lx.numpy(), wl.astype(np.float32))

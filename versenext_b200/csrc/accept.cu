@@ -1013,7 +1013,158 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
   return VN_OK;
 }
 
+// ---- row-level pieces for a vocabulary split across GPUs ----------------------------------------------------
+// The same kernels as above, driven row by row with the softmax statistics supplied from outside: a rank that
+// holds a slice of the vocabulary computes the slice's statistics and residual mass, the ranks merge those few
+// numbers, and the rank that owns the sampled token picks it.
+
+// one warp per row: merge the chunk records of a row, read the logit of `tokens[row]` (a column of this block)
+__global__ void row_stats_reduce_kernel(RowSet rs, int R, int nchunks, const Partial* __restrict__ part, float temp,
+                                        const long long* __restrict__ tokens, float* __restrict__ out_m,
+                                        double* __restrict__ out_s, float* __restrict__ out_x) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= R) return;
+  const Partial* pp = part + (long long)r * nchunks;
+  float m = -CUDART_INF_F;
+  for (int c = lane; c < nchunks; c += 32) m = fmaxf(m, pp[c].m);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  double s = 0.0;
+  for (int c = lane; c < nchunks; c += 32) {
+    const Partial p = pp[c];
+    if (p.m != -CUDART_INF_F) s += p.s * exp((double)(p.m - m));
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    out_m[r] = m;
+    out_s[r] = s;
+    if (out_x) {
+      const long long t = tokens ? tokens[r] : -1;
+      out_x[r] = (t >= 0 && t < rs.V) ? scaled(row_ptr(rs, r, 0)[t], temp) : -CUDART_INF_F;
+    }
+  }
+}
+
+// decisions from outside: mode 1 residual of (p, q), 2 plain p, 3 p without `removed`, 0 nothing
+__global__ void row_decision_kernel(int R, const int* __restrict__ mode, const float* __restrict__ m_p,
+                                    const double* __restrict__ s_p, const float* __restrict__ m_q,
+                                    const double* __restrict__ s_q, const long long* __restrict__ removed,
+                                    const float* __restrict__ u, Decision* __restrict__ dec) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= R) return;
+  Decision d;
+  d.n_acc = 0; d.mode = mode[r]; d.pos = 0;
+  d.x = removed ? (int)removed[r] : -1;
+  d.m_p = m_p[r]; d.inv_sp = 1.0 / s_p[r];
+  d.m_q = m_q ? m_q[r] : 0.f; d.inv_sq = s_q ? 1.0 / s_q[r] : 0.0;
+  d.u = u ? u[r] : 0.f;
+  dec[r] = d;
+}
+
+__global__ void row_mass_reduce_kernel(int R, int nchunks, const int* __restrict__ mode, const double* __restrict__ mass,
+                                       double* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= R) return;
+  double a = 0.0, b = 0.0;
+  if (mode[r] != 0)
+    for (int c = lane; c < nchunks; c += 32) { a += mass[((long long)r * nchunks + c) * 2]; b += mass[((long long)r * nchunks + c) * 2 + 1]; }
+  a = warp_sum(a); b = warp_sum(b);
+  if (lane == 0) { out[r * 2] = a; out[r * 2 + 1] = b; }
+}
+
+static int32_t row_set(vn_ctx* ctx, const float* p, long long p_stride, const float* q, long long q_stride, int R, int V,
+                       RowSet* rs, bool* vec) {
+  VN_REQUIRE(ctx, R >= 0 && V >= 1 && p, "bad sizes R=%d V=%d", R, V);
+  rs->p = p; rs->q = q; rs->p_sb = p_stride; rs->p_si = 0; rs->q_sb = q_stride; rs->q_si = 0;
+  rs->np = 1; rs->nq = q ? 1 : 0; rs->V = V;
+  auto aligned16 = [](const void* ptr) { return ((uintptr_t)ptr & 15) == 0; };
+  *vec = (V % 4 == 0) && aligned16(p) && (p_stride % 4 == 0) && (!q || (aligned16(q) && q_stride % 4 == 0));
+  return VN_OK;
+}
+
+// residual chunk masses of R rows into the workspace; returns the pointers
+static int32_t row_residual_chunks(vn_ctx* ctx, const RowSet& rs, bool vec, int R, float temp, const int* mode,
+                                   const float* m_p, const double* s_p, const float* m_q, const double* s_q,
+                                   const long long* removed, const float* u, Decision** dec_out, double** mass_out) {
+  const int nchunks = ceil_div(rs.V, CHUNK);
+  const size_t off_mass = ((size_t)R * sizeof(Decision) + 255) & ~(size_t)255;
+  void* ws;
+  int32_t st = vn_workspace(ctx, off_mass + (size_t)R * nchunks * 2 * sizeof(double), &ws);
+  if (st) return st;
+  Decision* dec = (Decision*)ws;
+  double* mass = (double*)((char*)ws + off_mass);
+  VN_LAUNCH(ctx, row_decision_kernel, ceil_div(R, 128), 128, 0, R, mode, m_p, s_p, m_q, s_q, removed, u, dec);
+  dim3 g(nchunks, R);
+  if (vec) VN_LAUNCH(ctx, accept_residual_kernel<true>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);
+  else     VN_LAUNCH(ctx, accept_residual_kernel<false>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);
+  *dec_out = dec; *mass_out = mass;
+  return VN_OK;
+}
+
 extern "C" {
+
+int32_t vn_row_stats(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, float temperature,
+                     const int64_t* tokens_dev, float* out_max_dev, double* out_sum_dev, float* out_logit_dev) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, temperature > 0.f && out_max_dev && out_sum_dev, "temperature must be positive, outputs non-null");
+  if (R == 0) return VN_OK;
+  RowSet rs; bool vec;
+  int32_t st = row_set(ctx, logits_dev, row_stride, nullptr, 0, R, V, &rs, &vec);
+  if (st) return st;
+  const float temp = fmaxf(temperature, 1e-8f);
+  const int nchunks = ceil_div(V, CHUNK);
+  void* ws;
+  st = vn_workspace(ctx, (size_t)R * nchunks * sizeof(Partial), &ws);
+  if (st) return st;
+  Partial* part = (Partial*)ws;
+  const int grid = (int)std::min<long long>((long long)R * ((nchunks + 1) / 2), (long long)ctx->sm_count * 8);
+  st = launch_accept_stats(ctx, vec, false, grid, rs, R, nchunks, temp, part);
+  if (st) return st;
+  VN_LAUNCH(ctx, row_stats_reduce_kernel, ceil_div(R, 4), 128, 0, rs, R, nchunks, part, temp,
+            reinterpret_cast<const long long*>(tokens_dev), out_max_dev, out_sum_dev, out_logit_dev);
+  return VN_OK;
+}
+
+int32_t vn_row_residual(vn_ctx* ctx, const float* p_dev, int64_t p_stride, const float* q_dev, int64_t q_stride, int32_t R,
+                        int32_t V, float temperature, const int32_t* mode_dev, const float* m_p_dev, const double* s_p_dev,
+                        const float* m_q_dev, const double* s_q_dev, const int64_t* removed_dev, double* out_mass_dev) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, temperature > 0.f && mode_dev && m_p_dev && s_p_dev && out_mass_dev, "null argument");
+  VN_REQUIRE(ctx, !q_dev || (m_q_dev && s_q_dev), "draft statistics missing");
+  if (R == 0) return VN_OK;
+  RowSet rs; bool vec;
+  int32_t st = row_set(ctx, p_dev, p_stride, q_dev, q_stride, R, V, &rs, &vec);
+  if (st) return st;
+  Decision* dec; double* mass;
+  st = row_residual_chunks(ctx, rs, vec, R, fmaxf(temperature, 1e-8f), mode_dev, m_p_dev, s_p_dev, m_q_dev, s_q_dev,
+                           reinterpret_cast<const long long*>(removed_dev), nullptr, &dec, &mass);
+  if (st) return st;
+  VN_LAUNCH(ctx, row_mass_reduce_kernel, ceil_div(R, 4), 128, 0, R, ceil_div(V, CHUNK), mode_dev, mass, out_mass_dev);
+  return VN_OK;
+}
+
+int32_t vn_row_pick(vn_ctx* ctx, const float* p_dev, int64_t p_stride, const float* q_dev, int64_t q_stride, int32_t R,
+                    int32_t V, float temperature, const int32_t* mode_dev, const float* m_p_dev, const double* s_p_dev,
+                    const float* m_q_dev, const double* s_q_dev, const int64_t* removed_dev, const float* u_dev,
+                    int64_t* out_token_dev) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, temperature > 0.f && mode_dev && m_p_dev && s_p_dev && u_dev && out_token_dev, "null argument");
+  VN_REQUIRE(ctx, !q_dev || (m_q_dev && s_q_dev), "draft statistics missing");
+  if (R == 0) return VN_OK;
+  RowSet rs; bool vec;
+  int32_t st = row_set(ctx, p_dev, p_stride, q_dev, q_stride, R, V, &rs, &vec);
+  if (st) return st;
+  const float temp = fmaxf(temperature, 1e-8f);
+  Decision* dec; double* mass;
+  st = row_residual_chunks(ctx, rs, vec, R, temp, mode_dev, m_p_dev, s_p_dev, m_q_dev, s_q_dev,
+                           reinterpret_cast<const long long*>(removed_dev), u_dev, &dec, &mass);
+  if (st) return st;
+  VN_LAUNCH(ctx, accept_pick_kernel, R, STATS_THREADS, 0, rs, 0, ceil_div(V, CHUNK), temp, dec, mass,
+            reinterpret_cast<long long*>(out_token_dev));
+  return VN_OK;
+}
 
 int32_t vn_accept(vn_ctx* ctx, const float* p_logits_dev, const float* q_logits_dev, const int64_t* draft_dev,
                   const float* u_accept_dev, const float* u_sample_dev, uint64_t seed, uint32_t offset,
