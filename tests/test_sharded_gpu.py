@@ -64,3 +64,56 @@ def test_row_stats_against_numpy():
     inside = (tok >= 0) & (tok < V)
     wl = np.where(inside, xs[np.arange(R), np.clip(tok, 0, V - 1)], -np.inf)
     np.testing.assert_array_equal(lx.numpy(), wl.astype(np.float32))
+
+
+def _nccl_worker(rank, world, port, out):
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    import versenext_b200 as vn
+    from versenext_b200 import dist as vd
+    from versenext_b200.sharded import DeviceShardOps, ShardedAccept, run_distributed
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ctx = vn.Context.get(rank)
+        B, k, V, T = 6, 4, 20000, 0.9
+        p, q, draft, ua, us = _inputs(B, k, V, seed=77)
+        lo, hi = vd.vocab_shard(V, world, rank, align=128)
+        ops = DeviceShardOps(ctx, ctx.from_numpy(np.ascontiguousarray(p[..., lo:hi])),
+                             ctx.from_numpy(np.ascontiguousarray(q[..., lo:hi])), T)
+        n, t = run_distributed(ShardedAccept(ops, draft, ua, us, lo, rank, T))
+        out.put((rank, n, t))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_over_nccl():
+    """The same protocol with one process per GPU and NCCL all-gathers (needs two GPUs; skipped on one)."""
+    import socket
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    qout = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, qout)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    got = [qout.get(timeout=300) for _ in procs]
+    for pr in procs:
+        pr.join(timeout=60)
+        assert pr.exitcode == 0
+    p, q, draft, ua, us = _inputs(6, 4, 20000, seed=77)
+    want_n, want_t = OA.accept(p, q, draft, ua, us, 0.9, 0)
+    for _, n, t in got:
+        np.testing.assert_array_equal(n, want_n)
+        np.testing.assert_array_equal(t, want_t)
