@@ -194,6 +194,12 @@ int32_t vn_model_finalize(vn_model* m);
  * quantize.py:187-214), "int4" (per output channel, :231-258), "int4g128" */
 int32_t vn_model_quantize(vn_model* m, const char* scheme);
 int32_t vn_model_param_bytes(vn_model* m, uint64_t* out);
+/* LM head restricted to vocabulary columns [v_lo, v_lo + n_cols): out[r, j] = hidden[r] . head.weight[v_lo + j]
+ * for `rows` rows of final-norm hidden states (float32 [rows, dim], as vn_model_forward returns them in
+ * out_hidden); out row pitch out_ld floats.  The building block of a head split by columns over several GPUs
+ * (no counterpart in the reference, whose head is one Linear, cometspark.py:690-696). */
+int32_t vn_model_head(vn_model* m, const float* hidden_dev, int32_t rows, int32_t v_lo, int32_t n_cols,
+                      float* out_logits_dev, int64_t out_ld);
 /* Device-side conditions raised by forwards since the last call, read after a stream synchronisation and
  * cleared: *bad_token != 0 when a token id outside [0, vocab) was met (the kernels clamp it instead of reading
  * outside the embedding table; the reference raises IndexError from NumPy fancy indexing, vnnn.py:453-460);

@@ -117,3 +117,58 @@ def test_two_ranks_over_nccl():
     for _, n, t in got:
         np.testing.assert_array_equal(n, want_n)
         np.testing.assert_array_equal(t, want_t)
+
+
+def test_sharded_head_and_acceptance_from_hidden_states():
+    """The data flow of a head split by columns: final-norm hidden rows -> each shard's logits (`vn_model_head`) ->
+    the three-exchange acceptance.  Against the unsharded path on the same model: full logits from the forward,
+    acceptance by `vn_accept` with the same injected uniforms."""
+    import versenext_b200 as vn
+    from oracle import model as OM
+    from versenext_b200 import dist as vd, sampling
+    from versenext_b200.sharded import DeviceShardOps, ShardedAccept, run_emulated
+    ctx = vn.Context.get(0)
+    models = []
+    for seed in (41, 42):                                   # target, draft: same shape, different weights
+        cfg = OM.mate_config(vocab_size=1024, dim=256, n_layer=2, n_head=4, n_kv_head=2, window_size=24,
+                             num_global_tokens=20, max_seq_len=256, init_std=0.05, num_dense_parts=2,
+                             num_experts_per_part=2, top_k=1)
+        sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=seed, gate_std=1.0).items()}
+        kw = cfg.to_dict()
+        kw.pop("init_std")
+        m = vn.VerseNexLM(dtype="bf16", **kw)
+        m.load_state_dict(sd)
+        models.append(m)
+    target, draft_model = models
+    rng = np.random.default_rng(12)
+    B, k, V, T = 5, 4, 1024, 0.8
+    toks = rng.integers(0, V, (B, 30 + k + 1))
+    full, hid = [], []
+    for m in models:
+        cache = m.new_cache(B, 64)
+        m.forward_cached(toks[:, :30], cache, last_only=True)
+        cache.commit(30, np.full(B, 30, np.int32))
+        lg, hd = m.forward_cached(toks[:, 30:], cache, want_hidden=True)
+        full.append(lg)
+        hid.append(hd)
+    p_full = full[0].numpy()                                # [B, k+1, V]
+    q_full = full[1].numpy()[:, :k]
+    draft = np.argmax(q_full + rng.gumbel(size=q_full.shape), -1).astype(np.int64)
+    ua = rng.random((B, k)).astype(np.float32)
+    us = rng.random((B, k + 1)).astype(np.float32)
+    want_n, want_t = sampling.accept(ctx, p_full, q_full, draft, u_accept=ua, u_sample=us, temperature=T)
+    want_n, want_t = want_n.numpy(), want_t.numpy()
+    world = 3
+    parts = []
+    for r in range(world):
+        lo, hi = vd.vocab_shard(V, world, r, align=128)
+        ps = target.head_columns(hid[0], lo, hi - lo)       # [B * (k+1), hi - lo]
+        np.testing.assert_allclose(ps.numpy().reshape(B, k + 1, hi - lo), p_full[..., lo:hi], rtol=0, atol=1e-5)
+        qs_all = draft_model.head_columns(hid[1], lo, hi - lo).numpy().reshape(B, k + 1, hi - lo)[:, :k]
+        qs = ctx.from_numpy(np.ascontiguousarray(qs_all))
+        ops = DeviceShardOps(ctx, ps.reshape(B, k + 1, hi - lo), qs, T)
+        parts.append(ShardedAccept(ops, draft, ua, us, lo, r, T))
+    for n, t in run_emulated(parts):
+        np.testing.assert_array_equal(n, want_n)
+        np.testing.assert_array_equal(t, want_t)
+    target.check()

@@ -455,7 +455,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
                                   q, lane, n0, row0, cnt, (int)blockIdx.y, vec_ok, swi_ok);
         }
       }
-      if (tma_out && issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before exit
+      // the staging tiles must have been read before the CTA gives its shared memory back; the writes themselves
+      // are complete and visible when the grid completes, which is what every consumer waits for
+      if (tma_out && issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
     if (tr && threadIdx.x == 64) tr[5] = clock_now();     // this warp's stores issued
   }

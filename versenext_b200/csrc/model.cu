@@ -875,6 +875,48 @@ int32_t vn_model_param_bytes(vn_model* m, uint64_t* out) {
   return VN_OK;
 }
 
+int32_t vn_model_head(vn_model* m, const float* hidden_dev, int32_t rows, int32_t v_lo, int32_t n_cols,
+                      float* out_logits_dev, int64_t out_ld) {
+  if (!m || !hidden_dev || !out_logits_dev) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  const Config& c = m->cfg;
+  VN_REQUIRE(ctx, m->finalized, "model is not finalised");
+  VN_REQUIRE(ctx, m->qmode == 0, "vn_model_head needs dense head weights");
+  VN_REQUIRE(ctx, rows >= 0 && v_lo >= 0 && n_cols >= 0 && (long long)v_lo + n_cols <= c.vocab && out_ld >= n_cols,
+             "column range [%d, %d) outside the vocabulary of %d", v_lo, v_lo + n_cols, c.vocab);
+  if (rows == 0 || n_cols == 0) return VN_OK;
+  const int D = c.dim;
+  for (int r0 = 0; r0 < rows; r0 += 256) {          // blocks of at most 256 rows: the decode GEMM's limit
+    const int nr = std::min(256, rows - r0);
+    TRY(ensure_rows(m, nr));
+    GemmArgs g;
+    g.lda = D; g.ldw = D; g.C = out_logits_dev + (long long)r0 * out_ld; g.ldc = out_ld; g.M = nr; g.N = n_cols; g.K = D;
+    g.tag = "gemm_head_shard";
+    const long long n = (long long)nr * D;
+    if (c.bf16) {
+      VN_LAUNCH(ctx, cast_rows_kernel<__nv_bfloat16>, (unsigned)ceil_div(n, 256ll), 256, 0, hidden_dev + (long long)r0 * D,
+                (__nv_bfloat16*)m->h, n);
+      g.A = m->h;
+      g.W = (const __nv_bfloat16*)m->head + (long long)v_lo * D;
+      GemmArgs probe = g;
+      if (m->use_tc && gemm_tc_supported(probe) && out_ld % 4 == 0 && n_cols >= 1) {
+        TRY(ensure_partial(m, 1024));
+        TcPlan direct;
+        direct.error_flag = m->tc_error;
+        TRY(launch_gemm_tc(ctx, g, m->cap_rows, direct));
+      } else {
+        TRY(linear(m, g));
+      }
+    } else {
+      g.A = hidden_dev + (long long)r0 * D;
+      g.W = (const float*)m->head + (long long)v_lo * D;
+      TRY(linear(m, g));
+    }
+  }
+  return VN_OK;
+}
+
 int32_t vn_model_status(vn_model* m, int32_t* bad_token, int32_t* wait_timeout) {
   if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
   vn_ctx* ctx = m->ctx;

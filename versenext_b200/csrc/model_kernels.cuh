@@ -23,6 +23,13 @@ __global__ void convert_rows_kernel(const float* __restrict__ src, T* __restrict
   dst[(r * row_mul + row_off) * dst_ld + c] = from_f<T>(src[i]);
 }
 
+// fp32 rows -> storage dtype (the GEMM's activation format)
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ src, T* __restrict__ dst, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = from_f<T>(src[i]);
+}
+
 // ---- embedding gather (verse_torch/vnnn.py:453-460) + optional sqrt(dim) scale (base_model.py:201-203)
 template <typename T>
 __global__ void embed_kernel(const long long* __restrict__ tokens, const T* __restrict__ emb, float* __restrict__ x,

@@ -158,6 +158,15 @@ class VerseNexLM:
         self.ctx._check(self.ctx.lib.vn_model_param_bytes(self.handle, C.byref(n)))
         return int(n.value)
 
+    def head_columns(self, hidden, v_lo: int, n_cols: int) -> DeviceArray:
+        """Logits of vocabulary columns [v_lo, v_lo + n_cols) for final-norm hidden rows (R, dim): the LM head of a
+        rank that owns only those columns."""
+        h = as_device(self.ctx, hidden, np.float32)
+        R = h.size // self.dim
+        out = self.ctx.empty((R, n_cols), np.float32)
+        self.ctx._check(self.ctx.lib.vn_model_head(self.handle, _ptr(h), R, int(v_lo), int(n_cols), _ptr(out), n_cols))
+        return out
+
     def check(self):
         """Raise what the forwards since the last check ran into on the device: IndexError for a token id outside
         the vocabulary (as NumPy indexing does in the reference, vnnn.py:453-460), RuntimeError for a kernel
