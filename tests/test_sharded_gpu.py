@@ -172,3 +172,105 @@ def test_sharded_head_and_acceptance_from_hidden_states():
         np.testing.assert_array_equal(n, want_n)
         np.testing.assert_array_equal(t, want_t)
     target.check()
+
+
+def _small_pair(vn, OM, vocab=1024):
+    out = []
+    for seed, n_layer in ((51, 2), (52, 1)):                # target, draft
+        cfg = OM.mate_config(vocab_size=vocab, dim=256, n_layer=n_layer, n_head=4, n_kv_head=2, window_size=24,
+                             num_global_tokens=20, max_seq_len=256, init_std=0.05, num_dense_parts=2,
+                             num_experts_per_part=2, top_k=1)
+        sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=seed, gate_std=1.0).items()}
+        kw = cfg.to_dict()
+        kw.pop("init_std")
+        m = vn.VerseNexLM(dtype="bf16", **kw)
+        m.load_state_dict(sd)
+        out.append(m)
+    return out
+
+
+def _engine_tokens(eng, prompts, rounds):
+    eng.prefill(prompts)
+    for _ in range(rounds):
+        eng.step()
+    c = eng.counts()
+    h = eng.history.numpy()
+    return [h[b, :c[b]].copy() for b in range(len(c))]
+
+
+def test_sharded_engine_equals_plain_engine_on_one_rank():
+    """With one rank the column-split round (hidden rows -> head columns -> exchanges) must commit exactly the tokens
+    of the plain engine: same Philox streams, same acceptance rule."""
+    import versenext_b200 as vn
+    from oracle import model as OM
+    from versenext_b200.sharded_engine import ShardedSpecEngine
+    target, draft = _small_pair(vn, OM)
+    prompts = np.random.default_rng(13).integers(0, 1024, (6, 20))
+    kw = dict(max_batch=6, max_seq=128, k=3, temperature=0.9, seed=17)
+    plain = _engine_tokens(vn.SpecEngine(target, draft, top_k=0, graph=False, **kw), prompts, 6)
+    shard = _engine_tokens(ShardedSpecEngine(target, draft, **kw), prompts, 6)
+    for a, b in zip(plain, shard):
+        np.testing.assert_array_equal(a, b)
+    assert sum(len(a) for a in plain) > 6 * 6               # some proposals were accepted
+
+
+def _engine_worker(rank, world, port, out):
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    import versenext_b200 as vn
+    from oracle import model as OM
+    from versenext_b200.sharded_engine import ShardedSpecEngine
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ctx = vn.Context.get(rank)
+        cfgs = []
+        models = []
+        for seed, n_layer in ((51, 2), (52, 1)):
+            cfg = OM.mate_config(vocab_size=1024, dim=256, n_layer=n_layer, n_head=4, n_kv_head=2, window_size=24,
+                                 num_global_tokens=20, max_seq_len=256, init_std=0.05, num_dense_parts=2,
+                                 num_experts_per_part=2, top_k=1)
+            sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=seed, gate_std=1.0).items()}
+            kw = cfg.to_dict()
+            kw.pop("init_std")
+            m = vn.VerseNexLM(dtype="bf16", device=f"cuda:{rank}", **kw)
+            m.load_state_dict(sd)
+            models.append(m)
+        prompts = np.random.default_rng(100 + rank).integers(0, 1024, (4, 20))
+        kw = dict(max_batch=4, max_seq=128, k=3, temperature=0.9, seed=17 + rank)
+        plain = _engine_tokens(vn.SpecEngine(models[0], models[1], top_k=0, graph=False, **kw), prompts, 5)
+        shard = _engine_tokens(ShardedSpecEngine(models[0], models[1], **kw), prompts, 5)
+        out.put((rank, all(np.array_equal(a, b) for a, b in zip(plain, shard)), sum(len(a) for a in plain)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_engine_two_ranks_over_nccl():
+    """Two processes, two GPUs: requests split over the ranks and the head split by columns; every rank commits the
+    tokens its plain single-GPU engine commits for the same requests (needs two GPUs; skipped on one)."""
+    import socket
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    qout = ctx.Queue()
+    procs = [ctx.Process(target=_engine_worker, args=(r, 2, port, qout)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    got = [qout.get(timeout=300) for _ in procs]
+    for pr in procs:
+        pr.join(timeout=60)
+        assert pr.exitcode == 0
+    for rank, same, n in got:
+        assert same, f"rank {rank}: sharded round differs from the plain engine"
+        assert n > 0
