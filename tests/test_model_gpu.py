@@ -343,10 +343,13 @@ def _dequantised_state_dict(sd, cfg, scheme):
     return out
 
 
+@pytest.mark.parametrize("gemm", ["tcgen05", "mma"])
 @pytest.mark.parametrize("scheme", ["int8", "int4", "int4g128"])
-def test_weight_only_quantised_model(scheme):
+def test_weight_only_quantised_model(scheme, gemm, monkeypatch):
     """INT8 / INT4 per output channel (reference schemes) and INT4 group-128: the device model against the
-    reference forward run on the dequantised weights; MoD + TriSparse, chain then cached continuation."""
+    reference forward run on the dequantised weights; MoD + TriSparse, chain then cached continuation.  Both
+    GEMM paths: raw bytes dequantised into the tcgen05 operand stage (default), and the mma.sync kernels."""
+    monkeypatch.setenv("VN_GEMM_TCQ", "1" if gemm == "tcgen05" else "0")     # read when the model is quantised
     cfg = OM.mate_config(vocab_size=320, dim=128, n_layer=2, n_head=4, n_kv_head=2, window_size=16,
                          num_global_tokens=8, max_seq_len=128, init_std=0.08, num_dense_parts=2,
                          num_experts_per_part=2, top_k=1, expert_hidden=192, mlp_hidden_multiple=3)
@@ -369,6 +372,34 @@ def test_weight_only_quantised_model(scheme):
         m.load_tensor("norm.weight", np.ones(128, np.float32))
     with pytest.raises(ValueError):
         m.quantize("int8")
+
+
+@pytest.mark.parametrize("scheme,tol", [("int8", 2e-3), ("int4", 2e-3), ("int4g128", 1e-2)])
+def test_quantised_tcgen05_gemm_equals_mma_gemm(scheme, tol, monkeypatch):
+    """185 rows (six 32-token accumulator chunks over both epilogue groups, a ragged last one), head_dim 64,
+    routed experts with uneven segment sizes: the tcgen05 path must reproduce the mma.sync path, which applies
+    the scales to fp32 accumulators.  Per-row schemes feed identical integer operands to both (only the fp32
+    summation order differs); group-128 rounds q * scale to bf16 in the operand (relative 2^-9 per weight)."""
+    cfg = hd64_cfg()
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=29, gate_std=1.0).items()}
+    rng = np.random.default_rng(12)
+    B = 5
+    ctx_tok = rng.integers(0, 384, (B, 37))
+    nxt = rng.integers(0, 384, (B, 5))
+    outs = []
+    for flag in ("0", "1"):
+        monkeypatch.setenv("VN_GEMM_TCQ", flag)
+        m = build(cfg, sd, "bf16")
+        m.quantize(scheme)
+        cache = m.new_cache(B, 128)
+        a = m.forward_cached(ctx_tok, cache).numpy()
+        cache.commit(37, np.full(B, 37, np.int32))
+        b = m.forward_cached(nxt, cache).numpy()
+        m.check()
+        outs.append((a, b))
+    assert np.isfinite(outs[1][0]).all() and np.isfinite(outs[1][1]).all()
+    assert rel_err(outs[1][0], outs[0][0]) < tol
+    assert rel_err(outs[1][1], outs[0][1]) < tol
 
 
 def test_quantise_needs_bf16_and_known_scheme():

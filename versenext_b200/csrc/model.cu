@@ -8,6 +8,7 @@
 #include "attn_mma.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_mma_q.cuh"
+#include "gemm_tcq.cuh"
 
 #include <math.h>
 #include <stdlib.h>
@@ -418,6 +419,11 @@ int tc_splits(const vn_ctx* ctx, int N, int K, int nseg) {
   return ceil_div(nkb, per);   // effective number of K ranges
 }
 
+// dense bf16 weights or their quantised copy: the same pipeline, with the dequantising operand stage in front
+int32_t tc_launch(vn_ctx* ctx, const GemmArgs& g, long long a_rows, TcPlan& plan) {
+  return g.wq ? launch_gemm_tcq(ctx, g, a_rows, plan) : launch_gemm_tc(ctx, g, a_rows, plan);
+}
+
 // launches the GEMM into the split-K workspace; returns the number of partial slices through *splits_out
 int32_t tc_partial(vn_model* m, GemmArgs g, long long a_rows, long long c_rows, int* splits_out) {
   vn_ctx* ctx = m->ctx;
@@ -426,7 +432,7 @@ int32_t tc_partial(vn_model* m, GemmArgs g, long long a_rows, long long c_rows, 
   TcPlan plan;
   plan.splits = splits; plan.force_partial = true;
   plan.partial = m->partial; plan.rows_total = c_rows; plan.error_flag = m->tc_error;
-  TRY(launch_gemm_tc(ctx, g, a_rows, plan));
+  TRY(tc_launch(ctx, g, a_rows, plan));
   *splits_out = plan.splits_used;
   return VN_OK;
 }
@@ -457,6 +463,13 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
   TcPlan direct;
   TRY(ensure_partial(m, 1024));
   direct.error_flag = m->tc_error;
+  // dense weight, or its quantised copy with the scales (rows_per_seg: output rows of one expert)
+  auto pick = [&](GemmArgs& g, void* q, float* qs, long long rows_per_seg) {
+    if (!m->qmode) return;
+    g.W = q; g.w_scale = qs; g.wq = m->qmode;
+    g.ws_stride = rows_per_seg * (m->qmode == 3 ? (g.K + 127) / 128 : 1);
+  };
+  const int use_cluster = m->qmode ? 0 : m->use_cluster;   // the cluster reduce exists for dense weights only
   // expert_count is zero between forwards: the combine kernel of every MoD layer leaves it so
   VN_LAUNCH_PDL(ctx, embed_norm_kernel<T>, M, 256, 0, (const long long*)tokens, (const T*)m->emb, m->x,
                 m->layers[0].norm1, (T*)m->h, D, c.vocab, emb_scale, 1e-6f, m->status);
@@ -468,13 +481,14 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     GemmArgs g;
     // ---- attention block
     g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.M = M; g.N = qkv_ld; g.K = D; g.tag = "gemm_qkv";
+    pick(g, L.q[0], L.qs[0], 0);
     tc_detail::TcRope rope;
     rope.cos_t = m->rope_cos; rope.sin_t = m->rope_sin; rope.lens = kv->lens;
     rope.depth = tree ? m->depth_dev : (const int*)nullptr;
     rope.kc = kv->k[li]; rope.vc = kv->v[li]; rope.q_out = m->qkv; rope.ldq = qkv_ld;
     rope.Tn = Tn; rope.H = H; rope.n_kv = n_kv; rope.hd = hd; rope.max_seq = kv->max_seq;
     rope.use_rope = c.use_rope; rope.rope_rows = m->rope_rows; rope.slot_offset = slot_offset;
-    if (m->use_cluster && gemm_tc_cluster_supported(g, tc_detail::TC_CL_QKV, &rope)) {
+    if (use_cluster && gemm_tc_cluster_supported(g, tc_detail::TC_CL_QKV, &rope)) {
       TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_QKV, nullptr, &rope));
     } else {
       TRY(tc_partial(m, g, cap, M, &sp));
@@ -500,9 +514,10 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     g = GemmArgs();
     g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.M = M; g.N = D; g.K = H * hd; g.tag = "gemm_proj";
     g.ldc = D;
+    pick(g, L.q[1], L.qs[1], 0);
     // the residual add needs a norm kernel behind it either way, so the cluster reduce only pays for the
     // projections whose finalize kernel disappears (q|k|v, gate|up); VN_TC_CLUSTER=2 forces it here too
-    if (m->use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
+    if (use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
       TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_ADD, m->x, nullptr));
       VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm2, (T*)m->h, mod ? m->h32 : (float*)nullptr, 1, 0, D,
                     1e-6f);
@@ -518,7 +533,8 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.A = m->h; g.lda = D; g.W = L.w_gateup; g.ldw = D; g.M = M; g.N = 2 * c.mlp_hidden; g.K = D;
       g.tag = "gemm_gateup";
       g.C = m->act; g.ldc = c.mlp_hidden; g.c_bf16 = 1;
-      if (m->use_cluster && gemm_tc_cluster_supported(g, tc_detail::TC_CL_SWIGLU, nullptr)) {
+      pick(g, L.q[2], L.qs[2], 0);
+      if (use_cluster && gemm_tc_cluster_supported(g, tc_detail::TC_CL_SWIGLU, nullptr)) {
         TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_SWIGLU, nullptr, nullptr));
       } else {
         TRY(tc_partial(m, g, cap, M, &sp));
@@ -530,7 +546,8 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.A = m->act; g.lda = c.mlp_hidden; g.W = L.w_down; g.ldw = c.mlp_hidden; g.M = M; g.N = D; g.K = c.mlp_hidden;
       g.tag = "gemm_down";
       g.ldc = D;
-      if (m->use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
+      pick(g, L.q[3], L.qs[3], 0);
+      if (use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
         TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_ADD, m->x, nullptr));
         if (next_norm)
           VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
@@ -551,11 +568,13 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.A = m->hs; g.lda = D; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
       g.C = m->act; g.ldc = eh; g.M = M; g.N = 2 * eh; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = 1;
       g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne; g.tag = "gemm_expert_gateup";
-      TRY(launch_gemm_tc(ctx, g, (long long)M * S, direct));
+      pick(g, L.q[4], L.qs[4], 2 * eh);
+      TRY(tc_launch(ctx, g, (long long)M * S, direct));
       g = GemmArgs();
       g.A = m->act; g.lda = eh; g.W = L.e_down; g.ldw = eh; g.w_stride = (long long)D * eh;
       g.M = M; g.N = D; g.K = eh; g.seg_off = m->expert_off; g.seg_cnt = m->expert_count; g.nseg = ne;
       g.tag = "gemm_expert_down";
+      pick(g, L.q[5], L.qs[5], D);
       TRY(tc_partial(m, g, (long long)M * S, (long long)M * S, &sp));
       VN_LAUNCH_PDL(ctx, mod_combine_split_kernel, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
                 m->slot_w, m->part_w, D, c.P, c.top_k, m->expert_count, m->expert_cur, ne);
@@ -570,7 +589,8 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = m->head; g.ldw = D; g.C = out_logits; g.ldc = c.vocab; g.M = rows_out; g.N = c.vocab;
     g.K = D; g.tag = "gemm_head";
-    TRY(launch_gemm_tc(ctx, g, cap, direct));
+    pick(g, m->head_q, m->head_qs, 0);
+    TRY(tc_launch(ctx, g, cap, direct));
   }
   return VN_OK;
 }
@@ -858,7 +878,8 @@ int32_t vn_model_quantize(vn_model* m, const char* scheme) {
   if (!c.tie && m->head) { VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); VN_CUDA(ctx, cudaFree(m->head)); m->head = nullptr; }
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   m->qmode = mode;
-  m->use_tc = false;
+  // VN_GEMM_TCQ=0 in the environment: keep the quantised mma.sync GEMMs instead of the tcgen05 ones
+  { const char* e = getenv("VN_GEMM_TCQ"); if (e && e[0] == '0') m->use_tc = false; }
   // embedding + norms + routers + sinks stay as they were
   uint64_t keep = (uint64_t)c.vocab * D * m->esz + (uint64_t)D * 4;
   for (auto& L : m->layers) {
