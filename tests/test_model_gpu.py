@@ -402,6 +402,24 @@ def test_quantised_tcgen05_gemm_equals_mma_gemm(scheme, tol, monkeypatch):
     assert rel_err(outs[1][1], outs[0][1]) < tol
 
 
+@pytest.mark.parametrize("scheme", ["int8", "int4g128"])
+def test_quantised_head_on_a_column_range(scheme):
+    """A rank that owns vocabulary columns [lo, hi) of a quantised target: its slice of the head (raw bytes and
+    scales offset by whole rows) gives the same logits as those columns of the full quantised forward."""
+    cfg = hd64_cfg()
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=30, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    m.quantize(scheme)
+    toks = np.random.default_rng(13).integers(0, 384, (3, 9))
+    cache = m.new_cache(3, 32)
+    lg, hid = m.forward_cached(toks, cache, want_hidden=True)
+    full = lg.numpy().reshape(27, 384)
+    for lo, hi in ((0, 128), (128, 384), (256, 384)):
+        part = m.head_columns(hid, lo, hi - lo).numpy()
+        np.testing.assert_allclose(part, full[:, lo:hi], rtol=0, atol=1e-5)
+    m.check()
+
+
 def test_quantise_needs_bf16_and_known_scheme():
     cfg = OM.small_config()
     m = build(cfg, OM.init_state_dict(cfg, seed=4))

@@ -868,7 +868,12 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   a.kb_per_split = (nkb + splits - 1) / splits;
   // about 108 KB of stages per CTA so that two CTAs share an SM (one drains its accumulator while the other
   // streams); at least two stages of the largest token block, and no more than the k range needs
-  size_t budget = std::min<size_t>(108 * 1024, stage_bytes * 8);
+  // (a grid that leaves SMs idle anyway gives each CTA the whole SM: a k range of four or five blocks is then in
+  // flight at once instead of waiting for a stage to come back)
+  const long long ctas = (long long)ceil_div(g.N, BF) * ceil_div(nkb, a.kb_per_split) * g.nseg;
+  static const bool wide_on = [] { const char* e = getenv("VN_TC_WIDE"); return !(e && e[0] == '0'); }();
+  const size_t cap = (wide_on && ctas <= ctx->sm_count) ? 200 * 1024 : 108 * 1024;
+  size_t budget = std::min<size_t>(cap, stage_bytes * 8);
   budget = std::min(budget, std::max<size_t>(2, a.kb_per_split) * stage_bytes);
   budget = std::max(budget, 2 * stage_bytes);
   budget = std::max<size_t>(budget, 64 * 1024);       // the epilogue stages four 16 KB tiles in the freed stage memory

@@ -52,8 +52,9 @@ __device__ __forceinline__ void i4x8_to_bf16(unsigned x, float sc, unsigned (&o)
 
 template <int QMODE, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 2)
-gemm_tcq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs g,
-                const float* __restrict__ w_scale, long long ws_stride) {
+gemm_tcq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                const __grid_constant__ CUtensorMap tm_out, TcArgs g, const float* __restrict__ w_scale,
+                long long ws_stride) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ unsigned long long bar_full[8], bar_empty[8], bar_conv[8], bar_acc;
   __shared__ unsigned tmem_base_slot;
@@ -241,17 +242,39 @@ gemm_tcq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                               ? (g.N % 4 == 0 && ((uintptr_t)g.partial & 15) == 0)
                               : (g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 15) == 0);
       const bool swi_ok = MODE == TC_SWIGLU && g.ldc % 4 == 0 && g.N % 4 == 0 && ((uintptr_t)g.C & 7) == 0;
+      const bool tma_out = (MODE == TC_PARTIAL || MODE == TC_STORE) && g.tma_out;   // uniform over the CTA
+      const bool issuer = ((warp - 2) & 3) == 0 && lane == 0;                        // one thread per group
       for (int ch = grp; ch < nchunk; ch += 2) {
         unsigned r[32];
         tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (QMODE != 3) {
+        if (tma_out) {
+          // scaled registers -> a 32 x 128 fp32 tile in the freed stage memory -> one asynchronous tensor store
+          const int jb = ch >> 1;
+          float* tile = reinterpret_cast<float*>(base + ((size_t)grp * g.out_bufs + (jb % g.out_bufs)) * (32 * BF * 4));
+          if (jb >= g.out_bufs) {           // the tile is being reused: its earlier store must have read it
+            if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+          }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * rs);
+          for (int i = 0; i < 32; ++i) tile[i * BF + f] = __uint_as_float(r[i]) * rs;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+          if (issuer) {
+            tma_store_3d(&tm_out, tile, n0, row0 + ch * 32, MODE == TC_PARTIAL ? (int)blockIdx.y : 0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        } else {
+          if (QMODE != 3) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * rs);
+          }
+          tc_epilogue_chunk<MODE>(g, r, base + grp * (32 * 1024), ch, (ch >> 1) & 1, 2 + grp, q, lane, n0, row0, cnt,
+                                  (int)blockIdx.y, vec_ok, swi_ok);
         }
-        tc_epilogue_chunk<MODE>(g, r, base + grp * (32 * 1024), ch, (ch >> 1) & 1, 2 + grp, q, lane, n0, row0, cnt,
-                                (int)blockIdx.y, vec_ok, swi_ok);
       }
+      // the staging tiles must have been read before the CTA gives its shared memory back
+      if (tma_out && issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -313,7 +336,12 @@ inline int32_t launch_gemm_tcq_mode(vn_ctx* ctx, const GemmArgs& g, long long a_
   a.kb_per_split = (nkb + splits - 1) / splits;
   // as in the dense kernel: about 108 KB of stages so that two CTAs share an SM, never less than the 64 KB the
   // epilogue's staging tiles take in the freed stage memory
-  size_t budget = std::min<size_t>(108 * 1024, stage_bytes * 8);
+  // (a grid that leaves SMs idle anyway gives each CTA the whole SM: a k range of four or five blocks is then in
+  // flight at once instead of waiting for a stage to come back)
+  const long long ctas = (long long)ceil_div(g.N, BF) * ceil_div(nkb, a.kb_per_split) * g.nseg;
+  static const bool wide_on = [] { const char* e = getenv("VN_TC_WIDE"); return !(e && e[0] == '0'); }();
+  const size_t cap = (wide_on && ctas <= ctx->sm_count) ? 200 * 1024 : 108 * 1024;
+  size_t budget = std::min<size_t>(cap, stage_bytes * 8);
   budget = std::min(budget, std::max<size_t>(2, a.kb_per_split) * stage_bytes);
   budget = std::max(budget, 2 * stage_bytes);
   budget = std::max<size_t>(budget, 64 * 1024);
@@ -326,9 +354,27 @@ inline int32_t launch_gemm_tcq_mode(vn_ctx* ctx, const GemmArgs& g, long long a_
   a.partial = (gy > 1 || plan.force_partial) ? plan.partial : nullptr;
   a.partial_stride = plan.rows_total * (long long)g.N;
   a.error_flag = plan.error_flag;
-  a.out_bufs = 1;
   if ((gy > 1 || plan.force_partial) && !plan.partial) return vn_fail(ctx, VN_ERR_INVALID, "split-K needs a workspace");
   const int mode = a.partial ? TC_PARTIAL : g.epi == EPI_SWIGLU ? TC_SWIGLU : TC_STORE;
+  // dense fp32 outputs leave through TMA stores, as in the dense kernel (VN_TC_TMA_STORE=0: staged float4 stores)
+  static const bool tma_store_on = [] { const char* e = getenv("VN_TC_TMA_STORE"); return !(e && e[0] == '0'); }();
+  CUtensorMap tm_out = tm_x;      // placeholder when unused
+  a.tma_out = 0; a.out_bufs = 1;
+  if (tma_store_on && !g.seg_cnt && g.N >= BF && g.N % 4 == 0 && (mode == TC_PARTIAL || (mode == TC_STORE && !g.c_bf16))) {
+    const bool part = mode == TC_PARTIAL;
+    const float* optr = part ? a.partial : reinterpret_cast<const float*>(g.C);
+    const long long old_ = part ? g.N : g.ldc;
+    const long long slice = part ? a.partial_stride : (long long)g.M * old_;
+    const long long rows = part ? plan.rows_total : g.M;
+    if (((uintptr_t)optr & 15) == 0 && old_ % 4 == 0 && slice % 4 == 0 &&
+        make_out_map(&tm_out, optr, g.N, rows, part ? gy : 1, old_, slice)) {
+      const int per_group = (((g.M + 31) / 32) + 1) / 2;               // chunks the busier epilogue group drains
+      budget = std::max<size_t>(budget, (size_t)std::min(per_group, 3) * 2 * 32 * BF * 4);
+      a.smem_budget = (unsigned)budget;
+      a.out_bufs = (int)std::min<size_t>(per_group, budget / (2 * 32 * BF * 4));
+      a.tma_out = a.out_bufs >= 1 ? 1 : 0;
+    }
+  }
   const size_t smem = budget + 1024;
   static unsigned long long attr_set = 0;
   if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
@@ -340,11 +386,11 @@ inline int32_t launch_gemm_tcq_mode(vn_ctx* ctx, const GemmArgs& g, long long a_
   dim3 grid(ceil_div(g.N, BF), gy, g.nseg);
   const char* name = g.tag ? g.tag : "gemm_tcq_kernel";
   if (mode == TC_PARTIAL)
-    VN_LAUNCH_PDL_LEVEL(ctx, 1, name, (gemm_tcq_kernel<QMODE, TC_PARTIAL>), grid, TC_THREADS, smem, tm_w, tm_x, a, g.w_scale, g.ws_stride);
+    VN_LAUNCH_PDL_LEVEL(ctx, 1, name, (gemm_tcq_kernel<QMODE, TC_PARTIAL>), grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a, g.w_scale, g.ws_stride);
   else if (mode == TC_SWIGLU)
-    VN_LAUNCH_PDL_LEVEL(ctx, 1, name, (gemm_tcq_kernel<QMODE, TC_SWIGLU>), grid, TC_THREADS, smem, tm_w, tm_x, a, g.w_scale, g.ws_stride);
+    VN_LAUNCH_PDL_LEVEL(ctx, 1, name, (gemm_tcq_kernel<QMODE, TC_SWIGLU>), grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a, g.w_scale, g.ws_stride);
   else
-    VN_LAUNCH_PDL_LEVEL(ctx, 1, name, (gemm_tcq_kernel<QMODE, TC_STORE>), grid, TC_THREADS, smem, tm_w, tm_x, a, g.w_scale, g.ws_stride);
+    VN_LAUNCH_PDL_LEVEL(ctx, 1, name, (gemm_tcq_kernel<QMODE, TC_STORE>), grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a, g.w_scale, g.ws_stride);
   return VN_OK;
 }
 

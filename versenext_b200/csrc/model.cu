@@ -903,7 +903,6 @@ int32_t vn_model_head(vn_model* m, const float* hidden_dev, int32_t rows, int32_
   VN_CHECK_CTX(ctx);
   const Config& c = m->cfg;
   VN_REQUIRE(ctx, m->finalized, "model is not finalised");
-  VN_REQUIRE(ctx, m->qmode == 0, "vn_model_head needs dense head weights");
   VN_REQUIRE(ctx, rows >= 0 && v_lo >= 0 && n_cols >= 0 && (long long)v_lo + n_cols <= c.vocab && out_ld >= n_cols,
              "column range [%d, %d) outside the vocabulary of %d", v_lo, v_lo + n_cols, c.vocab);
   if (rows == 0 || n_cols == 0) return VN_OK;
@@ -919,13 +918,19 @@ int32_t vn_model_head(vn_model* m, const float* hidden_dev, int32_t rows, int32_
       VN_LAUNCH(ctx, cast_rows_kernel<__nv_bfloat16>, (unsigned)ceil_div(n, 256ll), 256, 0, hidden_dev + (long long)r0 * D,
                 (__nv_bfloat16*)m->h, n);
       g.A = m->h;
-      g.W = (const __nv_bfloat16*)m->head + (long long)v_lo * D;
+      if (m->qmode) {     // the quantised head copy: rows v_lo .. of the bytes (or nibbles) and of the scales
+        g.W = (const unsigned char*)m->head_q + (long long)v_lo * (m->qmode == 1 ? D : D / 2);
+        g.w_scale = m->head_qs + (long long)v_lo * (m->qmode == 3 ? (D + 127) / 128 : 1);
+        g.wq = m->qmode;
+      } else {
+        g.W = (const __nv_bfloat16*)m->head + (long long)v_lo * D;
+      }
       GemmArgs probe = g;
-      if (m->use_tc && gemm_tc_supported(probe) && out_ld % 4 == 0 && n_cols >= 1) {
+      if (m->use_tc && (m->qmode ? gemm_tcq_supported(probe) : gemm_tc_supported(probe)) && out_ld % 4 == 0 && n_cols >= 1) {
         TRY(ensure_partial(m, 1024));
         TcPlan direct;
         direct.error_flag = m->tc_error;
-        TRY(launch_gemm_tc(ctx, g, m->cap_rows, direct));
+        TRY(tc_launch(ctx, g, m->cap_rows, direct));
       } else {
         TRY(linear(m, g));
       }
