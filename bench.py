@@ -270,6 +270,8 @@ def run_spec(args):
         B = max(1, SPEC["B"] // world)
     t_build = time.perf_counter()
     target, draft = build_spec_models(f"cuda:{local}")
+    if args.quant:                       # weight-only quantised target (the INT8 / INT4 variants of the workload)
+        target.quantize(args.quant)
     t_build = time.perf_counter() - t_build
     warm = max(args.warmup, 3)
     max_seq = T0 + (warm + 4 * args.steps + 40) * (k + 1) + 64
@@ -358,12 +360,14 @@ def run_spec(args):
     prof_ms = max(sum(v["ms"] for v in rep.values()) / n_prof, 1e-9)
     gemm_ms = sum(v["ms"] for n, v in rep.items() if n.startswith("gemm_")) / n_prof * (step_ms / prof_ms)
     nbytes = spec_step_bytes(B, ctx_len)
+    if args.quant:   # streamed weights: everything but the bf16 embedding table (the head has its own quantised copy)
+        nbytes += target.param_bytes() - 248320 * 1024 * 2 - MATE_PARAMS * 2
     peak, peak_kind = peaks()
     achieved = nbytes / (step_ms * 1e-3) / 1e9
     top = sorted(rep.items(), key=lambda kv: -kv[1]["ms"])
     roofline = {"bound": "hbm", "kernel": "verify+sample step (all kernels of the target forward and acceptance)",
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": f"of {peak_kind}", "traffic": SPEC_STEP_TRAFFIC, "step_ms": step_ms, "algorithmic_bytes": nbytes,
+                "peak_kind": f"of {peak_kind}", "traffic": None if args.quant else SPEC_STEP_TRAFFIC, "step_ms": step_ms, "algorithmic_bytes": nbytes,
                 "gemm_ms": gemm_ms, "gemm_weight_gbs": MATE_PARAMS * 2 / (gemm_ms * 1e-3) / 1e9,
                 "kernel_share": {n: v["ms"] / n_prof / prof_ms for n, v in top},
                 "kernel_ms_per_step": {n: v["ms"] / n_prof for n, v in top},
@@ -387,7 +391,8 @@ def run_spec(args):
             "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if args.strong else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": SPEC_WORKLOAD, "per_gpu_requests": B, "context_tokens": ctx_len,
+            "config": {"workload": SPEC_WORKLOAD + (f", target weights {args.quant}" if args.quant else ""),
+                       "per_gpu_requests": B, "context_tokens": ctx_len,
                        "l2": "weights (2.2 GB) larger than L2, no flush", "step": "one speculative round"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clk,
             "accept_rate": accept_rate, "tokens_per_round_per_request": committed / world / B / args.steps,
@@ -582,6 +587,8 @@ def main():
     ap.add_argument("--workload", default="spec", choices=["spec", "accept"])
     ap.add_argument("--strong", action="store_true",
                     help="spec workload: split the configuration's 32 requests over the ranks (default: 32 per rank)")
+    ap.add_argument("--quant", default=None, choices=["int8", "int4", "int4g128"],
+                    help="spec workload: quantise the target's linear weights (not the default benchmark line)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-sampler", action="store_true", help="spec workload: skip the sampler GB/s measurement")
     args = ap.parse_args()

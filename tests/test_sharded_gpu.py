@@ -214,6 +214,25 @@ def test_sharded_engine_equals_plain_engine_on_one_rank():
     assert sum(len(a) for a in plain) > 6 * 6               # some proposals were accepted
 
 
+@pytest.mark.parametrize("scheme", ["int8", "int4g128"])
+def test_sharded_engine_with_a_quantised_target(scheme):
+    """Vocabulary-sharded acceptance on a weight-only quantised target (the INT8 / INT4 variants of the sharded
+    configuration): the column-split head works on the quantised head copy, and the round commits the tokens of
+    the plain engine run on the same quantised models."""
+    import versenext_b200 as vn
+    from oracle import model as OM
+    from versenext_b200.sharded_engine import ShardedSpecEngine
+    target, draft = _small_pair(vn, OM)
+    target.quantize(scheme)
+    prompts = np.random.default_rng(14).integers(0, 1024, (6, 20))
+    kw = dict(max_batch=6, max_seq=128, k=3, temperature=0.9, seed=19)
+    plain = _engine_tokens(vn.SpecEngine(target, draft, top_k=0, graph=False, **kw), prompts, 6)
+    shard = _engine_tokens(ShardedSpecEngine(target, draft, **kw), prompts, 6)
+    for a, b in zip(plain, shard):
+        np.testing.assert_array_equal(a, b)
+    target.check()
+
+
 def _engine_worker(rank, world, port, out):
     import os
     import sys
