@@ -37,6 +37,7 @@ int32_t vn_ctx_destroy(vn_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   if (ctx->ws) cudaFree(ctx->ws);
   if (ctx->flush) cudaFree(ctx->flush);
+  if (ctx->tickets) cudaFree(ctx->tickets);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return VN_OK;
@@ -230,6 +231,15 @@ void vn_prof_begin(vn_ctx* ctx, const char* name) {
 
 void vn_prof_end(vn_ctx* ctx) {
   if (!ctx->prof.empty()) cudaEventRecord(ctx->prof.back().b, ctx->stream);
+}
+
+int32_t vn_tickets(vn_ctx* ctx, int** out) {
+  if (!ctx->tickets) {
+    VN_CUDA(ctx, cudaMalloc((void**)&ctx->tickets, sizeof(int) * VN_TICKETS));
+    VN_CUDA(ctx, cudaMemsetAsync(ctx->tickets, 0, sizeof(int) * VN_TICKETS, ctx->stream));
+  }
+  *out = ctx->tickets;
+  return VN_OK;
 }
 
 int32_t vn_workspace(vn_ctx* ctx, size_t bytes, void** out) {

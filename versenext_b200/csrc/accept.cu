@@ -12,8 +12,10 @@
 // different summation order cannot move a decision relative to the CPU restatement.
 //
 // Top-k path: accept_topk_kernel reduces every row to its (token, scaled logit) list of the
-// entries >= the k-th largest value (radix select on order-preserving keys), then
-// accept_topk_decide_kernel applies the same rule on those short lists.
+// entries >= the k-th largest value (bound pass + rank counting, radix select as the fallback), the
+// slices of a row are merged, and the same rule is applied on those short lists: three launches.  Opt-in
+// (VN_TOPK_FUSE=1) the three steps run in one launch: the CTA that takes a row's last arrival ticket merges it,
+// the CTA that takes a sequence's last ticket decides it, with the same code as the separate kernels.
 #include <stdlib.h>
 #include "common.cuh"
 #include <math_constants.h>
@@ -485,13 +487,40 @@ struct TopkRow {
   int overflow;          // 1 when ties at the threshold did not fit
   int tok[KEEP_MAX];     // ascending token id
   float val[KEEP_MAX];   // scaled logit
+  int pad[30];           // whole 128-byte lines: no two lists share a cache line (a CTA reads lists that CTAs on
+                         // other SMs wrote earlier in the same kernel; a shared line could be stale in its L1)
 };
+static_assert(sizeof(TopkRow) % 128 == 0, "TopkRow must cover whole cache lines");
+
+// what the decision step needs besides the lists
+struct DecideArgs {
+  int B, k, np, nq;
+  const long long* draft;
+  const float* u_acc;
+  const float* u_smp;
+  uint64_t seed;
+  uint32_t offset_host;
+  const unsigned* offset_dev;
+  int bonus, smp_purpose, pos_base;
+  int* out_len;
+  long long* out_tok;
+};
+
+// merge + decision code shared by the fused tail of accept_topk_kernel and the standalone kernels
+__device__ void topk_merge_rows(const TopkRow* pr, int chunks, int top_k, TopkRow* o, float* s_val, int* s_tok,
+                                int* s_off, int* s_n, float* s_kth, int* s_cnt);
+constexpr int DEC_ROWS = 16, DEC_ENT = 64;
+__device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& da, const TopkRow* rows,
+                                             int (*s_tok)[DEC_ENT], float (*s_val)[DEC_ENT], int* s_n);
 
 // One CTA per row.  Radix select (11 + 11 + 10 bits) of the k-th largest key.  After each level
 // the number of keys that can still be kept is known from the histogram; as soon as they fit in
 // shared memory they are gathered (one more read of the row) and the select finishes there.
-__global__ void __launch_bounds__(1024)
-accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* __restrict__ out) {
+// (two CTAs per SM: the select loops need 32 registers; the decision code of the fused tail, which one warp of a
+// few CTAs runs once, is kept out of line and may spill)
+__global__ void __launch_bounds__(1024, 2)
+accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, TopkRow* merged, int* tickets,
+                   DecideArgs da) {
   pdl_trigger();
   pdl_wait();
   // blockIdx.x = row * chunks + chunk: every CTA selects inside its own slice of the row; the slices'
@@ -504,9 +533,12 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* __rest
   const int V = max(0, min(slice, rs.V - base0)), tid = threadIdx.x, nt = blockDim.x;
   const bool scale = temp != 1.0f;
   const int want = top_k < V ? top_k : V;
-  __shared__ uint32_t hist[2048];
-  __shared__ uint32_t c_key[CAND_MAX];
-  __shared__ int c_tok[CAND_MAX];
+  // one pool, used in turn by the select (histogram + candidates, 16 KB), the merge of a row's slices (32 KB) and
+  // the decision step (8 KB)
+  __shared__ __align__(16) unsigned char s_pool[32768];
+  uint32_t* hist = reinterpret_cast<uint32_t*>(s_pool);                   // [2048]
+  uint32_t* c_key = reinterpret_cast<uint32_t*>(s_pool + 8192);           // [CAND_MAX]
+  int* c_tok = reinterpret_cast<int*>(s_pool + 12288);                    // [CAND_MAX]
   __shared__ int wcount[32];
   __shared__ uint32_t s_prefix, s_mask, s_kth;
   __shared__ int s_need, s_ncand, s_done, s_nout, s_base;
@@ -690,26 +722,56 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* __rest
     }
     if (tid == 0) { o->n = min(s_base, KEEP_MAX); o->overflow = s_base > KEEP_MAX; }
   }
+  if (!tickets) return;        // unfused: the merge and decision kernels follow in the stream
+  // ---- fused tail: the CTA that finishes a row's last slice merges the row; the CTA that finishes a sequence's
+  // last row takes the sequence's decisions.  Arrival counters (release: fence before the ticket; acquire: fence
+  // after it), no waiting anywhere; the last arrival sets the counter back to zero for the next launch.
+  __shared__ int s_last;
+  const int n_rows = gridDim.x / chunks;
+  if (chunks > 1) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int last = atomicAdd(&tickets[r], 1) == chunks - 1;
+      if (last) tickets[r] = 0;
+      s_last = last;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    __shared__ int s_off[65], s_n[64], s_cnt;
+    __shared__ float s_kthf;
+    topk_merge_rows(out + (long long)r * chunks, chunks, top_k, merged + r, reinterpret_cast<float*>(s_pool),
+                    reinterpret_cast<int*>(s_pool + 16384), s_off, s_n, &s_kthf, &s_cnt);
+  }
+  const int b = r / rows_per_seq;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int last = atomicAdd(&tickets[n_rows + b], 1) == rows_per_seq - 1;
+    if (last) tickets[n_rows + b] = 0;
+    s_last = last;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (tid < 32) {
+    __shared__ int s_dn[DEC_ROWS];
+    topk_decide_seq(b, tid, da, merged, reinterpret_cast<int(*)[DEC_ENT]>(s_pool),
+                    reinterpret_cast<float(*)[DEC_ENT]>(s_pool + DEC_ROWS * DEC_ENT * 4), s_dn);
+  }
 }
 
 // Merge the slices' lists of one row: the global k-th largest value is found among the candidates by rank
 // counting, everything >= it is kept; slices are in ascending token order, so the output is too.
-__global__ void __launch_bounds__(1024)
-accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_k, TopkRow* __restrict__ out) {
-  pdl_trigger();
-  pdl_wait();
+__device__ void topk_merge_rows(const TopkRow* pr, int chunks, int top_k, TopkRow* o, float* s_val, int* s_tok,
+                                int* s_off, int* s_n, float* s_kth, int* s_cnt) {
   constexpr int MERGE_MAX = 4096;
-  __shared__ float s_val[MERGE_MAX];
-  __shared__ int s_tok[MERGE_MAX];
-  __shared__ int s_off[65];
-  __shared__ float s_kth;
-  __shared__ int s_cnt;
-  const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
-  const TopkRow* pr = parts + (long long)r * chunks;
-  // list lengths in one round trip (chunks <= 64), exclusive offsets by one warp
-  __shared__ int s_n[64];
+  const int tid = threadIdx.x, nt = blockDim.x;
+  __syncthreads();             // the caller's earlier use of the shared arrays is over
+  // list lengths in one round trip (chunks <= 64), exclusive offsets by one thread
   if (tid < 64) s_n[tid] = tid < chunks ? pr[tid].n : 0;
-  if (tid == 0) { s_kth = -CUDART_INF_F; s_cnt = 0; }
+  if (tid == 0) { *s_kth = -CUDART_INF_F; *s_cnt = 0; }
   __syncthreads();
   if (tid == 0) {
     int acc = 0;
@@ -731,20 +793,31 @@ accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_
     const float vi = s_val[i];
     int greater = 0, geq = 0;
     for (int j = 0; j < n; ++j) { greater += s_val[j] > vi; geq += s_val[j] >= vi; }
-    if (greater < want && geq >= want) s_kth = vi;   // every writer holds the same value
+    if (greater < want && geq >= want) *s_kth = vi;   // every writer holds the same value
   }
   __syncthreads();
-  const float kth = s_kth;
-  TopkRow* o = out + r;
+  const float kth = *s_kth;
   for (int i = tid; i < n; i += nt)
     if (s_val[i] >= kth) {
       int pos = 0;
       for (int j = 0; j < i; ++j) pos += s_val[j] >= kth;
       if (pos < KEEP_MAX) { o->tok[pos] = s_tok[i]; o->val[pos] = s_val[i]; }
-      atomicAdd(&s_cnt, 1);
+      atomicAdd(s_cnt, 1);
     }
   __syncthreads();
-  if (tid == 0) { o->n = min(s_cnt, KEEP_MAX); o->overflow = s_cnt > KEEP_MAX; }
+  if (tid == 0) { o->n = min(*s_cnt, KEEP_MAX); o->overflow = *s_cnt > KEEP_MAX; }
+}
+
+__global__ void __launch_bounds__(1024)
+accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_k, TopkRow* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float s_val[4096];
+  __shared__ int s_tok[4096];
+  __shared__ int s_off[65], s_n[64], s_cnt;
+  __shared__ float s_kth;
+  const int r = blockIdx.x;
+  topk_merge_rows(parts + (long long)r * chunks, chunks, top_k, out + r, s_val, s_tok, s_off, s_n, &s_kth, &s_cnt);
 }
 
 // ---- warp-cooperative helpers on a kept list ------------------------------------------------------------
@@ -786,31 +859,25 @@ __device__ __forceinline__ float list_find(const ListView& r, int token) {
 }
 
 // One warp per sequence: acceptance tests, then the inverse CDF over the kept list of the row to sample.
-__global__ void __launch_bounds__(128)
-accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restrict__ rows,
-                          const long long* __restrict__ draft, const float* __restrict__ u_acc,
-                          const float* __restrict__ u_smp, uint64_t seed, uint32_t offset_host,
-                          const unsigned* __restrict__ offset_dev, int bonus, int smp_purpose, int pos_base,
-                          int* __restrict__ out_len, long long* __restrict__ out_tok) {
-  pdl_trigger();
-  pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (b >= B) return;
-  const uint32_t offset = offset_host + (offset_dev ? *offset_dev : 0u);
+// s_tok / s_val / s_n: this warp's staging arrays in shared memory.
+__device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& da, const TopkRow* rows,
+                                             int (*s_tok)[DEC_ENT], float (*s_val)[DEC_ENT], int* s_n) {
+  const int k = da.k, np = da.np, nq = da.nq, bonus = da.bonus, smp_purpose = da.smp_purpose, pos_base = da.pos_base;
+  const long long* draft = da.draft;
+  const float* u_acc = da.u_acc;
+  const float* u_smp = da.u_smp;
+  const uint64_t seed = da.seed;
+  int* out_len = da.out_len;
+  long long* out_tok = da.out_tok;
+  const uint32_t offset = da.offset_host + (da.offset_dev ? *da.offset_dev : 0u);
   const int rows_per_seq = np + nq;
   const TopkRow* rb = rows + (long long)b * rows_per_seq;
   // The lists of this sequence are read many times below, each read a dependent round trip to L2: copy them
   // into shared memory first when they fit (at most DEC_ROWS rows of DEC_ENT entries, the usual case).
-  constexpr int DEC_ROWS = 16, DEC_ENT = 64;
-  __shared__ int s_tok[4][DEC_ROWS][DEC_ENT];
-  __shared__ float s_val[4][DEC_ROWS][DEC_ENT];
-  __shared__ int s_n[4][DEC_ROWS];
-  const int wslot = threadIdx.x >> 5;
   bool staged = rows_per_seq <= DEC_ROWS;
   if (staged) {
     int nmax = 0;
-    for (int r = lane; r < rows_per_seq; r += 32) { const int nr = rb[r].n; s_n[wslot][r] = nr; nmax = max(nmax, nr); }
+    for (int r = lane; r < rows_per_seq; r += 32) { const int nr = rb[r].n; s_n[r] = nr; nmax = max(nmax, nr); }
     __syncwarp();
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
@@ -819,15 +886,15 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
   if (staged) {
     for (int idx = lane; idx < rows_per_seq * DEC_ENT; idx += 32) {
       const int r = idx / DEC_ENT, i = idx % DEC_ENT;
-      if (i < s_n[wslot][r]) { s_tok[wslot][r][i] = rb[r].tok[i]; s_val[wslot][r][i] = rb[r].val[i]; }
+      if (i < s_n[r]) { s_tok[r][i] = rb[r].tok[i]; s_val[r][i] = rb[r].val[i]; }
     }
     __syncwarp();
   }
   auto view = [&](int r) {
     ListView v;
-    v.n = staged ? s_n[wslot][r] : rb[r].n;
-    v.tok = staged ? s_tok[wslot][r] : rb[r].tok;
-    v.val = staged ? s_val[wslot][r] : rb[r].val;
+    v.n = staged ? s_n[r] : rb[r].n;
+    v.tok = staged ? s_tok[r] : rb[r].tok;
+    v.val = staged ? s_val[r] : rb[r].val;
     return v;
   };
   long long* tok = out_tok + (long long)b * (k + 1);
@@ -938,6 +1005,20 @@ accept_topk_decide_kernel(int B, int k, int np, int nq, const TopkRow* __restric
   }
 }
 
+
+__global__ void __launch_bounds__(128)
+accept_topk_decide_kernel(DecideArgs da, const TopkRow* __restrict__ rows) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, wslot = threadIdx.x >> 5;
+  const int b = blockIdx.x * (blockDim.x >> 5) + wslot;
+  if (b >= da.B) return;
+  __shared__ int s_tok[4][DEC_ROWS][DEC_ENT];
+  __shared__ float s_val[4][DEC_ROWS][DEC_ENT];
+  __shared__ int s_n[4][DEC_ROWS];
+  topk_decide_seq(b, lane, da, rows, s_tok[wslot], s_val[wslot], s_n[wslot]);
+}
+
 }  // namespace
 
 int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_si,
@@ -977,10 +1058,24 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
     if (st) return st;
     TopkRow* rows = (TopkRow*)ws;                 // merged lists [n_rows]
     TopkRow* parts = rows + n_rows;               // per-slice lists [n_rows * chunks]
-    VN_LAUNCH_PDL(ctx, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, chunks > 1 ? parts : rows);
-    if (chunks > 1) VN_LAUNCH_PDL(ctx, accept_topk_merge_kernel, n_rows, 1024, 0, parts, chunks, top_k, rows);
-    VN_LAUNCH_PDL(ctx, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, B, k, rs.np, rs.nq, rows, d64, u_acc, u_smp,
-              seed, offset, ctx->offset_src, bonus, smp_purpose, pos_base, out_len, o64);
+    DecideArgs da;
+    da.B = B; da.k = k; da.np = rs.np; da.nq = rs.nq; da.draft = d64; da.u_acc = u_acc; da.u_smp = u_smp;
+    da.seed = seed; da.offset_host = offset; da.offset_dev = ctx->offset_src; da.bonus = bonus;
+    da.smp_purpose = smp_purpose; da.pos_base = pos_base; da.out_len = out_len; da.out_tok = o64;
+    // VN_TOPK_FUSE=1 (read on every call): one launch, in which the CTA that completes a row merges its slices and
+    // the CTA that completes a sequence decides it (arrival counters, nothing waits).  Measured on B200 the round
+    // is no faster than with the three kernels in stream order (2.44 against 2.43 ms: the tail CTAs run the merge
+    // and the single-warp decision while holding half an SM each), so the three launches stay the default.
+    const char* fuse_env = getenv("VN_TOPK_FUSE");
+    const bool fuse_on = fuse_env && fuse_env[0] == '1';
+    int* tickets = nullptr;
+    if (fuse_on && (long long)n_rows + B <= VN_TICKETS) { st = vn_tickets(ctx, &tickets); if (st) return st; }
+    VN_LAUNCH_PDL(ctx, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, chunks > 1 ? parts : rows,
+                  rows, tickets, da);
+    if (!tickets) {
+      if (chunks > 1) VN_LAUNCH_PDL(ctx, accept_topk_merge_kernel, n_rows, 1024, 0, parts, chunks, top_k, rows);
+      VN_LAUNCH_PDL(ctx, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, da, rows);
+    }
     return VN_OK;
   }
 

@@ -23,6 +23,9 @@ struct vn_ctx {
   size_t ws_bytes = 0;
   void* flush = nullptr;
   size_t flush_bytes = 0;
+  // arrival counters for kernels whose last CTA finishes a row's work (VN_TICKETS ints, zero between kernels:
+  // whoever takes the last ticket sets the counter back)
+  int* tickets = nullptr;
   int sm_count = 148;
   // when set, every Philox offset of the acceptance / sampling kernels is incremented by *offset_src
   // (a round counter that lives on the device, so that a captured graph draws fresh numbers on every replay)
@@ -39,6 +42,8 @@ struct vn_ctx {
   std::vector<ProfRec> prof;
 };
 
+constexpr int VN_TICKETS = 1 << 16;
+int32_t vn_tickets(vn_ctx* ctx, int** out);
 void vn_prof_begin(vn_ctx* ctx, const char* name);
 void vn_prof_end(vn_ctx* ctx);
 

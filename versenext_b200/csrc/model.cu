@@ -470,6 +470,12 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     g.ws_stride = rows_per_seg * (m->qmode == 3 ? (g.K + 127) / 128 : 1);
   };
   const int use_cluster = m->qmode ? 0 : m->use_cluster;   // the cluster reduce exists for dense weights only
+  // A GEMM whose whole K range fits one CTA (the draft model's projections) has nothing to reduce: as a cluster
+  // of one it applies RoPE + cache append or SwiGLU itself and the finalize kernel behind it disappears.
+  static const bool single_on = [] { const char* e = getenv("VN_TC_SINGLE"); return !(e && e[0] == '0'); }();
+  auto fused = [&](const GemmArgs& g) {
+    return use_cluster || (single_on && !m->qmode && tc_splits(ctx, g.N, g.K, 1) == 1);
+  };
   // expert_count is zero between forwards: the combine kernel of every MoD layer leaves it so
   VN_LAUNCH_PDL(ctx, embed_norm_kernel<T>, M, 256, 0, (const long long*)tokens, (const T*)m->emb, m->x,
                 m->layers[0].norm1, (T*)m->h, D, c.vocab, emb_scale, 1e-6f, m->status);
@@ -488,7 +494,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     rope.kc = kv->k[li]; rope.vc = kv->v[li]; rope.q_out = m->qkv; rope.ldq = qkv_ld;
     rope.Tn = Tn; rope.H = H; rope.n_kv = n_kv; rope.hd = hd; rope.max_seq = kv->max_seq;
     rope.use_rope = c.use_rope; rope.rope_rows = m->rope_rows; rope.slot_offset = slot_offset;
-    if (use_cluster && gemm_tc_cluster_supported(g, tc_detail::TC_CL_QKV, &rope)) {
+    if (fused(g) && gemm_tc_cluster_supported(g, tc_detail::TC_CL_QKV, &rope)) {
       TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_QKV, nullptr, &rope));
     } else {
       TRY(tc_partial(m, g, cap, M, &sp));
@@ -534,7 +540,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.tag = "gemm_gateup";
       g.C = m->act; g.ldc = c.mlp_hidden; g.c_bf16 = 1;
       pick(g, L.q[2], L.qs[2], 0);
-      if (use_cluster && gemm_tc_cluster_supported(g, tc_detail::TC_CL_SWIGLU, nullptr)) {
+      if (fused(g) && gemm_tc_cluster_supported(g, tc_detail::TC_CL_SWIGLU, nullptr)) {
         TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_SWIGLU, nullptr, nullptr));
       } else {
         TRY(tc_partial(m, g, cap, M, &sp));
