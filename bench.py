@@ -402,6 +402,77 @@ def run_spec(args):
         dist.destroy_process_group()
 
 
+def run_sharded(args):
+    """The vocabulary-sharded configuration: 32 requests per rank, 1024-token prompts, k = 6, T = 1.0, full-vocabulary
+    rule, target linears INT8 (or --quant), LM head and acceptance split by vocabulary columns over the ranks
+    (hidden-row all-gather + three small exchanges per round, host-staged).  Not the default benchmark line."""
+    import versenext_b200 as vn
+    from versenext_b200.sharded_engine import ShardedSpecEngine
+    world, rank, local, dist = dist_setup(args.gpus)
+    ctx = vn.Context.get(local)
+    B, k, T0 = 32, 6, 1024
+    scheme = args.quant or "int8"
+    target, draft = build_spec_models(f"cuda:{local}")
+    target.quantize(scheme)
+    warm = max(args.warmup, 3)
+    rounds = warm + args.steps + 8
+    eng = ShardedSpecEngine(target, draft, max_batch=B, max_seq=T0 + rounds * (k + 1) + 64, k=k, temperature=1.0,
+                            seed=5, max_new_tokens=rounds * (k + 1))
+    eng.prefill(np.random.default_rng([5, rank]).integers(0, 248320, (B, T0)).astype(np.int64))
+    for _ in range(warm):
+        eng.step()
+    c0 = eng.counts().sum()
+    clocks = ClockSampler(local).start() if rank == 0 else None
+    barrier_sync(dist, ctx)
+    l0 = ctx.launch_count()
+    t0 = time.perf_counter()          # a round synchronises with the host several times: wall clock is the honest one
+    for _ in range(args.steps):
+        eng.step()
+    ctx.sync()
+    ms = (time.perf_counter() - t0) * 1e3
+    barrier_sync(dist, ctx)
+    launches = ctx.launch_count() - l0
+    clk = clocks.stop() if clocks else None
+    committed = float(eng.counts().sum() - c0)
+    ms = max_over_ranks(dist, ms, local)
+    if dist is not None:
+        import torch
+        t = torch.tensor([committed], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t)
+        committed = float(t.item())
+    value = committed / (ms * 1e-3)
+    ctx_len = int(eng.t_cache.per_seq_lens.mean())
+    # streamed per round and rank: the quantised block weights, this rank's columns of the head, the K/V window
+    head_bytes = 248320 * 1024 * (1 if scheme == "int8" else 0.5)
+    nbytes = (target.param_bytes() - 248320 * 1024 * 2 - head_bytes * (1 - 1 / world)
+              + 20 * B * min(ctx_len, 1024) * 2 * 512 * 2)
+    peak, peak_kind = peaks()
+    step_ms = ms / args.steps
+    achieved = nbytes / (step_ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": "accepted tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"sharded: mate target with {scheme} linears + 2-layer D=256 draft, k=6, T=1.0, "
+                                   f"full-vocabulary rule, 32 requests/GPU, 1024-token prompts, LM head and acceptance "
+                                   f"split by vocabulary columns over {world} rank(s), exchanges staged through the host",
+                       "per_gpu_requests": B, "context_tokens": ctx_len, "step": "one speculative round",
+                       "timing": "wall clock around the rounds (max over ranks)"},
+            "roofline": {"bound": "hbm", "kernel": "whole round (draft, verify, column-split head, sharded acceptance, "
+                                                   "host-staged exchanges)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": f"of {peak_kind}", "traffic": None, "algorithmic_bytes": nbytes},
+            "cpu_baseline": None, "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": None,
+                                          "d2h_bytes_per_step": None},
+            "gpu_launches": launches, "clocks": clk,
+            "accept_rate": float(eng.accept_len.numpy().mean() / k),
+            "tokens_per_round_per_request": committed / world / B / args.steps,
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def accept_quick(ctx, steps=20):
     """sampler GB/s of the isolated acceptance op (second half of the headline metric)."""
     from versenext_b200 import sampling
@@ -584,7 +655,7 @@ def main():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="spec", choices=["spec", "accept"])
+    ap.add_argument("--workload", default="spec", choices=["spec", "accept", "sharded"])
     ap.add_argument("--strong", action="store_true",
                     help="spec workload: split the configuration's 32 requests over the ranks (default: 32 per rank)")
     ap.add_argument("--quant", default=None, choices=["int8", "int4", "int4g128"],
@@ -593,9 +664,9 @@ def main():
     ap.add_argument("--no-sampler", action="store_true", help="spec workload: skip the sampler GB/s measurement")
     args = ap.parse_args()
     if args.impl == "reference":
-        (run_reference_spec if args.workload == "spec" else run_reference)(args)
+        (run_reference if args.workload == "accept" else run_reference_spec)(args)
     else:
-        (run_spec if args.workload == "spec" else run_accept)(args)
+        {"spec": run_spec, "accept": run_accept, "sharded": run_sharded}[args.workload](args)
 
 
 if __name__ == "__main__":

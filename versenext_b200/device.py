@@ -54,6 +54,10 @@ class Context:
         h = C.c_void_p()
         _lib.check(None, self.lib.vn_ctx_create(self.device, C.byref(h)))
         self.handle = h
+        self._pool: dict = {}
+        self._pool_class: dict = {}
+        self._pool_bytes = 0
+        self._pool_lock = threading.Lock()
 
     @classmethod
     def get(cls, device: int = 0) -> "Context":
@@ -66,13 +70,62 @@ class Context:
         _lib.check(self.handle, status)
 
     # -- memory ------------------------------------------------------------
-    def alloc(self, nbytes: int) -> int:
+    # Blocks of up to POOL_BLOCK_MAX bytes are kept in size classes when they are freed and handed out again
+    # (cudaMalloc / cudaFree cost tens of microseconds each and cudaFree waits for the device).  Everything the
+    # context does runs on its one stream, so a block that is reused is touched in stream order.
+    POOL_BLOCK_MAX = 64 << 20
+    POOL_TOTAL_MAX = 1 << 30
+
+    @staticmethod
+    def _size_class(nbytes: int) -> int:
+        n = max(int(nbytes), 256)
+        if n <= (1 << 20):
+            return 1 << (n - 1).bit_length()          # powers of two up to 1 MiB
+        return (n + (1 << 20) - 1) & ~((1 << 20) - 1)  # then whole MiB
+
+    def _raw_alloc(self, nbytes: int) -> int:
         p = C.c_void_p()
         self._check(self.lib.vn_alloc(self.handle, int(nbytes), C.byref(p)))
         return p.value
 
+    def alloc(self, nbytes: int) -> int:
+        if nbytes > self.POOL_BLOCK_MAX:
+            return self._raw_alloc(nbytes)
+        cls = self._size_class(nbytes)
+        with self._pool_lock:
+            free = self._pool.get(cls)
+            if free:
+                self._pool_bytes -= cls
+                return free.pop()
+        try:
+            ptr = self._raw_alloc(cls)
+        except (MemoryError, RuntimeError):
+            self.release_pool()                        # out of memory: give the cached blocks back and try once more
+            ptr = self._raw_alloc(cls)
+        with self._pool_lock:
+            self._pool_class[ptr] = cls
+        return ptr
+
     def free(self, ptr: int):
+        with self._pool_lock:
+            cls = self._pool_class.get(ptr)
+            if cls is not None and self._pool_bytes + cls <= self.POOL_TOTAL_MAX:
+                self._pool.setdefault(cls, []).append(ptr)
+                self._pool_bytes += cls
+                return
+            self._pool_class.pop(ptr, None)
         self._check(self.lib.vn_free(self.handle, C.c_void_p(ptr)))
+
+    def release_pool(self):
+        """Return every cached block to the driver."""
+        with self._pool_lock:
+            blocks = [p for lst in self._pool.values() for p in lst]
+            self._pool.clear()
+            self._pool_bytes = 0
+            for p in blocks:
+                self._pool_class.pop(p, None)
+        for p in blocks:
+            self.lib.vn_free(self.handle, C.c_void_p(p))
 
     def empty(self, shape, dtype=np.float32) -> "DeviceArray":
         shape = tuple(int(s) for s in (shape if isinstance(shape, (tuple, list)) else (shape,)))
@@ -229,7 +282,7 @@ class DeviceArray:
     def __del__(self):
         if getattr(self, "_owner", False) and self.ptr:
             try:
-                self.ctx.lib.vn_free(self.ctx.handle, C.c_void_p(self.ptr))
+                self.ctx.free(self.ptr)
             except Exception:
                 pass
             self.ptr = 0
