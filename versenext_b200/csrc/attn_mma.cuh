@@ -355,6 +355,7 @@ inline int32_t launch_attn_mma(vn_ctx* ctx, const AttnArgs& a, int B) {
                                       (int)smem));
     attr_set |= 1ull << (ctx->device & 63);
   }
-  VN_LAUNCH_PDL(ctx, attn_detail::trisparse_attn_mma_kernel, grid, attn_detail::AW * 32, smem, a);
+  VN_LAUNCH_PDL_LEVEL(ctx, (vn_pdl_mask() & 1) ? 1 : 2, "attn_detail::trisparse_attn_mma_kernel", attn_detail::trisparse_attn_mma_kernel, grid,
+                      attn_detail::AW * 32, smem, a);
   return VN_OK;
 }

@@ -1,5 +1,6 @@
 // Shared host-side plumbing of the library: context, error reporting, launch accounting.
 #pragma once
+#include <stdlib.h>
 
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -167,6 +168,16 @@ inline cudaError_t vn_launch_pdl(vn_ctx* ctx, int level, void (*kernel)(KArgs...
   VN_LAUNCH_PDL_LEVEL(ctx, 2, name, kernel, grid, block, smem, __VA_ARGS__)
 #define VN_LAUNCH_PDL(ctx, kernel, grid, block, smem, ...) \
   VN_LAUNCH_PDL_LEVEL(ctx, 2, #kernel, kernel, grid, block, smem, __VA_ARGS__)
+// Kernel families that join the default level one by one: VN_PDL_MASK in the environment, a sum of
+// 1 attention, 2 q|k|v finalize, 4 split-K add + norm, 8 split-K SwiGLU, 16 routing / dispatch / combine.
+// Default 4: measured on B200 (config-4 round, 2.425 ms with none) 1 -> 2.423, 2 -> 2.424, 4 -> 2.398, 8 -> 2.425,
+// 16 -> 2.425, 4+1 -> 2.403, 4+8 -> 2.400, all -> 2.418: only the 35 add + norm launches per forward pay.
+inline int vn_pdl_mask() {
+  static const int m = [] { const char* e = getenv("VN_PDL_MASK"); return e ? atoi(e) : 4; }();
+  return m;
+}
+#define VN_LAUNCH_PDL_BIT(ctx, bit, kernel, grid, block, smem, ...) \
+  VN_LAUNCH_PDL_LEVEL(ctx, (vn_pdl_mask() & (bit)) ? 1 : 2, #kernel, kernel, grid, block, smem, __VA_ARGS__)
 
 int32_t vn_workspace(vn_ctx* ctx, size_t bytes, void** out);
 

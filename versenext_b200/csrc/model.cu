@@ -498,7 +498,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_QKV, nullptr, &rope));
     } else {
       TRY(tc_partial(m, g, cap, M, &sp));
-      VN_LAUNCH_PDL(ctx, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld,
+      VN_LAUNCH_PDL_BIT(ctx, 2, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld,
                     m->qkv, m->rope_cos, m->rope_sin, kv->lens, tree ? m->depth_dev : (const int*)nullptr,
                     (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
     }
@@ -529,7 +529,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
                     1e-6f);
     } else {
       TRY(tc_partial(m, g, cap, M, &sp));
-      VN_LAUNCH_PDL(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, L.norm2,
+      VN_LAUNCH_PDL_BIT(ctx, 4, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, L.norm2,
                     (T*)m->h, mod ? m->h32 : (float*)nullptr, D, 1e-6f);
     }
     // ---- feed-forward block
@@ -545,7 +545,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       } else {
         TRY(tc_partial(m, g, cap, M, &sp));
         const long long pairs = (long long)M * c.mlp_hidden;
-        VN_LAUNCH_PDL(ctx, splitk_swiglu_kernel<T>, (unsigned)ceil_div(pairs, 256ll), 256, 0, m->partial, sp,
+        VN_LAUNCH_PDL_BIT(ctx, 8, splitk_swiglu_kernel<T>, (unsigned)ceil_div(pairs, 256ll), 256, 0, m->partial, sp,
                   (long long)M * 2 * c.mlp_hidden, (T*)m->act, 2 * c.mlp_hidden, pairs);
       }
       g = GemmArgs();
@@ -559,7 +559,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
           VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
       } else {
         TRY(tc_partial(m, g, cap, M, &sp));
-        VN_LAUNCH_PDL(ctx, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm,
+        VN_LAUNCH_PDL_BIT(ctx, 4, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm,
                       (T*)m->h, (float*)nullptr, D, 1e-6f);
       }
     } else {
@@ -567,8 +567,8 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       RouteArgs r;
       r.h = m->h32; r.gates = L.router; r.slot_expert = m->slot_expert; r.slot_w = m->slot_w; r.part_w = m->part_w;
       r.expert_count = m->expert_count; r.M = M; r.D = D; r.P = c.P; r.E = c.E; r.top_k = c.top_k;
-      VN_LAUNCH_PDL(ctx, mod_route_kernel, M, 512, 0, r);
-      VN_LAUNCH_PDL(ctx, mod_dispatch_kernel<T>, M * S, 128, 0, (const T*)m->h, m->slot_expert, m->expert_count,
+      VN_LAUNCH_PDL_BIT(ctx, 16, mod_route_kernel, M, 512, 0, r);
+      VN_LAUNCH_PDL_BIT(ctx, 16, mod_dispatch_kernel<T>, M * S, 128, 0, (const T*)m->h, m->slot_expert, m->expert_count,
                     m->expert_off, m->expert_cur, m->slot_pos, (T*)m->hs, ne, S, D);
       g = GemmArgs();
       g.A = m->hs; g.lda = D; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
@@ -582,7 +582,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.tag = "gemm_expert_down";
       pick(g, L.q[5], L.qs[5], D);
       TRY(tc_partial(m, g, (long long)M * S, (long long)M * S, &sp));
-      VN_LAUNCH_PDL(ctx, mod_combine_split_kernel, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
+      VN_LAUNCH_PDL_BIT(ctx, 16, mod_combine_split_kernel, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
                 m->slot_w, m->part_w, D, c.P, c.top_k, m->expert_count, m->expert_cur, ne);
       if (next_norm)
         VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
