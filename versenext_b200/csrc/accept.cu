@@ -1070,11 +1070,11 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
     const bool fuse_on = fuse_env && fuse_env[0] == '1';
     int* tickets = nullptr;
     if (fuse_on && (long long)n_rows + B <= VN_TICKETS) { st = vn_tickets(ctx, &tickets); if (st) return st; }
-    VN_LAUNCH_PDL(ctx, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, chunks > 1 ? parts : rows,
+    VN_LAUNCH_PDL_BIT(ctx, 64, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, chunks > 1 ? parts : rows,
                   rows, tickets, da);
     if (!tickets) {
-      if (chunks > 1) VN_LAUNCH_PDL(ctx, accept_topk_merge_kernel, n_rows, 1024, 0, parts, chunks, top_k, rows);
-      VN_LAUNCH_PDL(ctx, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, da, rows);
+      if (chunks > 1) VN_LAUNCH_PDL_BIT(ctx, 128, accept_topk_merge_kernel, n_rows, 1024, 0, parts, chunks, top_k, rows);
+      VN_LAUNCH_PDL_BIT(ctx, 256, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, da, rows);
     }
     return VN_OK;
   }

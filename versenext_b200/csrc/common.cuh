@@ -169,11 +169,13 @@ inline cudaError_t vn_launch_pdl(vn_ctx* ctx, int level, void (*kernel)(KArgs...
 #define VN_LAUNCH_PDL(ctx, kernel, grid, block, smem, ...) \
   VN_LAUNCH_PDL_LEVEL(ctx, 2, #kernel, kernel, grid, block, smem, __VA_ARGS__)
 // Kernel families that join the default level one by one: VN_PDL_MASK in the environment, a sum of
-// 1 attention, 2 q|k|v finalize, 4 split-K add + norm, 8 split-K SwiGLU, 16 routing / dispatch / combine.
-// Default 4: measured on B200 (config-4 round, 2.425 ms with none) 1 -> 2.423, 2 -> 2.424, 4 -> 2.398, 8 -> 2.425,
-// 16 -> 2.425, 4+1 -> 2.403, 4+8 -> 2.400, all -> 2.418: only the 35 add + norm launches per forward pay.
+// 1 attention, 2 q|k|v finalize, 4 split-K add + norm, 8 split-K SwiGLU, 16 routing / dispatch / combine,
+// 32 RMSNorm / embedding, 64 top-k select, 128 top-k merge, 256 top-k decisions.
+// Default 12: measured on B200 (config-4 round, 2.425 ms with none) 1 -> 2.423, 2 -> 2.424, 4 -> 2.398, 16 -> 2.425,
+// all of 1..16 -> 2.418; with the two-pairs-per-thread SwiGLU finalize 4 -> 2.387, 4+8 -> 2.382, and adding 32, 64,
+// 128 or 256 to 4 stays within +-0.002 ms: the small grids that directly follow a GEMM are the ones that pay.
 inline int vn_pdl_mask() {
-  static const int m = [] { const char* e = getenv("VN_PDL_MASK"); return e ? atoi(e) : 4; }();
+  static const int m = [] { const char* e = getenv("VN_PDL_MASK"); return e ? atoi(e) : 12; }();
   return m;
 }
 #define VN_LAUNCH_PDL_BIT(ctx, bit, kernel, grid, block, smem, ...) \

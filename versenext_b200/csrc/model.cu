@@ -477,7 +477,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     return use_cluster || (single_on && !m->qmode && tc_splits(ctx, g.N, g.K, 1) == 1);
   };
   // expert_count is zero between forwards: the combine kernel of every MoD layer leaves it so
-  VN_LAUNCH_PDL(ctx, embed_norm_kernel<T>, M, 256, 0, (const long long*)tokens, (const T*)m->emb, m->x,
+  VN_LAUNCH_PDL_BIT(ctx, 32, embed_norm_kernel<T>, M, 256, 0, (const long long*)tokens, (const T*)m->emb, m->x,
                 m->layers[0].norm1, (T*)m->h, D, c.vocab, emb_scale, 1e-6f, m->status);
   for (int li = 0; li < c.n_layer; ++li) {
     Layer& L = m->layers[li];
@@ -525,7 +525,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     // projections whose finalize kernel disappears (q|k|v, gate|up); VN_TC_CLUSTER=2 forces it here too
     if (use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
       TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_ADD, m->x, nullptr));
-      VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm2, (T*)m->h, mod ? m->h32 : (float*)nullptr, 1, 0, D,
+      VN_LAUNCH_PDL_BIT(ctx, 32, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm2, (T*)m->h, mod ? m->h32 : (float*)nullptr, 1, 0, D,
                     1e-6f);
     } else {
       TRY(tc_partial(m, g, cap, M, &sp));
@@ -545,7 +545,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       } else {
         TRY(tc_partial(m, g, cap, M, &sp));
         const long long pairs = (long long)M * c.mlp_hidden;
-        VN_LAUNCH_PDL_BIT(ctx, 8, splitk_swiglu_kernel<T>, (unsigned)ceil_div(pairs, 256ll), 256, 0, m->partial, sp,
+        VN_LAUNCH_PDL_BIT(ctx, 8, splitk_swiglu_kernel<T>, (unsigned)ceil_div(pairs, 512ll), 256, 0, m->partial, sp,
                   (long long)M * 2 * c.mlp_hidden, (T*)m->act, 2 * c.mlp_hidden, pairs);
       }
       g = GemmArgs();
@@ -556,7 +556,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       if (use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
         TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_ADD, m->x, nullptr));
         if (next_norm)
-          VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
+          VN_LAUNCH_PDL_BIT(ctx, 32, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
       } else {
         TRY(tc_partial(m, g, cap, M, &sp));
         VN_LAUNCH_PDL_BIT(ctx, 4, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm,
@@ -585,12 +585,12 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       VN_LAUNCH_PDL_BIT(ctx, 16, mod_combine_split_kernel, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
                 m->slot_w, m->part_w, D, c.P, c.top_k, m->expert_count, m->expert_cur, ne);
       if (next_norm)
-        VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
+        VN_LAUNCH_PDL_BIT(ctx, 32, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
     }
   }
   const int rows_out = last_only ? B : M;
   const int row_mul = last_only ? Tn : 1, row_add = last_only ? Tn - 1 : 0;
-  VN_LAUNCH_PDL(ctx, rmsnorm_kernel<T>, rows_out, 256, 0, m->x, m->norm_f, (T*)m->h, out_hidden, row_mul, row_add, D, 1e-6f);
+  VN_LAUNCH_PDL_BIT(ctx, 32, rmsnorm_kernel<T>, rows_out, 256, 0, m->x, m->norm_f, (T*)m->h, out_hidden, row_mul, row_add, D, 1e-6f);
   if (out_logits) {
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = m->head; g.ldw = D; g.C = out_logits; g.ldc = c.vocab; g.M = rows_out; g.N = c.vocab;

@@ -594,17 +594,34 @@ __global__ void splitk_swiglu_kernel(const float* __restrict__ partial, int spli
                                      T* __restrict__ act, int N, long long total_pairs) {
   pdl_trigger();
   pdl_wait();
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total_pairs) return;
   const int half = N / 2;
-  const long long row = i / half;
-  const int j = (int)(i % half);
-  float g = 0.f, u = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float2 p = *reinterpret_cast<const float2*>(partial + (long long)s * pstride + row * N + 2 * j);
-    g += p.x; u += p.y;
+  if ((N & 3) == 0) {
+    // two neighbouring pairs per thread: one 16-byte load per split (independent loads, summed in split order)
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= total_pairs) return;
+    const long long row = i / half;
+    const int j = (int)(i % half);
+    const float* p = partial + row * N + 2 * j;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) {
+      const float4 t = *reinterpret_cast<const float4*>(p + (long long)s * pstride);
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+    act[row * half + j] = from_f<T>(silu_ref(acc.x) * acc.y);
+    act[row * half + j + 1] = from_f<T>(silu_ref(acc.z) * acc.w);
+    return;
   }
-  act[row * half + j] = from_f<T>(silu_ref(g) * u);
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2, e = 0; e < 2 && i < total_pairs; ++e, ++i) {
+    const long long row = i / half;
+    const int j = (int)(i % half);
+    float g = 0.f, u = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float2 p = *reinterpret_cast<const float2*>(partial + (long long)s * pstride + row * N + 2 * j);
+      g += p.x; u += p.y;
+    }
+    act[row * half + j] = from_f<T>(silu_ref(g) * u);
+  }
 }
 
 // copy the routed tokens' normalised activations into expert order: dst[pos] = src[sorted_row[pos]]
