@@ -192,6 +192,29 @@ def test_batched_stochastic_engine_matches_oracle():
     np.testing.assert_array_equal(toks, want["tokens"])
 
 
+def test_forward_recurrent_matches_whole_sequence_forward():
+    """CometSparkNexLM.forward_recurrent (cometspark.py:737-767): token by token with the returned states the
+    logits equal those of one forward over the whole sequence; T != 1 is an AssertionError
+    (tri_sparse_attn.py:635) and a full cache a RuntimeError."""
+    cfg = OM.small_config()
+    sd = OM.init_state_dict(cfg, seed=6)
+    m = build(cfg, sd)
+    toks = np.random.default_rng(6).integers(0, cfg.vocab_size, (2, 9))
+    full = np.asarray(m(toks).data)
+    states = None
+    for t in range(toks.shape[1]):
+        lg, states = m.forward_recurrent(toks[:, t:t + 1], states)
+        assert lg.shape == (2, 1, cfg.vocab_size) and len(states) == cfg.n_layer
+        assert rel_err(np.asarray(lg.data)[:, 0], full[:, t]) < 1e-3
+    with pytest.raises(AssertionError):
+        m.forward_recurrent(toks[:, :2], states)
+    tiny = build(OM.small_config(max_seq_len=4), sd)
+    st = None
+    with pytest.raises(RuntimeError):
+        for t in range(6):
+            _, st = tiny.forward_recurrent(toks[:, t:t + 1], st)
+
+
 def test_generate_api_sampling_and_eos():
     cfg = OM.small_config()
     sd = OM.init_state_dict(cfg, seed=4)

@@ -266,6 +266,35 @@ class VerseNexLM:
 
     __call__ = forward
 
+    def forward_recurrent(self, input_ids, states=None):
+        """One decoding step, CometSparkNexLM.forward_recurrent (cometspark.py:737-767): input_ids (B, 1) ->
+        (logits (B, 1, V), new_states) with one state entry per layer.
+
+        The reference threads per-layer dicts of grown K/V arrays through the call; here every entry of the
+        returned list is the same device-resident `KVCache`, extended in place by the step (a list taken from an
+        earlier step therefore sees the later tokens too).  `states=None` starts a fresh cache of `max_seq_len`
+        positions; more than one token per call raises AssertionError as the reference's attention does
+        (tri_sparse_attn.py:635), a full cache raises RuntimeError."""
+        from .speculative import Tensor, _unwrap
+        ids = _unwrap(input_ids)
+        ids = ids if isinstance(ids, DeviceArray) else np.asarray(ids, dtype=np.int64)
+        if ids.ndim == 1:
+            ids = ids.reshape(-1, 1)
+        B, T = ids.shape
+        assert T == 1, f"forward_recurrent takes one token per sequence, got T={T}"
+        if states is None:
+            cache = self.new_cache(B, self.max_seq_len)
+        else:
+            cache = states[0]
+            if not isinstance(cache, KVCache) or cache.max_batch < B:
+                raise ValueError("states must be the list returned by an earlier forward_recurrent call of this batch")
+        if int(cache.per_seq_lens[:B].max()) + 1 > cache.max_seq:
+            raise RuntimeError(f"KV cache overflow: {cache.max_seq} positions are in use")
+        logits = self.forward_cached(ids, cache)
+        cache.commit(1, np.ones(B, np.int32))
+        self.check()
+        return Tensor(logits), [cache] * self.n_layer
+
     # -- generate (cometspark.py:773-830) -------------------------------------------
     def generate(self, idx, max_new_tokens: Optional[int] = None, temperature: float = 1.0,
                  top_k: Optional[int] = None, eos_id: Optional[int] = None, max_safe_limit: int = 100_000,
