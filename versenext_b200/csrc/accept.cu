@@ -482,6 +482,16 @@ __device__ __forceinline__ float key_value(uint32_t k) {
   return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
+// neighbours of a float in the ordering of the reals (NaN and the infinity in the direction of travel stay put)
+__device__ __forceinline__ float next_up(float x) {
+  if (x != x || x == CUDART_INF_F) return x;
+  if (x == 0.f) return __int_as_float(1);
+  int b = __float_as_int(x);
+  b += b >= 0 ? 1 : -1;
+  return __int_as_float(b);
+}
+__device__ __forceinline__ float next_down(float x) { return -next_up(-x); }
+
 struct TopkRow {
   int n;                 // kept entries
   int overflow;          // 1 when ties at the threshold did not fit
@@ -551,6 +561,8 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, T
   // buffer and take the radix select below.
   __shared__ uint32_t s_bmax[256];
   __shared__ uint32_t s_lo;
+  __shared__ float s_xlo;
+  __shared__ int s_fast;
   const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
   const int V4 = vec ? (V >> 2) : 0;
   const float4* row4 = reinterpret_cast<const float4*>(row);
@@ -581,10 +593,47 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, T
       if (greater < want && geq >= want) s_lo = mine;   // every writer holds the same key
     }
     __syncthreads();
+    // The gather pass compares raw logits: x / temp is monotone in x, so "scaled key >= lo" is "x >= x_lo" for the
+    // smallest float x_lo whose quotient reaches lo's value; one thread finds it by stepping single floats around
+    // lo * temp (a handful of steps).  The division then runs for the few candidates only, not for every logit.
+    if (tid == 0) {
+      int fast = 0;
+      float xlo = -CUDART_INF_F;
+      const uint32_t lo_key = s_lo;
+      if (lo_key != 0u) {
+        const float lo_val = key_value(lo_key);
+        if (!scale) { xlo = lo_val; fast = lo_val == lo_val; }
+        else if (lo_val == lo_val && fabsf(lo_val) != CUDART_INF_F) {
+          float c = lo_val * temp;
+          int it = 0;
+          while (it < 64 && !(__fdiv_rn(c, temp) >= lo_val)) { c = next_up(c); ++it; }
+          while (it < 64 && __fdiv_rn(next_down(c), temp) >= lo_val && next_down(c) != c) { c = next_down(c); ++it; }
+          fast = it < 64 && c == c && __fdiv_rn(c, temp) >= lo_val && !(__fdiv_rn(next_down(c), temp) >= lo_val);
+          xlo = c;
+        }
+      }
+      s_xlo = xlo; s_fast = fast;
+    }
+    __syncthreads();
   }
   // candidates: every entry with key >= lo (slot order is arbitrary, the select below ranks them)
-  auto gather = [&](uint32_t lo) {
+  auto gather = [&](uint32_t lo, bool fast, float xlo) {
     int i = tid;
+    if (fast) {
+      for (; i < V4; i += nt) {
+        const float4 a = __ldg(row4 + i);
+        if (fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)) >= xlo) {
+          const float xs[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (xs[e] >= xlo) {
+              const uint32_t key = order_key(scale ? __fdiv_rn(xs[e], temp) : xs[e]);
+              const int slot = atomicAdd(&s_ncand, 1);
+              if (slot < CAND_MAX) { c_key[slot] = key; c_tok[slot] = base0 + 4 * i + e; }
+            }
+        }
+      }
+    }
     for (; i < V4; i += nt) {
       const float4 a = __ldg(row4 + i);
       const float xs[4] = {a.x, a.y, a.z, a.w};
@@ -608,7 +657,7 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, T
   };
   bool have = false;
   if (want > 0) {
-    gather(s_lo);
+    gather(s_lo, s_fast != 0, s_xlo);
     __syncthreads();
     have = s_ncand <= CAND_MAX;
     __syncthreads();
@@ -669,7 +718,7 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, T
       __syncthreads();
       if (tid == 0) s_ncand = 0;
       __syncthreads();
-      gather(lo);
+      gather(lo, false, 0.f);
       __syncthreads();
       have = true;
     }
