@@ -841,7 +841,7 @@ inline bool gemm_tc_cluster_supported(const GemmArgs& g, int mode, const tc_deta
 }
 
 // read on every launch so that a test can switch it
-inline int persist_level_env() { const char* e = getenv("VN_TC_PERSIST"); return e ? atoi(e) : 0; }
+inline int persist_level_env() { const char* e = getenv("VN_TC_PERSIST"); return e ? atoi(e) : -1; }
 
 // Supported: bf16 operands, K-major, 16-byte aligned rows, tokens <= 256, A rows contiguous (no gather).
 inline bool gemm_tc_supported(const GemmArgs& g) {
@@ -933,13 +933,18 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   }
   dim3 grid(ceil_div(g.N, BF), gy, g.nseg);
   const char* name = g.tag ? g.tag : "gemm_tc_kernel";
-  // Persistent variant (one CTA per SM walks the tiles, accumulator double buffered), opt-in: VN_TC_PERSIST=1 for
-  // GEMMs with more tiles than two per SM, =2 for every GEMM it supports.  Measured on B200 it matches the
-  // one-tile-per-CTA kernel within 3 % on the LM head and the expert GEMMs (their limit is the rate at which TMA
-  // delivers weight plus re-fetched token tiles, about 7.3 TB/s over all SMs), so it is not the default.
+  // Persistent variant (one CTA per SM walks the tiles, accumulator double buffered).  VN_TC_PERSIST=0 never,
+  // =1 for GEMMs with more tiles than two per SM, =2 for every GEMM it supports.  Measured on B200 it matches the
+  // one-tile-per-CTA kernel within 3 % on the target's LM head and expert GEMMs (their limit is the rate at which
+  // TMA delivers weight plus re-fetched token tiles, about 7.3 TB/s over all SMs), so by default it is used only
+  // for short K ranges (below).
   const int persist_level = persist_level_env();
   const long long tiles_total = (long long)grid.x * grid.y * grid.z;
-  if (persist_level > 0 && (mode == TC_STORE || mode == TC_SWIGLU || mode == TC_PARTIAL) &&
+  // Unset (-1): only where a tile's K range is at most four blocks and there are more than two tiles per SM (the
+  // draft model's LM head: 1,940 tiles of four k blocks), where the per-tile set-up is what the tile loop saves;
+  // measured -15 us per round there, +24 us on the target's GEMMs when forced everywhere.
+  const bool persist_auto = persist_level < 0 && a.kb_per_split <= 4 && tiles_total > 2ll * ctx->sm_count;
+  if ((persist_level > 0 || persist_auto) && (mode == TC_STORE || mode == TC_SWIGLU || mode == TC_PARTIAL) &&
       (persist_level >= 2 || tiles_total > 2ll * ctx->sm_count) && tiles_total < (1ll << 30)) {
     const size_t stages_max = (216 * 1024 - PERSIST_STAGING) / stage_bytes;
     if (stages_max >= 2) {
