@@ -1096,11 +1096,13 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
 
   if (!greedy && top_k > 0 && top_k < V) {
     VN_REQUIRE(ctx, top_k <= KEEP_MAX, "top_k %d above the supported maximum %d", top_k, KEEP_MAX);
-    // slices per row: about one CTA per SM (measured best on B200: fewer, longer slices and a smaller merge beat
-    // two or four CTAs per SM), at least 8192 logits each
+    // slices per row: a little under one CTA per SM (measured on B200 for the draft's 32 rows: 4 slices per row
+    // 2.325 ms per round, 3 slices 2.326, 5 slices 2.335, 2 slices 2.335, 10 slices 2.42: fewer, longer slices and
+    // a smaller merge win), at least 8192 logits each
     const int n_rows = B * rows_per_seq;
-    static const int topk_ctas_per_sm = [] { const char* e = getenv("VN_TOPK_CTAS_PER_SM"); return e ? std::max(1, atoi(e)) : 1; }();
-    int chunks = std::min(std::min(16, std::max(1, V / 8192)), std::max(1, ceil_div(topk_ctas_per_sm * ctx->sm_count, n_rows)));
+    static const double topk_ctas_per_sm = [] { const char* e = getenv("VN_TOPK_CTAS_PER_SM"); return e ? std::max(0.05, atof(e)) : 0.75; }();
+    const int cta_target = std::max(1, (int)(topk_ctas_per_sm * ctx->sm_count + 0.5));
+    int chunks = std::min(std::min(16, std::max(1, V / 8192)), std::max(1, ceil_div(cta_target, n_rows)));
     chunks = std::max(1, std::min(chunks, 2048 / std::max(top_k, 1)));
     void* ws;
     int32_t st = vn_workspace(ctx, sizeof(TopkRow) * (size_t)n_rows * (chunks + 1), &ws);
