@@ -16,10 +16,10 @@ GPU, calling it does.
 from . import _lib
 from .device import Context, DeviceArray, as_device
 from .backend import DeviceBackend, B200Backend, get_backend, clear_backend_cache
-from .speculative import SpeculativeDecoder, Tensor
+from .speculative import SpeculativeDecoder, Tensor, no_grad
 from .model import VerseNexLM, CometSparkNexLM, KVCache
 from .engine import SpecEngine
 from . import sampling
 
 __all__ = ["Context", "DeviceArray", "as_device", "DeviceBackend", "B200Backend", "get_backend",
-           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "sampling", "VerseNexLM", "CometSparkNexLM", "KVCache", "SpecEngine"]
+           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "no_grad", "sampling", "VerseNexLM", "CometSparkNexLM", "KVCache", "SpecEngine"]

@@ -148,13 +148,21 @@ class B200Backend(DeviceBackend):
         # full-D tables carry the half table twice; both forms reduce to (T, half)
         cos = cos[..., :half] if cos.shape[-1] >= D else cos
         sin = sin[..., :half] if sin.shape[-1] >= D else sin
-        T = x.shape[-2]
-        cos = np.broadcast_to(cos, (T, half)) if cos.ndim <= 2 else cos.reshape(-1, half)[-T:]
-        sin = np.broadcast_to(sin, (T, half)) if sin.ndim <= 2 else sin.reshape(-1, half)[-T:]
-        c, s = self._f32(np.ascontiguousarray(cos)), self._f32(np.ascontiguousarray(sin))
+        T = x.shape[-2] if x.ndim >= 2 else 1
+        if cos.ndim <= 2 and sin.ndim <= 2:
+            # one (T, half) table shared by every leading index of x
+            cos, sin = np.broadcast_to(cos, (T, half)), np.broadcast_to(sin, (T, half))
+            outer = x.size // (T * D)
+        else:
+            # tables with leading axes of their own (e.g. one per batch row) broadcast against x[..., :half]
+            # exactly as the NumPy expression of the reference does: one table row per row of x
+            lead = tuple(x.shape[:-1])
+            cos = np.broadcast_to(cos, lead + (half,)).reshape(-1, half)
+            sin = np.broadcast_to(sin, lead + (half,)).reshape(-1, half)
+            outer, T = 1, x.size // D
+        c, s_ = self._f32(np.ascontiguousarray(cos)), self._f32(np.ascontiguousarray(sin))
         out = self.ctx.empty(x.shape, np.float32)
-        self.ctx._check(self.ctx.lib.vn_rope(self.ctx.handle, _p(x), _p(c), _p(s), _p(out),
-                                             x.size // (T * D), T, D))
+        self.ctx._check(self.ctx.lib.vn_rope(self.ctx.handle, _p(x), _p(c), _p(s_), _p(out), outer, T, D))
         return out
 
     def attention(self, q, k, v, mask=None):

@@ -202,6 +202,12 @@ class DeviceArray:
         return len(self.shape)
 
     @property
+    def data(self):
+        """The array itself: callers written against verse_torch.Tensor read `.data` (tensor.py:394), and a
+        device buffer is its own backend-native payload."""
+        return self
+
+    @property
     def size(self):
         return int(np.prod(self.shape, dtype=np.int64))
 

@@ -33,6 +33,7 @@ class Tensor:
     """Minimal stand-in for verse_torch.Tensor at this boundary: `.data`, `.shape`, `.ndim`."""
 
     requires_grad = False
+    grad = None
 
     def __init__(self, data, requires_grad: bool = False):
         self.data = data
@@ -61,8 +62,25 @@ class _Tracked(np.ndarray):
         self._dirty[0] = True
         super().__setitem__(key, value)
 
+    def __array_ufunc__(self, ufunc, method, *inputs, out=None, **kwargs):
+        # in-place arithmetic (`w *= 2`, `np.add(w, 1, out=w)`) reaches the array here, not through __setitem__
+        plain = tuple(x.view(np.ndarray) if isinstance(x, _Tracked) else x for x in inputs)
+        if method == "at" and isinstance(inputs[0], _Tracked):
+            inputs[0]._dirty[0] = True
+        if out is not None:
+            for o in out:
+                if isinstance(o, _Tracked):
+                    o._dirty[0] = True
+            kwargs["out"] = tuple(o.view(np.ndarray) if isinstance(o, _Tracked) else o for o in out)
+        res = getattr(ufunc, method)(*plain, **kwargs)
+        if out is not None and method != "at":
+            return out[0] if len(out) == 1 else out
+        return res
+
 
 class _Param:
+    grad = None
+
     def __init__(self, arr):
         self._data = _Tracked(np.ascontiguousarray(arr, dtype=np.float32))
 
@@ -107,6 +125,7 @@ class SpeculativeDecoder:
         self._device = device
         self._ctx: Optional[Context] = None
         self._w_dev: Optional[DeviceArray] = None
+        self._w_ids = [None] * self.num_draft_heads
 
     # -- device state --------------------------------------------------------
     @property
@@ -117,12 +136,32 @@ class SpeculativeDecoder:
         return self._ctx
 
     def _weights(self) -> DeviceArray:
-        dirty = self._w_dev is None or any(h.weight.data._dirty[0] for h in self.draft_heads)
+        """Stacked (k*V, D) device copy of the head weights, refreshed when a head changed.
+
+        `head.weight` may be this module's parameter object or anything a caller assigned in its place that
+        carries a `.data` array (the reference's tests assign `head.weight = Tensor(ndarray)`,
+        tests/test_speculative_decode.py:159-167).  Writes through the tracked array type are seen; a plain
+        ndarray cannot report in-place writes, so a head holding one is uploaded again on every call."""
+        arrays, dirty = [], self._w_dev is None
+        for i, h in enumerate(self.draft_heads):
+            w = h.weight
+            a = w.data if hasattr(w, "data") and not isinstance(w, np.ndarray) else w
+            flag = getattr(a, "_dirty", None)
+            if flag is None or flag[0] or self._w_ids[i] != id(a):
+                dirty = True
+            arrays.append(a)
         if dirty:
-            stacked = np.concatenate([h.weight.data for h in self.draft_heads], axis=0)  # (k*V, D)
-            self._w_dev = self.ctx.from_numpy(np.asarray(stacked, dtype=np.float32))
-            for h in self.draft_heads:
-                h.weight.data._dirty[0] = False
+            for a in arrays:
+                if tuple(np.shape(a)) != (self.vocab_size, self.dim):
+                    raise ValueError(f"draft head weight has shape {tuple(np.shape(a))}, "
+                                     f"expected {(self.vocab_size, self.dim)}")
+            stacked = np.concatenate([np.asarray(a, dtype=np.float32) for a in arrays], axis=0)  # (k*V, D)
+            self._w_dev = self.ctx.from_numpy(stacked)
+            for i, a in enumerate(arrays):
+                self._w_ids[i] = id(a)
+                flag = getattr(a, "_dirty", None)
+                if flag is not None:
+                    flag[0] = False
         return self._w_dev
 
     # -- draft ---------------------------------------------------------------
@@ -147,6 +186,7 @@ class SpeculativeDecoder:
         k, V, D = self.num_draft_heads, self.vocab_size, self.dim
         if h.shape[1] != D:
             raise ValueError(f"hidden feature size {h.shape[1]} != dim {D}")
+        self._last_hidden = h          # (B, D) device rows: what draft_loss(...).backward() differentiates against
         ctx = self.ctx
         logits = ctx.empty((B, k * V), np.float32)   # row b = [head0 | head1 | ...]
         import ctypes as C
@@ -238,18 +278,65 @@ class SpeculativeDecoder:
 
     # -- training helper (out of the decode path; kept callable) --------------
     def draft_loss(self, draft_logits, target_tokens):
-        """Mean cross-entropy over heads (speculative.py:316-348).  Host arithmetic: training-side
-        helper, not part of the accelerated path."""
-        target_tokens = np.asarray(target_tokens)
-        if target_tokens.shape[1] != len(draft_logits):
-            raise ValueError("target_tokens second dim must equal the number of draft heads")
-        total = 0.0
+        """Mean cross-entropy over heads (speculative.py:316-348).  Host arithmetic: a training-side helper that
+        is not part of the accelerated path.  Returns a scalar with `.data` and `.backward()`; `backward` fills
+        `head.weight.grad` from the hidden rows of the last `draft` call."""
+        target_tokens = np.asarray(_unwrap(target_tokens))
+        if target_tokens.ndim != 2 or target_tokens.shape[1] != len(draft_logits):
+            raise ValueError("target_tokens must be (B, k) with k equal to the number of draft heads")
+        k = len(draft_logits)
+        total, grads = 0.0, []
         for i, lg in enumerate(draft_logits):
             x = np.asarray(_unwrap(lg), dtype=np.float64)
             x = x - x.max(axis=-1, keepdims=True)
-            lse = np.log(np.exp(x).sum(axis=-1))
-            total += float(np.mean(lse - x[np.arange(x.shape[0]), target_tokens[:, i]]))
-        return total / len(draft_logits)
+            e = np.exp(x)
+            p = e / e.sum(axis=-1, keepdims=True)
+            rows = np.arange(x.shape[0])
+            total += float(np.mean(-np.log(p[rows, target_tokens[:, i]])))
+            g = p.copy()
+            g[rows, target_tokens[:, i]] -= 1.0
+            grads.append(g / (x.shape[0] * k))
+        return _Loss(total / k, self, grads)
+
+
+class _Loss(float):
+    """Scalar loss: a float with the `.data` / `.item()` / `.backward()` handles the reference's Tensor has."""
+
+    def __new__(cls, value, decoder=None, grads=None):
+        obj = super().__new__(cls, value)
+        obj._decoder, obj._grads = decoder, grads
+        return obj
+
+    @property
+    def data(self):
+        return np.asarray(float(self), dtype=np.float32)
+
+    def item(self):
+        return float(self)
+
+    def backward(self):
+        dec = self._decoder
+        h = getattr(dec, "_last_hidden", None)
+        if h is None:
+            raise RuntimeError("draft_loss.backward needs the hidden rows of a preceding draft() call")
+        for head, g in zip(dec.draft_heads, self._grads):
+            gw = (g.T @ np.asarray(h, dtype=np.float64)).astype(np.float32)     # (V, D)
+            w = head.weight
+            try:
+                w.grad = gw if getattr(w, "grad", None) is None else w.grad + gw
+            except AttributeError:
+                pass
+
+
+class no_grad:
+    """Context manager with the name callers of the reference use around inference (verse_torch/tensor.py:99-133).
+    This package records no autograd graph, so it changes nothing."""
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
 
 
 def _last_rows(ctx: Context, h: DeviceArray) -> DeviceArray:
