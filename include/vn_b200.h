@@ -194,6 +194,24 @@ int32_t vn_model_finalize(vn_model* m);
  * quantize.py:187-214), "int4" (per output channel, :231-258), "int4g128" */
 int32_t vn_model_quantize(vn_model* m, const char* scheme);
 int32_t vn_model_param_bytes(vn_model* m, uint64_t* out);
+/* The quantiser on its own: w_dev float32 [rows, K] (device) -> q_dev and scale_dev (device), byte for byte what
+ * quantize_int8 / quantize_int4 + _pack_int4 return (verse_torch/quantize.py:187-258, :36-66):
+ *   "int8"      q int8 [rows, K],                scale float32 [rows]
+ *   "int4"      packed uint8 [rows, ceil(K/2)],  scale float32 [rows]   (even index in the low nibble)
+ *   "int4g128"  packed uint8 [rows, K/2],        scale float32 [rows, ceil(K/128)] holding bf16-representable values */
+int32_t vn_quantize(vn_ctx* ctx, const float* w_dev, int64_t rows, int32_t K, const char* scheme, void* q_dev,
+                    float* scale_dev);
+/* One linear that is already quantised -- the `packed` and `scale` arrays of a reference QuantizedLinear
+ * (verse_torch/quantize.py:382-440; scale (rows, 1) float32) -- goes to the device as it is, no re-quantisation.
+ * name: the linear's state_dict name ("blocks.3.attn.wq.weight", "head.weight", ...); host pointers.  A model takes
+ * all its linears this way or none (the other tensors still arrive through vn_model_load_tensor); the head needs
+ * its own quantised copy, as the reference's compressed models have (compress.py:817-822).  bf16 models only. */
+int32_t vn_model_load_quant_tensor(vn_model* m, const char* name, const char* scheme, const void* packed,
+                                   const float* scale, int64_t rows, int64_t K);
+/* Read the quantised bytes and the scales of one linear back (host buffers of exactly the tensor's size):
+ * what vn_model_quantize produced on the device, or what vn_model_load_quant_tensor was given. */
+int32_t vn_model_read_quant(vn_model* m, const char* name, void* q_host, size_t q_bytes, float* scale_host,
+                            size_t n_scales);
 /* LM head restricted to vocabulary columns [v_lo, v_lo + n_cols): out[r, j] = hidden[r] . head.weight[v_lo + j]
  * for `rows` rows of final-norm hidden states (float32 [rows, dim], as vn_model_forward returns them in
  * out_hidden); out row pitch out_ld floats.  The building block of a head split by columns over several GPUs

@@ -20,6 +20,7 @@ from .speculative import SpeculativeDecoder, Tensor, no_grad
 from .model import VerseNexLM, CometSparkNexLM, KVCache
 from .engine import SpecEngine
 from . import sampling
+from . import quant
 
 __all__ = ["Context", "DeviceArray", "as_device", "DeviceBackend", "B200Backend", "get_backend",
-           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "no_grad", "sampling", "VerseNexLM", "CometSparkNexLM", "KVCache", "SpecEngine"]
+           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "no_grad", "sampling", "quant", "VerseNexLM", "CometSparkNexLM", "KVCache", "SpecEngine"]

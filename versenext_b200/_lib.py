@@ -90,6 +90,9 @@ PROTOTYPES = {
     "vn_model_load_tensor": [_p, C.c_char_p, _p, _i32, C.POINTER(_i64)],
     "vn_model_finalize": [_p],
     "vn_model_quantize": [_p, C.c_char_p],
+    "vn_quantize": [_p, _p, _i64, _i32, C.c_char_p, _p, _p],
+    "vn_model_load_quant_tensor": [_p, C.c_char_p, C.c_char_p, _p, _p, _i64, _i64],
+    "vn_model_read_quant": [_p, C.c_char_p, _p, _sz, _p, _sz],
     "vn_row_stats": [_p, _p, _i64, _i32, _i32, _f32, _p, _p, _p, _p],
     "vn_row_residual": [_p, _p, _i64, _p, _i64, _i32, _i32, _f32, _p, _p, _p, _p, _p, _p, _p],
     "vn_row_pick": [_p, _p, _i64, _p, _i64, _i32, _i32, _f32, _p, _p, _p, _p, _p, _p, _p, _p],

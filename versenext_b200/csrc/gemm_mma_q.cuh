@@ -192,14 +192,17 @@ __device__ __forceinline__ float block_max_256(float v, float* sm) {
 }
 
 // QMODE 1 / 2: scale = max|w| / qmax (1 / qmax for an all-zero row), q = rint(w / scale) clipped
-template <int QMODE>
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16* __restrict__ w, int K,
+__device__ __forceinline__ float q_in(const __nv_bfloat16& v) { return __bfloat162float(v); }
+__device__ __forceinline__ float q_in(const float& v) { return v; }
+
+template <int QMODE, typename TW = __nv_bfloat16>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const TW* __restrict__ w, int K,
                                                             unsigned char* __restrict__ q, float* __restrict__ scale) {
   __shared__ float sm[8];
   const long long row = blockIdx.x;
-  const __nv_bfloat16* wr = w + row * K;
+  const TW* wr = w + row * K;
   float mx = 0.f;
-  for (int k = threadIdx.x; k < K; k += 256) mx = fmaxf(mx, fabsf(__bfloat162float(wr[k])));
+  for (int k = threadIdx.x; k < K; k += 256) mx = fmaxf(mx, fabsf(q_in(wr[k])));
   mx = block_max_256(mx, sm);
   const float qmax = QMODE == 1 ? 127.f : 7.f;
   const float sc = __fdiv_rn(mx > 0.f ? mx : 1.0f, qmax);
@@ -207,26 +210,27 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
   if (QMODE == 1) {
     signed char* qr = reinterpret_cast<signed char*>(q) + row * K;
     for (int k = threadIdx.x; k < K; k += 256) {
-      float v = rintf(__fdiv_rn(__bfloat162float(wr[k]), sc));
+      float v = rintf(__fdiv_rn(q_in(wr[k]), sc));
       qr[k] = (signed char)fminf(fmaxf(v, -127.f), 127.f);
     }
   } else {
-    unsigned char* qr = q + row * (K / 2);
-    for (int k2 = threadIdx.x; k2 < K / 2; k2 += 256) {
-      const float a = fminf(fmaxf(rintf(__fdiv_rn(__bfloat162float(wr[2 * k2]), sc)), -8.f), 7.f);
-      const float b = fminf(fmaxf(rintf(__fdiv_rn(__bfloat162float(wr[2 * k2 + 1]), sc)), -8.f), 7.f);
+    unsigned char* qr = q + row * ((K + 1) / 2);      // an odd K pads the last high nibble with zero (quantize.py:36-66)
+    for (int k2 = threadIdx.x; k2 < (K + 1) / 2; k2 += 256) {
+      const float a = fminf(fmaxf(rintf(__fdiv_rn(q_in(wr[2 * k2]), sc)), -8.f), 7.f);
+      const float b = (2 * k2 + 1 < K) ? fminf(fmaxf(rintf(__fdiv_rn(q_in(wr[2 * k2 + 1]), sc)), -8.f), 7.f) : 0.f;
       qr[k2] = (unsigned char)(((int)a & 0xf) | (((int)b & 0xf) << 4));
     }
   }
 }
 
 // QMODE 3: one scale per 128 input features, rounded to bfloat16 before the division
-__global__ void __launch_bounds__(128) quantize_g128_kernel(const __nv_bfloat16* __restrict__ w, int K,
+template <typename TW = __nv_bfloat16>
+__global__ void __launch_bounds__(128) quantize_g128_kernel(const TW* __restrict__ w, int K,
                                                             unsigned char* __restrict__ q, float* __restrict__ scale) {
   const long long row = blockIdx.x;
   const int grp = blockIdx.y, groups = (K + 127) / 128;
   const int col = grp * 128 + (int)threadIdx.x;            // a last group shorter than 128 is padded with zeros
-  const float v = col < K ? __bfloat162float(w[row * K + col]) : 0.f;
+  const float v = col < K ? q_in(w[row * K + col]) : 0.f;
   float mx = fabsf(v);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));

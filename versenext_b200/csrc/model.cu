@@ -129,6 +129,7 @@ struct vn_model {
   int* depth_dev = nullptr; unsigned long long* anc_dev = nullptr; int* rows_dev = nullptr;
   float* stage = nullptr; size_t stage_elems = 0;
   int qmode = 0;                 // 0 dense, 1 int8, 2 int4 per channel, 3 int4 group-128 (vn_model_quantize)
+  int preq_mode = 0;             // scheme of linears that arrive already quantised (vn_model_load_quant_tensor)
   void* head_q = nullptr;        // quantised LM head (its own copy: the embedding table stays dense)
   float* head_qs = nullptr;
   void* hs = nullptr;            // [M * slots, D] routed activations in expert order (tcgen05 path)
@@ -601,6 +602,97 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
   return VN_OK;
 }
 
+
+// ---- linears addressed by their state_dict name: where their rows live in the stacked / interleaved matrices ----
+struct LinearSlot {
+  int layer = -1;        // -1: the LM head
+  int slot = 0;          // index into Layer::q / qs (0 qkv, 1 proj, 2 gate|up, 3 down, 4 expert gate|up, 5 expert down)
+  long long base = 0, row_mul = 1, row_off = 0;   // destination row of source row r: base + r * row_mul + row_off
+  long long rows = 0, K = 0;                      // shape of the named tensor
+};
+
+bool locate_linear(const vn_model* m, const std::string& n, LinearSlot* o) {
+  const Config& c = m->cfg;
+  const long long D = c.dim, qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
+  if (n == "head.weight") { o->layer = -1; o->rows = c.vocab; o->K = D; return true; }
+  if (n.rfind("blocks.", 0) != 0) return false;
+  const size_t dot = n.find('.', 7);
+  if (dot == std::string::npos) return false;
+  const int li = atoi(n.substr(7, dot - 7).c_str());
+  if (li < 0 || li >= c.n_layer) return false;
+  o->layer = li;
+  const int kind = c.kind[li];
+  const std::string rest = n.substr(dot + 1);
+  if (rest == "attn.wq.weight") { o->slot = 0; o->rows = qd; o->K = D; return true; }
+  if (rest == "attn.wk.weight") { o->slot = 0; o->base = qd; o->rows = kvd; o->K = D; return true; }
+  if (rest == "attn.wv.weight") { o->slot = 0; o->base = qd + kvd; o->rows = kvd; o->K = D; return true; }
+  if (rest == "attn.proj.weight") { o->slot = 1; o->rows = D; o->K = qd; return true; }
+  if (kind == 0) {
+    if (rest == "ffn.w_gate.weight") { o->slot = 2; o->row_mul = 2; o->rows = c.mlp_hidden; o->K = D; return true; }
+    if (rest == "ffn.w_up.weight") { o->slot = 2; o->row_mul = 2; o->row_off = 1; o->rows = c.mlp_hidden; o->K = D; return true; }
+    if (rest == "ffn.w_down.weight") { o->slot = 3; o->rows = D; o->K = c.mlp_hidden; return true; }
+    return false;
+  }
+  if (rest.rfind("ffn.parts.", 0) != 0) return false;
+  const size_t d2 = rest.find('.', 10);
+  if (d2 == std::string::npos) return false;
+  const int p = atoi(rest.substr(10, d2 - 10).c_str());
+  const std::string r2 = rest.substr(d2 + 1);
+  if (p < 0 || p >= c.P || r2.rfind("experts.", 0) != 0) return false;
+  const size_t d3 = r2.find('.', 8);
+  if (d3 == std::string::npos) return false;
+  const int ex = atoi(r2.substr(8, d3 - 8).c_str());
+  if (ex < 0 || ex >= c.E) return false;
+  const std::string r3 = r2.substr(d3 + 1);
+  const long long ge = (long long)p * c.E + ex, eh = c.expert_hidden;
+  if (r3 == "w_gate.weight") { o->slot = 4; o->base = ge * 2 * eh; o->row_mul = 2; o->rows = eh; o->K = D; return true; }
+  if (r3 == "w_up.weight") { o->slot = 4; o->base = ge * 2 * eh; o->row_mul = 2; o->row_off = 1; o->rows = eh; o->K = D; return true; }
+  if (r3 == "w_down.weight") { o->slot = 5; o->base = ge * D; o->rows = D; o->K = eh; return true; }
+  return false;
+}
+
+inline size_t q_row_bytes(int mode, long long K) { return (size_t)(mode == 1 ? K : K / 2); }
+inline size_t q_row_scales(int mode, long long K) { return (size_t)(mode == 3 ? (K + 127) / 128 : 1); }
+
+// buffers for linears that arrive quantised; the dense buffers of those linears are given back
+int32_t alloc_quant(vn_model* m, int mode) {
+  vn_ctx* ctx = m->ctx;
+  const Config& c = m->cfg;
+  const long long D = c.dim, qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
+  auto A = [&](void** q, float** qs, long long rows, long long K) -> int32_t {
+    TRY(dev_alloc(ctx, q, (size_t)rows * q_row_bytes(mode, K)));
+    TRY(dev_alloc(ctx, (void**)qs, (size_t)rows * q_row_scales(mode, K) * 4));
+    return VN_OK;
+  };
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  auto F = [](void** p) { if (*p) cudaFree(*p); *p = nullptr; };
+  for (auto& L : m->layers) {
+    TRY(A(&L.q[0], &L.qs[0], qd + 2 * kvd, D));
+    TRY(A(&L.q[1], &L.qs[1], D, qd));
+    F(&L.wqkv); F(&L.wproj);
+    if (L.kind == 0) {
+      TRY(A(&L.q[2], &L.qs[2], 2ll * c.mlp_hidden, D));
+      TRY(A(&L.q[3], &L.qs[3], D, c.mlp_hidden));
+      F(&L.w_gateup); F(&L.w_down);
+    } else {
+      const long long ne = (long long)c.P * c.E;
+      TRY(A(&L.q[4], &L.qs[4], ne * 2 * c.expert_hidden, D));
+      TRY(A(&L.q[5], &L.qs[5], ne * D, c.expert_hidden));
+      F(&L.e_gateup); F(&L.e_down);
+    }
+  }
+  TRY(A(&m->head_q, &m->head_qs, c.vocab, D));
+  if (m->head != m->emb) F(&m->head);
+  m->preq_mode = mode;
+  return VN_OK;
+}
+
+int scheme_mode(const char* scheme) {
+  if (!scheme) return 0;
+  const std::string s(scheme);
+  return s == "int8" ? 1 : (s == "int4" ? 2 : (s == "int4g128" ? 3 : 0));
+}
+
 struct NameRoute { int layer; std::string rest; };
 
 }  // namespace
@@ -687,6 +779,10 @@ int32_t vn_model_load_tensor(vn_model* m, const char* name, const float* data, i
   VN_REQUIRE(ctx, m->qmode == 0, "the model is quantised: its dense weights are gone, create a new model to reload");
   const Config& c = m->cfg;
   const std::string n(name);
+  if (m->preq_mode) {
+    LinearSlot ls;
+    VN_REQUIRE(ctx, !locate_linear(m, n, &ls), "%s: this model takes its linears quantised (vn_model_load_quant_tensor)", name);
+  }
   const long long r = shape[0], cl = ndim == 2 ? shape[1] : 1;
   const long long D = c.dim;
   auto expect = [&](long long er, long long ec) -> bool { return r == er && cl == ec; };
@@ -764,7 +860,7 @@ int32_t vn_model_finalize(vn_model* m) {
   const Config& c = m->cfg;
   // every tensor of the reference's state_dict must have arrived (head.weight may be omitted when tied)
   std::vector<std::string> want = {"tok_emb.weight", "norm.weight"};
-  if (!c.tie) want.push_back("head.weight");
+  if (!c.tie || m->preq_mode) want.push_back("head.weight");   // a quantised head is its own copy (compress.py:817-822)
   for (int i = 0; i < c.n_layer; ++i) {
     const std::string p = "blocks." + std::to_string(i) + ".";
     for (const char* s : {"norm1.weight", "norm2.weight", "attn.gate_logits", "attn.wq.weight", "attn.wk.weight",
@@ -810,17 +906,46 @@ int32_t vn_model_finalize(vn_model* m) {
   }
   // sink K / V = wk(global_tokens), wv(global_tokens): fixed per layer (tri_sparse_attn.py:223-242)
   const long long D = c.dim, qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
+  const int pm = m->preq_mode;
   for (auto& L : m->layers) {
     for (int which = 0; which < 2; ++which) {
       GemmArgs g;
-      g.A = L.sink; g.lda = D;
-      g.W = (char*)L.wqkv + (size_t)(qd + which * kvd) * D * m->esz; g.ldw = D;
+      g.A = L.sink; g.lda = D; g.ldw = D;
       g.C = which ? L.sink_v : L.sink_k; g.ldc = kvd; g.M = c.n_sink; g.N = (int)kvd; g.K = (int)D; g.c_bf16 = c.bf16;
-      if (c.bf16) TRY((launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g)));
-      else TRY((launch_gemm_simt<float, float>(ctx, g)));
+      if (pm) {           // the k / v rows of the quantised q|k|v matrix, dequantised inside the GEMM
+        const long long r0 = qd + which * kvd;
+        g.W = (const unsigned char*)L.q[0] + (size_t)r0 * q_row_bytes(pm, D);
+        g.w_scale = L.qs[0] + (size_t)r0 * q_row_scales(pm, D);
+        g.wq = pm;
+        if (!gemm_mma_q_supported(g)) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised GEMM shape K=%d unsupported", g.K);
+        TRY(launch_gemm_mma_q(ctx, g));
+      } else {
+        g.W = (char*)L.wqkv + (size_t)(qd + which * kvd) * D * m->esz;
+        if (c.bf16) TRY((launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g)));
+        else TRY((launch_gemm_simt<float, float>(ctx, g)));
+      }
     }
   }
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (pm) {
+    // linears arrived quantised: the model is now what vn_model_quantize would have left behind
+    uint64_t bytes = 0;
+    auto add = [&](long long rows, long long K) { bytes += (uint64_t)rows * (q_row_bytes(pm, K) + q_row_scales(pm, K) * 4); };
+    for (auto& L : m->layers) {
+      add(qd + 2 * kvd, D); add(D, qd);
+      if (L.kind == 0) { add(2ll * c.mlp_hidden, D); add(D, c.mlp_hidden); }
+      else { const long long ne = (long long)c.P * c.E; add(ne * 2 * c.expert_hidden, D); add(ne * D, c.expert_hidden); }
+    }
+    add(c.vocab, D);
+    uint64_t keep = (uint64_t)c.vocab * D * m->esz + (uint64_t)D * 4;
+    for (auto& L : m->layers) {
+      keep += 2ull * D * 4 + (uint64_t)c.n_sink * D * m->esz;
+      if (L.kind == 1) keep += (uint64_t)(c.P + c.P * c.E) * D * 4;
+    }
+    m->param_bytes = keep + bytes;
+    m->qmode = pm;
+    { const char* e = getenv("VN_GEMM_TCQ"); if (e && e[0] == '0') m->use_tc = false; }
+  }
   m->finalized = true;
   return VN_OK;
 }
@@ -840,7 +965,7 @@ static int32_t quantize_matrix(vn_model* m, void** dense, long long rows, int K,
   else {
     VN_REQUIRE(ctx, rows < (1ll << 31) && (K + 127) / 128 < 65536, "matrix too large");
     dim3 grid((unsigned)rows, (K + 127) / 128);
-    VN_LAUNCH(ctx, mmaq_detail::quantize_g128_kernel, grid, 128, 0, w, K, (unsigned char*)*q, *qs);
+    VN_LAUNCH(ctx, mmaq_detail::quantize_g128_kernel<__nv_bfloat16>, grid, 128, 0, w, K, (unsigned char*)*q, *qs);
   }
   *bytes += qbytes + nscale * 4;
   if (release) {
@@ -899,6 +1024,90 @@ int32_t vn_model_quantize(vn_model* m, const char* scheme) {
 int32_t vn_model_param_bytes(vn_model* m, uint64_t* out) {
   if (!m || !out) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
   *out = m->param_bytes;
+  return VN_OK;
+}
+
+int32_t vn_quantize(vn_ctx* ctx, const float* w_dev, int64_t rows, int32_t K, const char* scheme, void* q_dev,
+                    float* scale_dev) {
+  VN_CHECK_CTX(ctx);
+  const int mode = scheme_mode(scheme);
+  VN_REQUIRE(ctx, mode != 0, "unknown quantisation scheme %s (int8 | int4 | int4g128)", scheme ? scheme : "(null)");
+  VN_REQUIRE(ctx, w_dev && q_dev && scale_dev && rows >= 0 && K >= 1 && rows < (1ll << 31), "bad arguments");
+  if (rows == 0) return VN_OK;
+  if (mode == 1) {
+    auto kfn = mmaq_detail::quantize_rows_kernel<1, float>;
+    VN_LAUNCH_NAMED(ctx, "quantize_rows_kernel", kfn, (unsigned)rows, 256, 0, w_dev, K, (unsigned char*)q_dev, scale_dev);
+  } else if (mode == 2) {
+    auto kfn = mmaq_detail::quantize_rows_kernel<2, float>;
+    VN_LAUNCH_NAMED(ctx, "quantize_rows_kernel", kfn, (unsigned)rows, 256, 0, w_dev, K, (unsigned char*)q_dev, scale_dev);
+  } else {
+    VN_REQUIRE(ctx, K % 2 == 0 && (K + 127) / 128 < 65536, "int4g128 needs an even in_features below 2^23");
+    dim3 grid((unsigned)rows, (K + 127) / 128);
+    auto kfn = mmaq_detail::quantize_g128_kernel<float>;
+    VN_LAUNCH_NAMED(ctx, "quantize_g128_kernel", kfn, grid, 128, 0, w_dev, K, (unsigned char*)q_dev, scale_dev);
+  }
+  return VN_OK;
+}
+
+int32_t vn_model_load_quant_tensor(vn_model* m, const char* name, const char* scheme, const void* packed,
+                                   const float* scale, int64_t rows, int64_t K) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, name && packed && scale, "null argument");
+  const int mode = scheme_mode(scheme);
+  VN_REQUIRE(ctx, mode != 0, "unknown quantisation scheme %s (int8 | int4 | int4g128)", scheme ? scheme : "(null)");
+  if (!m->cfg.bf16) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised linears need a bf16 model");
+  VN_REQUIRE(ctx, m->qmode == 0, "the model is already quantised");
+  VN_REQUIRE(ctx, m->preq_mode == 0 || m->preq_mode == mode, "%s: one scheme per model (linears so far arrived as scheme %d)", name, m->preq_mode);
+  const std::string n(name);
+  LinearSlot ls;
+  VN_REQUIRE(ctx, locate_linear(m, n, &ls), "%s is not a linear of this model", name);
+  VN_REQUIRE(ctx, rows == ls.rows && K == ls.K, "%s: shape (%lld, %lld) expected (%lld, %lld)", name, (long long)rows,
+             (long long)K, ls.rows, ls.K);
+  VN_REQUIRE(ctx, K % 64 == 0, "in_features %lld not supported by the quantised kernels (multiple of 64 needed)", (long long)K);
+  if (!m->preq_mode) {
+    for (const auto& w : m->loaded) {
+      LinearSlot other;
+      VN_REQUIRE(ctx, !locate_linear(m, w, &other), "%s was loaded dense: a model takes all its linears dense or all quantised", w.c_str());
+    }
+    TRY(alloc_quant(m, mode));
+  }
+  unsigned char* q = (unsigned char*)(ls.layer < 0 ? m->head_q : m->layers[ls.layer].q[ls.slot]);
+  float* qs = ls.layer < 0 ? m->head_qs : m->layers[ls.layer].qs[ls.slot];
+  const size_t rb = q_row_bytes(mode, K), sb = q_row_scales(mode, K) * 4;
+  VN_CUDA(ctx, cudaMemcpy2DAsync(q + (size_t)(ls.base + ls.row_off) * rb, (size_t)ls.row_mul * rb, packed, rb, rb, (size_t)rows,
+                                 cudaMemcpyHostToDevice, ctx->stream));
+  VN_CUDA(ctx, cudaMemcpy2DAsync((char*)qs + (size_t)(ls.base + ls.row_off) * sb, (size_t)ls.row_mul * sb, scale, sb, sb,
+                                 (size_t)rows, cudaMemcpyHostToDevice, ctx->stream));
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));     // the host buffers may be reused by the caller
+  m->loaded.insert(n);
+  m->finalized = false;
+  return VN_OK;
+}
+
+int32_t vn_model_read_quant(vn_model* m, const char* name, void* q_host, size_t q_bytes, float* scale_host,
+                            size_t n_scales) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, name && q_host && scale_host, "null argument");
+  const int mode = m->qmode ? m->qmode : m->preq_mode;
+  VN_REQUIRE(ctx, mode != 0, "the model holds no quantised weights");
+  LinearSlot ls;
+  VN_REQUIRE(ctx, locate_linear(m, std::string(name), &ls), "%s is not a linear of this model", name);
+  const size_t rb = q_row_bytes(mode, ls.K), sb = q_row_scales(mode, ls.K) * 4;
+  VN_REQUIRE(ctx, q_bytes == (size_t)ls.rows * rb && n_scales * 4 == (size_t)ls.rows * sb,
+             "%s: buffers of %zu bytes / %zu scales, expected %zu / %zu", name, q_bytes, n_scales,
+             (size_t)ls.rows * rb, (size_t)ls.rows * sb / 4);
+  const unsigned char* q = (const unsigned char*)(ls.layer < 0 ? m->head_q : m->layers[ls.layer].q[ls.slot]);
+  const float* qs = ls.layer < 0 ? m->head_qs : m->layers[ls.layer].qs[ls.slot];
+  VN_REQUIRE(ctx, q && qs, "%s has no quantised copy", name);
+  VN_CUDA(ctx, cudaMemcpy2DAsync(q_host, rb, q + (size_t)(ls.base + ls.row_off) * rb, (size_t)ls.row_mul * rb, rb,
+                                 (size_t)ls.rows, cudaMemcpyDeviceToHost, ctx->stream));
+  VN_CUDA(ctx, cudaMemcpy2DAsync(scale_host, sb, (const char*)qs + (size_t)(ls.base + ls.row_off) * sb, (size_t)ls.row_mul * sb,
+                                 sb, (size_t)ls.rows, cudaMemcpyDeviceToHost, ctx->stream));
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return VN_OK;
 }
 

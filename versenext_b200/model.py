@@ -35,6 +35,37 @@ def _ptr(a):
     return C.c_void_p(a.ptr) if a is not None else C.c_void_p(None)
 
 
+def _as_quantised(v):
+    """(packed, scale, qtype) when `v` is a linear in quantised form, else None."""
+    if isinstance(v, tuple) and len(v) == 3 and isinstance(v[2], str):
+        return v
+    inner = getattr(v, "_qlin", v)          # QLinear module -> the QuantizedLinear it wraps
+    if hasattr(inner, "packed") and hasattr(inner, "scale") and hasattr(inner, "qtype"):
+        return inner.packed, inner.scale, inner.qtype
+    return None
+
+
+def _is_router_gate(name: str) -> bool:
+    return name.endswith("router.gate.weight") or name.endswith("part_router.gate.weight")
+
+
+def _dequantise_host(packed, scale, qtype):
+    """q * scale as float32 (verse_torch/quantize.py:216-229, :260-275); used for the few small gate matrices only."""
+    packed = np.asarray(packed)
+    if qtype == "int8":
+        q = packed.astype(np.float32)
+    else:
+        lo = (packed & 0x0F).astype(np.int16)
+        hi = ((packed >> 4) & 0x0F).astype(np.int16)
+        q = np.empty(packed.shape[:-1] + (packed.shape[-1] * 2,), np.float32)
+        q[..., 0::2] = np.where(lo >= 8, lo - 16, lo)
+        q[..., 1::2] = np.where(hi >= 8, hi - 16, hi)
+    sc = np.asarray(scale, dtype=np.float32).reshape(q.shape[0], -1)
+    if sc.shape[1] > 1:
+        return (q.reshape(q.shape[0], sc.shape[1], -1) * sc[..., None]).reshape(q.shape)
+    return q * sc
+
+
 class KVCache:
     """Per-layer K / V of shape (max_batch, max_seq, n_kv_head, head_dim) with per-sequence lengths.
 
@@ -181,11 +212,75 @@ class VerseNexLM:
         self._finalized = False
 
     def load_state_dict(self, sd: dict, strict: bool = True):
+        """name -> float32 array (vnnn.py:235-285).  A value may also be an already quantised linear: an object
+        with `packed`, `scale` and `qtype` (the reference's QuantizedLinear, quantize.py:382-440, or the QLinear
+        module that wraps one in `_qlin`, compress.py:739-756) or a `(packed, scale, qtype)` tuple; those go to
+        the device as they are (`load_quant_tensor`)."""
+        quantised = {n: v for n, v in sd.items() if _as_quantised(v) is not None}
         for name, value in sd.items():
-            if name == "head.weight" and self.tie_weights:
+            if name in quantised:
+                continue
+            if name == "head.weight" and self.tie_weights and not quantised:
                 continue
             self.load_tensor(name, getattr(value, "data", value))
+        for name, value in quantised.items():
+            packed, scale, qtype = _as_quantised(value)
+            if _is_router_gate(name):
+                # router gates stay float32 on the device: a quantised gate is expanded here (q * scale)
+                self.load_tensor(name, _dequantise_host(packed, scale, qtype))
+            else:
+                self.load_quant_tensor(name, packed, scale, qtype)
         self.finalize()
+
+    def load_quant_tensor(self, name: str, packed, scale, qtype: str = "int4"):
+        """One linear in its quantised form, exactly the bytes and scales given (no re-quantisation).
+        packed: int8 (out, in) for "int8", uint8 (out, in/2) for "int4" / "int4g128"; scale: (out, 1) or (out,)
+        float32, (out, in/128) for "int4g128"."""
+        packed = np.ascontiguousarray(packed)
+        rows = packed.shape[0]
+        K = packed.shape[1] if qtype == "int8" else packed.shape[1] * 2
+        if qtype == "int8" and packed.dtype != np.int8 or qtype != "int8" and packed.dtype != np.uint8:
+            raise ValueError(f"{name}: packed has dtype {packed.dtype}, expected int8 (int8) or uint8 (int4 schemes)")
+        sc = np.ascontiguousarray(np.asarray(scale, dtype=np.float32).reshape(rows, -1))
+        want = (K + 127) // 128 if qtype == "int4g128" else 1
+        if sc.shape[1] != want:
+            raise ValueError(f"{name}: scale has {sc.shape[1]} values per row, expected {want}")
+        self.ctx._check(self.ctx.lib.vn_model_load_quant_tensor(
+            self.handle, name.encode(), qtype.encode(), packed.ctypes.data_as(C.c_void_p),
+            sc.ctypes.data_as(C.c_void_p), rows, K))
+        self.quantized = qtype
+        self._finalized = False
+
+    def read_quant(self, name: str):
+        """(q, scale) of one linear of a quantised model as they sit on the device: int8 (out, in) or packed uint8
+        (out, in/2), scale float32 (out, 1) or (out, in/128)."""
+        qtype = getattr(self, "quantized", None)
+        if qtype is None:
+            raise ValueError("the model holds no quantised weights")
+        rows, K = self.linear_shape(name)
+        q = np.empty((rows, K) if qtype == "int8" else (rows, K // 2), np.int8 if qtype == "int8" else np.uint8)
+        sc = np.empty((rows, (K + 127) // 128 if qtype == "int4g128" else 1), np.float32)
+        self.ctx._check(self.ctx.lib.vn_model_read_quant(self.handle, name.encode(), q.ctypes.data_as(C.c_void_p),
+                                                         q.nbytes, sc.ctypes.data_as(C.c_void_p), sc.size))
+        return q, sc
+
+    def linear_shape(self, name: str):
+        """(out_features, in_features) of a linear given by its state_dict name."""
+        D, hd = self.dim, self.head_dim
+        qd, kvd = self.n_head * hd, self.n_kv_head * hd
+        c = self._config
+        hidden = ((c["mlp_hidden_multiple"] * D * 2.0 / 3.0 + 63) // 64) * 64
+        eh = c["expert_hidden"] or max(int(D * 8.0 / 3.0 / 64.0) * 64, 64)
+        leaf = name.split(".")[-2]
+        if name == "head.weight":
+            return self.vocab_size, D
+        if ".experts." in name:
+            return {"w_gate": (eh, D), "w_up": (eh, D), "w_down": (D, eh)}[leaf]
+        table = {"wq": (qd, D), "wk": (kvd, D), "wv": (kvd, D), "proj": (D, qd), "w_gate": (int(hidden), D),
+                 "w_up": (int(hidden), D), "w_down": (D, int(hidden))}
+        if leaf not in table:
+            raise ValueError(f"{name} is not a linear of this model")
+        return table[leaf]
 
     def finalize(self):
         if self.use_rope:
