@@ -237,3 +237,76 @@ def test_invalid_arguments_raise(ctx):
         sampling.accept(ctx, p, None, np.zeros((2, 40), np.int64), temperature=0.0, shape=(2, 40, 10))
     with pytest.raises(ValueError):
         sampling.accept(ctx, p, None, d, temperature=1.0, top_k=5000, shape=(2, 2, 100000))
+
+
+def _draft_from_topk(rng, q, temperature, top_k):
+    B, k, _ = q.shape
+    d = np.empty((B, k), np.int64)
+    for b in range(B):
+        for i in range(k):
+            d[b, i] = OA._inverse_cdf(OA.softmax64(q[b, i], temperature, top_k), float(rng.random()))
+    return d
+
+
+def test_topk_full_vocabulary_matches_oracle(ctx):
+    """The acceptance path a speculative round runs -- top-k 50 at temperature 0.8 over the whole vocabulary of
+    248,320 -- against the oracle, decisions and tokens bit-exact.  Rows are shaped to walk every branch of the
+    select: plain logits (bound pass suffices), an adversarial order plus heavy ties above the bound (the
+    candidate buffer overflows and the radix select takes over), ties exactly at the k-th value (all kept), a row
+    of few distinct values."""
+    rng = np.random.default_rng(50)
+    B, k, V, top_k, T = 5, 4, 248320, 50, 0.8
+    p, q, _ = make(rng, B, k, V)
+    # (1) sixty large distinct values packed into the first 60 positions (they fall to a handful of the bound
+    # pass's thread groups) and 1,100 entries tied at a value above the bound but below the k-th largest
+    p[1, 0, :60] = 20.0 + np.arange(60, dtype=np.float32) * 0.25
+    p[1, 0, rng.choice(np.arange(100, 12000), 1100, replace=False)] = 9.5
+    # (2) thirty distinct values on top, then forty entries tied at the value where the k-th falls
+    p[2, 1, rng.choice(V, 30, replace=False)] = 15.0 + np.arange(30, dtype=np.float32)
+    p[2, 1, rng.choice(np.arange(5000, 240000), 40, replace=False)] = 12.0
+    # (3) the same on a draft row: q's support is what decides q(x)
+    q[3, 2, rng.choice(V, 200, replace=False)] = 11.0
+    # (4) a row with three distinct values only
+    p[4, 3] = np.where(rng.random(V) < 0.001, 2.0, np.where(rng.random(V) < 0.5, -1.0, -3.0)).astype(np.float32)
+    draft = _draft_from_topk(rng, q, T, top_k)
+    ua = rng.random((B, k)).astype(np.float32)
+    us = rng.random((B, k + 1)).astype(np.float32)
+    # proposals equal to the target's arg-max with u = 0 are always accepted: sequence 0 runs through to the bonus
+    # token, the others reach the position of their shaped row
+    for b, upto in ((0, k), (2, 1), (3, 2), (4, 3)):
+        draft[b, :upto] = np.argmax(p[b, :upto], -1)
+        ua[b, :upto] = 0.0
+    n, t = run(ctx, p, q, draft, u_accept=ua, u_sample=us, temperature=T, top_k=top_k)
+    wn, wt = OA.accept(p, q, draft, ua, us, T, top_k)
+    np.testing.assert_array_equal(n, wn)
+    np.testing.assert_array_equal(t, wt)
+    # the shaped rows were really used by at least one decision each
+    kept1 = np.count_nonzero(p[1, 0] / np.float32(T) >= np.sort(p[1, 0] / np.float32(T))[-top_k])
+    kept2 = np.count_nonzero(p[2, 1] >= np.sort(p[2, 1])[-top_k])
+    assert kept1 == 50 and kept2 == 70
+    assert wn[0] == k and wn[2] >= 1 and wn[3] >= 2 and wn[4] >= 3
+    # Philox-driven call on the same rows
+    n, t = run(ctx, p, q, draft, seed=77, offset=3, temperature=T, top_k=top_k)
+    ua2, us2 = OP.uniforms_for_call(77, 3, B, k)
+    wn, wt = OA.accept(p, q, draft, ua2, us2, T, top_k)
+    np.testing.assert_array_equal(n, wn)
+    np.testing.assert_array_equal(t, wt)
+
+
+def test_cfg2_full_batch_row_subset_matches_oracle(ctx):
+    """B = 64, k = 4, V = 248,320 (the isolated acceptance workload at full size) with Philox uniforms: the
+    device call runs on all 64 sequences, the oracle re-computes a subset of them (a sequence's result depends
+    on its own rows and its own Philox row index only)."""
+    rng = np.random.default_rng(1234)
+    B, k, V = 64, 4, 248320
+    q = rng.standard_normal((B, k, V), dtype=np.float32) * 2.0
+    p = np.empty((B, k + 1, V), np.float32)
+    p[:, :k] = q + rng.standard_normal((B, k, V), dtype=np.float32) * 0.5
+    p[:, k] = rng.standard_normal((B, V), dtype=np.float32) * 2.0
+    draft = np.argmax(q + rng.gumbel(size=q.shape).astype(np.float32), -1).astype(np.int64)
+    n, t = run(ctx, p, q, draft, seed=1234, offset=0, temperature=1.0)
+    ua, us = OP.uniforms_for_call(1234, 0, B, k)
+    rows = [0, 1, 17, 31, 32, 50, 63]
+    wn, wt = OA.accept(p[rows], q[rows], draft[rows], ua[rows], us[rows], 1.0, 0)
+    np.testing.assert_array_equal(n[rows], wn)
+    np.testing.assert_array_equal(t[rows], wt)
