@@ -218,6 +218,11 @@ int32_t vn_model_read_quant(vn_model* m, const char* name, void* q_host, size_t 
  * (no counterpart in the reference, whose head is one Linear, cometspark.py:690-696). */
 int32_t vn_model_head(vn_model* m, const float* hidden_dev, int32_t rows, int32_t v_lo, int32_t n_cols,
                       float* out_logits_dev, int64_t out_ld);
+/* Which ALiBi rule the following forwards of this model use.  0 (default): the whole-sequence forward's -- every
+ * earlier key, path switched off once more than 1024 keys are visible (tri_sparse_attn.py:489-530, :600).
+ * Non-zero: the one-token recurrent step's -- its state keeps the last window_size keys only, so the path sees
+ * those and stays on while that count is at most 1024 (tri_sparse_attn.py:676-731).  No effect without ALiBi. */
+int32_t vn_model_set_recurrent(vn_model* m, int32_t on);
 /* Device-side conditions raised by forwards since the last call, read after a stream synchronisation and
  * cleared: *bad_token != 0 when a token id outside [0, vocab) was met (the kernels clamp it instead of reading
  * outside the embedding table; the reference raises IndexError from NumPy fancy indexing, vnnn.py:453-460);

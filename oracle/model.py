@@ -226,9 +226,14 @@ def tree_depths_and_ancestors(parents):
     return depth, anc
 
 
-def attention(sd, cfg: Config, prefix, x, cache, parents, rope):
+def attention(sd, cfg: Config, prefix, x, cache, parents, rope, recurrent=False):
     """TriSparseAttention.forward for x [B,T,D] on top of `cache`
-    ({'k','v'} each [B,Tc,n_kv,hd], or None)."""
+    ({'k','v'} each [B,Tc,n_kv,hd], or None).
+
+    recurrent=True restates TriSparseAttention.forward_recurrent (tri_sparse_attn.py:619-760): the state keeps
+    only the last `window_size` keys (:676-684), so the ALiBi path sees those keys only and stays switched on
+    as long as that count is at most 1024 (:717); the cache kept here is untrimmed and the window is applied
+    as a mask, which selects the same keys."""
     B, T, D = x.shape
     H, hd, n_kv = cfg.n_head, cfg.head_dim, cfg.n_kv_head
     n_rep = H // n_kv
@@ -281,10 +286,13 @@ def attention(sd, cfg: Config, prefix, x, cache, parents, rope):
 
     if cfg.use_alibi:
         tk_eff = np.full(T, Tk) if parents is None else (pos + 1)
+        if recurrent:
+            tk_eff = np.minimum(pos + 1, cfg.window_size)
         use_c = tk_eff <= ALIBI_MAX_T
         if np.any(use_c):
             slopes = (1.0 / (2.0 ** (np.arange(1, H + 1, dtype=F32) / H))).astype(F32)
-            bias = np.where(visible & (dist >= 0),
+            seen = visible & (dist < cfg.window_size) if recurrent else visible
+            bias = np.where(seen & (dist >= 0),
                             -slopes[:, None, None] * dist[None].astype(F32),
                             F32(-1e9)).astype(F32)
             out_c = softmax(scores + bias[None]) @ vr
@@ -330,7 +338,7 @@ def mod_layer(sd, cfg: Config, prefix, x):
     return out.reshape(x.shape).astype(F32)
 
 
-def forward_hidden(sd, cfg: Config, tokens, cache=None, parents=None):
+def forward_hidden(sd, cfg: Config, tokens, cache=None, parents=None, recurrent=False):
     """Final-norm hidden states [B,T,D] and the new per-layer KV cache."""
     tokens = np.asarray(tokens, dtype=np.int64)
     x = sd["tok_emb.weight"][tokens].astype(F32)
@@ -343,7 +351,7 @@ def forward_hidden(sd, cfg: Config, tokens, cache=None, parents=None):
     for i, kind in enumerate(cfg.layer_pattern):
         p = f"blocks.{i}."
         a, c = attention(sd, cfg, p, rmsnorm(x, sd[p + "norm1.weight"]),
-                         None if cache is None else cache[i], parents, rope)
+                         None if cache is None else cache[i], parents, rope, recurrent)
         new_cache.append(c)
         x = x + a
         h = rmsnorm(x, sd[p + "norm2.weight"])
@@ -355,10 +363,30 @@ def forward_hidden(sd, cfg: Config, tokens, cache=None, parents=None):
     return rmsnorm(x, sd["norm.weight"]), new_cache
 
 
-def forward(sd, cfg: Config, tokens, cache=None, parents=None):
+def forward(sd, cfg: Config, tokens, cache=None, parents=None, recurrent=False):
     """Logits [B,T,V] and the new cache."""
-    h, c = forward_hidden(sd, cfg, tokens, cache, parents)
+    h, c = forward_hidden(sd, cfg, tokens, cache, parents, recurrent)
     return linear(h, sd["head.weight"]), c
+
+
+def generate_greedy_recurrent(sd, cfg: Config, prompt, max_new_tokens, eos_id=None):
+    """`generate` with its default arguments (cometspark.py:773-866): greedy decoding on the recurrent path.
+    The prompt warms the state up token by token, then the LAST PROMPT TOKEN IS FED A SECOND TIME and its logits
+    give the first new token (:848-856); generation stops early when every row emits `eos_id`, and an `eos_id`
+    column is appended when the last column is not all `eos_id` (:823-829)."""
+    cur = np.asarray(prompt, dtype=np.int64)
+    if cur.ndim == 1:
+        cur = cur[None, :]
+    _, cache = forward(sd, cfg, cur, recurrent=True)       # a causal forward equals token-by-token warm-up
+    for _ in range(int(max_new_tokens)):
+        lg, cache = forward(sd, cfg, cur[:, -1:], cache=cache, recurrent=True)
+        nxt = np.argmax(lg[:, -1], axis=-1).astype(np.int64)
+        cur = np.concatenate([cur, nxt[:, None]], axis=1)
+        if eos_id is not None and np.all(nxt == eos_id):
+            break
+    if eos_id is not None and cur.shape[1] > 0 and not np.all(cur[:, -1] == eos_id):
+        cur = np.concatenate([cur, np.full((cur.shape[0], 1), eos_id, dtype=cur.dtype)], axis=1)
+    return cur
 
 
 def commit_cache(cache, base_len, keep_slots):

@@ -2,7 +2,7 @@
 
 Run once, in a container that has the reference checkout:
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference [fixture names ...]
 
 It imports the reference's own classes (verse_torch, verse_nex), feeds them
 seeded inputs and stores inputs + outputs as small .npz files.  The tests
@@ -274,9 +274,112 @@ def gen_backend():
          attention=be.attention(q, k, v), attention_mask=be.attention(q, k, v, mask))
 
 
+# ---------------------------------------------------------------------------
+# 6. Sampling: the probability vectors the reference's two samplers draw from
+# ---------------------------------------------------------------------------
+
+class _RecordingRng:
+    """Stands in for the NumPy generator inside the reference's samplers: keeps the probability vector
+    that `choice` is asked to draw from and returns index 0."""
+
+    def __init__(self):
+        self.calls = []
+
+    def choice(self, n, p=None, **kw):
+        self.calls.append((int(n) if np.isscalar(n) else len(n), np.array(p, copy=True)))
+        return 0
+
+
+def gen_sampling():
+    """`Sampler.sample` (verse_infra/verse_inference/sampler.py:86-138: threshold rule, ties kept) and
+    `VerseNexLM._generate_with_logits` (verse_nex/cometspark.py:892-911: argpartition rule, exactly k kept):
+    both run unmodified; the generator they draw with is replaced by a recorder."""
+    sys.path.insert(0, os.path.join(REF, "packages", "verse_infra"))
+    from verse_infra.verse_inference.sampler import Sampler
+    import verse_nex.cometspark as cs
+    rng = np.random.default_rng(41)
+    V = 1000
+    rows = rng.normal(0, 2.0, (6, V)).astype(np.float32)
+    rows[2, rng.choice(V, 7, replace=False)] = rows[2].max() + 1.0       # seven-way tie on top
+    rows[3, rng.choice(V, 30, replace=False)] = np.sort(rows[3])[-10]    # ties exactly at the 10th largest
+    rows[4] = np.round(rows[4])                                          # few distinct values
+    cases = [(1.0, 0), (0.8, 50), (0.8, 10), (1.3, 5), (0.5, 1), (1.0, 2000)]
+    out = {"rows": rows, "temperature": np.array([c[0] for c in cases], np.float32),
+           "top_k": np.array([c[1] for c in cases], np.int64)}
+    for ci, (T, k) in enumerate(cases):
+        for ri in range(rows.shape[0]):
+            smp = Sampler(temperature=T, top_k=k, top_p=1.0, seed=0)
+            rec = _RecordingRng()
+            smp._rng = rec
+            smp.sample(rows[ri])
+            out[f"sampler_c{ci}_r{ri}"] = rec.calls[0][1].astype(np.float64)
+    # the generate path: a real (tiny) model whose forward is replaced by the fixed logits rows
+    cfg = OM.small_config(vocab_size=V)
+    m = ref_model(cfg, seed=3)
+    for ci, (T, k) in enumerate(cases):
+        rec = _RecordingRng()
+        real_rng = np.random.default_rng
+        np.random.default_rng = lambda *a, **kw: rec
+        m.forward = lambda idx: Tensor(np.broadcast_to(rows[:, None, :], (rows.shape[0], idx.data.shape[1], V)).copy(),
+                                       requires_grad=False)
+        try:
+            m._generate_with_logits(np.zeros((rows.shape[0], 3), np.int64), 1, T, (k if k > 0 else None))
+        finally:
+            np.random.default_rng = real_rng
+        # with top-k the code draws an index into top_idx[b]; re-derive top_idx exactly as the code does
+        scaled = rows / max(T, 1e-8)
+        for ri in range(rows.shape[0]):
+            full = np.zeros(V, np.float64)
+            if k > 0:
+                kk = min(k, V)
+                top_idx = np.argpartition(-scaled, kth=kk - 1, axis=-1)[:, :kk]
+                full[top_idx[ri]] = rec.calls[ri][1]
+            else:
+                full[:] = rec.calls[0][1][ri] if rec.calls[0][1].ndim == 2 else rec.calls[ri][1]
+            out[f"generate_c{ci}_r{ri}"] = full
+    save("sampling_reference.npz", **out)
+
+
+# ---------------------------------------------------------------------------
+# 7. The recurrent decoding path and the greedy `generate` built on it, longer than the window
+# ---------------------------------------------------------------------------
+
+def gen_recurrent():
+    """`forward_recurrent` token by token (cometspark.py:737-767; attention state trimmed to the last
+    `window_size` keys, tri_sparse_attn.py:676-684) and `generate` with its defaults (greedy, :817-818, which
+    feeds the last prompt token a second time, :848-856) for sequences longer than the window, with the ALiBi
+    path on (small config) and with RoPE (miniature mate config)."""
+    out = {}
+    for tag, cfg, seed in (("alibi", OM.small_config(tie_weights=False, init_std=0.2), 201),
+                           ("rope", OM.mate_config(vocab_size=512, dim=64, n_layer=2, n_head=4, n_kv_head=2,
+                                                   window_size=16, num_global_tokens=8, max_seq_len=256,
+                                                   init_std=0.2, num_dense_parts=2, num_experts_per_part=2, top_k=1,
+                                                   layer_pattern=["trisparse", "trisparse"], embedding_scale=False),
+                            202)):
+        sd = OM.init_state_dict(cfg, seed=seed, gate_std=1.0)
+        m = ref_model(cfg, sd)
+        for n, v in sd.items():
+            out[f"{tag}.{n}"] = v
+        W = cfg.window_size
+        T = 2 * W + 9
+        toks = np.random.default_rng(seed).integers(0, cfg.vocab_size, (2, T)).astype(np.int64)
+        states, rows = None, []
+        with no_grad():
+            for t in range(T):
+                lg, states = m.forward_recurrent(Tensor(toks[:, t:t + 1]), states)
+                rows.append(np.asarray(lg.data)[:, 0])
+        out[f"{tag}_tokens"] = toks
+        out[f"{tag}_recurrent_logits"] = np.stack(rows, axis=1).astype(np.float32)      # (B, T, V)
+        out[f"{tag}_generate"] = m.generate(toks[:, :W + 5], max_new_tokens=W + 7)
+        out[f"{tag}_generate_eos"] = m.generate(toks[:1, :6], max_new_tokens=12, eos_id=int(out[f"{tag}_generate"][0, W + 6]))
+        print(tag, "recurrent", out[f"{tag}_recurrent_logits"].shape, "generate", out[f"{tag}_generate"].shape,
+              "distinct", len(np.unique(out[f"{tag}_generate"][0, W + 5:])))
+    save("recurrent_reference.npz", **out)
+
+
 if __name__ == "__main__":
-    gen_spec()
-    gen_small()
-    gen_mini()
-    gen_quant()
-    gen_backend()
+    only = set(sys.argv[2:])          # e.g. `make_golden.py /path/to/reference sampling recurrent`
+    for name, fn in (("spec", gen_spec), ("small", gen_small), ("mini", gen_mini), ("quant", gen_quant),
+                     ("backend", gen_backend), ("sampling", gen_sampling), ("recurrent", gen_recurrent)):
+        if not only or name in only:
+            fn()

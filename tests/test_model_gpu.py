@@ -53,7 +53,8 @@ def test_small_config_logits_and_greedy_stream(golden):
     m = build(cfg, _sd(g, "a_t."))
     lg = m(g["prompt"]).data.numpy()
     assert rel_err(lg, g["a_logits"]) < 1e-3
-    out = m.generate(g["prompt"], max_new_tokens=128)
+    # temperature 0 takes the reference's whole-sequence route (arg-max of `forward`'s last row, cometspark.py:892-893)
+    out = m.generate(g["prompt"], max_new_tokens=128, temperature=0.0)
     np.testing.assert_array_equal(out, g["a_greedy"])
 
 
@@ -75,7 +76,7 @@ def test_nondegenerate_variant_matches_reference_streams(golden):
     t_cfg, t_sd, d_cfg, d_sd = variant_b()
     t, d = build(t_cfg, t_sd), build(d_cfg, d_sd)
     assert rel_err(t(g["prompt"]).data.numpy(), g["b_logits"]) < 1e-3
-    np.testing.assert_array_equal(t.generate(g["prompt"], max_new_tokens=96), g["b_greedy"])
+    np.testing.assert_array_equal(t.generate(g["prompt"], max_new_tokens=96, temperature=0.0), g["b_greedy"])
     eng = vn.SpecEngine(t, d, max_batch=1, max_seq=256, k=4, temperature=0.0, bonus=False, max_new_tokens=128)
     eng.prefill(g["prompt"])
     rounds = accepted = 0
@@ -213,6 +214,37 @@ def test_forward_recurrent_matches_whole_sequence_forward():
     with pytest.raises(RuntimeError):
         for t in range(6):
             _, st = tiny.forward_recurrent(toks[:, t:t + 1], st)
+
+
+def _recurrent_case(g, tag):
+    cfg = (OM.small_config(tie_weights=False, init_std=0.2) if tag == "alibi" else
+           OM.mate_config(vocab_size=512, dim=64, n_layer=2, n_head=4, n_kv_head=2, window_size=16,
+                          num_global_tokens=8, max_seq_len=256, init_std=0.2, num_dense_parts=2,
+                          num_experts_per_part=2, top_k=1, layer_pattern=["trisparse", "trisparse"],
+                          embedding_scale=False))
+    sd = {n[len(tag) + 1:]: g[n] for n in g.files if n.startswith(tag + ".")}
+    return cfg, sd
+
+
+@pytest.mark.parametrize("tag", ["alibi", "rope"])
+def test_recurrent_route_against_the_reference_beyond_the_window(golden, tag):
+    """`forward_recurrent` token by token for more than two windows, and `generate` with its default arguments
+    (greedy on the recurrent route: last prompt token fed twice, EOS stop, EOS column appended) against what
+    the reference's own methods returned for the same weights (tests/golden/recurrent_reference.npz)."""
+    g = golden("recurrent_reference.npz")
+    cfg, sd = _recurrent_case(g, tag)
+    m = build(cfg, sd)
+    toks, want = g[f"{tag}_tokens"], g[f"{tag}_recurrent_logits"]
+    states = None
+    got = []
+    for t in range(toks.shape[1]):
+        lg, states = m.forward_recurrent(toks[:, t:t + 1], states)
+        got.append(np.asarray(lg.data)[:, 0])
+    assert rel_err(np.stack(got, 1), want) < 1e-3
+    W = cfg.window_size
+    np.testing.assert_array_equal(m.generate(toks[:, :W + 5], max_new_tokens=W + 7), g[f"{tag}_generate"])
+    eos = int(g[f"{tag}_generate"][0, W + 6])
+    np.testing.assert_array_equal(m.generate(toks[:1, :6], max_new_tokens=12, eos_id=eos), g[f"{tag}_generate_eos"])
 
 
 def test_generate_api_sampling_and_eos():

@@ -210,3 +210,54 @@ def test_topk_keeps_ties_and_masks_rest():
     p = OA.softmax64(x, 1.0, 2)
     assert p[0, 1] > 0 and p[0, 2] > 0 and p[0, 3] > 0 and p[0, 0] == 0 and p[0, 4] == 0
     np.testing.assert_allclose(p.sum(), 1.0)
+
+
+# ---- sampling rules and the recurrent decoding path, pinned to vectors recorded from the reference ----------------
+def test_sampling_probabilities_match_the_reference_samplers(golden):
+    """`softmax64(x, T, top_k)` is the distribution both reference samplers draw from: `Sampler.sample`
+    (threshold rule, every logit >= the k-th largest kept) on every row, `_generate_with_logits` (argpartition,
+    exactly k kept) wherever the k-th largest value is not tied; with ties the latter keeps a k-subset of it."""
+    from oracle import accept as OA
+    g = golden("sampling_reference.npz")
+    rows = g["rows"]
+    for ci, (T, k) in enumerate(zip(g["temperature"], g["top_k"])):
+        for ri in range(rows.shape[0]):
+            mine = OA.softmax64(rows[ri], float(T), int(k))
+            ref = g[f"sampler_c{ci}_r{ri}"]
+            assert np.array_equal(mine > 0, ref > 0), (ci, ri)
+            np.testing.assert_allclose(mine, ref, rtol=2e-5, atol=1e-9)
+            gen = g[f"generate_c{ci}_r{ri}"]
+            scaled = rows[ri] / np.float32(max(T, 1e-8))
+            kk = min(int(k), rows.shape[1]) if k > 0 else rows.shape[1]
+            kth = np.sort(scaled)[-kk]
+            if np.count_nonzero(scaled >= kth) == kk:
+                np.testing.assert_allclose(mine, gen, rtol=2e-5, atol=1e-9)
+            else:                               # ties at the threshold: exactly k of the tied set survive
+                assert np.count_nonzero(gen) == kk and np.all((gen > 0) <= (mine > 0)), (ci, ri)
+
+
+@pytest.mark.parametrize("tag", ["alibi", "rope"])
+def test_recurrent_path_matches_the_reference_beyond_the_window(golden, tag):
+    g = golden("recurrent_reference.npz")
+    cfg = (OM.small_config(tie_weights=False, init_std=0.2) if tag == "alibi" else
+           OM.mate_config(vocab_size=512, dim=64, n_layer=2, n_head=4, n_kv_head=2, window_size=16,
+                          num_global_tokens=8, max_seq_len=256, init_std=0.2, num_dense_parts=2,
+                          num_experts_per_part=2, top_k=1, layer_pattern=["trisparse", "trisparse"],
+                          embedding_scale=False))
+    sd = {n[len(tag) + 1:]: g[n] for n in g.files if n.startswith(tag + ".")}
+    toks = g[f"{tag}_tokens"]
+    want = g[f"{tag}_recurrent_logits"]
+    got, _ = OM.forward(sd, cfg, toks, recurrent=True)
+    assert float(np.max(np.abs(got - want)) / np.max(np.abs(want))) < 1e-4
+    if tag == "alibi":
+        # the whole-sequence forward lets the ALiBi path see every earlier key; with slopes >= 1/2 a key beyond
+        # the window carries a weight below e^-16, so the two rules agree far inside the tolerance while the
+        # path is on (they part only past 1,024 keys, where the whole-sequence forward switches the path off)
+        full, _ = OM.forward(sd, cfg, toks)
+        assert float(np.max(np.abs(full - want)) / np.max(np.abs(want))) < 1e-4
+    W = cfg.window_size
+    out = OM.generate_greedy_recurrent(sd, cfg, toks[:, :W + 5], W + 7)
+    np.testing.assert_array_equal(out, g[f"{tag}_generate"])
+    eos = int(g[f"{tag}_generate"][0, W + 6])
+    out = OM.generate_greedy_recurrent(sd, cfg, toks[:1, :6], 12, eos_id=eos)
+    np.testing.assert_array_equal(out, g[f"{tag}_generate_eos"])

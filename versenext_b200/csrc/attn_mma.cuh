@@ -140,7 +140,10 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
               vis = vis && (a.anc ? ((r.anc >> n) & 1ull) != 0 : n <= r.tq) && kpos <= r.pos;
             }
             if (MODE == 0) vis = vis && (r.pos - kpos) < a.window;
-            else sc -= r.slope * (float)(r.pos - kpos);
+            else {
+              sc -= r.slope * (float)(r.pos - kpos);
+              if (a.alibi_window > 0) vis = vis && (r.pos - kpos) < a.alibi_window;
+            }
           }
           c[i][e] = vis ? sc : -CUDART_INF_F;
         }
@@ -258,7 +261,8 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
   // final output of this thread after the cross-warp merge: row = tid / 16, dims 4 * (tid % 16) .. +3
   float fin[4] = {0.f, 0.f, 0.f, 0.f};
   const int mrow = tid >> 4, mcol = (tid & 15) * 4;
-  const bool use_c = a.use_alibi && (a.anc ? true : (len + a.Tn) <= a.alibi_max);
+  const bool use_c = a.use_alibi &&
+                     (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max);
   unsigned char* ring = attn_smem + warp * (RING * 4096);
 
   if (tr && tid == 0) tr[1] = clock_stamp();     // row setup and Q fragments done
@@ -271,7 +275,8 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
     } else if (path == 1) {
       attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf, depth, warp, lane, ring, o, m, l);
     } else {
-      attend<2>(a, Kc, Vc, ks, 0, hi_new, len, row, qf, depth, warp, lane, ring, o, m, l);
+      const int lo_c = a.alibi_window > 0 ? max(0, pos_min - a.alibi_window + 1) : 0;
+      attend<2>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, lane, ring, o, m, l);
     }
     if (tr && tid == 0 && path < 3) tr[2 + 2 * path] = clock_stamp();   // this warp's keys done
     // each warp parks its partial result.  Column n of tile j is output dim 8n + j, so thread (g, t) holds dims
@@ -317,7 +322,8 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
       if (path == 2 && a.anc) {
         const int r = tile0 + mrow;
         const int tq = r < R ? r % a.Tn : 0;
-        if (len + (depth ? depth[tq] : tq) + 1 > a.alibi_max) gate = 0.f;
+        const int tk = len + (depth ? depth[tq] : tq) + 1;
+        if ((a.alibi_window > 0 ? min(tk, a.alibi_window) : tk) > a.alibi_max) gate = 0.f;
       }
       if (L > 0.f) {
         const float inv = gate / L;

@@ -140,6 +140,7 @@ struct vn_model {
   // (VN_TC_CLUSTER=1: q|k|v and gate|up, 2: also the residual projections).  Off by default: on B200 the
   // cluster launch plus the reduce cost 3.5-5 us per GEMM, as much as the finalize kernel it removes.
   int use_cluster = 0;
+  bool recurrent = false;        // vn_model_set_recurrent: ALiBi path as in the reference's one-token recurrent step
   bool use_tc = true;            // VN_GEMM_TC=0 in the environment: keep the mma.sync GEMMs
   bool force_simt_attn = false;  // VN_ATTN_SIMT=1 in the environment: keep the SIMT attention kernel (A/B checks)
 };
@@ -317,6 +318,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
     a.out = m->attn; a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
     a.Tn = Tn; a.H = H; a.n_kv = n_kv; a.hd = hd; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink;
     a.use_alibi = c.use_alibi; a.alibi_max = 1024; a.slot_offset = slot_offset;
+    a.alibi_window = m->recurrent ? c.window : 0;
     a.g_a = 1.f / (1.f + expf(-L.gate_logits[0]));
     a.g_b = 1.f / (1.f + expf(-L.gate_logits[1]));
     a.g_c = 1.f / (1.f + expf(-L.gate_logits[2]));
@@ -508,6 +510,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     a.out = m->attn; a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
     a.Tn = Tn; a.H = H; a.n_kv = n_kv; a.hd = hd; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink;
     a.use_alibi = c.use_alibi; a.alibi_max = 1024; a.slot_offset = slot_offset;
+    a.alibi_window = m->recurrent ? c.window : 0;
     a.g_a = 1.f / (1.f + expf(-L.gate_logits[0]));
     a.g_b = 1.f / (1.f + expf(-L.gate_logits[1]));
     a.g_c = 1.f / (1.f + expf(-L.gate_logits[2]));
@@ -1155,6 +1158,12 @@ int32_t vn_model_head(vn_model* m, const float* hidden_dev, int32_t rows, int32_
       TRY(linear(m, g));
     }
   }
+  return VN_OK;
+}
+
+int32_t vn_model_set_recurrent(vn_model* m, int32_t on) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
+  m->recurrent = on != 0;
   return VN_OK;
 }
 

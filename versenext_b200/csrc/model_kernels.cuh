@@ -165,6 +165,10 @@ struct AttnArgs {
   const unsigned long long* anc;  // [T] ancestor-or-self bit mask over new slots, or null (chain: causal)
   int Tn, H, n_kv, hd, max_seq, window, n_sink, slot_offset;
   int use_alibi, alibi_max;
+  // > 0: the ALiBi path of the reference's one-token recurrent step (tri_sparse_attn.py:676-731): its state keeps
+  // the last `alibi_window` keys only, so the path sees those keys and is switched on while that count, not the
+  // whole length, is at most alibi_max.  0: the whole-sequence rule (every earlier key, off beyond alibi_max).
+  int alibi_window = 0;
   float g_a, g_b, g_c;   // sigmoid(gate_logits)
   float scale;
   long long* trace = nullptr;   // optional [CTAs][8] cycle stamps of the tensor-core kernel's phases
@@ -320,11 +324,13 @@ __global__ void __launch_bounds__(256) trisparse_attn_kernel(AttnArgs a) {
     for (int i = 0; i < 8; ++i) out[i] += acc.o[i] * inv;
   }
   // ---- path C: full causal + ALiBi bias -slope_h * (i - j), only while T_k <= 1024 (:489-530, :600) --
-  const int tk_eff = a.anc ? (pos + 1) : (len + n_new);
+  int tk_eff = a.anc ? (pos + 1) : (len + n_new);
+  if (a.alibi_window > 0) tk_eff = min(pos + 1, a.alibi_window);
   if (a.use_alibi && tk_eff <= a.alibi_max) {
     GroupAcc acc; acc.init();
     const float slope = 1.0f / exp2f((float)(h + 1) / (float)a.H);
-    for (int j = grp; j < len; j += 4) {
+    const int lo_c = a.alibi_window > 0 ? max(0, pos - a.alibi_window + 1) : 0;
+    for (int j = lo_c + grp; j < len; j += 4) {
       const float s = score(kc + (long long)j * kstride) - slope * (float)(pos - j);
       float v[8]; value(vc + (long long)j * kstride, v);
       acc.push(s, v);
@@ -332,7 +338,7 @@ __global__ void __launch_bounds__(256) trisparse_attn_kernel(AttnArgs a) {
     for (int n = grp; n < n_new; n += 4) {
       const bool vis = a.anc ? ((anc >> n) & 1ull) : (n <= t);
       const int pn = len + (a.depth ? a.depth[n] : n);
-      if (!vis || pn > pos) continue;
+      if (!vis || pn > pos || (a.alibi_window > 0 && pos - pn >= a.alibi_window)) continue;
       const float s = score(kc + (long long)(len + n) * kstride) - slope * (float)(pos - pn);
       float v[8]; value(vc + (long long)(len + n) * kstride, v);
       acc.push(s, v);

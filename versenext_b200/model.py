@@ -385,47 +385,67 @@ class VerseNexLM:
                 raise ValueError("states must be the list returned by an earlier forward_recurrent call of this batch")
         if int(cache.per_seq_lens[:B].max()) + 1 > cache.max_seq:
             raise RuntimeError(f"KV cache overflow: {cache.max_seq} positions are in use")
-        logits = self.forward_cached(ids, cache)
+        self._set_recurrent(True)        # the ALiBi path of the one-token step sees the last window_size keys only
+        try:
+            logits = self.forward_cached(ids, cache)
+        finally:
+            self._set_recurrent(False)
         cache.commit(1, np.ones(B, np.int32))
         self.check()
         return Tensor(logits), [cache] * self.n_layer
+
+    def _set_recurrent(self, on: bool):
+        self.ctx._check(self.ctx.lib.vn_model_set_recurrent(self.handle, int(bool(on))))
 
     # -- generate (cometspark.py:773-830) -------------------------------------------
     def generate(self, idx, max_new_tokens: Optional[int] = None, temperature: float = 1.0,
                  top_k: Optional[int] = None, eos_id: Optional[int] = None, max_safe_limit: int = 100_000,
                  seed: int = 0) -> np.ndarray:
         """Autoregressive generation with the KV cache.  As in the reference, `temperature == 1.0 and
-        top_k is None` means GREEDY decoding (cometspark.py:817-818); any other setting samples from
-        softmax(logits / T) over the top-k.  Uniforms come from Philox(seed)."""
+        top_k is None` means GREEDY decoding on the recurrent route (cometspark.py:817-818, :832-866), with that
+        route's two peculiarities kept: the last prompt token is fed twice, and the ALiBi path sees the last
+        `window_size` keys.  Any other setting follows `_generate_with_logits` (:868-915): whole-sequence
+        semantics, arg-max for `temperature <= 0`, else a draw from softmax(logits / T) over the top-k with
+        uniforms from Philox(seed)."""
         from .speculative import _unwrap
         ids = np.asarray(_unwrap(idx))
         if ids.ndim == 1:
             ids = ids[None, :]
         ids = ids.astype(np.int64)
         limit = max_safe_limit if max_new_tokens is None else int(max_new_tokens)
-        greedy = (temperature == 1.0 and top_k is None) or temperature <= 0
+        recurrent = temperature == 1.0 and top_k is None     # the reference's greedy + recurrent route (:817-818)
         B, T0 = ids.shape
-        cap = T0 + min(limit, 1 << 20) + 1
+        cap = T0 + min(limit, 1 << 20) + 2
         if self.use_rope:
             cap = min(cap, 2 * max(self.max_seq_len, 16))   # rows of the RoPE table
         cache = self.new_cache(B, cap)
-        logits = self.forward_cached(ids, cache, last_only=True)
-        cache.commit(T0, np.full(B, T0, np.int32))
         out = [ids]
-        for step in range(limit):
-            lg = logits.reshape(B, self.vocab_size)
-            if greedy:
-                nxt = sampling.argmax(self.ctx, lg)
-            else:
-                nxt = sampling.sample(self.ctx, lg, temperature=temperature, top_k=top_k or 0, seed=seed, offset=step)
-            host = nxt.numpy()
-            out.append(host[:, None])
-            if eos_id is not None and np.all(host == eos_id):
-                break
-            if step + 1 == limit:
-                break
-            logits = self.forward_cached(nxt.reshape(B, 1), cache, last_only=True)
-            cache.commit(1, np.ones(B, np.int32))
+        self._set_recurrent(recurrent)
+        try:
+            logits = self.forward_cached(ids, cache, last_only=True)
+            cache.commit(T0, np.full(B, T0, np.int32))
+            if recurrent and limit > 0:
+                # the reference warms its state up with the whole prompt and then feeds the LAST PROMPT TOKEN ONCE
+                # MORE; the logits of that second pass pick the first new token (cometspark.py:848-856)
+                logits = self.forward_cached(ids[:, -1:], cache, last_only=True)
+                cache.commit(1, np.ones(B, np.int32))
+            for step in range(limit):
+                lg = logits.reshape(B, self.vocab_size)
+                if recurrent or temperature <= 0:
+                    nxt = sampling.argmax(self.ctx, lg)
+                else:
+                    nxt = sampling.sample(self.ctx, lg, temperature=temperature, top_k=top_k or 0, seed=seed,
+                                          offset=step)
+                host = nxt.numpy()
+                out.append(host[:, None])
+                if eos_id is not None and np.all(host == eos_id):
+                    break
+                if step + 1 == limit:
+                    break
+                logits = self.forward_cached(nxt.reshape(B, 1), cache, last_only=True)
+                cache.commit(1, np.ones(B, np.int32))
+        finally:
+            self._set_recurrent(False)
         self.check()
         res = np.concatenate(out, axis=1)
         if eos_id is not None and res.shape[1] > 0 and not np.all(res[:, -1] == eos_id):
