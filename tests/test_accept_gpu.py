@@ -310,3 +310,31 @@ def test_cfg2_full_batch_row_subset_matches_oracle(ctx):
     wn, wt = OA.accept(p[rows], q[rows], draft[rows], ua[rows], us[rows], 1.0, 0)
     np.testing.assert_array_equal(n[rows], wn)
     np.testing.assert_array_equal(t[rows], wt)
+
+
+def test_sampling_distribution_equals_the_reference_samplers(ctx, golden):
+    """The distribution `vn_sample` draws from, read off through injected uniforms, against the probability
+    vectors recorded from the reference's `Sampler.sample` (sampler.py:86-138; ties at the k-th value kept):
+    for every kept token, uniforms just inside both ends and in the middle of its CDF interval must return it,
+    so every interval edge sits within a thousandth of the token's probability of the reference's."""
+    from versenext_b200 import sampling
+    g = golden("sampling_reference.npz")
+    rows = g["rows"]
+    for ci, (T, k) in enumerate(zip(g["temperature"], g["top_k"])):
+        for ri in range(rows.shape[0]):
+            ref = g[f"sampler_c{ci}_r{ri}"]
+            kept = np.flatnonzero(ref > 0)
+            cdf = np.cumsum(ref[kept])
+            lo = np.concatenate([[0.0], cdf[:-1]]) / cdf[-1]
+            hi = cdf / cdf[-1]
+            wide = (hi - lo) > 1e-5                   # float32 uniforms cannot address narrower intervals
+            toks, us = [], []
+            for frac in (0.002, 0.5, 0.998):
+                us.append(lo[wide] + frac * (hi[wide] - lo[wide]))
+                toks.append(kept[wide])
+            us, toks = np.concatenate(us).astype(np.float32), np.concatenate(toks)
+            ok = (us > 0) & (us < 1)
+            us, toks = us[ok], toks[ok]
+            lg = np.broadcast_to(rows[ri], (us.size, rows.shape[1])).copy()
+            got = sampling.sample(ctx, lg, temperature=float(T), top_k=int(k), uniforms=us).numpy()
+            np.testing.assert_array_equal(got, toks, err_msg=f"case {ci} row {ri}")
