@@ -162,8 +162,10 @@ int32_t vn_accept_strided(vn_ctx* ctx, const float* p_logits_dev, int64_t p_stri
  *   - sizes whose scratch exceeds the array (B * (2k+1) * ceil(V/4096) * 16 bytes plus about
  *     1 KB per sequence must stay below 2 MiB: e.g. B=128, k=4, V=248320 fits, B=256 does not)
  *     are rejected with VN_ERR_INVALID and a message that names both numbers;
- *   - the first call on a device looks up the array's device address; make that first call
- *     before any stream capture is begun;
+ *   - the first call on a device looks up the array's device address (the CUDA runtime may load the
+ *     library's device code at that moment, which is when the 2 MiB become resident): make that first
+ *     call at start-up, before any stream capture is begun;
+ *   - a round counter installed with vn_set_offset_source shifts the Philox offset as it does for vn_accept;
  *   - all calls share the one array: two calls that overlap on the GPU (different contexts /
  *     streams of the same device) race; calls on one context are ordered by its stream. */
 int32_t vn_accept_noalloc(vn_ctx* ctx, const float* p_logits_dev, const float* q_logits_dev,

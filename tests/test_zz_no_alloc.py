@@ -72,6 +72,39 @@ def test_noalloc_matches_allocating_entry_point_twice_in_a_row():
     assert got[0][0] == 4
 
 
+def test_noalloc_follows_the_device_round_counter_and_allocates_nothing():
+    """With a round counter on the device (what a captured decode round uses) both entry points draw the same
+    Philox numbers; and a warm call leaves the amount of free device memory where it was."""
+    import versenext_b200 as vn
+    ctx = vn.Context.get(0)
+    rng = np.random.default_rng(7)
+    p, q, draft = _inputs(rng, 9, 4, 20000)
+    pd, qd, dd = ctx.from_numpy(p), ctx.from_numpy(q), ctx.from_numpy(draft)
+    counter = ctx.from_numpy(np.array([5], np.uint32))
+    base = _run(ctx, "vn_accept", pd, qd, dd, 31, 0, 1.0)
+    ctx._check(ctx.lib.vn_set_offset_source(ctx.handle, _ptr(counter)))
+    try:
+        want = _run(ctx, "vn_accept", pd, qd, dd, 31, 0, 1.0)
+        got = _run(ctx, "vn_accept_noalloc", pd, qd, dd, 31, 0, 1.0)
+    finally:
+        ctx._check(ctx.lib.vn_set_offset_source(ctx.handle, None))
+    np.testing.assert_array_equal(got[0], want[0])
+    np.testing.assert_array_equal(got[1], want[1])
+    shifted = _run(ctx, "vn_accept_noalloc", pd, qd, dd, 31, 5, 1.0)      # the same offset given by the host
+    np.testing.assert_array_equal(shifted[1], got[1])
+    assert not np.array_equal(base[1], got[1])                            # the counter really moved the streams
+    # nothing allocated: outputs come from the caller, scratch from the library image
+    out_len, out_tok = ctx.zeros((9,), np.int32), ctx.zeros((9, 5), np.int64)
+    ctx.sync()
+    free0, _ = ctx.mem_info()
+    for _ in range(3):
+        ctx._check(ctx.lib.vn_accept_noalloc(ctx.handle, _ptr(pd), _ptr(qd), _ptr(dd), None, None, 31, 0, 1.0, 1,
+                                             9, 4, 20000, _ptr(out_len), _ptr(out_tok)))
+    ctx.sync()
+    free1, _ = ctx.mem_info()
+    assert free1 == free0
+
+
 def test_noalloc_rejects_sizes_beyond_its_scratch():
     import versenext_b200 as vn
     ctx = vn.Context.get(0)

@@ -1416,8 +1416,9 @@ int32_t vn_accept_noalloc(vn_ctx* ctx, const float* p_logits_dev, const float* q
   // over from the previous call has to be cleared
   const int grid = (int)std::min<long long>((long long)n_part, (long long)ctx->sm_count * 8);
   { const int32_t st_ = launch_accept_stats(ctx, vec, greedy, grid, rs, B, nchunks, temp, part); if (st_) return st_; }
+  // the device-side round counter (vn_set_offset_source) shifts the Philox offset here exactly as in vn_accept
   VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_accept_dev, u_sample_dev, seed, offset,
-            (const unsigned*)nullptr, temp, (int)greedy, bonus, 1, 0, dec, out_len_dev, o64);
+            ctx->offset_src, temp, (int)greedy, bonus, 1, 0, dec, out_len_dev, o64);
   if (!greedy) {
     dim3 g(nchunks, B);
     if (vec) VN_LAUNCH(ctx, accept_residual_kernel<true>, g, STATS_THREADS, 0, rs, nchunks, temp, dec, mass);
