@@ -35,6 +35,12 @@ import sys
 import threading
 import time
 
+if "reference" in sys.argv[1:] or "--impl=reference" in sys.argv[1:]:
+    # The CPU arm uses every host core.  BLAS reads these variables when NumPy loads it, so they are set before
+    # the import below; torchrun exports OMP_NUM_THREADS=1 to its workers, which is overridden here on purpose.
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(os.cpu_count() or 1)
+
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -131,6 +137,44 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def blas_threads():
+    """Threads the BLAS behind NumPy really uses (threadpoolctl), else the environment's request."""
+    try:
+        from threadpoolctl import threadpool_info
+        n = [int(d.get("num_threads", 0)) for d in threadpool_info() if d.get("user_api") == "blas"]
+        if n:
+            return max(n)
+    except Exception:
+        pass
+    return int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+
+
+def timed_repeats(run_k_steps, prepare, ctx, dist, local, min_repeats=5, min_total_ms=1000.0, max_repeats=40):
+    """`prepare()` (untimed) then K steps between two CUDA events on the context's stream, bracketed by a
+    barrier and a device synchronisation on both sides, repeated until at least `min_repeats` repeats and
+    `min_total_ms` of timed work are in.  Every repeat's time is the maximum over the ranks.
+    Returns the list of repeat times in ms."""
+    reps = []
+    while True:
+        prepare()
+        barrier_sync(dist, ctx)
+        e0, e1 = ctx.event(), ctx.event()
+        e0.record()
+        run_k_steps()
+        e1.record()
+        ms = e0.elapsed_ms(e1)
+        barrier_sync(dist, ctx)
+        reps.append(max_over_ranks(dist, ms, local))
+        if len(reps) >= min_repeats and (sum(reps) >= min_total_ms or len(reps) >= max_repeats):
+            return reps
+
+
+def spread(reps, steps):
+    per = sorted(r / steps for r in reps)
+    return {"repeats": len(per), "median_ms_per_step": statistics.median(per), "min_ms_per_step": per[0],
+            "max_ms_per_step": per[-1], "timed_ms_total": sum(reps)}
+
+
 def dist_setup(n_gpus):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -203,7 +247,7 @@ def cpu_accept_sample(n_seq, repeats=1):
 
 SPEC = dict(B=32, prompt=512, k=4, temperature=0.8, top_k=50, seed=4, new_tokens=256)
 SPEC_WORKLOAD = ("spec: mate target (D=1024, L=20: 5 MoD + 15 TriSparse, V=248320, bf16) + 2-layer D=256 draft, "
-                 "k=4, T=0.8, top-k 50, 32 requests/GPU, 512-token prompts")
+                 "k=4, T=0.8, top-k 50, 32 requests of 512-token prompts")
 MATE_PARAMS = 1107375164
 
 
@@ -261,24 +305,93 @@ def cpu_spec_sample(max_seconds=25.0, rounds=2, warmup=1):
     return committed / dt, dt, done
 
 
+def _spec_engine(vn, target, draft, B, args, warm):
+    k, T0 = SPEC["k"], SPEC["prompt"]
+    rounds = warm + args.steps + 8
+    return vn.SpecEngine(target, draft, max_batch=B, max_seq=T0 + rounds * (k + 1) + 64, k=k,
+                         temperature=SPEC["temperature"], top_k=SPEC["top_k"], seed=SPEC["seed"], bonus=True,
+                         max_new_tokens=rounds * (k + 1))
+
+
+def _time_engine(eng, ctx, dist, local, steps, warm):
+    """Rounds per second of one engine: every repeat starts from the state right after prefill (so the context
+    length, and with it the K/V window that is read, is the same in every repeat), runs `warm` untimed rounds
+    and then exactly `steps` timed ones.  Returns (repeat times ms, tokens committed in the timed rounds of the
+    last repeat on this rank)."""
+    box = {}
+
+    def prepare():
+        eng.rewind()
+        for _ in range(warm):
+            eng.step()
+        box["c0"] = int(eng.counts().sum())
+
+    def run():
+        for _ in range(steps):
+            eng.step()
+
+    reps = timed_repeats(run, prepare, ctx, dist, local)
+    return reps, int(eng.counts().sum()) - box["c0"]
+
+
+def _sum_over_ranks(dist, value, local):
+    if dist is None:
+        return float(value)
+    import torch
+    t = torch.tensor([float(value)], dtype=torch.float64, device=f"cuda:{local}")
+    dist.all_reduce(t)
+    return float(t.item())
+
+
+def _sharded_check(vn, target, draft, dist, ctx, local, world, rank, rounds=4):
+    """Vocabulary-sharded head + acceptance over the ranks (the one data path with an exchange): a few rounds of
+    the sharded engine on this rank's requests must commit exactly the tokens of its plain engine."""
+    from versenext_b200.sharded_engine import ShardedSpecEngine
+    B, k, T0 = 8, SPEC["k"], 64
+    prompts = spec_prompts(B, T0, 99, rank)
+    kw = dict(max_batch=B, max_seq=T0 + (rounds + 2) * (k + 1) + 16, k=k, temperature=1.0, seed=5,
+              max_new_tokens=(rounds + 2) * (k + 1))
+    plain = vn.SpecEngine(target, draft, top_k=0, bonus=True, graph=False, **kw)
+    plain.prefill(prompts)
+    for _ in range(rounds):
+        plain.step()
+    want = plain.history.numpy()[:, :rounds]
+    want_counts = plain.counts()
+    del plain
+    sh = ShardedSpecEngine(target, draft, **kw)
+    sh.prefill(prompts)
+    sh.step()                                   # warm-up round (buffers, communicators)
+    sh.rewind()
+    barrier_sync(dist, ctx)
+    t0 = time.perf_counter()
+    for _ in range(rounds):
+        sh.step()
+    ctx.sync()
+    ms = (time.perf_counter() - t0) * 1e3 / rounds
+    ok = bool(np.array_equal(sh.counts(), want_counts) and np.array_equal(sh.history.numpy()[:, :rounds], want))
+    ok_all = _sum_over_ranks(dist, 1.0 if ok else 0.0, local) == world
+    return {"ok": bool(ok_all), "ms_per_round": max_over_ranks(dist, ms, local), "n_ranks": world,
+            "requests_per_rank": B, "rounds": rounds,
+            "what": "ShardedSpecEngine (LM head + acceptance split by vocabulary columns over the ranks) commits "
+                    "the same tokens as the plain engine on every rank"}
+
+
 def run_spec(args):
     import versenext_b200 as vn
     world, rank, local, dist = dist_setup(args.gpus)
     ctx = vn.Context.get(local)
-    B, k, T0 = SPEC["B"], SPEC["k"], SPEC["prompt"]
-    if args.strong:                      # the 32 requests of the configuration split over the ranks
-        B = max(1, SPEC["B"] // world)
+    k, T0 = SPEC["k"], SPEC["prompt"]
+    # The configuration is 32 requests in all, split evenly over the ranks: strong scaling.  (--weak: 32 per rank.)
+    B = SPEC["B"] if args.weak else max(1, SPEC["B"] // world)
     t_build = time.perf_counter()
     target, draft = build_spec_models(f"cuda:{local}")
     if args.quant:                       # weight-only quantised target (the INT8 / INT4 variants of the workload)
         target.quantize(args.quant)
     t_build = time.perf_counter() - t_build
     warm = max(args.warmup, 3)
-    max_seq = T0 + (warm + 4 * args.steps + 40) * (k + 1) + 64
-    eng = vn.SpecEngine(target, draft, max_batch=B, max_seq=max_seq, k=k, temperature=SPEC["temperature"],
-                        top_k=SPEC["top_k"], seed=SPEC["seed"], bonus=True,
-                        max_new_tokens=(warm + 4 * args.steps + 40) * (k + 1))
-    prompts = spec_prompts(B, T0, SPEC["seed"], rank)
+    eng = _spec_engine(vn, target, draft, B, args, warm)
+    prompts = spec_prompts(SPEC["B"] if args.weak else max(SPEC["B"], world), T0, SPEC["seed"], rank if args.weak else 0)
+    prompts = prompts[:B] if args.weak else prompts[rank * B:(rank + 1) * B]
     ctx.sync()
     t_pre = time.perf_counter()
     eng.prefill(prompts)
@@ -286,35 +399,25 @@ def run_spec(args):
     t_pre = time.perf_counter() - t_pre
     for _ in range(warm):
         eng.step()
-    c0 = eng.counts().sum()
-    # ---- timed region: K rounds, state resident on the device, no host synchronisation inside
+    # ---- timed region: K rounds, state resident on the device, no host synchronisation inside; repeated
     clocks = ClockSampler(local).start() if rank == 0 else None
-    barrier_sync(dist, ctx)
     l0 = ctx.launch_count()
-    e0, e1 = ctx.event(), ctx.event()
-    e0.record()
-    for _ in range(args.steps):
-        eng.step()
-    e1.record()
-    ms = e0.elapsed_ms(e1)
-    barrier_sync(dist, ctx)
-    launches = ctx.launch_count() - l0
+    reps, committed_rank = _time_engine(eng, ctx, dist, local, args.steps, warm)
+    launches_per_repeat = (ctx.launch_count() - l0) // len(reps)
     clk = clocks.stop() if clocks else None
-    c1 = eng.counts().sum()
-    ms = max_over_ranks(dist, ms, local)
-    committed = float(c1 - c0)
-    if dist is not None:
-        import torch
-        t = torch.tensor([committed], dtype=torch.float64, device=f"cuda:{local}")
-        dist.all_reduce(t)
-        committed = float(t.item())
+    ms = statistics.median(reps)
+    committed = _sum_over_ranks(dist, committed_rank, local)
     value = committed / (ms * 1e-3)
     accept_rate = float(eng.accept_len.numpy().mean() / k)
     ctx_len = int(eng.t_cache.per_seq_lens.mean())
+    launches = launches_per_repeat * args.steps // (args.steps + warm)
 
     # ---- end to end through the host-facing call: pinned host tokens in, committed tokens out, every round
     h_pair = ctx.pinned((B, 2), np.int64)
     h_len, h_tok = ctx.pinned((B,), np.int32), ctx.pinned((B, k + 1), np.int64)
+    eng.rewind()
+    for _ in range(warm):
+        eng.step()
     eng.pair.copy_to_pinned_async(h_pair)
     ctx.sync()
 
@@ -336,7 +439,7 @@ def run_spec(args):
         got += e2e_step()
     barrier_sync(dist, ctx)
     e2e_s = max_over_ranks(dist, time.perf_counter() - t0, local)
-    e2e = {"value": got * world / e2e_s, "unit": "tok/s", "steps": n_e2e,
+    e2e = {"value": _sum_over_ranks(dist, got, local) / e2e_s, "unit": "tok/s", "steps": n_e2e,
            "h2d_bytes_per_step": int(h_pair.nbytes),
            "d2h_bytes_per_step": int(h_len.nbytes + h_tok.nbytes + h_pair.nbytes)}
 
@@ -344,14 +447,25 @@ def run_spec(args):
     # durations with CUDA events around every launch (eager; each pair of events adds a few microseconds,
     # so these give the SHARES, the graph timing gives the step time)
     n_prof = min(args.steps, 16)
+    eng.rewind()
+    for _ in range(warm):
+        eng.step()
+    lens0 = eng.t_cache.per_seq_lens.copy()
     eng.verify_accept_only(graph=False)
     eng.verify_accept_only(graph=True)
-    v0, v1 = ctx.event(), ctx.event()
-    v0.record()
-    for _ in range(n_prof):
-        eng.verify_accept_only(graph=True)
-    v1.record()
-    step_ms = v0.elapsed_ms(v1) / n_prof
+    v_reps = []
+    for _ in range(5):
+        eng.t_cache.set_lengths(lens0)                 # every repeat at the same context length
+        eng._len_bound = int(lens0.max())
+        v0, v1 = ctx.event(), ctx.event()
+        v0.record()
+        for _ in range(n_prof):
+            eng.verify_accept_only(graph=True)
+        v1.record()
+        v_reps.append(v0.elapsed_ms(v1) / n_prof)
+    eng.t_cache.set_lengths(lens0)
+    eng._len_bound = int(lens0.max())
+    step_ms = statistics.median(v_reps)
     ctx.profile(True)
     for _ in range(n_prof):
         eng.verify_accept_only()
@@ -367,19 +481,37 @@ def run_spec(args):
     top = sorted(rep.items(), key=lambda kv: -kv[1]["ms"])
     roofline = {"bound": "hbm", "kernel": "verify+sample step (all kernels of the target forward and acceptance)",
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": f"of {peak_kind}", "traffic": None if args.quant else SPEC_STEP_TRAFFIC, "step_ms": step_ms, "algorithmic_bytes": nbytes,
+                "peak_kind": f"of {peak_kind}",
+                "traffic": SPEC_STEP_TRAFFIC if (not args.quant and B == SPEC["B"]) else None,
+                "step_ms": step_ms, "step_ms_repeats": v_reps, "algorithmic_bytes": nbytes,
                 "gemm_ms": gemm_ms, "gemm_weight_gbs": MATE_PARAMS * 2 / (gemm_ms * 1e-3) / 1e9,
                 "kernel_share": {n: v["ms"] / n_prof / prof_ms for n, v in top},
                 "kernel_ms_per_step": {n: v["ms"] / n_prof for n, v in top},
                 "kernel_launches_per_step": {n: v["launches"] / n_prof for n, v in top}}
 
+    # ---- N > 1: the same models with 32 requests on every rank (weak scaling), and the sharded data path
+    weak = sharded = None
+    if world > 1 and not args.weak:
+        if not args.no_weak:
+            eng_w = _spec_engine(vn, target, draft, SPEC["B"], args, warm)
+            eng_w.prefill(spec_prompts(SPEC["B"], T0, SPEC["seed"], rank))
+            for _ in range(warm):
+                eng_w.step()
+            reps_w, c_w = _time_engine(eng_w, ctx, dist, local, args.steps, warm)
+            ms_w = statistics.median(reps_w)
+            weak = {"value": _sum_over_ranks(dist, c_w, local) / (ms_w * 1e-3), "unit": "tok/s",
+                    "ms_per_step": ms_w / args.steps, "per_gpu_requests": SPEC["B"], "scaling": "weak",
+                    **spread(reps_w, args.steps)}
+            del eng_w
+        if not args.no_sharded:
+            sharded = _sharded_check(vn, target, draft, dist, ctx, local, world, rank)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        import os as _os
         tps, secs, rounds = cpu_spec_sample()
-        cpu = {"value": tps, "unit": "tok/s", "cores": _os.cpu_count(), "kind": "port",
+        cpu = {"value": tps, "unit": "tok/s", "cores": blas_threads(), "kind": "port",
                "sample": f"1 of 32 requests, {rounds} rounds ({secs:.1f} s), full re-forward per round as the "
-                         "reference does; NumPy restatement (oracle/), fp32, BLAS threads = all cores"}
+                         f"reference does; NumPy restatement (oracle/), fp32, {blas_threads()} BLAS threads"}
     sampler = None
     if rank == 0 and world == 1 and not args.no_sampler:
         del eng
@@ -389,17 +521,25 @@ def run_spec(args):
         print(json.dumps({
             "metric": "accepted tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong" if args.strong else "weak",
+            "scaling": "weak" if args.weak else "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": SPEC_WORKLOAD + (f", target weights {args.quant}" if args.quant else ""),
-                       "per_gpu_requests": B, "context_tokens": ctx_len,
-                       "l2": "weights (2.2 GB) larger than L2, no flush", "step": "one speculative round"},
+            "config": spec_config(args.quant),
+            "timing": spread(reps, args.steps),
+            "per_gpu_requests": B, "context_tokens": ctx_len,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clk,
             "accept_rate": accept_rate, "tokens_per_round_per_request": committed / world / B / args.steps,
             "prefill_s": t_pre, "weights_build_s": t_build, "sampler": sampler,
+            "weak_32_per_gpu": weak, "sharded": sharded,
         }))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def spec_config(quant=None):
+    """The `config` object of the default workload: the same in the device arm and in the CPU arm."""
+    return {"workload": SPEC_WORKLOAD + (f", target weights {quant}" if quant else ""),
+            "requests": SPEC["B"], "requests_split": "evenly over the ranks (32 / N per GPU)",
+            "l2": "weights (2.2 GB) larger than L2, no flush", "step": "one speculative round over the batch"}
 
 
 def run_sharded(args):
@@ -499,16 +639,220 @@ def run_reference_spec(args):
     if rank != 0:
         return
     budget = 150.0
-    warm = min(max(args.warmup, 0), 3)
-    tps, secs, rounds = cpu_spec_sample(max_seconds=budget, rounds=max(1, args.steps), warmup=warm)
-    sample = (f"1 of 32 requests per step, {rounds} rounds run inside a {budget:.0f} s budget; full re-forward per "
-              "round as the reference does; NumPy restatement (oracle/), fp32, BLAS threads = all cores")
+    warm = max(args.warmup, 0)
+    tps, secs, rounds = cpu_spec_sample(max_seconds=budget, rounds=max(1, args.steps), warmup=min(warm, 3))
+    threads = blas_threads()
+    sample = (f"1 of the 32 requests per step, {rounds} rounds run inside a {budget:.0f} s budget ({min(warm, 3)} untimed "
+              f"warm-up rounds); full re-forward of [context, draft] per round as the reference does; NumPy restatement "
+              f"of the reference algorithm (oracle/, kind 'port': the reference itself is Python and does not travel to "
+              f"this machine), fp32, {threads} BLAS threads on {os.cpu_count()} host cores")
     print(json.dumps({
         "impl": "reference", "metric": "accepted tok/s", "value": tps, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": rounds, "warmup": warm, "ms_per_step": secs / max(rounds, 1) * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": SPEC_WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": spec_config(args.quant),
+        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------
+# tree verification (16-node draft tree on a 2048-token cache, batch 8) and the small CPU-runnable configuration
+# ---------------------------------------------------------------------------
+
+TREE = dict(B=8, ctx=2048, parents=[-1, -1, -1, -1, 0, 0, 1, 1, 4, 4, 5, 5, 6, 6, 7, 7], seed=3)
+TREE_WORKLOAD = ("tree: mate target (bf16), 16-node draft tree (4 roots, 2 children under each of the first two, 2 under "
+                 "each of those), ancestor-bitmask attention on a 2048-token cache, batch 8")
+
+
+def run_tree(args):
+    import ctypes as C
+    import versenext_b200 as vn
+    from versenext_b200 import synthetic as S
+    world, rank, local, dist = dist_setup(args.gpus)
+    ctx = vn.Context.get(local)
+    B, T0, parents = TREE["B"], TREE["ctx"], TREE["parents"]
+    n = len(parents)
+    tk = S.mate_kwargs()
+    target = vn.VerseNexLM(dtype="bf16", device=f"cuda:{local}", **tk)
+    S.load_random(target, tk, seed=0)
+    if args.quant:
+        target.quantize(args.quant)
+    rng = np.random.default_rng([TREE["seed"], rank])
+    cache = target.new_cache(B, T0 + n + 16)
+    prompt = rng.integers(0, 248320, (B, T0)).astype(np.int64)
+    for lo in range(0, T0, 512):
+        target.forward_cached(prompt[:, lo:lo + 512], cache, want_logits=False, want_hidden=True, last_only=True)
+        cache.commit(512, np.full(B, 512, np.int32))
+    nodes = ctx.from_numpy(rng.integers(0, 248320, (B, n)).astype(np.int64))
+    logits = ctx.empty((B, n, 248320), np.float32)
+    pred = ctx.empty((B * n,), np.int64)
+
+    def issue():
+        target.forward_cached(nodes, cache, parents=parents, out_logits=logits)
+        ctx._check(ctx.lib.vn_sample(ctx.handle, C.c_void_p(logits.ptr), 248320, B * n, 248320, 0.0, 0, None, 0, 0, 0, 0,
+                                     C.c_void_p(pred.ptr)))
+
+    issue()                                # eager once: buffers, attributes, the tree's masks
+    ctx._check(ctx.lib.vn_graph_begin(ctx.handle))
+    try:
+        issue()
+    finally:
+        g = C.c_void_p()
+        ctx._check(ctx.lib.vn_graph_end(ctx.handle, C.byref(g)))
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        ctx._check(ctx.lib.vn_graph_launch(ctx.handle, g))
+    clocks = ClockSampler(local).start() if rank == 0 else None
+    l0 = ctx.launch_count()
+    issue()
+    launches = (ctx.launch_count() - l0) * args.steps
+    reps = timed_repeats(lambda: [ctx._check(ctx.lib.vn_graph_launch(ctx.handle, g)) for _ in range(args.steps)],
+                         lambda: None, ctx, dist, local)
+    clk = clocks.stop() if clocks else None
+    ms = statistics.median(reps)
+    step_ms = ms / args.steps
+    target.check()
+    nbytes = MATE_PARAMS * 2 + 20 * B * min(T0, 1024) * 2 * 512 * 2
+    peak, peak_kind = peaks()
+    achieved = nbytes / (step_ms * 1e-3) / 1e9
+    # end to end: the tree's tokens from pinned host memory, the nodes' arg-max tokens back
+    h_nodes, h_pred = ctx.pinned((B, n), np.int64), ctx.pinned((B * n,), np.int64)
+    h_nodes[...] = nodes.numpy()
+
+    def e2e_step():
+        nodes.copy_from_pinned_async(h_nodes)
+        ctx._check(ctx.lib.vn_graph_launch(ctx.handle, g))
+        pred.copy_to_pinned_async(h_pred)
+        ctx.sync()
+
+    e2e_step()
+    barrier_sync(dist, ctx)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier_sync(dist, ctx)
+    e2e_s = max_over_ranks(dist, time.perf_counter() - t0, local)
+    ctx._check(ctx.lib.vn_graph_destroy(ctx.handle, g))
+    if rank == 0:
+        print(json.dumps({
+            "metric": "verified tree nodes/s", "value": B * n * world * args.steps / (ms * 1e-3), "unit": "nodes/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": step_ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": TREE_WORKLOAD + (f", target weights {args.quant}" if args.quant else ""),
+                       "parents": parents, "step": "one target forward over the 16 nodes of every sequence + arg-max "
+                       "per node", "l2": "weights (2.2 GB) larger than L2, no flush"},
+            "timing": spread(reps, args.steps),
+            "roofline": {"bound": "hbm", "kernel": "tree verify step (all kernels of the target forward over 128 node "
+                         "rows, LM head, arg-max)", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None, "step_ms": step_ms,
+                         "algorithmic_bytes": nbytes, "target_ms": 0.53},
+            "cpu_baseline": None,
+            "e2e": {"value": B * n * world * args.steps / e2e_s, "unit": "nodes/s",
+                    "h2d_bytes_per_step": int(h_nodes.nbytes), "d2h_bytes_per_step": int(h_pred.nbytes)},
+            "gpu_launches": launches, "clocks": clk,
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+SMALL = dict(vocab_size=256, dim=64, n_layer=2, n_head=4, n_kv_head=2, window_size=32, num_global_tokens=4,
+             use_alibi=True, use_rope=False, max_seq_len=256, tie_weights=True)
+SMALL_WORKLOAD = ("small: VerseNexLM dim 64, 2 TriSparse layers, vocab 256, fp32 + 1-layer draft, k=4, greedy, batch 1, "
+                  "32-token prompt, 128 generated tokens")
+
+
+def _small_weights():
+    from versenext_b200 import synthetic as S
+    tk, dk = dict(SMALL), dict(SMALL, n_layer=1)
+    t_sd = dict(S.random_tensors(tk, seed=0, init_std=0.2))
+    d_sd = dict(S.random_tensors(dk, seed=1, init_std=0.2))
+    d_sd["tok_emb.weight"] = t_sd["tok_emb.weight"]
+    return tk, dk, t_sd, d_sd
+
+
+def cpu_small_run():
+    """The whole small configuration on the host (NumPy restatement of the reference loop): tok/s, seconds."""
+    from oracle import model as OM
+    from oracle import spec as OS
+    tk, dk, t_sd, d_sd = _small_weights()
+    t_cfg, d_cfg = OM.Config(**tk), OM.Config(**dk)
+    t_sd["head.weight"], d_sd["head.weight"] = t_sd["tok_emb.weight"], d_sd["tok_emb.weight"]
+    prompt = np.random.default_rng(0).integers(0, 256, (1, 32)).astype(np.int64)
+    t0 = time.perf_counter()
+    st = OS.generate(t_sd, t_cfg, d_sd, d_cfg, prompt, 4, 128, temperature=0.0, bonus=False)
+    dt = time.perf_counter() - t0
+    return 128 / dt, dt, st
+
+
+def run_small(args):
+    import versenext_b200 as vn
+    world, rank, local, dist = dist_setup(args.gpus)
+    ctx = vn.Context.get(local)
+    tk, dk, t_sd, d_sd = _small_weights()
+    target = vn.VerseNexLM(dtype="f32", device=f"cuda:{local}", **tk)
+    target.load_state_dict(t_sd)
+    draft = vn.VerseNexLM(dtype="f32", device=f"cuda:{local}", **dk)
+    draft.load_state_dict(d_sd)
+    prompt = np.random.default_rng(0).integers(0, 256, (1, 32)).astype(np.int64)
+    eng = vn.SpecEngine(target, draft, max_batch=1, max_seq=256, k=4, temperature=0.0, bonus=False, max_new_tokens=160)
+    toks, st = eng.generate(prompt, 128)
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        eng.generate(prompt, 128)
+    clocks = ClockSampler(local).start() if rank == 0 else None
+    barrier_sync(dist, ctx)
+    l0 = ctx.launch_count()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        toks, st = eng.generate(prompt, 128)          # prompt from the host, tokens back to the host: end to end
+    barrier_sync(dist, ctx)
+    secs = max_over_ranks(dist, time.perf_counter() - t0, local)
+    launches = ctx.launch_count() - l0
+    clk = clocks.stop() if clocks else None
+    # device-resident part: the rounds alone, after prefill
+    eng.prefill(prompt)
+    for _ in range(3):
+        eng.step()
+    reps = timed_repeats(lambda: [eng.step() for _ in range(32)], lambda: (eng.rewind(), eng.step()), ctx, dist, local,
+                         min_total_ms=200.0)
+    round_ms = statistics.median(reps) / 32
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        tps, dt, cst = cpu_small_run()
+        cpu = {"value": tps, "unit": "tok/s", "cores": blas_threads(), "kind": "port",
+               "sample": f"the whole configuration: 128 tokens in {cst['rounds']} rounds ({dt:.1f} s), full re-forward per "
+                         "round as the reference does; NumPy restatement (oracle/)",
+               "same_tokens_as_device": bool(np.array_equal(cst["tokens"], toks))}
+    if rank == 0:
+        value = 128 * world * args.steps / secs
+        print(json.dumps({
+            "metric": "accepted tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": SMALL_WORKLOAD, "step": "one whole generation of 128 tokens (prefill + rounds)",
+                       "l2": "model fits in L2: latency-bound by construction"},
+            "roofline": None, "round_ms": round_ms, "rounds": st["rounds"], "cpu_baseline": cpu,
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": int(prompt.nbytes),
+                    "d2h_bytes_per_step": int(toks.nbytes)},
+            "gpu_launches": launches, "clocks": clk,
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_reference_small(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    tps, dt, st = cpu_small_run()
+    sample = f"the whole configuration once ({dt:.1f} s, {st['rounds']} rounds), NumPy restatement (oracle/), {blas_threads()} BLAS threads"
+    print(json.dumps({
+        "impl": "reference", "metric": "accepted tok/s", "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": 1,
+        "warmup": 0, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": SMALL_WORKLOAD, "step": "one whole generation of 128 tokens (prefill + rounds)",
+                   "l2": "model fits in L2: latency-bound by construction"},
+        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": blas_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -655,18 +999,21 @@ def main():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="spec", choices=["spec", "accept", "sharded"])
-    ap.add_argument("--strong", action="store_true",
-                    help="spec workload: split the configuration's 32 requests over the ranks (default: 32 per rank)")
+    ap.add_argument("--workload", default="spec", choices=["spec", "accept", "sharded", "tree", "small"])
+    ap.add_argument("--weak", action="store_true",
+                    help="spec workload: 32 requests on every rank (default: the configuration's 32 split over the ranks)")
+    ap.add_argument("--no-weak", action="store_true", help="N > 1: skip the extra 32-per-GPU measurement")
+    ap.add_argument("--no-sharded", action="store_true", help="N > 1: skip the sharded-head check")
     ap.add_argument("--quant", default=None, choices=["int8", "int4", "int4g128"],
                     help="spec workload: quantise the target's linear weights (not the default benchmark line)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-sampler", action="store_true", help="spec workload: skip the sampler GB/s measurement")
     args = ap.parse_args()
     if args.impl == "reference":
-        (run_reference if args.workload == "accept" else run_reference_spec)(args)
+        {"accept": run_reference, "small": run_reference_small}.get(args.workload, run_reference_spec)(args)
     else:
-        {"spec": run_spec, "accept": run_accept, "sharded": run_sharded}[args.workload](args)
+        {"spec": run_spec, "accept": run_accept, "sharded": run_sharded, "tree": run_tree,
+         "small": run_small}[args.workload](args)
 
 
 if __name__ == "__main__":

@@ -127,6 +127,7 @@ struct vn_model {
   int* expert_count = nullptr; int* expert_off = nullptr; int* expert_cur = nullptr;
   int* sorted_row = nullptr; int* slot_pos = nullptr;
   int* depth_dev = nullptr; unsigned long long* anc_dev = nullptr; int* rows_dev = nullptr;
+  std::vector<int> tree_parents;   // the tree whose depths and ancestor masks depth_dev / anc_dev hold
   float* stage = nullptr; size_t stage_elems = 0;
   int qmode = 0;                 // 0 dense, 1 int8, 2 int4 per channel, 3 int4 group-128 (vn_model_quantize)
   int preq_mode = 0;             // scheme of linears that arrive already quantised (vn_model_load_quant_tensor)
@@ -690,6 +691,35 @@ int32_t alloc_quant(vn_model* m, int mode) {
   return VN_OK;
 }
 
+// sink K / V = wk(global_tokens), wv(global_tokens): fixed per layer (tri_sparse_attn.py:223-242).  With quantised
+// linears (mode != 0) the k / v rows of the quantised q|k|v matrix are dequantised inside the GEMM, which is what
+// the reference's compressed model computes (its wk / wv are quantised linears by then).
+int32_t compute_sinks(vn_model* m, int mode) {
+  vn_ctx* ctx = m->ctx;
+  const Config& c = m->cfg;
+  const long long D = c.dim, qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
+  for (auto& L : m->layers) {
+    for (int which = 0; which < 2; ++which) {
+      GemmArgs g;
+      g.A = L.sink; g.lda = D; g.ldw = D;
+      g.C = which ? L.sink_v : L.sink_k; g.ldc = kvd; g.M = c.n_sink; g.N = (int)kvd; g.K = (int)D; g.c_bf16 = c.bf16;
+      if (mode) {
+        const long long r0 = qd + which * kvd;
+        g.W = (const unsigned char*)L.q[0] + (size_t)r0 * q_row_bytes(mode, D);
+        g.w_scale = L.qs[0] + (size_t)r0 * q_row_scales(mode, D);
+        g.wq = mode;
+        if (!gemm_mma_q_supported(g)) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised GEMM shape K=%d unsupported", g.K);
+        TRY(launch_gemm_mma_q(ctx, g));
+      } else {
+        g.W = (char*)L.wqkv + (size_t)(qd + which * kvd) * D * m->esz;
+        if (c.bf16) TRY((launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g)));
+        else TRY((launch_gemm_simt<float, float>(ctx, g)));
+      }
+    }
+  }
+  return VN_OK;
+}
+
 int scheme_mode(const char* scheme) {
   if (!scheme) return 0;
   const std::string s(scheme);
@@ -907,28 +937,9 @@ int32_t vn_model_finalize(vn_model* m) {
     VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     m->rope_rows = rows;
   }
-  // sink K / V = wk(global_tokens), wv(global_tokens): fixed per layer (tri_sparse_attn.py:223-242)
   const long long D = c.dim, qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
   const int pm = m->preq_mode;
-  for (auto& L : m->layers) {
-    for (int which = 0; which < 2; ++which) {
-      GemmArgs g;
-      g.A = L.sink; g.lda = D; g.ldw = D;
-      g.C = which ? L.sink_v : L.sink_k; g.ldc = kvd; g.M = c.n_sink; g.N = (int)kvd; g.K = (int)D; g.c_bf16 = c.bf16;
-      if (pm) {           // the k / v rows of the quantised q|k|v matrix, dequantised inside the GEMM
-        const long long r0 = qd + which * kvd;
-        g.W = (const unsigned char*)L.q[0] + (size_t)r0 * q_row_bytes(pm, D);
-        g.w_scale = L.qs[0] + (size_t)r0 * q_row_scales(pm, D);
-        g.wq = pm;
-        if (!gemm_mma_q_supported(g)) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised GEMM shape K=%d unsupported", g.K);
-        TRY(launch_gemm_mma_q(ctx, g));
-      } else {
-        g.W = (char*)L.wqkv + (size_t)(qd + which * kvd) * D * m->esz;
-        if (c.bf16) TRY((launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g)));
-        else TRY((launch_gemm_simt<float, float>(ctx, g)));
-      }
-    }
-  }
+  TRY(compute_sinks(m, pm));
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (pm) {
     // linears arrived quantised: the model is now what vn_model_quantize would have left behind
@@ -1010,6 +1021,8 @@ int32_t vn_model_quantize(vn_model* m, const char* scheme) {
   void* head = m->head;
   TRY(quantize_matrix(m, &head, c.vocab, (int)D, mode, &m->head_q, &m->head_qs, false, &bytes));
   if (!c.tie && m->head) { VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); VN_CUDA(ctx, cudaFree(m->head)); m->head = nullptr; }
+  // the sink K / V are what the quantised wk / wv give from here on, as in the reference's compressed model
+  TRY(compute_sinks(m, mode));
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   m->qmode = mode;
   // VN_GEMM_TCQ=0 in the environment: keep the quantised mma.sync GEMMs instead of the tcgen05 ones
@@ -1362,9 +1375,15 @@ int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
       TRY(dev_alloc(ctx, (void**)&m->depth_dev, 64 * 4));
       TRY(dev_alloc(ctx, (void**)&m->anc_dev, 64 * 8));
     }
-    VN_CUDA(ctx, cudaMemcpyAsync(m->depth_dev, depth.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
-    VN_CUDA(ctx, cudaMemcpyAsync(m->anc_dev, anc.data(), T * 8, cudaMemcpyHostToDevice, ctx->stream));
-    VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // the same tree as last time is already on the device: nothing to copy and nothing to wait for, so a forward
+    // over a fixed tree shape can be captured into a CUDA graph once it has run eagerly
+    const std::vector<int> now(parents_host, parents_host + T);
+    if (now != m->tree_parents) {
+      VN_CUDA(ctx, cudaMemcpyAsync(m->depth_dev, depth.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
+      VN_CUDA(ctx, cudaMemcpyAsync(m->anc_dev, anc.data(), T * 8, cudaMemcpyHostToDevice, ctx->stream));
+      VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      m->tree_parents = now;
+    }
   }
   TRY(ensure_rows(m, B * T));
   if (m->cfg.bf16 && m->use_tc && B * T <= 256 && m->cfg.dim % 8 == 0 && m->cfg.dim <= 2048 &&

@@ -90,7 +90,17 @@ class SpecEngine:
                 model.forward_cached(part, cache, want_logits=False, want_hidden=True, last_only=True)
                 cache.commit(n, np.full(B, n, np.int32))
                 done += n
-        self.pair.copy_from_host(prompts[:, -2:])
+        self._prompt_len = T
+        self._prompt_pair = prompts[:, -2:].copy()
+        self.rewind()
+
+    def rewind(self):
+        """Back to the state right after `prefill`: generated tokens are dropped, the prompt's K/V stay in both
+        caches (a sequence's entries behind its length are simply overwritten by the next rounds)."""
+        T = self._prompt_len
+        self.t_cache.set_lengths(np.full(self.B, T - 1, np.int32))
+        self.d_cache.set_lengths(np.full(self.B, T - 2, np.int32))
+        self.pair.copy_from_host(self._prompt_pair)
         for buf in (self.count, self.round_dev):
             self.ctx._check(self.ctx.lib.vn_memset(self.ctx.handle, _ptr(buf), 0, buf.nbytes))
         self.rounds_run = 0
