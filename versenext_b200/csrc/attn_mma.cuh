@@ -43,8 +43,8 @@ template <int MODE>
 __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* __restrict__ Kb,
                                        const __nv_bfloat16* __restrict__ Vb, long long ks, int lo, int hi, int len,
                                        const RowInfo (&row)[2], const unsigned (&qf)[4][4], const int* s_depth,
-                                       int warp, int lane, unsigned char* ring, float (&o)[8][4], float (&m)[2],
-                                       float (&l)[2]) {
+                                       int warp, int nw, int lane, unsigned char* ring, float (&o)[8][4],
+                                       float (&m)[2], float (&l)[2]) {
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int j = 0; j < 8; ++j)
@@ -56,12 +56,13 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
   int pos_max = max(row[0].pos, row[1].pos);     // latest query position of the tile
 #pragma unroll
   for (int o_ = 16; o_ > 0; o_ >>= 1) pos_max = max(pos_max, __shfl_xor_sync(0xffffffffu, pos_max, o_));
-  // This warp's blocks (warp, warp + AW, ...) stream through its own ring of RING stages in shared memory:
+  // `warp` is this warp's index inside the group of `nw` warps that share this key range.
+  // This warp's blocks (warp, warp + nw, ...) stream through its own ring of RING stages in shared memory:
   // 16 key rows of 128 bytes for K, then the same for V, 16-byte chunks XOR-swizzled with the row so that the
   // fragment loads below are free of bank conflicts.  cp.async keeps RING - 1 blocks in flight per warp.
-  const int n_my = nblk > warp ? (nblk - warp + AW - 1) / AW : 0;
+  const int n_my = nblk > warp ? (nblk - warp + nw - 1) / nw : 0;
   auto issue = [&](int it) {
-    const int j0 = lo + (warp + it * AW) * 16;
+    const int j0 = lo + (warp + it * nw) * 16;
     unsigned char* st = ring + (it % RING) * 4096;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -80,7 +81,7 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
     mma_detail::cp_async_commit();
   }
   for (int it = 0; it < n_my; ++it) {
-    const int j0 = lo + (warp + it * AW) * 16;
+    const int j0 = lo + (warp + it * nw) * 16;
     mma_detail::cp_async_wait<RING - 2>();
     __syncwarp();                                  // block `it` has landed; everyone is done with block it - 1
     if (it + RING - 1 < n_my) issue(it + RING - 1);
@@ -199,6 +200,7 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
   extern __shared__ __align__(128) unsigned char attn_smem[];
   __shared__ float sM[AW][16], sL[AW][16];
   __shared__ int s_depth[64];
+  __shared__ __align__(16) float s_q[16 * 64];     // fused mode: the tile's query rows after the split-K sum and RoPE
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
   const int n_rep = a.H / a.n_kv;
@@ -236,6 +238,78 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
   }
   const int hi_new = a.anc ? len + a.Tn : len + tq_max + 1;  // appended slots this tile can see
 
+  const long long ks = (long long)a.n_kv * 64;
+  __nv_bfloat16* Kc = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a.kc)) + ((long long)b * a.max_seq * a.n_kv + kvh) * 64;
+  __nv_bfloat16* Vc = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a.vc)) + ((long long)b * a.max_seq * a.n_kv + kvh) * 64;
+  const __nv_bfloat16* Ks = reinterpret_cast<const __nv_bfloat16*>(a.sink_k) + (long long)kvh * 64;
+  const __nv_bfloat16* Vs = reinterpret_cast<const __nv_bfloat16*>(a.sink_v) + (long long)kvh * 64;
+
+  if (a.partial) {
+    // ---- fused q|k|v finalize: this CTA sums the split-K slices of exactly the columns it needs -- the query rows
+    // of its tile and the new K / V rows of its kv head -- applies RoPE, appends K / V to the cache (every tile of a
+    // (sequence, kv head) writes the same values) and keeps the query rows in shared memory.  Work items are groups
+    // of four feature pairs (j, j + 32): float4 loads from every slice.
+    const long long ld = a.partial_ld;
+    const int half = 32;
+    auto sum4 = [&](long long at) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int sp = 0; sp < a.splits; ++sp) {
+        const float4 v = *reinterpret_cast<const float4*>(a.partial + (long long)sp * a.pstride + at);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      return acc;
+    };
+    auto rot4 = [&](float4& x1, float4& x2, int pos, int j) {
+      if (!a.use_rope) return;
+      const int pp = pos < a.rope_rows ? pos : a.rope_rows - 1;
+      const float4 c = *reinterpret_cast<const float4*>(a.cos_t + (long long)pp * half + j);
+      const float4 sn = *reinterpret_cast<const float4*>(a.sin_t + (long long)pp * half + j);
+      const float4 o1 = make_float4(x1.x * c.x + (-x2.x) * sn.x, x1.y * c.y + (-x2.y) * sn.y,
+                                    x1.z * c.z + (-x2.z) * sn.z, x1.w * c.w + (-x2.w) * sn.w);
+      const float4 o2 = make_float4(x2.x * c.x + x1.x * sn.x, x2.y * c.y + x1.y * sn.y,
+                                    x2.z * c.z + x1.z * sn.z, x2.w * c.w + x1.w * sn.w);
+      x1 = o1; x2 = o2;
+    };
+    const int n_q = 16 * 8, n_k = a.Tn * 8, n_v = a.Tn * 16;
+    for (int it = tid; it < n_q + n_k + n_v; it += AW * 32) {
+      if (it < n_q) {
+        const int rl = it >> 3, j = (it & 7) * 4, r = tile0 + rl;
+        float4 x1 = make_float4(0.f, 0.f, 0.f, 0.f), x2 = x1;
+        if (r < R) {
+          const int tq = r % a.Tn, hrep = r / a.Tn;
+          const long long at = (long long)(b * a.Tn + tq) * ld + (kvh * n_rep + hrep) * 64 + j;
+          x1 = sum4(at); x2 = sum4(at + half);
+          rot4(x1, x2, len + (depth ? depth[tq] : tq), j);
+        }
+        *reinterpret_cast<float4*>(s_q + rl * 64 + j) = x1;
+        *reinterpret_cast<float4*>(s_q + rl * 64 + half + j) = x2;
+      } else if (it < n_q + n_k) {
+        const int i2 = it - n_q, tn = i2 >> 3, j = (i2 & 7) * 4;
+        const int slot = len + tn;
+        if (slot < a.max_seq) {
+          const long long at = (long long)(b * a.Tn + tn) * ld + (a.H + kvh) * 64 + j;
+          float4 x1 = sum4(at), x2 = sum4(at + half);
+          rot4(x1, x2, len + (depth ? depth[tn] : tn), j);
+          __nv_bfloat16* dst = Kc + (long long)slot * ks + j;
+          reinterpret_cast<__nv_bfloat162*>(dst)[0] = __floats2bfloat162_rn(x1.x, x1.y);
+          reinterpret_cast<__nv_bfloat162*>(dst)[1] = __floats2bfloat162_rn(x1.z, x1.w);
+          reinterpret_cast<__nv_bfloat162*>(dst + half)[0] = __floats2bfloat162_rn(x2.x, x2.y);
+          reinterpret_cast<__nv_bfloat162*>(dst + half)[1] = __floats2bfloat162_rn(x2.z, x2.w);
+        }
+      } else {
+        const int i2 = it - n_q - n_k, tn = i2 >> 4, j = (i2 & 15) * 4;
+        const int slot = len + tn;
+        if (slot < a.max_seq) {
+          const float4 x = sum4((long long)(b * a.Tn + tn) * ld + (a.H + a.n_kv + kvh) * 64 + j);
+          __nv_bfloat16* dst = Vc + (long long)slot * ks + j;
+          reinterpret_cast<__nv_bfloat162*>(dst)[0] = __floats2bfloat162_rn(x.x, x.y);
+          reinterpret_cast<__nv_bfloat162*>(dst)[1] = __floats2bfloat162_rn(x.z, x.w);
+        }
+      }
+    }
+    __syncthreads();   // query rows are in shared memory; this CTA's K / V rows are visible to its own later loads
+  }
+
   // Q fragments, dims permuted as described at the top of the file
   unsigned qf[4][4];
 #pragma unroll
@@ -243,7 +317,8 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
     const int r = tile0 + g + 8 * h;
     const int rr = r < R ? r : 0;
     const int tq = rr % a.Tn, hrep = rr / a.Tn;
-    const float* q = a.q + (long long)(b * a.Tn + tq) * a.ld_q + (kvh * n_rep + hrep) * 64 + 16 * t;
+    const float* q = a.partial ? s_q + (g + 8 * h) * 64 + 16 * t
+                               : a.q + (long long)(b * a.Tn + tq) * a.ld_q + (kvh * n_rep + hrep) * 64 + 16 * t;
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
       const float4 v = *reinterpret_cast<const float4*>(q + 4 * s);
@@ -252,12 +327,6 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
     }
   }
 
-  const long long ks = (long long)a.n_kv * 64;
-  const __nv_bfloat16* Kc = reinterpret_cast<const __nv_bfloat16*>(a.kc) + ((long long)b * a.max_seq * a.n_kv + kvh) * 64;
-  const __nv_bfloat16* Vc = reinterpret_cast<const __nv_bfloat16*>(a.vc) + ((long long)b * a.max_seq * a.n_kv + kvh) * 64;
-  const __nv_bfloat16* Ks = reinterpret_cast<const __nv_bfloat16*>(a.sink_k) + (long long)kvh * 64;
-  const __nv_bfloat16* Vs = reinterpret_cast<const __nv_bfloat16*>(a.sink_v) + (long long)kvh * 64;
-
   // final output of this thread after the cross-warp merge: row = tid / 16, dims 4 * (tid % 16) .. +3
   float fin[4] = {0.f, 0.f, 0.f, 0.f};
   const int mrow = tid >> 4, mcol = (tid & 15) * 4;
@@ -265,74 +334,84 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
                      (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max);
   unsigned char* ring = attn_smem + warp * (RING * 4096);
 
-  if (tr && tid == 0) tr[1] = clock_stamp();     // row setup and Q fragments done
-  for (int path = 0; path < 3; ++path) {
-    if (path == 2 && !use_c) break;
-    float o[8][4], m[2], l[2];
-    if (path == 0) {
-      const int lo = max(0, pos_min - a.window + 1);
-      attend<0>(a, Kc, Vc, ks, lo, hi_new, len, row, qf, depth, warp, lane, ring, o, m, l);
-    } else if (path == 1) {
-      attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf, depth, warp, lane, ring, o, m, l);
-    } else {
-      const int lo_c = a.alibi_window > 0 ? max(0, pos_min - a.alibi_window + 1) : 0;
-      attend<2>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, lane, ring, o, m, l);
-    }
-    if (tr && tid == 0 && path < 3) tr[2 + 2 * path] = clock_stamp();   // this warp's keys done
-    // each warp parks its partial result.  Column n of tile j is output dim 8n + j, so thread (g, t) holds dims
-    // 16t .. 16t+15 of rows g and g + 8: four 16-byte chunks per row, chunk c stored at c ^ bit3(c) ^ 2*(row & 1),
-    // which spreads the eight lanes of a quarter warp over all banks for the stores here and the loads below
-    {
-      float4* mine = reinterpret_cast<float4*>(ring);
+  // each warp parks its partial result.  Column n of tile j is output dim 8n + j, so thread (g, t) holds dims
+  // 16t .. 16t+15 of rows g and g + 8: four 16-byte chunks per row, chunk c stored at c ^ bit3(c) ^ 2*(row & 1),
+  // which spreads the eight lanes of a quarter warp over all banks for the stores here and the loads of the merge
+  auto park = [&](const float (&o)[8][4], const float (&m)[2], const float (&l)[2]) {
+    float4* mine = reinterpret_cast<float4*>(ring);
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int r = g + 8 * h;
+    for (int h = 0; h < 2; ++h) {
+      const int r = g + 8 * h;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int c = 4 * t + k, e = 2 * h + (k >> 1), j = (k & 1) * 4;
-          mine[r * 16 + (c ^ ((c >> 3) & 1) ^ ((r & 1) << 1))] = make_float4(o[j][e], o[j + 1][e], o[j + 2][e], o[j + 3][e]);
-        }
+      for (int k = 0; k < 4; ++k) {
+        const int c = 4 * t + k, e = 2 * h + (k >> 1), j = (k & 1) * 4;
+        mine[r * 16 + (c ^ ((c >> 3) & 1) ^ ((r & 1) << 1))] = make_float4(o[j][e], o[j + 1][e], o[j + 2][e], o[j + 3][e]);
       }
     }
     if (t == 0) {
       sM[warp][g] = m[0]; sL[warp][g] = l[0];
       sM[warp][g + 8] = m[1]; sL[warp][g + 8] = l[1];
     }
-    __syncthreads();
-    {
-      float M = -CUDART_INF_F;
-#pragma unroll
-      for (int w = 0; w < AW; ++w) M = fmaxf(M, sM[w][mrow]);
-      float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-      if (M != -CUDART_INF_F) {
-#pragma unroll
-        for (int w = 0; w < AW; ++w) {
-          const float mw = sM[w][mrow];
-          if (mw == -CUDART_INF_F) continue;
-          const float cw = __expf(mw - M);
-          L += sL[w][mrow] * cw;
-          const int c = tid & 15;
-          const float4 v = reinterpret_cast<const float4*>(attn_smem + w * (RING * 4096))[
-              mrow * 16 + (c ^ ((c >> 3) & 1) ^ ((mrow & 1) << 1))];
-          acc[0] += v.x * cw; acc[1] += v.y * cw; acc[2] += v.z * cw; acc[3] += v.w * cw;
-        }
-      }
-      // ALiBi path of a tree node is gated by its own T_k (position + 1 <= 1024)
-      float gate = path == 0 ? a.g_a : (path == 1 ? a.g_b : a.g_c);
-      if (path == 2 && a.anc) {
-        const int r = tile0 + mrow;
-        const int tq = r < R ? r % a.Tn : 0;
-        const int tk = len + (depth ? depth[tq] : tq) + 1;
-        if ((a.alibi_window > 0 ? min(tk, a.alibi_window) : tk) > a.alibi_max) gate = 0.f;
-      }
-      if (L > 0.f) {
-        const float inv = gate / L;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) fin[e] += acc[e] * inv;
+  };
+  // merge of the warps [w0, w1) that shared one path: this thread's four output dims of row mrow, times gate / sum
+  auto merge = [&](int w0, int w1, float gate) {
+    float M = -CUDART_INF_F;
+    for (int w = w0; w < w1; ++w) M = fmaxf(M, sM[w][mrow]);
+    float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (M != -CUDART_INF_F) {
+      for (int w = w0; w < w1; ++w) {
+        const float mw = sM[w][mrow];
+        if (mw == -CUDART_INF_F) continue;
+        const float cw = __expf(mw - M);
+        L += sL[w][mrow] * cw;
+        const int c = tid & 15;
+        const float4 v = reinterpret_cast<const float4*>(attn_smem + w * (RING * 4096))[
+            mrow * 16 + (c ^ ((c >> 3) & 1) ^ ((mrow & 1) << 1))];
+        acc[0] += v.x * cw; acc[1] += v.y * cw; acc[2] += v.z * cw; acc[3] += v.w * cw;
       }
     }
+    if (L > 0.f) {
+      const float inv = gate / L;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) fin[e] += acc[e] * inv;
+    }
+  };
+
+  if (tr && tid == 0) tr[1] = clock_stamp();     // row setup and Q fragments done
+  // ---- window path and sink path side by side: the warps are split between the two key ranges in proportion to
+  // their block counts (each path keeps its own softmax; both are merged in one pass afterwards)
+  {
+    const int lo = max(0, pos_min - a.window + 1);
+    const int nblk_w = hi_new > lo ? (hi_new - lo + 15) >> 4 : 0;
+    const int nblk_s = (a.n_sink + 15) >> 4;
+    int nw = (AW * nblk_w + (nblk_w + nblk_s) / 2) / max(nblk_w + nblk_s, 1);
+    nw = nw < 1 ? 1 : (nw > AW - 1 ? AW - 1 : nw);
+    float o[8][4], m[2], l[2];
+    if (warp < nw) attend<0>(a, Kc, Vc, ks, lo, hi_new, len, row, qf, depth, warp, nw, lane, ring, o, m, l);
+    else attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf, depth, warp - nw, AW - nw, lane, ring, o, m, l);
+    if (tr && tid == 0) tr[2] = clock_stamp();   // this warp's keys done
+    park(o, m, l);
     __syncthreads();
-    if (tr && tid == 0 && path < 2) tr[3 + 2 * path] = clock_stamp();   // merge of this path done
+    merge(0, nw, a.g_a);
+    merge(nw, AW, a.g_b);
+    if (tr && tid == 0) tr[3] = clock_stamp();   // merge done
+  }
+  if (use_c) {
+    __syncthreads();                             // everybody has read the parked tiles
+    float o[8][4], m[2], l[2];
+    const int lo_c = a.alibi_window > 0 ? max(0, pos_min - a.alibi_window + 1) : 0;
+    attend<2>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, AW, lane, ring, o, m, l);
+    park(o, m, l);
+    __syncthreads();
+    // ALiBi path of a tree node is gated by its own T_k (position + 1 <= 1024)
+    float gate = a.g_c;
+    if (a.anc) {
+      const int r = tile0 + mrow;
+      const int tq = r < R ? r % a.Tn : 0;
+      const int tk = len + (depth ? depth[tq] : tq) + 1;
+      if ((a.alibi_window > 0 ? min(tk, a.alibi_window) : tk) > a.alibi_max) gate = 0.f;
+    }
+    merge(0, AW, gate);
   }
   const int r = tile0 + mrow;
   if (r < R) {

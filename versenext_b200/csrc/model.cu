@@ -498,14 +498,6 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     rope.kc = kv->k[li]; rope.vc = kv->v[li]; rope.q_out = m->qkv; rope.ldq = qkv_ld;
     rope.Tn = Tn; rope.H = H; rope.n_kv = n_kv; rope.hd = hd; rope.max_seq = kv->max_seq;
     rope.use_rope = c.use_rope; rope.rope_rows = m->rope_rows; rope.slot_offset = slot_offset;
-    if (fused(g) && gemm_tc_cluster_supported(g, tc_detail::TC_CL_QKV, &rope)) {
-      TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_QKV, nullptr, &rope));
-    } else {
-      TRY(tc_partial(m, g, cap, M, &sp));
-      VN_LAUNCH_PDL_BIT(ctx, 2, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld,
-                    m->qkv, m->rope_cos, m->rope_sin, kv->lens, tree ? m->depth_dev : (const int*)nullptr,
-                    (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
-    }
     AttnArgs a;
     a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[li]; a.vc = kv->v[li]; a.sink_k = L.sink_k; a.sink_v = L.sink_v;
     a.out = m->attn; a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
@@ -516,7 +508,24 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     a.g_b = 1.f / (1.f + expf(-L.gate_logits[1]));
     a.g_c = 1.f / (1.f + expf(-L.gate_logits[2]));
     a.scale = 1.0f / sqrtf((float)hd);
-    if (attn_mma_supported(a, true) && !m->force_simt_attn) {
+    const bool attn_tc = attn_mma_supported(a, true) && !m->force_simt_attn;
+    // the tensor-core attention kernel sums the projection's split-K slices itself (with RoPE and the cache append)
+    // when a tile's CTA has few new rows to reduce; VN_ATTN_FUSE=0 keeps the separate finalize kernel
+    static const bool fuse_on = [] { const char* e = getenv("VN_ATTN_FUSE"); return !(e && e[0] == '0'); }();
+    if (fused(g) && gemm_tc_cluster_supported(g, tc_detail::TC_CL_QKV, &rope)) {
+      TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_QKV, nullptr, &rope));
+    } else {
+      TRY(tc_partial(m, g, cap, M, &sp));
+      if (attn_tc && fuse_on && Tn <= 64 && qkv_ld % 4 == 0) {
+        a.partial = m->partial; a.splits = sp; a.pstride = (long long)M * qkv_ld; a.partial_ld = qkv_ld;
+        a.cos_t = m->rope_cos; a.sin_t = m->rope_sin; a.use_rope = c.use_rope; a.rope_rows = m->rope_rows;
+      } else {
+        VN_LAUNCH_PDL_BIT(ctx, 2, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld,
+                      m->qkv, m->rope_cos, m->rope_sin, kv->lens, tree ? m->depth_dev : (const int*)nullptr,
+                      (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
+      }
+    }
+    if (attn_tc) {
       TRY(launch_attn_mma(ctx, a, B));
     } else {
       dim3 grid(ceil_div(H, 8), M);

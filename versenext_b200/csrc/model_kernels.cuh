@@ -172,6 +172,15 @@ struct AttnArgs {
   float g_a, g_b, g_c;   // sigmoid(gate_logits)
   float scale;
   long long* trace = nullptr;   // optional [CTAs][8] cycle stamps of the tensor-core kernel's phases
+  // Tensor-core kernel only, fused q|k|v finalize: when `partial` is set, q / k / v of the new positions are still
+  // split-K slices [splits][rows][partial_ld] of the projection; the attention CTA sums the columns it needs,
+  // applies RoPE and appends K / V to the cache itself (q is then not read from `q`).
+  const float* partial = nullptr;
+  int splits = 0;
+  long long pstride = 0, partial_ld = 0;
+  const float* cos_t = nullptr;
+  const float* sin_t = nullptr;
+  int use_rope = 0, rope_rows = 0;
 };
 
 // online-softmax state of one 8-lane group: running max, running sum, 8 output dims per lane
