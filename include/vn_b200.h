@@ -178,6 +178,13 @@ int32_t vn_accept_noalloc(vn_ctx* ctx, const float* p_logits_dev, const float* q
 int32_t vn_sample(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, float temperature,
                   int32_t top_k, const float* uniforms_dev, uint64_t seed, uint32_t offset, uint32_t position,
                   uint32_t purpose, int64_t* out_tokens_dev);
+/* vn_sample that also leaves every row's kept list -- the (token, scaled logit) pairs at or above the k-th largest
+ * value, ascending token id -- in lists_out_dev ([R] records of vn_topk_row_bytes() bytes each, or NULL): a draft
+ * model samples its proposal from that list, and vn_verify_accept later needs the very same list as q. */
+int32_t vn_sample_lists(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, float temperature,
+                        int32_t top_k, const float* uniforms_dev, uint64_t seed, uint32_t offset, uint32_t position,
+                        uint32_t purpose, int64_t* out_tokens_dev, void* lists_out_dev);
+size_t vn_topk_row_bytes(void);
 /* Philox uniforms exactly as vn_accept draws them (for tests) */
 int32_t vn_philox_uniform(vn_ctx* ctx, uint64_t seed, uint32_t offset, int32_t B, int32_t n,
                           int32_t purpose, float* out_dev);
@@ -260,6 +267,28 @@ int32_t vn_kv_read(vn_kv* kv, int32_t layer, int32_t seq, int32_t which /*0=k 1=
 int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int32_t B, int32_t T,
                          const int32_t* parents_host, float* out_hidden_dev, float* out_logits_dev,
                          int32_t last_only, int32_t slot_offset);
+
+/* Verify + accept in one call: the target forward over the T = k (+1 with bonus) new positions of every sequence
+ * (tokens_dev [B, T]: last committed token, then the proposals), the LM head, and the acceptance rule of vn_accept
+ * -- replaces head(x) (cometspark.py:690-697), the softmax / top-k (cometspark.py:892-911) and the compare
+ * (speculative.py:216-223) of one verification round.  With temperature > 0 and 0 < top_k < vocab on a bf16 model
+ * the head is FUSED with the selection: a GEMM over the first 8,192 vocabulary columns bounds every row's k-th
+ * largest logit from below, the full head GEMM's epilogue keeps only the logits at or above that bound (a few
+ * hundred per row), and the decisions are taken on those lists -- the [B, T, V] logits are never written.  Results
+ * are those of vn_model_forward + vn_accept_strided bit for bit.  p_logits_scratch_dev [B, T, V] must be supplied:
+ * it is written only when a row has so many ties at its bound that its candidate list (4,096 entries) overflows
+ * -- a device flag then switches the stored-logits path on inside the same launch sequence -- and whenever the
+ * fused head does not apply (greedy or full-vocabulary rule, fp32 or quantised model), where this call is the
+ * forward followed by vn_accept_strided.
+ *   q of the draft rows: q_lists_dev (records left by vn_sample_lists; row (b, i) at record b * ql_stride_b +
+ *   i * ql_stride_i) and / or q_logits_dev with element strides as in vn_accept_strided (the fused head prefers
+ *   the lists, the stored-logits route needs the logits), or both NULL (point-mass proposals).  Uniforms, seed, offset, outputs: as vn_accept.  Appends K/V like vn_model_forward: commit with
+ *   vn_kv_commit. */
+int32_t vn_verify_accept(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int32_t B, int32_t T, int32_t k,
+                         const void* q_lists_dev, int64_t ql_stride_b, int64_t ql_stride_i, const float* q_logits_dev,
+                         int64_t q_stride_b, int64_t q_stride_i, const int64_t* draft_dev, const float* u_accept_dev,
+                         const float* u_sample_dev, uint64_t seed, uint32_t offset, float temperature, int32_t top_k,
+                         int32_t bonus, float* p_logits_scratch_dev, int32_t* out_len_dev, int64_t* out_tokens_dev);
 
 /* ---- round bookkeeping on the device (no counterpart in the reference: its loop is host code,
  *      speculative.py:280-293) -------------------------------------------------------------------- */

@@ -78,6 +78,10 @@ PROTOTYPES = {
     "vn_accept_noalloc": [_p, _p, _p, _p, _p, _p, _u64, _u32, _f32, _i32, _i32, _i32, _i32, _p, _p],
     "vn_philox_uniform": [_p, _u64, _u32, _i32, _i32, _i32, _p],
     "vn_sample": [_p, _p, _i64, _i32, _i32, _f32, _i32, _p, _u64, _u32, _u32, _u32, _p],
+    "vn_sample_lists": [_p, _p, _i64, _i32, _i32, _f32, _i32, _p, _u64, _u32, _u32, _u32, _p, _p],
+    "vn_topk_row_bytes": [],
+    "vn_verify_accept": [_p, _p, _p, _i32, _i32, _i32, _p, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _u64, _u32, _f32,
+                         _i32, _i32, _p, _p, _p],
     "vn_spec_gather": [_p, _p, _p, _i32, _i32, _i32, _p, _p],
     "vn_spec_advance": [_p, _p, _i32, _i32, _p, _p, _i32, _p, _p],
     "vn_set_offset_source": [_p, _p],
@@ -109,7 +113,7 @@ PROTOTYPES = {
     "vn_kv_read": [_p, _i32, _i32, _i32, _p, _i32],
     "vn_model_forward": [_p, _p, _p, _i32, _i32, _p, _p, _p, _i32, _i32],
 }
-_RESTYPE = {"vn_last_error": C.c_char_p}
+_RESTYPE = {"vn_last_error": C.c_char_p, "vn_topk_row_bytes": C.c_size_t}
 
 _lib = None
 

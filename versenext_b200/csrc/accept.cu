@@ -13,11 +13,17 @@
 //
 // Top-k path: accept_topk_kernel reduces every row to its (token, scaled logit) list of the
 // entries >= the k-th largest value (bound pass + rank counting, radix select as the fallback), the
-// slices of a row are merged, and the same rule is applied on those short lists: three launches.  Opt-in
-// (VN_TOPK_FUSE=1) the three steps run in one launch: the CTA that takes a row's last arrival ticket merges it,
-// the CTA that takes a sequence's last ticket decides it, with the same code as the separate kernels.
+// slices of a row are merged, and the same rule is applied on those short lists: three launches.
+//
+// Fused LM head (vn_k1_*, driven by vn_verify_accept): the target's logits never reach HBM.  A small GEMM over the
+// first columns of the head gives every row a lower bound of its k-th largest logit (k1_bound_kernel), the full
+// head GEMM's epilogue appends the logits at or above it to per-row candidate lists, k1_finish_kernel turns a
+// candidate list into the same kept list the select above produces, and the decision kernel runs unchanged.  If a
+// candidate list overflows (heavy ties), a device flag switches on the classic path inside the same launch
+// sequence: its kernels return at once while the flag is clear.
 #include <stdlib.h>
 #include "common.cuh"
+#include "k1.h"
 #include <math_constants.h>
 
 namespace {
@@ -505,6 +511,10 @@ static_assert(sizeof(TopkRow) % 128 == 0, "TopkRow must cover whole cache lines"
 // what the decision step needs besides the lists
 struct DecideArgs {
   int B, k, np, nq;
+  // kept lists: row j < np of sequence b at p_rows[b * p_sb + j], draft row i at q_rows[b * q_sb + i * q_si]
+  const TopkRow* p_rows;
+  const TopkRow* q_rows;
+  long long p_sb, q_sb, q_si;
   const long long* draft;
   const float* u_acc;
   const float* u_smp;
@@ -516,23 +526,18 @@ struct DecideArgs {
   long long* out_tok;
 };
 
-// merge + decision code shared by the fused tail of accept_topk_kernel and the standalone kernels
-__device__ void topk_merge_rows(const TopkRow* pr, int chunks, int top_k, TopkRow* o, float* s_val, int* s_tok,
-                                int* s_off, int* s_n, float* s_kth, int* s_cnt);
 constexpr int DEC_ROWS = 16, DEC_ENT = 64;
-__device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& da, const TopkRow* rows,
-                                             int (*s_tok)[DEC_ENT], float (*s_val)[DEC_ENT], int* s_n);
 
 // One CTA per row.  Radix select (11 + 11 + 10 bits) of the k-th largest key.  After each level
 // the number of keys that can still be kept is known from the histogram; as soon as they fit in
 // shared memory they are gathered (one more read of the row) and the select finishes there.
-// (two CTAs per SM: the select loops need 32 registers; the decision code of the fused tail, which one warp of a
-// few CTAs runs once, is kept out of line and may spill)
+// `out_sb`: list of slice c of row j of sequence b goes to out[(b * out_sb + j) * chunks + c] (lets the rows of a
+// call land inside a larger per-sequence array).  `run_if`: see the GEMM's TcArgs::run_if.
 __global__ void __launch_bounds__(1024, 2)
-accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, TopkRow* merged, int* tickets,
-                   DecideArgs da) {
+accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, long long out_sb, const int* run_if) {
   pdl_trigger();
   pdl_wait();
+  if (run_if && *reinterpret_cast<const volatile int*>(run_if) == 0) return;
   // blockIdx.x = row * chunks + chunk: every CTA selects inside its own slice of the row; the slices'
   // lists are merged by accept_topk_merge_kernel (the row's k largest are among the slices' k largest)
   const int rows_per_seq = rs.np + rs.nq;
@@ -543,9 +548,8 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, T
   const int V = max(0, min(slice, rs.V - base0)), tid = threadIdx.x, nt = blockDim.x;
   const bool scale = temp != 1.0f;
   const int want = top_k < V ? top_k : V;
-  // one pool, used in turn by the select (histogram + candidates, 16 KB), the merge of a row's slices (32 KB) and
-  // the decision step (8 KB)
-  __shared__ __align__(16) unsigned char s_pool[32768];
+  // histogram + candidates (16 KB)
+  __shared__ __align__(16) unsigned char s_pool[16384];
   uint32_t* hist = reinterpret_cast<uint32_t*>(s_pool);                   // [2048]
   uint32_t* c_key = reinterpret_cast<uint32_t*>(s_pool + 8192);           // [CAND_MAX]
   int* c_tok = reinterpret_cast<int*>(s_pool + 12288);                    // [CAND_MAX]
@@ -723,7 +727,7 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, T
       have = true;
     }
   }
-  TopkRow* o = out + blockIdx.x;
+  TopkRow* o = out + ((long long)(r / rows_per_seq) * out_sb + (r % rows_per_seq)) * chunks + chunk;
   if (have) {
     const int nc = min(s_ncand, CAND_MAX);
     // exact k-th largest among the candidates by rank counting (nc is small)
@@ -770,44 +774,6 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, T
       __syncthreads();
     }
     if (tid == 0) { o->n = min(s_base, KEEP_MAX); o->overflow = s_base > KEEP_MAX; }
-  }
-  if (!tickets) return;        // unfused: the merge and decision kernels follow in the stream
-  // ---- fused tail: the CTA that finishes a row's last slice merges the row; the CTA that finishes a sequence's
-  // last row takes the sequence's decisions.  Arrival counters (release: fence before the ticket; acquire: fence
-  // after it), no waiting anywhere; the last arrival sets the counter back to zero for the next launch.
-  __shared__ int s_last;
-  const int n_rows = gridDim.x / chunks;
-  if (chunks > 1) {
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const int last = atomicAdd(&tickets[r], 1) == chunks - 1;
-      if (last) tickets[r] = 0;
-      s_last = last;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    __shared__ int s_off[65], s_n[64], s_cnt;
-    __shared__ float s_kthf;
-    topk_merge_rows(out + (long long)r * chunks, chunks, top_k, merged + r, reinterpret_cast<float*>(s_pool),
-                    reinterpret_cast<int*>(s_pool + 16384), s_off, s_n, &s_kthf, &s_cnt);
-  }
-  const int b = r / rows_per_seq;
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int last = atomicAdd(&tickets[n_rows + b], 1) == rows_per_seq - 1;
-    if (last) tickets[n_rows + b] = 0;
-    s_last = last;
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  if (tid < 32) {
-    __shared__ int s_dn[DEC_ROWS];
-    topk_decide_seq(b, tid, da, merged, reinterpret_cast<int(*)[DEC_ENT]>(s_pool),
-                    reinterpret_cast<float(*)[DEC_ENT]>(s_pool + DEC_ROWS * DEC_ENT * 4), s_dn);
   }
 }
 
@@ -857,16 +823,20 @@ __device__ void topk_merge_rows(const TopkRow* pr, int chunks, int top_k, TopkRo
   if (tid == 0) { o->n = min(*s_cnt, KEEP_MAX); o->overflow = *s_cnt > KEEP_MAX; }
 }
 
+// parts: [rows][chunks] in row order; row r = (sequence r / rps, row r % rps) goes to out[(r / rps) * out_sb + r % rps]
 __global__ void __launch_bounds__(1024)
-accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_k, TopkRow* __restrict__ out) {
+accept_topk_merge_kernel(const TopkRow* __restrict__ parts, int chunks, int top_k, TopkRow* __restrict__ out, int rps,
+                         long long out_sb, const int* run_if) {
   pdl_trigger();
   pdl_wait();
+  if (run_if && *reinterpret_cast<const volatile int*>(run_if) == 0) return;
   __shared__ float s_val[4096];
   __shared__ int s_tok[4096];
   __shared__ int s_off[65], s_n[64], s_cnt;
   __shared__ float s_kth;
   const int r = blockIdx.x;
-  topk_merge_rows(parts + (long long)r * chunks, chunks, top_k, out + r, s_val, s_tok, s_off, s_n, &s_kth, &s_cnt);
+  topk_merge_rows(parts + (long long)r * chunks, chunks, top_k, out + (long long)(r / rps) * out_sb + r % rps, s_val, s_tok,
+                  s_off, s_n, &s_kth, &s_cnt);
 }
 
 // ---- warp-cooperative helpers on a kept list ------------------------------------------------------------
@@ -909,7 +879,7 @@ __device__ __forceinline__ float list_find(const ListView& r, int token) {
 
 // One warp per sequence: acceptance tests, then the inverse CDF over the kept list of the row to sample.
 // s_tok / s_val / s_n: this warp's staging arrays in shared memory.
-__device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& da, const TopkRow* rows,
+__device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& da,
                                              int (*s_tok)[DEC_ENT], float (*s_val)[DEC_ENT], int* s_n) {
   const int k = da.k, np = da.np, nq = da.nq, bonus = da.bonus, smp_purpose = da.smp_purpose, pos_base = da.pos_base;
   const long long* draft = da.draft;
@@ -920,13 +890,15 @@ __device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& 
   long long* out_tok = da.out_tok;
   const uint32_t offset = da.offset_host + (da.offset_dev ? *da.offset_dev : 0u);
   const int rows_per_seq = np + nq;
-  const TopkRow* rb = rows + (long long)b * rows_per_seq;
+  auto rowp = [&](int r) -> const TopkRow* {
+    return r < np ? da.p_rows + (long long)b * da.p_sb + r : da.q_rows + (long long)b * da.q_sb + (long long)(r - np) * da.q_si;
+  };
   // The lists of this sequence are read many times below, each read a dependent round trip to L2: copy them
   // into shared memory first when they fit (at most DEC_ROWS rows of DEC_ENT entries, the usual case).
   bool staged = rows_per_seq <= DEC_ROWS;
   if (staged) {
     int nmax = 0;
-    for (int r = lane; r < rows_per_seq; r += 32) { const int nr = rb[r].n; s_n[r] = nr; nmax = max(nmax, nr); }
+    for (int r = lane; r < rows_per_seq; r += 32) { const int nr = rowp(r)->n; s_n[r] = nr; nmax = max(nmax, nr); }
     __syncwarp();
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
@@ -935,15 +907,16 @@ __device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& 
   if (staged) {
     for (int idx = lane; idx < rows_per_seq * DEC_ENT; idx += 32) {
       const int r = idx / DEC_ENT, i = idx % DEC_ENT;
-      if (i < s_n[r]) { s_tok[r][i] = rb[r].tok[i]; s_val[r][i] = rb[r].val[i]; }
+      if (i < s_n[r]) { const TopkRow* rp = rowp(r); s_tok[r][i] = rp->tok[i]; s_val[r][i] = rp->val[i]; }
     }
     __syncwarp();
   }
   auto view = [&](int r) {
     ListView v;
-    v.n = staged ? s_n[r] : rb[r].n;
-    v.tok = staged ? s_tok[r] : rb[r].tok;
-    v.val = staged ? s_val[r] : rb[r].val;
+    const TopkRow* rp = rowp(r);
+    v.n = staged ? s_n[r] : rp->n;
+    v.tok = staged ? s_tok[r] : rp->tok;
+    v.val = staged ? s_val[r] : rp->val;
     return v;
   };
   long long* tok = out_tok + (long long)b * (k + 1);
@@ -1056,7 +1029,7 @@ __device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& 
 
 
 __global__ void __launch_bounds__(128)
-accept_topk_decide_kernel(DecideArgs da, const TopkRow* __restrict__ rows) {
+accept_topk_decide_kernel(DecideArgs da) {
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, wslot = threadIdx.x >> 5;
@@ -1065,16 +1038,136 @@ accept_topk_decide_kernel(DecideArgs da, const TopkRow* __restrict__ rows) {
   __shared__ int s_tok[4][DEC_ROWS][DEC_ENT];
   __shared__ float s_val[4][DEC_ROWS][DEC_ENT];
   __shared__ int s_n[4][DEC_ROWS];
-  topk_decide_seq(b, lane, da, rows, s_tok[wslot], s_val[wslot], s_n[wslot]);
+  topk_decide_seq(b, lane, da, s_tok[wslot], s_val[wslot], s_n[wslot]);
+}
+
+
+// ---- fused LM head: bound, finish ---------------------------------------------------------------------------
+// Descending bitonic sort of N (a power of two) 64-bit keys in shared memory by all threads of the CTA.
+template <typename K>
+__device__ void bitonic_sort_desc(K* a, int N) {
+  const int tid = threadIdx.x, nt = blockDim.x;
+  for (int k = 2; k <= N; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = tid; i < N; i += nt) {
+        const int ixj = i ^ j;
+        if (ixj > i) {
+          const K x = a[i], y = a[ixj];
+          const bool desc = (i & k) == 0;
+          if (desc ? x < y : x > y) { a[i] = y; a[ixj] = x; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// One CTA per target row: the k-th largest of the row's first nb logits is a lower bound of the k-th largest of
+// the whole row (a subset's k-th largest never exceeds the full set's).  The bound handed to the GEMM epilogue is
+// the SMALLEST raw logit whose temperature-scaled value reaches the scaled bound, so that a logit whose quotient
+// ties with the k-th value after rounding is still collected.  Also clears the row's candidate counter and the
+// call's fallback flag.
+__global__ void __launch_bounds__(1024)
+k1_bound_kernel(const float* __restrict__ boot, int nb, int top_k, float temp, float* __restrict__ tau,
+                int* __restrict__ count, int* __restrict__ fallback) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ uint32_t keys[8192];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  int N = 64;
+  while (N < nb) N <<= 1;
+  const float* src = boot + (long long)row * nb;
+  for (int i = tid; i < N; i += blockDim.x) keys[i] = i < nb ? order_key(src[i]) : 0u;
+  __syncthreads();
+  bitonic_sort_desc(keys, N);
+  if (tid == 0) {
+    float t = -CUDART_INF_F;
+    if (top_k <= nb) {
+      const float xk = key_value(keys[top_k - 1]);
+      t = xk;
+      if (temp != 1.0f && xk == xk && fabsf(xk) != CUDART_INF_F) {
+        const float sk = __fdiv_rn(xk, temp);
+        int it = 0;
+        while (it < 64 && next_down(t) != t && __fdiv_rn(next_down(t), temp) >= sk) { t = next_down(t); ++it; }
+        if (it >= 64) t = -CUDART_INF_F;      // could not pin the edge down: collect everything, the overflow path decides
+      } else if (xk != xk) {
+        t = -CUDART_INF_F;
+      }
+    }
+    tau[row] = t;
+    count[row] = 0;
+    if (row == 0) *fallback = 0;
+  }
+}
+
+// One CTA per target row: candidates (raw logit, token) -> the kept list the select kernel would have produced:
+// every entry whose scaled value is >= the k-th largest scaled value, ascending token id.  A list that ran past
+// its capacity, or more than KEEP_MAX kept entries, raises the fallback flag instead.
+__global__ void __launch_bounds__(1024)
+k1_finish_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_tok, const int* __restrict__ count,
+                 int cap, int top_k, float temp, int V, TopkRow* __restrict__ out, int* __restrict__ fallback) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ unsigned long long comp[VN_K1_CAP];
+  __shared__ int s_keep;
+  const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+  const int n = count[row];
+  const int want = top_k < V ? top_k : V;
+  TopkRow* o = out + row;
+  if (n > cap || n < want) {                 // uniform over the CTA
+    if (tid == 0) { atomicExch(fallback, 1); o->n = 0; o->overflow = 1; }
+    return;
+  }
+  int N = 64;
+  while (N < n) N <<= 1;
+  const bool scale = temp != 1.0f;
+  const float* cv = cand_val + (long long)row * cap;
+  const int* ct = cand_tok + (long long)row * cap;
+  for (int i = tid; i < N; i += nt) {
+    unsigned long long c = 0ull;
+    if (i < n) {
+      const float x = cv[i];
+      const uint32_t key = order_key(scale ? __fdiv_rn(x, temp) : x);
+      c = ((unsigned long long)key << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)ct[i]);
+    }
+    comp[i] = c;
+  }
+  if (tid == 0) s_keep = 0;
+  __syncthreads();
+  bitonic_sort_desc(comp, N);
+  const uint32_t kth = (uint32_t)(comp[want - 1] >> 32);
+  // kept entries are the sorted prefix with key >= kth: its length is the index of the first smaller key
+  for (int i = tid; i < n; i += nt) {
+    const bool in = (uint32_t)(comp[i] >> 32) >= kth;
+    const bool next_in = i + 1 < n && (uint32_t)(comp[i + 1] >> 32) >= kth;
+    if (in && !next_in) s_keep = i + 1;
+  }
+  __syncthreads();
+  const int keep = s_keep;
+  if (keep > KEEP_MAX) {
+    if (tid == 0) { atomicExch(fallback, 1); o->n = 0; o->overflow = 1; }
+    return;
+  }
+  // ascending token id: rank of each kept entry among the kept ones (a few dozen entries as a rule)
+  for (int i = tid; i < keep; i += nt) {
+    const uint32_t ti = 0xFFFFFFFFu - (uint32_t)comp[i];
+    int pos = 0;
+    for (int j = 0; j < keep; ++j) pos += (0xFFFFFFFFu - (uint32_t)comp[j]) < ti;
+    o->tok[pos] = (int)ti;
+    o->val[pos] = key_value((uint32_t)(comp[i] >> 32));
+  }
+  if (tid == 0) { o->n = keep; o->overflow = 0; }
 }
 
 }  // namespace
 
+// lists_out (top-k path only): the kept lists of the p rows are left there ([B][np] records) for a later call
 int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_si,
                            const float* q, long long q_sb, long long q_si, const int64_t* draft,
                            const float* u_acc, const float* u_smp, uint64_t seed, uint32_t offset,
                            float temperature, int32_t top_k, int32_t bonus, int32_t B, int32_t k, int32_t V,
-                           int32_t* out_len, int64_t* out_tok, int32_t smp_purpose, int32_t pos_base) {
+                           int32_t* out_len, int64_t* out_tok, int32_t smp_purpose, int32_t pos_base,
+                           void* lists_out) {
   VN_CHECK_CTX(ctx);
   VN_REQUIRE(ctx, B >= 0 && k >= 0 && k <= MAX_K && V >= 1, "bad sizes B=%d k=%d V=%d (k <= %d)", B, k, V, MAX_K);
   VN_REQUIRE(ctx, p && out_tok, "null pointer");
@@ -1107,26 +1200,28 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
     void* ws;
     int32_t st = vn_workspace(ctx, sizeof(TopkRow) * (size_t)n_rows * (chunks + 1), &ws);
     if (st) return st;
-    TopkRow* rows = (TopkRow*)ws;                 // merged lists [n_rows]
+    TopkRow* rows = (TopkRow*)ws;                 // merged lists [B][rows_per_seq]
     TopkRow* parts = rows + n_rows;               // per-slice lists [n_rows * chunks]
+    long long out_sb = rows_per_seq;
+    if (lists_out) {
+      VN_REQUIRE(ctx, rs.nq == 0, "kept lists can only be handed out for calls without draft rows");
+      rows = (TopkRow*)lists_out;
+      out_sb = rs.np;
+    }
     DecideArgs da;
     da.B = B; da.k = k; da.np = rs.np; da.nq = rs.nq; da.draft = d64; da.u_acc = u_acc; da.u_smp = u_smp;
     da.seed = seed; da.offset_host = offset; da.offset_dev = ctx->offset_src; da.bonus = bonus;
     da.smp_purpose = smp_purpose; da.pos_base = pos_base; da.out_len = out_len; da.out_tok = o64;
-    // VN_TOPK_FUSE=1 (read on every call): one launch, in which the CTA that completes a row merges its slices and
-    // the CTA that completes a sequence decides it (arrival counters, nothing waits).  Measured on B200 the round
-    // is no faster than with the three kernels in stream order (2.44 against 2.43 ms: the tail CTAs run the merge
-    // and the single-warp decision while holding half an SM each), so the three launches stay the default.
-    const char* fuse_env = getenv("VN_TOPK_FUSE");
-    const bool fuse_on = fuse_env && fuse_env[0] == '1';
-    int* tickets = nullptr;
-    if (fuse_on && (long long)n_rows + B <= VN_TICKETS) { st = vn_tickets(ctx, &tickets); if (st) return st; }
-    VN_LAUNCH_PDL_BIT(ctx, 64, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, chunks > 1 ? parts : rows,
-                  rows, tickets, da);
-    if (!tickets) {
-      if (chunks > 1) VN_LAUNCH_PDL_BIT(ctx, 128, accept_topk_merge_kernel, n_rows, 1024, 0, parts, chunks, top_k, rows);
-      VN_LAUNCH_PDL_BIT(ctx, 256, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, da, rows);
+    da.p_rows = rows; da.p_sb = out_sb; da.q_rows = rows + rs.np; da.q_sb = out_sb; da.q_si = 1;
+    if (chunks > 1) {
+      VN_LAUNCH_PDL_BIT(ctx, 64, accept_topk_kernel, n_rows * chunks, 1024, 0, rs, top_k, temp, chunks, parts,
+                        (long long)rows_per_seq, (const int*)nullptr);
+      VN_LAUNCH_PDL_BIT(ctx, 128, accept_topk_merge_kernel, n_rows, 1024, 0, parts, chunks, top_k, rows, rows_per_seq, out_sb,
+                        (const int*)nullptr);
+    } else {
+      VN_LAUNCH_PDL_BIT(ctx, 64, accept_topk_kernel, n_rows, 1024, 0, rs, top_k, temp, 1, rows, out_sb, (const int*)nullptr);
     }
+    VN_LAUNCH_PDL_BIT(ctx, 256, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, da);
     return VN_OK;
   }
 
@@ -1249,6 +1344,95 @@ static int32_t row_residual_chunks(vn_ctx* ctx, const RowSet& rs, bool vec, int 
   return VN_OK;
 }
 
+size_t vn_topk_row_bytes_impl() { return sizeof(TopkRow); }
+
+int32_t vn_k1_layout(vn_ctx* ctx, int B, int np, int top_k, int V, vn_k1* out) {
+  static const int boot_cols = [] { const char* e = getenv("VN_K1_BOOT"); return e ? std::max(256, std::min(8192, atoi(e))) : 8192; }();
+  vn_k1 k;
+  k.rows = B * np;
+  k.cap = VN_K1_CAP;
+  k.nb = std::min(V, boot_cols) & ~127;          // whole 128-column tiles of the head
+  if (k.nb < 128) k.nb = std::min(V, 128);
+  static const double topk_ctas_per_sm = [] { const char* e = getenv("VN_TOPK_CTAS_PER_SM"); return e ? std::max(0.05, atof(e)) : 0.75; }();
+  const int cta_target = std::max(1, (int)(topk_ctas_per_sm * ctx->sm_count + 0.5));
+  int chunks = std::min(std::min(16, std::max(1, V / 8192)), std::max(1, ceil_div(cta_target, std::max(k.rows, 1))));
+  k.chunks = std::max(1, std::min(chunks, 2048 / std::max(top_k, 1)));
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t o_boot = 0;
+  const size_t o_tau = up(o_boot + (size_t)k.rows * k.nb * 4);
+  const size_t o_cnt = up(o_tau + (size_t)k.rows * 4);
+  const size_t o_flag = up(o_cnt + (size_t)k.rows * 4);
+  const size_t o_val = up(o_flag + 256);
+  const size_t o_tok = up(o_val + (size_t)k.rows * k.cap * 4);
+  const size_t o_lists = up(o_tok + (size_t)k.rows * k.cap * 4);
+  const size_t o_parts = up(o_lists + (size_t)k.rows * sizeof(TopkRow));
+  const size_t total = o_parts + (size_t)k.rows * k.chunks * sizeof(TopkRow);
+  void* ws;
+  int32_t st = vn_workspace(ctx, total, &ws);
+  if (st) return st;
+  char* base = (char*)ws;
+  k.boot = (float*)(base + o_boot); k.tau = (float*)(base + o_tau); k.count = (int*)(base + o_cnt);
+  k.fallback = (int*)(base + o_flag); k.cand_val = (float*)(base + o_val); k.cand_tok = (int*)(base + o_tok);
+  k.p_lists = base + o_lists; k.parts = base + o_parts;
+  *out = k;
+  return VN_OK;
+}
+
+int32_t vn_k1_bound(vn_ctx* ctx, const vn_k1& k1, int top_k, float temp) {
+  VN_REQUIRE(ctx, k1.nb <= 8192 && top_k >= 1, "bound GEMM wider than the bound kernel sorts");
+  VN_LAUNCH_PDL(ctx, k1_bound_kernel, k1.rows, 1024, 0, (const float*)k1.boot, k1.nb, top_k, temp, k1.tau, k1.count,
+                k1.fallback);
+  return VN_OK;
+}
+
+int32_t vn_k1_accept(vn_ctx* ctx, const vn_k1& k1, const float* p_fallback, long long p_sb, long long p_si,
+                     const void* q_lists, long long ql_sb, long long ql_si, const float* q_logits, long long q_sb,
+                     long long q_si, const int64_t* draft, const float* u_acc, const float* u_smp, uint64_t seed,
+                     uint32_t offset, float temperature, int32_t top_k, int32_t bonus, int32_t B, int32_t k, int32_t V,
+                     int32_t* out_len, int64_t* out_tok) {
+  VN_REQUIRE(ctx, temperature > 0.f && top_k >= 1 && top_k <= KEEP_MAX && top_k < V, "the fused head needs temperature > 0 and 0 < top_k < V");
+  VN_REQUIRE(ctx, k >= 0 && k <= MAX_K && B >= 1 && out_tok, "bad arguments");
+  const float temp = fmaxf(temperature, 1e-8f);
+  const int np = bonus ? k + 1 : k;
+  VN_REQUIRE(ctx, k1.rows == B * np, "candidate buffers were laid out for another shape");
+  TopkRow* p_rows = (TopkRow*)k1.p_lists;
+  VN_LAUNCH_PDL(ctx, k1_finish_kernel, k1.rows, 1024, 0, (const float*)k1.cand_val, (const int*)k1.cand_tok,
+                (const int*)k1.count, k1.cap, top_k, temp, V, p_rows, k1.fallback);
+  if (p_fallback) {
+    // classic select on the stored logits, only when the flag is up (its kernels return at once otherwise)
+    RowSet rs;
+    rs.p = p_fallback; rs.q = nullptr; rs.p_sb = p_sb; rs.p_si = p_si; rs.q_sb = 0; rs.q_si = 0; rs.np = np; rs.nq = 0; rs.V = V;
+    if (k1.chunks > 1) {
+      VN_LAUNCH_PDL(ctx, accept_topk_kernel, k1.rows * k1.chunks, 1024, 0, rs, top_k, temp, k1.chunks, (TopkRow*)k1.parts,
+                    (long long)np, (const int*)k1.fallback);
+      VN_LAUNCH_PDL(ctx, accept_topk_merge_kernel, k1.rows, 1024, 0, (const TopkRow*)k1.parts, k1.chunks, top_k, p_rows, np,
+                    (long long)np, (const int*)k1.fallback);
+    } else {
+      VN_LAUNCH_PDL(ctx, accept_topk_kernel, k1.rows, 1024, 0, rs, top_k, temp, 1, p_rows, (long long)np, (const int*)k1.fallback);
+    }
+  }
+  DecideArgs da;
+  da.B = B; da.k = k; da.np = np; da.nq = 0; da.draft = reinterpret_cast<const long long*>(draft);
+  da.u_acc = u_acc; da.u_smp = u_smp; da.seed = seed; da.offset_host = offset; da.offset_dev = ctx->offset_src;
+  da.bonus = bonus; da.smp_purpose = 1; da.pos_base = 0; da.out_len = out_len;
+  da.out_tok = reinterpret_cast<long long*>(out_tok);
+  da.p_rows = p_rows; da.p_sb = np; da.q_rows = nullptr; da.q_sb = 0; da.q_si = 0;
+  if (k > 0 && q_lists) {
+    da.nq = k; da.q_rows = (const TopkRow*)q_lists; da.q_sb = ql_sb; da.q_si = ql_si;
+  } else if (k > 0 && q_logits) {
+    // the draft rows' lists are selected here from their logits, into the slice-list region: the classic select of
+    // the target rows (when it runs at all) has finished with that region by then (stream order)
+    VN_REQUIRE(ctx, (size_t)B * k <= (size_t)k1.rows * k1.chunks, "no room for the draft rows' lists");
+    TopkRow* q_rows = (TopkRow*)k1.parts;
+    RowSet rs;
+    rs.p = q_logits; rs.q = nullptr; rs.p_sb = q_sb; rs.p_si = q_si; rs.q_sb = 0; rs.q_si = 0; rs.np = k; rs.nq = 0; rs.V = V;
+    VN_LAUNCH_PDL(ctx, accept_topk_kernel, B * k, 1024, 0, rs, top_k, temp, 1, q_rows, (long long)k, (const int*)nullptr);
+    da.nq = k; da.q_rows = q_rows; da.q_sb = k; da.q_si = 1;
+  }
+  VN_LAUNCH_PDL_BIT(ctx, 256, accept_topk_decide_kernel, ceil_div(B, 4), 128, 0, da);
+  return VN_OK;
+}
+
 extern "C" {
 
 int32_t vn_row_stats(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, float temperature,
@@ -1318,7 +1502,7 @@ int32_t vn_accept(vn_ctx* ctx, const float* p_logits_dev, const float* q_logits_
                   int32_t* out_len_dev, int64_t* out_tokens_dev) {
   const long long np = bonus ? k + 1 : k;
   return vn_accept_impl(ctx, p_logits_dev, np * V, V, q_logits_dev, (long long)k * V, V, draft_dev, u_accept_dev,
-                        u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev, out_tokens_dev, 1, 0);
+                        u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev, out_tokens_dev, 1, 0, nullptr);
 }
 
 int32_t vn_accept_strided(vn_ctx* ctx, const float* p_logits_dev, int64_t p_stride_b, int64_t p_stride_i,
@@ -1328,7 +1512,7 @@ int32_t vn_accept_strided(vn_ctx* ctx, const float* p_logits_dev, int64_t p_stri
                           int32_t B, int32_t k, int32_t V, int32_t* out_len_dev, int64_t* out_tokens_dev) {
   return vn_accept_impl(ctx, p_logits_dev, p_stride_b, p_stride_i, q_logits_dev, q_stride_b, q_stride_i, draft_dev,
                         u_accept_dev, u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev,
-                        out_tokens_dev, 1, 0);
+                        out_tokens_dev, 1, 0, nullptr);
 }
 
 int32_t vn_sample(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, float temperature,
@@ -1339,9 +1523,24 @@ int32_t vn_sample(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int3
   if (R == 0) return VN_OK;
   int32_t st = vn_accept_impl(ctx, logits_dev, row_stride, 0, nullptr, 0, 0, nullptr, uniforms_dev, uniforms_dev, seed,
                               offset, temperature, top_k, 1, R, 0, V, nullptr, out_tokens_dev, (int32_t)purpose,
-                              (int32_t)position);
+                              (int32_t)position, nullptr);
   return st;
 }
+
+int32_t vn_sample_lists(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, float temperature,
+                        int32_t top_k, const float* uniforms_dev, uint64_t seed, uint32_t offset, uint32_t position,
+                        uint32_t purpose, int64_t* out_tokens_dev, void* lists_out_dev) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, R >= 0 && out_tokens_dev, "bad arguments");
+  VN_REQUIRE(ctx, !lists_out_dev || (temperature > 0.f && top_k > 0 && top_k < V),
+             "kept lists exist on the top-k path only (temperature > 0, 0 < top_k < V)");
+  if (R == 0) return VN_OK;
+  return vn_accept_impl(ctx, logits_dev, row_stride, 0, nullptr, 0, 0, nullptr, uniforms_dev, uniforms_dev, seed, offset,
+                        temperature, top_k, 1, R, 0, V, nullptr, out_tokens_dev, (int32_t)purpose, (int32_t)position,
+                        lists_out_dev);
+}
+
+size_t vn_topk_row_bytes(void) { return vn_topk_row_bytes_impl(); }
 
 }  // extern "C"
 

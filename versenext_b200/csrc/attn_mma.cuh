@@ -18,7 +18,10 @@
 namespace attn_detail {
 
 constexpr int AW = 8;    // warps per CTA
-constexpr int RING = 3;  // key blocks per warp in shared memory (4 KB each)
+#ifndef VN_ATTN_RING
+#define VN_ATTN_RING 3
+#endif
+constexpr int RING = VN_ATTN_RING;  // key blocks per warp in shared memory (4 KB each)
 
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

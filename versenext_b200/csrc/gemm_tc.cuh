@@ -39,6 +39,17 @@ struct TcRope {
   int Tn, H, n_kv, hd, max_seq, use_rope, rope_rows, slot_offset;
 };
 
+// Candidate lists filled by the LM-head epilogue in TC_FILTER mode: instead of storing a row's logits, every logit
+// at or above the row's lower bound `tau` is appended to the row's list (order arbitrary; `count` may run past
+// `cap`, entries beyond it are dropped and the consumer sees the overflow from the count).
+struct CandBuf {
+  const float* tau = nullptr;   // [rows] raw-logit bound per token row
+  int* count = nullptr;         // [rows]
+  float* val = nullptr;         // [rows][cap] raw logits
+  int* tok = nullptr;           // [rows][cap] feature (vocabulary) index
+  int cap = 0;
+};
+
 struct TcArgs {
   void* C;                 // see epi
   const float* bias;
@@ -62,6 +73,9 @@ struct TcArgs {
   // their partial tiles through distributed shared memory; the epilogue below runs on the reduced rows
   float* resid;            // TC_CL_ADD: resid[row, n] += value (fp32, pitch ldc)
   TcRope rope;             // TC_CL_QKV
+  CandBuf cand;            // TC_FILTER
+  const int* run_if;       // when set: the whole grid returns at once unless *run_if != 0 (read after the wait for
+                           // the preceding kernels); lets a fallback sit in a captured graph at almost no cost
 };
 
 // SM cycle counter, ordered with the surrounding memory operations (for the optional phase stamps)
@@ -154,7 +168,8 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
 }
 
 enum { TC_PARTIAL = 0, TC_STORE = 1, TC_SWIGLU = 2, TC_ADD = 3,
-       TC_CL_STORE = 4, TC_CL_SWIGLU = 5, TC_CL_ADD = 6, TC_CL_QKV = 7 };   // >= TC_CL_STORE: cluster split-K
+       TC_CL_STORE = 4, TC_CL_SWIGLU = 5, TC_CL_ADD = 6, TC_CL_QKV = 7,     // 4 .. 7: cluster split-K
+       TC_FILTER = 8 };
 
 __device__ __forceinline__ unsigned cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ unsigned cluster_size() { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
@@ -182,7 +197,24 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
   const int f = q * 32 + lane, n = n0 + f;
   const int m0 = ch * 32;
   const int mrem = cnt - m0;               // tokens left from this chunk on (>= 1)
-    if (MODE >= TC_CL_STORE) {
+    if (MODE == TC_FILTER) {
+      // logits never leave the SM: the few that reach the row's bound are appended to the row's candidate list
+      if (n < g.N) {
+        const float* tau = g.cand.tau + row0 + m0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float v = __uint_as_float(r[i]);
+          if (i < mrem && v >= __ldg(tau + i)) {
+            const long long rowg = row0 + m0 + i;
+            const int slot = atomicAdd(g.cand.count + rowg, 1);
+            if (slot < g.cand.cap) {
+              g.cand.val[rowg * g.cand.cap + slot] = v;
+              g.cand.tok[rowg * g.cand.cap + slot] = n;
+            }
+          }
+        }
+      }
+    } else if (MODE >= TC_CL_STORE) {
       // whole partial tile [token][feature] in this CTA's shared memory; reduced after the cluster barrier
       float* tile = reinterpret_cast<float*>(base);
 #pragma unroll
@@ -295,6 +327,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     tr[6] = (long long)ns;
   }
   pdl_trigger();
+  if (g.run_if) {          // uniform over the grid: nothing has been allocated or initialised yet
+    pdl_wait();
+    if (*reinterpret_cast<const volatile int*>(g.run_if) == 0) return;
+  }
   // segment sizes are written by the routing kernels that precede this one; a dense block only waits
   // once its first weight tiles are on their way (weights never change)
   if (g.seg_cnt) { pdl_wait(); row0 = g.seg_off[z]; cnt = g.seg_cnt[z]; }
@@ -451,7 +487,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         } else {
-          tc_epilogue_chunk<MODE>(g, r, MODE >= TC_CL_STORE ? base : base + grp * (32 * 1024), ch, (ch >> 1) & 1, 2 + grp,
+          tc_epilogue_chunk<MODE>(g, r, (MODE >= TC_CL_STORE && MODE != TC_FILTER) ? base : base + grp * (32 * 1024), ch, (ch >> 1) & 1, 2 + grp,
                                   q, lane, n0, row0, cnt, (int)blockIdx.y, vec_ok, swi_ok);
         }
       }
@@ -461,7 +497,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
     if (tr && threadIdx.x == 64) tr[5] = clock_now();     // this warp's stores issued
   }
-  if (MODE >= TC_CL_STORE) {
+  if (MODE >= TC_CL_STORE && MODE != TC_FILTER) {
     __syncwarp();            // the single-lane roles above rejoin their warps before the aligned barriers
     cluster_sync_all();
     if (warp >= 2 && *(volatile int*)&s_error == 0) {
@@ -599,6 +635,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_trigger();
   pdl_wait();
+  if (g.run_if && *reinterpret_cast<const volatile int*>(g.run_if) == 0) return;
   // the longest segment fixes the stage size for the whole launch (uniform over the CTA)
   int maxcnt = g.M;
   if (g.seg_cnt) {
@@ -827,6 +864,8 @@ struct TcPlan {
   int cluster_mode = 0;          // 0: off, else tc_detail::TC_CL_STORE / TC_CL_SWIGLU / TC_CL_ADD / TC_CL_QKV
   float* resid = nullptr;        // TC_CL_ADD target (pitch g.ldc)
   tc_detail::TcRope rope = {};   // TC_CL_QKV
+  const tc_detail::CandBuf* filter = nullptr;   // set: candidate-filter epilogue instead of a store (TC_FILTER)
+  const int* run_if = nullptr;   // see TcArgs::run_if
 };
 
 // cluster split-K needs whole float4 groups per lane and, for the RoPE epilogue, heads that tile the 128 features
@@ -859,7 +898,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   const long long w_rows = g.seg_cnt ? (long long)(g.nseg - 1) * (g.w_stride / g.ldw) + g.N : g.N;
   if (!make_map(&tm_w, g.W, w_rows, g.K, g.ldw, BF) || !make_map(&tm_x, g.A, a_rows_total, g.K, g.lda, g.seg_cnt ? 16 : ntok))
     return vn_fail(ctx, VN_ERR_CUDA, "cuTensorMapEncodeTiled failed");
-  TcArgs a;
+  TcArgs a = {};
   a.C = g.C; a.bias = g.bias; a.ldc = g.ldc; a.M = g.M; a.N = g.N; a.K = g.K; a.ntok = ntok;
   a.x_box = g.seg_cnt ? 16 : ntok;
   const size_t stage_bytes = (size_t)BF * BK * 2 + (size_t)ntok * BK * 2;
@@ -889,6 +928,8 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   a.trace = plan.trace;
   a.resid = plan.resid;
   a.rope = plan.rope;
+  a.run_if = plan.run_if;
+  if (plan.filter) a.cand = *plan.filter;
   if (plan.cluster_mode) {
     if (gy > 8 || g.seg_cnt) return vn_fail(ctx, VN_ERR_INVALID, "cluster split-K: at most 8 K ranges, dense rows only");
     a.partial = nullptr;
@@ -898,6 +939,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   if (!plan.cluster_mode && (gy > 1 || plan.force_partial) && !plan.partial)
     return vn_fail(ctx, VN_ERR_INVALID, "split-K needs a workspace");
   const int mode = plan.cluster_mode ? plan.cluster_mode
+                   : plan.filter ? TC_FILTER
                    : a.partial ? TC_PARTIAL : g.epi == EPI_SWIGLU ? TC_SWIGLU : g.epi == EPI_ADD ? TC_ADD : TC_STORE;
   // dense fp32 outputs leave through TMA stores (VN_TC_TMA_STORE=0: staged float4 stores instead)
   static const bool tma_store_on = [] { const char* e = getenv("VN_TC_TMA_STORE"); return !(e && e[0] == '0'); }();
@@ -929,6 +971,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
     VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_CL_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
     VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_CL_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
     VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_CL_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<TC_FILTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
     attr_set |= 1ull << (ctx->device & 63);
   }
   dim3 grid(ceil_div(g.N, BF), gy, g.nseg);
@@ -944,7 +987,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   // draft model's LM head: 1,940 tiles of four k blocks), where the per-tile set-up is what the tile loop saves;
   // measured -15 us per round there, +24 us on the target's GEMMs when forced everywhere.
   const bool persist_auto = persist_level < 0 && a.kb_per_split <= 4 && tiles_total > 2ll * ctx->sm_count;
-  if ((persist_level > 0 || persist_auto) && (mode == TC_STORE || mode == TC_SWIGLU || mode == TC_PARTIAL) &&
+  if ((persist_level > 0 || persist_auto) && (mode == TC_STORE || mode == TC_SWIGLU || mode == TC_PARTIAL || mode == TC_FILTER) &&
       (persist_level >= 2 || tiles_total > 2ll * ctx->sm_count) && tiles_total < (1ll << 30)) {
     const size_t stages_max = (216 * 1024 - PERSIST_STAGING) / stage_bytes;
     if (stages_max >= 2) {
@@ -956,6 +999,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
         VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_persist_kernel<TC_PARTIAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_persist_kernel<TC_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_persist_kernel<TC_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        VN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_persist_kernel<TC_FILTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         pattr_set |= 1ull << (ctx->device & 63);
       }
       const int pgrid = (int)std::min<long long>(tiles_total, ctx->sm_count);
@@ -964,6 +1008,8 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
         VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_STORE>, pgrid, PERSIST_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
       else if (mode == TC_SWIGLU)
         VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_SWIGLU>, pgrid, PERSIST_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
+      else if (mode == TC_FILTER)
+        VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_FILTER>, pgrid, PERSIST_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
       else
         VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_persist_kernel<TC_PARTIAL>, pgrid, PERSIST_THREADS, psmem, tm_w, tm_x, a, tx, ty, tt);
       return VN_OK;
@@ -973,6 +1019,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
     case TC_PARTIAL: VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_PARTIAL>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
     case TC_SWIGLU:  VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
     case TC_ADD:     VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
+    case TC_FILTER:  VN_LAUNCH_PDL_LEVEL(ctx, 1, name, gemm_tc_kernel<TC_FILTER>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
     case TC_CL_STORE:  VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_STORE>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
     case TC_CL_SWIGLU: VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_SWIGLU>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;
     case TC_CL_ADD:    VN_LAUNCH_CLUSTER(ctx, 1, gy, name, gemm_tc_kernel<TC_CL_ADD>, grid, TC_THREADS, smem, tm_w, tm_x, tm_out, a); break;

@@ -9,6 +9,7 @@
 #include "gemm_tc.cuh"
 #include "gemm_mma_q.cuh"
 #include "gemm_tcq.cuh"
+#include "k1.h"
 
 #include <math.h>
 #include <stdlib.h>
@@ -1400,6 +1401,71 @@ int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
     return forward_tc(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
   if (m->cfg.bf16) return forward_t<__nv_bfloat16>(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
   return forward_t<float>(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
+}
+
+int32_t vn_verify_accept(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int32_t B, int32_t T, int32_t k,
+                         const void* q_lists_dev, int64_t ql_stride_b, int64_t ql_stride_i, const float* q_logits_dev,
+                         int64_t q_stride_b, int64_t q_stride_i, const int64_t* draft_dev, const float* u_accept_dev,
+                         const float* u_sample_dev, uint64_t seed, uint32_t offset, float temperature, int32_t top_k,
+                         int32_t bonus, float* p_logits_scratch_dev, int32_t* out_len_dev, int64_t* out_tokens_dev) {
+  if (!m || !kv) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  const Config& c = m->cfg;
+  const int np = bonus ? k + 1 : k;
+  VN_REQUIRE(ctx, k >= 0 && T == np && T >= 1, "T (%d) must be k + 1 with a bonus token, k without (k = %d)", T, k);
+  VN_REQUIRE(ctx, out_tokens_dev && (k == 0 || draft_dev), "null argument");
+  const int V = c.vocab;
+  // VN_K1=0 in the environment (read on every call, so that a test can compare the two routes): logits through HBM
+  const char* k1_env = getenv("VN_K1");
+  const bool k1_on = !(k1_env && k1_env[0] == '0');
+  const bool fused_head = k1_on && c.bf16 && m->use_tc && !m->qmode && (long long)B * T <= 256 && c.dim % 8 == 0 &&
+                          c.dim <= 2048 && tc_detail::encode_fn() != nullptr && temperature > 0.f && top_k > 0 &&
+                          top_k < V && top_k <= 1024 && V >= 1024;
+  if (!fused_head) {
+    // logits through HBM: the forward with the head, then the acceptance kernels on the stored rows
+    if (!p_logits_scratch_dev)
+      return vn_fail(ctx, VN_ERR_UNSUPPORTED, "this model / rule needs the logits in memory: pass p_logits_scratch_dev [B, T, V]");
+    VN_REQUIRE(ctx, q_lists_dev == nullptr || q_logits_dev != nullptr || temperature <= 0.f || k == 0,
+               "this model / rule selects from the draft rows' logits: pass q_logits_dev as well");
+    TRY(vn_model_forward(m, kv, tokens_dev, B, T, nullptr, nullptr, p_logits_scratch_dev, 0, 0));
+    return vn_accept_impl(ctx, p_logits_scratch_dev, (long long)T * V, V, q_logits_dev, q_stride_b, q_stride_i, draft_dev,
+                          u_accept_dev, u_sample_dev, seed, offset, temperature, top_k, bonus, B, k, V, out_len_dev,
+                          out_tokens_dev, 1, 0, nullptr);
+  }
+  // the logits buffer is only written when a row's candidate list overflows (heavy ties), but it has to exist
+  VN_REQUIRE(ctx, p_logits_scratch_dev, "p_logits_scratch_dev [B, T, V] is needed (used only when a candidate list overflows)");
+  // final-norm hidden rows of the B * T new positions (bf16, in the model's activation buffer)
+  TRY(vn_model_forward(m, kv, tokens_dev, B, T, nullptr, nullptr, nullptr, 0, 0));
+  const int rows = B * T, D = c.dim;
+  vn_k1 k1;
+  TRY(vn_k1_layout(ctx, B, np, top_k, V, &k1));
+  const float temp = fmaxf(temperature, 1e-8f);
+  TcPlan plain;
+  plain.error_flag = m->tc_error;
+  GemmArgs g;
+  g.A = m->h; g.lda = D; g.W = m->head; g.ldw = D; g.M = rows; g.K = D;
+  // (1) logits of the first head columns -> a lower bound of every row's k-th largest logit
+  g.C = k1.boot; g.ldc = k1.nb; g.N = k1.nb; g.tag = "gemm_head_bound";
+  TRY(launch_gemm_tc(ctx, g, m->cap_rows, plain));
+  TRY(vn_k1_bound(ctx, k1, top_k, temp));
+  // (2) the whole head: logits at or above the bound go to the rows' candidate lists, nothing else leaves the SMs
+  tc_detail::CandBuf cb;
+  cb.tau = k1.tau; cb.count = k1.count; cb.val = k1.cand_val; cb.tok = k1.cand_tok; cb.cap = k1.cap;
+  TcPlan filt;
+  filt.error_flag = m->tc_error; filt.filter = &cb;
+  g.C = nullptr; g.ldc = V; g.N = V; g.tag = "gemm_head_filter";
+  TRY(launch_gemm_tc(ctx, g, m->cap_rows, filt));
+  // (3) only when a candidate list overflowed: the head once more with its logits stored
+  if (p_logits_scratch_dev) {
+    TcPlan fb;
+    fb.error_flag = m->tc_error; fb.run_if = k1.fallback;
+    g.C = p_logits_scratch_dev; g.ldc = V; g.N = V; g.tag = "gemm_head_fallback";
+    TRY(launch_gemm_tc(ctx, g, m->cap_rows, fb));
+  }
+  return vn_k1_accept(ctx, k1, p_logits_scratch_dev, (long long)T * V, V, q_lists_dev, ql_stride_b, ql_stride_i, q_logits_dev,
+                      q_stride_b, q_stride_i, draft_dev, u_accept_dev, u_sample_dev, seed, offset, temperature, top_k, bonus,
+                      B, k, V, out_len_dev, out_tokens_dev);
 }
 
 }  // extern "C"

@@ -61,6 +61,11 @@ class SpecEngine:
         self.history = ctx.zeros((B, self.cap), np.int64)
         self.count = ctx.zeros((B,), np.int32)
         self.n_commit = ctx.zeros((B,), np.int32)
+        # kept lists of the draft's top-k selection, one record per (step, request): sampled from at draft time and
+        # read again as q by the acceptance step, so the draft rows are selected once per round
+        self.fused_head = self.temperature > 0 and 0 < self.top_k < V
+        self.row_bytes = int(ctx.lib.vn_topk_row_bytes())
+        self.q_lists = ctx.empty((k * B * self.row_bytes,), np.uint8) if self.fused_head else None
         self.round_dev = ctx.zeros((1,), np.uint32)               # rounds completed; offsets the Philox streams
         self.rounds_run = 0
         self.use_graph = bool(graph)
@@ -123,17 +128,22 @@ class SpecEngine:
                     else:
                         self.draft.forward_cached(self.step_tokens[i - 1].reshape(B, 1), self.d_cache,
                                                   last_only=True, out_logits=q_i, slot_offset=i + 1)
-                    ctx._check(lib.vn_sample(ctx.handle, _ptr(q_i), V, B, V, self.temperature, self.top_k, None,
-                                             self.seed, 0, i, PURPOSE_DRAFT, _ptr(self.step_tokens[i])))
+                    lists_i = C.c_void_p(self.q_lists.ptr + i * B * self.row_bytes) if self.fused_head else None
+                    ctx._check(lib.vn_sample_lists(ctx.handle, _ptr(q_i), V, B, V, self.temperature, self.top_k, None,
+                                                   self.seed, 0, i, PURPOSE_DRAFT, _ptr(self.step_tokens[i]), lists_i))
                 ctx._check(lib.vn_spec_gather(ctx.handle, _ptr(self.step_tokens), _ptr(self.pair), B, k,
                                               self.n_verify, _ptr(self.draft_tokens), _ptr(self.verify_tokens)))
-            # target: one forward over (last committed, d_0 .. d_{n_verify-2})
-            self.target.forward_cached(self.verify_tokens, self.t_cache, out_logits=self.p_logits)
-            ctx._check(lib.vn_accept_strided(
-                ctx.handle, _ptr(self.p_logits), self.n_verify * V, V,
+            # target: one forward over (last committed, d_0 .. d_{n_verify-2}), LM head and acceptance in one call;
+            # with top-k sampling the head is fused with the selection and q comes from the lists kept above
+            # (record of (request b, step i) at i * B + b)
+            if not self.target._finalized:
+                self.target.finalize()
+            ctx._check(lib.vn_verify_accept(
+                self.target.handle, self.t_cache.handle, _ptr(self.verify_tokens), B, self.n_verify, k,
+                _ptr(self.q_lists) if self.fused_head else None, 1, B,
                 None if greedy else _ptr(self.q_logits), V, B * V,
                 _ptr(self.draft_tokens), None, None, self.seed, 0, self.temperature, self.top_k,
-                int(self.bonus), B, k, V, _ptr(self.accept_len), _ptr(self.out_tokens)))
+                int(self.bonus), _ptr(self.p_logits), _ptr(self.accept_len), _ptr(self.out_tokens)))
             ctx._check(lib.vn_spec_advance(ctx.handle, _ptr(self.out_tokens), B, k, _ptr(self.pair),
                                            _ptr(self.history), self.cap, _ptr(self.count), _ptr(self.n_commit)))
             # both caches keep the first n_commit entries appended this round
