@@ -1043,55 +1043,48 @@ accept_topk_decide_kernel(DecideArgs da) {
 
 
 // ---- fused LM head: bound, finish ---------------------------------------------------------------------------
-// Descending bitonic sort of N (a power of two) 64-bit keys in shared memory by all threads of the CTA.
-template <typename K>
-__device__ void bitonic_sort_desc(K* a, int N) {
-  const int tid = threadIdx.x, nt = blockDim.x;
-  for (int k = 2; k <= N; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int i = tid; i < N; i += nt) {
-        const int ixj = i ^ j;
-        if (ixj > i) {
-          const K x = a[i], y = a[ixj];
-          const bool desc = (i & k) == 0;
-          if (desc ? x < y : x > y) { a[i] = y; a[ixj] = x; }
-        }
-      }
-      __syncthreads();
-    }
-  }
-}
-
-// One CTA per target row: the k-th largest of the row's first nb logits is a lower bound of the k-th largest of
-// the whole row (a subset's k-th largest never exceeds the full set's).  The bound handed to the GEMM epilogue is
-// the SMALLEST raw logit whose temperature-scaled value reaches the scaled bound, so that a logit whose quotient
-// ties with the k-th value after rounding is still collected.  Also clears the row's candidate counter and the
-// call's fallback flag.
+// One CTA per target row.  Every thread takes the maximum of its share of the row's first nb logits; the k-th
+// largest of those per-thread maxima is a lower bound of the k-th largest of the subset (they are k distinct
+// entries), hence of the whole row (a subset's k-th largest never exceeds the full set's) -- and with k far below
+// the number of threads it is almost as tight as the subset's own k-th largest.  The bound handed to the GEMM
+// epilogue is the SMALLEST raw logit whose temperature-scaled value reaches the scaled bound, so that a logit whose
+// quotient ties with the k-th value after rounding is still collected.  Also clears the row's candidate counter
+// and the call's fallback flag.
 __global__ void __launch_bounds__(1024)
 k1_bound_kernel(const float* __restrict__ boot, int nb, int top_k, float temp, float* __restrict__ tau,
                 int* __restrict__ count, int* __restrict__ fallback) {
   pdl_trigger();
   pdl_wait();
-  __shared__ uint32_t keys[8192];
-  const int row = blockIdx.x, tid = threadIdx.x;
-  int N = 64;
-  while (N < nb) N <<= 1;
+  __shared__ uint32_t s_max[1024];
+  __shared__ uint32_t s_kth;
+  const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
   const float* src = boot + (long long)row * nb;
-  for (int i = tid; i < N; i += blockDim.x) keys[i] = i < nb ? order_key(src[i]) : 0u;
+  float mx = -CUDART_INF_F;
+  int mine = 0;
+  for (int i = tid; i < nb; i += nt) { mx = fmaxf(mx, src[i]); ++mine; }
+  s_max[tid] = mine ? order_key(mx) : 0u;           // 0 sorts below every real key
+  if (tid == 0) s_kth = 0u;
   __syncthreads();
-  bitonic_sort_desc(keys, N);
+  const int groups = nb < nt ? nb : nt;             // threads that hold a value
+  if (top_k <= groups && tid < groups) {
+    const uint32_t me = s_max[tid];
+    int greater = 0, geq = 0;
+    for (int j = 0; j < groups; ++j) { const uint32_t o = s_max[j]; greater += o > me; geq += o >= me; }
+    if (greater < top_k && geq >= top_k) s_kth = me;    // every writer holds the same key
+  }
+  __syncthreads();
   if (tid == 0) {
     float t = -CUDART_INF_F;
-    if (top_k <= nb) {
-      const float xk = key_value(keys[top_k - 1]);
+    if (top_k <= groups && s_kth != 0u) {
+      const float xk = key_value(s_kth);
       t = xk;
-      if (temp != 1.0f && xk == xk && fabsf(xk) != CUDART_INF_F) {
+      if (xk != xk) {
+        t = -CUDART_INF_F;
+      } else if (temp != 1.0f && fabsf(xk) != CUDART_INF_F) {
         const float sk = __fdiv_rn(xk, temp);
         int it = 0;
         while (it < 64 && next_down(t) != t && __fdiv_rn(next_down(t), temp) >= sk) { t = next_down(t); ++it; }
         if (it >= 64) t = -CUDART_INF_F;      // could not pin the edge down: collect everything, the overflow path decides
-      } else if (xk != xk) {
-        t = -CUDART_INF_F;
       }
     }
     tau[row] = t;
@@ -1101,14 +1094,18 @@ k1_bound_kernel(const float* __restrict__ boot, int nb, int top_k, float temp, f
 }
 
 // One CTA per target row: candidates (raw logit, token) -> the kept list the select kernel would have produced:
-// every entry whose scaled value is >= the k-th largest scaled value, ascending token id.  A list that ran past
-// its capacity, or more than KEEP_MAX kept entries, raises the fallback flag instead.
+// every entry whose scaled value is >= the k-th largest scaled value, ascending token id.  The k-th largest is found
+// by rank counting over the candidates in shared memory.  A list that ran past its capacity, or more than KEEP_MAX
+// kept entries, raises the fallback flag instead.
 __global__ void __launch_bounds__(1024)
 k1_finish_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_tok, const int* __restrict__ count,
                  int cap, int top_k, float temp, int V, TopkRow* __restrict__ out, int* __restrict__ fallback) {
   pdl_trigger();
   pdl_wait();
-  __shared__ unsigned long long comp[VN_K1_CAP];
+  __shared__ uint32_t s_key[VN_K1_CAP];
+  __shared__ int s_ktok[KEEP_MAX];
+  __shared__ uint32_t s_kkey[KEEP_MAX];
+  __shared__ uint32_t s_kth;
   __shared__ int s_keep;
   const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
   const int n = count[row];
@@ -1118,30 +1115,28 @@ k1_finish_kernel(const float* __restrict__ cand_val, const int* __restrict__ can
     if (tid == 0) { atomicExch(fallback, 1); o->n = 0; o->overflow = 1; }
     return;
   }
-  int N = 64;
-  while (N < n) N <<= 1;
   const bool scale = temp != 1.0f;
   const float* cv = cand_val + (long long)row * cap;
   const int* ct = cand_tok + (long long)row * cap;
-  for (int i = tid; i < N; i += nt) {
-    unsigned long long c = 0ull;
-    if (i < n) {
-      const float x = cv[i];
-      const uint32_t key = order_key(scale ? __fdiv_rn(x, temp) : x);
-      c = ((unsigned long long)key << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)ct[i]);
-    }
-    comp[i] = c;
-  }
-  if (tid == 0) s_keep = 0;
-  __syncthreads();
-  bitonic_sort_desc(comp, N);
-  const uint32_t kth = (uint32_t)(comp[want - 1] >> 32);
-  // kept entries are the sorted prefix with key >= kth: its length is the index of the first smaller key
   for (int i = tid; i < n; i += nt) {
-    const bool in = (uint32_t)(comp[i] >> 32) >= kth;
-    const bool next_in = i + 1 < n && (uint32_t)(comp[i + 1] >> 32) >= kth;
-    if (in && !next_in) s_keep = i + 1;
+    const float x = cv[i];
+    s_key[i] = order_key(scale ? __fdiv_rn(x, temp) : x);
   }
+  if (tid == 0) { s_keep = 0; s_kth = 0u; }
+  __syncthreads();
+  for (int i = tid; i < n; i += nt) {
+    const uint32_t me = s_key[i];
+    int greater = 0, geq = 0;
+    for (int j = 0; j < n; ++j) { const uint32_t k2 = s_key[j]; greater += k2 > me; geq += k2 >= me; }
+    if (greater < want && geq >= want) s_kth = me;      // every writer holds the same key
+  }
+  __syncthreads();
+  const uint32_t kth = s_kth;
+  for (int i = tid; i < n; i += nt)
+    if (s_key[i] >= kth) {
+      const int slot = atomicAdd(&s_keep, 1);
+      if (slot < KEEP_MAX) { s_kkey[slot] = s_key[i]; s_ktok[slot] = ct[i]; }
+    }
   __syncthreads();
   const int keep = s_keep;
   if (keep > KEEP_MAX) {
@@ -1150,11 +1145,11 @@ k1_finish_kernel(const float* __restrict__ cand_val, const int* __restrict__ can
   }
   // ascending token id: rank of each kept entry among the kept ones (a few dozen entries as a rule)
   for (int i = tid; i < keep; i += nt) {
-    const uint32_t ti = 0xFFFFFFFFu - (uint32_t)comp[i];
+    const int ti = s_ktok[i];
     int pos = 0;
-    for (int j = 0; j < keep; ++j) pos += (0xFFFFFFFFu - (uint32_t)comp[j]) < ti;
-    o->tok[pos] = (int)ti;
-    o->val[pos] = key_value((uint32_t)(comp[i] >> 32));
+    for (int j = 0; j < keep; ++j) pos += s_ktok[j] < ti;
+    o->tok[pos] = ti;
+    o->val[pos] = key_value(s_kkey[i]);
   }
   if (tid == 0) { o->n = keep; o->overflow = 0; }
 }
@@ -1379,7 +1374,7 @@ int32_t vn_k1_layout(vn_ctx* ctx, int B, int np, int top_k, int V, vn_k1* out) {
 }
 
 int32_t vn_k1_bound(vn_ctx* ctx, const vn_k1& k1, int top_k, float temp) {
-  VN_REQUIRE(ctx, k1.nb <= 8192 && top_k >= 1, "bound GEMM wider than the bound kernel sorts");
+  VN_REQUIRE(ctx, top_k >= 1, "top_k must be positive");
   VN_LAUNCH_PDL(ctx, k1_bound_kernel, k1.rows, 1024, 0, (const float*)k1.boot, k1.nb, top_k, temp, k1.tau, k1.count,
                 k1.fallback);
   return VN_OK;

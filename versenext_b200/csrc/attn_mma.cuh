@@ -47,14 +47,19 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
                                        const __nv_bfloat16* __restrict__ Vb, long long ks, int lo, int hi, int len,
                                        const RowInfo (&row)[2], const unsigned (&qf)[4][4], const int* s_depth,
                                        int warp, int nw, int lane, unsigned char* ring, float (&o)[8][4],
-                                       float (&m)[2], float (&l)[2]) {
+                                       float (&m)[2], float (&l)[2], int phase = 0) {
+  // phase 0: everything.  phase 1: only put this warp's first key blocks on their way (they do not depend on the
+  // query rows, so the caller can do that before its own set-up work).  phase 2: the rest, after a phase-1 call
+  // with the same arguments.
   const int g = lane >> 2, t = lane & 3;
+  if (phase != 1) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < 8; ++j)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
-  m[0] = m[1] = -CUDART_INF_F;
-  l[0] = l[1] = 0.f;
+      for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+    m[0] = m[1] = -CUDART_INF_F;
+    l[0] = l[1] = 0.f;
+  }
   const int nblk = hi > lo ? (hi - lo + 15) >> 4 : 0;
   int pos_max = max(row[0].pos, row[1].pos);     // latest query position of the tile
 #pragma unroll
@@ -78,11 +83,14 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
       mma_detail::cp_async16(st + 2048 + soff, Vb + (long long)key * ks + c * 8, true);
     }
   };
+  if (phase != 2) {
 #pragma unroll
-  for (int s = 0; s < RING - 1; ++s) {
-    if (s < n_my) issue(s);
-    mma_detail::cp_async_commit();
+    for (int s = 0; s < RING - 1; ++s) {
+      if (s < n_my) issue(s);
+      mma_detail::cp_async_commit();
+    }
   }
+  if (phase == 1) return;
   for (int it = 0; it < n_my; ++it) {
     const int j0 = lo + (warp + it * nw) * 16;
     mma_detail::cp_async_wait<RING - 2>();
@@ -197,7 +205,7 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
   }
 }
 
-__global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a) {
+__global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_mma_kernel(AttnArgs a) {
   // per warp: a ring of RING key blocks; after a path's keys the first 4 KB of the warp's ring hold its
   // partial output (16 rows x 64 dims fp32, 16-byte chunks swizzled) for the merge across warps
   extern __shared__ __align__(128) unsigned char attn_smem[];
@@ -246,6 +254,37 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
   __nv_bfloat16* Vc = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a.vc)) + ((long long)b * a.max_seq * a.n_kv + kvh) * 64;
   const __nv_bfloat16* Ks = reinterpret_cast<const __nv_bfloat16*>(a.sink_k) + (long long)kvh * 64;
   const __nv_bfloat16* Vs = reinterpret_cast<const __nv_bfloat16*>(a.sink_v) + (long long)kvh * 64;
+
+  // ---- the warps are split between the window keys and the sink keys in proportion to their block counts (each
+  // path keeps its own softmax; both are merged in one pass afterwards)
+  const int lo_w = max(0, pos_min - a.window + 1);
+  const int nblk_w = hi_new > lo_w ? (hi_new - lo_w + 15) >> 4 : 0;
+  const int nblk_s = (a.n_sink + 15) >> 4;
+  int nw = 1;
+  {
+    int best = 1 << 30;
+    for (int c = 1; c < AW; ++c) {           // the split whose busier group has the fewest blocks per warp
+      const int cost = max((nblk_w + c - 1) / c, (nblk_s + AW - c - 1) / (AW - c));
+      if (cost < best) { best = cost; nw = c; }
+    }
+  }
+  unsigned char* ring = attn_smem + warp * (RING * 4096);
+  // This warp's first key blocks go on their way now, under the set-up work below: cached window keys and sink keys
+  // do not depend on this call's q | k | v.  A window warp whose first blocks reach into the rows that this very
+  // CTA appends below has to wait for them.
+  bool early = true;
+  if (warp < nw) {
+    const int last = warp + (RING - 2) * nw;                 // its last block of the first batch
+    early = a.partial == nullptr || lo_w + (min(last, max(nblk_w - 1, 0)) + 1) * 16 <= len;
+  }
+  {
+    unsigned qf0[4][4] = {};
+    float o0[8][4], m0[2], l0[2];
+    if (early) {
+      if (warp < nw) attend<0>(a, Kc, Vc, ks, lo_w, hi_new, len, row, qf0, depth, warp, nw, lane, ring, o0, m0, l0, 1);
+      else attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf0, depth, warp - nw, AW - nw, lane, ring, o0, m0, l0, 1);
+    }
+  }
 
   if (a.partial) {
     // ---- fused q|k|v finalize: this CTA sums the split-K slices of exactly the columns it needs -- the query rows
@@ -335,7 +374,6 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
   const int mrow = tid >> 4, mcol = (tid & 15) * 4;
   const bool use_c = a.use_alibi &&
                      (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max);
-  unsigned char* ring = attn_smem + warp * (RING * 4096);
 
   // each warp parks its partial result.  Column n of tile j is output dim 8n + j, so thread (g, t) holds dims
   // 16t .. 16t+15 of rows g and g + 8: four 16-byte chunks per row, chunk c stored at c ^ bit3(c) ^ 2*(row & 1),
@@ -381,17 +419,11 @@ __global__ void __launch_bounds__(AW * 32) trisparse_attn_mma_kernel(AttnArgs a)
   };
 
   if (tr && tid == 0) tr[1] = clock_stamp();     // row setup and Q fragments done
-  // ---- window path and sink path side by side: the warps are split between the two key ranges in proportion to
-  // their block counts (each path keeps its own softmax; both are merged in one pass afterwards)
+  // ---- window path and sink path side by side
   {
-    const int lo = max(0, pos_min - a.window + 1);
-    const int nblk_w = hi_new > lo ? (hi_new - lo + 15) >> 4 : 0;
-    const int nblk_s = (a.n_sink + 15) >> 4;
-    int nw = (AW * nblk_w + (nblk_w + nblk_s) / 2) / max(nblk_w + nblk_s, 1);
-    nw = nw < 1 ? 1 : (nw > AW - 1 ? AW - 1 : nw);
     float o[8][4], m[2], l[2];
-    if (warp < nw) attend<0>(a, Kc, Vc, ks, lo, hi_new, len, row, qf, depth, warp, nw, lane, ring, o, m, l);
-    else attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf, depth, warp - nw, AW - nw, lane, ring, o, m, l);
+    if (warp < nw) attend<0>(a, Kc, Vc, ks, lo_w, hi_new, len, row, qf, depth, warp, nw, lane, ring, o, m, l, early ? 2 : 0);
+    else attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf, depth, warp - nw, AW - nw, lane, ring, o, m, l, early ? 2 : 0);
     if (tr && tid == 0) tr[2] = clock_stamp();   // this warp's keys done
     park(o, m, l);
     __syncthreads();

@@ -68,7 +68,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if verbose:
                     print("compiled", os.path.basename(done))
     if jobs or not os.path.exists(OUT):
-        r = subprocess.run([NVCC, "-shared", "-o", OUT, *objs, "-lcudart"], capture_output=True, text=True)
+        r = subprocess.run([NVCC, "-shared", "-o", OUT, *objs, "-lcudart", "-ldl"], capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     return OUT

@@ -198,18 +198,31 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
   const int m0 = ch * 32;
   const int mrem = cnt - m0;               // tokens left from this chunk on (>= 1)
     if (MODE == TC_FILTER) {
-      // logits never leave the SM: the few that reach the row's bound are appended to the row's candidate list
-      if (n < g.N) {
-        const float* tau = g.cand.tau + row0 + m0;
+      // Logits never leave the SM: the few that reach the row's bound are appended to the row's candidate list.
+      // Lane i of the warp keeps the hit mask of token m0 + i and reserves that token's slots with ONE atomic for
+      // the whole warp (all 32 tokens' atomics are in flight together, no lane waits on a reply inside a loop).
+      const float* tau = g.cand.tau + row0 + m0;
+      const bool col_ok = n < g.N;
+      unsigned mymask = 0u;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const bool hit = col_ok && i < mrem && __uint_as_float(r[i]) >= __ldg(tau + (i < mrem ? i : 0));
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        if (lane == i) mymask = bal;
+      }
+      int mybase = 0;
+      if (mymask) mybase = atomicAdd(g.cand.count + row0 + m0 + lane, __popc(mymask));
+      if (__any_sync(0xffffffffu, mymask != 0u)) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(r[i]);
-          if (i < mrem && v >= __ldg(tau + i)) {
-            const long long rowg = row0 + m0 + i;
-            const int slot = atomicAdd(g.cand.count + rowg, 1);
+          const unsigned m_i = __shfl_sync(0xffffffffu, mymask, i);
+          const int b_i = __shfl_sync(0xffffffffu, mybase, i);
+          if ((m_i >> lane) & 1u) {
+            const int slot = b_i + __popc(m_i & ((1u << lane) - 1u));
             if (slot < g.cand.cap) {
-              g.cand.val[rowg * g.cand.cap + slot] = v;
-              g.cand.tok[rowg * g.cand.cap + slot] = n;
+              const long long at = (long long)(row0 + m0 + i) * g.cand.cap + slot;
+              g.cand.val[at] = __uint_as_float(r[i]);
+              g.cand.tok[at] = n;
             }
           }
         }
@@ -866,6 +879,8 @@ struct TcPlan {
   tc_detail::TcRope rope = {};   // TC_CL_QKV
   const tc_detail::CandBuf* filter = nullptr;   // set: candidate-filter epilogue instead of a store (TC_FILTER)
   const int* run_if = nullptr;   // see TcArgs::run_if
+  bool force_persist = false;    // walk the tiles with one CTA per SM whatever the shape (a flag-gated launch that
+                                 // mostly returns at once should not schedule thousands of CTAs to do so)
 };
 
 // cluster split-K needs whole float4 groups per lane and, for the RoPE epilogue, heads that tile the 128 features
@@ -987,8 +1002,8 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   // draft model's LM head: 1,940 tiles of four k blocks), where the per-tile set-up is what the tile loop saves;
   // measured -15 us per round there, +24 us on the target's GEMMs when forced everywhere.
   const bool persist_auto = persist_level < 0 && a.kb_per_split <= 4 && tiles_total > 2ll * ctx->sm_count;
-  if ((persist_level > 0 || persist_auto) && (mode == TC_STORE || mode == TC_SWIGLU || mode == TC_PARTIAL || mode == TC_FILTER) &&
-      (persist_level >= 2 || tiles_total > 2ll * ctx->sm_count) && tiles_total < (1ll << 30)) {
+  if ((persist_level > 0 || persist_auto || plan.force_persist) && (mode == TC_STORE || mode == TC_SWIGLU || mode == TC_PARTIAL || mode == TC_FILTER) &&
+      (persist_level >= 2 || plan.force_persist || tiles_total > 2ll * ctx->sm_count) && tiles_total < (1ll << 30)) {
     const size_t stages_max = (216 * 1024 - PERSIST_STAGING) / stage_bytes;
     if (stages_max >= 2) {
       const size_t pbudget = PERSIST_STAGING + std::min<size_t>(8, stages_max) * stage_bytes;

@@ -1459,7 +1459,7 @@ int32_t vn_verify_accept(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
   // (3) only when a candidate list overflowed: the head once more with its logits stored
   if (p_logits_scratch_dev) {
     TcPlan fb;
-    fb.error_flag = m->tc_error; fb.run_if = k1.fallback;
+    fb.error_flag = m->tc_error; fb.run_if = k1.fallback; fb.force_persist = true;
     g.C = p_logits_scratch_dev; g.ldc = V; g.N = V; g.tag = "gemm_head_fallback";
     TRY(launch_gemm_tc(ctx, g, m->cap_rows, fb));
   }
