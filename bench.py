@@ -346,19 +346,21 @@ def _sum_over_ranks(dist, value, local):
 def _sharded_check(vn, target, draft, dist, ctx, local, world, rank, rounds=4):
     """Vocabulary-sharded head + acceptance over the ranks (the one data path with an exchange): a few rounds of
     the sharded engine on this rank's requests must commit exactly the tokens of its plain engine."""
-    from versenext_b200.sharded_engine import ShardedSpecEngine
+    from versenext_b200.comm import Comm
+    from versenext_b200.sharded_engine import ShardedSpecEngine, rank_seed
     B, k, T0 = 8, SPEC["k"], 64
     prompts = spec_prompts(B, T0, 99, rank)
-    kw = dict(max_batch=B, max_seq=T0 + (rounds + 2) * (k + 1) + 16, k=k, temperature=1.0, seed=5,
+    kw = dict(max_batch=B, max_seq=T0 + (rounds + 2) * (k + 1) + 16, k=k, temperature=1.0,
               max_new_tokens=(rounds + 2) * (k + 1))
-    plain = vn.SpecEngine(target, draft, top_k=0, bonus=True, graph=False, **kw)
+    comm = Comm.from_torch_group(ctx) if dist is not None else None
+    plain = vn.SpecEngine(target, draft, top_k=0, bonus=True, graph=False, seed=rank_seed(5, rank), **kw)
     plain.prefill(prompts)
     for _ in range(rounds):
         plain.step()
     want = plain.history.numpy()[:, :rounds]
     want_counts = plain.counts()
     del plain
-    sh = ShardedSpecEngine(target, draft, **kw)
+    sh = ShardedSpecEngine(target, draft, seed=5, comm=comm, **kw)
     sh.prefill(prompts)
     sh.step()                                   # warm-up round (buffers, communicators)
     sh.rewind()
@@ -372,7 +374,8 @@ def _sharded_check(vn, target, draft, dist, ctx, local, world, rank, rounds=4):
     ok_all = _sum_over_ranks(dist, 1.0 if ok else 0.0, local) == world
     return {"ok": bool(ok_all), "ms_per_round": max_over_ranks(dist, ms, local), "n_ranks": world,
             "requests_per_rank": B, "rounds": rounds,
-            "what": "ShardedSpecEngine (LM head + acceptance split by vocabulary columns over the ranks) commits "
+            "what": "ShardedSpecEngine (LM head + acceptance split by vocabulary columns over the ranks, exchanges "
+                    "as NCCL all-gathers of device buffers on the library's stream, no host synchronisation) commits "
                     "the same tokens as the plain engine on every rank"}
 
 
@@ -544,10 +547,13 @@ def spec_config(quant=None):
 
 def run_sharded(args):
     """The vocabulary-sharded configuration: 32 requests per rank, 1024-token prompts, k = 6, T = 1.0, full-vocabulary
-    rule, target linears INT8 (or --quant), LM head and acceptance split by vocabulary columns over the ranks
-    (hidden-row all-gather + three small exchanges per round, host-staged).  Not the default benchmark line."""
+    rule, target linears INT8 (or --quant), LM head and acceptance split by vocabulary columns over the ranks: hidden
+    rows, per-row statistics and picked tokens cross the ranks as NCCL all-gathers of device buffers on the library's
+    stream, decisions stay on the device.  The same requests through the plain (unsharded) engine are timed beside it.
+    Not the default benchmark line."""
     import versenext_b200 as vn
-    from versenext_b200.sharded_engine import ShardedSpecEngine
+    from versenext_b200.comm import Comm
+    from versenext_b200.sharded_engine import ShardedSpecEngine, rank_seed
     world, rank, local, dist = dist_setup(args.gpus)
     ctx = vn.Context.get(local)
     B, k, T0 = 32, 6, 1024
@@ -556,32 +562,34 @@ def run_sharded(args):
     target.quantize(scheme)
     warm = max(args.warmup, 3)
     rounds = warm + args.steps + 8
-    eng = ShardedSpecEngine(target, draft, max_batch=B, max_seq=T0 + rounds * (k + 1) + 64, k=k, temperature=1.0,
-                            seed=5, max_new_tokens=rounds * (k + 1))
-    eng.prefill(np.random.default_rng([5, rank]).integers(0, 248320, (B, T0)).astype(np.int64))
+    comm = Comm.from_torch_group(ctx) if dist is not None else None
+    kw = dict(max_batch=B, max_seq=T0 + rounds * (k + 1) + 64, k=k, temperature=1.0, max_new_tokens=rounds * (k + 1))
+    prompts = np.random.default_rng([5, rank]).integers(0, 248320, (B, T0)).astype(np.int64)
+    eng = ShardedSpecEngine(target, draft, seed=5, comm=comm, **kw)
+    eng.prefill(prompts)
     for _ in range(warm):
         eng.step()
-    c0 = eng.counts().sum()
     clocks = ClockSampler(local).start() if rank == 0 else None
-    barrier_sync(dist, ctx)
     l0 = ctx.launch_count()
-    t0 = time.perf_counter()          # a round synchronises with the host several times: wall clock is the honest one
-    for _ in range(args.steps):
-        eng.step()
-    ctx.sync()
-    ms = (time.perf_counter() - t0) * 1e3
-    barrier_sync(dist, ctx)
-    launches = ctx.launch_count() - l0
+    reps, committed_rank = _time_engine(eng, ctx, dist, local, args.steps, warm)
+    launches = (ctx.launch_count() - l0) // len(reps) * args.steps // (args.steps + warm)
     clk = clocks.stop() if clocks else None
-    committed = float(eng.counts().sum() - c0)
-    ms = max_over_ranks(dist, ms, local)
-    if dist is not None:
-        import torch
-        t = torch.tensor([committed], dtype=torch.float64, device=f"cuda:{local}")
-        dist.all_reduce(t)
-        committed = float(t.item())
+    ms = statistics.median(reps)
+    committed = _sum_over_ranks(dist, committed_rank, local)
     value = committed / (ms * 1e-3)
     ctx_len = int(eng.t_cache.per_seq_lens.mean())
+    accept_rate = float(eng.accept_len.numpy().mean() / k)
+    sharded_tokens = eng.history.numpy()[:, :args.steps].copy()
+    del eng
+    # the same requests, full head on every rank, same Philox numbers: the round the sharded one is measured against
+    plain = vn.SpecEngine(target, draft, top_k=0, bonus=True, seed=rank_seed(5, rank), graph=True, **kw)
+    plain.prefill(prompts)
+    for _ in range(warm):
+        plain.step()
+    reps_p, _ = _time_engine(plain, ctx, dist, local, args.steps, warm)
+    same = bool(np.array_equal(plain.history.numpy()[:, :args.steps], sharded_tokens))
+    same_all = _sum_over_ranks(dist, 1.0 if same else 0.0, local) == world
+    ms_p = statistics.median(reps_p)
     # streamed per round and rank: the quantised block weights, this rank's columns of the head, the K/V window
     head_bytes = 248320 * 1024 * (1 if scheme == "int8" else 0.5)
     nbytes = (target.param_bytes() - 248320 * 1024 * 2 - head_bytes * (1 - 1 / world)
@@ -596,17 +604,19 @@ def run_sharded(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"sharded: mate target with {scheme} linears + 2-layer D=256 draft, k=6, T=1.0, "
                                    f"full-vocabulary rule, 32 requests/GPU, 1024-token prompts, LM head and acceptance "
-                                   f"split by vocabulary columns over {world} rank(s), exchanges staged through the host",
+                                   f"split by vocabulary columns over the ranks (NCCL all-gathers of device buffers)",
                        "per_gpu_requests": B, "context_tokens": ctx_len, "step": "one speculative round",
-                       "timing": "wall clock around the rounds (max over ranks)"},
+                       "l2": "weights larger than L2, no flush"},
+            "timing": spread(reps, args.steps),
+            "unsharded_round": {"ms_per_step": ms_p / args.steps, "ratio_sharded_over_unsharded": ms / ms_p,
+                                "same_tokens": bool(same_all), **spread(reps_p, args.steps)},
             "roofline": {"bound": "hbm", "kernel": "whole round (draft, verify, column-split head, sharded acceptance, "
-                                                   "host-staged exchanges)",
+                                                   "all-gathers)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "traffic": None, "algorithmic_bytes": nbytes},
-            "cpu_baseline": None, "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": None,
-                                          "d2h_bytes_per_step": None},
-            "gpu_launches": launches, "clocks": clk,
-            "accept_rate": float(eng.accept_len.numpy().mean() / k),
+            "cpu_baseline": None, "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0,
+                                          "d2h_bytes_per_step": 0},
+            "gpu_launches": launches, "clocks": clk, "accept_rate": accept_rate,
             "tokens_per_round_per_request": committed / world / B / args.steps,
         }))
     if dist is not None:

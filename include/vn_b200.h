@@ -43,6 +43,7 @@ enum vn_dtype { VN_F32 = 0, VN_BF16 = 1, VN_I8 = 2, VN_I4 = 3, VN_I64 = 4, VN_I3
 typedef struct vn_ctx vn_ctx;
 typedef struct vn_model vn_model;
 typedef struct vn_kv vn_kv;
+typedef struct vn_comm vn_comm;
 
 /* ---- lifecycle ------------------------------------------------------- */
 int32_t vn_version(void);
@@ -62,6 +63,9 @@ int32_t vn_memset(vn_ctx* ctx, void* dev, int32_t byte, size_t bytes);
 int32_t vn_h2d(vn_ctx* ctx, void* dst_dev, const void* src, size_t bytes);   /* synchronous */
 int32_t vn_d2h(vn_ctx* ctx, void* dst, const void* src_dev, size_t bytes);   /* synchronous */
 int32_t vn_d2d(vn_ctx* ctx, void* dst_dev, const void* src_dev, size_t bytes);
+/* `rows` rows of width_bytes each between two pitched device buffers (asynchronous, on the context's stream) */
+int32_t vn_copy_2d(vn_ctx* ctx, void* dst_dev, size_t dst_pitch, const void* src_dev, size_t src_pitch, size_t width_bytes,
+                   size_t rows);
 int32_t vn_host_alloc(vn_ctx* ctx, size_t bytes, void** out);                /* pinned */
 int32_t vn_host_free(vn_ctx* ctx, void* p);
 int32_t vn_h2d_async(vn_ctx* ctx, void* dst_dev, const void* src_pinned, size_t bytes);
@@ -122,6 +126,30 @@ int32_t vn_row_pick(vn_ctx* ctx, const float* p_dev, int64_t p_stride, const flo
                     int32_t V, float temperature, const int32_t* mode_dev, const float* m_p_dev, const double* s_p_dev,
                     const float* m_q_dev, const double* s_q_dev, const int64_t* removed_dev, const float* u_dev,
                     int64_t* out_token_dev);
+
+/* ---- collectives: the vocabulary-sharded LM head + acceptance is the one step of this path with an exchange.
+ * The reference's only collective is torch.distributed.all_reduce in its training loop
+ * (packages/verse_torch/verse_torch/training.py:2260-2266); nothing on its decode path communicates.
+ * NCCL is bound at run time (libnccl.so.2); without it these calls return VN_ERR_NCCL.  One communicator per context,
+ * all traffic on the context's stream, peers' data lands in this GPU's own memory before any kernel reads it. */
+int32_t vn_comm_unique_id(uint8_t* out128);      /* rank 0 makes it, every rank passes the same 128 bytes below */
+int32_t vn_comm_create(vn_ctx* ctx, const uint8_t* unique_id128, int32_t world, int32_t rank, vn_comm** out);
+int32_t vn_comm_destroy(vn_comm* comm);
+int32_t vn_comm_info(vn_comm* comm, int32_t* world, int32_t* rank);
+/* recv_dev [world][bytes_per_rank] <- every rank's send_dev [bytes_per_rank]; asynchronous on the stream */
+int32_t vn_all_gather(vn_comm* comm, const void* send_dev, void* recv_dev, size_t bytes_per_rank);
+/* Acceptance with the vocabulary split over the ranks of `comm` (NULL: one rank), decisions taken on the device:
+ * every rank passes its columns [v_lo, v_lo + Vs) of the target logits p_dev [Bt, k+1, Vs] and draft logits q_dev
+ * [Bt, k, Vs] (or NULL) of ALL Bt = world x B_local sequences, and the draft tokens draft_dev [Bt, k]; three
+ * all-gathers of a few numbers per row (softmax statistics, residual masses, the picked token) give every rank
+ * the same out_len_dev [Bt] / out_tokens_dev [Bt, k+1] as vn_accept on the unsplit logits (full-vocabulary rule,
+ * temperature > 0, bonus token).  Philox: sequence g draws as request g % B_local with seed + (g / B_local) *
+ * seed_stride, i.e. what rank g / B_local draws in its own vn_accept calls when it folds its rank into the seed
+ * the same way.  No host synchronisation. */
+int32_t vn_shard_accept(vn_ctx* ctx, vn_comm* comm, const float* p_dev, const float* q_dev, const int64_t* draft_dev,
+                        int32_t v_lo, int32_t Vs, float temperature, uint64_t seed, uint64_t seed_stride, uint32_t offset,
+                        int32_t B_local, int32_t Bt, int32_t k, int32_t bonus, int32_t* out_len_dev,
+                        int64_t* out_tokens_dev);
 
 /* ---- acceptance / rejection sampling ---------------------------------- */
 /* Replaces the argmax compare + accept loop of SpeculativeDecoder

@@ -262,17 +262,23 @@ def _engine_worker(rank, world, port, out):
             m.load_state_dict(sd)
             models.append(m)
         prompts = np.random.default_rng(100 + rank).integers(0, 1024, (4, 20))
-        kw = dict(max_batch=4, max_seq=128, k=3, temperature=0.9, seed=17 + rank)
-        plain = _engine_tokens(vn.SpecEngine(models[0], models[1], top_k=0, graph=False, **kw), prompts, 5)
-        shard = _engine_tokens(ShardedSpecEngine(models[0], models[1], **kw), prompts, 5)
+        from versenext_b200.comm import Comm
+        from versenext_b200.sharded_engine import rank_seed
+        comm = Comm.from_torch_group(ctx)
+        kw = dict(max_batch=4, max_seq=128, k=3, temperature=0.9)
+        # the plain engine of this rank draws with the seed the sharded engine gives this rank's requests
+        plain = _engine_tokens(vn.SpecEngine(models[0], models[1], top_k=0, graph=False, seed=rank_seed(17, rank), **kw),
+                               prompts, 5)
+        shard = _engine_tokens(ShardedSpecEngine(models[0], models[1], seed=17, comm=comm, **kw), prompts, 5)
         out.put((rank, all(np.array_equal(a, b) for a, b in zip(plain, shard)), sum(len(a) for a in plain)))
     finally:
         dist.destroy_process_group()
 
 
 def test_sharded_engine_two_ranks_over_nccl():
-    """Two processes, two GPUs: requests split over the ranks and the head split by columns; every rank commits the
-    tokens its plain single-GPU engine commits for the same requests (needs two GPUs; skipped on one)."""
+    """Two processes, two GPUs: requests split over the ranks and the head split by columns, hidden rows and per-row
+    statistics exchanged by the library's own NCCL all-gathers, decisions taken on the device; every rank commits
+    the tokens its plain single-GPU engine commits for the same requests (needs two GPUs; skipped on one)."""
     import socket
     import torch
     if torch.cuda.device_count() < 2:

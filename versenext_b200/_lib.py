@@ -53,6 +53,7 @@ PROTOTYPES = {
     "vn_h2d": [_p, _p, _p, _sz],
     "vn_d2h": [_p, _p, _p, _sz],
     "vn_d2d": [_p, _p, _p, _sz],
+    "vn_copy_2d": [_p, _p, _sz, _p, _sz, _sz, _sz],
     "vn_host_alloc": [_p, _sz, C.POINTER(_p)],
     "vn_host_free": [_p, _p],
     "vn_h2d_async": [_p, _p, _p, _sz],
@@ -82,6 +83,12 @@ PROTOTYPES = {
     "vn_topk_row_bytes": [],
     "vn_verify_accept": [_p, _p, _p, _i32, _i32, _i32, _p, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _u64, _u32, _f32,
                          _i32, _i32, _p, _p, _p],
+    "vn_comm_unique_id": [_p],
+    "vn_comm_create": [_p, _p, _i32, _i32, C.POINTER(_p)],
+    "vn_comm_destroy": [_p],
+    "vn_comm_info": [_p, C.POINTER(_i32), C.POINTER(_i32)],
+    "vn_all_gather": [_p, _p, _p, _sz],
+    "vn_shard_accept": [_p, _p, _p, _p, _p, _i32, _i32, _f32, _u64, _u64, _u32, _i32, _i32, _i32, _i32, _p, _p],
     "vn_spec_gather": [_p, _p, _p, _i32, _i32, _i32, _p, _p],
     "vn_spec_advance": [_p, _p, _i32, _i32, _p, _p, _i32, _p, _p],
     "vn_set_offset_source": [_p, _p],

@@ -111,6 +111,16 @@ int32_t vn_d2d(vn_ctx* ctx, void* dst_dev, const void* src_dev, size_t bytes) {
   return VN_OK;
 }
 
+int32_t vn_copy_2d(vn_ctx* ctx, void* dst_dev, size_t dst_pitch, const void* src_dev, size_t src_pitch, size_t width_bytes,
+                   size_t rows) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, dst_pitch >= width_bytes && src_pitch >= width_bytes, "pitch below the row width");
+  if (width_bytes == 0 || rows == 0) return VN_OK;
+  VN_CUDA(ctx, cudaMemcpy2DAsync(dst_dev, dst_pitch, src_dev, src_pitch, width_bytes, rows, cudaMemcpyDeviceToDevice,
+                                 ctx->stream));
+  return VN_OK;
+}
+
 int32_t vn_host_alloc(vn_ctx* ctx, size_t bytes, void** out) {
   VN_CHECK_CTX(ctx);
   VN_REQUIRE(ctx, out, "out is null");

@@ -1052,7 +1052,7 @@ accept_topk_decide_kernel(DecideArgs da) {
 // and the call's fallback flag.
 __global__ void __launch_bounds__(1024)
 k1_bound_kernel(const float* __restrict__ boot, int nb, int top_k, float temp, float* __restrict__ tau,
-                int* __restrict__ count, int* __restrict__ fallback) {
+                int* __restrict__ count, int count_stride, int* __restrict__ fallback) {
   pdl_trigger();
   pdl_wait();
   __shared__ uint32_t s_max[1024];
@@ -1088,27 +1088,34 @@ k1_bound_kernel(const float* __restrict__ boot, int nb, int top_k, float temp, f
       }
     }
     tau[row] = t;
-    count[row] = 0;
+    count[(long long)row * count_stride] = 0;
     if (row == 0) *fallback = 0;
   }
 }
 
-// One CTA per target row: candidates (raw logit, token) -> the kept list the select kernel would have produced:
-// every entry whose scaled value is >= the k-th largest scaled value, ascending token id.  The k-th largest is found
-// by rank counting over the candidates in shared memory.  A list that ran past its capacity, or more than KEEP_MAX
-// kept entries, raises the fallback flag instead.
-__global__ void __launch_bounds__(1024)
+// One CTA (256 threads) per target row: candidates (raw logit, token) -> the kept list the select kernel would have
+// produced: every entry whose scaled value is >= the k-th largest scaled value, ascending token id.  Rank counting
+// over all candidates would cost n^2 comparisons, so the list is first cut down the same way the bound was made:
+// the k-th largest of the per-thread maxima bounds the k-th largest candidate from below, and only the candidates
+// at or above it (a few more than k as a rule) are ranked.  A list that ran past its capacity, or more than
+// KEEP_MAX kept entries, raises the fallback flag instead.
+constexpr int K1_FIN_THREADS = 256;
+__global__ void __launch_bounds__(K1_FIN_THREADS)
 k1_finish_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_tok, const int* __restrict__ count,
-                 int cap, int top_k, float temp, int V, TopkRow* __restrict__ out, int* __restrict__ fallback) {
+                 int count_stride, int cap, int top_k, float temp, int V, TopkRow* __restrict__ out,
+                 int* __restrict__ fallback) {
   pdl_trigger();
   pdl_wait();
   __shared__ uint32_t s_key[VN_K1_CAP];
+  __shared__ uint32_t s_gmax[K1_FIN_THREADS];
+  __shared__ int s_ci[KEEP_MAX];            // indices (into the candidate list) of the short list
+  __shared__ uint32_t s_ck[KEEP_MAX];
   __shared__ int s_ktok[KEEP_MAX];
   __shared__ uint32_t s_kkey[KEEP_MAX];
-  __shared__ uint32_t s_kth;
-  __shared__ int s_keep;
+  __shared__ uint32_t s_lo, s_kth;
+  __shared__ int s_nc, s_keep;
   const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
-  const int n = count[row];
+  const int n = count[(long long)row * count_stride];
   const int want = top_k < V ? top_k : V;
   TopkRow* o = out + row;
   if (n > cap || n < want) {                 // uniform over the CTA
@@ -1118,32 +1125,54 @@ k1_finish_kernel(const float* __restrict__ cand_val, const int* __restrict__ can
   const bool scale = temp != 1.0f;
   const float* cv = cand_val + (long long)row * cap;
   const int* ct = cand_tok + (long long)row * cap;
+  uint32_t gmax = 0u;
   for (int i = tid; i < n; i += nt) {
     const float x = cv[i];
-    s_key[i] = order_key(scale ? __fdiv_rn(x, temp) : x);
+    const uint32_t key = order_key(scale ? __fdiv_rn(x, temp) : x);
+    s_key[i] = key;
+    gmax = key > gmax ? key : gmax;
   }
-  if (tid == 0) { s_keep = 0; s_kth = 0u; }
+  s_gmax[tid] = gmax;                        // 0 (below every real key) for a thread without candidates
+  if (tid == 0) { s_lo = 0u; s_kth = 0u; s_nc = 0; s_keep = 0; }
   __syncthreads();
-  for (int i = tid; i < n; i += nt) {
-    const uint32_t me = s_key[i];
+  // lower bound of the k-th largest candidate: the k-th largest thread maximum (when at least k threads hold one)
+  {
+    const uint32_t me = s_gmax[tid];
     int greater = 0, geq = 0;
-    for (int j = 0; j < n; ++j) { const uint32_t k2 = s_key[j]; greater += k2 > me; geq += k2 >= me; }
-    if (greater < want && geq >= want) s_kth = me;      // every writer holds the same key
+    for (int j = 0; j < nt; ++j) { const uint32_t k2 = s_gmax[j]; greater += k2 > me; geq += k2 >= me; }
+    if (me != 0u && greater < want && geq >= want) s_lo = me;     // every writer holds the same key
   }
   __syncthreads();
-  const uint32_t kth = s_kth;
+  const uint32_t lo = s_lo;                  // 0: fewer than k threads have candidates, every candidate stays
   for (int i = tid; i < n; i += nt)
-    if (s_key[i] >= kth) {
-      const int slot = atomicAdd(&s_keep, 1);
-      if (slot < KEEP_MAX) { s_kkey[slot] = s_key[i]; s_ktok[slot] = ct[i]; }
+    if (s_key[i] >= lo) {
+      const int slot = atomicAdd(&s_nc, 1);
+      if (slot < KEEP_MAX) { s_ci[slot] = i; s_ck[slot] = s_key[i]; }
     }
   __syncthreads();
-  const int keep = s_keep;
-  if (keep > KEEP_MAX) {
+  const int nc = s_nc;
+  if (nc > KEEP_MAX) {                       // heavy ties around the bound: the stored-logits path sorts it out
     if (tid == 0) { atomicExch(fallback, 1); o->n = 0; o->overflow = 1; }
     return;
   }
-  // ascending token id: rank of each kept entry among the kept ones (a few dozen entries as a rule)
+  // exact k-th largest among the short list (it holds every candidate >= lo, so at least k of them)
+  for (int i = tid; i < nc; i += nt) {
+    const uint32_t me = s_ck[i];
+    int greater = 0, geq = 0;
+    for (int j = 0; j < nc; ++j) { const uint32_t k2 = s_ck[j]; greater += k2 > me; geq += k2 >= me; }
+    if (greater < want && geq >= want) s_kth = me;
+  }
+  __syncthreads();
+  const uint32_t kth = s_kth;
+  for (int i = tid; i < nc; i += nt)
+    if (s_ck[i] >= kth) {
+      const int slot = atomicAdd(&s_keep, 1);
+      s_kkey[slot] = s_ck[i];                // slot < nc <= KEEP_MAX
+      s_ktok[slot] = ct[s_ci[i]];
+    }
+  __syncthreads();
+  const int keep = s_keep;
+  // ascending token id: rank of each kept entry among the kept ones
   for (int i = tid; i < keep; i += nt) {
     const int ti = s_ktok[i];
     int pos = 0;
@@ -1152,6 +1181,194 @@ k1_finish_kernel(const float* __restrict__ cand_val, const int* __restrict__ can
     o->val[pos] = key_value(s_kkey[i]);
   }
   if (tid == 0) { o->n = keep; o->overflow = 0; }
+}
+
+
+// ---- acceptance over a vocabulary split across ranks, on the device -------------------------------------------------
+// Every rank holds columns [v_lo, v_lo + Vs) of the target and draft logits of ALL sequences (Bt = world x B of them).
+// Three all-gathers of a few numbers per row make every rank take identical decisions (each rank merges the ranks'
+// contributions in rank order, in float64):
+//   1. per row (max, sum exp) of the shard and the shard's scaled logit of the draft token (-inf when another shard
+//      owns it)  -> global softmax statistics, p(x), q(x), the accept tests, the row to sample;
+//   2. the shard's residual mass sum max(0, p - q) (and sum p) of that row  -> the shard that holds the sampled token
+//      (shards in ascending token order) and the fraction of its mass at which the token lies;
+//   3. the token picked inside that shard.
+// Same arithmetic as the single-GPU kernels above: float32 exp(x - max), float64 sums, accept iff u q(x) < p(x).
+
+// exchange 1, send side: [6][Bt][k+1] doubles = p max, p sum, p logit of x, q max, q sum, q logit of x (q padded at k)
+__global__ void shard_pack1_kernel(RowSet rs, int Bt, int k, int nchunks, const Partial* __restrict__ part, float temp,
+                                   const long long* __restrict__ draft, int v_lo, double* __restrict__ send) {
+  const int lane = threadIdx.x & 31;
+  const int rows_per_seq = rs.np + rs.nq;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= Bt * rows_per_seq) return;
+  const int b = r / rows_per_seq, j = r % rows_per_seq;
+  const Partial* pp = part + (long long)r * nchunks;
+  float m = -CUDART_INF_F;
+  for (int c = lane; c < nchunks; c += 32) m = fmaxf(m, pp[c].m);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  double s = 0.0;
+  for (int c = lane; c < nchunks; c += 32) {
+    const Partial p = pp[c];
+    if (p.m != -CUDART_INF_F) s += p.s * exp((double)(p.m - m));
+  }
+  s = warp_sum(s);
+  if (lane != 0) return;
+  const bool is_q = j >= rs.np;
+  const int pos = is_q ? j - rs.np : j;
+  double x = -CUDART_INF;
+  if (pos < k) {
+    const long long t = draft[(long long)b * k + pos] - v_lo;
+    if (t >= 0 && t < rs.V) x = (double)scaled(row_ptr(rs, b, j)[t], temp);
+  }
+  const long long plane = (long long)Bt * (k + 1), at = (long long)b * (k + 1) + pos;
+  const int f = is_q ? 3 : 0;
+  send[(f + 0) * plane + at] = (double)m;
+  send[(f + 1) * plane + at] = s;
+  send[(f + 2) * plane + at] = x;
+  if (!is_q && rs.nq == 0) {       // no draft rows: neutral padding so that the merge below needs no special case
+    send[3 * plane + at] = -CUDART_INF; send[4 * plane + at] = 0.0; send[5 * plane + at] = -CUDART_INF;
+  }
+  if (is_q && pos == k - 1) {      // pad the draft planes at position k
+    const long long ak = (long long)b * (k + 1) + k;
+    send[3 * plane + ak] = -CUDART_INF; send[4 * plane + ak] = 0.0; send[5 * plane + ak] = -CUDART_INF;
+  }
+}
+
+// after exchange 1: one thread per sequence merges the ranks' statistics, runs the accept tests and fixes the row to
+// sample.  Philox rows: sequence g of the gathered batch is request g % B_local of rank g / B_local, which draws
+// with seed + (g / B_local) * seed_stride -- the numbers that rank's own single-GPU engine draws.
+__global__ void shard_decide_kernel(const double* __restrict__ g1, int world, int Bt, int k, int has_q, int bonus,
+                                    const long long* __restrict__ draft, int v_lo, uint64_t seed, uint64_t seed_stride,
+                                    int B_local, uint32_t offset_host, const unsigned* __restrict__ offset_dev,
+                                    Decision* __restrict__ dec, int* __restrict__ out_len,
+                                    long long* __restrict__ out_tok) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= Bt) return;
+  const uint32_t offset = offset_host + (offset_dev ? *offset_dev : 0u);
+  const uint64_t sd = seed + (uint64_t)(b / B_local) * seed_stride;
+  const uint32_t prow = (uint32_t)(b % B_local);
+  const long long plane = (long long)Bt * (k + 1), rstride = 6 * plane;
+  auto merged = [&](int f, int pos, double& M, double& S, double& X) {
+    const long long at = (long long)b * (k + 1) + pos;
+    M = -CUDART_INF; X = -CUDART_INF;
+    for (int r = 0; r < world; ++r) {
+      M = fmax(M, g1[r * rstride + (f + 0) * plane + at]);
+      X = fmax(X, g1[r * rstride + (f + 2) * plane + at]);
+    }
+    S = 0.0;
+    for (int r = 0; r < world; ++r) {
+      const double mr = g1[r * rstride + (f + 0) * plane + at];
+      if (mr != -CUDART_INF) S += g1[r * rstride + (f + 1) * plane + at] * exp(mr - M);
+    }
+  };
+  Decision d;
+  d.mode = 0; d.pos = 0; d.x = -1; d.m_p = d.m_q = 0.f; d.inv_sp = d.inv_sq = 0.0; d.u = 0.f;
+  long long* tok = out_tok + (long long)b * (k + 1);
+  for (int i = 0; i <= k; ++i) tok[i] = -1;
+  int n = 0;
+  for (; n < k; ++n) {
+    double PM, PS, PX, QM = 0.0, QS = 1.0, QX = 0.0;
+    merged(0, n, PM, PS, PX);
+    const double p = PX == -CUDART_INF ? 0.0 : (double)expf((float)(PX - PM)) / PS;
+    double q = 1.0;
+    if (has_q) {
+      merged(3, n, QM, QS, QX);
+      q = QX == -CUDART_INF ? 0.0 : (double)expf((float)(QX - QM)) / QS;
+    }
+    const float u = philox_uniform(sd, offset, prow, n, 0);
+    if ((double)u * q < p) { tok[n] = draft[(long long)b * k + n]; continue; }
+    d.mode = has_q ? 1 : 3;
+    d.pos = n;
+    d.x = (int)(draft[(long long)b * k + n] - v_lo);      // column of this shard, or outside it
+    d.m_p = (float)PM; d.inv_sp = 1.0 / PS;
+    if (has_q) { d.m_q = (float)QM; d.inv_sq = 1.0 / QS; }
+    break;
+  }
+  if (d.mode == 0 && bonus) {
+    double PM, PS, PX;
+    merged(0, k, PM, PS, PX);
+    d.mode = 2; d.pos = k; d.m_p = (float)PM; d.inv_sp = 1.0 / PS;
+  }
+  if (d.mode) d.u = philox_uniform(sd, offset, prow, d.pos, 1);
+  d.n_acc = n;
+  out_len[b] = n;
+  dec[b] = d;
+}
+
+// exchange 2, send side: the shard's residual mass and p mass of every sequence's sampled row
+__global__ void shard_pack2_kernel(int Bt, int nchunks, const Decision* __restrict__ dec, const double* __restrict__ mass,
+                                   double* __restrict__ send) {
+  const int lane = threadIdx.x & 31;
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b >= Bt) return;
+  double r = 0.0, p = 0.0;
+  if (dec[b].mode) {
+    // chunk order: lane-strided partial sums added in a fixed tree, the same on every rank for its own data
+    for (int c = lane; c < nchunks; c += 32) { r += mass[((long long)b * nchunks + c) * 2]; p += mass[((long long)b * nchunks + c) * 2 + 1]; }
+  }
+  r = warp_sum(r); p = warp_sum(p);
+  if (lane == 0) { send[b * 2] = r; send[b * 2 + 1] = p; }
+}
+
+// after exchange 2: which shard owns the sampled token; the owner gets the fraction of its own mass as its uniform
+__global__ void shard_owner_kernel(const double* __restrict__ g2, int world, int rank, int Bt,
+                                   const Decision* __restrict__ dec, Decision* __restrict__ dec_pick) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= Bt) return;
+  Decision d = dec[b];
+  const int mode_in = d.mode;
+  d.mode = 0;
+  if (mode_in) {
+    double tot_r = 0.0;
+    for (int r = 0; r < world; ++r) tot_r += g2[((long long)r * Bt + b) * 2];
+    const int plain = !(tot_r > 0.0);                     // residual vanished everywhere: sample p itself
+    double total = 0.0;
+    for (int r = 0; r < world; ++r) total += g2[((long long)r * Bt + b) * 2 + plain];
+    const double target0 = (double)d.u * total;
+    double cum = 0.0, target = target0;
+    int owner = -1, last_nz = -1;
+    double before = 0.0;
+    for (int r = 0; r < world; ++r) {
+      const double w = g2[((long long)r * Bt + b) * 2 + plain];
+      if (w > 0.0) last_nz = r;
+      if (owner < 0 && cum + w > target0) { owner = r; before = cum; }
+      cum += w;
+    }
+    if (owner < 0) {                                      // rounding pushed the target past the total
+      owner = last_nz < 0 ? world - 1 : last_nz;
+      before = 0.0;
+      for (int r = 0; r < owner; ++r) before += g2[((long long)r * Bt + b) * 2 + plain];
+      target = before + g2[((long long)owner * Bt + b) * 2 + plain];
+    }
+    if (owner == rank) {
+      const double mine = g2[((long long)owner * Bt + b) * 2 + plain];
+      double frac = mine > 0.0 ? (target - before) / mine : 0.0;
+      frac = frac < 0.0 ? 0.0 : (frac > 1.0 ? 1.0 : frac);
+      d.mode = plain ? 2 : mode_in;
+      d.u = (float)frac;
+    }
+  }
+  dec_pick[b] = d;
+}
+
+// exchange 3, send side: the global id of the token this shard picked, or -1
+__global__ void shard_pack3_kernel(int Bt, int k, int v_lo, const Decision* __restrict__ dec_pick,
+                                   const long long* __restrict__ picked, long long* __restrict__ send) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= Bt) return;
+  const Decision d = dec_pick[b];
+  send[b] = d.mode ? picked[(long long)b * (k + 1) + d.n_acc] + v_lo : -1;
+}
+
+__global__ void shard_finish_kernel(const long long* __restrict__ g3, int world, int Bt, int k,
+                                    const Decision* __restrict__ dec, long long* __restrict__ out_tok) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= Bt || dec[b].mode == 0) return;
+  long long t = -1;
+  for (int r = 0; r < world; ++r) t = max(t, g3[(long long)r * Bt + b]);
+  out_tok[(long long)b * (k + 1) + dec[b].pos] = t;
 }
 
 }  // namespace
@@ -1339,6 +1556,92 @@ static int32_t row_residual_chunks(vn_ctx* ctx, const RowSet& rs, bool vec, int 
   return VN_OK;
 }
 
+struct vn_comm;
+int32_t vn_comm_gather(vn_ctx* ctx, vn_comm* c, const void* send_dev, void* recv_dev, size_t bytes_per_rank, int* world,
+                       int* rank);
+
+extern "C" int32_t vn_shard_accept(vn_ctx* ctx, vn_comm* comm, const float* p_dev, const float* q_dev,
+                                   const int64_t* draft_dev, int32_t v_lo, int32_t Vs, float temperature, uint64_t seed,
+                                   uint64_t seed_stride, uint32_t offset, int32_t B_local, int32_t Bt, int32_t k,
+                                   int32_t bonus, int32_t* out_len_dev, int64_t* out_tokens_dev) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, p_dev && draft_dev && out_len_dev && out_tokens_dev, "null argument");
+  VN_REQUIRE(ctx, temperature > 0.f, "the sharded rule is the stochastic one (temperature > 0)");
+  VN_REQUIRE(ctx, Bt >= 1 && k >= 1 && k <= MAX_K && Vs >= 0 && B_local >= 1 && Bt % B_local == 0, "bad sizes");
+  int world = 1, rank = 0;
+  vn_comm_gather(ctx, comm, nullptr, nullptr, 0, &world, &rank);
+  VN_REQUIRE(ctx, Bt == world * B_local, "Bt (%d) must be world (%d) x B_local (%d)", Bt, world, B_local);
+  const float temp = fmaxf(temperature, 1e-8f);
+  const int np = bonus ? k + 1 : k;
+  VN_REQUIRE(ctx, bonus, "the sharded round always scores k + 1 positions");
+  RowSet rs;
+  rs.p = p_dev; rs.q = q_dev; rs.np = np; rs.nq = q_dev ? k : 0;
+  rs.p_sb = (long long)np * Vs; rs.p_si = Vs; rs.q_sb = (long long)k * Vs; rs.q_si = Vs; rs.V = Vs;
+  const int rows_per_seq = rs.np + rs.nq;
+  const int nchunks = std::max(1, ceil_div(Vs, CHUNK));
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t n_part = (size_t)Bt * rows_per_seq * nchunks;
+  const size_t plane1 = (size_t)6 * Bt * (k + 1) * sizeof(double);
+  const size_t o_part = 0;
+  const size_t o_s1 = up(o_part + n_part * sizeof(Partial));
+  const size_t o_g1 = up(o_s1 + plane1);
+  const size_t o_dec = up(o_g1 + plane1 * world);
+  const size_t o_dec2 = up(o_dec + (size_t)Bt * sizeof(Decision));
+  const size_t o_mass = up(o_dec2 + (size_t)Bt * sizeof(Decision));
+  const size_t o_s2 = up(o_mass + (size_t)Bt * nchunks * 2 * sizeof(double));
+  const size_t o_g2 = up(o_s2 + (size_t)Bt * 2 * sizeof(double));
+  const size_t o_pick = up(o_g2 + (size_t)Bt * 2 * sizeof(double) * world);
+  const size_t o_s3 = up(o_pick + (size_t)Bt * (k + 1) * sizeof(long long));
+  const size_t o_g3 = up(o_s3 + (size_t)Bt * sizeof(long long));
+  const size_t total = o_g3 + (size_t)Bt * sizeof(long long) * world;
+  void* ws;
+  int32_t st = vn_workspace(ctx, total, &ws);
+  if (st) return st;
+  char* base = (char*)ws;
+  Partial* part = (Partial*)(base + o_part);
+  double* s1 = (double*)(base + o_s1); double* g1 = (double*)(base + o_g1);
+  Decision* dec = (Decision*)(base + o_dec); Decision* dec2 = (Decision*)(base + o_dec2);
+  double* mass = (double*)(base + o_mass);
+  double* s2 = (double*)(base + o_s2); double* g2 = (double*)(base + o_g2);
+  long long* picked = (long long*)(base + o_pick);
+  long long* s3 = (long long*)(base + o_s3); long long* g3 = (long long*)(base + o_g3);
+  const long long* d64 = reinterpret_cast<const long long*>(draft_dev);
+  long long* o64 = reinterpret_cast<long long*>(out_tokens_dev);
+  auto aligned16 = [](const void* ptr) { return ((uintptr_t)ptr & 15) == 0; };
+  const bool vec = (Vs % 4 == 0) && aligned16(rs.p) && (!rs.nq || aligned16(rs.q));
+  // ---- exchange 1
+  if (Vs > 0) {
+    const int grid = (int)std::min<long long>((long long)Bt * rows_per_seq * ((nchunks + 1) / 2), (long long)ctx->sm_count * 8);
+    st = launch_accept_stats(ctx, vec, false, grid, rs, Bt, nchunks, temp, part);
+    if (st) return st;
+  } else {
+    VN_CUDA(ctx, cudaMemsetAsync(part, 0xff, n_part * sizeof(Partial), ctx->stream));   // unreachable in practice
+  }
+  VN_LAUNCH(ctx, shard_pack1_kernel, ceil_div(Bt * rows_per_seq, 4), 128, 0, rs, Bt, k, nchunks, (const Partial*)part, temp, d64,
+            v_lo, s1);
+  st = vn_comm_gather(ctx, comm, s1, g1, plane1, nullptr, nullptr);
+  if (st) return st;
+  VN_LAUNCH(ctx, shard_decide_kernel, ceil_div(Bt, 128), 128, 0, (const double*)g1, world, Bt, k, rs.nq ? 1 : 0, bonus, d64,
+            v_lo, seed, seed_stride, B_local, offset, ctx->offset_src, dec, out_len_dev, o64);
+  // ---- exchange 2
+  {
+    dim3 g(nchunks, Bt);
+    if (vec) VN_LAUNCH(ctx, accept_residual_kernel<true>, g, STATS_THREADS, 0, rs, nchunks, temp, (const Decision*)dec, mass);
+    else     VN_LAUNCH(ctx, accept_residual_kernel<false>, g, STATS_THREADS, 0, rs, nchunks, temp, (const Decision*)dec, mass);
+  }
+  VN_LAUNCH(ctx, shard_pack2_kernel, ceil_div(Bt, 4), 128, 0, Bt, nchunks, (const Decision*)dec, (const double*)mass, s2);
+  st = vn_comm_gather(ctx, comm, s2, g2, (size_t)Bt * 2 * sizeof(double), nullptr, nullptr);
+  if (st) return st;
+  VN_LAUNCH(ctx, shard_owner_kernel, ceil_div(Bt, 128), 128, 0, (const double*)g2, world, rank, Bt, (const Decision*)dec, dec2);
+  // ---- exchange 3
+  VN_LAUNCH(ctx, accept_pick_kernel, Bt, STATS_THREADS, 0, rs, k, nchunks, temp, (const Decision*)dec2, (const double*)mass, picked);
+  VN_LAUNCH(ctx, shard_pack3_kernel, ceil_div(Bt, 128), 128, 0, Bt, k, v_lo, (const Decision*)dec2, (const long long*)picked, s3);
+  st = vn_comm_gather(ctx, comm, s3, g3, (size_t)Bt * sizeof(long long), nullptr, nullptr);
+  if (st) return st;
+  VN_LAUNCH(ctx, shard_finish_kernel, ceil_div(Bt, 128), 128, 0, (const long long*)g3, world, Bt, k, (const Decision*)dec, o64);
+  return VN_OK;
+}
+
 size_t vn_topk_row_bytes_impl() { return sizeof(TopkRow); }
 
 int32_t vn_k1_layout(vn_ctx* ctx, int B, int np, int top_k, int V, vn_k1* out) {
@@ -1356,7 +1659,8 @@ int32_t vn_k1_layout(vn_ctx* ctx, int B, int np, int top_k, int V, vn_k1* out) {
   const size_t o_boot = 0;
   const size_t o_tau = up(o_boot + (size_t)k.rows * k.nb * 4);
   const size_t o_cnt = up(o_tau + (size_t)k.rows * 4);
-  const size_t o_flag = up(o_cnt + (size_t)k.rows * 4);
+  k.count_stride = 32;                           // one 128-byte line per row's counter: the epilogue's atomics spread over L2
+  const size_t o_flag = up(o_cnt + (size_t)k.rows * k.count_stride * 4);
   const size_t o_val = up(o_flag + 256);
   const size_t o_tok = up(o_val + (size_t)k.rows * k.cap * 4);
   const size_t o_lists = up(o_tok + (size_t)k.rows * k.cap * 4);
@@ -1375,8 +1679,10 @@ int32_t vn_k1_layout(vn_ctx* ctx, int B, int np, int top_k, int V, vn_k1* out) {
 
 int32_t vn_k1_bound(vn_ctx* ctx, const vn_k1& k1, int top_k, float temp) {
   VN_REQUIRE(ctx, top_k >= 1, "top_k must be positive");
-  VN_LAUNCH_PDL(ctx, k1_bound_kernel, k1.rows, 1024, 0, (const float*)k1.boot, k1.nb, top_k, temp, k1.tau, k1.count,
-                k1.fallback);
+  // 256 threads: the k-th largest of 256 group maxima costs 256 x 256 comparisons, four times that many threads
+  // would cost sixteen times as many for a bound that is hardly tighter
+  VN_LAUNCH_PDL(ctx, k1_bound_kernel, k1.rows, 256, 0, (const float*)k1.boot, k1.nb, top_k, temp, k1.tau, k1.count,
+                k1.count_stride, k1.fallback);
   return VN_OK;
 }
 
@@ -1391,8 +1697,8 @@ int32_t vn_k1_accept(vn_ctx* ctx, const vn_k1& k1, const float* p_fallback, long
   const int np = bonus ? k + 1 : k;
   VN_REQUIRE(ctx, k1.rows == B * np, "candidate buffers were laid out for another shape");
   TopkRow* p_rows = (TopkRow*)k1.p_lists;
-  VN_LAUNCH_PDL(ctx, k1_finish_kernel, k1.rows, 1024, 0, (const float*)k1.cand_val, (const int*)k1.cand_tok,
-                (const int*)k1.count, k1.cap, top_k, temp, V, p_rows, k1.fallback);
+  VN_LAUNCH_PDL(ctx, k1_finish_kernel, k1.rows, K1_FIN_THREADS, 0, (const float*)k1.cand_val, (const int*)k1.cand_tok,
+                (const int*)k1.count, k1.count_stride, k1.cap, top_k, temp, V, p_rows, k1.fallback);
   if (p_fallback) {
     // classic select on the stored logits, only when the flag is up (its kernels return at once otherwise)
     RowSet rs;

@@ -113,18 +113,16 @@ int32_t vn_all_gather(vn_comm* c, const void* send_dev, void* recv_dev, size_t b
 
 }  // extern "C"
 
-// used by the sharded acceptance (accept.cu)
-int32_t vn_comm_gather(vn_comm* c, const void* send_dev, void* recv_dev, size_t bytes_per_rank, int* world, int* rank) {
+// used by the sharded acceptance (accept.cu): a missing communicator is a world of one
+int32_t vn_comm_gather(vn_ctx* ctx, vn_comm* c, const void* send_dev, void* recv_dev, size_t bytes_per_rank, int* world,
+                       int* rank) {
   if (world) *world = c ? c->world : 1;
   if (rank) *rank = c ? c->rank : 0;
+  if (bytes_per_rank == 0) return VN_OK;
   if (!c || c->world == 1) {
-    // a single rank: the gathered array is the rank's own contribution
-    cudaError_t e = cudaSuccess;
-    if (send_dev != recv_dev && bytes_per_rank) {
-      vn_ctx* ctx = c ? c->ctx : nullptr;
-      e = cudaMemcpyAsync(recv_dev, send_dev, bytes_per_rank, cudaMemcpyDeviceToDevice, ctx ? ctx->stream : 0);
-    }
-    return e == cudaSuccess ? VN_OK : vn_fail(c ? c->ctx : nullptr, VN_ERR_CUDA, "copy failed: %s", cudaGetErrorString(e));
+    if (send_dev != recv_dev)
+      VN_CUDA(ctx, cudaMemcpyAsync(recv_dev, send_dev, bytes_per_rank, cudaMemcpyDeviceToDevice, ctx->stream));
+    return VN_OK;
   }
   return vn_all_gather(c, send_dev, recv_dev, bytes_per_rank);
 }

@@ -44,7 +44,8 @@ struct TcRope {
 // `cap`, entries beyond it are dropped and the consumer sees the overflow from the count).
 struct CandBuf {
   const float* tau = nullptr;   // [rows] raw-logit bound per token row
-  int* count = nullptr;         // [rows]
+  int* count = nullptr;         // row r's counter at count[r * count_stride]
+  int count_stride = 1;
   float* val = nullptr;         // [rows][cap] raw logits
   int* tok = nullptr;           // [rows][cap] feature (vocabulary) index
   int cap = 0;
@@ -211,7 +212,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
         if (lane == i) mymask = bal;
       }
       int mybase = 0;
-      if (mymask) mybase = atomicAdd(g.cand.count + row0 + m0 + lane, __popc(mymask));
+      if (mymask) mybase = atomicAdd(g.cand.count + (long long)(row0 + m0 + lane) * g.cand.count_stride, __popc(mymask));
       if (__any_sync(0xffffffffu, mymask != 0u)) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {

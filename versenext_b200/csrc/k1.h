@@ -9,7 +9,8 @@ struct vn_k1 {
   int nb = 0;              // head columns of the bound GEMM
   float* boot = nullptr;   // [rows][nb] logits of the first nb vocabulary columns
   float* tau = nullptr;    // [rows] raw-logit lower bound of the row's k-th largest logit
-  int* count = nullptr;    // [rows] candidates appended by the head GEMM's epilogue
+  int* count = nullptr;    // [rows * count_stride] candidates appended by the head GEMM's epilogue (row r at r * count_stride)
+  int count_stride = 1;
   float* cand_val = nullptr;
   int* cand_tok = nullptr;  // [rows][cap]
   int* fallback = nullptr;  // device flag: a candidate list overflowed, the classic path below has to run

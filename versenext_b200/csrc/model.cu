@@ -1421,7 +1421,7 @@ int32_t vn_verify_accept(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
   const bool k1_on = !(k1_env && k1_env[0] == '0');
   const bool fused_head = k1_on && c.bf16 && m->use_tc && !m->qmode && (long long)B * T <= 256 && c.dim % 8 == 0 &&
                           c.dim <= 2048 && tc_detail::encode_fn() != nullptr && temperature > 0.f && top_k > 0 &&
-                          top_k < V && top_k <= 1024 && V >= 1024;
+                          top_k < V && top_k <= 128 && V >= 1024;
   if (!fused_head) {
     // logits through HBM: the forward with the head, then the acceptance kernels on the stored rows
     if (!p_logits_scratch_dev)
@@ -1451,7 +1451,7 @@ int32_t vn_verify_accept(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
   TRY(vn_k1_bound(ctx, k1, top_k, temp));
   // (2) the whole head: logits at or above the bound go to the rows' candidate lists, nothing else leaves the SMs
   tc_detail::CandBuf cb;
-  cb.tau = k1.tau; cb.count = k1.count; cb.val = k1.cand_val; cb.tok = k1.cand_tok; cb.cap = k1.cap;
+  cb.tau = k1.tau; cb.count = k1.count; cb.count_stride = k1.count_stride; cb.val = k1.cand_val; cb.tok = k1.cand_tok; cb.cap = k1.cap;
   TcPlan filt;
   filt.error_flag = m->tc_error; filt.filter = &cb;
   g.C = nullptr; g.ldc = V; g.N = V; g.tag = "gemm_head_filter";

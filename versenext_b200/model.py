@@ -315,7 +315,7 @@ class VerseNexLM:
     # -- forward -----------------------------------------------------------------
     def forward_cached(self, tokens, cache: KVCache, parents=None, last_only: bool = False,
                        want_logits: bool = True, want_hidden: bool = False, slot_offset: int = 0,
-                       out_logits: Optional[DeviceArray] = None):
+                       out_logits: Optional[DeviceArray] = None, out_hidden: Optional[DeviceArray] = None):
         """T new positions per sequence on top of `cache` (appended, not yet committed).
 
         tokens (B, T) int64 host or device; parents: list of T tree parents (-1 = child of the last
@@ -329,7 +329,7 @@ class VerseNexLM:
         if want_logits:
             logits = out_logits if out_logits is not None else self.ctx.empty((B, rows, self.vocab_size), np.float32)
         if want_hidden:
-            hidden = self.ctx.empty((B, rows, self.dim), np.float32)
+            hidden = out_hidden if out_hidden is not None else self.ctx.empty((B, rows, self.dim), np.float32)
         par = None
         if parents is not None:
             par = np.ascontiguousarray(parents, dtype=np.int32)
