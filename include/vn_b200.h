@@ -271,6 +271,10 @@ int32_t vn_model_status(vn_model* m, int32_t* bad_token, int32_t* wait_timeout);
  * with per-sequence lengths (verse_nex/kv_cache_parallel.py:42-283). */
 int32_t vn_kv_create(vn_model* m, int32_t max_batch, int32_t max_seq, vn_kv** out);
 int32_t vn_kv_destroy(vn_kv* kv);
+/* A second handle on sequences [first, first + count) of a cache: forwards, commits, resets and length calls on it
+ * act on those sequences only (a serving loop prefills one free slot while the others keep their state).  The view
+ * shares the parent's memory; destroy it before the parent. */
+int32_t vn_kv_view(vn_kv* kv, int32_t first, int32_t count, vn_kv** out);
 int32_t vn_kv_reset_seq(vn_kv* kv, int32_t seq);          /* seq < 0: all */
 int32_t vn_kv_lengths(vn_kv* kv, int32_t* out_host);      /* [max_batch] */
 int32_t vn_kv_set_lengths(vn_kv* kv, const int32_t* lens_host);

@@ -482,3 +482,57 @@ def test_quantise_needs_bf16_and_known_scheme():
         m.quantize("int8")
     with pytest.raises(ValueError):
         m.quantize("fp3")
+
+
+# ---- generate() and serving through the speculative engine ---------------------------------------------------------
+def test_generate_through_the_engine_equals_the_reference_streams(golden):
+    """`generate(..., draft=...)`: greedy decoding routed through the speculative engine gives the reference's
+    greedy streams (whole-sequence route, temperature 0) and the recurrent route's output (default arguments:
+    last prompt token fed twice) token for token."""
+    g = golden("model_small.npz")
+    t = build(OM.small_config(), _sd(g, "a_t."))
+    d = build(OM.small_config(n_layer=1), _sd(g, "a_d."))
+    np.testing.assert_array_equal(t.generate(g["prompt"], max_new_tokens=128, temperature=0.0, draft=d), g["a_greedy"])
+    t_cfg, t_sd, d_cfg, d_sd = variant_b()
+    t2, d2 = build(t_cfg, t_sd), build(d_cfg, d_sd)
+    np.testing.assert_array_equal(t2.generate(g["prompt"], max_new_tokens=96, temperature=0.0, draft=d2, k=3), g["b_greedy"])
+    r = golden("recurrent_reference.npz")
+    for tag in ("alibi", "rope"):
+        cfg, sd = _recurrent_case(r, tag)
+        m = build(cfg, sd)
+        dsd = dict(sd)
+        toks = r[f"{tag}_tokens"]
+        W = cfg.window_size
+        # the model drafts for itself: every proposal is accepted, the stream is the reference's
+        np.testing.assert_array_equal(m.generate(toks[:, :W + 5], max_new_tokens=W + 7, draft=m), r[f"{tag}_generate"])
+        eos = int(r[f"{tag}_generate"][0, W + 6])
+        np.testing.assert_array_equal(m.generate(toks[:1, :6], max_new_tokens=12, eos_id=eos, draft=m),
+                                      r[f"{tag}_generate_eos"])
+
+
+def test_continuous_batching_serves_ragged_requests():
+    """Seven requests of different prompt lengths and token budgets on three slots: a request leaves its slot when it
+    is done and the next one is prefilled into it; every request's tokens equal its own greedy generation."""
+    import versenext_b200 as vn
+    t_cfg, t_sd, d_cfg, d_sd = variant_b()
+    t, d = build(t_cfg, t_sd), build(d_cfg, d_sd)
+    rng = np.random.default_rng(77)
+    lens = [5, 17, 9, 30, 2, 12, 21]
+    budgets = [20, 7, 33, 12, 25, 1, 16]
+    prompts = [rng.integers(0, 256, n).astype(np.int64) for n in lens]
+    eng = vn.SpecEngine(t, d, max_batch=3, max_seq=128, k=4, temperature=0.0, bonus=True, max_new_tokens=40)
+    got = eng.serve(prompts, budgets, poll_every=2)
+    for p, n, out in zip(prompts, budgets, got):
+        want = t.generate(p[None], max_new_tokens=n, temperature=0.0)[0, len(p):]
+        np.testing.assert_array_equal(out, want)
+    # EOS: a request stops at its first EOS token, which is kept
+    eos = int(got[2][10])
+    got2 = eng.serve(prompts, budgets, eos_id=eos, poll_every=3)
+    for p, n, full, out in zip(prompts, budgets, got, got2):
+        hit = np.flatnonzero(full == eos)
+        want = full[:hit[0] + 1] if hit.size else full
+        np.testing.assert_array_equal(out, want)
+    with pytest.raises(ValueError):
+        eng.serve([np.array([1])], 4)
+    with pytest.raises(IndexError):
+        eng.admit(5, prompts[0])

@@ -113,6 +113,7 @@ PROTOTYPES = {
     "vn_model_status": [_p, C.POINTER(_i32), C.POINTER(_i32)],
     "vn_kv_create": [_p, _i32, _i32, C.POINTER(_p)],
     "vn_kv_destroy": [_p],
+    "vn_kv_view": [_p, _i32, _i32, C.POINTER(_p)],
     "vn_kv_reset_seq": [_p, _i32],
     "vn_kv_lengths": [_p, _p],
     "vn_kv_set_lengths": [_p, _p],

@@ -154,7 +154,14 @@ struct vn_kv {
   void** planes_dev = nullptr;  // [2 * n_layer] device array of plane pointers (k0, v0, k1, v1, ...)
   int* lens = nullptr;       // device [max_batch]
   std::vector<int> len_ub;   // host upper bound of every length
+  vn_kv* parent = nullptr;   // set for a view (vn_kv_view): planes and lengths belong to the parent
+  int parent_first = 0;      // first sequence of the parent this view covers
 };
+
+// host upper bound of sequence b's length; a view shares its parent's record
+static inline int& kv_ub(vn_kv* kv, int b) {
+  return kv->parent ? kv->parent->len_ub[kv->parent_first + b] : kv->len_ub[b];
+}
 
 namespace {
 
@@ -1246,11 +1253,39 @@ int32_t vn_kv_destroy(vn_kv* kv) {
   if (!kv) return VN_OK;
   cudaSetDevice(kv->m->ctx->device);
   cudaStreamSynchronize(kv->m->ctx->stream);
-  for (void* p : kv->k) cudaFree(p);
-  for (void* p : kv->v) cudaFree(p);
+  if (!kv->parent) {
+    for (void* p : kv->k) cudaFree(p);
+    for (void* p : kv->v) cudaFree(p);
+    if (kv->lens) cudaFree(kv->lens);
+  }
   if (kv->planes_dev) cudaFree(kv->planes_dev);
-  if (kv->lens) cudaFree(kv->lens);
   delete kv;
+  return VN_OK;
+}
+
+int32_t vn_kv_view(vn_kv* kv, int32_t first, int32_t count, vn_kv** out) {
+  if (!kv || !out) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
+  vn_model* m = kv->m;
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  if (first < 0 || count < 1 || first + count > kv->max_batch)
+    return vn_fail(ctx, VN_ERR_INDEX, "sequences [%d, %d) outside the cache's %d", first, first + count, kv->max_batch);
+  vn_kv* v = new vn_kv();
+  v->m = m; v->max_batch = count; v->max_seq = kv->max_seq;
+  v->parent = kv->parent ? kv->parent : kv;
+  v->parent_first = kv->parent_first + first;
+  const size_t seq_bytes = (size_t)kv->max_seq * m->cfg.n_kv * m->cfg.hd * m->esz;
+  std::vector<void*> planes;
+  for (int i = 0; i < m->cfg.n_layer; ++i) {
+    v->k.push_back((char*)kv->k[i] + (size_t)first * seq_bytes);
+    v->v.push_back((char*)kv->v[i] + (size_t)first * seq_bytes);
+    planes.push_back(v->k.back()); planes.push_back(v->v.back());
+  }
+  if (dev_alloc(ctx, (void**)&v->planes_dev, planes.size() * sizeof(void*)) != VN_OK) { delete v; return VN_ERR_OOM; }
+  VN_CUDA(ctx, cudaMemcpyAsync(v->planes_dev, planes.data(), planes.size() * sizeof(void*), cudaMemcpyHostToDevice, ctx->stream));
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  v->lens = kv->lens + first;
+  *out = v;
   return VN_OK;
 }
 
@@ -1260,7 +1295,7 @@ int32_t vn_kv_lengths(vn_kv* kv, int32_t* out_host) {
   VN_CHECK_CTX(ctx);
   VN_CUDA(ctx, cudaMemcpyAsync(out_host, kv->lens, (size_t)kv->max_batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  for (int b = 0; b < kv->max_batch; ++b) kv->len_ub[b] = out_host[b];
+  for (int b = 0; b < kv->max_batch; ++b) kv_ub(kv, b) = out_host[b];
   return VN_OK;
 }
 
@@ -1273,7 +1308,7 @@ int32_t vn_kv_set_lengths(vn_kv* kv, const int32_t* lens_host) {
       return vn_fail(ctx, VN_ERR_OVERFLOW, "length %d of sequence %d outside [0, %d]", lens_host[b], b, kv->max_seq);
   VN_CUDA(ctx, cudaMemcpyAsync(kv->lens, lens_host, (size_t)kv->max_batch * 4, cudaMemcpyHostToDevice, ctx->stream));
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  for (int b = 0; b < kv->max_batch; ++b) kv->len_ub[b] = lens_host[b];
+  for (int b = 0; b < kv->max_batch; ++b) kv_ub(kv, b) = lens_host[b];
   return VN_OK;
 }
 
@@ -1284,10 +1319,10 @@ int32_t vn_kv_reset_seq(vn_kv* kv, int32_t seq) {
   if (seq >= kv->max_batch) return vn_fail(ctx, VN_ERR_INDEX, "sequence %d out of range (%d)", seq, kv->max_batch);
   if (seq < 0) {
     VN_CUDA(ctx, cudaMemsetAsync(kv->lens, 0, (size_t)kv->max_batch * 4, ctx->stream));
-    std::fill(kv->len_ub.begin(), kv->len_ub.end(), 0);
+    for (int b = 0; b < kv->max_batch; ++b) kv_ub(kv, b) = 0;
   } else {
     VN_CUDA(ctx, cudaMemsetAsync(kv->lens + seq, 0, 4, ctx->stream));
-    kv->len_ub[seq] = 0;
+    kv_ub(kv, seq) = 0;
   }
   return VN_OK;
 }
@@ -1320,7 +1355,7 @@ int32_t vn_kv_commit(vn_kv* kv, int32_t n_new, const int32_t* keep_idx_dev, int3
     }
   }
   VN_LAUNCH_PDL(ctx, kv_advance_kernel, ceil_div(B, 128), 128, 0, kv->lens, n_keep_dev, keep_add, n_new, kv->max_seq, B);
-  for (int b = 0; b < B; ++b) kv->len_ub[b] = std::min(kv->len_ub[b] + n_new, kv->max_seq);
+  for (int b = 0; b < B; ++b) kv_ub(kv, b) = std::min(kv_ub(kv, b) + n_new, kv->max_seq);
   return VN_OK;
 }
 
@@ -1361,7 +1396,7 @@ int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
   // capacity: conservative host bound first, exact lengths only when that trips
   const int limit = m->cfg.use_rope ? std::min(kv->max_seq, m->rope_rows) : kv->max_seq;
   bool over = false;
-  for (int b = 0; b < B; ++b) over |= kv->len_ub[b] + slot_offset + T > limit;
+  for (int b = 0; b < B; ++b) over |= kv_ub(kv, b) + slot_offset + T > limit;
   if (over) {
     std::vector<int32_t> lens(kv->max_batch);
     TRY(vn_kv_lengths(kv, lens.data()));

@@ -212,25 +212,130 @@ class SpecEngine:
             raise ValueError(f"only {int(c.min())} tokens available")
         return self.history.numpy()[:, :n]
 
-    def generate(self, prompts, max_new_tokens: int):
-        """Run rounds until every request has `max_new_tokens` tokens.  Returns (tokens (B, T + new), stats)."""
+    def generate(self, prompts, max_new_tokens: int, eos_id: Optional[int] = None):
+        """Run rounds until every request has `max_new_tokens` tokens, or -- with `eos_id` -- until there is a step
+        at which every request emitted EOS (the stop rule of the reference's loops, cometspark.py:862-865; rows are
+        returned uncut, the caller trims at that step).  Returns (tokens (B, T + new), stats)."""
         prompts = np.ascontiguousarray(prompts, dtype=np.int64)
         if max_new_tokens + self.k + 1 > self.cap:
             raise ValueError("max_new_tokens exceeds the engine's history capacity")
         self.prefill(prompts)
+        n = max_new_tokens
         while True:
             # a request gains at least one token per round: poll the counters only now and then
-            need = max_new_tokens - int(self.counts().min())
+            c = self.counts()
+            have = min(int(c.min()), max_new_tokens)
+            if eos_id is not None and have > 0:
+                stop = np.flatnonzero(np.all(self.history.numpy()[:, :have] == eos_id, axis=0))
+                if stop.size:
+                    n = int(stop[0]) + 1
+                    break
+            need = max_new_tokens - have
             if need <= 0:
                 break
             for _ in range(max(1, need // (self.k + 1))):
                 self.step()
         self.target.check()          # token ids in range, no kernel wait ran out
         self.draft.check()
-        new = self.tokens(max_new_tokens)
+        new = self.tokens(n)
         stats = dict(rounds=self.rounds_run, proposed=self.rounds_run * self.k * self.B,
                      committed=int(self.counts().sum()))
         return np.concatenate([prompts, new], axis=1), stats
+
+    # -- serving: requests come and go, slots are reused ------------------------------------------------------
+    def admit(self, slot: int, prompt):
+        """Start a new request in slot `slot` (whatever ran there is dropped): its prompt is prefilled into that
+        slot's rows of both caches through cache views while the other slots keep their state."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.int64).reshape(-1)
+        T = prompt.shape[0]
+        if T < 2:
+            raise ValueError("a request needs at least two prompt tokens")
+        if not 0 <= slot < self.B:
+            raise IndexError(f"slot {slot} outside [0, {self.B})")
+        if T + self.k + 2 > self.max_seq:
+            raise RuntimeError(f"prompt of {T} tokens does not fit the cache's {self.max_seq} positions")
+        for cache, model, upto in ((self.t_cache, self.target, T - 1), (self.d_cache, self.draft, T - 2)):
+            view = cache.view(slot, 1)
+            view.reset()
+            done = 0
+            while done < upto:
+                n = min(4096, upto - done)
+                part = self.ctx.from_numpy(prompt[None, done:done + n])
+                model.forward_cached(part, view, want_logits=False, want_hidden=True, last_only=True)
+                view.commit(n, np.full(1, n, np.int32))
+                done += n
+        self.pair[slot:slot + 1].copy_from_host(prompt[None, -2:])
+        cnt = self.count[slot:slot + 1]
+        self.ctx._check(self.ctx.lib.vn_memset(self.ctx.handle, _ptr(cnt), 0, cnt.nbytes))
+        self._len_bound = max(self._len_bound, T - 1)
+
+    def _park(self, slot: int):
+        """An idle slot keeps running (the batch shape is fixed) on an empty context, so that it cannot overflow."""
+        self.t_cache.view(slot, 1).reset()
+        self.d_cache.view(slot, 1).reset()
+        self.pair[slot:slot + 1].copy_from_host(np.zeros((1, 2), np.int64))
+        cnt = self.count[slot:slot + 1]
+        self.ctx._check(self.ctx.lib.vn_memset(self.ctx.handle, _ptr(cnt), 0, cnt.nbytes))
+
+    def serve(self, prompts, max_new_tokens, eos_id: Optional[int] = None, poll_every: int = 4):
+        """Continuous batching: `prompts` is any number of requests (1-D token arrays of any lengths); at most
+        `max_batch` run at a time, and a request that has produced `max_new_tokens` tokens (an int, or one per
+        request) or an EOS leaves its slot to the next waiting one.  Every `poll_every` rounds the host reads the
+        per-slot counters and tokens (a few KB) to find finished requests; nothing else synchronises.
+        Returns the list of generated token arrays (prompt excluded, EOS included), in request order."""
+        from collections import deque
+        reqs = [np.ascontiguousarray(p, dtype=np.int64).reshape(-1) for p in prompts]
+        limits = [int(max_new_tokens)] * len(reqs) if np.isscalar(max_new_tokens) else [int(x) for x in max_new_tokens]
+        if len(limits) != len(reqs):
+            raise ValueError("one max_new_tokens per request")
+        if max(limits, default=0) + self.k + 1 > self.cap:
+            raise ValueError("max_new_tokens exceeds the engine's history capacity")
+        results = [None] * len(reqs)
+        waiting = deque(range(len(reqs)))
+        running = [-1] * self.B
+        self.t_cache.reset()
+        self.d_cache.reset()
+        self._len_bound = 0
+        for buf in (self.count, self.round_dev):
+            self.ctx._check(self.ctx.lib.vn_memset(self.ctx.handle, _ptr(buf), 0, buf.nbytes))
+        for slot in range(self.B):
+            if waiting:
+                running[slot] = waiting.popleft()
+                self.admit(slot, reqs[running[slot]])
+            else:
+                self._park(slot)
+        while any(r >= 0 for r in running):
+            for _ in range(max(1, int(poll_every))):
+                self.step()
+            c = self.counts()
+            h = self.history.numpy()
+            for slot, r in enumerate(running):
+                if r < 0:
+                    self._park(slot)             # keep idle slots short
+                    continue
+                got = h[slot, :min(int(c[slot]), self.cap)]
+                end = -1
+                if eos_id is not None:
+                    hit = np.flatnonzero(got[:limits[r]] == eos_id)
+                    if hit.size:
+                        end = int(hit[0]) + 1
+                if end < 0 and got.shape[0] >= limits[r]:
+                    end = limits[r]
+                if end >= 0:
+                    results[r] = got[:end].copy()
+                    if waiting:
+                        running[slot] = waiting.popleft()
+                        self.admit(slot, reqs[running[slot]])
+                    else:
+                        running[slot] = -1
+                        self._park(slot)
+            if all(r < 0 for r in running):
+                break
+            lens = self.t_cache.per_seq_lens
+            self._len_bound = int(lens.max())
+        self.target.check()
+        self.draft.check()
+        return results
 
     def __del__(self):
         try:

@@ -75,13 +75,25 @@ class KVCache:
     (accepted path) and drops the rest (rejected suffix) by compacting in place.
     """
 
-    def __init__(self, model: "VerseNexLM", max_batch: int, max_seq: int):
+    def __init__(self, model: "VerseNexLM", max_batch: int, max_seq: int, _view_of: Optional["KVCache"] = None,
+                 _first: int = 0):
         self.model = model
         self.ctx = model.ctx
         self.max_batch, self.max_seq = int(max_batch), int(max_seq)
+        self._parent = _view_of            # keeps the owning cache alive
         h = C.c_void_p()
-        self.ctx._check(self.ctx.lib.vn_kv_create(model.handle, self.max_batch, self.max_seq, C.byref(h)))
+        if _view_of is None:
+            self.ctx._check(self.ctx.lib.vn_kv_create(model.handle, self.max_batch, self.max_seq, C.byref(h)))
+        else:
+            self.ctx._check(self.ctx.lib.vn_kv_view(_view_of.handle, int(_first), self.max_batch, C.byref(h)))
         self.handle = h
+
+    def view(self, first: int, count: int = 1) -> "KVCache":
+        """Sequences [first, first + count) of this cache as a cache of their own (shared memory): a serving loop
+        prefills one free slot through it while the other sequences keep decoding."""
+        if first < 0 or count < 1 or first + count > self.max_batch:
+            raise IndexError(f"sequences [{first}, {first + count}) outside the cache's {self.max_batch}")
+        return KVCache(self.model, count, self.max_seq, _view_of=self, _first=first)
 
     @property
     def per_seq_lens(self) -> np.ndarray:
@@ -400,7 +412,7 @@ class VerseNexLM:
     # -- generate (cometspark.py:773-830) -------------------------------------------
     def generate(self, idx, max_new_tokens: Optional[int] = None, temperature: float = 1.0,
                  top_k: Optional[int] = None, eos_id: Optional[int] = None, max_safe_limit: int = 100_000,
-                 seed: int = 0) -> np.ndarray:
+                 seed: int = 0, draft: Optional["VerseNexLM"] = None, k: int = 4) -> np.ndarray:
         """Autoregressive generation with the KV cache.  As in the reference, `temperature == 1.0 and
         top_k is None` means GREEDY decoding on the recurrent route (cometspark.py:817-818, :832-866), with that
         route's two peculiarities kept: the last prompt token is fed twice, and the ALiBi path sees the last
@@ -414,6 +426,8 @@ class VerseNexLM:
         ids = ids.astype(np.int64)
         limit = max_safe_limit if max_new_tokens is None else int(max_new_tokens)
         recurrent = temperature == 1.0 and top_k is None     # the reference's greedy + recurrent route (:817-818)
+        if draft is not None:
+            return self._generate_speculative(ids, limit, temperature, top_k, eos_id, seed, draft, k, recurrent)
         B, T0 = ids.shape
         cap = T0 + min(limit, 1 << 20) + 2
         if self.use_rope:
@@ -450,6 +464,44 @@ class VerseNexLM:
         res = np.concatenate(out, axis=1)
         if eos_id is not None and res.shape[1] > 0 and not np.all(res[:, -1] == eos_id):
             res = np.concatenate([res, np.full((B, 1), eos_id, dtype=res.dtype)], axis=1)
+        return res
+
+    def _generate_speculative(self, ids, limit, temperature, top_k, eos_id, seed, draft, k, recurrent):
+        """`generate` through the speculative engine (`draft` proposes k tokens per round, this model verifies them).
+        Greedy settings give exactly the tokens of the plain loop above, in fewer target forwards; sampling settings
+        draw from the same distribution (rejection sampling) but not the same Philox stream."""
+        from .engine import SpecEngine
+        B, T0 = ids.shape
+        greedy = recurrent or temperature <= 0
+        prompts = ids
+        if recurrent:
+            # the recurrent route feeds the last prompt token twice (cometspark.py:848-856): it simply is part of the
+            # context the first new token is predicted from
+            prompts = np.concatenate([ids, ids[:, -1:]], axis=1)
+        if prompts.shape[1] < 2:
+            prompts = np.concatenate([prompts[:, :1], prompts], axis=1) if not recurrent else prompts
+        if prompts.shape[1] < 2:
+            raise ValueError("speculative generation needs at least two context tokens")
+        T1 = prompts.shape[1]
+        limit = min(limit, 1 << 20)
+        eng = SpecEngine(self, draft, max_batch=B, max_seq=T1 + limit + 2 * (k + 1) + 2, k=k,
+                         temperature=0.0 if greedy else temperature, top_k=0 if greedy else (top_k or 0), seed=seed,
+                         bonus=True, max_new_tokens=limit)
+        self._set_recurrent(recurrent)
+        draft._set_recurrent(recurrent)
+        try:
+            out, _ = eng.generate(prompts, limit, eos_id=eos_id)
+        finally:
+            self._set_recurrent(False)
+            draft._set_recurrent(False)
+        res = np.concatenate([ids, out[:, T1:]], axis=1)
+        if eos_id is not None:
+            new = res[:, T0:]
+            stop = np.flatnonzero(np.all(new == eos_id, axis=0))     # the plain loop stops when every row emits EOS
+            if stop.size:
+                res = res[:, :T0 + int(stop[0]) + 1]
+            if res.shape[1] > 0 and not np.all(res[:, -1] == eos_id):
+                res = np.concatenate([res, np.full((B, 1), eos_id, dtype=res.dtype)], axis=1)
         return res
 
     def __del__(self):
