@@ -123,11 +123,8 @@ def test_no_bonus_and_deterministic_proposals(ctx):
     assert np.all(t[:, k] == -1)
 
 
-@pytest.mark.parametrize("fused", ["0", "1"])
 @pytest.mark.parametrize("V,top_k", [(300, 5), (5000, 50), (33000, 50), (5000, 1), (64, 200)])
-def test_topk_matches_oracle(ctx, V, top_k, fused, monkeypatch):
-    # fused = "1": select, merge of a row's slices and the decisions in one launch (arrival counters)
-    monkeypatch.setenv("VN_TOPK_FUSE", fused)       # read on every call
+def test_topk_matches_oracle(ctx, V, top_k):
     rng = np.random.default_rng(V + top_k)
     B, k = 8, 4
     p, q, draft = make(rng, B, k, V)

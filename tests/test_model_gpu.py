@@ -323,26 +323,6 @@ def test_tensor_core_attention_head_dim_64(variant):
     assert rel_err(lg, want) < 2e-2
 
 
-@pytest.mark.parametrize("level", ["1", "2"])
-def test_cluster_split_k_reduce(level, monkeypatch):
-    """Opt-in split-K through thread-block clusters (distributed shared memory reduce, RoPE + cache append /
-    SwiGLU / residual add in the GEMM epilogue): the same logits as the workspace path, chain and tree."""
-    monkeypatch.setenv("VN_TC_CLUSTER", level)     # read when the device model is created
-    cfg = hd64_cfg()
-    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=23, gate_std=1.0).items()}
-    m = build(cfg, sd, "bf16")
-    rng = np.random.default_rng(9)
-    B = 3
-    ctx_tok = rng.integers(0, 384, (B, 40))
-    cache = m.new_cache(B, 128)
-    lg0 = m.forward_cached(ctx_tok, cache).numpy()
-    want0, oc = OM.forward(sd, cfg, ctx_tok)
-    assert rel_err(lg0, want0) < 2e-2
-    cache.commit(40, np.full(B, 40, np.int32))
-    nxt = rng.integers(0, 384, (B, 5))
-    lg = m.forward_cached(nxt, cache).numpy()
-    want, oc2 = OM.forward(sd, cfg, nxt, cache=oc)
-    assert rel_err(lg, want) < 2e-2
     cache.commit(5, np.full(B, 5, np.int32))
     parents = [-1, 0, 0, 1, 1, 2]
     nodes = rng.integers(0, 384, (B, 6))

@@ -187,6 +187,25 @@ __device__ __forceinline__ float4 ld_dsmem_f4(unsigned local_addr, unsigned rank
   return v;
 }
 
+// TC_FILTER staging: hits parked in shared memory (behind a 16-byte header whose first int counts them)
+struct FilterHit { int row; float val; int tok; };
+constexpr int FILTER_STAGE = 1024;             // 12 KB of the epilogue's staging memory
+
+// called by all `nthreads` epilogue threads after a barrier behind the last tc_epilogue_chunk<TC_FILTER> of a tile
+__device__ __forceinline__ void filter_flush(const TcArgs& g, unsigned char* base, int tid_epi, int nthreads) {
+  const int* s_n = reinterpret_cast<const int*>(base);
+  const FilterHit* s_hit = reinterpret_cast<const FilterHit*>(base + 16);
+  const int n = *s_n < FILTER_STAGE ? *s_n : FILTER_STAGE;
+  for (int e = tid_epi; e < n; e += nthreads) {
+    const FilterHit h = s_hit[e];
+    const int slot = atomicAdd(g.cand.count + (long long)h.row * g.cand.count_stride, 1);
+    if (slot < g.cand.cap) {
+      g.cand.val[(long long)h.row * g.cand.cap + slot] = h.val;
+      g.cand.tok[(long long)h.row * g.cand.cap + slot] = h.tok;
+    }
+  }
+}
+
 // Epilogue of one 32-token chunk of the accumulator (r[i] = feature f of token m0 + i for this thread).
 // `base` points at 32 KB of shared memory for two staging tiles (`buf` selects one; callers alternate so that a
 // tile is not rewritten while another warp still reads it) shared by the four warps that meet at named barrier
@@ -199,31 +218,25 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
   const int m0 = ch * 32;
   const int mrem = cnt - m0;               // tokens left from this chunk on (>= 1)
     if (MODE == TC_FILTER) {
-      // Logits never leave the SM: the few that reach the row's bound are appended to the row's candidate list.
-      // Lane i of the warp keeps the hit mask of token m0 + i and reserves that token's slots with ONE atomic for
-      // the whole warp (all 32 tokens' atomics are in flight together, no lane waits on a reply inside a loop).
+      // Logits never leave the SM: the few that reach the row's bound (well under one in a hundred) are parked in
+      // shared memory as (row, value, column); filter_flush below hands them to the rows' lists in global memory
+      // with all of the CTA's atomics in flight together -- an atomic per hit inside this loop would stall the warp
+      // for an L2 round trip every time.
       const float* tau = g.cand.tau + row0 + m0;
-      const bool col_ok = n < g.N;
-      unsigned mymask = 0u;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const bool hit = col_ok && i < mrem && __uint_as_float(r[i]) >= __ldg(tau + (i < mrem ? i : 0));
-        const unsigned bal = __ballot_sync(0xffffffffu, hit);
-        if (lane == i) mymask = bal;
-      }
-      int mybase = 0;
-      if (mymask) mybase = atomicAdd(g.cand.count + (long long)(row0 + m0 + lane) * g.cand.count_stride, __popc(mymask));
-      if (__any_sync(0xffffffffu, mymask != 0u)) {
+      int* s_n = reinterpret_cast<int*>(base);
+      FilterHit* s_hit = reinterpret_cast<FilterHit*>(base + 16);
+      if (n < g.N) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const unsigned m_i = __shfl_sync(0xffffffffu, mymask, i);
-          const int b_i = __shfl_sync(0xffffffffu, mybase, i);
-          if ((m_i >> lane) & 1u) {
-            const int slot = b_i + __popc(m_i & ((1u << lane) - 1u));
-            if (slot < g.cand.cap) {
-              const long long at = (long long)(row0 + m0 + i) * g.cand.cap + slot;
-              g.cand.val[at] = __uint_as_float(r[i]);
-              g.cand.tok[at] = n;
+          const float v = __uint_as_float(r[i]);
+          if (i < mrem && v >= __ldg(tau + i)) {
+            const int e = atomicAdd(s_n, 1);
+            if (e < FILTER_STAGE) {
+              s_hit[e].row = row0 + m0 + i; s_hit[e].val = v; s_hit[e].tok = n;
+            } else {                            // staging full (heavy ties): straight to the list
+              const long long rowg = row0 + m0 + i;
+              const int slot = atomicAdd(g.cand.count + rowg * g.cand.count_stride, 1);
+              if (slot < g.cand.cap) { g.cand.val[rowg * g.cand.cap + slot] = v; g.cand.tok[rowg * g.cand.cap + slot] = n; }
             }
           }
         }
@@ -469,6 +482,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       // One instantiation per epilogue kind keeps this unrolled loop small: with all kinds in one body the
       // loop outgrew the instruction cache and the epilogue took 9 us for 160 tokens instead of about 1.
       const int nchunk = (cnt + 31) >> 5;
+      if (MODE == TC_FILTER) {                 // the stage memory is free now: its head holds the parked hits
+        if (threadIdx.x == 64) *reinterpret_cast<int*>(base) = 0;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+      }
       // float4 rows need 16-byte alignment of every row start (uniform over the CTA)
       const bool vec_ok = MODE == TC_PARTIAL
                               ? (g.N % 4 == 0 && ((uintptr_t)g.partial & 15) == 0)
@@ -501,9 +518,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         } else {
-          tc_epilogue_chunk<MODE>(g, r, (MODE >= TC_CL_STORE && MODE != TC_FILTER) ? base : base + grp * (32 * 1024), ch, (ch >> 1) & 1, 2 + grp,
+          tc_epilogue_chunk<MODE>(g, r, (MODE >= TC_CL_STORE || MODE == TC_FILTER) ? base : base + grp * (32 * 1024), ch, (ch >> 1) & 1, 2 + grp,
                                   q, lane, n0, row0, cnt, (int)blockIdx.y, vec_ok, swi_ok);
         }
+      }
+      if (MODE == TC_FILTER) {
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        filter_flush(g, base, (int)threadIdx.x - 64, 256);
       }
       // the staging tiles must have been read before the CTA gives its shared memory back; the writes themselves
       // are complete and visible when the grid completes, which is what every consumer waits for
@@ -791,6 +812,10 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       }
       if (!go) break;                    // uniform over the four warps
       const int nchunk = (cnt + 31) >> 5;
+      if (MODE == TC_FILTER) {                 // the staging area in front of the stages holds the parked hits
+        if (threadIdx.x == 64) *reinterpret_cast<int*>(base) = 0;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
       for (int ch = 0; ch < nchunk; ++ch, ++chunk_no) {
         unsigned r[32];
         tmem_ld32(tmem_base + (unsigned)buf * ncols_buf + ((unsigned)(q * 32) << 16) + (unsigned)(ch * 32), r);
@@ -801,6 +826,11 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
         tc_epilogue_chunk<MODE>(g, r, base, ch, chunk_no & 1, 2, q, lane, n0, row0, cnt, y, vec_ok, swi_ok);
+      }
+      if (MODE == TC_FILTER) {
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        filter_flush(g, base, (int)threadIdx.x - 64, 128);
+        asm volatile("bar.sync 2, 128;" ::: "memory");   // nobody parks the next tile's hits while these are read
       }
       ++t;
     }

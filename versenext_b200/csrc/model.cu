@@ -138,10 +138,6 @@ struct vn_model {
   float* partial = nullptr;      // split-K workspace of the tcgen05 path
   size_t partial_bytes = 0;
   int* tc_error = nullptr;       // device word raised by a bounded wait that ran out
-  // Split-K reduced inside thread-block clusters through distributed shared memory, epilogue in the GEMM
-  // (VN_TC_CLUSTER=1: q|k|v and gate|up, 2: also the residual projections).  Off by default: on B200 the
-  // cluster launch plus the reduce cost 3.5-5 us per GEMM, as much as the finalize kernel it removes.
-  int use_cluster = 0;
   bool recurrent = false;        // vn_model_set_recurrent: ALiBi path as in the reference's one-token recurrent step
   bool use_tc = true;            // VN_GEMM_TC=0 in the environment: keep the mma.sync GEMMs
   bool force_simt_attn = false;  // VN_ATTN_SIMT=1 in the environment: keep the SIMT attention kernel (A/B checks)
@@ -449,13 +445,12 @@ int32_t tc_partial(vn_model* m, GemmArgs g, long long a_rows, long long c_rows, 
   return VN_OK;
 }
 
-// split-K inside thread-block clusters: the K ranges of a feature tile reduce through distributed shared
-// memory and the epilogue (residual add, SwiGLU, RoPE + cache append) runs in the GEMM itself
+// a GEMM whose whole K range fits one CTA: the epilogue (SwiGLU, RoPE + cache append) runs in the GEMM itself
 int32_t tc_cluster(vn_model* m, const GemmArgs& g, long long a_rows, int mode, float* resid,
                    const tc_detail::TcRope* rope) {
   vn_ctx* ctx = m->ctx;
   TcPlan plan;
-  plan.splits = std::min(8, tc_splits(ctx, g.N, g.K, 1));
+  plan.splits = 1;
   plan.error_flag = m->tc_error;
   plan.cluster_mode = mode;
   plan.resid = resid;
@@ -481,12 +476,11 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     g.W = q; g.w_scale = qs; g.wq = m->qmode;
     g.ws_stride = rows_per_seg * (m->qmode == 3 ? (g.K + 127) / 128 : 1);
   };
-  const int use_cluster = m->qmode ? 0 : m->use_cluster;   // the cluster reduce exists for dense weights only
   // A GEMM whose whole K range fits one CTA (the draft model's projections) has nothing to reduce: as a cluster
   // of one it applies RoPE + cache append or SwiGLU itself and the finalize kernel behind it disappears.
   static const bool single_on = [] { const char* e = getenv("VN_TC_SINGLE"); return !(e && e[0] == '0'); }();
   auto fused = [&](const GemmArgs& g) {
-    return use_cluster || (single_on && !m->qmode && tc_splits(ctx, g.N, g.K, 1) == 1);
+    return single_on && !m->qmode && tc_splits(ctx, g.N, g.K, 1) == 1;
   };
   // expert_count is zero between forwards: the combine kernel of every MoD layer leaves it so
   VN_LAUNCH_PDL_BIT(ctx, 32, embed_norm_kernel<T>, M, 256, 0, (const long long*)tokens, (const T*)m->emb, m->x,
@@ -543,17 +537,9 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.M = M; g.N = D; g.K = H * hd; g.tag = "gemm_proj";
     g.ldc = D;
     pick(g, L.q[1], L.qs[1], 0);
-    // the residual add needs a norm kernel behind it either way, so the cluster reduce only pays for the
-    // projections whose finalize kernel disappears (q|k|v, gate|up); VN_TC_CLUSTER=2 forces it here too
-    if (use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
-      TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_ADD, m->x, nullptr));
-      VN_LAUNCH_PDL_BIT(ctx, 32, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm2, (T*)m->h, mod ? m->h32 : (float*)nullptr, 1, 0, D,
-                    1e-6f);
-    } else {
-      TRY(tc_partial(m, g, cap, M, &sp));
-      VN_LAUNCH_PDL_BIT(ctx, 4, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, L.norm2,
-                    (T*)m->h, mod ? m->h32 : (float*)nullptr, D, 1e-6f);
-    }
+    TRY(tc_partial(m, g, cap, M, &sp));
+    VN_LAUNCH_PDL_BIT(ctx, 4, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, L.norm2,
+                  (T*)m->h, mod ? m->h32 : (float*)nullptr, D, 1e-6f);
     // ---- feed-forward block
     const float* next_norm = last ? nullptr : m->layers[li + 1].norm1;
     if (!mod) {
@@ -575,15 +561,9 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.tag = "gemm_down";
       g.ldc = D;
       pick(g, L.q[3], L.qs[3], 0);
-      if (use_cluster >= 2 && gemm_tc_cluster_supported(g, tc_detail::TC_CL_ADD, nullptr)) {
-        TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_ADD, m->x, nullptr));
-        if (next_norm)
-          VN_LAUNCH_PDL_BIT(ctx, 32, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
-      } else {
-        TRY(tc_partial(m, g, cap, M, &sp));
-        VN_LAUNCH_PDL_BIT(ctx, 4, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm,
-                      (T*)m->h, (float*)nullptr, D, 1e-6f);
-      }
+      TRY(tc_partial(m, g, cap, M, &sp));
+      VN_LAUNCH_PDL_BIT(ctx, 4, splitk_add_norm_kernel<T>, M, 256, 0, m->partial, sp, (long long)M * D, m->x, next_norm,
+                    (T*)m->h, (float*)nullptr, D, 1e-6f);
     } else {
       const int ne = c.P * c.E, S = c.P * c.top_k, eh = c.expert_hidden;
       RouteArgs r;
@@ -796,7 +776,6 @@ int32_t vn_model_create(vn_ctx* ctx, const char* config_json, vn_model** out) {
   m->ctx = ctx; m->cfg = c; m->esz = c.bf16 ? 2 : 4;
   { const char* e = getenv("VN_ATTN_SIMT"); m->force_simt_attn = e && e[0] == '1'; }
   { const char* e = getenv("VN_GEMM_TC"); m->use_tc = !(e && e[0] == '0'); }
-  { const char* e = getenv("VN_TC_CLUSTER"); m->use_cluster = e ? atoi(e) : 0; }
   int32_t st = alloc_weights(m);
   if (st != VN_OK) { vn_model_destroy(m); return st; }
   *out = m;
