@@ -260,6 +260,14 @@ int32_t vn_model_head(vn_model* m, const float* hidden_dev, int32_t rows, int32_
  * Non-zero: the one-token recurrent step's -- its state keeps the last window_size keys only, so the path sees
  * those and stays on while that count is at most 1024 (tri_sparse_attn.py:676-731).  No effect without ALiBi. */
 int32_t vn_model_set_recurrent(vn_model* m, int32_t on);
+/* Every wait inside the tensor-core GEMM kernels (for a pipeline stage, for the accumulator) gives up after a limit
+ * and raises the time-out condition that vn_model_status reports; the kernel then drains and returns, the context
+ * stays usable.  vn_model_set_wait_limit sets that limit in SM cycles for this GPU (0: the default, about a second).
+ * vn_model_probe_wait runs one such wait that nothing ever ends -- a barrier no one arrives at -- so that the whole
+ * path (limit, error word, status, exception) can be exercised without a fault: it returns VN_OK, the wait's length
+ * goes to *waited_cycles, and the next vn_model_status returns VN_ERR_TIMEOUT. */
+int32_t vn_model_set_wait_limit(vn_model* m, uint64_t cycles);
+int32_t vn_model_probe_wait(vn_model* m, int64_t* waited_cycles);
 /* Device-side conditions raised by forwards since the last call, read after a stream synchronisation and
  * cleared: *bad_token != 0 when a token id outside [0, vocab) was met (the kernels clamp it instead of reading
  * outside the embedding table; the reference raises IndexError from NumPy fancy indexing, vnnn.py:453-460);

@@ -508,3 +508,29 @@ def test_continuous_batching_serves_ragged_requests():
         eng.serve([np.array([1])], 4)
     with pytest.raises(IndexError):
         eng.admit(5, prompts[0])
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_not_fatal():
+    """Failure detection on the device without a fault: a wait on a barrier that nothing ever completes gives up
+    after the (shortened) limit, the model's status turns into RuntimeError, and the context keeps working."""
+    import ctypes as C
+    cfg = hd64_cfg()
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=29, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    lib, ctx = m.ctx.lib, m.ctx
+    toks = np.random.default_rng(1).integers(0, 384, (2, 12))
+    cache = m.new_cache(2, 64)
+    before = m.forward_cached(toks, cache).numpy()
+    m.check()                                                   # clean so far
+    ctx._check(lib.vn_model_set_wait_limit(m.handle, 2_000_000))          # about a millisecond
+    try:
+        waited = C.c_int64()
+        ctx._check(lib.vn_model_probe_wait(m.handle, C.byref(waited)))
+        assert 2_000_000 <= waited.value < 200_000_000
+        with pytest.raises(RuntimeError):
+            m.check()
+    finally:
+        ctx._check(lib.vn_model_set_wait_limit(m.handle, 0))
+    m.check()                                                   # the condition was cleared by reporting it
+    cache.reset()
+    np.testing.assert_array_equal(m.forward_cached(toks, cache).numpy(), before)   # same GPU, same answers

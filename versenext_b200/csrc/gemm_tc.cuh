@@ -28,6 +28,9 @@ constexpr int BK = 64;         // K elements per stage = one 128-byte swizzle ro
 constexpr int TC_THREADS = 320;      // TMA warp, MMA warp, two groups of four epilogue warps
 constexpr int PERSIST_THREADS = 192; // persistent variant: one epilogue group
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;  // ~1 s
+// the limit every bounded wait of these kernels uses, in SM cycles; vn_model_set_wait_limit changes it (a test makes
+// a wait run out in a millisecond instead of a second)
+__device__ unsigned long long g_wait_limit_cycles = WAIT_LIMIT_CYCLES;
 
 // RoPE + KV-cache append applied to the q | k | v projection (same meaning as in rope_append_kernel)
 struct TcRope {
@@ -114,7 +117,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
-    if ((unsigned long long)(clock64() - t0) > WAIT_LIMIT_CYCLES) return false;
+    if ((unsigned long long)(clock64() - t0) > g_wait_limit_cycles) return false;
   }
   return true;
 }
@@ -845,6 +848,20 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   }
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols) : "memory");
+  }
+}
+
+// A wait that nothing ends: one thread waits on an mbarrier no one arrives at, exactly as the GEMM's roles wait for a
+// stage, and raises the error word when the limit runs out.  Exercises the time-out path without a fault anywhere.
+__global__ void wait_probe_kernel(int* error_flag, long long* waited_cycles) {
+  __shared__ unsigned long long bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(&bar, 0);
+    if (waited_cycles) *waited_cycles = clock64() - t0;
+    if (!ok && error_flag) atomicExch(error_flag, 1);
   }
 }
 

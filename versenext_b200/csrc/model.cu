@@ -1176,6 +1176,32 @@ int32_t vn_model_set_recurrent(vn_model* m, int32_t on) {
   return VN_OK;
 }
 
+int32_t vn_model_set_wait_limit(vn_model* m, uint64_t cycles) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  const unsigned long long v = cycles ? (unsigned long long)cycles : tc_detail::WAIT_LIMIT_CYCLES;
+  VN_CUDA(ctx, cudaMemcpyToSymbolAsync(tc_detail::g_wait_limit_cycles, &v, sizeof v, 0, cudaMemcpyHostToDevice, ctx->stream));
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VN_OK;
+}
+
+int32_t vn_model_probe_wait(vn_model* m, int64_t* waited_cycles) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
+  vn_ctx* ctx = m->ctx;
+  VN_CHECK_CTX(ctx);
+  TRY(ensure_partial(m, 1024));          // makes sure the error word exists
+  long long* d_cycles = nullptr;
+  TRY(dev_alloc(ctx, (void**)&d_cycles, 8));
+  VN_LAUNCH(ctx, tc_detail::wait_probe_kernel, 1, 32, 0, m->tc_error, d_cycles);
+  long long h = 0;
+  VN_CUDA(ctx, cudaMemcpyAsync(&h, d_cycles, 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  cudaFree(d_cycles);
+  if (waited_cycles) *waited_cycles = h;
+  return VN_OK;
+}
+
 int32_t vn_model_status(vn_model* m, int32_t* bad_token, int32_t* wait_timeout) {
   if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null argument");
   vn_ctx* ctx = m->ctx;
