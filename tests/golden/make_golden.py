@@ -377,9 +377,36 @@ def gen_recurrent():
     save("recurrent_reference.npz", **out)
 
 
+# ---------------------------------------------------------------------------
+# 8. A model written by the reference into its .vn container (both weight formats)
+# ---------------------------------------------------------------------------
+
+def gen_vn():
+    import verse_torch.vn_format as vf
+    cfg = OM.mate_config(vocab_size=96, dim=32, n_layer=2, n_head=2, n_kv_head=1, window_size=8, num_global_tokens=4,
+                         max_seq_len=64, init_std=0.2, num_dense_parts=2, num_experts_per_part=2, top_k=1,
+                         expert_hidden=64, embedding_scale=False)
+    sd = OM.init_state_dict(cfg, seed=301, gate_std=1.0)
+    m = ref_model(cfg, sd)
+    toks = np.random.default_rng(301).integers(0, 96, (2, 19)).astype(np.int64)
+    out = {"tokens": toks, "logits": ref_forward(m, cfg, toks)}
+    for n, v in m.state_dict().items():
+        out["sd." + n] = np.array(v)
+    m.save_vn(os.path.join(HERE, "model_tiny_st.vn"))
+    had = vf._HAS_SAFETENSORS
+    vf._HAS_SAFETENSORS = False                  # the writer's fallback: one .npy member per tensor
+    try:
+        m.save_vn(os.path.join(HERE, "model_tiny_npz.vn"))
+    finally:
+        vf._HAS_SAFETENSORS = had
+    for f in ("model_tiny_st.vn", "model_tiny_npz.vn"):
+        print(f"wrote {f}: {os.path.getsize(os.path.join(HERE, f)) / 1024:.1f} KiB")
+    save("vn_reference.npz", **out)
+
+
 if __name__ == "__main__":
     only = set(sys.argv[2:])          # e.g. `make_golden.py /path/to/reference sampling recurrent`
     for name, fn in (("spec", gen_spec), ("small", gen_small), ("mini", gen_mini), ("quant", gen_quant),
-                     ("backend", gen_backend), ("sampling", gen_sampling), ("recurrent", gen_recurrent)):
+                     ("backend", gen_backend), ("sampling", gen_sampling), ("recurrent", gen_recurrent), ("vn", gen_vn)):
         if not only or name in only:
             fn()

@@ -548,8 +548,14 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.tag = "gemm_gateup";
       g.C = m->act; g.ldc = c.mlp_hidden; g.c_bf16 = 1;
       pick(g, L.q[2], L.qs[2], 0);
+      // VN_GATEUP_SPLIT=0: one CTA per feature tile over the whole K range with the SwiGLU epilogue (no finalize
+      // kernel, fewer but longer CTAs); 1: split-K partial tiles + the finalize kernel
+      static const bool gateup_split = [] { const char* e = getenv("VN_GATEUP_SPLIT"); return !(e && e[0] == '0'); }();
       if (fused(g) && gemm_tc_cluster_supported(g, tc_detail::TC_CL_SWIGLU, nullptr)) {
         TRY(tc_cluster(m, g, cap, tc_detail::TC_CL_SWIGLU, nullptr, nullptr));
+      } else if (!gateup_split) {
+        g.epi = EPI_SWIGLU;
+        TRY(tc_launch(ctx, g, cap, direct));
       } else {
         TRY(tc_partial(m, g, cap, M, &sp));
         const long long pairs = (long long)M * c.mlp_hidden;
@@ -584,10 +590,9 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       g.tag = "gemm_expert_down";
       pick(g, L.q[5], L.qs[5], D);
       TRY(tc_partial(m, g, (long long)M * S, (long long)M * S, &sp));
-      VN_LAUNCH_PDL_BIT(ctx, 16, mod_combine_split_kernel, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
-                m->slot_w, m->part_w, D, c.P, c.top_k, m->expert_count, m->expert_cur, ne);
-      if (next_norm)
-        VN_LAUNCH_PDL_BIT(ctx, 32, rmsnorm_kernel<T>, M, 256, 0, m->x, next_norm, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
+      // the next block's first RMSNorm rides on the combine (its rows are in registers there)
+      VN_LAUNCH_PDL_BIT(ctx, 16, mod_combine_split_kernel<T>, M, 256, 0, m->x, m->partial, sp, (long long)M * S * D, m->slot_pos,
+                m->slot_w, m->part_w, D, c.P, c.top_k, m->expert_count, m->expert_cur, ne, next_norm, (T*)m->h, 1e-6f);
     }
   }
   const int rows_out = last_only ? B : M;

@@ -682,14 +682,19 @@ __global__ void gather_sorted_kernel(const T* __restrict__ src, const int* __res
   for (int i = threadIdx.x; i < n16; i += blockDim.x) b[i] = a[i];
 }
 
-// combine with split-K partials of the expert outputs: y = sum_s ypart[s]
+// combine with split-K partials of the expert outputs: y = sum_s ypart[s]; x[row] += the weighted sum; then, if
+// norm_w, h = RMSNorm(x) * norm_w in the storage dtype (the next block's first norm, saving its launch).
+// One CTA per row; D <= 256 * 8.
+template <typename T>
 __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restrict__ x, const float* __restrict__ ypart,
                                                                 int splits, long long pstride,
                                                                 const int* __restrict__ slot_pos,
                                                                 const float* __restrict__ slot_w,
                                                                 const float* __restrict__ part_w, int D, int P,
                                                                 int top_k, int* __restrict__ zero_counts,
-                                                                int* __restrict__ zero_cursor, int n_zero) {
+                                                                int* __restrict__ zero_cursor, int n_zero,
+                                                                const float* __restrict__ norm_w, T* __restrict__ h,
+                                                                float eps) {
   pdl_trigger();
   pdl_wait();
   // the expert GEMMs were the last readers of the per-expert counts: leave them at zero for the next router
@@ -697,6 +702,8 @@ __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restric
     for (int i = threadIdx.x; i < n_zero; i += blockDim.x) { zero_counts[i] = 0; if (zero_cursor) zero_cursor[i] = 0; }
   __shared__ long long s_at[64];
   __shared__ float s_w[64];
+  __shared__ float s_pw[16];
+  __shared__ float sm[8];
   const int row = blockIdx.x;
   const int S = P * top_k;   // <= 64
   if (threadIdx.x < S) {
@@ -704,8 +711,15 @@ __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restric
     s_at[threadIdx.x] = (long long)slot_pos[s] * D;
     s_w[threadIdx.x] = slot_w[s];
   }
+  if (threadIdx.x >= 64 && threadIdx.x < 64 + P && P <= 16) s_pw[threadIdx.x - 64] = part_w[(long long)row * P + threadIdx.x - 64];
   __syncthreads();
-  for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+  float4 v[2];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int d = (threadIdx.x + i * 256) * 4;
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (d >= D) continue;
     float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < P; ++p) {
       float4 comb = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -720,13 +734,34 @@ __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restric
         const float w = s_w[sl];
         comb.x += yv.x * w; comb.y += yv.y * w; comb.z += yv.z * w; comb.w += yv.w * w;
       }
-      const float pw = part_w[(long long)row * P + p];
+      const float pw = P <= 16 ? s_pw[p] : part_w[(long long)row * P + p];
       out.x += comb.x * pw; out.y += comb.y * pw; out.z += comb.z * pw; out.w += comb.w * pw;
     }
     float4* xp = reinterpret_cast<float4*>(x + (long long)row * D + d);
     float4 xv = *xp;
     xv.x += out.x; xv.y += out.y; xv.z += out.z; xv.w += out.w;
     *xp = xv;
+    v[i] = xv;
+    ss += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+  }
+  if (!norm_w) return;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += sm[i];
+  const float r = sqrtf(tot / (float)D + eps);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int d = (threadIdx.x + i * 256) * 4;
+    if (d < D) {
+      const float4 w = *reinterpret_cast<const float4*>(norm_w + d);
+      T* hp = h + (long long)row * D + d;
+      hp[0] = from_f<T>(v[i].x / r * w.x); hp[1] = from_f<T>(v[i].y / r * w.y);
+      hp[2] = from_f<T>(v[i].z / r * w.z); hp[3] = from_f<T>(v[i].w / r * w.w);
+    }
   }
 }
 

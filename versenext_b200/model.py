@@ -189,6 +189,21 @@ class VerseNexLM:
         self._finalized = False
         self._scratch_cache: Optional[KVCache] = None
 
+    @classmethod
+    def from_pretrained(cls, path: str, dtype: str = "f32", device: str = "cuda", **overrides) -> "VerseNexLM":
+        """A model from a `.vn` file, or from a directory holding `model.vn` (CometSparkNexLM.from_pretrained,
+        verse_nex/cometspark.py:1077-1141).  The reference's pickle formats (`.pt`) are not read."""
+        import os
+        from .vn_file import load_vn
+        p = str(path)
+        if os.path.isdir(p):
+            p = os.path.join(p, "model.vn")
+            if not os.path.exists(p):
+                raise FileNotFoundError(f"no model.vn in {path}")
+        elif not p.endswith(".vn"):
+            raise ValueError("only the .vn container is read (pickled .pt checkpoints are not)")
+        return load_vn(p, dtype=dtype, device=device, **overrides)
+
     # -- reference-compatible helpers -----------------------------------------
     def get_config(self) -> dict:
         return dict(self._config)
