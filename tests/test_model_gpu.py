@@ -323,6 +323,55 @@ def test_tensor_core_attention_head_dim_64(variant):
     assert rel_err(lg, want) < 2e-2
 
 
+def test_fused_layer_stack_of_a_draft_model():
+    """A small all-TriSparse bf16 model runs its layer stack as one cooperative kernel (bounded grid barriers between
+    the phases).  Against the oracle and against the chain of separate kernels: decode steps of 1 and of 3 rows per
+    sequence, GQA, window edge, sinks, ALiBi, ragged lengths; the launch count shows which route ran."""
+    cfg = OM.small_config(vocab_size=384, dim=256, n_layer=3, n_head=4, n_kv_head=2, window_size=24,
+                          num_global_tokens=20, max_seq_len=256)
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=33, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    ctx = m.ctx
+    rng = np.random.default_rng(12)
+    B = 5
+    ctx_tok = rng.integers(0, 384, (B, 41))
+    outs = {}
+    for fused in (True, False):
+        m.set_fused_stack(fused)
+        cache = m.new_cache(B, 128)
+        lg0 = m.forward_cached(ctx_tok, cache).numpy()          # 205 rows: the chain either way
+        want0, oc = OM.forward(sd, cfg, ctx_tok)
+        assert rel_err(lg0, want0) < 2e-2
+        lens = np.array([41, 33, 17, 41, 2], np.int32)           # ragged: rows keep different prefixes
+        cache.commit(41, lens)
+        got = []
+        for tn in (1, 3, 1):
+            nxt = rng.integers(0, 384, (B, tn)) if fused else outs["tok"][len(got)]
+            l0 = ctx.launch_count()
+            lg = m.forward_cached(nxt, cache).numpy()
+            n_launch = ctx.launch_count() - l0
+            assert (n_launch <= 3) == fused, n_launch             # stack + head (+ nothing else) vs some twenty
+            got.append((nxt, lg))
+            cache.commit(tn, np.full(B, tn, np.int32))
+        outs[fused] = got
+        if fused:
+            outs["tok"] = [g[0] for g in got]
+    for (t1, a), (t2, b) in zip(outs[True], outs[False]):
+        assert np.array_equal(t1, t2)
+        assert rel_err(a, b) < 1e-2
+    # last_only and the hidden rows
+    m.set_fused_stack(True)
+    cache = m.new_cache(B, 128)
+    m.forward_cached(ctx_tok, cache, want_logits=False)
+    cache.commit(41, np.full(B, 41, np.int32))
+    nxt = rng.integers(0, 384, (B, 2))
+    lg_last = m.forward_cached(nxt, cache, last_only=True).numpy()
+    lg_all = m.forward_cached(nxt, cache).numpy()
+    assert np.array_equal(lg_last.reshape(B, -1), lg_all[:, -1].reshape(B, -1))
+    want, _ = OM.forward(sd, cfg, np.concatenate([ctx_tok, nxt], 1))
+    assert rel_err(lg_all, want[:, -2:]) < 2e-2
+
+
 def test_persistent_gemm_variant(monkeypatch):
     """Opt-in persistent tile-loop GEMM (one CTA per SM, double-buffered TMEM accumulator), forced onto the small
     shapes of this model: dense store, split-K partial and per-expert SwiGLU tiles give the same logits."""

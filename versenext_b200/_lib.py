@@ -110,6 +110,7 @@ PROTOTYPES = {
     "vn_model_param_bytes": [_p, C.POINTER(_u64)],
     "vn_model_head": [_p, _p, _i32, _i32, _i32, _p, _i64],
     "vn_model_set_recurrent": [_p, _i32],
+    "vn_model_set_fused_stack": [_p, _i32],
     "vn_model_set_wait_limit": [_p, _u64],
     "vn_model_probe_wait": [_p, C.POINTER(_i64)],
     "vn_model_status": [_p, C.POINTER(_i32), C.POINTER(_i32)],

@@ -205,22 +205,21 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
   }
 }
 
-__global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_mma_kernel(AttnArgs a) {
+// One (sequence, kv head, row tile) of the attention: bx = sequence * n_kv + kv head, by = tile of 16 query rows.
+// Called by all AW * 32 threads of a CTA; attn_smem: AW * RING * 4096 bytes of shared memory, 128-byte aligned.
+// Everything another kernel -- or, inside a persistent kernel, another CTA -- wrote shortly before is read past L1
+// (cp.async.cg, __ldcg).
+__device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, unsigned char* attn_smem, long long* tr) {
   // per warp: a ring of RING key blocks; after a path's keys the first 4 KB of the warp's ring hold its
   // partial output (16 rows x 64 dims fp32, 16-byte chunks swizzled) for the merge across warps
-  extern __shared__ __align__(128) unsigned char attn_smem[];
   __shared__ float sM[AW][16], sL[AW][16];
   __shared__ int s_depth[64];
   __shared__ __align__(16) float s_q[16 * 64];     // fused mode: the tile's query rows after the split-K sum and RoPE
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
+  const int b = bx / a.n_kv, kvh = bx % a.n_kv;
   const int n_rep = a.H / a.n_kv;
   const int R = a.Tn * n_rep;
-  const int tile0 = blockIdx.y * 16;
-  long long* tr = a.trace ? a.trace + 8ll * (blockIdx.x + (long long)gridDim.x * blockIdx.y) : nullptr;
-  if (tr && tid == 0) tr[0] = clock_stamp();
-  pdl_trigger();
-  pdl_wait();
+  const int tile0 = by * 16;
   const int len = a.lens[b] + a.slot_offset;
   if (a.depth) {
     if (tid < 64) s_depth[tid] = tid < a.Tn ? a.depth[tid] : 0;
@@ -363,7 +362,8 @@ __global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_mma_kernel(AttnArgs
                                : a.q + (long long)(b * a.Tn + tq) * a.ld_q + (kvh * n_rep + hrep) * 64 + 16 * t;
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      const float4 v = *reinterpret_cast<const float4*>(q + 4 * s);
+      const float4 v = a.partial ? *reinterpret_cast<const float4*>(q + 4 * s)
+                                 : __ldcg(reinterpret_cast<const float4*>(q + 4 * s));
       qf[s][h] = r < R ? pack_bf16(v.x, v.y) : 0u;
       qf[s][2 + h] = r < R ? pack_bf16(v.z, v.w) : 0u;
     }
@@ -457,6 +457,15 @@ __global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_mma_kernel(AttnArgs
     reinterpret_cast<__nv_bfloat162*>(out)[0] = v0;
     reinterpret_cast<__nv_bfloat162*>(out)[1] = v1;
   }
+}
+
+__global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_mma_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char attn_smem_dyn[];
+  long long* tr = a.trace ? a.trace + 8ll * (blockIdx.x + (long long)gridDim.x * blockIdx.y) : nullptr;
+  if (tr && threadIdx.x == 0) tr[0] = clock_stamp();
+  pdl_trigger();
+  pdl_wait();
+  attn_tile(a, blockIdx.x, blockIdx.y, attn_smem_dyn, tr);
 }
 
 }  // namespace attn_detail

@@ -6,6 +6,7 @@
 #include "gemm_mma.cuh"
 #include "model_kernels.cuh"
 #include "attn_mma.cuh"
+#include "draft_kernel.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_mma_q.cuh"
 #include "gemm_tcq.cuh"
@@ -138,7 +139,9 @@ struct vn_model {
   float* partial = nullptr;      // split-K workspace of the tcgen05 path
   size_t partial_bytes = 0;
   int* tc_error = nullptr;       // device word raised by a bounded wait that ran out
+  unsigned* stack_bar = nullptr; // two device words: arrivals and generation of the fused layer stack's grid barrier
   bool recurrent = false;        // vn_model_set_recurrent: ALiBi path as in the reference's one-token recurrent step
+  bool fused_stack = true;       // vn_model_set_fused_stack / VN_DRAFT_STACK=0: the layer stack as one cooperative kernel
   bool use_tc = true;            // VN_GEMM_TC=0 in the environment: keep the mma.sync GEMMs
   bool force_simt_attn = false;  // VN_ATTN_SIMT=1 in the environment: keep the SIMT attention kernel (A/B checks)
 };
@@ -403,6 +406,8 @@ int32_t ensure_partial(vn_model* m, size_t bytes) {
   if (!m->tc_error) {
     TRY(dev_alloc(ctx, (void**)&m->tc_error, 4));
     VN_CUDA(ctx, cudaMemsetAsync(m->tc_error, 0, 4, ctx->stream));
+    TRY(dev_alloc(ctx, (void**)&m->stack_bar, 8));
+    VN_CUDA(ctx, cudaMemsetAsync(m->stack_bar, 0, 8, ctx->stream));
   }
   if (bytes <= m->partial_bytes) return VN_OK;
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -458,6 +463,76 @@ int32_t tc_cluster(vn_model* m, const GemmArgs& g, long long a_rows, int mode, f
   return launch_gemm_tc(ctx, g, a_rows, plan);
 }
 
+// ---- the fused layer stack (draft_kernel.cuh): which models and shapes it takes, and its launch -----------
+// VN_DRAFT_STACK=0 in the environment keeps the chain of separate kernels.
+bool draft_stack_ok(const vn_model* m, const vn_kv* kv, int B, int Tn, bool tree) {
+  static const bool on = [] { const char* e = getenv("VN_DRAFT_STACK"); return !(e && e[0] == '0'); }();
+  const Config& c = m->cfg;
+  if (!on || !m->fused_stack || tree || m->esz != 2 || m->qmode || !m->use_tc || m->force_simt_attn || c.use_rope) return false;
+  if (c.n_layer > draft_detail::MAX_LAYERS || c.hd != 64 || c.n_head % c.n_kv) return false;
+  for (int li = 0; li < c.n_layer; ++li)
+    if (m->layers[li].kind != 0) return false;
+  const int M = B * Tn, qd = c.n_head * c.hd;
+  if (M < 1 || M > 64 || (size_t)M * c.dim * 4 > 65536 || (c.dim % 8) || (qd % 8) || (c.mlp_hidden % 8)) return false;
+  const int widest = std::max(std::max(c.dim, qd), c.mlp_hidden);
+  if ((size_t)M * (widest + 8) * 2 > (size_t)draft_detail::STAGE_BYTES) return false;
+  if (draft_detail::wbuf_bytes(c.dim, qd, qd + 2 * c.n_kv * c.hd, c.mlp_hidden, 128) > 32768) return false;
+  (void)kv;
+  return true;
+}
+
+int32_t launch_draft_stack(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, float* out_hidden, int last_only,
+                           int slot_offset) {
+  vn_ctx* ctx = m->ctx;
+  const Config& c = m->cfg;
+  draft_detail::Args a;
+  for (int li = 0; li < c.n_layer; ++li) {
+    const Layer& L = m->layers[li];
+    draft_detail::LayerW& w = a.L[li];
+    w.wqkv = (const __nv_bfloat16*)L.wqkv; w.wproj = (const __nv_bfloat16*)L.wproj;
+    w.wgu = (const __nv_bfloat16*)L.w_gateup; w.wdown = (const __nv_bfloat16*)L.w_down;
+    w.norm1 = L.norm1; w.norm2 = L.norm2; w.sink_k = L.sink_k; w.sink_v = L.sink_v;
+    w.kc = kv->k[li]; w.vc = kv->v[li];
+    w.g_a = 1.f / (1.f + expf(-L.gate_logits[0]));
+    w.g_b = 1.f / (1.f + expf(-L.gate_logits[1]));
+    w.g_c = 1.f / (1.f + expf(-L.gate_logits[2]));
+  }
+  a.n_layer = c.n_layer; a.B = B; a.Tn = Tn; a.D = c.dim; a.H = c.n_head; a.n_kv = c.n_kv; a.hd = c.hd;
+  a.hidden = c.mlp_hidden; a.V = c.vocab;
+  a.tokens = (const long long*)tokens; a.emb = (const __nv_bfloat16*)m->emb;
+  a.emb_scale = c.emb_scale ? sqrtf((float)c.dim) : 1.0f; a.norm_f = m->norm_f;
+  a.x = m->x; a.q = m->qkv; a.attn = (__nv_bfloat16*)m->attn; a.act = (__nv_bfloat16*)m->act;
+  a.h_out = (__nv_bfloat16*)m->h; a.hidden_out = out_hidden;
+  a.lens = kv->lens; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink; a.use_alibi = c.use_alibi;
+  a.alibi_window = m->recurrent ? c.window : 0; a.slot_offset = slot_offset; a.last_only = last_only;
+  a.bar = m->stack_bar; a.status = m->status; a.error_flag = m->tc_error;
+  const int n_rep = c.n_head / c.n_kv;
+  const int n_items = B * c.n_kv * ceil_div(Tn * n_rep, 16);
+  const int grid = std::min(ctx->sm_count, n_items > 128 ? ctx->sm_count : 128);
+  const int qd = c.n_head * c.hd;
+  const size_t smem = draft_detail::STAGE_BYTES + (((size_t)B * Tn * c.dim * 4 + 127) & ~(size_t)127) +
+                      draft_detail::wbuf_bytes(c.dim, qd, qd + 2 * c.n_kv * c.hd, c.mlp_hidden, grid);
+  static unsigned long long attr_set = 0;
+  if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
+    VN_CUDA(ctx, cudaFuncSetAttribute(draft_detail::draft_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      draft_detail::STAGE_BYTES + 65536 + 32768));
+    attr_set |= 1ull << (ctx->device & 63);
+  }
+  // cooperative: all CTAs are resident together, which the grid barriers need
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(draft_detail::DT); cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeCooperative; at[0].val.cooperative = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  if (ctx->profiling) vn_prof_begin(ctx, "draft_layers_kernel");
+  cudaError_t e = cudaLaunchKernelEx(&cfg, draft_detail::draft_layers_kernel, a);
+  if (ctx->profiling) vn_prof_end(ctx);
+  ctx->launches++;
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return vn_fail(ctx, VN_ERR_CUDA, "launch of draft_layers_kernel failed: %s", cudaGetErrorString(e));
+  return VN_OK;
+}
+
 int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, bool tree, float* out_hidden,
                    float* out_logits, int last_only, int slot_offset) {
   typedef __nv_bfloat16 T;
@@ -482,6 +557,12 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
   auto fused = [&](const GemmArgs& g) {
     return single_on && !m->qmode && tc_splits(ctx, g.N, g.K, 1) == 1;
   };
+  const int rows_out = last_only ? B : M;
+  // a small all-TriSparse model (the draft): the whole layer stack and the final norm in one cooperative kernel
+  const bool stack = draft_stack_ok(m, kv, B, Tn, tree);
+  if (stack) {
+    TRY(launch_draft_stack(m, kv, tokens, B, Tn, out_hidden, last_only, slot_offset));
+  } else {
   // expert_count is zero between forwards: the combine kernel of every MoD layer leaves it so
   VN_LAUNCH_PDL_BIT(ctx, 32, embed_norm_kernel<T>, M, 256, 0, (const long long*)tokens, (const T*)m->emb, m->x,
                 m->layers[0].norm1, (T*)m->h, D, c.vocab, emb_scale, 1e-6f, m->status);
@@ -595,9 +676,9 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
                 m->slot_w, m->part_w, D, c.P, c.top_k, m->expert_count, m->expert_cur, ne, next_norm, (T*)m->h, 1e-6f);
     }
   }
-  const int rows_out = last_only ? B : M;
   const int row_mul = last_only ? Tn : 1, row_add = last_only ? Tn - 1 : 0;
   VN_LAUNCH_PDL_BIT(ctx, 32, rmsnorm_kernel<T>, rows_out, 256, 0, m->x, m->norm_f, (T*)m->h, out_hidden, row_mul, row_add, D, 1e-6f);
+  }
   if (out_logits) {
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = m->head; g.ldw = D; g.C = out_logits; g.ldc = c.vocab; g.M = rows_out; g.N = c.vocab;
@@ -799,7 +880,7 @@ int32_t vn_model_destroy(vn_model* m) {
   }
   F(m->x); F(m->h); F(m->h32); F(m->qkv); F(m->attn); F(m->act); F(m->y); F(m->slot_expert); F(m->slot_w); F(m->part_w);
   F(m->expert_count); F(m->expert_off); F(m->expert_cur); F(m->sorted_row); F(m->slot_pos); F(m->depth_dev);
-  F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->head_q); F(m->head_qs);
+  F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->stack_bar); F(m->head_q); F(m->head_qs);
   for (auto& L : m->layers) for (int i = 0; i < 6; ++i) { F(L.q[i]); F(L.qs[i]); }
   delete m;
   return VN_OK;
@@ -1181,6 +1262,12 @@ int32_t vn_model_set_recurrent(vn_model* m, int32_t on) {
   return VN_OK;
 }
 
+int32_t vn_model_set_fused_stack(vn_model* m, int32_t on) {
+  if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
+  m->fused_stack = on != 0;
+  return VN_OK;
+}
+
 int32_t vn_model_set_wait_limit(vn_model* m, uint64_t cycles) {
   if (!m) return vn_fail(nullptr, VN_ERR_INVALID, "null model");
   vn_ctx* ctx = m->ctx;
@@ -1220,6 +1307,7 @@ int32_t vn_model_status(vn_model* m, int32_t* bad_token, int32_t* wait_timeout) 
   if (m->tc_error) {
     VN_CUDA(ctx, cudaMemcpyAsync(&to, m->tc_error, 4, cudaMemcpyDeviceToHost, ctx->stream));
     VN_CUDA(ctx, cudaMemsetAsync(m->tc_error, 0, 4, ctx->stream));
+    if (to && m->stack_bar) VN_CUDA(ctx, cudaMemsetAsync(m->stack_bar, 0, 8, ctx->stream));
   }
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (bad_token) *bad_token = tok;

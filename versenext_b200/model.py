@@ -424,6 +424,11 @@ class VerseNexLM:
     def _set_recurrent(self, on: bool):
         self.ctx._check(self.ctx.lib.vn_model_set_recurrent(self.handle, int(bool(on))))
 
+    def set_fused_stack(self, on: bool):
+        """Run the whole layer stack as one cooperative kernel where the model allows it (small all-TriSparse bf16
+        models: the draft); off keeps the chain of separate kernels."""
+        self.ctx._check(self.ctx.lib.vn_model_set_fused_stack(self.handle, int(bool(on))))
+
     # -- generate (cometspark.py:773-830) -------------------------------------------
     def generate(self, idx, max_new_tokens: Optional[int] = None, temperature: float = 1.0,
                  top_k: Optional[int] = None, eos_id: Optional[int] = None, max_safe_limit: int = 100_000,
