@@ -260,10 +260,12 @@ int32_t vn_model_head(vn_model* m, const float* hidden_dev, int32_t rows, int32_
  * Non-zero: the one-token recurrent step's -- its state keeps the last window_size keys only, so the path sees
  * those and stays on while that count is at most 1024 (tri_sparse_attn.py:676-731).  No effect without ALiBi. */
 int32_t vn_model_set_recurrent(vn_model* m, int32_t on);
-/* A small bf16 model whose layers are all TriSparse (the draft of a speculative round; at most 4 layers, head_dim 64,
- * no RoPE, at most 64 new rows per forward) runs its whole layer stack and the final norm as ONE cooperative kernel
- * whose CTAs meet at bounded grid barriers, instead of a chain of some thirty launches.  On by default; 0 keeps the
- * chain (the two agree to rounding: the order of summation inside a dot product differs). */
+/* A small bf16 model whose layers are all TriSparse (the draft of a speculative round; at most 4 layers, dim <= 256,
+ * head_dim 64, no RoPE, at most 64 new rows per forward) can run its whole layer stack and the final norm as ONE
+ * cooperative kernel whose CTAs meet at bounded grid barriers, instead of a chain of launches.  Off by default (the
+ * chain is as fast on B200); non-zero switches it on for this model.  The two agree to rounding: the order of
+ * summation inside a dot product differs.  A barrier wait that runs out raises the same time-out condition as the
+ * GEMM kernels' waits (vn_model_status returns VN_ERR_TIMEOUT), and the kernel still terminates. */
 int32_t vn_model_set_fused_stack(vn_model* m, int32_t on);
 /* Every wait inside the tensor-core GEMM kernels (for a pipeline stage, for the accumulator) gives up after a limit
  * and raises the time-out condition that vn_model_status reports; the kernel then drains and returns, the context

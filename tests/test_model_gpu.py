@@ -370,6 +370,18 @@ def test_fused_layer_stack_of_a_draft_model():
     assert np.array_equal(lg_last.reshape(B, -1), lg_all[:, -1].reshape(B, -1))
     want, _ = OM.forward(sd, cfg, np.concatenate([ctx_tok, nxt], 1))
     assert rel_err(lg_all, want[:, -2:]) < 2e-2
+    # a grid-barrier wait that runs out: one cycle is never enough for the CTAs to meet.  The kernel walks on and
+    # terminates, the status turns into RuntimeError, and the next forward (barrier words reset) is right again.
+    lib = ctx.lib
+    ctx._check(lib.vn_model_set_wait_limit(m.handle, 1))
+    try:
+        m.forward_cached(nxt, cache, want_logits=False, want_hidden=True)     # the stack kernel alone, no GEMM
+        with pytest.raises(RuntimeError):
+            m.check()
+    finally:
+        ctx._check(lib.vn_model_set_wait_limit(m.handle, 0))
+    m.check()
+    assert np.array_equal(m.forward_cached(nxt, cache).numpy(), lg_all)
 
 
 def test_persistent_gemm_variant(monkeypatch):

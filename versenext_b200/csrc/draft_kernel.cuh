@@ -54,6 +54,7 @@ struct Args {
   unsigned* bar;                    // [0] arrivals of the current barrier, [1] generation
   int* status;                      // token id out of range
   int* error_flag;                  // a barrier wait ran out
+  long long* trace;                 // optional [64] nanosecond stamps of CTA 0 at the phase boundaries, or null
 };
 
 __device__ __forceinline__ void grid_barrier(const Args& a, int n_cta) {
@@ -73,7 +74,6 @@ __device__ __forceinline__ void grid_barrier(const Args& a, int n_cta) {
           if (a.error_flag) atomicExch(a.error_flag, 1);
           break;
         }
-        __nanosleep(64);
       }
     }
     __threadfence();
@@ -81,81 +81,174 @@ __device__ __forceinline__ void grid_barrier(const Args& a, int n_cta) {
   __syncthreads();
 }
 
-__device__ __forceinline__ float bf16_round_f(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-
-// dot of a staged bf16 row with a bf16 weight row, both in shared memory (the weight row is the same for the lanes of
-// a warp that share an output feature: a broadcast)
-__device__ __forceinline__ float dot_bf16(const __nv_bfloat16* __restrict__ s_row, const __nv_bfloat16* __restrict__ w, int K) {
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  for (int k = 0; k < K; k += 8) {
-    const uint4 sv = *reinterpret_cast<const uint4*>(s_row + k);
-    const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
-    const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sv);
-    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
-    const float2 x0 = __bfloat1622float2(s2[0]), y0 = __bfloat1622float2(w2[0]);
-    const float2 x1 = __bfloat1622float2(s2[1]), y1 = __bfloat1622float2(w2[1]);
-    const float2 x2 = __bfloat1622float2(s2[2]), y2 = __bfloat1622float2(w2[2]);
-    const float2 x3 = __bfloat1622float2(s2[3]), y3 = __bfloat1622float2(w2[3]);
-    a0 = fmaf(x0.x, y0.x, a0); a1 = fmaf(x0.y, y0.y, a1);
-    a2 = fmaf(x1.x, y1.x, a2); a3 = fmaf(x1.y, y1.y, a3);
-    a0 = fmaf(x2.x, y2.x, a0); a1 = fmaf(x2.y, y2.y, a1);
-    a2 = fmaf(x3.x, y3.x, a2); a3 = fmaf(x3.y, y3.y, a3);
+__device__ __forceinline__ void stamp(const Args& a, int& n) {
+  if (a.trace && blockIdx.x == 0 && threadIdx.x == 0 && n < 64) {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    a.trace[n] = t;
   }
-  return (a0 + a1) + (a2 + a3);
+  ++n;
 }
 
-// Shared memory of a CTA: [0, STAGE_BYTES) the attention ring, or the staged bf16 rows a projection reads;
-// then M * D floats for a copy of the residual rows; then the CTA's slice of the next projection's weights.
+__device__ __forceinline__ float bf16_round_f(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// out[m][j] = sum_k s[m][k] * w[j][k] for the M staged rows and up to 16 weight rows, on the tensor cores
+// (mma.sync m16n8k16, bf16 in, float32 accumulate).  The 8 warps split the row tiles and the K range; their partial
+// tiles meet in `red` ([8 warps][16][16] floats), where sum_at() adds them in a fixed order.  Rows >= M of s and rows
+// >= n of w hold whatever the memory held: they only feed outputs that nobody reads.
+struct CtaGemm {
+  int n_mt, mt_pad, ks;      // row tiles of 16, the same rounded up to a power of two, K slices (mt_pad * ks = 8)
+};
+__device__ __forceinline__ CtaGemm cta_gemm_shape(int M) {
+  CtaGemm g;
+  g.n_mt = (M + 15) >> 4;
+  g.mt_pad = g.n_mt <= 1 ? 1 : (g.n_mt == 2 ? 2 : 4);
+  g.ks = (DT / 32) / g.mt_pad;
+  return g;
+}
+__device__ __forceinline__ void cta_gemm(const CtaGemm& g, const __nv_bfloat16* s, int lda, const __nv_bfloat16* w, int ldw,
+                                         int K, float* red) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = warp % g.mt_pad, sl = warp / g.mt_pad;
+  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  if (mt < g.n_mt) {
+    const __nv_bfloat16* a_p = s + (size_t)(mt * 16 + (lane & 15)) * lda + ((lane >> 4) << 3);
+    const __nv_bfloat16* b_p = w + (size_t)((lane & 7) + ((lane >> 4) << 3)) * ldw + (((lane >> 3) & 1) << 3);
+    for (int kk = sl * 16; kk < K; kk += g.ks * 16) {
+      unsigned af[4], bf[2][2];
+      mma_detail::ldmatrix_x4(af[0], af[1], af[2], af[3], a_p + kk);
+      mma_detail::ldmatrix_x4(bf[0][0], bf[0][1], bf[1][0], bf[1][1], b_p + kk);
+      mma_detail::mma_bf16(acc[0], af, bf[0]);
+      mma_detail::mma_bf16(acc[1], af, bf[1]);
+    }
+  }
+  float* r = red + warp * 256;
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = (lane >> 2) + h * 8, col = j * 8 + (lane & 3) * 2;
+      r[row * 16 + col] = acc[j][h * 2];
+      r[row * 16 + col + 1] = acc[j][h * 2 + 1];
+    }
+  __syncthreads();
+}
+__device__ __forceinline__ float sum_at(const CtaGemm& g, const float* red, int m, int j) {
+  const int mt = m >> 4, row = m & 15;
+  float v = 0.f;
+  for (int sl = 0; sl < g.ks; ++sl) v += red[(sl * g.mt_pad + mt) * 256 + row * 16 + j];
+  return v;
+}
+
+// Shared memory of a CTA: [0, STAGE_BYTES) the attention ring, or the staged bf16 rows a projection reads; then
+// the warps' partial product tiles; then the CTA's slice of the next projection's weights.
 // The weights of the NEXT phase are fetched (cp.async) before the barrier that ends the current one, so their
 // latency hides behind the barrier; every staging routine ends with a wait on all of the thread's copies.
 
-// this CTA's rows [r0, r1) of a row-major bf16 matrix with K columns -> wbuf (asynchronous; no wait here)
+// this CTA's rows [r0, r1) of a row-major bf16 matrix with K columns -> wbuf rows of K + 8 (asynchronous; no wait here)
 __device__ __forceinline__ void prefetch_w(__nv_bfloat16* wbuf, const __nv_bfloat16* __restrict__ W, int r0, int r1, int K) {
-  if (r1 <= r0) return;
-  const int chunks = ((r1 - r0) * K) >> 3;
-  const __nv_bfloat16* src = W + (long long)r0 * K;
-  for (int i = threadIdx.x; i < chunks; i += DT) mma_detail::cp_async16(wbuf + i * 8, src + i * 8, true);
+  if (r1 > r0) {
+    const int cpr = K >> 3, chunks = (r1 - r0) * cpr, ld = K + 8;
+    const __nv_bfloat16* src = W + (long long)r0 * K;
+    for (int i = threadIdx.x; i < chunks; i += DT) {
+      const int r = i / cpr, c = i - r * cpr;
+      mma_detail::cp_async16(wbuf + r * ld + c * 8, src + (long long)i * 8, true);
+    }
+  }
   mma_detail::cp_async_commit();
 }
 
 // RMSNorm of all M rows of the residual stream into shared memory as bf16 ([M][D + 8]).  first: the rows are the
 // embeddings of the step's tokens (layer 0), and the rows this CTA owns (m % n_cta == cta) are also written to x.
-__device__ __forceinline__ void stage_norm(const Args& a, const float* __restrict__ w, __nv_bfloat16* s, float* xs, int M,
-                                           bool first, int cta, int n_cta) {
+// A warp takes four rows at a time, a lane 8 consecutive elements of each (D <= 256): the rows'
+// loads (past L1: other SMs wrote x) are all in flight together and the values stay in registers for the second pass.
+constexpr int NORM_TRIPS = 1;
+__device__ __forceinline__ void stage_norm(const Args& a, const float* __restrict__ w, __nv_bfloat16* s, int M, bool first,
+                                           int cta, int n_cta) {
   const int D = a.D, ld = D + 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __nv_bfloat16* es = reinterpret_cast<__nv_bfloat16*>(xs);
-  if (first) {
-    const int chunks = D >> 3;
-    for (int i = threadIdx.x; i < M * chunks; i += DT) {
-      const int m = i / chunks, c = i - m * chunks;
-      long long tok = a.tokens[m];
-      if (tok < 0 || tok >= a.V) { atomicExch(a.status, 1); tok = tok < 0 ? 0 : a.V - 1; }
-      mma_detail::cp_async16(es + m * D + c * 8, a.emb + tok * D + c * 8, true);
+  float wv[NORM_TRIPS][8];
+#pragma unroll
+  for (int t = 0; t < NORM_TRIPS; ++t) {
+    const int d = t * 256 + lane * 8;
+    if (d < D) {
+      const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + d)), w1 = __ldg(reinterpret_cast<const float4*>(w + d + 4));
+      wv[t][0] = w0.x; wv[t][1] = w0.y; wv[t][2] = w0.z; wv[t][3] = w0.w;
+      wv[t][4] = w1.x; wv[t][5] = w1.y; wv[t][6] = w1.z; wv[t][7] = w1.w;
     }
-  } else {
-    const int chunks = D >> 2;
-    for (int i = threadIdx.x; i < M * chunks; i += DT)
-      mma_detail::cp_async16(xs + i * 4, a.x + (long long)i * 4, true);
   }
-  mma_detail::cp_async_commit();
-  mma_detail::cp_async_wait<0>();
-  __syncthreads();
-  for (int m = warp; m < M; m += DT / 32) {          // one warp per row
-    float ss = 0.f;
-    for (int d = lane; d < D; d += 32) {
-      const float v = first ? __bfloat162float(es[m * D + d]) * a.emb_scale : xs[m * D + d];
-      if (first && m % n_cta == cta) a.x[(long long)m * D + d] = v;
-      ss += v * v;
+  for (int m0 = warp; m0 < M; m0 += 4 * (DT / 32)) {
+    float v[4][NORM_TRIPS][8];
+    float ss[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int m = m0 + i * (DT / 32);
+      if (m >= M) continue;
+      const __nv_bfloat16* e = nullptr;
+      if (first) {
+        long long tok = a.tokens[m];
+        if (tok < 0 || tok >= a.V) { if (lane == 0) atomicExch(a.status, 1); tok = tok < 0 ? 0 : a.V - 1; }
+        e = a.emb + tok * D;
+      }
+#pragma unroll
+      for (int t = 0; t < NORM_TRIPS; ++t) {
+        const int d = t * 256 + lane * 8;
+        if (d >= D) continue;
+        if (first) {
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(e + d));
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h2[j]);
+            v[i][t][2 * j] = f.x * a.emb_scale; v[i][t][2 * j + 1] = f.y * a.emb_scale;
+          }
+        } else {
+          const float4 lo = __ldcg(reinterpret_cast<const float4*>(a.x + (long long)m * D + d));
+          const float4 hi = __ldcg(reinterpret_cast<const float4*>(a.x + (long long)m * D + d + 4));
+          v[i][t][0] = lo.x; v[i][t][1] = lo.y; v[i][t][2] = lo.z; v[i][t][3] = lo.w;
+          v[i][t][4] = hi.x; v[i][t][5] = hi.y; v[i][t][6] = hi.z; v[i][t][7] = hi.w;
+        }
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float r = sqrtf(ss / (float)D + 1e-6f);
-    for (int d = lane; d < D; d += 32) {
-      const float v = first ? __bfloat162float(es[m * D + d]) * a.emb_scale : xs[m * D + d];
-      s[m * ld + d] = __float2bfloat16_rn(v / r * w[d]);
+    for (int i = 0; i < 4; ++i) {
+      const int m = m0 + i * (DT / 32);
+      if (m >= M) continue;
+#pragma unroll
+      for (int t = 0; t < NORM_TRIPS; ++t) {
+        const int d = t * 256 + lane * 8;
+        if (d >= D) continue;
+        if (first && m % n_cta == cta) {
+          float4* xp = reinterpret_cast<float4*>(a.x + (long long)m * D + d);
+          xp[0] = make_float4(v[i][t][0], v[i][t][1], v[i][t][2], v[i][t][3]);
+          xp[1] = make_float4(v[i][t][4], v[i][t][5], v[i][t][6], v[i][t][7]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss[i] += v[i][t][j] * v[i][t][j];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], o);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int m = m0 + i * (DT / 32);
+      if (m >= M) continue;
+      const float r = sqrtf(ss[i] / (float)D + 1e-6f);
+#pragma unroll
+      for (int t = 0; t < NORM_TRIPS; ++t) {
+        const int d = t * 256 + lane * 8;
+        if (d >= D) continue;
+        __align__(16) __nv_bfloat16 o8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o8[j] = __float2bfloat16_rn(v[i][t][j] / r * wv[t][j]);
+        *reinterpret_cast<uint4*>(s + m * ld + d) = *reinterpret_cast<const uint4*>(o8);
+      }
     }
   }
+  mma_detail::cp_async_wait<0>();        // the weight slice fetched before the last barrier
   __syncthreads();
 }
 
@@ -173,15 +266,17 @@ __device__ __forceinline__ void stage_rows(const __nv_bfloat16* __restrict__ src
 
 // bytes of dynamic shared memory the kernel needs for a model / step shape (host and device agree on the layout)
 __host__ __device__ inline int slice_rows(int n, int n_cta) { return (n + n_cta - 1) / n_cta; }
+__host__ __device__ inline size_t pad16(int n) { return (size_t)((n + 15) & ~15); }
 __host__ __device__ inline size_t wbuf_bytes(int D, int qd, int n_qkv, int hidden, int n_cta) {
-  size_t w = (size_t)slice_rows(n_qkv, n_cta) * D;
-  const size_t c = (size_t)slice_rows(D, n_cta) * qd, d = (size_t)2 * slice_rows(hidden, n_cta) * D,
-               e = (size_t)slice_rows(D, n_cta) * hidden;
+  size_t w = pad16(slice_rows(n_qkv, n_cta)) * (D + 8);
+  const size_t c = pad16(slice_rows(D, n_cta)) * (qd + 8), d = pad16(2 * slice_rows(hidden, n_cta)) * (D + 8),
+               e = pad16(slice_rows(D, n_cta)) * (hidden + 8);
   if (c > w) w = c;
   if (d > w) w = d;
   if (e > w) w = e;
   return (w * 2 + 127) & ~(size_t)127;
 }
+constexpr int RED_BYTES = (DT / 32) * 256 * 4;   // the warps' partial tiles
 
 __global__ void __launch_bounds__(DT, 1) draft_layers_kernel(Args a) {
   extern __shared__ __align__(128) unsigned char dsm[];
@@ -189,8 +284,9 @@ __global__ void __launch_bounds__(DT, 1) draft_layers_kernel(Args a) {
   const int M = a.B * a.Tn, D = a.D, hd = a.hd;
   const int qd = a.H * hd, kvd = a.n_kv * hd, n_qkv = qd + 2 * kvd;
   __nv_bfloat16* s = reinterpret_cast<__nv_bfloat16*>(dsm);
-  float* xs = reinterpret_cast<float*>(dsm + STAGE_BYTES);
-  __nv_bfloat16* wbuf = reinterpret_cast<__nv_bfloat16*>(dsm + STAGE_BYTES + (((size_t)M * D * 4 + 127) & ~(size_t)127));
+  float* red = reinterpret_cast<float*>(dsm + STAGE_BYTES);
+  __nv_bfloat16* wbuf = reinterpret_cast<__nv_bfloat16*>(dsm + STAGE_BYTES + RED_BYTES);
+  const CtaGemm cg = cta_gemm_shape(M);
   const int n_rep = a.H / a.n_kv;
   const int tiles = (a.Tn * n_rep + 15) >> 4;
   const int n_items = a.B * a.n_kv * tiles;
@@ -198,31 +294,40 @@ __global__ void __launch_bounds__(DT, 1) draft_layers_kernel(Args a) {
   const int perA = slice_rows(n_qkv, n_cta), a0 = min(n_qkv, cta * perA), a1 = min(n_qkv, a0 + perA);
   const int perC = slice_rows(D, n_cta), c0 = min(D, cta * perC), c1 = min(D, c0 + perC);
   const int perD = slice_rows(a.hidden, n_cta), d0 = min(a.hidden, cta * perD), d1 = min(a.hidden, d0 + perD);
+  int ns = 0;
+  stamp(a, ns);
   prefetch_w(wbuf, a.L[0].wqkv, a0, a1, D);
   for (int li = 0; li < a.n_layer; ++li) {
     const LayerW& L = a.L[li];
     // ---- A: norm1 + q|k|v for this CTA's output features; K / V rows go straight into the cache
-    stage_norm(a, L.norm1, s, xs, M, li == 0, cta, n_cta);
-    for (int i = threadIdx.x; i < (a1 - a0) * M; i += DT) {
-      const int oi = i / M, o = a0 + oi, m = i - oi * M;
-      const float v = dot_bf16(s + m * (D + 8), wbuf + oi * D, D);
-      if (o < qd) {
-        a.q[(long long)m * qd + o] = v;
-      } else {
-        const int b = m / a.Tn, t = m - b * a.Tn;
-        const int slot = a.lens[b] + a.slot_offset + t;
-        if (slot < a.max_seq) {
-          const bool is_k = o < qd + kvd;
-          const int c = is_k ? o - qd : o - qd - kvd;
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(is_k ? L.kc : L.vc) +
-                               ((long long)b * a.max_seq + slot) * kvd + c;
-          *dst = __float2bfloat16_rn(v);
+    stage_norm(a, L.norm1, s, M, li == 0, cta, n_cta);
+    stamp(a, ns);
+    for (int nc = 0; nc < a1 - a0; nc += 16) {
+      cta_gemm(cg, s, D + 8, wbuf + nc * (D + 8), D + 8, D, red);
+      const int nn = min(16, a1 - a0 - nc);
+      for (int i = threadIdx.x; i < nn * M; i += DT) {
+        const int m = i / nn, oi = i - m * nn, o = a0 + nc + oi;
+        const float v = sum_at(cg, red, m, oi);
+        if (o < qd) {
+          a.q[(long long)m * qd + o] = v;
+        } else {
+          const int b = m / a.Tn, t = m - b * a.Tn;
+          const int slot = a.lens[b] + a.slot_offset + t;
+          if (slot < a.max_seq) {
+            const bool is_k = o < qd + kvd;
+            const int c = is_k ? o - qd : o - qd - kvd;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(is_k ? L.kc : L.vc) +
+                                 ((long long)b * a.max_seq + slot) * kvd + c;
+            *dst = __float2bfloat16_rn(v);
+          }
         }
       }
+      __syncthreads();
     }
-    __syncthreads();
     prefetch_w(wbuf, L.wproj, c0, c1, qd);
+    stamp(a, ns);
     grid_barrier(a, n_cta);
+    stamp(a, ns);
     // ---- B: attention, one (sequence, kv head, row tile) at a time
     {
       AttnArgs t;
@@ -236,59 +341,97 @@ __global__ void __launch_bounds__(DT, 1) draft_layers_kernel(Args a) {
         __syncthreads();
       }
     }
+    stamp(a, ns);
     grid_barrier(a, n_cta);
+    stamp(a, ns);
     // ---- C: output projection + residual add for this CTA's features
     stage_rows(a.attn, s, M, qd);
-    for (int i = threadIdx.x; i < (c1 - c0) * M; i += DT) {
-      const int oi = i / M, o = c0 + oi, m = i - oi * M;
-      const float v = dot_bf16(s + m * (qd + 8), wbuf + oi * qd, qd);
-      float* xp = a.x + (long long)m * D + o;
-      *xp = __ldcg(xp) + v;
+    stamp(a, ns);
+    for (int nc = 0; nc < c1 - c0; nc += 16) {
+      cta_gemm(cg, s, qd + 8, wbuf + nc * (qd + 8), qd + 8, qd, red);
+      const int nn = min(16, c1 - c0 - nc);
+      for (int i = threadIdx.x; i < nn * M; i += DT) {
+        const int m = i / nn, oi = i - m * nn;
+        float* xp = a.x + (long long)m * D + c0 + nc + oi;
+        *xp = __ldcg(xp) + sum_at(cg, red, m, oi);
+      }
+      __syncthreads();
     }
-    __syncthreads();
     prefetch_w(wbuf, L.wgu, 2 * d0, 2 * d1, D);
+    stamp(a, ns);
     grid_barrier(a, n_cta);
-    // ---- D: norm2 + gate|up + SwiGLU for this CTA's hidden units
-    stage_norm(a, L.norm2, s, xs, M, false, cta, n_cta);
-    for (int i = threadIdx.x; i < (d1 - d0) * M; i += DT) {
-      const int ji = i / M, j = d0 + ji, m = i - ji * M;
-      const float gt = dot_bf16(s + m * (D + 8), wbuf + (2 * ji) * D, D);
-      const float up = dot_bf16(s + m * (D + 8), wbuf + (2 * ji + 1) * D, D);
-      a.act[(long long)m * a.hidden + j] = __float2bfloat16_rn(silu_ref(gt) * up);
+    stamp(a, ns);
+    // ---- D: norm2 + gate|up + SwiGLU for this CTA's hidden units (rows 2j, 2j + 1 of the interleaved matrix)
+    stage_norm(a, L.norm2, s, M, false, cta, n_cta);
+    stamp(a, ns);
+    for (int nc = 0; nc < 2 * (d1 - d0); nc += 16) {
+      cta_gemm(cg, s, D + 8, wbuf + nc * (D + 8), D + 8, D, red);
+      const int np = min(8, d1 - d0 - nc / 2);
+      for (int i = threadIdx.x; i < np * M; i += DT) {
+        const int m = i / np, ji = i - m * np;
+        const float gt = sum_at(cg, red, m, 2 * ji), up = sum_at(cg, red, m, 2 * ji + 1);
+        a.act[(long long)m * a.hidden + d0 + nc / 2 + ji] = __float2bfloat16_rn(silu_ref(gt) * up);
+      }
+      __syncthreads();
     }
-    __syncthreads();
     prefetch_w(wbuf, L.wdown, c0, c1, a.hidden);
+    stamp(a, ns);
     grid_barrier(a, n_cta);
+    stamp(a, ns);
     // ---- E: down projection + residual add
     stage_rows(a.act, s, M, a.hidden);
-    for (int i = threadIdx.x; i < (c1 - c0) * M; i += DT) {
-      const int oi = i / M, o = c0 + oi, m = i - oi * M;
-      const float v = dot_bf16(s + m * (a.hidden + 8), wbuf + oi * a.hidden, a.hidden);
-      float* xp = a.x + (long long)m * D + o;
-      *xp = __ldcg(xp) + v;
+    stamp(a, ns);
+    for (int nc = 0; nc < c1 - c0; nc += 16) {
+      cta_gemm(cg, s, a.hidden + 8, wbuf + nc * (a.hidden + 8), a.hidden + 8, a.hidden, red);
+      const int nn = min(16, c1 - c0 - nc);
+      for (int i = threadIdx.x; i < nn * M; i += DT) {
+        const int m = i / nn, oi = i - m * nn;
+        float* xp = a.x + (long long)m * D + c0 + nc + oi;
+        *xp = __ldcg(xp) + sum_at(cg, red, m, oi);
+      }
+      __syncthreads();
     }
-    __syncthreads();
     if (li + 1 < a.n_layer) prefetch_w(wbuf, a.L[li + 1].wqkv, a0, a1, D);
+    stamp(a, ns);
     grid_barrier(a, n_cta);
+    stamp(a, ns);
   }
   // ---- final norm of the rows the head needs (every row, or the last position of every sequence)
   {
     const int rows_out = a.last_only ? a.B : M;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int r = cta * (DT / 32) + warp; r < rows_out; r += n_cta * (DT / 32)) {
+    for (int r = cta + warp * n_cta; r < rows_out; r += n_cta * (DT / 32)) {     // spread over the CTAs first
       const long long src = a.last_only ? (long long)r * a.Tn + a.Tn - 1 : r;
       float ss = 0.f;
-      for (int d = lane; d < D; d += 32) { const float v = __ldcg(a.x + src * D + d); ss += v * v; }
+      for (int d = lane * 8; d < D; d += 256) {
+        const float4 lo = __ldcg(reinterpret_cast<const float4*>(a.x + src * D + d));
+        const float4 hi = __ldcg(reinterpret_cast<const float4*>(a.x + src * D + d + 4));
+        ss += lo.x * lo.x + lo.y * lo.y + lo.z * lo.z + lo.w * lo.w + hi.x * hi.x + hi.y * hi.y + hi.z * hi.z + hi.w * hi.w;
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       const float rr = sqrtf(ss / (float)D + 1e-6f);
-      for (int d = lane; d < D; d += 32) {
-        const float v = __ldcg(a.x + src * D + d) / rr * a.norm_f[d];
-        a.h_out[(long long)r * D + d] = __float2bfloat16_rn(v);
-        if (a.hidden_out) a.hidden_out[(long long)r * D + d] = v;
+      for (int d = lane * 8; d < D; d += 256) {
+        const float4 lo = __ldcg(reinterpret_cast<const float4*>(a.x + src * D + d));
+        const float4 hi = __ldcg(reinterpret_cast<const float4*>(a.x + src * D + d + 4));
+        const float xv[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.norm_f + d));
+        const float4 w1 = __ldg(reinterpret_cast<const float4*>(a.norm_f + d + 4));
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float v[8];
+        __align__(16) __nv_bfloat16 o8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { v[i] = xv[i] / rr * wv[i]; o8[i] = __float2bfloat16_rn(v[i]); }
+        *reinterpret_cast<uint4*>(a.h_out + (long long)r * D + d) = *reinterpret_cast<const uint4*>(o8);
+        if (a.hidden_out) {
+          float4* hp = reinterpret_cast<float4*>(a.hidden_out + (long long)r * D + d);
+          hp[0] = make_float4(v[0], v[1], v[2], v[3]);
+          hp[1] = make_float4(v[4], v[5], v[6], v[7]);
+        }
       }
     }
   }
+  stamp(a, ns);
 }
 
 }  // namespace draft_detail

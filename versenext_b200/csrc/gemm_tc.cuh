@@ -116,8 +116,9 @@ __device__ __forceinline__ bool mbar_try(unsigned long long* bar, unsigned parit
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
+  const unsigned long long limit = g_wait_limit_cycles;
   while (!mbar_try(bar, parity)) {
-    if ((unsigned long long)(clock64() - t0) > g_wait_limit_cycles) return false;
+    if ((unsigned long long)(clock64() - t0) > limit) return false;
   }
   return true;
 }
@@ -194,19 +195,6 @@ __device__ __forceinline__ float4 ld_dsmem_f4(unsigned local_addr, unsigned rank
 struct FilterHit { int row; float val; int tok; };
 constexpr int FILTER_STAGE = 1024;             // 12 KB of the epilogue's staging memory
 
-// one hit -> the CTA's staging list, or straight to the row's list in global memory when the staging list is full
-__device__ __noinline__ void filter_park(const TcArgs& g, unsigned char* base, int row, float v, int tok) {
-  int* s_n = reinterpret_cast<int*>(base);
-  FilterHit* s_hit = reinterpret_cast<FilterHit*>(base + 16);
-  const int e = atomicAdd(s_n, 1);
-  if (e < FILTER_STAGE) {
-    s_hit[e].row = row; s_hit[e].val = v; s_hit[e].tok = tok;
-  } else {                                      // heavy ties
-    const int slot = atomicAdd(g.cand.count + (long long)row * g.cand.count_stride, 1);
-    if (slot < g.cand.cap) { g.cand.val[(long long)row * g.cand.cap + slot] = v; g.cand.tok[(long long)row * g.cand.cap + slot] = tok; }
-  }
-}
-
 // called by all `nthreads` epilogue threads after a barrier behind the last tc_epilogue_chunk<TC_FILTER> of a tile
 __device__ __forceinline__ void filter_flush(const TcArgs& g, unsigned char* base, int tid_epi, int nthreads) {
   const int* s_n = reinterpret_cast<const int*>(base);
@@ -238,20 +226,24 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
       // shared memory as (row, value, column); filter_flush below hands them to the rows' lists in global memory
       // with all of the CTA's atomics in flight together -- an atomic per hit inside this loop would stall the warp
       // for an L2 round trip every time.
-      // The compare loop is unrolled (the accumulator registers cannot be indexed at run time) and must stay tiny:
-      // it only builds a bit mask; the rare hits are parked by an out-of-line call, so that the unrolled body does
-      // not outgrow the instruction cache.
       const float* tau = g.cand.tau + row0 + m0;
-      unsigned mask = 0u;
+      int* s_n = reinterpret_cast<int*>(base);
+      FilterHit* s_hit = reinterpret_cast<FilterHit*>(base + 16);
       if (n < g.N) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i < mrem && __uint_as_float(r[i]) >= __ldg(tau + i)) mask |= 1u << i;
-      }
-      if (mask) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if ((mask >> i) & 1u) filter_park(g, base, row0 + m0 + i, __uint_as_float(r[i]), n);
+        for (int i = 0; i < 32; ++i) {
+          const float v = __uint_as_float(r[i]);
+          if (i < mrem && v >= __ldg(tau + i)) {
+            const int e = atomicAdd(s_n, 1);
+            if (e < FILTER_STAGE) {
+              s_hit[e].row = row0 + m0 + i; s_hit[e].val = v; s_hit[e].tok = n;
+            } else {                            // staging full (heavy ties): straight to the list
+              const long long rowg = row0 + m0 + i;
+              const int slot = atomicAdd(g.cand.count + rowg * g.cand.count_stride, 1);
+              if (slot < g.cand.cap) { g.cand.val[rowg * g.cand.cap + slot] = v; g.cand.tok[rowg * g.cand.cap + slot] = n; }
+            }
+          }
+        }
       }
     } else if (MODE >= TC_CL_STORE) {
       // whole partial tile [token][feature] in this CTA's shared memory; reduced after the cluster barrier

@@ -141,7 +141,7 @@ struct vn_model {
   int* tc_error = nullptr;       // device word raised by a bounded wait that ran out
   unsigned* stack_bar = nullptr; // two device words: arrivals and generation of the fused layer stack's grid barrier
   bool recurrent = false;        // vn_model_set_recurrent: ALiBi path as in the reference's one-token recurrent step
-  bool fused_stack = true;       // vn_model_set_fused_stack / VN_DRAFT_STACK=0: the layer stack as one cooperative kernel
+  bool fused_stack = false;      // vn_model_set_fused_stack / VN_DRAFT_STACK=1: the layer stack as one cooperative kernel
   bool use_tc = true;            // VN_GEMM_TC=0 in the environment: keep the mma.sync GEMMs
   bool force_simt_attn = false;  // VN_ATTN_SIMT=1 in the environment: keep the SIMT attention kernel (A/B checks)
 };
@@ -464,18 +464,20 @@ int32_t tc_cluster(vn_model* m, const GemmArgs& g, long long a_rows, int mode, f
 }
 
 // ---- the fused layer stack (draft_kernel.cuh): which models and shapes it takes, and its launch -----------
-// VN_DRAFT_STACK=0 in the environment keeps the chain of separate kernels.
+// Off unless vn_model_set_fused_stack(model, 1) or VN_DRAFT_STACK=1 in the environment asks for it: on B200 the
+// chain of separate kernels with programmatic dependent launch is as fast (the ten grid barriers of a 2-layer model
+// cost what the launches cost), so the chain stays the default.
 bool draft_stack_ok(const vn_model* m, const vn_kv* kv, int B, int Tn, bool tree) {
-  static const bool on = [] { const char* e = getenv("VN_DRAFT_STACK"); return !(e && e[0] == '0'); }();
+  static const bool env_on = [] { const char* e = getenv("VN_DRAFT_STACK"); return e && e[0] == '1'; }();
   const Config& c = m->cfg;
-  if (!on || !m->fused_stack || tree || m->esz != 2 || m->qmode || !m->use_tc || m->force_simt_attn || c.use_rope) return false;
+  if (!(env_on || m->fused_stack) || tree || m->esz != 2 || m->qmode || !m->use_tc || m->force_simt_attn || c.use_rope) return false;
   if (c.n_layer > draft_detail::MAX_LAYERS || c.hd != 64 || c.n_head % c.n_kv) return false;
   for (int li = 0; li < c.n_layer; ++li)
     if (m->layers[li].kind != 0) return false;
   const int M = B * Tn, qd = c.n_head * c.hd;
-  if (M < 1 || M > 64 || (size_t)M * c.dim * 4 > 65536 || (c.dim % 8) || (qd % 8) || (c.mlp_hidden % 8)) return false;
+  if (M < 1 || M > 64 || c.dim > 256 * draft_detail::NORM_TRIPS || (c.dim % 16) || (qd % 16) || (c.mlp_hidden % 16)) return false;
   const int widest = std::max(std::max(c.dim, qd), c.mlp_hidden);
-  if ((size_t)M * (widest + 8) * 2 > (size_t)draft_detail::STAGE_BYTES) return false;
+  if ((size_t)((M + 15) & ~15) * (widest + 8) * 2 > (size_t)draft_detail::STAGE_BYTES) return false;
   if (draft_detail::wbuf_bytes(c.dim, qd, qd + 2 * c.n_kv * c.hd, c.mlp_hidden, 128) > 32768) return false;
   (void)kv;
   return true;
@@ -506,16 +508,28 @@ int32_t launch_draft_stack(vn_model* m, vn_kv* kv, const int64_t* tokens, int B,
   a.lens = kv->lens; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink; a.use_alibi = c.use_alibi;
   a.alibi_window = m->recurrent ? c.window : 0; a.slot_offset = slot_offset; a.last_only = last_only;
   a.bar = m->stack_bar; a.status = m->status; a.error_flag = m->tc_error;
+  // VN_STACK_TRACE=1 (debugging aid, eager launches only): CTA 0's time stamps at the phase boundaries go to stderr
+  static const bool trace_on = [] { const char* e = getenv("VN_STACK_TRACE"); return e && e[0] == '1'; }();
+  static long long* trace_dev = nullptr;
+  cudaStreamCaptureStatus cap_st = cudaStreamCaptureStatusNone;
+  a.trace = nullptr;
+  if (trace_on) {
+    cudaStreamIsCapturing(ctx->stream, &cap_st);
+    if (cap_st == cudaStreamCaptureStatusNone) {
+      if (!trace_dev) cudaMalloc(&trace_dev, 64 * sizeof(long long));
+      cudaMemsetAsync(trace_dev, 0, 64 * sizeof(long long), ctx->stream);
+      a.trace = trace_dev;
+    }
+  }
   const int n_rep = c.n_head / c.n_kv;
   const int n_items = B * c.n_kv * ceil_div(Tn * n_rep, 16);
   const int grid = std::min(ctx->sm_count, n_items > 128 ? ctx->sm_count : 128);
   const int qd = c.n_head * c.hd;
-  const size_t smem = draft_detail::STAGE_BYTES + (((size_t)B * Tn * c.dim * 4 + 127) & ~(size_t)127) +
-                      draft_detail::wbuf_bytes(c.dim, qd, qd + 2 * c.n_kv * c.hd, c.mlp_hidden, grid);
+  const size_t smem = draft_detail::STAGE_BYTES + draft_detail::RED_BYTES + draft_detail::wbuf_bytes(c.dim, qd, qd + 2 * c.n_kv * c.hd, c.mlp_hidden, grid);
   static unsigned long long attr_set = 0;
   if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
     VN_CUDA(ctx, cudaFuncSetAttribute(draft_detail::draft_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      draft_detail::STAGE_BYTES + 65536 + 32768));
+                                      draft_detail::STAGE_BYTES + draft_detail::RED_BYTES + 32768));
     attr_set |= 1ull << (ctx->device & 63);
   }
   // cooperative: all CTAs are resident together, which the grid barriers need
@@ -530,6 +544,14 @@ int32_t launch_draft_stack(vn_model* m, vn_kv* kv, const int64_t* tokens, int B,
   ctx->launches++;
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return vn_fail(ctx, VN_ERR_CUDA, "launch of draft_layers_kernel failed: %s", cudaGetErrorString(e));
+  if (a.trace) {
+    long long t[64];
+    cudaStreamSynchronize(ctx->stream);
+    cudaMemcpy(t, trace_dev, sizeof t, cudaMemcpyDeviceToHost);
+    fprintf(stderr, "stack trace (us since start):");
+    for (int i = 1; i < 64 && t[i]; ++i) fprintf(stderr, " %.2f", (t[i] - t[0]) * 1e-3);
+    fprintf(stderr, "\n");
+  }
   return VN_OK;
 }
 

@@ -426,7 +426,7 @@ class VerseNexLM:
 
     def set_fused_stack(self, on: bool):
         """Run the whole layer stack as one cooperative kernel where the model allows it (small all-TriSparse bf16
-        models: the draft); off keeps the chain of separate kernels."""
+        models: the draft).  Off by default: the chain of separate kernels is as fast on B200."""
         self.ctx._check(self.ctx.lib.vn_model_set_fused_stack(self.handle, int(bool(on))))
 
     # -- generate (cometspark.py:773-830) -------------------------------------------
