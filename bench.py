@@ -52,7 +52,7 @@ ACCEPT = dict(B=64, k=4, V=248320, seed=1234, temperature=1.0)
 # DRAM bytes of one verify + accept step of the default workload, summed over its kernels from the ncu capture
 # summarised in profiles/spec_step_dram_traffic.txt (B=32, ctx about 550).  ncu flushes the caches before every
 # kernel, so partial tiles and logits that the real run finds in L2 count as DRAM here: an upper bound.
-SPEC_STEP_TRAFFIC = 4264900000
+SPEC_STEP_TRAFFIC = 3565000000
 
 
 def accept_bytes(B, k, V):
@@ -795,6 +795,47 @@ def cpu_small_run():
     return 128 / dt, dt, st
 
 
+def run_layer(args):
+    """One MoD + one TriSparse layer of the mate shapes (D=1024, 16 heads / 8 KV heads, window 1024, 128 sinks) with a
+    small vocabulary: the per-layer kernels of the verify step on a case small enough for a full ncu capture
+    (about 60 MB of weights, 0.3 GB of KV cache).  32 sequences at context 1100, 5 new rows each, as in the round."""
+    import versenext_b200 as vn
+    from versenext_b200 import synthetic as S
+    world, rank, local, dist = dist_setup(args.gpus)
+    ctx = vn.Context.get(local)
+    kw = S.mate_kwargs(vocab_size=8192, n_layer=2, layer_pattern=["mod", "trisparse"], max_seq_len=2048)
+    m = vn.VerseNexLM(dtype="bf16", device=f"cuda:{local}", **kw)
+    S.load_random(m, kw, seed=3)
+    B, T0, Tn = 32, 1100, 5
+    rng = np.random.default_rng(5)
+    cache = m.new_cache(B, T0 + 64)
+    for lo in range(0, T0, 220):                       # prefill in pieces of 220 positions
+        m.forward_cached(rng.integers(0, 8192, (B, 220)).astype(np.int64), cache, want_logits=False)
+        cache.commit(220, np.full(B, 220, np.int32))
+    nxt = ctx.from_numpy(rng.integers(0, 8192, (B, Tn)).astype(np.int64))
+    out = ctx.empty((B, Tn, 8192), np.float32)
+    for _ in range(max(args.warmup, 3)):
+        m.forward_cached(nxt, cache, out_logits=out)
+    barrier_sync(dist, ctx)
+    l0 = ctx.launch_count()
+    e0, e1 = ctx.event(), ctx.event()
+    e0.record()
+    for _ in range(args.steps):
+        m.forward_cached(nxt, cache, out_logits=out)
+    e1.record()
+    barrier_sync(dist, ctx)
+    ms = max_over_ranks(dist, e0.elapsed_ms(e1), local) / args.steps
+    if rank == 0:
+        print(json.dumps({"metric": "two-layer slice forward", "value": ms, "unit": "ms", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                          "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": "layer: one MoD + one TriSparse layer of the mate shapes, V=8192, "
+                                                 "32 sequences at context 1100, 5 new rows each (eager launches)"},
+                          "gpu_launches": ctx.launch_count() - l0}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_small(args):
     import versenext_b200 as vn
     world, rank, local, dist = dist_setup(args.gpus)
@@ -1009,7 +1050,7 @@ def main():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="spec", choices=["spec", "accept", "sharded", "tree", "small"])
+    ap.add_argument("--workload", default="spec", choices=["spec", "accept", "sharded", "tree", "small", "layer"])
     ap.add_argument("--weak", action="store_true",
                     help="spec workload: 32 requests on every rank (default: the configuration's 32 split over the ranks)")
     ap.add_argument("--no-weak", action="store_true", help="N > 1: skip the extra 32-per-GPU measurement")
@@ -1023,7 +1064,7 @@ def main():
         {"accept": run_reference, "small": run_reference_small}.get(args.workload, run_reference_spec)(args)
     else:
         {"spec": run_spec, "accept": run_accept, "sharded": run_sharded, "tree": run_tree,
-         "small": run_small}[args.workload](args)
+         "small": run_small, "layer": run_layer}[args.workload](args)
 
 
 if __name__ == "__main__":

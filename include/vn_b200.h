@@ -315,6 +315,20 @@ int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
                          const int32_t* parents_host, float* out_hidden_dev, float* out_logits_dev,
                          int32_t last_only, int32_t slot_offset);
 
+/* The draft side of one speculative round with a draft MODEL (the north star's replacement for the k linear heads of
+ * SpeculativeDecoder.draft, speculative.py:110-162): k proposals per request, token by token, all on the device.
+ *   pair_dev [B, 2] int64: the last two committed tokens of every request; the draft's cache holds everything
+ *   before them.  Step 0 forwards both (slots len, len + 1), step i > 0 forwards proposal i - 1 (slot len + i + 1);
+ *   nothing is committed: after the round keep the first n entries with vn_kv_commit(kv, k + 1, ...).
+ *   Step i writes its last-position logits to q_logits_dev [k, B, V] (the acceptance test needs q), samples with
+ *   the Philox counter (position i, row b, purpose 2, offset) -- argmax when temperature <= 0 -- into
+ *   step_tokens_dev [k, B], and, when q_lists_dev is given ([k, B] records of vn_topk_row_bytes() bytes), leaves the
+ *   kept top-k list there for vn_verify_accept.  No synchronisation, no allocation once the model's buffers have the
+ *   size: the whole call can sit inside a captured graph. */
+int32_t vn_draft_propose(vn_model* draft, vn_kv* kv, const int64_t* pair_dev, int32_t B, int32_t k, float temperature,
+                         int32_t top_k, uint64_t seed, uint32_t offset, float* q_logits_dev, int64_t* step_tokens_dev,
+                         void* q_lists_dev);
+
 /* Verify + accept in one call: the target forward over the T = k (+1 with bonus) new positions of every sequence
  * (tokens_dev [B, T]: last committed token, then the proposals), the LM head, and the acceptance rule of vn_accept
  * -- replaces head(x) (cometspark.py:690-697), the softmax / top-k (cometspark.py:892-911) and the compare

@@ -231,6 +231,9 @@ static int32_t launch_accept_stats(vn_ctx* ctx, bool vec, bool greedy, int grid,
 // ---- kernel B: per-sequence decision --------------------------------------
 __device__ __forceinline__ float scaled(float x, float temp) { return temp != 1.0f ? __fdiv_rn(x, temp) : x; }
 
+// one warp per row of the sequence (at least 4 warps): the rows' chunk records are merged side by side
+static inline int decide_threads(int rows_per_seq) { return 32 * std::min(32, std::max(4, rows_per_seq)); }
+
 __global__ void accept_decide_kernel(RowSet rs, int B, int k, int nchunks, const Partial* __restrict__ part,
                                      const long long* __restrict__ draft, const float* __restrict__ u_acc,
                                      const float* __restrict__ u_smp, uint64_t seed, uint32_t offset_host,
@@ -447,19 +450,37 @@ accept_pick_kernel(RowSet rs, int k, int nchunks, float temp, const Decision* __
     w[e] = v;
     local += v;
   }
-  s_part[tid] = local;
-  __syncthreads();
-  if (tid == 0) {
-    double cum = s_before; int chosen = -1; int last_nz = -1;
-    for (int t = 0; t < STATS_THREADS; ++t) {
-      if (s_part[t] > 0.0) last_nz = t;
-      if (chosen < 0 && cum + s_part[t] > s_target) { chosen = t; s_before = cum; }
-      cum += s_part[t];
+  // which thread's 16 tokens hold the target: an exclusive scan of the threads' sums (warp shuffles, then the
+  // warps' totals), the first thread whose running sum passes the target; the last thread with weight when
+  // rounding pushed the target past the total
+  {
+    const int lane = tid & 31, warp = tid >> 5;
+    double incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const double up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
     }
-    if (chosen < 0) { chosen = last_nz < 0 ? 0 : last_nz; s_before = -1.0; }
-    s_thread = chosen;
+    if (lane == 31) s_part[warp] = incl;
+    if (tid == 0) s_thread = 0x7fffffff;
+    __shared__ int s_last;
+    if (tid == 0) s_last = -1;
+    __syncthreads();
+    double before = s_before;
+    for (int w2 = 0; w2 < warp; ++w2) before += s_part[w2];
+    const double excl = before + (incl - local);
+    if (excl + local > s_target) atomicMin(&s_thread, tid);
+    if (local > 0.0) atomicMax(&s_last, tid);
+    __syncthreads();
+    const int chosen = s_thread;
+    __syncthreads();
+    if (chosen == 0x7fffffff) {
+      if (tid == 0) { s_thread = s_last < 0 ? 0 : s_last; s_before = -1.0; }
+    } else if (tid == chosen) {
+      s_before = excl;
+    }
+    __syncthreads();
   }
-  __syncthreads();
   if (tid == s_thread) {
     int pick = -1, last_nz = -1;
     if (s_before >= 0.0) {
@@ -1455,7 +1476,7 @@ int32_t vn_accept_impl(vn_ctx* ctx, const float* p, long long p_sb, long long p_
   const long long nitems = (long long)n_part;
   const int grid = (int)std::min<long long>(nitems, (long long)ctx->sm_count * 8);
   { const int32_t st_ = launch_accept_stats(ctx, vec, greedy, grid, rs, B, nchunks, temp, part); if (st_) return st_; }
-  VN_LAUNCH(ctx, accept_decide_kernel, B, 128, 0, rs, B, k, nchunks, part, d64, u_acc, u_smp, seed, offset,
+  VN_LAUNCH(ctx, accept_decide_kernel, B, decide_threads(rows_per_seq), 0, rs, B, k, nchunks, part, d64, u_acc, u_smp, seed, offset,
             ctx->offset_src, temp, (int)greedy, bonus, smp_purpose, pos_base, dec, out_len, o64);
   if (!greedy) {
     dim3 g(nchunks, B);

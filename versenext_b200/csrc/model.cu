@@ -1558,6 +1558,28 @@ int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
   return forward_t<float>(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
 }
 
+int32_t vn_draft_propose(vn_model* draft, vn_kv* kv, const int64_t* pair_dev, int32_t B, int32_t k, float temperature,
+                         int32_t top_k, uint64_t seed, uint32_t offset, float* q_logits_dev, int64_t* step_tokens_dev,
+                         void* q_lists_dev) {
+  if (!draft || !kv) return vn_fail(nullptr, VN_ERR_INVALID, "null draft model or cache");
+  vn_ctx* ctx = draft->ctx;
+  VN_CHECK_CTX(ctx);
+  if (!pair_dev || !q_logits_dev || !step_tokens_dev || B < 1 || k < 1)
+    return vn_fail(ctx, VN_ERR_INVALID, "vn_draft_propose: null buffer, B < 1 or k < 1");
+  const long long V = draft->cfg.vocab;
+  const size_t row_bytes = vn_topk_row_bytes();
+  for (int i = 0; i < k; ++i) {
+    float* q_i = q_logits_dev + (long long)i * B * V;
+    // step 0 consumes the last two committed tokens (the cache holds everything before them); step i the proposal i - 1
+    if (i == 0) TRY(vn_model_forward(draft, kv, pair_dev, B, 2, nullptr, nullptr, q_i, 1, 0));
+    else TRY(vn_model_forward(draft, kv, step_tokens_dev + (long long)(i - 1) * B, B, 1, nullptr, nullptr, q_i, 1, i + 1));
+    void* lists_i = q_lists_dev ? (void*)((unsigned char*)q_lists_dev + (size_t)i * B * row_bytes) : nullptr;
+    TRY(vn_sample_lists(ctx, q_i, V, B, (int32_t)V, temperature, top_k, nullptr, seed, offset, (uint32_t)i, 2u,
+                        step_tokens_dev + (long long)i * B, lists_i));
+  }
+  return VN_OK;
+}
+
 int32_t vn_verify_accept(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int32_t B, int32_t T, int32_t k,
                          const void* q_lists_dev, int64_t ql_stride_b, int64_t ql_stride_i, const float* q_logits_dev,
                          int64_t q_stride_b, int64_t q_stride_i, const int64_t* draft_dev, const float* u_accept_dev,

@@ -119,18 +119,14 @@ class SpecEngine:
         ctx._check(lib.vn_set_offset_source(ctx.handle, _ptr(self.round_dev)))
         try:
             if draft_part:
-                # draft: k proposals; the first forward consumes the last two committed tokens
-                for i in range(k):
-                    q_i = self.q_logits[i]
-                    if i == 0:
-                        self.draft.forward_cached(self.pair, self.d_cache, last_only=True, out_logits=q_i,
-                                                  slot_offset=0)
-                    else:
-                        self.draft.forward_cached(self.step_tokens[i - 1].reshape(B, 1), self.d_cache,
-                                                  last_only=True, out_logits=q_i, slot_offset=i + 1)
-                    lists_i = C.c_void_p(self.q_lists.ptr + i * B * self.row_bytes) if self.fused_head else None
-                    ctx._check(lib.vn_sample_lists(ctx.handle, _ptr(q_i), V, B, V, self.temperature, self.top_k, None,
-                                                   self.seed, 0, i, PURPOSE_DRAFT, _ptr(self.step_tokens[i]), lists_i))
+                # draft: k proposals, token by token on the device; the first forward consumes the last two
+                # committed tokens.  Step i's kept top-k list stays at record i * B + b for the fused verify.
+                if not self.draft._finalized:
+                    self.draft.finalize()
+                ctx._check(lib.vn_draft_propose(
+                    self.draft.handle, self.d_cache.handle, _ptr(self.pair), B, k, self.temperature, self.top_k,
+                    self.seed, 0, _ptr(self.q_logits), _ptr(self.step_tokens),
+                    _ptr(self.q_lists) if self.fused_head else None))
                 ctx._check(lib.vn_spec_gather(ctx.handle, _ptr(self.step_tokens), _ptr(self.pair), B, k,
                                               self.n_verify, _ptr(self.draft_tokens), _ptr(self.verify_tokens)))
             # target: one forward over (last committed, d_0 .. d_{n_verify-2}), LM head and acceptance in one call;
