@@ -61,6 +61,20 @@ def test_ops_accept_device_arrays_and_odd_shapes(be):
     np.testing.assert_allclose(be.matmul(b3, c3).numpy(), b3 @ c3, rtol=1e-4, atol=1e-5)
 
 
+@pytest.mark.parametrize("rows", [1, 2, 3, 5, 8, 9, 17, 32, 33])
+def test_linear_with_few_rows_and_many_features(be, rows):
+    """Few rows against a wide weight matrix take the weight-streaming kernel (up to 32 rows; 33 the tiled one):
+    feature counts that are no multiple of the warps' groups of four, with and without bias, K = 128 and 1024."""
+    rng = np.random.default_rng(rows)
+    for K, N in ((128, 1027), (1024, 4098)):
+        x = rng.normal(0, 1, (rows, K)).astype(np.float32)
+        w = rng.normal(0, 1, (N, K)).astype(np.float32)
+        b = rng.normal(0, 1, (N,)).astype(np.float32)
+        want = x.astype(np.float64) @ w.T.astype(np.float64)
+        np.testing.assert_allclose(be.linear(x, w).numpy(), want, rtol=2e-5, atol=2e-4)
+        np.testing.assert_allclose(be.linear(x, w, b).numpy(), want + b, rtol=2e-5, atol=2e-4)
+
+
 def test_shape_errors(be):
     with pytest.raises(ValueError):
         be.matmul(np.zeros((2, 3), np.float32), np.zeros((4, 5), np.float32))

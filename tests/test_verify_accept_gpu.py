@@ -165,3 +165,67 @@ def OA_sample(rows, T, top_k, seed, position):
         u = OP.uniform(seed, 0, r, position, 2)
         out[r] = OA._inverse_cdf(OA.softmax64(rows[r], T, top_k), float(u))
     return out
+
+
+def test_draft_propose_equals_the_step_by_step_loop():
+    """`vn_draft_propose`: k forwards + top-k sampling in one C call -- the same proposals, logits and kept lists as
+    the loop of `vn_model_forward` (two tokens first, then one at a growing slot offset) and `vn_sample_lists`
+    written out by hand; a second call on the same state repeats them (nothing was committed)."""
+    import versenext_b200 as vn
+    rng = np.random.default_rng(77)
+    V, B, k, top_k, T = 4096, 5, 4, 12, 0.9
+    cfg = OM.small_config(vocab_size=V, dim=128, n_layer=2, n_head=2, n_kv_head=2, window_size=32, num_global_tokens=8,
+                          max_seq_len=256)
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=4, gate_std=1.0).items()}
+    kw = cfg.to_dict()
+    kw.pop("init_std")
+    d = vn.VerseNexLM(dtype="bf16", **kw)
+    d.load_state_dict(sd)
+    ctx, lib = d.ctx, d.ctx.lib
+    cache = d.new_cache(B, 128)
+    d.forward_cached(rng.integers(0, V, (B, 30)), cache, want_logits=False)
+    cache.commit(30, np.full(B, 30, np.int32))
+    pair = ctx.from_numpy(rng.integers(0, V, (B, 2)).astype(np.int64))
+    rec = int(lib.vn_topk_row_bytes())
+    seed = 99
+
+    def by_hand():
+        q = ctx.zeros((k, B, V), np.float32)
+        steps = ctx.zeros((k, B), np.int64)
+        lists = ctx.zeros((k * B * rec,), np.uint8)
+        for i in range(k):
+            if i == 0:
+                d.forward_cached(pair, cache, last_only=True, out_logits=q[i], slot_offset=0)
+            else:
+                d.forward_cached(steps[i - 1].reshape(B, 1), cache, last_only=True, out_logits=q[i], slot_offset=i + 1)
+            ctx._check(lib.vn_sample_lists(ctx.handle, _ptr(q[i]), V, B, V, T, top_k, None, seed, 3, i, 2, _ptr(steps[i]),
+                                           C.c_void_p(lists.ptr + i * B * rec)))
+        return q.numpy(), steps.numpy(), lists.numpy()
+
+    def one_call():
+        q = ctx.zeros((k, B, V), np.float32)
+        steps = ctx.zeros((k, B), np.int64)
+        lists = ctx.zeros((k * B * rec,), np.uint8)
+        ctx._check(lib.vn_draft_propose(d.handle, cache.handle, _ptr(pair), B, k, T, top_k, seed, 3, _ptr(q), _ptr(steps),
+                                        _ptr(lists)))
+        return q.numpy(), steps.numpy(), lists.numpy()
+
+    want = by_hand()
+    got = one_call()
+    again = one_call()
+    for a, b, c in zip(want, got, again):
+        np.testing.assert_array_equal(a, b)
+        np.testing.assert_array_equal(b, c)
+    assert got[1].min() >= 0 and got[1].max() < V
+    # the proposals are draws from the draft's own top-k distribution: every token lies in its row's kept set
+    for i in range(k):
+        kth = np.sort(got[0][i], axis=-1)[:, -top_k]
+        assert np.all(got[0][i][np.arange(B), got[1][i]] >= kth)
+    # greedy rule: arg-max proposals, no lists
+    q = ctx.zeros((k, B, V), np.float32)
+    steps = ctx.zeros((k, B), np.int64)
+    ctx._check(lib.vn_draft_propose(d.handle, cache.handle, _ptr(pair), B, k, 0.0, 0, seed, 0, _ptr(q), _ptr(steps), None))
+    np.testing.assert_array_equal(steps.numpy(), np.argmax(q.numpy(), -1))
+    with pytest.raises(ValueError):
+        ctx._check(lib.vn_draft_propose(d.handle, cache.handle, _ptr(pair), B, 0, T, top_k, seed, 0, _ptr(q), _ptr(steps), None))
+    d.check()

@@ -2,6 +2,8 @@
 #include "common.cuh"
 #include "gemm.cuh"
 #include <math_constants.h>
+#include <stdint.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -115,6 +117,61 @@ __global__ void __launch_bounds__(128) attention_kernel(const float* __restrict_
   }
 }
 
+
+// ---- fp32 linear for a few rows against a large weight matrix (the k draft heads of SpeculativeDecoder.draft:
+// 4 x 248,320 x 1,024 fp32 = 4 GB of weights for 1 to 32 hidden rows, speculative.py:150-158) -------------------
+// Weight streaming: a warp owns SK_NR consecutive output features and walks K in float4 steps, one 512-byte coalesced
+// segment of every weight row per trip, against up to 8 rows of x at a time (x is a few KB: it stays in L1).  With
+// more than 8 rows the warp makes one pass per group of 8 over the same weight rows, which it finds in L1 / L2, so
+// DRAM still sees every weight once.  Per output: each lane sums its k = 4 * lane + 128 * i terms in order, then the
+// lanes are added by a shuffle tree: deterministic.
+constexpr int SK_NR = 4;
+template <int MR>
+__global__ void __launch_bounds__(256, 2) linear_skinny_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                            const float* __restrict__ bias, float* __restrict__ y,
+                                                            int M, long long N, int K) {
+  const int lane = threadIdx.x & 31;
+  const long long n0 = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * SK_NR;
+  if (n0 >= N) return;
+  const float* wr[SK_NR];
+#pragma unroll
+  for (int j = 0; j < SK_NR; ++j) wr[j] = w + (n0 + j < N ? n0 + j : N - 1) * (long long)K;
+  for (int m0 = 0; m0 < M; m0 += MR) {
+    float acc[SK_NR][MR];
+#pragma unroll
+    for (int j = 0; j < SK_NR; ++j)
+#pragma unroll
+      for (int i = 0; i < MR; ++i) acc[j][i] = 0.f;
+#pragma unroll 1
+    for (int k = lane * 4; k < K; k += 128) {
+      float4 wv[SK_NR];
+#pragma unroll
+      for (int j = 0; j < SK_NR; ++j) wv[j] = *reinterpret_cast<const float4*>(wr[j] + k);
+#pragma unroll
+      for (int i = 0; i < MR; ++i) {
+        const int m = m0 + i < M ? m0 + i : M - 1;
+        const float4 xv = __ldg(reinterpret_cast<const float4*>(x + (long long)m * K + k));
+#pragma unroll
+        for (int j = 0; j < SK_NR; ++j) {
+          acc[j][i] = fmaf(xv.x, wv[j].x, acc[j][i]);
+          acc[j][i] = fmaf(xv.y, wv[j].y, acc[j][i]);
+          acc[j][i] = fmaf(xv.z, wv[j].z, acc[j][i]);
+          acc[j][i] = fmaf(xv.w, wv[j].w, acc[j][i]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < SK_NR; ++j)
+#pragma unroll
+      for (int i = 0; i < MR; ++i) {
+        float v = acc[j][i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && m0 + i < M && n0 + j < N) y[(long long)(m0 + i) * N + n0 + j] = v + (bias ? bias[n0 + j] : 0.f);
+      }
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -139,6 +196,17 @@ int32_t vn_linear(vn_ctx* ctx, const float* x, const float* w, const float* bias
   VN_REQUIRE(ctx, x && w && y, "null pointer");
   VN_REQUIRE(ctx, M >= 0 && N >= 0 && K >= 0, "bad shape");
   if (M * N == 0) return VN_OK;
+  // few rows against many output features: the weight-streaming kernel
+  // VN_LINEAR_SKINNY_MAX: most rows the streaming kernel takes (default 32; 0 keeps the tiled kernel: A/B timing)
+  static const int skinny_max = [] { const char* e = getenv("VN_LINEAR_SKINNY_MAX"); return e ? atoi(e) : 32; }();
+  if (M <= skinny_max && N >= 1024 && K % 4 == 0 && K >= 128 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+    const unsigned grid = (unsigned)ceil_div(N, (int64_t)(8 * SK_NR));
+    if (M == 1) VN_LAUNCH(ctx, linear_skinny_kernel<1>, grid, 256, 0, x, w, bias, y, (int)M, (long long)N, (int)K);
+    else if (M == 2) VN_LAUNCH(ctx, linear_skinny_kernel<2>, grid, 256, 0, x, w, bias, y, (int)M, (long long)N, (int)K);
+    else if (M <= 4) VN_LAUNCH(ctx, linear_skinny_kernel<4>, grid, 256, 0, x, w, bias, y, (int)M, (long long)N, (int)K);
+    else VN_LAUNCH(ctx, linear_skinny_kernel<8>, grid, 256, 0, x, w, bias, y, (int)M, (long long)N, (int)K);
+    return VN_OK;
+  }
   GemmArgs g;
   g.A = x; g.lda = K; g.W = w; g.ldw = K; g.C = y; g.ldc = N; g.bias = bias;
   g.M = (int)M; g.N = (int)N; g.K = (int)K;

@@ -210,6 +210,9 @@ class ShardedAccept:
         self.B, self.k = self.draft.shape
         self.ua = np.asarray(u_accept, dtype=np.float32) if u_accept is not None else None
         self.us = np.asarray(u_sample, dtype=np.float32) if u_sample is not None else None
+        if not self.greedy and (self.ua is None or self.us is None):
+            raise ValueError("the host protocol needs u_accept (B, k) and u_sample (B, k + 1) for the stochastic rule; "
+                             "the device path (vn_shard_accept) draws its own Philox numbers")
         self.acc = np.zeros(self.B, dtype=np.int32)
         self.out = np.full((self.B, self.k + 1), -1, dtype=np.int64)
 

@@ -358,10 +358,9 @@ def _split_heads(ctx: Context, logits: DeviceArray, B: int, k: int, V: int) -> L
         return [logits.reshape(k, V)[i:i + 1] for i in range(k)]
     import ctypes as C
     outs = []
-    for i in range(k):
+    for i in range(k):                       # head i: B rows of V floats, k * V floats apart -> one pitched copy
         o = ctx.empty((B, V), np.float32)
-        for b in range(B):
-            ctx._check(ctx.lib.vn_d2d(ctx.handle, C.c_void_p(o.ptr + b * V * 4),
-                                      C.c_void_p(logits.ptr + (b * k + i) * V * 4), V * 4))
+        ctx._check(ctx.lib.vn_copy_2d(ctx.handle, C.c_void_p(o.ptr), V * 4, C.c_void_p(logits.ptr + i * V * 4), k * V * 4,
+                                      V * 4, B))
         outs.append(o)
     return outs
