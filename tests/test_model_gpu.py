@@ -384,6 +384,33 @@ def test_fused_layer_stack_of_a_draft_model():
     assert np.array_equal(m.forward_cached(nxt, cache).numpy(), lg_all)
 
 
+def test_prompt_gemms_on_the_tensor_core_kernel_in_row_segments(monkeypatch):
+    """More than 256 rows (a prompt): the dense projections run on the tcgen05 kernel as segments of 256 rows that
+    share one weight matrix.  393 rows = one full segment + 137 (no multiple of 16); against the oracle and against
+    the mma.sync kernels; then a decode step on the cache the prompt left."""
+    cfg = hd64_cfg()
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=41, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    rng = np.random.default_rng(14)
+    B, T = 3, 131
+    toks = rng.integers(0, 384, (B, T))
+    want, oc = OM.forward(sd, cfg, toks)
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("VN_PREFILL_TC", flag)
+        cache = m.new_cache(B, 192)
+        l0 = m.ctx.launch_count()
+        outs[flag] = m.forward_cached(toks, cache).numpy()
+        assert rel_err(outs[flag], want) < 2e-2
+        cache.commit(T, np.full(B, T, np.int32))
+        nxt = rng.integers(0, 384, (B, 2)) if flag == "1" else nxt
+        lg = m.forward_cached(nxt, cache).numpy()
+        want2, _ = OM.forward(sd, cfg, nxt, cache=oc)
+        assert rel_err(lg, want2) < 2e-2
+    assert rel_err(outs["1"], outs["0"]) < 1e-2
+    m.check()
+
+
 def test_persistent_gemm_variant(monkeypatch):
     """Opt-in persistent tile-loop GEMM (one CTA per SM, double-buffered TMEM accumulator), forced onto the small
     shapes of this model: dense store, split-K partial and per-expert SwiGLU tiles give the same logits."""

@@ -139,6 +139,8 @@ struct vn_model {
   float* partial = nullptr;      // split-K workspace of the tcgen05 path
   size_t partial_bytes = 0;
   int* tc_error = nullptr;       // device word raised by a bounded wait that ran out
+  int* row_seg = nullptr;        // [2][row_seg_n] offsets and counts of the 256-row segments a prompt's GEMMs use
+  int row_seg_cap = 0, row_seg_n = 0, row_seg_rows = 0;
   unsigned* stack_bar = nullptr; // two device words: arrivals and generation of the fused layer stack's grid barrier
   bool recurrent = false;        // vn_model_set_recurrent: ALiBi path as in the reference's one-token recurrent step
   bool fused_stack = false;      // vn_model_set_fused_stack / VN_DRAFT_STACK=1: the layer stack as one cooperative kernel
@@ -278,6 +280,8 @@ int32_t ensure_rows(vn_model* m, int M) {
 }
 
 // one Linear: C = A @ W^T with the epilogue, dispatching on the storage dtype
+int32_t ensure_partial(vn_model* m, size_t bytes);
+
 int32_t linear(vn_model* m, GemmArgs g) {
   vn_ctx* ctx = m->ctx;
   if (g.wq) {
@@ -285,6 +289,37 @@ int32_t linear(vn_model* m, GemmArgs g) {
     return launch_gemm_mma_q(ctx, g);
   }
   if (m->cfg.bf16) {
+    // Many rows (a prompt): the tcgen05 kernel takes the rows as segments of 256 -- the same code path as the experts'
+    // row segments, every segment with the same weight matrix (stride 0).  A weight tile is then fetched once per
+    // segment, from L2 after the first.  VN_PREFILL_TC=0 (read per call) keeps the mma.sync kernel.
+    const char* pe = getenv("VN_PREFILL_TC");
+    if (m->use_tc && !(pe && pe[0] == '0') && g.M > 256 && !g.seg_cnt && !g.a_rows && g.nseg == 1 && !g.bias &&
+        g.K % 8 == 0 && g.ldw_k == 1 && tc_detail::encode_fn() != nullptr &&
+        (g.epi == EPI_STORE || g.epi == EPI_ADD || g.epi == EPI_SWIGLU)) {
+      const int nseg = ceil_div(g.M, 256);
+      if (m->row_seg_rows != g.M) {
+        if (nseg > m->row_seg_cap) {
+          VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+          if (m->row_seg) VN_CUDA(ctx, cudaFree(m->row_seg));
+          m->row_seg = nullptr; m->row_seg_cap = 0;
+          TRY(dev_alloc(ctx, (void**)&m->row_seg, (size_t)2 * nseg * sizeof(int)));
+          m->row_seg_cap = nseg;
+        }
+        std::vector<int> host(2 * (size_t)nseg);
+        for (int i = 0; i < nseg; ++i) { host[i] = 256 * i; host[nseg + i] = std::min(256, g.M - 256 * i); }
+        VN_CUDA(ctx, cudaMemcpyAsync(m->row_seg, host.data(), host.size() * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+        VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // host vector goes out of scope
+        m->row_seg_rows = g.M; m->row_seg_n = nseg;
+      }
+      TRY(ensure_partial(m, 1024));                               // the error word
+      GemmArgs g2 = g;
+      g2.M = 256; g2.seg_off = m->row_seg; g2.seg_cnt = m->row_seg + m->row_seg_n; g2.nseg = nseg; g2.w_stride = 0;
+      if (gemm_tc_supported(g2)) {
+        TcPlan plan;
+        plan.error_flag = m->tc_error;
+        return launch_gemm_tc(ctx, g2, g.M, plan);
+      }
+    }
     if (gemm_mma_supported(g)) return launch_gemm_mma(ctx, g);
     return launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g);
   }
@@ -902,7 +937,7 @@ int32_t vn_model_destroy(vn_model* m) {
   }
   F(m->x); F(m->h); F(m->h32); F(m->qkv); F(m->attn); F(m->act); F(m->y); F(m->slot_expert); F(m->slot_w); F(m->part_w);
   F(m->expert_count); F(m->expert_off); F(m->expert_cur); F(m->sorted_row); F(m->slot_pos); F(m->depth_dev);
-  F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->stack_bar); F(m->head_q); F(m->head_qs);
+  F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->stack_bar); F(m->row_seg); F(m->head_q); F(m->head_qs);
   for (auto& L : m->layers) for (int i = 0; i < 6; ++i) { F(L.q[i]); F(L.qs[i]); }
   delete m;
   return VN_OK;
