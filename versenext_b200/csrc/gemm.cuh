@@ -18,6 +18,8 @@ struct GemmArgs {
   // segmented (grouped) mode: blockIdx.z selects a segment of rows and its own weight matrix
   const int* seg_off = nullptr;   // [nseg] first row of the segment (device)
   const int* seg_cnt = nullptr;   // [nseg] rows in the segment (device)
+  const int* seg_w = nullptr;     // [nseg] which of the n_w weight matrices a segment uses (device), or null: segment z uses matrix z
+  int n_w = 0;                    // number of weight matrices when seg_w is given
   const int* a_rows = nullptr;    // optional gather: A row = a_rows[row]
   long long w_stride = 0;         // elements between consecutive segments' / batches' weights
   long long a_stride = 0, c_stride = 0;  // plain batched mode (no seg_cnt): per-z offsets of A and C

@@ -68,7 +68,8 @@ struct TcArgs {
   int epi, c_bf16;
   const int* seg_off;      // segmented mode (blockIdx.z = segment)
   const int* seg_cnt;
-  long long w_rows_per_seg;  // rows of W between consecutive segments
+  long long w_rows_per_seg;  // rows of W between consecutive weight matrices
+  const int* seg_w;          // weight matrix of segment z, or null (matrix z)
   float* partial;          // split-K workspace [gridDim.y][rows_total][N] or null
   long long partial_stride;  // rows_total * N
   int* error_flag;
@@ -408,7 +409,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const int w_row = (int)((long long)z * g.w_rows_per_seg) + n0;
+      const int w_row = (int)((long long)(g.seg_w ? g.seg_w[z] : z) * g.w_rows_per_seg) + n0;
       int kb_first = 0;
       if (!g.seg_cnt) {
         const int npre = nkb < S ? nkb : S;
@@ -744,7 +745,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         tile_info(id, z, y, n0, row0, cnt, kb0, nkb);
         if (cnt <= 0 || nkb <= 0) continue;
         const int cnt16 = (cnt + 15) & ~15;
-        const int w_row = (int)((long long)z * g.w_rows_per_seg) + n0;
+        const int w_row = (int)((long long)(g.seg_w ? g.seg_w[z] : z) * g.w_rows_per_seg) + n0;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(&bar_empty[s], ((it / S) & 1) ^ 1)) { s_error = 1; ok = false; break; }
@@ -959,7 +960,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   if (g.M <= 0 || g.N <= 0) return VN_OK;
   const int ntok = (g.M + 15) & ~15;
   CUtensorMap tm_w, tm_x;
-  const long long w_rows = g.seg_cnt ? (long long)(g.nseg - 1) * (g.w_stride / g.ldw) + g.N : g.N;
+  const long long w_rows = g.seg_cnt ? (long long)((g.seg_w ? g.n_w : g.nseg) - 1) * (g.w_stride / g.ldw) + g.N : g.N;
   if (!make_map(&tm_w, g.W, w_rows, g.K, g.ldw, BF) || !make_map(&tm_x, g.A, a_rows_total, g.K, g.lda, g.seg_cnt ? 16 : ntok))
     return vn_fail(ctx, VN_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   TcArgs a = {};
@@ -984,6 +985,7 @@ inline int32_t launch_gemm_tc(vn_ctx* ctx, const GemmArgs& g, long long a_rows_t
   a.epi = g.epi; a.c_bf16 = g.c_bf16;
   a.seg_off = g.seg_off; a.seg_cnt = g.seg_cnt;
   a.w_rows_per_seg = g.seg_cnt ? g.w_stride / g.ldw : 0;
+  a.seg_w = g.seg_w;
   const int gy = ceil_div(nkb, a.kb_per_split);
   plan.splits_used = gy;
   a.partial = (gy > 1 || plan.force_partial) ? plan.partial : nullptr;

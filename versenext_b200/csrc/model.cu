@@ -16,6 +16,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <set>
+#include <type_traits>
 
 namespace {
 
@@ -139,6 +140,8 @@ struct vn_model {
   float* partial = nullptr;      // split-K workspace of the tcgen05 path
   size_t partial_bytes = 0;
   int* tc_error = nullptr;       // device word raised by a bounded wait that ran out
+  int* sub_seg = nullptr;        // [3][sub_cap] offsets, counts and experts of the experts' 256-row pieces (prompt forwards)
+  int sub_cap = 0;
   int* row_seg = nullptr;        // [2][row_seg_n] offsets and counts of the 256-row segments a prompt's GEMMs use
   int row_seg_cap = 0, row_seg_n = 0, row_seg_rows = 0;
   unsigned* stack_bar = nullptr; // two device words: arrivals and generation of the fused layer stack's grid barrier
@@ -401,6 +404,42 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
       VN_LAUNCH(ctx, mod_offsets_kernel, 1, 32, 0, m->expert_count, m->expert_off, m->expert_cur, ne);
       VN_LAUNCH(ctx, mod_scatter_kernel, ceil_div(M * S, 256), 256, 0, m->slot_expert, m->expert_off, m->expert_cur,
                 m->sorted_row, m->slot_pos, M * S, S);
+      // Many routed rows on a bf16 model: the experts' segments are cut into pieces of at most 256 rows and run on
+      // the tcgen05 kernel (rows copied into expert order first, so that TMA loads them; a piece names its expert's
+      // weights through seg_w).  Otherwise the mma.sync kernels gather the rows themselves.
+      const char* pe = getenv("VN_PREFILL_TC");
+      const int n_sub = ne + ceil_div(M * S, 256);
+      const bool tc_experts = std::is_same<T, __nv_bfloat16>::value && m->use_tc && !m->qmode && !(pe && pe[0] == '0') &&
+                              (long long)M * S > 256 && m->hs && D % 8 == 0 && eh % 8 == 0 && n_sub <= 65535 &&
+                              tc_detail::encode_fn() != nullptr;
+      if (tc_experts) {
+        if (n_sub > m->sub_cap) {
+          VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+          if (m->sub_seg) VN_CUDA(ctx, cudaFree(m->sub_seg));
+          m->sub_seg = nullptr; m->sub_cap = 0;
+          TRY(dev_alloc(ctx, (void**)&m->sub_seg, (size_t)3 * n_sub * sizeof(int)));
+          m->sub_cap = n_sub;
+        }
+        int* sub_off = m->sub_seg; int* sub_cnt = m->sub_seg + m->sub_cap; int* sub_w = m->sub_seg + 2 * m->sub_cap;
+        VN_LAUNCH(ctx, mod_subseg_kernel, 1, 32, 0, (const int*)m->expert_count, (const int*)m->expert_off, ne, sub_off,
+                  sub_cnt, sub_w, n_sub);
+        VN_LAUNCH(ctx, gather_sorted_kernel<T>, M * S, 128, 0, (const T*)m->h, (const int*)m->sorted_row, (T*)m->hs, D);
+        TRY(ensure_partial(m, 1024));
+        TcPlan plan;
+        plan.error_flag = m->tc_error;
+        g = GemmArgs();
+        g.A = m->hs; g.lda = D; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
+        g.C = m->act; g.ldc = eh; g.M = 256; g.N = 2 * eh; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = 1;
+        g.seg_off = sub_off; g.seg_cnt = sub_cnt; g.seg_w = sub_w; g.n_w = ne; g.nseg = n_sub; g.tag = "gemm_expert_gateup";
+        TRY(launch_gemm_tc(ctx, g, (long long)M * S, plan));
+        g = GemmArgs();
+        g.A = m->act; g.lda = eh; g.W = L.e_down; g.ldw = eh; g.w_stride = (long long)D * eh; g.C = m->y; g.ldc = D;
+        g.M = 256; g.N = D; g.K = eh; g.seg_off = sub_off; g.seg_cnt = sub_cnt; g.seg_w = sub_w; g.n_w = ne; g.nseg = n_sub;
+        g.tag = "gemm_expert_down";
+        TcPlan plan2;
+        plan2.error_flag = m->tc_error;
+        TRY(launch_gemm_tc(ctx, g, (long long)M * S, plan2));
+      } else {
       g = GemmArgs();
       g.A = m->h; g.lda = D; g.a_rows = m->sorted_row; g.W = L.e_gateup; g.ldw = D; g.w_stride = (long long)2 * eh * D;
       g.C = m->act; g.ldc = eh; g.M = M; g.N = 2 * eh; g.K = D; g.epi = EPI_SWIGLU; g.c_bf16 = c.bf16;
@@ -413,6 +452,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
       g.tag = "gemm_expert_down";
       pick(g, L.e_down, L.q[5], L.qs[5], D);
       TRY(linear(m, g));
+      }
       VN_LAUNCH(ctx, mod_combine_kernel, M, 256, 0, m->x, m->y, m->slot_pos, m->slot_w, m->part_w, D, c.P, c.top_k);
       VN_CUDA(ctx, cudaMemsetAsync(m->expert_count, 0, ne * 4, ctx->stream));   // zero between forwards
       VN_CUDA(ctx, cudaMemsetAsync(m->expert_cur, 0, ne * 4, ctx->stream));
@@ -937,7 +977,7 @@ int32_t vn_model_destroy(vn_model* m) {
   }
   F(m->x); F(m->h); F(m->h32); F(m->qkv); F(m->attn); F(m->act); F(m->y); F(m->slot_expert); F(m->slot_w); F(m->part_w);
   F(m->expert_count); F(m->expert_off); F(m->expert_cur); F(m->sorted_row); F(m->slot_pos); F(m->depth_dev);
-  F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->stack_bar); F(m->row_seg); F(m->head_q); F(m->head_qs);
+  F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->stack_bar); F(m->row_seg); F(m->sub_seg); F(m->head_q); F(m->head_qs);
   for (auto& L : m->layers) for (int i = 0; i < 6; ++i) { F(L.q[i]); F(L.qs[i]); }
   delete m;
   return VN_OK;

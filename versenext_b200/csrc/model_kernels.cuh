@@ -460,6 +460,22 @@ __global__ void mod_offsets_kernel(const int* __restrict__ count, int* __restric
   }
 }
 
+// The experts' row segments cut into pieces of at most 256 rows (what one CTA of the tensor-core GEMM takes as its
+// token dimension): sub_off / sub_cnt / sub_w [n_sub_max] = first row, rows and expert of piece i; unused pieces get 0 rows.
+__global__ void mod_subseg_kernel(const int* __restrict__ count, const int* __restrict__ offset, int n_expert,
+                                  int* __restrict__ sub_off, int* __restrict__ sub_cnt, int* __restrict__ sub_w, int n_sub_max) {
+  pdl_trigger();
+  pdl_wait();
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int n = 0;
+    for (int e = 0; e < n_expert; ++e)
+      for (int r = 0; r < count[e] && n < n_sub_max; r += 256) {
+        sub_off[n] = offset[e] + r; sub_cnt[n] = min(256, count[e] - r); sub_w[n] = e; ++n;
+      }
+    for (; n < n_sub_max; ++n) { sub_off[n] = 0; sub_cnt[n] = 0; sub_w[n] = 0; }
+  }
+}
+
 // place every (token, slot) in its expert's segment; sorted_row[pos] = token row, slot_pos[token, slot] = pos
 __global__ void mod_scatter_kernel(const int* __restrict__ slot_expert, const int* __restrict__ offset,
                                    int* __restrict__ cursor, int* __restrict__ sorted_row, int* __restrict__ slot_pos,
