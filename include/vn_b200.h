@@ -362,6 +362,23 @@ int32_t vn_spec_gather(vn_ctx* ctx, const int64_t* step_tokens_dev, const int64_
 int32_t vn_spec_advance(vn_ctx* ctx, const int64_t* out_tokens_dev, int32_t B, int32_t k, int64_t* pair_dev,
                         int64_t* history_dev, int32_t cap, int32_t* count_dev, int32_t* n_commit_dev);
 
+/* Tree proposals (the north star's "batched or tree verification", greedy rule).
+ * vn_top_m: the m (<= 8) largest logits of each of R rows, best first, ties to the lower token id: the children a
+ *   draft proposes under one tree node.  Row r at logits_dev + r * row_stride; tokens to out_dev[r * out_stride + j].
+ * vn_tree_accept_greedy: after the target scored a tree (vn_model_forward with parents over T rows per sequence:
+ *   row 0 = the last committed token, rows 1 .. T-1 the nodes; parent_dev [T] = row of each row's parent, -1 for
+ *   row 0) and its arg-max per row is in target_arg_dev [B, T]: walk from row 0 along the children that carry the
+ *   target's token.  out_len_dev [B] = nodes accepted (<= depth), out_tokens_dev [B, depth + 1] = their tokens plus
+ *   the target's token at the stop, -1 padded -- exactly what greedy decoding of the target alone emits
+ *   (speculative.py:280-287 generalised from a chain to a tree).  keep_target_dev / keep_draft_dev [B, depth + 1]:
+ *   slot lists for vn_kv_commit of the two caches (count = accepted + 1 for both; the draft is taken to have
+ *   appended the last two committed tokens at slots 0, 1 and node row r at slot r + 1). */
+int32_t vn_top_m(vn_ctx* ctx, const float* logits_dev, int64_t row_stride, int32_t R, int32_t V, int32_t m,
+                 int64_t* out_dev, int64_t out_stride);
+int32_t vn_tree_accept_greedy(vn_ctx* ctx, const int64_t* tokens_dev, const int64_t* target_arg_dev, const int32_t* parent_dev,
+                              int32_t B, int32_t T, int32_t depth, int32_t* out_len_dev, int64_t* out_tokens_dev,
+                              int32_t* keep_target_dev, int32_t* keep_draft_dev);
+
 /* Device-side round counter: while set, every Philox offset passed to vn_accept* / vn_sample is
  * incremented by *counter_dev, and vn_spec_advance adds one to it at the end of a round. */
 int32_t vn_set_offset_source(vn_ctx* ctx, const uint32_t* counter_dev);

@@ -570,6 +570,102 @@ def test_generate_through_the_engine_equals_the_reference_streams(golden):
                                       r[f"{tag}_generate_eos"])
 
 
+CFG3_TREE = [-1, -1, -1, -1, 0, 0, 1, 1, 4, 4, 5, 5, 6, 6, 7, 7]
+
+
+def test_top_m_and_greedy_tree_acceptance_kernels():
+    """`vn_top_m` against a stable sort (ties to the lower id), `vn_tree_accept_greedy` against a walk in Python on
+    random trees' tokens: accepted path, committed tokens, the slot lists for both caches."""
+    import ctypes as C
+    import versenext_b200 as vn
+    ctx = vn.Context.get(0)
+    lib = ctx.lib
+    rng = np.random.default_rng(8)
+    R, V = 5, 3001
+    x = rng.integers(-6, 6, (R, V)).astype(np.float32)             # many ties
+    xd = ctx.from_numpy(x)
+    for m in (1, 3, 8):
+        out = ctx.zeros((R, 9), np.int64)
+        ctx._check(lib.vn_top_m(ctx.handle, C.c_void_p(xd.ptr), V, R, V, m, C.c_void_p(out.ptr), 9))
+        want = np.argsort(-x, axis=-1, kind="stable")[:, :m]
+        np.testing.assert_array_equal(out.numpy()[:, :m], want)
+    with pytest.raises(ValueError):
+        ctx._check(lib.vn_top_m(ctx.handle, C.c_void_p(xd.ptr), V, R, V, 9, C.c_void_p(out.ptr), 9))
+    parents, B, D = CFG3_TREE, 64, 3
+    T = len(parents) + 1
+    prow = np.array([-1] + [p + 1 for p in parents], np.int32)
+    tok = rng.integers(0, 6, (B, T)).astype(np.int64)
+    arg = rng.integers(0, 6, (B, T)).astype(np.int64)
+    for b in range(0, B, 3):                                        # make long paths likely in a third of the rows
+        cur = 0
+        for _ in range(D):
+            kids = [c for c in range(T) if prow[c] == cur]
+            if not kids:
+                break
+            nxt = kids[rng.integers(0, len(kids))]
+            arg[b, cur] = tok[b, nxt]
+            cur = nxt
+    o_len, o_tok = ctx.zeros((B,), np.int32), ctx.zeros((B, D + 1), np.int64)
+    kt, kd = ctx.zeros((B, D + 1), np.int32), ctx.zeros((B, D + 1), np.int32)
+    tok_d, arg_d, prow_d = ctx.from_numpy(tok), ctx.from_numpy(arg), ctx.from_numpy(prow)     # kept alive over the call
+    ctx._check(lib.vn_tree_accept_greedy(ctx.handle, C.c_void_p(tok_d.ptr), C.c_void_p(arg_d.ptr),
+                                         C.c_void_p(prow_d.ptr), B, T, D, C.c_void_p(o_len.ptr),
+                                         C.c_void_p(o_tok.ptr), C.c_void_p(kt.ptr), C.c_void_p(kd.ptr)))
+    o_len, o_tok, kt, kd = o_len.numpy(), o_tok.numpy(), kt.numpy(), kd.numpy()
+    seen = set()
+    for b in range(B):
+        cur, path = 0, []
+        while len(path) < D:
+            hit = [c for c in range(cur + 1, T) if prow[c] == cur and tok[b, c] == arg[b, cur]]
+            if not hit:
+                break
+            path.append(hit[0])
+            cur = hit[0]
+        a = len(path)
+        seen.add(a)
+        assert o_len[b] == a
+        want_tok = [tok[b, r] for r in path] + [arg[b, cur]] + [-1] * (D - a)
+        np.testing.assert_array_equal(o_tok[b], want_tok)
+        np.testing.assert_array_equal(kt[b, :a + 1], [0] + path)
+        np.testing.assert_array_equal(kd[b, :a + 1], ([0, 1] + [r + 1 for r in path])[:a + 1])
+    assert {0, 1, 2, 3} <= seen
+
+
+def test_tree_engine_commits_the_targets_greedy_stream(golden):
+    """Tree proposals (configuration 3's 16-node tree, and a plain chain written as a tree): the committed tokens are
+    the reference's greedy streams token for token, with a draft that often agrees (variant b) and one that rarely
+    does; more than one token per round is committed where the draft agrees."""
+    import versenext_b200 as vn
+    g = golden("model_small.npz")
+    t = build(OM.small_config(), _sd(g, "a_t."))
+    d = build(OM.small_config(n_layer=1), _sd(g, "a_d."))
+    eng = vn.TreeSpecEngine(t, d, CFG3_TREE, max_batch=1, max_seq=256, max_new_tokens=160)
+    toks, st = eng.generate(g["prompt"], 128)
+    np.testing.assert_array_equal(toks[:, :g["a_greedy"].shape[1]], g["a_greedy"])
+    t_cfg, t_sd, d_cfg, d_sd = variant_b()
+    t2, d2 = build(t_cfg, t_sd), build(d_cfg, d_sd)
+    rounds = {}
+    for name, tree in (("cfg3", CFG3_TREE), ("chain", [-1, 0, 1]), ("wide", [-1, -1, -1, -1, -1, -1])):
+        eng = vn.TreeSpecEngine(t2, d2, tree, max_batch=1, max_seq=256, max_new_tokens=128)
+        toks, st = eng.generate(g["prompt"], 96)
+        np.testing.assert_array_equal(toks[:, :g["b_greedy"].shape[1]], g["b_greedy"])
+        rounds[name] = st["rounds"]
+    assert rounds["cfg3"] <= rounds["chain"] < 96              # the tree never needs more rounds than its own first path
+    # a batch of ragged prompts (left as they are: each row its own length is not supported by prefill, so equal
+    # lengths, different contents) against per-request chain decoding
+    rng = np.random.default_rng(3)
+    prompts = rng.integers(0, 256, (4, 19))
+    eng = vn.TreeSpecEngine(t2, d2, CFG3_TREE, max_batch=4, max_seq=256, max_new_tokens=64)
+    toks, _ = eng.generate(prompts, 40)
+    for b in range(4):
+        want = t2.generate(prompts[b:b + 1], max_new_tokens=40, temperature=0.0, draft=d2, k=3)
+        np.testing.assert_array_equal(toks[b:b + 1, :want.shape[1]], want)
+    with pytest.raises(ValueError):
+        vn.TreeSpecEngine(t2, d2, [-1, 2, 0], max_batch=1, max_seq=64)
+    with pytest.raises(ValueError):
+        vn.TreeSpecEngine(t2, d2, [-1, -1, 0, 1, 0], max_batch=1, max_seq=64)
+
+
 def test_continuous_batching_serves_ragged_requests():
     """Seven requests of different prompt lengths and token budgets on three slots: a request leaves its slot when it
     is done and the next one is prefilled into it; every request's tokens equal its own greedy generation."""

@@ -4,6 +4,7 @@ Public surface (names follow the reference):
   SpeculativeDecoder                      verse_nex/speculative.py:55
   VerseNexLM (= CometSparkNexLM), KVCache verse_nex/cometspark.py:294, kv_cache_parallel.py:42
   SpecEngine                              batched draft -> verify -> accept -> commit loop
+  TreeSpecEngine                          the same with tree proposals (greedy rule)
   ShardedSpecEngine, Comm, rank_seed      the same with the LM head split by vocabulary columns over NCCL ranks
   VNFileReader, load_vn                   verse_torch/vn_format.py:527 (.vn container)
   get_backend / clear_backend_cache,
@@ -21,6 +22,7 @@ from .backend import DeviceBackend, B200Backend, get_backend, clear_backend_cach
 from .speculative import SpeculativeDecoder, Tensor, no_grad
 from .model import VerseNexLM, CometSparkNexLM, KVCache
 from .engine import SpecEngine
+from .tree_engine import TreeSpecEngine
 from .comm import Comm
 from .sharded_engine import ShardedSpecEngine, rank_seed
 from .vn_file import VNFileReader, load_vn
@@ -28,5 +30,5 @@ from . import sampling
 from . import quant
 
 __all__ = ["Context", "DeviceArray", "as_device", "DeviceBackend", "B200Backend", "get_backend",
-           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "no_grad", "sampling", "quant", "VerseNexLM", "CometSparkNexLM", "KVCache", "SpecEngine",
+           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "no_grad", "sampling", "quant", "VerseNexLM", "CometSparkNexLM", "KVCache", "SpecEngine", "TreeSpecEngine",
            "ShardedSpecEngine", "Comm", "rank_seed", "VNFileReader", "load_vn"]
