@@ -744,6 +744,33 @@ def run_tree(args):
     barrier_sync(dist, ctx)
     e2e_s = max_over_ranks(dist, time.perf_counter() - t0, local)
     ctx._check(ctx.lib.vn_graph_destroy(ctx.handle, g))
+    # the whole round with tree proposals: the 2-layer draft expands the tree, the target verifies it, the accepted
+    # path is committed in both caches (TreeSpecEngine, greedy rule), replayed from a CUDA graph
+    tree_engine = None
+    if not args.quant:
+        del cache, logits
+        dk = S.draft_kwargs()
+        draft = vn.VerseNexLM(dtype="bf16", device=f"cuda:{local}", **dk)
+        S.load_random(draft, dk, seed=1)
+        rounds = warm + args.steps + 4
+        eng = vn.TreeSpecEngine(target, draft, parents, max_batch=B, max_seq=T0 + rounds * 4 + 64,
+                                max_new_tokens=rounds * 4)
+        eng.prefill(prompt)
+        for _ in range(warm):
+            eng.step()
+        c0 = int(eng.counts().sum())
+        e0, e1 = ctx.event(), ctx.event()
+        e0.record()
+        for _ in range(args.steps):
+            eng.step()
+        e1.record()
+        barrier_sync(dist, ctx)
+        t_ms = max_over_ranks(dist, e0.elapsed_ms(e1), local) / args.steps
+        committed = int(eng.counts().sum()) - c0
+        tree_engine = {"ms_per_round": t_ms, "tokens_per_round_per_request": committed / (args.steps * B),
+                       "accepted_tok_s": committed * world / (t_ms * args.steps * 1e-3),
+                       "what": "TreeSpecEngine round: draft tree expansion (3 levels) + target forward over 17 rows per "
+                               "request + greedy path acceptance + cache commits, B = 8, context 2048"}
     if rank == 0:
         print(json.dumps({
             "metric": "verified tree nodes/s", "value": B * n * world * args.steps / (ms * 1e-3), "unit": "nodes/s",
@@ -760,7 +787,7 @@ def run_tree(args):
             "cpu_baseline": None,
             "e2e": {"value": B * n * world * args.steps / e2e_s, "unit": "nodes/s",
                     "h2d_bytes_per_step": int(h_nodes.nbytes), "d2h_bytes_per_step": int(h_pred.nbytes)},
-            "gpu_launches": launches, "clocks": clk,
+            "gpu_launches": launches, "clocks": clk, "tree_engine": tree_engine,
         }))
     if dist is not None:
         dist.destroy_process_group()

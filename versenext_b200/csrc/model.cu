@@ -15,6 +15,7 @@
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+#include <algorithm>
 #include <set>
 #include <type_traits>
 
@@ -1617,8 +1618,12 @@ int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
     }
     // the same tree as last time is already on the device: nothing to copy and nothing to wait for, so a forward
     // over a fixed tree shape can be captured into a CUDA graph once it has run eagerly
+    // (a tree that is the first T nodes of the stored one has the same depths and masks: also nothing to copy, so a
+    // caller that grows one tree level by level uploads it once)
     const std::vector<int> now(parents_host, parents_host + T);
-    if (now != m->tree_parents) {
+    const bool is_prefix = now.size() <= m->tree_parents.size() &&
+                           std::equal(now.begin(), now.end(), m->tree_parents.begin());
+    if (!is_prefix) {
       VN_CUDA(ctx, cudaMemcpyAsync(m->depth_dev, depth.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
       VN_CUDA(ctx, cudaMemcpyAsync(m->anc_dev, anc.data(), T * 8, cudaMemcpyHostToDevice, ctx->stream));
       VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

@@ -7,8 +7,9 @@ root along the children that carry the target's own arg-max.  The committed toke
 greedy continuation: the stream equals `VerseNexLM.generate(..., temperature=0)` of the target alone, whatever the
 draft and the tree (what the reference's greedy rule guarantees for a chain, speculative.py:280-287).
 
-Everything stays on the device (tokens, arg-max, path, cache commits); the round is issued eagerly, launch by launch
-(the draft's forwards use a different tree per level, and a model keeps one tree's masks at a time).
+Everything stays on the device (tokens, arg-max, path, cache commits), so after the first, eager round the launch
+sequence is replayed from a CUDA graph like the chain engine's (the draft's per-level trees are the first nodes of one
+tree, whose masks a model uploads once).
 
 `parents` describes the tree in breadth-first order: parents[i] = index of node i's parent, -1 for the first level;
 depth never decreases along the list and the children of a node are consecutive.  BASELINE configuration 3's tree is
@@ -28,7 +29,7 @@ from .model import _ptr
 
 class TreeSpecEngine(SpecEngine):
     def __init__(self, target, draft, parents: Sequence[int], max_batch: int, max_seq: int,
-                 max_new_tokens: int = 4096):
+                 max_new_tokens: int = 4096, graph: bool = True):
         parents = [int(p) for p in parents]
         n = len(parents)
         if n < 1 or n > 63:
@@ -50,7 +51,7 @@ class TreeSpecEngine(SpecEngine):
                 raise ValueError("at most 8 children per node")
         D = max(depth)
         super().__init__(target, draft, max_batch, max_seq, k=D, temperature=0.0, top_k=0, seed=0, bonus=True,
-                         max_new_tokens=max_new_tokens, graph=False)
+                         max_new_tokens=max_new_tokens, graph=graph)
         ctx, B, V = self.ctx, self.B, self.V
         self.parents, self.depth, self.kids, self.n_nodes, self.D = parents, depth, kids, n, D
         self.T = n + 1                                   # verify rows per request: last committed token + the nodes
@@ -68,6 +69,8 @@ class TreeSpecEngine(SpecEngine):
         self.parent_rows = ctx.from_numpy(np.array([-1] + [p + 1 for p in parents], np.int32))
         self.q_logits = None                             # the chain engine's proposal buffers are not used
         self.step_tokens = self.draft_tokens = None
+        # per level: the tokens of the nodes known so far (depth <= level), a fixed buffer so that a graph can hold it
+        self.level_tokens = {lv: ctx.zeros((B, sum(1 for d in depth if d <= lv)), np.int64) for lv in range(1, D)}
 
     # -- one round -----------------------------------------------------------------
     def _issue_round(self, draft_part: bool = True):
@@ -82,8 +85,8 @@ class TreeSpecEngine(SpecEngine):
             # deeper levels: forward the tree as far as it is known (nodes of depth <= level, behind the two tokens
             # above), read the rows of the level's nodes that have children
             for level in range(1, D):
-                cnt = sum(1 for d in self.depth if d <= level)
-                toks = ctx.empty((B, cnt), np.int64)
+                toks = self.level_tokens[level]
+                cnt = toks.shape[1]
                 ctx._check(lib.vn_copy_2d(ctx.handle, _ptr(toks), cnt * i64, _ptr(self.node_tokens), n * i64, cnt * i64, B))
                 lg = self.d_logits.reshape(-1)[:B * cnt * V].reshape(B, cnt, V)
                 self.draft.forward_cached(toks, self.d_cache, parents=self.parents[:cnt], out_logits=lg, slot_offset=2)
@@ -113,10 +116,9 @@ class TreeSpecEngine(SpecEngine):
                                         _ptr(self.n_commit), 0))
 
     def step(self):
-        self._check_capacity()
-        self._issue_round()
-        self._len_bound += self.D + 1        # at most depth + 1 entries stay
-        self.rounds_run += 1
+        before = self._len_bound
+        super().step()                       # eager first, then the captured graph
+        self._len_bound = before + self.D + 1   # at most depth + 1 of the appended entries stay
 
     def verify_accept_only(self, graph: bool = False):
         raise NotImplementedError("the tree engine has no separate verify step")
