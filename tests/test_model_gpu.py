@@ -411,6 +411,40 @@ def test_prompt_gemms_on_the_tensor_core_kernel_in_row_segments(monkeypatch):
     m.check()
 
 
+@pytest.mark.parametrize("n_kv", [1, 2, 4])
+def test_prompt_attention_kernel_shares_key_blocks_between_tiles(n_kv, monkeypatch):
+    """Prompts of a RoPE model without ALiBi take the attention kernel whose eight warps hold eight row tiles and
+    share the key blocks: a first chunk on an empty cache (window 24 shorter than the chunk, 20 sinks, 77 positions:
+    no multiple of 16), a second chunk on top of it, ragged committed lengths; against the oracle and against the
+    one-tile-per-CTA kernel; GQA with 4, 2 and 1 query heads per kv head."""
+    cfg = hd64_cfg(n_kv_head=n_kv)
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=50 + n_kv, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    rng = np.random.default_rng(n_kv)
+    B = 3
+    c1, c2 = rng.integers(0, 384, (B, 77)), rng.integers(0, 384, (B, 45))
+    want1, oc = OM.forward(sd, cfg, c1)
+    want2, _ = OM.forward(sd, cfg, c2, cache=oc)
+    got = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("VN_ATTN_PREFILL", flag)
+        cache = m.new_cache(B, 160)
+        a = m.forward_cached(c1, cache).numpy()
+        cache.commit(77, np.full(B, 77, np.int32))
+        b = m.forward_cached(c2, cache).numpy()
+        assert rel_err(a, want1) < 2e-2 and rel_err(b, want2) < 2e-2
+        got[flag] = (a, b)
+        # ragged: sequences keep 77, 40 and 9 positions of the first chunk, then the second chunk again
+        cache.set_lengths(np.array([77, 40, 9], np.int32))
+        r = m.forward_cached(c2, cache).numpy()
+        for i, keep in enumerate((77, 40, 9)):
+            _, oci = OM.forward(sd, cfg, c1[i:i + 1, :keep])
+            wi, _ = OM.forward(sd, cfg, c2[i:i + 1], cache=oci)
+            assert rel_err(r[i:i + 1], wi) < 2e-2
+    assert rel_err(got["1"][0], got["0"][0]) < 1e-2 and rel_err(got["1"][1], got["0"][1]) < 1e-2
+    m.check()
+
+
 def test_persistent_gemm_variant(monkeypatch):
     """Opt-in persistent tile-loop GEMM (one CTA per SM, double-buffered TMEM accumulator), forced onto the small
     shapes of this model: dense store, split-K partial and per-expert SwiGLU tiles give the same logits."""

@@ -12,6 +12,7 @@
 //   O = P V   : thread (g, t) loads dims [8g, 8g+8) of key rows 2t, 2t+1, 2t+8, 2t+9 (16 contiguous bytes each)
 //               and pairs the rows with byte permutes; accumulator column n of tile j is output dim 8n + j.
 #pragma once
+#include <type_traits>
 #include "model_kernels.cuh"
 #include "gemm_mma.cuh"
 
@@ -40,6 +41,115 @@ struct RowInfo {
   float slope;
   unsigned long long anc;
 };
+
+// One block of 16 keys against the warp's 16 query rows: S = Q K^T, scale / bias / mask, online soft-max update,
+// O += P V.  st: the block in shared memory (16 rows of 128 bytes for K, then the same for V at +2048, 16-byte chunks
+// XOR-swizzled with the row).  tq_min >= 0: appended keys that every row of the tile sees (key's new-slot number
+// <= tq_min, chains only) need no mask either.
+template <int MODE>
+__device__ __forceinline__ void attend_block(const AttnArgs& a, const unsigned char* st, int j0, int hi, int len,
+                                             const RowInfo (&row)[2], const unsigned (&qf)[4][4], const int* s_depth,
+                                             int pos_max, int tq_min, int g, int t, float (&o)[8][4], float (&m)[2],
+                                             float (&l)[2]) {
+  // ---- K: rows 8i + g, dims 16t .. 16t+15 (chunks 2t, 2t+1)
+  unsigned kr[2][8];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const unsigned char* rp = st + (8 * i + g) * 128;
+    const uint4 u0 = *reinterpret_cast<const uint4*>(rp + (((2 * t) ^ g) << 4));
+    const uint4 u1 = *reinterpret_cast<const uint4*>(rp + (((2 * t + 1) ^ g) << 4));
+    kr[i][0] = u0.x; kr[i][1] = u0.y; kr[i][2] = u0.z; kr[i][3] = u0.w;
+    kr[i][4] = u1.x; kr[i][5] = u1.y; kr[i][6] = u1.z; kr[i][7] = u1.w;
+  }
+  // ---- V: rows {2t, 2t+1, 2t+8, 2t+9}, dims 8g .. 8g+7 (chunk g)
+  unsigned vr[4][4];
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    const int r = 2 * t + (x & 1) + ((x >> 1) << 3);
+    const uint4 u = *reinterpret_cast<const uint4*>(st + 2048 + r * 128 + ((g ^ (r & 7)) << 4));
+    vr[x][0] = u.x; vr[x][1] = u.y; vr[x][2] = u.z; vr[x][3] = u.w;
+  }
+  // ---- S = Q K^T for two tiles of 8 keys
+  float c[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const unsigned bfrag[2] = {kr[i][2 * s], kr[i][2 * s + 1]};
+      mma_detail::mma_bf16(c[i], qf[s], bfrag);
+    }
+  }
+  // ---- scale, bias, mask.  A block of committed keys that every row of the tile sees needs no mask
+  // (rows beyond R compute on real keys too; their result is never stored)
+  const bool plain = j0 + 16 <= hi && (MODE == 1 || (MODE == 0 && pos_max - j0 < a.window &&
+                                                       (j0 + 16 <= len || (tq_min >= 0 && !a.anc && j0 >= len && j0 + 15 - len <= tq_min))));
+  if (plain) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[i][e] *= a.scale;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = j0 + 8 * i + 2 * t + (e & 1);
+        const RowInfo& r = row[e >> 1];
+        bool vis = r.valid && key < hi;
+        float sc = c[i][e] * a.scale;
+        if (MODE == 0 || MODE == 2) {
+          int kpos = key;
+          if (key >= len) {
+            const int n = key - len;
+            kpos = len + (s_depth ? s_depth[n < 64 ? n : 63] : n);
+            vis = vis && (a.anc ? ((r.anc >> n) & 1ull) != 0 : n <= r.tq) && kpos <= r.pos;
+          }
+          if (MODE == 0) vis = vis && (r.pos - kpos) < a.window;
+          else {
+            sc -= r.slope * (float)(r.pos - kpos);
+            if (a.alibi_window > 0) vis = vis && (r.pos - kpos) < a.alibi_window;
+          }
+        }
+        c[i][e] = vis ? sc : -CUDART_INF_F;
+      }
+  }
+  // ---- online softmax (rows g and g+8; a row lives in the 4 lanes of a quad)
+  float pr[2][4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float mx = fmaxf(fmaxf(c[0][2 * h], c[0][2 * h + 1]), fmaxf(c[1][2 * h], c[1][2 * h + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m[h], mx);
+    float corr = 1.f;
+    if (mn == -CUDART_INF_F) {
+      pr[0][2 * h] = pr[0][2 * h + 1] = pr[1][2 * h] = pr[1][2 * h + 1] = 0.f;
+    } else {
+      corr = __expf(m[h] - mn);
+      pr[0][2 * h] = __expf(c[0][2 * h] - mn);
+      pr[0][2 * h + 1] = __expf(c[0][2 * h + 1] - mn);
+      pr[1][2 * h] = __expf(c[1][2 * h] - mn);
+      pr[1][2 * h + 1] = __expf(c[1][2 * h + 1] - mn);
+    }
+    l[h] = l[h] * corr + pr[0][2 * h] + pr[0][2 * h + 1] + pr[1][2 * h] + pr[1][2 * h + 1];
+    m[h] = mn;
+    if (corr != 1.f) {   // the running maximum moved: rare after the first blocks
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { o[j][2 * h] *= corr; o[j][2 * h + 1] *= corr; }
+    }
+  }
+  // ---- O += P V
+  const unsigned pa[4] = {pack_bf16(pr[0][0], pr[0][1]), pack_bf16(pr[0][2], pr[0][3]),
+                          pack_bf16(pr[1][0], pr[1][1]), pack_bf16(pr[1][2], pr[1][3])};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
+    const unsigned bfrag[2] = {__byte_perm(vr[0][j >> 1], vr[1][j >> 1], sel),
+                               __byte_perm(vr[2][j >> 1], vr[3][j >> 1], sel)};
+    mma_detail::mma_bf16(o[j], pa, bfrag);
+  }
+}
 
 // mode 0: window path (cached keys within the window, appended keys by ancestry), 1: sinks, 2: ALiBi path
 template <int MODE>
@@ -98,103 +208,7 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
     if (it + RING - 1 < n_my) issue(it + RING - 1);
     mma_detail::cp_async_commit();
     const unsigned char* st = ring + (it % RING) * 4096;
-    // ---- K: rows 8i + g, dims 16t .. 16t+15 (chunks 2t, 2t+1)
-    unsigned kr[2][8];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const unsigned char* rp = st + (8 * i + g) * 128;
-      const uint4 u0 = *reinterpret_cast<const uint4*>(rp + (((2 * t) ^ g) << 4));
-      const uint4 u1 = *reinterpret_cast<const uint4*>(rp + (((2 * t + 1) ^ g) << 4));
-      kr[i][0] = u0.x; kr[i][1] = u0.y; kr[i][2] = u0.z; kr[i][3] = u0.w;
-      kr[i][4] = u1.x; kr[i][5] = u1.y; kr[i][6] = u1.z; kr[i][7] = u1.w;
-    }
-    // ---- V: rows {2t, 2t+1, 2t+8, 2t+9}, dims 8g .. 8g+7 (chunk g)
-    unsigned vr[4][4];
-#pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const int r = 2 * t + (x & 1) + ((x >> 1) << 3);
-      const uint4 u = *reinterpret_cast<const uint4*>(st + 2048 + r * 128 + ((g ^ (r & 7)) << 4));
-      vr[x][0] = u.x; vr[x][1] = u.y; vr[x][2] = u.z; vr[x][3] = u.w;
-    }
-    // ---- S = Q K^T for two tiles of 8 keys
-    float c[2][4];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
-#pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        const unsigned bfrag[2] = {kr[i][2 * s], kr[i][2 * s + 1]};
-        mma_detail::mma_bf16(c[i], qf[s], bfrag);
-      }
-    }
-    // ---- scale, bias, mask.  A block of committed keys that every row of the tile sees needs no mask
-    // (rows beyond R compute on real keys too; their result is never stored)
-    const bool plain = j0 + 16 <= hi && (MODE == 1 || (MODE == 0 && j0 + 16 <= len && pos_max - j0 < a.window));
-    if (plain) {
-#pragma unroll
-      for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) c[i][e] *= a.scale;
-    } else {
-#pragma unroll
-      for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = j0 + 8 * i + 2 * t + (e & 1);
-          const RowInfo& r = row[e >> 1];
-          bool vis = r.valid && key < hi;
-          float sc = c[i][e] * a.scale;
-          if (MODE == 0 || MODE == 2) {
-            int kpos = key;
-            if (key >= len) {
-              const int n = key - len;
-              kpos = len + (s_depth ? s_depth[n < 64 ? n : 63] : n);
-              vis = vis && (a.anc ? ((r.anc >> n) & 1ull) != 0 : n <= r.tq) && kpos <= r.pos;
-            }
-            if (MODE == 0) vis = vis && (r.pos - kpos) < a.window;
-            else {
-              sc -= r.slope * (float)(r.pos - kpos);
-              if (a.alibi_window > 0) vis = vis && (r.pos - kpos) < a.alibi_window;
-            }
-          }
-          c[i][e] = vis ? sc : -CUDART_INF_F;
-        }
-    }
-    // ---- online softmax (rows g and g+8; a row lives in the 4 lanes of a quad)
-    float pr[2][4];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float mx = fmaxf(fmaxf(c[0][2 * h], c[0][2 * h + 1]), fmaxf(c[1][2 * h], c[1][2 * h + 1]));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float mn = fmaxf(m[h], mx);
-      float corr = 1.f;
-      if (mn == -CUDART_INF_F) {
-        pr[0][2 * h] = pr[0][2 * h + 1] = pr[1][2 * h] = pr[1][2 * h + 1] = 0.f;
-      } else {
-        corr = __expf(m[h] - mn);
-        pr[0][2 * h] = __expf(c[0][2 * h] - mn);
-        pr[0][2 * h + 1] = __expf(c[0][2 * h + 1] - mn);
-        pr[1][2 * h] = __expf(c[1][2 * h] - mn);
-        pr[1][2 * h + 1] = __expf(c[1][2 * h + 1] - mn);
-      }
-      l[h] = l[h] * corr + pr[0][2 * h] + pr[0][2 * h + 1] + pr[1][2 * h] + pr[1][2 * h + 1];
-      m[h] = mn;
-      if (corr != 1.f) {   // the running maximum moved: rare after the first blocks
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { o[j][2 * h] *= corr; o[j][2 * h + 1] *= corr; }
-      }
-    }
-    // ---- O += P V
-    const unsigned pa[4] = {pack_bf16(pr[0][0], pr[0][1]), pack_bf16(pr[0][2], pr[0][3]),
-                            pack_bf16(pr[1][0], pr[1][1]), pack_bf16(pr[1][2], pr[1][3])};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
-      const unsigned bfrag[2] = {__byte_perm(vr[0][j >> 1], vr[1][j >> 1], sel),
-                                 __byte_perm(vr[2][j >> 1], vr[3][j >> 1], sel)};
-      mma_detail::mma_bf16(o[j], pa, bfrag);
-    }
+    attend_block<MODE>(a, st, j0, hi, len, row, qf, s_depth, pos_max, -1, g, t, o, m, l);
   }
   __syncwarp();   // the ring is reused by the caller
   // row sums live spread over the quad
@@ -468,6 +482,138 @@ __global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_mma_kernel(AttnArgs
   attn_tile(a, blockIdx.x, blockIdx.y, attn_smem_dyn, tr);
 }
 
+// ---- prompt attention: the eight warps of a CTA take eight different 16-row tiles of one (sequence, kv head) --
+// neighbouring positions, all of the kv head's query heads -- and share the key blocks, which the CTA streams once
+// through a ring of three 32-key stages.  Every warp keeps its tile's two soft-max states (window, then sinks) to
+// itself, so nothing is merged across warps and the tile is stored straight from the accumulators.  For chains
+// without ALiBi (prompts of the mate target); everything else takes attn_tile.
+constexpr int PF_STAGES = 3;
+constexpr int PF_STAGE_BYTES = 8192;          // two 16-key blocks: K 2 KB + V 2 KB each
+
+__global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_prefill_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char pf_smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
+  const int n_rep = a.H / a.n_kv;
+  const int pb_per_cta = AW / n_rep;                       // blocks of 16 positions per CTA
+  const int hrep = warp % n_rep, pb = blockIdx.y * pb_per_cta + warp / n_rep;
+  const int len = a.lens[b] + a.slot_offset;
+  const bool tile_on = 16 * pb < a.Tn;
+  const int tq_min = 16 * pb, tq_max = min(a.Tn, 16 * pb + 16) - 1;
+  RowInfo row[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int tq = 16 * pb + g + 8 * h;
+    row[h].valid = tile_on && tq < a.Tn;
+    row[h].tq = row[h].valid ? tq : 0;
+    row[h].pos = len + row[h].tq;
+    row[h].slope = 0.f;
+    row[h].anc = 0ull;
+  }
+  const int pos_min = len + tq_min, pos_max = len + tq_max;
+  const int P0 = blockIdx.y * pb_per_cta * 16, P1 = min(a.Tn, P0 + pb_per_cta * 16);
+  const long long ks = (long long)a.n_kv * 64;
+  const __nv_bfloat16* Kc = reinterpret_cast<const __nv_bfloat16*>(a.kc) + ((long long)b * a.max_seq * a.n_kv + kvh) * 64;
+  const __nv_bfloat16* Vc = reinterpret_cast<const __nv_bfloat16*>(a.vc) + ((long long)b * a.max_seq * a.n_kv + kvh) * 64;
+  const __nv_bfloat16* Ks = reinterpret_cast<const __nv_bfloat16*>(a.sink_k) + (long long)kvh * 64;
+  const __nv_bfloat16* Vs = reinterpret_cast<const __nv_bfloat16*>(a.sink_v) + (long long)kvh * 64;
+
+  // Q fragments of this warp's tile (dims permuted as in attn_tile)
+  unsigned qf[4][4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float* q = a.q + (long long)(b * a.Tn + row[h].tq) * a.ld_q + (kvh * n_rep + hrep) * 64 + 16 * t;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(q + 4 * s));
+      qf[s][h] = row[h].valid ? pack_bf16(v.x, v.y) : 0u;
+      qf[s][2 + h] = row[h].valid ? pack_bf16(v.z, v.w) : 0u;
+    }
+  }
+
+  float fin[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) fin[j][e] = 0.f;
+
+  // one pass over the keys [lo, hi) of Kb / Vb: every thread copies one (key, 16-byte chunk) of K and of V per stage
+  auto pass = [&](auto mode_tag, const __nv_bfloat16* Kb, const __nv_bfloat16* Vb, int lo, int hi, int hi_tile, float gate) {
+    constexpr int MODE = decltype(mode_tag)::value;
+    float o[8][4], m[2], l[2];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+    m[0] = m[1] = -CUDART_INF_F;
+    l[0] = l[1] = 0.f;
+    const int nst = hi > lo ? (hi - lo + 31) >> 5 : 0;
+    auto issue = [&](int s) {
+      unsigned char* st = pf_smem + (s % PF_STAGES) * PF_STAGE_BYTES;
+      const int sb = tid >> 7, r = (tid & 127) >> 3, c = tid & 7;
+      int key = lo + s * 32 + sb * 16 + r;
+      key = key < hi ? key : hi - 1;
+      const int soff = sb * 4096 + r * 128 + ((c ^ (r & 7)) << 4);
+      mma_detail::cp_async16(st + soff, Kb + (long long)key * ks + c * 8, true);
+      mma_detail::cp_async16(st + 2048 + soff, Vb + (long long)key * ks + c * 8, true);
+    };
+#pragma unroll
+    for (int s = 0; s < PF_STAGES - 1; ++s) {
+      if (s < nst) issue(s);
+      mma_detail::cp_async_commit();
+    }
+    for (int s = 0; s < nst; ++s) {
+      mma_detail::cp_async_wait<PF_STAGES - 2>();
+      __syncthreads();                          // stage s has landed for everybody; stage s - 1 is free again
+      if (s + PF_STAGES - 1 < nst) issue(s + PF_STAGES - 1);
+      mma_detail::cp_async_commit();
+      if (!tile_on) continue;
+      const unsigned char* st = pf_smem + (s % PF_STAGES) * PF_STAGE_BYTES;
+#pragma unroll
+      for (int sb = 0; sb < 2; ++sb) {
+        const int j0 = lo + s * 32 + sb * 16;
+        if (j0 >= hi_tile) continue;                                        // behind the tile's last position
+        if (MODE == 0 && pos_min - (j0 + 15) >= a.window) continue;         // before every row's window
+        attend_block<MODE>(a, st + sb * 4096, j0, hi_tile, len, row, qf, nullptr, pos_max, MODE == 0 ? tq_min : -1, g, t,
+                           o, m, l);
+      }
+    }
+    mma_detail::cp_async_wait<0>();
+    __syncthreads();                            // the ring is free for the next pass
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float L = l[h];
+      L += __shfl_xor_sync(0xffffffffu, L, 1);
+      L += __shfl_xor_sync(0xffffffffu, L, 2);
+      if (L > 0.f) {
+        const float inv = gate / L;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { fin[j][2 * h] += o[j][2 * h] * inv; fin[j][2 * h + 1] += o[j][2 * h + 1] * inv; }
+      }
+    }
+  };
+  const int lo_w = max(0, len + P0 - a.window + 1);
+  pass(std::integral_constant<int, 0>(), Kc, Vc, lo_w, len + P1, len + tq_max + 1, a.g_a);
+  pass(std::integral_constant<int, 1>(), Ks, Vs, 0, a.n_sink, a.n_sink, a.g_b);
+
+  // thread (g, t) holds dims 16t .. 16t+15 of rows g and g + 8: dim 16t + 4k + i is fin[(k & 1) * 4 + i][2h + (k >> 1)]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!row[h].valid) continue;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out) + (long long)(b * a.Tn + row[h].tq) * a.H * 64 +
+                         (kvh * n_rep + hrep) * 64 + 16 * t;
+    unsigned w[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int e = 2 * h + (k >> 1), j = (k & 1) * 4;
+      w[2 * k] = pack_bf16(fin[j][e], fin[j + 1][e]);
+      w[2 * k + 1] = pack_bf16(fin[j + 2][e], fin[j + 3][e]);
+    }
+    reinterpret_cast<uint4*>(out)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(out)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
 }  // namespace attn_detail
 
 inline bool attn_mma_supported(const AttnArgs& a, bool bf16) {
@@ -486,5 +632,25 @@ inline int32_t launch_attn_mma(vn_ctx* ctx, const AttnArgs& a, int B) {
   }
   VN_LAUNCH_PDL_LEVEL(ctx, (vn_pdl_mask() & 1) ? 1 : 2, "attn_detail::trisparse_attn_mma_kernel", attn_detail::trisparse_attn_mma_kernel, grid,
                       attn_detail::AW * 32, smem, a);
+  return VN_OK;
+}
+
+// prompts: many new rows per sequence, a chain, no ALiBi path, q already reduced (VN_ATTN_PREFILL=0, read per call,
+// keeps the one-tile-per-CTA kernel)
+inline bool attn_prefill_supported(const AttnArgs& a, bool bf16) {
+  const char* e = getenv("VN_ATTN_PREFILL");
+  if (e && e[0] == '0') return false;
+  const int n_rep = a.n_kv > 0 ? a.H / a.n_kv : 0;
+  return bf16 && a.hd == 64 && !a.anc && !a.depth && !a.use_alibi && !a.partial && a.Tn >= 32 && (a.ld_q % 4) == 0 &&
+         (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 8) && a.H == n_rep * a.n_kv && a.n_sink >= 1;
+}
+
+inline int32_t launch_attn_prefill(vn_ctx* ctx, const AttnArgs& a, int B) {
+  const int n_rep = a.H / a.n_kv;
+  const int pb_per_cta = attn_detail::AW / n_rep;
+  dim3 grid(B * a.n_kv, ceil_div(ceil_div(a.Tn, 16), pb_per_cta));
+  const size_t smem = (size_t)attn_detail::PF_STAGES * attn_detail::PF_STAGE_BYTES;
+  VN_LAUNCH_NAMED(ctx, "trisparse_attn_prefill_kernel", attn_detail::trisparse_attn_prefill_kernel, grid, attn_detail::AW * 32,
+                  smem, a);
   return VN_OK;
 }

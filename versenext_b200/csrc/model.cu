@@ -370,7 +370,9 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
     a.g_b = 1.f / (1.f + expf(-L.gate_logits[1]));
     a.g_c = 1.f / (1.f + expf(-L.gate_logits[2]));
     a.scale = 1.0f / sqrtf((float)hd);
-    if (attn_mma_supported(a, c.bf16 != 0) && !m->force_simt_attn) {
+    if (attn_prefill_supported(a, c.bf16 != 0) && !m->force_simt_attn) {
+      TRY(launch_attn_prefill(ctx, a, B));
+    } else if (attn_mma_supported(a, c.bf16 != 0) && !m->force_simt_attn) {
       TRY(launch_attn_mma(ctx, a, B));
     } else {
       dim3 grid(ceil_div(H, 8), M);
