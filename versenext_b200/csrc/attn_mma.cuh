@@ -44,9 +44,9 @@ struct RowInfo {
 
 // One block of 16 keys against the warp's 16 query rows: S = Q K^T, scale / bias / mask, online soft-max update,
 // O += P V.  st: the block in shared memory (16 rows of 128 bytes for K, then the same for V at +2048, 16-byte chunks
-// XOR-swizzled with the row).  tq_min >= 0: appended keys that every row of the tile sees (key's new-slot number
-// <= tq_min, chains only) need no mask either.
-template <int MODE>
+// XOR-swizzled with the row).  CHAIN_NEW (chains only): appended keys that every row of the tile sees (the key's
+// new-slot number <= tq_min) need no mask either.
+template <int MODE, bool CHAIN_NEW = false>
 __device__ __forceinline__ void attend_block(const AttnArgs& a, const unsigned char* st, int j0, int hi, int len,
                                              const RowInfo (&row)[2], const unsigned (&qf)[4][4], const int* s_depth,
                                              int pos_max, int tq_min, int g, int t, float (&o)[8][4], float (&m)[2],
@@ -83,7 +83,7 @@ __device__ __forceinline__ void attend_block(const AttnArgs& a, const unsigned c
   // ---- scale, bias, mask.  A block of committed keys that every row of the tile sees needs no mask
   // (rows beyond R compute on real keys too; their result is never stored)
   const bool plain = j0 + 16 <= hi && (MODE == 1 || (MODE == 0 && pos_max - j0 < a.window &&
-                                                       (j0 + 16 <= len || (tq_min >= 0 && !a.anc && j0 >= len && j0 + 15 - len <= tq_min))));
+                                                       (j0 + 16 <= len || (CHAIN_NEW && j0 >= len && j0 + 15 - len <= tq_min))));
   if (plain) {
 #pragma unroll
     for (int i = 0; i < 2; ++i)
@@ -208,7 +208,7 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
     if (it + RING - 1 < n_my) issue(it + RING - 1);
     mma_detail::cp_async_commit();
     const unsigned char* st = ring + (it % RING) * 4096;
-    attend_block<MODE>(a, st, j0, hi, len, row, qf, s_depth, pos_max, -1, g, t, o, m, l);
+    attend_block<MODE, false>(a, st, j0, hi, len, row, qf, s_depth, pos_max, 0, g, t, o, m, l);
   }
   __syncwarp();   // the ring is reused by the caller
   // row sums live spread over the quad
@@ -574,8 +574,7 @@ __global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_prefill_kernel(Attn
         const int j0 = lo + s * 32 + sb * 16;
         if (j0 >= hi_tile) continue;                                        // behind the tile's last position
         if (MODE == 0 && pos_min - (j0 + 15) >= a.window) continue;         // before every row's window
-        attend_block<MODE>(a, st + sb * 4096, j0, hi_tile, len, row, qf, nullptr, pos_max, MODE == 0 ? tq_min : -1, g, t,
-                           o, m, l);
+        attend_block<MODE, MODE == 0>(a, st + sb * 4096, j0, hi_tile, len, row, qf, nullptr, pos_max, tq_min, g, t, o, m, l);
       }
     }
     mma_detail::cp_async_wait<0>();
