@@ -700,6 +700,29 @@ def test_tree_engine_commits_the_targets_greedy_stream(golden):
         vn.TreeSpecEngine(t2, d2, [-1, -1, 0, 1, 0], max_batch=1, max_seq=64)
 
 
+def test_tree_engine_round_with_more_than_256_rows_in_a_graph():
+    """16 requests x 17 tree rows = 272 rows per target forward: beyond the 256-row decode path, so the captured round
+    holds the many-row GEMM route (row segments filled by a kernel, nothing copied from the host while capturing).
+    The replayed graph commits exactly what the eager rounds commit."""
+    import versenext_b200 as vn
+    cfg = hd64_cfg()
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=61, gate_std=1.0).items()}
+    dcfg = hd64_cfg(n_layer=1, layer_pattern=["trisparse"])
+    dsd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(dcfg, seed=62, gate_std=1.0).items()}
+    dsd["tok_emb.weight"] = sd["tok_emb.weight"]
+    t, d = build(cfg, sd, "bf16"), build(dcfg, dsd, "bf16")
+    prompts = np.random.default_rng(9).integers(0, 384, (16, 23))
+    outs = []
+    for graph in (True, False):
+        eng = vn.TreeSpecEngine(t, d, CFG3_TREE, max_batch=16, max_seq=160, max_new_tokens=48, graph=graph)
+        toks, st = eng.generate(prompts, 24)
+        outs.append(toks[:, :23 + 24])
+        assert st["rounds"] >= 6
+    np.testing.assert_array_equal(outs[0], outs[1])
+    t.check()
+    d.check()
+
+
 def test_continuous_batching_serves_ragged_requests():
     """Seven requests of different prompt lengths and token budgets on three slots: a request leaves its slot when it
     is done and the next one is prefilled into it; every request's tokens equal its own greedy generation."""

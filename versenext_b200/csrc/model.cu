@@ -144,7 +144,7 @@ struct vn_model {
   int* sub_seg = nullptr;        // [3][sub_cap] offsets, counts and experts of the experts' 256-row pieces (prompt forwards)
   int sub_cap = 0;
   int* row_seg = nullptr;        // [2][row_seg_n] offsets and counts of the 256-row segments a prompt's GEMMs use
-  int row_seg_cap = 0, row_seg_n = 0, row_seg_rows = 0;
+  int row_seg_cap = 0;
   unsigned* stack_bar = nullptr; // two device words: arrivals and generation of the fused layer stack's grid barrier
   bool recurrent = false;        // vn_model_set_recurrent: ALiBi path as in the reference's one-token recurrent step
   bool fused_stack = false;      // vn_model_set_fused_stack / VN_DRAFT_STACK=1: the layer stack as one cooperative kernel
@@ -262,6 +262,15 @@ int32_t ensure_rows(vn_model* m, int M) {
   TRY(dev_alloc(ctx, &m->attn, R * D * e));
   TRY(dev_alloc(ctx, &m->act, R * S * hid * e));
   TRY(dev_alloc(ctx, (void**)&m->rows_dev, R * 4));
+  // segment tables of a prompt's GEMMs (rows in blocks of 256; the experts' pieces), sized for the row capacity so
+  // that a forward never allocates them: filled by kernels on the stream
+  if (m->row_seg) cudaFree(m->row_seg);
+  if (m->sub_seg) cudaFree(m->sub_seg);
+  m->row_seg = m->sub_seg = nullptr;
+  m->row_seg_cap = (int)(R / 256 + 2);
+  TRY(dev_alloc(ctx, (void**)&m->row_seg, (size_t)2 * m->row_seg_cap * sizeof(int)));
+  m->sub_cap = (int)(c.P * c.E + R * S / 256 + 2);
+  TRY(dev_alloc(ctx, (void**)&m->sub_seg, (size_t)3 * m->sub_cap * sizeof(int)));
   if (has_mod) {
     TRY(dev_alloc(ctx, (void**)&m->y, R * S * D * 4));
     if (c.bf16) TRY(dev_alloc(ctx, &m->hs, R * S * D * e));
@@ -301,27 +310,16 @@ int32_t linear(vn_model* m, GemmArgs g) {
         g.K % 8 == 0 && g.ldw_k == 1 && tc_detail::encode_fn() != nullptr &&
         (g.epi == EPI_STORE || g.epi == EPI_ADD || g.epi == EPI_SWIGLU)) {
       const int nseg = ceil_div(g.M, 256);
-      if (m->row_seg_rows != g.M) {
-        if (nseg > m->row_seg_cap) {
-          VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-          if (m->row_seg) VN_CUDA(ctx, cudaFree(m->row_seg));
-          m->row_seg = nullptr; m->row_seg_cap = 0;
-          TRY(dev_alloc(ctx, (void**)&m->row_seg, (size_t)2 * nseg * sizeof(int)));
-          m->row_seg_cap = nseg;
-        }
-        std::vector<int> host(2 * (size_t)nseg);
-        for (int i = 0; i < nseg; ++i) { host[i] = 256 * i; host[nseg + i] = std::min(256, g.M - 256 * i); }
-        VN_CUDA(ctx, cudaMemcpyAsync(m->row_seg, host.data(), host.size() * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
-        VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // host vector goes out of scope
-        m->row_seg_rows = g.M; m->row_seg_n = nseg;
-      }
+      if (nseg <= m->row_seg_cap) {
+      VN_LAUNCH(ctx, row_segments_kernel, ceil_div(nseg, 128), 128, 0, m->row_seg, m->row_seg + m->row_seg_cap, nseg, g.M);
       TRY(ensure_partial(m, 1024));                               // the error word
       GemmArgs g2 = g;
-      g2.M = 256; g2.seg_off = m->row_seg; g2.seg_cnt = m->row_seg + m->row_seg_n; g2.nseg = nseg; g2.w_stride = 0;
+      g2.M = 256; g2.seg_off = m->row_seg; g2.seg_cnt = m->row_seg + m->row_seg_cap; g2.nseg = nseg; g2.w_stride = 0;
       if (gemm_tc_supported(g2)) {
         TcPlan plan;
         plan.error_flag = m->tc_error;
         return launch_gemm_tc(ctx, g2, g.M, plan);
+      }
       }
     }
     if (gemm_mma_supported(g)) return launch_gemm_mma(ctx, g);
@@ -413,16 +411,9 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
       const char* pe = getenv("VN_PREFILL_TC");
       const int n_sub = ne + ceil_div(M * S, 256);
       const bool tc_experts = std::is_same<T, __nv_bfloat16>::value && m->use_tc && !m->qmode && !(pe && pe[0] == '0') &&
-                              (long long)M * S > 256 && m->hs && D % 8 == 0 && eh % 8 == 0 && n_sub <= 65535 &&
+                              (long long)M * S > 256 && m->hs && D % 8 == 0 && eh % 8 == 0 && n_sub <= 65535 && n_sub <= m->sub_cap &&
                               tc_detail::encode_fn() != nullptr;
       if (tc_experts) {
-        if (n_sub > m->sub_cap) {
-          VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-          if (m->sub_seg) VN_CUDA(ctx, cudaFree(m->sub_seg));
-          m->sub_seg = nullptr; m->sub_cap = 0;
-          TRY(dev_alloc(ctx, (void**)&m->sub_seg, (size_t)3 * n_sub * sizeof(int)));
-          m->sub_cap = n_sub;
-        }
         int* sub_off = m->sub_seg; int* sub_cnt = m->sub_seg + m->sub_cap; int* sub_w = m->sub_seg + 2 * m->sub_cap;
         VN_LAUNCH(ctx, mod_subseg_kernel, 1, 32, 0, (const int*)m->expert_count, (const int*)m->expert_off, ne, sub_off,
                   sub_cnt, sub_w, n_sub);

@@ -460,6 +460,12 @@ __global__ void mod_offsets_kernel(const int* __restrict__ count, int* __restric
   }
 }
 
+// rows 0 .. M-1 in blocks of 256: off[i] = 256 i, cnt[i] = rows in block i
+__global__ void row_segments_kernel(int* __restrict__ off, int* __restrict__ cnt, int nseg, int M) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < nseg) { off[i] = 256 * i; cnt[i] = min(256, M - 256 * i); }
+}
+
 // The experts' row segments cut into pieces of at most 256 rows (what one CTA of the tensor-core GEMM takes as its
 // token dimension): sub_off / sub_cnt / sub_w [n_sub_max] = first row, rows and expert of piece i; unused pieces get 0 rows.
 __global__ void mod_subseg_kernel(const int* __restrict__ count, const int* __restrict__ offset, int n_expert,
