@@ -57,26 +57,31 @@ struct Args {
   long long* trace;                 // optional [64] nanosecond stamps of CTA 0 at the phase boundaries, or null
 };
 
+// Sense-reversing grid barrier on two words (arrivals, generation).  Thread 0 of every CTA arrives with an
+// acquire-release atomic at GPU scope -- the CTA's earlier writes are ordered before it through the block barrier in
+// front -- the last one resets the count and bumps the generation with a release, the others poll the generation with
+// acquire loads.  No full memory fences.  The wait is bounded.
 __device__ __forceinline__ void grid_barrier(const Args& a, int n_cta) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    volatile unsigned* gen = a.bar + 1;
-    const unsigned my_gen = *gen;
-    __threadfence();                                  // this CTA's writes before its arrival
-    if (atomicAdd(a.bar, 1u) == (unsigned)n_cta - 1u) {
-      a.bar[0] = 0u;
-      __threadfence();
-      atomicAdd(a.bar + 1, 1u);                       // releases everybody
+    unsigned my_gen, prev;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(my_gen) : "l"(a.bar + 1) : "memory");
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(a.bar) : "memory");
+    if (prev == (unsigned)n_cta - 1u) {
+      asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(a.bar), "r"(0u) : "memory");
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" :: "l"(a.bar + 1) : "memory");
     } else {
       const long long t0 = clock64();
-      while (*gen == my_gen) {
-        if ((unsigned long long)(clock64() - t0) > tc_detail::g_wait_limit_cycles) {
+      const unsigned long long limit = tc_detail::g_wait_limit_cycles;
+      unsigned g = my_gen;
+      while (g == my_gen) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(g) : "l"(a.bar + 1) : "memory");
+        if (g == my_gen && (unsigned long long)(clock64() - t0) > limit) {
           if (a.error_flag) atomicExch(a.error_flag, 1);
           break;
         }
       }
     }
-    __threadfence();
   }
   __syncthreads();
 }
