@@ -17,6 +17,7 @@
 // Split-K: blockIdx.y selects a K range; partial tiles go to a workspace [split][rows][N] and are reduced by
 // the caller's finalize kernel (deterministic order).
 #pragma once
+#include <math_constants.h>
 #include <cuda.h>
 #include <stdlib.h>
 #include "gemm.cuh"
@@ -227,14 +228,33 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
       // shared memory as (row, value, column); filter_flush below hands them to the rows' lists in global memory
       // with all of the CTA's atomics in flight together -- an atomic per hit inside this loop would stall the warp
       // for an L2 round trip every time.
+      // The rows' bounds first, all 32 loads in flight together: inside the compare loop below a load could not be
+      // moved across the shared-memory atomic of a hit, and the loop ran at one exposed load latency per row
+      // (5.6 us per 160-row tile with no hit at all; the plain store epilogue takes 2.4 us).
       const float* tau = g.cand.tau + row0 + m0;
+      float tv[32];
+      if (mrem >= 32 && (reinterpret_cast<uintptr_t>(tau) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 t4 = __ldg(reinterpret_cast<const float4*>(tau) + i);
+          tv[4 * i] = t4.x; tv[4 * i + 1] = t4.y; tv[4 * i + 2] = t4.z; tv[4 * i + 3] = t4.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) tv[i] = i < mrem ? __ldg(tau + i) : CUDART_INF_F;
+      }
+      // which of the 32 rows hit: a bit mask without branches; three threads in four have no hit in a chunk and
+      // leave here
+      unsigned hit = 0u;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) hit |= (__uint_as_float(r[i]) >= tv[i] ? 1u : 0u) << i;
       int* s_n = reinterpret_cast<int*>(base);
       FilterHit* s_hit = reinterpret_cast<FilterHit*>(base + 16);
-      if (n < g.N) {
+      if (n < g.N && hit) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float v = __uint_as_float(r[i]);
-          if (i < mrem && v >= __ldg(tau + i)) {
+          if ((hit >> i) & 1u) {
             const int e = atomicAdd(s_n, 1);
             if (e < FILTER_STAGE) {
               s_hit[e].row = row0 + m0 + i; s_hit[e].val = v; s_hit[e].tok = n;
