@@ -248,21 +248,55 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcArgs& g, const unsigne
       unsigned hit = 0u;
 #pragma unroll
       for (int i = 0; i < 32; ++i) hit |= (__uint_as_float(r[i]) >= tv[i] ? 1u : 0u) << i;
+      // Parking: one shared-memory atomic per warp and chunk reserves room for all of the warp's hits (a prefix
+      // sum over the lanes' hit counts gives each lane its place); a lane then stores its hits one after the other.
+      // An atomic per hit inside the diverged 32-way loop cost 4.5 us per tile.
       int* s_n = reinterpret_cast<int*>(base);
       FilterHit* s_hit = reinterpret_cast<FilterHit*>(base + 16);
-      if (n < g.N && hit) {
+      const unsigned mine = n < g.N ? hit : 0u;
+      const int cntl = __popc(mine);
+      int incl = cntl;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const int total = __shfl_sync(0xffffffffu, incl, 31);
+      if (total) {                               // uniform over the warp
+        int first = 0;
+        if (lane == 31) first = atomicAdd(s_n, total);
+        first = __shfl_sync(0xffffffffu, first, 31);
+        int pos = first + incl - cntl;
+        // Straight-line, predicated stores: the 32 copies of this body must stay tiny.  With the overflow path
+        // (64-bit addresses, a global atomic) inside, the rarely taken copies were fetched cold every time they ran:
+        // 3 us per tile.
+        const int pos0 = pos;
+        bool over = false;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(r[i]);
-          if ((hit >> i) & 1u) {
-            const int e = atomicAdd(s_n, 1);
-            if (e < FILTER_STAGE) {
-              s_hit[e].row = row0 + m0 + i; s_hit[e].val = v; s_hit[e].tok = n;
-            } else {                            // staging full (heavy ties): straight to the list
+          const bool bit = (mine >> i) & 1u;
+          const bool ok = bit && pos < FILTER_STAGE;
+          if (ok) {
+            FilterHit* dst = s_hit + pos;
+            dst->row = row0 + m0 + i; dst->val = __uint_as_float(r[i]); dst->tok = n;
+          }
+          over |= bit && !ok;
+          pos += bit ? 1 : 0;
+        }
+        if (over) {                              // staging full (heavy ties): the rest goes straight to the lists
+          pos = pos0;
+#pragma unroll 1
+          for (int i = 0; i < 32; ++i) {
+            if (!((mine >> i) & 1u)) continue;
+            if (pos >= FILTER_STAGE) {
+              float v = 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v = j == i ? __uint_as_float(r[j]) : v;
               const long long rowg = row0 + m0 + i;
               const int slot = atomicAdd(g.cand.count + rowg * g.cand.count_stride, 1);
               if (slot < g.cand.cap) { g.cand.val[rowg * g.cand.cap + slot] = v; g.cand.tok[rowg * g.cand.cap + slot] = n; }
             }
+            ++pos;
           }
         }
       }
