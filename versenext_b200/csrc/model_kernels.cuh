@@ -569,6 +569,13 @@ __global__ void __launch_bounds__(256) splitk_add_norm_kernel(const float* __res
                                                               const float* __restrict__ norm_w, T* __restrict__ y,
                                                               float* __restrict__ y32, int D, float eps) {
   pdl_trigger();
+  // the norm weights never change: fetched before the wait on the preceding kernel, used after the row sum
+  float4 wn[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int d = (threadIdx.x + i * 256) * 4;
+    wn[i] = (norm_w && d < D) ? __ldg(reinterpret_cast<const float4*>(norm_w + d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   pdl_wait();
   __shared__ float sm[8];
   const long long row = blockIdx.x;
@@ -605,9 +612,13 @@ __global__ void __launch_bounds__(256) splitk_add_norm_kernel(const float* __res
   for (int i = 0; i < 2; ++i) {
     const int d = (threadIdx.x + i * 256) * 4;
     if (d < D) {
-      const float4 w = *reinterpret_cast<const float4*>(norm_w + d);
+      const float4 w = wn[i];
       const float o0 = v[i].x / r * w.x, o1 = v[i].y / r * w.y, o2 = v[i].z / r * w.z, o3 = v[i].w / r * w.w;
-      if (y) { y[row * D + d] = from_f<T>(o0); y[row * D + d + 1] = from_f<T>(o1); y[row * D + d + 2] = from_f<T>(o2); y[row * D + d + 3] = from_f<T>(o3); }
+      if (y) {
+        __align__(16) T o4[4] = {from_f<T>(o0), from_f<T>(o1), from_f<T>(o2), from_f<T>(o3)};
+        if (sizeof(T) == 2) *reinterpret_cast<uint2*>(y + row * D + d) = *reinterpret_cast<const uint2*>(o4);
+        else *reinterpret_cast<float4*>(y + row * D + d) = *reinterpret_cast<const float4*>(o4);
+      }
       if (y32) *reinterpret_cast<float4*>(y32 + row * D + d) = make_float4(o0, o1, o2, o3);
     }
   }
