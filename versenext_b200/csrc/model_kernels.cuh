@@ -729,6 +729,13 @@ __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restric
                                                                 const float* __restrict__ norm_w, T* __restrict__ h,
                                                                 float eps) {
   pdl_trigger();
+  // the norm weights never change: fetched before the wait on the preceding kernel, used after the row sum
+  float4 wn[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int d = (threadIdx.x + i * 256) * 4;
+    wn[i] = (norm_w && d < D) ? __ldg(reinterpret_cast<const float4*>(norm_w + d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   pdl_wait();
   // the expert GEMMs were the last readers of the per-expert counts: leave them at zero for the next router
   if (blockIdx.x == 0)
@@ -753,7 +760,38 @@ __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restric
     const int d = (threadIdx.x + i * 256) * 4;
     v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (d >= D) continue;
+    float4* xp = reinterpret_cast<float4*>(x + (long long)row * D + d);
+    float4 xv = *xp;                                   // independent of the expert outputs: on its way early
     float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (S <= 8 && splits <= 2) {
+      // the usual shape (4 parts x top-2, one or two K slices): every slot's slices are requested before the first
+      // is used -- one round trip to L2 instead of one per slot; the sums keep the order of the general loop below
+      float4 t[8][2];
+#pragma unroll
+      for (int sl = 0; sl < 8; ++sl)
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          t[sl][q] = (sl < S && q < splits) ? *reinterpret_cast<const float4*>(ypart + (long long)q * pstride + s_at[sl] + d)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < P; ++p) {
+        float4 comb = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < top_k; ++j) {
+          const int sl = p * top_k + j;
+          float4 yv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            float4 tq = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int z = 0; z < 8; ++z) tq = z == sl ? t[z][q] : tq;
+            if (q < splits) { yv.x += tq.x; yv.y += tq.y; yv.z += tq.z; yv.w += tq.w; }
+          }
+          const float w = s_w[sl];
+          comb.x += yv.x * w; comb.y += yv.y * w; comb.z += yv.z * w; comb.w += yv.w * w;
+        }
+        const float pw = P <= 16 ? s_pw[p] : part_w[(long long)row * P + p];
+        out.x += comb.x * pw; out.y += comb.y * pw; out.z += comb.z * pw; out.w += comb.w * pw;
+      }
+    } else
     for (int p = 0; p < P; ++p) {
       float4 comb = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int j = 0; j < top_k; ++j) {
@@ -770,8 +808,6 @@ __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restric
       const float pw = P <= 16 ? s_pw[p] : part_w[(long long)row * P + p];
       out.x += comb.x * pw; out.y += comb.y * pw; out.z += comb.z * pw; out.w += comb.w * pw;
     }
-    float4* xp = reinterpret_cast<float4*>(x + (long long)row * D + d);
-    float4 xv = *xp;
     xv.x += out.x; xv.y += out.y; xv.z += out.z; xv.w += out.w;
     *xp = xv;
     v[i] = xv;
@@ -790,10 +826,12 @@ __global__ void __launch_bounds__(256) mod_combine_split_kernel(float* __restric
   for (int i = 0; i < 2; ++i) {
     const int d = (threadIdx.x + i * 256) * 4;
     if (d < D) {
-      const float4 w = *reinterpret_cast<const float4*>(norm_w + d);
+      const float4 w = wn[i];
+      __align__(16) T o4[4] = {from_f<T>(v[i].x / r * w.x), from_f<T>(v[i].y / r * w.y), from_f<T>(v[i].z / r * w.z),
+                                 from_f<T>(v[i].w / r * w.w)};
       T* hp = h + (long long)row * D + d;
-      hp[0] = from_f<T>(v[i].x / r * w.x); hp[1] = from_f<T>(v[i].y / r * w.y);
-      hp[2] = from_f<T>(v[i].z / r * w.z); hp[3] = from_f<T>(v[i].w / r * w.w);
+      if (sizeof(T) == 2) *reinterpret_cast<uint2*>(hp) = *reinterpret_cast<const uint2*>(o4);
+      else *reinterpret_cast<float4*>(hp) = *reinterpret_cast<const float4*>(o4);
     }
   }
 }
