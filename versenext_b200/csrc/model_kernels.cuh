@@ -684,23 +684,49 @@ __global__ void mod_dispatch_kernel(const T* __restrict__ src, const int* __rest
   pdl_wait();
   __shared__ int s_pos;
   const int i = blockIdx.x;
-  if (threadIdx.x == 0) {
+  // the token's row is on its way while warp 0 finds the destination (up to two 16-byte pieces per thread)
+  const uint4* a = reinterpret_cast<const uint4*>(src + (long long)(i / S) * D);
+  const int n16 = D * (int)sizeof(T) / 16;
+  uint4 piece[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int j = threadIdx.x + u * blockDim.x;
+    piece[u] = j < n16 ? a[j] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (threadIdx.x < 32) {
+    // exclusive prefix of the expert counts by the lanes of one warp: all counts are requested at once (a loop of
+    // one thread waited for every count before it could ask for the next)
+    const int lane = threadIdx.x;
     const int e = slot_expert[i];
-    int acc = 0, mine = 0;
-    for (int x = 0; x < n_expert; ++x) {
-      if (x == e) mine = acc;
-      if (i == 0) offset[x] = acc;          // the GEMMs read the segment starts from here
-      acc += count[x];
+    int base = 0, mine = 0;
+    for (int x0 = 0; x0 < n_expert; x0 += 32) {
+      const int x = x0 + lane;
+      const int c = x < n_expert ? count[x] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const int excl = base + incl - c;
+      if (i == 0 && x < n_expert) offset[x] = excl;       // the GEMMs read the segment starts from here
+      if (e >= x0 && e < x0 + 32) mine = __shfl_sync(0xffffffffu, excl, e - x0);
+      base += __shfl_sync(0xffffffffu, incl, 31);
     }
-    const int pos = mine + atomicAdd(&cursor[e], 1);
-    slot_pos[i] = pos;
-    s_pos = pos;
+    if (lane == 0) {
+      const int pos = mine + atomicAdd(&cursor[e], 1);
+      slot_pos[i] = pos;
+      s_pos = pos;
+    }
   }
   __syncthreads();
-  const uint4* a = reinterpret_cast<const uint4*>(src + (long long)(i / S) * D);
   uint4* b = reinterpret_cast<uint4*>(dst + (long long)s_pos * D);
-  const int n16 = D * (int)sizeof(T) / 16;
-  for (int j = threadIdx.x; j < n16; j += blockDim.x) b[j] = a[j];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int j = threadIdx.x + u * blockDim.x;
+    if (j < n16) b[j] = piece[u];
+  }
+  for (int j = threadIdx.x + 2 * blockDim.x; j < n16; j += blockDim.x) b[j] = a[j];
 }
 
 template <typename T>
