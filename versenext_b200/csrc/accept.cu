@@ -926,9 +926,24 @@ __device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& 
     staged = nmax <= DEC_ENT;
   }
   if (staged) {
-    for (int idx = lane; idx < rows_per_seq * DEC_ENT; idx += 32) {
-      const int r = idx / DEC_ENT, i = idx % DEC_ENT;
-      if (i < s_n[r]) { const TopkRow* rp = rowp(r); s_tok[r][i] = rp->tok[i]; s_val[r][i] = rp->val[i]; }
+    // eight entries per lane are requested before the first is stored: a plain copy loop waits for every load
+    // before it can issue the next (some forty round trips to L2 for nine rows)
+    const int total = rows_per_seq * DEC_ENT;
+    for (int idx0 = 0; idx0 < total; idx0 += 32 * 8) {
+      int tk[8]; float vl[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = idx0 + u * 32 + lane;
+        const int r = idx / DEC_ENT, i = idx % DEC_ENT;
+        tk[u] = 0; vl[u] = 0.f;
+        if (idx < total && i < s_n[r]) { const TopkRow* rp = rowp(r); tk[u] = rp->tok[i]; vl[u] = rp->val[i]; }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = idx0 + u * 32 + lane;
+        const int r = idx / DEC_ENT, i = idx % DEC_ENT;
+        if (idx < total && i < s_n[r]) { s_tok[r][i] = tk[u]; s_val[r][i] = vl[u]; }
+      }
     }
     __syncwarp();
   }
@@ -945,8 +960,14 @@ __device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& 
   __syncwarp();
   int n = 0;
   int sample_row = -1, q_row = -1, removed = -1;
+  // the k proposals and their uniforms in one round trip (lane n holds position n), not one per loop trip
+  int x_lane = 0; float u_lane = 0.f;
+  if (lane < k) {
+    x_lane = (int)draft[(long long)b * k + lane];
+    u_lane = u_acc ? u_acc[(long long)b * k + lane] : philox_uniform(seed, offset, b, pos_base + lane, 0);
+  }
   for (; n < k; ++n) {
-    const int x = (int)draft[(long long)b * k + n];
+    const int x = __shfl_sync(0xffffffffu, x_lane, n);
     float mp; double sp;
     list_stats(view(n), lane, mp, sp);
     const float vp = list_value(view(n), lane, x);
@@ -958,7 +979,7 @@ __device__ __noinline__ void topk_decide_seq(int b, int lane, const DecideArgs& 
       const float vq = list_value(view(np + n), lane, x);
       q = vq == -CUDART_INF_F ? 0.0 : (double)expf(vq - mq) / sq;
     }
-    const float u = u_acc ? u_acc[(long long)b * k + n] : philox_uniform(seed, offset, b, pos_base + n, 0);
+    const float u = __shfl_sync(0xffffffffu, u_lane, n);
     if ((double)u * q < p) { if (lane == 0) tok[n] = x; continue; }
     sample_row = n;
     if (nq) q_row = np + n; else removed = x;
