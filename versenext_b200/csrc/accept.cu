@@ -645,8 +645,7 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, l
   auto gather = [&](uint32_t lo, bool fast, float xlo) {
     int i = tid;
     if (fast) {
-      for (; i < V4; i += nt) {
-        const float4 a = __ldg(row4 + i);
+      auto take = [&](const float4& a, int at) {
         if (fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)) >= xlo) {
           const float xs[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
@@ -654,10 +653,18 @@ accept_topk_kernel(RowSet rs, int top_k, float temp, int chunks, TopkRow* out, l
             if (xs[e] >= xlo) {
               const uint32_t key = order_key(scale ? __fdiv_rn(xs[e], temp) : xs[e]);
               const int slot = atomicAdd(&s_ncand, 1);
-              if (slot < CAND_MAX) { c_key[slot] = key; c_tok[slot] = base0 + 4 * i + e; }
+              if (slot < CAND_MAX) { c_key[slot] = key; c_tok[slot] = base0 + 4 * at + e; }
             }
         }
+      };
+      // four loads in flight per thread, as in the bound pass: behind the atomic of a candidate the next load of a
+      // one-at-a-time loop could not be issued early
+      for (; i + 3 * nt < V4; i += 4 * nt) {
+        const float4 a0 = __ldg(row4 + i), a1 = __ldg(row4 + i + nt), a2 = __ldg(row4 + i + 2 * nt),
+                     a3 = __ldg(row4 + i + 3 * nt);
+        take(a0, i); take(a1, i + nt); take(a2, i + 2 * nt); take(a3, i + 3 * nt);
       }
+      for (; i < V4; i += nt) take(__ldg(row4 + i), i);
     }
     for (; i < V4; i += nt) {
       const float4 a = __ldg(row4 + i);
@@ -1103,7 +1110,14 @@ k1_bound_kernel(const float* __restrict__ boot, int nb, int top_k, float temp, f
   const float* src = boot + (long long)row * nb;
   float mx = -CUDART_INF_F;
   int mine = 0;
-  for (int i = tid; i < nb; i += nt) { mx = fmaxf(mx, src[i]); ++mine; }
+  for (int i0 = tid; i0 < nb; i0 += 8 * nt) {      // eight loads in flight per thread
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) x[u] = i0 + u * nt < nb ? src[i0 + u * nt] : -CUDART_INF_F;
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (i0 + u * nt < nb) { mx = fmaxf(mx, x[u]); ++mine; }
+  }
   s_max[tid] = mine ? order_key(mx) : 0u;           // 0 sorts below every real key
   if (tid == 0) s_kth = 0u;
   __syncthreads();
@@ -1168,11 +1182,19 @@ k1_finish_kernel(const float* __restrict__ cand_val, const int* __restrict__ can
   const float* cv = cand_val + (long long)row * cap;
   const int* ct = cand_tok + (long long)row * cap;
   uint32_t gmax = 0u;
-  for (int i = tid; i < n; i += nt) {
-    const float x = cv[i];
-    const uint32_t key = order_key(scale ? __fdiv_rn(x, temp) : x);
-    s_key[i] = key;
-    gmax = key > gmax ? key : gmax;
+  for (int i0 = tid; i0 < n; i0 += 8 * nt) {      // eight candidates per thread requested before the first is used
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) x[u] = i0 + u * nt < n ? cv[i0 + u * nt] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * nt;
+      if (i < n) {
+        const uint32_t key = order_key(scale ? __fdiv_rn(x[u], temp) : x[u]);
+        s_key[i] = key;
+        gmax = key > gmax ? key : gmax;
+      }
+    }
   }
   s_gmax[tid] = gmax;                        // 0 (below every real key) for a thread without candidates
   if (tid == 0) { s_lo = 0u; s_kth = 0u; s_nc = 0; s_keep = 0; }
