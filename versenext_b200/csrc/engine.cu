@@ -14,12 +14,18 @@ __global__ void spec_gather_kernel(const long long* __restrict__ step_tokens, co
   pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
-  verify[(long long)b * n_verify] = pair[b * 2 + 1];
-  for (int i = 0; i < k; ++i) {
-    const long long t = step_tokens[(long long)i * B + b];
-    draft[(long long)b * k + i] = t;
-    if (i + 1 < n_verify) verify[(long long)b * n_verify + i + 1] = t;
-  }
+  // all of the request's proposals are requested before the first is stored (k <= 16)
+  long long t[16];
+  const long long last = pair[b * 2 + 1];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) t[i] = i < k ? step_tokens[(long long)i * B + b] : 0;
+  verify[(long long)b * n_verify] = last;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    if (i < k) {
+      draft[(long long)b * k + i] = t[i];
+      if (i + 1 < n_verify) verify[(long long)b * n_verify + i + 1] = t[i];
+    }
 }
 
 // out_tokens [B, k+1] (committed tokens of this round, -1 padded) -> history, counts, pair, n_commit
@@ -33,9 +39,13 @@ __global__ void spec_advance_kernel(const long long* __restrict__ out_tokens, in
   if (b >= B) return;
   long long prev = pair[b * 2], last = pair[b * 2 + 1];
   int c = count[b], n = 0;
-  for (int i = 0; i <= k; ++i) {
-    const long long t = out_tokens[(long long)b * (k + 1) + i];
-    if (t < 0) break;
+  long long tk[17];                          // the round's tokens in one round trip (k <= 16)
+#pragma unroll
+  for (int i = 0; i < 17; ++i) tk[i] = i <= k ? out_tokens[(long long)b * (k + 1) + i] : -1;
+#pragma unroll
+  for (int i = 0; i < 17; ++i) {
+    const long long t = tk[i];
+    if (i > k || t < 0 || n != i) continue;  // stop at the first -1: later slots do not count
     if (c < cap) history[(long long)b * cap + c] = t;
     ++c; ++n;
     prev = last; last = t;
@@ -138,8 +148,8 @@ extern "C" {
 int32_t vn_spec_gather(vn_ctx* ctx, const int64_t* step_tokens_dev, const int64_t* pair_dev, int32_t B, int32_t k,
                        int32_t n_verify, int64_t* draft_dev, int64_t* verify_dev) {
   VN_CHECK_CTX(ctx);
-  VN_REQUIRE(ctx, step_tokens_dev && pair_dev && draft_dev && verify_dev && B >= 1 && k >= 1 && n_verify >= 1 &&
-             n_verify <= k + 1, "bad arguments");
+  VN_REQUIRE(ctx, step_tokens_dev && pair_dev && draft_dev && verify_dev && B >= 1 && k >= 1 && k <= 16 && n_verify >= 1 &&
+             n_verify <= k + 1, "bad arguments (k in [1, 16], n_verify in [1, k + 1])");
   VN_LAUNCH_PDL(ctx, spec_gather_kernel, ceil_div(B, 128), 128, 0, (const long long*)step_tokens_dev,
             (const long long*)pair_dev, B, k, n_verify, (long long*)draft_dev, (long long*)verify_dev);
   return VN_OK;
@@ -148,8 +158,8 @@ int32_t vn_spec_gather(vn_ctx* ctx, const int64_t* step_tokens_dev, const int64_
 int32_t vn_spec_advance(vn_ctx* ctx, const int64_t* out_tokens_dev, int32_t B, int32_t k, int64_t* pair_dev,
                         int64_t* history_dev, int32_t cap, int32_t* count_dev, int32_t* n_commit_dev) {
   VN_CHECK_CTX(ctx);
-  VN_REQUIRE(ctx, out_tokens_dev && pair_dev && history_dev && count_dev && n_commit_dev && B >= 1 && k >= 0 && cap >= 0,
-             "bad arguments");
+  VN_REQUIRE(ctx, out_tokens_dev && pair_dev && history_dev && count_dev && n_commit_dev && B >= 1 && k >= 0 && k <= 16 &&
+             cap >= 0, "bad arguments (k in [0, 16])");
   VN_LAUNCH_PDL(ctx, spec_advance_kernel, ceil_div(B, 128), 128, 0, (const long long*)out_tokens_dev, B, k,
             (long long*)pair_dev, (long long*)history_dev, cap, count_dev, n_commit_dev,
             const_cast<unsigned*>(ctx->offset_src));
