@@ -288,7 +288,7 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   bool early = true;
   if (warp < nw) {
     const int last = warp + (RING - 2) * nw;                 // its last block of the first batch
-    early = a.partial == nullptr || lo_w + (min(last, max(nblk_w - 1, 0)) + 1) * 16 <= len;
+    early = lo_w + (min(last, max(nblk_w - 1, 0)) + 1) * 16 <= len;
   }
   {
     unsigned qf0[4][4] = {};
@@ -299,11 +299,11 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
     }
   }
 
-  // In the fused mode the kernel is launched as a programmatic dependent of the q|k|v GEMM: everything above touched
-  // only sequence lengths, static tables and cache entries below `len` (committed, or appended by earlier forwards,
-  // which ended in plainly launched kernels), so it ran while the GEMM was still finishing; the GEMM's partial sums
-  // are read from here on.
-  if (a.partial) pdl_wait();
+  // The kernel is launched as a programmatic dependent of the kernel that produces q | k | v: everything above
+  // touched only sequence lengths, static tables and cache entries below `len` (committed, or appended by earlier
+  // forwards, which ended in plainly launched kernels), so it ran while that kernel was still finishing; its output
+  // (the partial sums, or q and the appended K / V rows) is read from here on.
+  pdl_wait();
   if (a.partial) {
     // ---- fused q|k|v finalize: this CTA sums the split-K slices of exactly the columns it needs -- the query rows
     // of its tile and the new K / V rows of its kv head -- applies RoPE, appends K / V to the cache (every tile of a
@@ -483,7 +483,6 @@ __global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_mma_kernel(AttnArgs
   long long* tr = a.trace ? a.trace + 8ll * (blockIdx.x + (long long)gridDim.x * blockIdx.y) : nullptr;
   if (tr && threadIdx.x == 0) tr[0] = clock_stamp();
   pdl_trigger();
-  if (!a.partial) pdl_wait();        // unfused: the first key blocks may already be rows the preceding kernel wrote
   attn_tile(a, blockIdx.x, blockIdx.y, attn_smem_dyn, tr);
 }
 
@@ -634,9 +633,9 @@ inline int32_t launch_attn_mma(vn_ctx* ctx, const AttnArgs& a, int B) {
                                       (int)smem));
     attr_set |= 1ull << (ctx->device & 63);
   }
-  // VN_ATTN_PDL=0 (read once): plain launch also in the fused mode
+  // VN_ATTN_PDL=0 (read once): plain launch
   static const bool attn_pdl = [] { const char* e = getenv("VN_ATTN_PDL"); return !(e && e[0] == '0'); }();
-  const int level = ((vn_pdl_mask() & 1) || (attn_pdl && a.partial)) ? 1 : 2;
+  const int level = ((vn_pdl_mask() & 1) || attn_pdl) ? 1 : 2;
   VN_LAUNCH_PDL_LEVEL(ctx, level, "attn_detail::trisparse_attn_mma_kernel", attn_detail::trisparse_attn_mma_kernel, grid,
                       attn_detail::AW * 32, smem, a);
   return VN_OK;
