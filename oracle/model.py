@@ -31,6 +31,9 @@ from typing import List, Optional
 
 import numpy as np
 
+from . import delta
+from .delta import DELTA_KINDS
+
 F32 = np.float32
 ALIBI_MAX_T = 1024  # tri_sparse_attn.py:94
 
@@ -46,6 +49,8 @@ class Config:
     layer_pattern: Optional[List[str]] = None
     window_size: int = 512
     num_global_tokens: int = 64
+    anchor_interval: int = 128
+    latent_dim: Optional[int] = None
     use_alibi: bool = True
     use_rope: bool = False
     max_seq_len: int = 2048
@@ -114,12 +119,16 @@ def param_shapes(cfg: Config) -> dict:
         p = f"blocks.{i}."
         s[p + "norm1.weight"] = (D,)
         s[p + "norm2.weight"] = (D,)
-        s[p + "attn.gate_logits"] = (3,)
-        s[p + "attn.wq.weight"] = (cfg.n_head * hd, D)
-        s[p + "attn.wk.weight"] = (kv, D)
-        s[p + "attn.wv.weight"] = (kv, D)
-        s[p + "attn.proj.weight"] = (D, cfg.n_head * hd)
-        s[p + "attn.global_tokens.weight"] = (cfg.num_global_tokens, D)
+        if kind in DELTA_KINDS:
+            for n, shp in delta.attn_param_shapes(cfg, kind).items():
+                s[p + "attn." + n] = shp
+        else:
+            s[p + "attn.gate_logits"] = (3,)
+            s[p + "attn.wq.weight"] = (cfg.n_head * hd, D)
+            s[p + "attn.wk.weight"] = (kv, D)
+            s[p + "attn.wv.weight"] = (kv, D)
+            s[p + "attn.proj.weight"] = (D, cfg.n_head * hd)
+            s[p + "attn.global_tokens.weight"] = (cfg.num_global_tokens, D)
         if kind == "mod":
             s[p + "ffn.part_router.gate.weight"] = (cfg.num_dense_parts, D)
             for q in range(cfg.num_dense_parts):
@@ -344,14 +353,18 @@ def forward_hidden(sd, cfg: Config, tokens, cache=None, parents=None, recurrent=
     x = sd["tok_emb.weight"][tokens].astype(F32)
     if cfg.embedding_scale:
         x = (x * F32(np.sqrt(cfg.dim))).astype(F32)
-    Tc = 0 if cache is None else cache[0]["k"].shape[1]
+    Tc = 0 if cache is None else cache_len(cache)
     rope = rope_table(cfg.head_dim, max(cfg.max_seq_len, Tc + tokens.shape[1] + 1),
                       cfg.rope_theta) if cfg.use_rope else None
     new_cache = []
     for i, kind in enumerate(cfg.layer_pattern):
         p = f"blocks.{i}."
-        a, c = attention(sd, cfg, p, rmsnorm(x, sd[p + "norm1.weight"]),
-                         None if cache is None else cache[i], parents, rope, recurrent)
+        if kind in DELTA_KINDS:
+            a, c = delta.attention(sd, cfg, p + "attn.", kind, rmsnorm(x, sd[p + "norm1.weight"]),
+                                   None if cache is None else cache[i], parents, rope)
+        else:
+            a, c = attention(sd, cfg, p, rmsnorm(x, sd[p + "norm1.weight"]),
+                             None if cache is None else cache[i], parents, rope, recurrent)
         new_cache.append(c)
         x = x + a
         h = rmsnorm(x, sd[p + "norm2.weight"])
@@ -389,14 +402,24 @@ def generate_greedy_recurrent(sd, cfg: Config, prompt, max_new_tokens, eos_id=No
     return cur
 
 
+def cache_len(cache):
+    """Cached positions per sequence (a vda layer's entry nests one cache per sub-module)."""
+    c = cache[0]
+    while "k" not in c:
+        c = next(iter(c.values()))
+    return c["k"].shape[1]
+
+
 def commit_cache(cache, base_len, keep_slots):
     """KV commit / rollback: keep the first `base_len` cached positions and,
     of the entries appended after them, those at `keep_slots` (in order)."""
-    out = []
     sel = np.concatenate([np.arange(base_len), base_len + np.asarray(keep_slots, dtype=np.int64)])
-    for c in cache:
-        out.append({"k": c["k"][:, sel], "v": c["v"][:, sel]})
-    return out
+
+    def pick(c):
+        if "k" in c:
+            return {"k": c["k"][:, sel], "v": c["v"][:, sel]}
+        return {n: pick(v) for n, v in c.items()}
+    return [pick(c) for c in cache]
 
 
 def bf16_round(a):

@@ -404,9 +404,49 @@ def gen_vn():
     save("vn_reference.npz", **out)
 
 
+# ---------------------------------------------------------------------------
+# 9. Delta attention family (vda / dsa / kda / gmla layers)
+# ---------------------------------------------------------------------------
+
+def gen_delta():
+    """Whole-sequence logits of models built from the delta attention kinds: a short case per layout (every class
+    on its full-matrix route) and one of 1100 tokens (every class beyond its 1024-key switch)."""
+    from verse_nex.delta_attention import build_verse_delta_pattern
+    out = {}
+    for n in (1, 5, 6, 9, 10, 14):
+        out[f"pattern_{n}"] = np.array(build_verse_delta_pattern(n))
+    from oracle import delta as OD
+    # A: rope, GQA, one layer of every kind
+    cfg, sd = OD.golden_case("a")
+    m = ref_model(cfg, sd)
+    toks = np.random.default_rng(32).integers(0, 96, (2, 40)).astype(np.int64)
+    out["a_tokens"] = toks
+    out["a_logits"] = ref_forward(m, cfg, toks)
+    out["a_greedy"] = ref_greedy(m, cfg, toks[:, :8], 24)
+    # B: no rope, multi-head, a latent narrower than K | V, anchors wider apart than the window
+    cfg, sd = OD.golden_case("b")
+    m = ref_model(cfg, sd)
+    toks = np.random.default_rng(34).integers(0, 80, (3, 33)).astype(np.int64)
+    out["b_tokens"] = toks
+    out["b_logits"] = ref_forward(m, cfg, toks)
+    # C: 1100 tokens -- dense routes fall back to window (+ sinks), KDA goes chunk-wise with its anchors concatenated
+    cfg, sd = OD.golden_case("c")
+    m = ref_model(cfg, sd)
+    toks = np.random.default_rng(36).integers(0, 64, (1, 1100)).astype(np.int64)
+    rows = np.array([0, 1, 39, 40, 47, 48, 95, 96, 500, 960, 1023, 1024] + list(range(1088, 1100)))
+    lg = ref_forward(m, cfg, toks)
+    out["c_tokens"] = toks
+    out["c_rows"] = rows
+    out["c_logits"] = lg[:, rows]
+    # the same model at 1024 tokens is still on the full-matrix routes
+    lg = ref_forward(m, cfg, toks[:, :1024])
+    out["c_logits_1024"] = lg[:, rows[:11]]
+    save("delta_reference.npz", **out)
+
+
 if __name__ == "__main__":
     only = set(sys.argv[2:])          # e.g. `make_golden.py /path/to/reference sampling recurrent`
     for name, fn in (("spec", gen_spec), ("small", gen_small), ("mini", gen_mini), ("quant", gen_quant),
-                     ("backend", gen_backend), ("sampling", gen_sampling), ("recurrent", gen_recurrent), ("vn", gen_vn)):
+                     ("backend", gen_backend), ("sampling", gen_sampling), ("recurrent", gen_recurrent), ("vn", gen_vn), ("delta", gen_delta)):
         if not only or name in only:
             fn()

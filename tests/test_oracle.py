@@ -261,3 +261,58 @@ def test_recurrent_path_matches_the_reference_beyond_the_window(golden, tag):
     eos = int(g[f"{tag}_generate"][0, W + 6])
     out = OM.generate_greedy_recurrent(sd, cfg, toks[:1, :6], 12, eos_id=eos)
     np.testing.assert_array_equal(out, g[f"{tag}_generate_eos"])
+
+
+def test_delta_attention_family_against_the_reference(golden):
+    """vda / dsa / kda / gmla layers: whole-sequence logits recorded from the reference classes, on the full-matrix
+    routes (cases a, b, c at 1024 tokens) and beyond the 1024-key switch (case c at 1100 tokens, where KDA's
+    chunk-wise route counts an anchor inside the window slice twice)."""
+    from oracle import delta as OD
+    g = golden("delta_reference.npz")
+    for n in (1, 5, 6, 9, 10, 14):
+        assert list(g[f"pattern_{n}"]) == OD.build_verse_delta_pattern(n)
+    for tag in ("a", "b"):
+        cfg, sd = OD.golden_case(tag)
+        lg, _ = OM.forward(sd, cfg, g[tag + "_tokens"])
+        np.testing.assert_allclose(lg, g[tag + "_logits"], rtol=2e-4, atol=2e-5)
+    cfg, sd = OD.golden_case("c")
+    rows = g["c_rows"]
+    lg, _ = OM.forward(sd, cfg, g["c_tokens"])
+    np.testing.assert_allclose(lg[:, rows], g["c_logits"], rtol=2e-4, atol=2e-5)
+    lg, _ = OM.forward(sd, cfg, g["c_tokens"][:, :1024])
+    np.testing.assert_allclose(lg[:, rows[:11]], g["c_logits_1024"], rtol=2e-4, atol=2e-5)
+    # greedy continuation, token for token
+    cfg, sd = OD.golden_case("a")
+    cur = g["a_greedy"][:, :8]
+    for _ in range(24):
+        nxt = np.argmax(OM.forward(sd, cfg, cur)[0][:, -1], -1)
+        cur = np.concatenate([cur, nxt[:, None]], axis=1)
+    np.testing.assert_array_equal(cur, g["a_greedy"])
+
+
+def test_delta_cache_and_tree_equal_the_whole_sequence_forward():
+    from oracle import delta as OD
+    cfg, sd = OD.golden_case("a")
+    rng = np.random.default_rng(3)
+    toks = rng.integers(0, cfg.vocab_size, (2, 30))
+    full, _ = OM.forward(sd, cfg, toks)
+    l1, cache = OM.forward(sd, cfg, toks[:, :17])
+    l2, cache2 = OM.forward(sd, cfg, toks[:, 17:], cache=cache)
+    np.testing.assert_allclose(np.concatenate([l1, l2], 1), full, rtol=2e-4, atol=2e-5)
+    # commit keeps a prefix of the appended entries in every nested plane
+    kept = OM.commit_cache(cache2, 17, [0, 1, 2])
+    assert OM.cache_len(kept) == 20
+    l3, _ = OM.forward(sd, cfg, toks[:, 20:], cache=kept)
+    np.testing.assert_allclose(l3, full[:, 20:], rtol=2e-4, atol=2e-5)
+    parents = [-1, -1, 0, 0, 1, 2, 2, 5]
+    nodes = rng.integers(0, cfg.vocab_size, (1, len(parents)))
+    _, cache = OM.forward(sd, cfg, toks[:1, :20])
+    lg_tree, _ = OM.forward(sd, cfg, nodes, cache=cache, parents=parents)
+    for i in range(len(parents)):
+        path, j = [], i
+        while j >= 0:
+            path.append(j)
+            j = parents[j]
+        seq = np.concatenate([toks[:1, :20], nodes[:, path[::-1]]], axis=1)
+        lg, _ = OM.forward(sd, cfg, seq)
+        np.testing.assert_allclose(lg_tree[:, i], lg[:, -1], rtol=2e-4, atol=2e-5)
