@@ -1,0 +1,135 @@
+"""Layers of the delta attention kinds (vda / dsa / kda / gmla, verse_nex/delta_attention.py) on the device, against
+logits recorded from the reference classes (tests/golden/delta_reference.npz) and against the CPU oracle."""
+
+import numpy as np
+import pytest
+
+from oracle import delta as OD
+from oracle import model as OM
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b):
+    return float(np.max(np.abs(np.asarray(a, np.float64) - b)) / max(np.max(np.abs(b)), 1e-30))
+
+
+def build(cfg, sd, dtype="f32"):
+    import versenext_b200 as vn
+    kw = cfg.to_dict()
+    kw.pop("init_std")
+    m = vn.VerseNexLM(dtype=dtype, **kw)
+    m.load_state_dict(sd)
+    return m
+
+
+@pytest.mark.parametrize("dtype,tol", [("f32", 1e-3), ("bf16", 2e-2)])
+def test_delta_layers_against_the_reference_logits(golden, dtype, tol):
+    """Whole-sequence logits: one layer of every kind with RoPE and GQA (a), no RoPE / multi-head / narrow latent
+    (b), and the model of case c at 1024 keys (full-matrix routes) and at 1100 keys (window fall-backs; KDA counts an
+    anchor inside its chunk's window slice twice)."""
+    g = golden("delta_reference.npz")
+    for tag in ("a", "b", "c"):
+        cfg, sd = OD.golden_case(tag)
+        if dtype == "bf16":        # the oracle run on the same bf16-rounded weights
+            sd = {n: OM.bf16_round(v) for n, v in sd.items()}
+        m = build(cfg, sd, dtype)
+        toks = g[tag + "_tokens"]
+        if tag != "c":
+            ref = g[tag + "_logits"] if dtype == "f32" else OM.forward(sd, cfg, toks)[0]
+            assert rel_err(m(toks).data.numpy(), ref) < tol, tag
+            continue
+        rows = g["c_rows"]
+        for n, key, sel in ((1100, "c_logits", rows), (1024, "c_logits_1024", rows[:11])):
+            ref = g[key] if dtype == "f32" else OM.forward(sd, cfg, toks[:, :n])[0][:, sel]
+            assert rel_err(m(toks[:, :n]).data.numpy()[:, sel], ref) < tol, (tag, n)
+
+
+def test_delta_cache_chain_tree_and_commit():
+    """New positions on top of the cache equal the whole-sequence forward: a chain, a tree (every node against the
+    forward over its own path), a committed path, and a chain that crosses the 1024-key switch."""
+    cfg, sd = OD.golden_case("a")
+    m = build(cfg, sd)
+    rng = np.random.default_rng(3)
+    toks = rng.integers(0, cfg.vocab_size, (2, 30))
+    full = OM.forward(sd, cfg, toks)[0]
+    cache = m.new_cache(2, 64)
+    l1 = m.forward_cached(toks[:, :17], cache).numpy()
+    cache.commit(17, np.full(2, 17, np.int32))
+    l2 = m.forward_cached(toks[:, 17:], cache).numpy()
+    assert rel_err(np.concatenate([l1, l2], 1), full) < 1e-3
+    # keep 3 of the 13 appended entries, run the rest again
+    cache.commit(13, np.full(2, 3, np.int32))
+    np.testing.assert_array_equal(cache.per_seq_lens, [20, 20])
+    l3 = m.forward_cached(toks[:, 20:], cache).numpy()
+    assert rel_err(l3, full[:, 20:]) < 1e-3
+    # tree on top of 20 cached tokens; then commit the path 1 -> 4 and continue
+    parents = [-1, -1, 0, 0, 1, 2, 2, 5]
+    nodes = rng.integers(0, cfg.vocab_size, (2, len(parents)))
+    lt = m.forward_cached(nodes, cache, parents=parents).numpy()
+    _, oc = OM.forward(sd, cfg, toks[:, :20])
+    want, _ = OM.forward(sd, cfg, nodes, cache=oc, parents=parents)
+    assert rel_err(lt, want) < 1e-3
+    cache.commit(len(parents), np.full(2, 2, np.int32), keep_idx=np.tile(np.array([1, 4, 0, 0], np.int32), (2, 1)))
+    np.testing.assert_array_equal(cache.per_seq_lens, [22, 22])
+    tail = rng.integers(0, cfg.vocab_size, (2, 5))
+    seq = np.concatenate([toks[:, :20], nodes[:, [1, 4]], tail], axis=1)
+    l4 = m.forward_cached(tail, cache).numpy()
+    assert rel_err(l4, OM.forward(sd, cfg, seq)[0][:, 22:]) < 1e-3
+    m.check()
+    # 1020 cached keys + 8 new ones: the new rows are beyond the switch, their keys are cached and new ones
+    cfg, sd = OD.golden_case("c")
+    m = build(cfg, sd)
+    toks = rng.integers(0, cfg.vocab_size, (1, 1028))
+    cache = m.new_cache(1, 1100)
+    m.forward_cached(toks[:, :1020], cache, last_only=True)
+    cache.commit(1020, np.full(1, 1020, np.int32))
+    got = m.forward_cached(toks[:, 1020:], cache).numpy()
+    _, oc = OM.forward(sd, cfg, toks[:, :1020])
+    want, _ = OM.forward(sd, cfg, toks[:, 1020:], cache=oc)
+    assert rel_err(got, want) < 1e-3
+    m.check()
+
+
+def test_delta_model_generates_and_verifies_like_the_reference(golden):
+    """Greedy generation equals the stream recorded from the reference; the speculative engines (chain and tree) with
+    a delta target commit exactly that stream, whatever the draft proposes."""
+    import versenext_b200 as vn
+    g = golden("delta_reference.npz")
+    cfg, sd = OD.golden_case("a")
+    t = build(cfg, sd)
+    prompt = g["a_greedy"][:, :8]
+    np.testing.assert_array_equal(t.generate(prompt, max_new_tokens=24, temperature=0.0), g["a_greedy"])
+    d_cfg = OM.Config(vocab_size=cfg.vocab_size, dim=32, n_layer=2, n_head=2, n_kv_head=1, layer_pattern=["gmla", "kda"],
+                      window_size=8, num_global_tokens=4, anchor_interval=4, use_alibi=False, use_rope=True,
+                      max_seq_len=64, init_std=0.1)
+    d = build(d_cfg, OM.init_state_dict(d_cfg, seed=41, gate_std=1.0))
+    eng = vn.SpecEngine(t, d, max_batch=2, max_seq=64, k=3, temperature=0.0, bonus=True, max_new_tokens=32)
+    toks, _ = eng.generate(prompt, 24)
+    np.testing.assert_array_equal(toks[:, :32], g["a_greedy"])
+    tree = vn.TreeSpecEngine(t, d, [-1, -1, 0, 0, 1, 2], max_batch=2, max_seq=64, max_new_tokens=32)
+    toks, _ = tree.generate(prompt, 24)
+    np.testing.assert_array_equal(toks[:, :32], g["a_greedy"])
+    assert vn.build_verse_delta_pattern(10) == list(g["pattern_10"])
+    with pytest.raises(NotImplementedError):
+        t.quantize("int8")
+
+
+def test_delta_layers_bf16_head_dim_64_with_a_long_prompt():
+    """head_dim 64, bf16, 320 prompt rows (the projections then run as 256-row segments on the tcgen05 kernel) and a
+    decode step on the cache."""
+    cfg = OM.Config(vocab_size=128, dim=256, n_layer=2, n_head=4, n_kv_head=2, layer_pattern=["vda", "dsa"],
+                    window_size=32, num_global_tokens=8, anchor_interval=16, latent_dim=64, use_alibi=False,
+                    use_rope=True, max_seq_len=256, init_std=0.05)
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=51, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    rng = np.random.default_rng(5)
+    toks = rng.integers(0, cfg.vocab_size, (2, 161))
+    want = OM.forward(sd, cfg, toks)[0]
+    cache = m.new_cache(2, 256)
+    l1 = m.forward_cached(toks[:, :160], cache).numpy()
+    cache.commit(160, np.full(2, 160, np.int32))
+    l2 = m.forward_cached(toks[:, 160:], cache).numpy()
+    assert rel_err(l1, want[:, :160]) < 2e-2
+    assert rel_err(l2, want[:, 160:]) < 2e-2
+    m.check()

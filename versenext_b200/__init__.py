@@ -3,6 +3,7 @@
 Public surface (names follow the reference):
   SpeculativeDecoder                      verse_nex/speculative.py:55
   VerseNexLM (= CometSparkNexLM), KVCache verse_nex/cometspark.py:294, kv_cache_parallel.py:42
+  build_verse_delta_pattern               verse_nex/delta_attention.py:1218 (layer kinds vda / dsa / kda / gmla)
   SpecEngine                              batched draft -> verify -> accept -> commit loop
   TreeSpecEngine                          the same with tree proposals (greedy rule)
   ShardedSpecEngine, Comm, rank_seed      the same with the LM head split by vocabulary columns over NCCL ranks
@@ -20,7 +21,7 @@ from . import _lib
 from .device import Context, DeviceArray, as_device
 from .backend import DeviceBackend, B200Backend, get_backend, clear_backend_cache
 from .speculative import SpeculativeDecoder, Tensor, no_grad
-from .model import VerseNexLM, CometSparkNexLM, KVCache
+from .model import VerseNexLM, CometSparkNexLM, KVCache, build_verse_delta_pattern
 from .engine import SpecEngine
 from .tree_engine import TreeSpecEngine
 from .comm import Comm
@@ -30,5 +31,5 @@ from . import sampling
 from . import quant
 
 __all__ = ["Context", "DeviceArray", "as_device", "DeviceBackend", "B200Backend", "get_backend",
-           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "no_grad", "sampling", "quant", "VerseNexLM", "CometSparkNexLM", "KVCache", "SpecEngine", "TreeSpecEngine",
+           "clear_backend_cache", "SpeculativeDecoder", "Tensor", "no_grad", "sampling", "quant", "VerseNexLM", "CometSparkNexLM", "KVCache", "build_verse_delta_pattern", "SpecEngine", "TreeSpecEngine",
            "ShardedSpecEngine", "Comm", "rank_seed", "VNFileReader", "load_vn"]

@@ -6,6 +6,7 @@
 #include "gemm_mma.cuh"
 #include "model_kernels.cuh"
 #include "attn_mma.cuh"
+#include "delta_attn.cuh"
 #include "draft_kernel.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_mma_q.cuh"
@@ -24,12 +25,15 @@ namespace {
 struct Config {
   int vocab = 0, dim = 0, n_layer = 0, n_head = 0, n_kv = 0, hd = 0;
   int window = 512, n_sink = 64, use_alibi = 1, use_rope = 0, max_seq_len = 2048;
+  int anchor = 128, latent = 0;   // delta attention: anchor_interval, latent_dim (0: n_kv * hd)
   double rope_theta = 10000.0;
   int P = 5, E = 8, top_k = 3, expert_hidden = 0, mlp_hidden = 0, mlp_mult = 4;
   int tie = 1, emb_scale = 0;
   int bf16 = 0;
-  std::vector<int> kind;  // 0 trisparse, 1 mod
+  std::vector<int> kind;  // 0 trisparse, 1 mod (TriSparse attention + MoD feed-forward), 2 vda, 3 dsa, 4 kda, 5 gmla
 };
+
+inline bool is_delta(int kind) { return kind >= 2; }
 
 // ---- minimal JSON field access (flat object, as json.dumps of the constructor kwargs yields) -------------
 bool json_find(const std::string& s, const char* key, size_t* pos) {
@@ -79,8 +83,23 @@ bool json_str_list(const std::string& s, const char* key, std::vector<std::strin
   return true;
 }
 
+// one DSA / KDA / GMLA module of a delta-attention layer (verse_nex/delta_attention.py): a dsa / kda / gmla layer
+// has one, a vda layer one of each
+struct SubAttn {
+  int mode = 0;              // 0 dsa, 1 kda, 2 gmla
+  void* wqkv = nullptr;      // dsa, kda: [(H + 2 n_kv) hd, D] (q | k | v); gmla: [H hd, D] (q)
+  void* w_down = nullptr;    // gmla: [latent, D]              w_kv_down
+  void* w_up = nullptr;      // gmla: [2 n_kv hd, latent]      w_k_up | w_v_up
+  void* sink = nullptr;      // dsa: [n_sink, D] global_tokens.weight, and its K / V (finalize)
+  void* sink_k = nullptr;
+  void* sink_v = nullptr;
+  float* head_gate = nullptr;  // dsa, gmla: device [H] sigmoid(head_gate_logits)
+  int pair = 0;              // which K / V plane pair of the cache is this module's
+};
+
 struct Layer {
   int kind = 0;
+  std::vector<SubAttn> sub;  // delta kinds only
   float* norm1 = nullptr;
   float* norm2 = nullptr;
   float gate_logits[3] = {0.f, 0.f, 0.f};
@@ -146,6 +165,11 @@ struct vn_model {
   int* row_seg = nullptr;        // [2][row_seg_n] offsets and counts of the 256-row segments a prompt's GEMMs use
   int row_seg_cap = 0;
   unsigned* stack_bar = nullptr; // two device words: arrivals and generation of the fused layer stack's grid barrier
+  std::vector<int> pair0;        // per layer: its first K / V plane pair in a cache (a vda layer owns three pairs)
+  int n_pairs = 0;
+  bool has_delta = false;        // some layer is vda / dsa / kda / gmla
+  void* lat = nullptr;           // [M, latent] gmla latents, storage dtype
+  float* mix = nullptr;          // [M, H hd] running sum of a vda layer's modules
   bool recurrent = false;        // vn_model_set_recurrent: ALiBi path as in the reference's one-token recurrent step
   bool fused_stack = false;      // vn_model_set_fused_stack / VN_DRAFT_STACK=1: the layer stack as one cooperative kernel
   bool use_tc = true;            // VN_GEMM_TC=0 in the environment: keep the mma.sync GEMMs
@@ -222,12 +246,40 @@ int32_t alloc_weights(vn_model* m) {
     L.kind = c.kind[i];
     TRY(A((void**)&L.norm1, D * 4));
     TRY(A((void**)&L.norm2, D * 4));
-    TRY(A(&L.wqkv, qkv_rows * D * e));
     TRY(A(&L.wproj, D * (size_t)c.n_head * c.hd * e));
-    TRY(A(&L.sink, (size_t)c.n_sink * D * e));
-    TRY(dev_alloc(ctx, &L.sink_k, (size_t)c.n_sink * c.n_kv * c.hd * e));
-    TRY(dev_alloc(ctx, &L.sink_v, (size_t)c.n_sink * c.n_kv * c.hd * e));
-    if (L.kind == 0) {
+    m->pair0.push_back(m->n_pairs);
+    if (is_delta(L.kind)) {
+      m->has_delta = true;
+      const size_t qd = (size_t)c.n_head * c.hd, kvd = (size_t)c.n_kv * c.hd, lat = c.latent;
+      const int modes[3] = {0, 1, 2};
+      const int first = L.kind == 2 ? 0 : L.kind - 3, count = L.kind == 2 ? 3 : 1;
+      for (int si = 0; si < count; ++si) {
+        SubAttn S;
+        S.mode = modes[first + si];
+        S.pair = m->n_pairs++;
+        if (S.mode == 2) {
+          TRY(A(&S.wqkv, qd * D * e));
+          TRY(A(&S.w_down, lat * D * e));
+          TRY(A(&S.w_up, 2 * kvd * lat * e));
+        } else {
+          TRY(A(&S.wqkv, qkv_rows * D * e));
+        }
+        if (S.mode == 0) {
+          TRY(A(&S.sink, (size_t)c.n_sink * D * e));
+          TRY(dev_alloc(ctx, &S.sink_k, (size_t)c.n_sink * kvd * e));
+          TRY(dev_alloc(ctx, &S.sink_v, (size_t)c.n_sink * kvd * e));
+        }
+        if (S.mode != 1) TRY(A((void**)&S.head_gate, (size_t)c.n_head * 4));
+        L.sub.push_back(S);
+      }
+    } else {
+      m->n_pairs++;
+      TRY(A(&L.wqkv, qkv_rows * D * e));
+      TRY(A(&L.sink, (size_t)c.n_sink * D * e));
+      TRY(dev_alloc(ctx, &L.sink_k, (size_t)c.n_sink * c.n_kv * c.hd * e));
+      TRY(dev_alloc(ctx, &L.sink_v, (size_t)c.n_sink * c.n_kv * c.hd * e));
+    }
+    if (L.kind != 1) {
       TRY(A(&L.w_gateup, (size_t)2 * c.mlp_hidden * D * e));
       TRY(A(&L.w_down, D * (size_t)c.mlp_hidden * e));
     } else {
@@ -248,7 +300,7 @@ int32_t ensure_rows(vn_model* m, int M) {
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   void** bufs[] = {(void**)&m->x, &m->h, (void**)&m->h32, (void**)&m->qkv, &m->attn, &m->act, (void**)&m->y,
                    (void**)&m->slot_expert, (void**)&m->slot_w, (void**)&m->part_w, (void**)&m->sorted_row,
-                   (void**)&m->slot_pos, (void**)&m->rows_dev, &m->hs};
+                   (void**)&m->slot_pos, (void**)&m->rows_dev, &m->hs, &m->lat, (void**)&m->mix};
   for (void** b : bufs) { if (*b) cudaFree(*b); *b = nullptr; }
   const size_t e = m->esz, D = c.dim, R = (size_t)M + (M >> 2) + 32;
   bool has_mod = false;
@@ -262,6 +314,10 @@ int32_t ensure_rows(vn_model* m, int M) {
   TRY(dev_alloc(ctx, &m->attn, R * D * e));
   TRY(dev_alloc(ctx, &m->act, R * S * hid * e));
   TRY(dev_alloc(ctx, (void**)&m->rows_dev, R * 4));
+  if (m->has_delta) {
+    TRY(dev_alloc(ctx, &m->lat, R * (size_t)c.latent * e));
+    TRY(dev_alloc(ctx, (void**)&m->mix, R * (size_t)c.n_head * c.hd * 4));
+  }
   // segment tables of a prompt's GEMMs (rows in blocks of 256; the experts' pieces), sized for the row capacity so
   // that a forward never allocates them: filled by kernels on the stream
   if (m->row_seg) cudaFree(m->row_seg);
@@ -307,7 +363,7 @@ int32_t linear(vn_model* m, GemmArgs g) {
     // segment, from L2 after the first.  VN_PREFILL_TC=0 (read per call) keeps the mma.sync kernel.
     const char* pe = getenv("VN_PREFILL_TC");
     if (m->use_tc && !(pe && pe[0] == '0') && g.M > 256 && !g.seg_cnt && !g.a_rows && g.nseg == 1 && !g.bias &&
-        g.K % 8 == 0 && g.ldw_k == 1 && tc_detail::encode_fn() != nullptr &&
+        g.K % tc_detail::BK == 0 && g.N >= tc_detail::BF && g.ldw_k == 1 && tc_detail::encode_fn() != nullptr &&
         (g.epi == EPI_STORE || g.epi == EPI_ADD || g.epi == EPI_SWIGLU)) {
       const int nseg = ceil_div(g.M, 256);
       if (nseg <= m->row_seg_cap) {
@@ -326,6 +382,57 @@ int32_t linear(vn_model* m, GemmArgs g) {
     return launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g);
   }
   return launch_gemm_simt<float, float>(ctx, g);
+}
+
+// The attention part of a vda / dsa / kda / gmla layer (verse_nex/delta_attention.py): m->h (normalised rows) ->
+// m->attn (head-space output before the layer's projection).  Every module projects on its own, rotates and appends
+// its K / V to its own plane pair, and runs delta_attn_kernel; a vda layer sums its three modules with
+// sigmoid(gate_logits) (:1167-1168) through the fp32 buffer m->mix.
+template <typename T>
+int32_t delta_attention(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool tree, int slot_offset) {
+  vn_ctx* ctx = m->ctx;
+  const Config& c = m->cfg;
+  const int M = B * Tn, D = c.dim, H = c.n_head, hd = c.hd, n_kv = c.n_kv;
+  const int qd = H * hd, kvd = n_kv * hd, qkv_ld = qd + 2 * kvd;
+  const int n_sub = (int)L.sub.size();
+  for (int si = 0; si < n_sub; ++si) {
+    SubAttn& S = L.sub[si];
+    GemmArgs g;
+    g.A = m->h; g.lda = D; g.W = S.wqkv; g.ldw = D; g.C = m->qkv; g.ldc = qkv_ld; g.M = M; g.K = D;
+    if (S.mode == 2) {
+      // q; latent = w_kv_down(h) in the storage dtype; k | v = (w_k_up | w_v_up)(latent)   (:893-896)
+      g.N = qd; g.tag = "gemm_gmla_q";
+      TRY(linear(m, g));
+      g = GemmArgs();
+      g.A = m->h; g.lda = D; g.W = S.w_down; g.ldw = D; g.C = m->lat; g.ldc = c.latent; g.M = M; g.N = c.latent; g.K = D;
+      g.c_bf16 = c.bf16; g.tag = "gemm_gmla_down";
+      TRY(linear(m, g));
+      g = GemmArgs();
+      g.A = m->lat; g.lda = c.latent; g.W = S.w_up; g.ldw = c.latent; g.C = m->qkv + qd; g.ldc = qkv_ld; g.M = M;
+      g.N = 2 * kvd; g.K = c.latent; g.tag = "gemm_gmla_up";
+      TRY(linear(m, g));
+    } else {
+      g.N = qkv_ld; g.tag = "gemm_qkv";
+      TRY(linear(m, g));
+    }
+    VN_LAUNCH(ctx, rope_append_kernel<T>, M, 128, 0, m->qkv, m->rope_cos, m->rope_sin, kv->lens,
+              tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[S.pair], (T*)kv->v[S.pair], Tn, H, n_kv, hd, kv->max_seq,
+              c.use_rope, m->rope_rows, slot_offset);
+    DeltaArgs a;
+    a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[S.pair]; a.vc = kv->v[S.pair]; a.sink_k = S.sink_k; a.sink_v = S.sink_v;
+    a.head_gate = S.head_gate;
+    a.acc_in = si > 0 ? m->mix : nullptr;
+    a.acc_out = si + 1 < n_sub ? m->mix : nullptr;
+    a.out = si + 1 == n_sub ? m->attn : nullptr;
+    a.out_w = n_sub > 1 ? 0.5f * (1.0f + tanhf(0.5f * L.gate_logits[si])) : 1.0f;
+    a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
+    a.Tn = Tn; a.H = H; a.n_kv = n_kv; a.hd = hd; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink;
+    a.slot_offset = slot_offset; a.anchor = c.anchor; a.max_t = 1024; a.mode = S.mode;
+    a.scale = 1.0f / sqrtf((float)hd);
+    dim3 grid(ceil_div(H, 8), M);
+    VN_LAUNCH(ctx, delta_attn_kernel<T>, grid, 256, 0, a);
+  }
+  return VN_OK;
 }
 
 template <typename T>
@@ -351,15 +458,19 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
     Layer& L = m->layers[li];
     VN_LAUNCH(ctx, rmsnorm_kernel<T>, M, 256, 0, m->x, L.norm1, (T*)m->h, (float*)nullptr, 1, 0, D, 1e-6f);
     GemmArgs g;
+    if (is_delta(L.kind)) {
+      TRY(delta_attention<T>(m, kv, L, B, Tn, tree, slot_offset));
+    } else {
+    const int pr = m->pair0[li];
     g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.C = m->qkv; g.ldc = qkv_ld; g.M = M; g.N = qkv_ld; g.K = D;
     g.tag = "gemm_qkv";
     pick(g, L.wqkv, L.q[0], L.qs[0], 0);
     TRY(linear(m, g));
     VN_LAUNCH(ctx, rope_append_kernel<T>, M, 128, 0, m->qkv, m->rope_cos, m->rope_sin, kv->lens,
-              tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq,
+              tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[pr], (T*)kv->v[pr], Tn, H, n_kv, hd, kv->max_seq,
               c.use_rope, m->rope_rows, slot_offset);
     AttnArgs a;
-    a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[li]; a.vc = kv->v[li]; a.sink_k = L.sink_k; a.sink_v = L.sink_v;
+    a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[pr]; a.vc = kv->v[pr]; a.sink_k = L.sink_k; a.sink_v = L.sink_v;
     a.out = m->attn; a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
     a.Tn = Tn; a.H = H; a.n_kv = n_kv; a.hd = hd; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink;
     a.use_alibi = c.use_alibi; a.alibi_max = 1024; a.slot_offset = slot_offset;
@@ -375,6 +486,7 @@ int32_t forward_t(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, 
     } else {
       dim3 grid(ceil_div(H, 8), M);
       VN_LAUNCH(ctx, trisparse_attn_kernel<T>, grid, 256, 0, a);
+    }
     }
     g = GemmArgs();
     g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.C = m->x; g.ldc = D; g.M = M; g.N = D; g.K = H * hd;
@@ -873,6 +985,18 @@ int32_t compute_sinks(vn_model* m, int mode) {
   const Config& c = m->cfg;
   const long long D = c.dim, qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
   for (auto& L : m->layers) {
+    // a DSA module's sinks (delta_attention.py:451-459): the same product with the module's own wk / wv, dense only
+    for (auto& S : L.sub) {
+      if (S.mode != 0) continue;
+      for (int which = 0; which < 2; ++which) {
+        GemmArgs g;
+        g.A = S.sink; g.lda = D; g.ldw = D; g.W = (char*)S.wqkv + (size_t)(qd + which * kvd) * D * m->esz;
+        g.C = which ? S.sink_v : S.sink_k; g.ldc = kvd; g.M = c.n_sink; g.N = (int)kvd; g.K = (int)D; g.c_bf16 = c.bf16;
+        if (c.bf16) TRY((launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g)));
+        else TRY((launch_gemm_simt<float, float>(ctx, g)));
+      }
+    }
+    if (is_delta(L.kind)) continue;
     for (int which = 0; which < 2; ++which) {
       GemmArgs g;
       g.A = L.sink; g.lda = D; g.ldw = D;
@@ -919,6 +1043,7 @@ int32_t vn_model_create(vn_ctx* ctx, const char* config_json, vn_model** out) {
   c.n_kv = c.n_head;
   need("n_kv_head", &c.n_kv);
   need("window_size", &c.window); need("num_global_tokens", &c.n_sink); need("use_alibi", &c.use_alibi);
+  need("anchor_interval", &c.anchor); need("latent_dim", &c.latent);
   need("use_rope", &c.use_rope); need("max_seq_len", &c.max_seq_len);
   if (json_num(s, "rope_theta", &v)) c.rope_theta = v;
   need("num_dense_parts", &c.P); need("num_experts_per_part", &c.E); need("top_k", &c.top_k);
@@ -935,12 +1060,17 @@ int32_t vn_model_create(vn_ctx* ctx, const char* config_json, vn_model** out) {
   c.hd = c.dim / c.n_head;
   VN_REQUIRE(ctx, c.hd % 8 == 0 && c.hd <= 64, "head_dim %d unsupported (multiple of 8, at most 64)", c.hd);
   VN_REQUIRE(ctx, c.window >= 1 && c.n_sink >= 1, "window_size and num_global_tokens must be positive");
+  VN_REQUIRE(ctx, c.anchor >= 1, "anchor_interval must be >= 1, got %d", c.anchor);
+  if (c.latent <= 0) c.latent = c.n_kv * c.hd;      // delta_attention.py:858
   std::vector<std::string> pat;
   if (json_str_list(s, "layer_pattern", &pat)) {
     VN_REQUIRE(ctx, (int)pat.size() == c.n_layer, "layer_pattern length (%zu) must equal n_layer (%d)", pat.size(), c.n_layer);
     for (auto& k : pat) {
-      VN_REQUIRE(ctx, k == "trisparse" || k == "mod", "layer kind %s is not built (trisparse | mod)", k.c_str());
-      c.kind.push_back(k == "mod");
+      static const char* names[6] = {"trisparse", "mod", "vda", "dsa", "kda", "gmla"};
+      int code = -1;
+      for (int i = 0; i < 6; ++i) if (k == names[i]) code = i;
+      VN_REQUIRE(ctx, code >= 0, "layer kind %s unknown (trisparse | mod | vda | dsa | kda | gmla)", k.c_str());
+      c.kind.push_back(code);
     }
   } else {
     c.kind.assign(c.n_layer, 0);
@@ -973,6 +1103,9 @@ int32_t vn_model_destroy(vn_model* m) {
   F(m->expert_count); F(m->expert_off); F(m->expert_cur); F(m->sorted_row); F(m->slot_pos); F(m->depth_dev);
   F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->stack_bar); F(m->row_seg); F(m->sub_seg); F(m->head_q); F(m->head_qs);
   for (auto& L : m->layers) for (int i = 0; i < 6; ++i) { F(L.q[i]); F(L.qs[i]); }
+  for (auto& L : m->layers)
+    for (auto& S : L.sub) { F(S.wqkv); F(S.w_down); F(S.w_up); F(S.sink); F(S.sink_k); F(S.sink_v); F(S.head_gate); }
+  F(m->lat); F(m->mix);
   delete m;
   return VN_OK;
 }
@@ -1018,15 +1151,47 @@ int32_t vn_model_load_tensor(vn_model* m, const char* name, const float* data, i
     const long long qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
     if (rest == "norm1.weight") { SHAPE(D, 1); TRY(upload(m, data, L.norm1, 1, D, D, 1, 0, true)); }
     else if (rest == "norm2.weight") { SHAPE(D, 1); TRY(upload(m, data, L.norm2, 1, D, D, 1, 0, true)); }
-    else if (rest == "attn.gate_logits") { SHAPE(3, 1); memcpy(L.gate_logits, data, 12); }
+    else if (rest == "attn.gate_logits" && (!is_delta(L.kind) || L.kind == 2)) { SHAPE(3, 1); memcpy(L.gate_logits, data, 12); }
+    else if (is_delta(L.kind) && rest.rfind("attn.", 0) == 0 && rest != "attn.proj.weight") {
+      // a module's tensor: blocks.i.attn.<leaf> (dsa / kda / gmla layer) or blocks.i.attn.<dsa|kda|gmla>.<leaf> (vda)
+      std::string leaf = rest.substr(5);
+      SubAttn* S = nullptr;
+      if (L.kind == 2) {
+        const size_t d2 = leaf.find('.');
+        VN_REQUIRE(ctx, d2 != std::string::npos, "unexpected tensor %s", name);
+        const std::string sub = leaf.substr(0, d2);
+        const int which = sub == "dsa" ? 0 : (sub == "kda" ? 1 : (sub == "gmla" ? 2 : -1));
+        VN_REQUIRE(ctx, which >= 0, "unexpected tensor %s", name);
+        S = &L.sub[which];
+        leaf = leaf.substr(d2 + 1);
+      } else {
+        S = &L.sub[0];
+      }
+      const long long lat = c.latent;
+      if (leaf == "wq.weight") { SHAPE(qd, D); TRY(upload(m, data, S->wqkv, r, cl, D, 1, 0)); }
+      else if (S->mode != 2 && leaf == "wk.weight") { SHAPE(kvd, D); TRY(upload(m, data, S->wqkv, r, cl, D, 1, qd)); }
+      else if (S->mode != 2 && leaf == "wv.weight") { SHAPE(kvd, D); TRY(upload(m, data, S->wqkv, r, cl, D, 1, qd + kvd)); }
+      else if (S->mode == 0 && leaf == "global_tokens.weight") { SHAPE(c.n_sink, D); TRY(upload(m, data, S->sink, r, cl, D)); }
+      else if (S->mode == 2 && leaf == "w_kv_down.weight") { SHAPE(lat, D); TRY(upload(m, data, S->w_down, r, cl, D)); }
+      else if (S->mode == 2 && leaf == "w_k_up.weight") { SHAPE(kvd, lat); TRY(upload(m, data, S->w_up, r, cl, lat, 1, 0)); }
+      else if (S->mode == 2 && leaf == "w_v_up.weight") { SHAPE(kvd, lat); TRY(upload(m, data, S->w_up, r, cl, lat, 1, kvd)); }
+      else if (S->mode != 1 && leaf == "head_gate_logits") {
+        SHAPE(c.n_head, 1);
+        std::vector<float> gate(c.n_head);
+        for (int i = 0; i < c.n_head; ++i) gate[i] = 0.5f * (1.0f + tanhf(0.5f * data[i]));   // Tensor.sigmoid, tensor.py:824
+        VN_CUDA(ctx, cudaMemcpyAsync(S->head_gate, gate.data(), gate.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+        VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      }
+      else return vn_fail(ctx, VN_ERR_INVALID, "unexpected tensor %s", name);
+    }
     else if (rest == "attn.wq.weight") { SHAPE(qd, D); TRY(upload(m, data, L.wqkv, r, cl, D, 1, 0)); }
     else if (rest == "attn.wk.weight") { SHAPE(kvd, D); TRY(upload(m, data, L.wqkv, r, cl, D, 1, qd)); }
     else if (rest == "attn.wv.weight") { SHAPE(kvd, D); TRY(upload(m, data, L.wqkv, r, cl, D, 1, qd + kvd)); }
     else if (rest == "attn.proj.weight") { SHAPE(D, qd); TRY(upload(m, data, L.wproj, r, cl, qd)); }
     else if (rest == "attn.global_tokens.weight") { SHAPE(c.n_sink, D); TRY(upload(m, data, L.sink, r, cl, D)); }
-    else if (L.kind == 0 && rest == "ffn.w_gate.weight") { SHAPE(c.mlp_hidden, D); TRY(upload(m, data, L.w_gateup, r, cl, D, 2, 0)); }
-    else if (L.kind == 0 && rest == "ffn.w_up.weight") { SHAPE(c.mlp_hidden, D); TRY(upload(m, data, L.w_gateup, r, cl, D, 2, 1)); }
-    else if (L.kind == 0 && rest == "ffn.w_down.weight") { SHAPE(D, c.mlp_hidden); TRY(upload(m, data, L.w_down, r, cl, c.mlp_hidden)); }
+    else if (L.kind != 1 && rest == "ffn.w_gate.weight") { SHAPE(c.mlp_hidden, D); TRY(upload(m, data, L.w_gateup, r, cl, D, 2, 0)); }
+    else if (L.kind != 1 && rest == "ffn.w_up.weight") { SHAPE(c.mlp_hidden, D); TRY(upload(m, data, L.w_gateup, r, cl, D, 2, 1)); }
+    else if (L.kind != 1 && rest == "ffn.w_down.weight") { SHAPE(D, c.mlp_hidden); TRY(upload(m, data, L.w_down, r, cl, c.mlp_hidden)); }
     else if (L.kind == 1 && rest == "ffn.part_router.gate.weight") { SHAPE(c.P, D); TRY(upload(m, data, L.router, r, cl, D, 1, 0, true)); }
     else if (L.kind == 1 && rest.rfind("ffn.parts.", 0) == 0) {
       const size_t d2 = rest.find('.', 10);
@@ -1069,10 +1234,24 @@ int32_t vn_model_finalize(vn_model* m) {
   if (!c.tie || m->preq_mode) want.push_back("head.weight");   // a quantised head is its own copy (compress.py:817-822)
   for (int i = 0; i < c.n_layer; ++i) {
     const std::string p = "blocks." + std::to_string(i) + ".";
-    for (const char* s : {"norm1.weight", "norm2.weight", "attn.gate_logits", "attn.wq.weight", "attn.wk.weight",
-                          "attn.wv.weight", "attn.proj.weight", "attn.global_tokens.weight"})
-      want.push_back(p + s);
-    if (c.kind[i] == 0) {
+    for (const char* s : {"norm1.weight", "norm2.weight", "attn.proj.weight"}) want.push_back(p + s);
+    if (!is_delta(c.kind[i])) {
+      for (const char* s : {"attn.gate_logits", "attn.wq.weight", "attn.wk.weight", "attn.wv.weight",
+                            "attn.global_tokens.weight"})
+        want.push_back(p + s);
+    } else {
+      if (c.kind[i] == 2) want.push_back(p + "attn.gate_logits");
+      static const char* sub_name[3] = {"dsa", "kda", "gmla"};
+      for (const SubAttn& S : m->layers[i].sub) {
+        const std::string q = p + "attn." + (c.kind[i] == 2 ? std::string(sub_name[S.mode]) + "." : std::string());
+        want.push_back(q + "wq.weight");
+        if (S.mode == 2) for (const char* s : {"w_kv_down.weight", "w_k_up.weight", "w_v_up.weight"}) want.push_back(q + s);
+        else for (const char* s : {"wk.weight", "wv.weight"}) want.push_back(q + s);
+        if (S.mode == 0) want.push_back(q + "global_tokens.weight");
+        if (S.mode != 1) want.push_back(q + "head_gate_logits");
+      }
+    }
+    if (c.kind[i] != 1) {
       for (const char* s : {"ffn.w_gate.weight", "ffn.w_up.weight", "ffn.w_down.weight"}) want.push_back(p + s);
     } else {
       want.push_back(p + "ffn.part_router.gate.weight");
@@ -1171,6 +1350,7 @@ int32_t vn_model_quantize(vn_model* m, const char* scheme) {
   const std::string s(scheme);
   const int mode = s == "int8" ? 1 : (s == "int4" ? 2 : (s == "int4g128" ? 3 : 0));
   VN_REQUIRE(ctx, mode != 0, "unknown quantisation scheme %s (int8 | int4 | int4g128)", scheme);
+  if (m->has_delta) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "weight-only quantisation of vda / dsa / kda / gmla layers is not built");
   VN_REQUIRE(ctx, m->finalized, "quantise after vn_model_finalize");
   VN_REQUIRE(ctx, m->qmode == 0, "model is already quantised");
   if (!m->cfg.bf16) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "weight-only quantisation needs a bf16 model");
@@ -1247,6 +1427,7 @@ int32_t vn_model_load_quant_tensor(vn_model* m, const char* name, const char* sc
   const int mode = scheme_mode(scheme);
   VN_REQUIRE(ctx, mode != 0, "unknown quantisation scheme %s (int8 | int4 | int4g128)", scheme ? scheme : "(null)");
   if (!m->cfg.bf16) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised linears need a bf16 model");
+  if (m->has_delta) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised linears of vda / dsa / kda / gmla layers are not built");
   VN_REQUIRE(ctx, m->qmode == 0, "the model is already quantised");
   VN_REQUIRE(ctx, m->preq_mode == 0 || m->preq_mode == mode, "%s: one scheme per model (linears so far arrived as scheme %d)", name, m->preq_mode);
   const std::string n(name);
@@ -1417,7 +1598,7 @@ int32_t vn_kv_create(vn_model* m, int32_t max_batch, int32_t max_seq, vn_kv** ou
   kv->m = m; kv->max_batch = max_batch; kv->max_seq = max_seq;
   const size_t plane = (size_t)max_batch * max_seq * m->cfg.n_kv * m->cfg.hd * m->esz;
   std::vector<void*> planes;
-  for (int i = 0; i < m->cfg.n_layer; ++i) {
+  for (int i = 0; i < m->n_pairs; ++i) {
     void *k = nullptr, *v = nullptr;
     if (cudaMalloc(&k, plane) != cudaSuccess || cudaMalloc(&v, plane) != cudaSuccess) {
       if (k) cudaFree(k);
@@ -1465,7 +1646,7 @@ int32_t vn_kv_view(vn_kv* kv, int32_t first, int32_t count, vn_kv** out) {
   v->parent_first = kv->parent_first + first;
   const size_t seq_bytes = (size_t)kv->max_seq * m->cfg.n_kv * m->cfg.hd * m->esz;
   std::vector<void*> planes;
-  for (int i = 0; i < m->cfg.n_layer; ++i) {
+  for (int i = 0; i < m->n_pairs; ++i) {
     v->k.push_back((char*)kv->k[i] + (size_t)first * seq_bytes);
     v->v.push_back((char*)kv->v[i] + (size_t)first * seq_bytes);
     planes.push_back(v->k.back()); planes.push_back(v->v.back());
@@ -1530,7 +1711,7 @@ int32_t vn_kv_commit(vn_kv* kv, int32_t n_new, const int32_t* keep_idx_dev, int3
     const int row_elems = m->cfg.n_kv * m->cfg.hd;
     const size_t smem = (size_t)n_new * row_elems * m->esz;
     VN_REQUIRE(ctx, smem <= 200 * 1024, "tree of %d nodes too large to compact in shared memory", n_new);
-    dim3 grid(B, 2 * m->cfg.n_layer);
+    dim3 grid(B, 2 * m->n_pairs);
     if (m->cfg.bf16) {
       if (smem > 48 * 1024)
         VN_CUDA(ctx, cudaFuncSetAttribute(kv_commit_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -1553,7 +1734,7 @@ int32_t vn_kv_read(vn_kv* kv, int32_t layer, int32_t seq, int32_t which, float* 
   vn_model* m = kv->m;
   vn_ctx* ctx = m->ctx;
   VN_CHECK_CTX(ctx);
-  if (layer < 0 || layer >= m->cfg.n_layer) return vn_fail(ctx, VN_ERR_INDEX, "layer %d out of range (%d)", layer, m->cfg.n_layer);
+  if (layer < 0 || layer >= m->n_pairs) return vn_fail(ctx, VN_ERR_INDEX, "layer %d out of range (%d)", layer, m->n_pairs);
   if (seq < 0 || seq >= kv->max_batch) return vn_fail(ctx, VN_ERR_INDEX, "sequence %d out of range (%d)", seq, kv->max_batch);
   VN_REQUIRE(ctx, n_positions >= 0 && n_positions <= kv->max_seq, "n_positions out of range");
   const size_t row = (size_t)m->cfg.n_kv * m->cfg.hd, n = row * n_positions;
@@ -1624,7 +1805,7 @@ int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
     }
   }
   TRY(ensure_rows(m, B * T));
-  if (m->cfg.bf16 && m->use_tc && B * T <= 256 && m->cfg.dim % 8 == 0 && m->cfg.dim <= 2048 &&
+  if (m->cfg.bf16 && m->use_tc && !m->has_delta && B * T <= 256 && m->cfg.dim % 8 == 0 && m->cfg.dim <= 2048 &&
       tc_detail::encode_fn() != nullptr)
     return forward_tc(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
   if (m->cfg.bf16) return forward_t<__nv_bfloat16>(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);

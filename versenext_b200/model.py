@@ -9,6 +9,9 @@ Differences that the device path brings (all additive):
   * `dtype="f32" | "bf16"` selects the storage type of weights, GEMM inputs
     and the KV cache (accumulation, residual stream, softmax and logits stay
     float32);
+  * layers of the delta attention kinds ("vda", "dsa", "kda", "gmla", verse_nex/delta_attention.py) compute the
+    whole-sequence forward of those classes on the cache (masks from absolute positions; a GMLA module caches the
+    K / V rebuilt from its latents); weight-only quantisation of such layers is not available;
   * `new_cache()` returns a `KVCache`; `forward_cached` runs T new positions
     (a chain, or a tree given `parents`) on top of it, which is what
     `SpeculativeDecoder.verify` re-computes from scratch in the reference
@@ -28,7 +31,19 @@ import numpy as np
 from . import sampling
 from .device import Context, DeviceArray, as_device
 
-VALID_KINDS = ("trisparse", "mod")
+VALID_KINDS = ("trisparse", "mod", "vda", "dsa", "kda", "gmla")      # VerseNexBlock.VALID_KINDS, cometspark.py:110
+
+
+def build_verse_delta_pattern(n_layer: int) -> List[str]:
+    """Layer kinds of the delta architecture (verse_nex/delta_attention.py:1218-1247): fewer than 6 layers all
+    "vda"; up to 9 four "vda" then "gmla"; from 10 on four "vda", "gmla" in between, two "dsa" at the end."""
+    if n_layer < 1:
+        raise ValueError(f"n_layer must be >= 1, got {n_layer}")
+    if n_layer < 6:
+        return ["vda"] * n_layer
+    if n_layer < 10:
+        return ["vda"] * 4 + ["gmla"] * (n_layer - 4)
+    return ["vda"] * 4 + ["gmla"] * (n_layer - 6) + ["dsa"] * 2
 
 
 def _ptr(a):
@@ -122,7 +137,8 @@ class KVCache:
         self.ctx._check(self.ctx.lib.vn_kv_commit(self.handle, int(n_new), _ptr(ki), stride, _ptr(nk), int(keep_add)))
 
     def get(self, layer_idx: int, seq_idx: int = 0, n_positions: Optional[int] = None):
-        """(k, v) float32 ndarrays of shape (n_positions, n_kv_head, head_dim) for one sequence."""
+        """(k, v) float32 ndarrays of shape (n_positions, n_kv_head, head_dim) for one sequence.  `layer_idx` counts
+        K / V plane pairs: one per layer, three (dsa, kda, gmla) for a "vda" layer."""
         if n_positions is None:
             n_positions = int(self.per_seq_lens[seq_idx])
         m = self.model
@@ -168,6 +184,10 @@ class VerseNexLM:
         self.tie_weights = bool(tie_weights)
         self.max_seq_len = int(max_seq_len)
         self.window_size = int(window_size)
+        self.anchor_interval = int(anchor_interval)
+        self.latent_dim = None if latent_dim is None else int(latent_dim)
+        if self.anchor_interval < 1:
+            raise ValueError(f"anchor_interval must be >= 1, got {anchor_interval}")
         self.use_rope, self.use_alibi = bool(use_rope), bool(use_alibi)
         self.rope_theta = float(rope_theta)
         self.embedding_scale = bool(embedding_scale)
@@ -175,7 +195,8 @@ class VerseNexLM:
         self.aux_loss_weight = aux_loss_weight
         self._config = dict(vocab_size=self.vocab_size, dim=self.dim, n_layer=self.n_layer, n_head=self.n_head,
                             n_kv_head=self.n_kv_head, layer_pattern=self.layer_pattern, window_size=int(window_size),
-                            num_global_tokens=int(num_global_tokens), use_alibi=self.use_alibi, use_rope=self.use_rope,
+                            num_global_tokens=int(num_global_tokens), anchor_interval=self.anchor_interval,
+                            latent_dim=self.latent_dim, use_alibi=self.use_alibi, use_rope=self.use_rope,
                             max_seq_len=self.max_seq_len, rope_theta=self.rope_theta,
                             num_dense_parts=int(num_dense_parts), num_experts_per_part=int(num_experts_per_part),
                             top_k=int(top_k), expert_hidden=expert_hidden, tie_weights=self.tie_weights,

@@ -47,12 +47,34 @@ def _shapes(kw: dict) -> Iterator[Tuple[str, tuple]]:
         p = f"blocks.{i}."
         yield p + "norm1.weight", (D,)
         yield p + "norm2.weight", (D,)
-        yield p + "attn.gate_logits", (3,)
-        yield p + "attn.wq.weight", (H * hd, D)
-        yield p + "attn.wk.weight", (n_kv * hd, D)
-        yield p + "attn.wv.weight", (n_kv * hd, D)
-        yield p + "attn.proj.weight", (D, H * hd)
-        yield p + "attn.global_tokens.weight", (kw.get("num_global_tokens", 64), D)
+        n_g = kw.get("num_global_tokens", 64)
+        if kind in ("vda", "dsa", "kda", "gmla"):
+            # the modules of verse_nex/delta_attention.py: a vda layer holds one of each under its own prefix
+            lat = kw.get("latent_dim") or n_kv * hd
+            for sub in (("dsa", "kda", "gmla") if kind == "vda" else (kind,)):
+                q = p + "attn." + (sub + "." if kind == "vda" else "")
+                yield q + "wq.weight", (H * hd, D)
+                if sub == "gmla":
+                    yield q + "w_kv_down.weight", (lat, D)
+                    yield q + "w_k_up.weight", (n_kv * hd, lat)
+                    yield q + "w_v_up.weight", (n_kv * hd, lat)
+                else:
+                    yield q + "wk.weight", (n_kv * hd, D)
+                    yield q + "wv.weight", (n_kv * hd, D)
+                if sub == "dsa":
+                    yield q + "global_tokens.weight", (n_g, D)
+                if sub != "kda":
+                    yield q + "head_gate_logits", (H,)
+            if kind == "vda":
+                yield p + "attn.gate_logits", (3,)
+            yield p + "attn.proj.weight", (D, H * hd)
+        else:
+            yield p + "attn.gate_logits", (3,)
+            yield p + "attn.wq.weight", (H * hd, D)
+            yield p + "attn.wk.weight", (n_kv * hd, D)
+            yield p + "attn.wv.weight", (n_kv * hd, D)
+            yield p + "attn.proj.weight", (D, H * hd)
+            yield p + "attn.global_tokens.weight", (n_g, D)
         if kind == "mod":
             yield p + "ffn.part_router.gate.weight", (P, D)
             for q in range(P):
