@@ -824,6 +824,140 @@ def cpu_small_run():
     return 128 / dt, dt, st
 
 
+DELTA_WORKLOAD = ("delta: the shipped mate preset with delta attention (D=1024, L=32: 4 vda + 26 gmla + 2 dsa, all SwiGLU, "
+                  "16 heads / 8 KV heads, window 1024, 128 sinks, anchor 128, V=248320, bf16) + 2-layer D=256 draft, "
+                  "k=4, T=0.8, top-k 50, 32 requests of 512-token prompts")
+
+
+def delta_kwargs():
+    """Constructor arguments of the shipped mate preset (spark/mate/config/cometspark_mate.yml: use_vda, 32 layers,
+    layer kinds from build_verse_delta_pattern)."""
+    import versenext_b200 as vn
+    from versenext_b200 import synthetic as S
+    return S.mate_kwargs(n_layer=32, layer_pattern=vn.build_verse_delta_pattern(32), anchor_interval=128)
+
+
+def cpu_delta_sample(max_seconds=25.0, rounds=2, warmup=1):
+    """The delta workload on the host (NumPy restatement): one request, full re-forward every round."""
+    from oracle import model as OM
+    from oracle import spec as OS
+    from versenext_b200 import synthetic as S
+    tk, dk = delta_kwargs(), S.draft_kwargs()
+    t_cfg = OM.Config(**tk)
+    d_cfg = OM.Config(**dk)
+    t_sd = dict(S.random_tensors(tk, seed=0))
+    t_sd["head.weight"] = t_sd["tok_emb.weight"]
+    d_sd = dict(S.random_tensors(dk, seed=1))
+    d_sd["head.weight"] = d_sd["tok_emb.weight"]
+    seq = spec_prompts(1, SPEC["prompt"], SPEC["seed"])
+    t0, done, committed = None, 0, 0
+    for i in range(warmup + rounds):
+        if i == warmup:
+            t0 = time.perf_counter()
+        if t0 is not None and time.perf_counter() - t0 > max_seconds:
+            break
+        st = OS.generate(t_sd, t_cfg, d_sd, d_cfg, seq, SPEC["k"], 10 ** 6, temperature=SPEC["temperature"],
+                         top_k=SPEC["top_k"], seed=SPEC["seed"], bonus=True, max_rounds=1)
+        new_seq = st["tokens"][0]
+        if i >= warmup:
+            committed += new_seq.shape[1] - seq.shape[1]
+            done += 1
+        seq = new_seq
+    dt = time.perf_counter() - t0
+    return committed / dt, dt, done
+
+
+def run_delta(args):
+    """The speculative round with a target made of delta attention layers (one GPU, or replicas)."""
+    import versenext_b200 as vn
+    from versenext_b200 import synthetic as S
+    world, rank, local, dist = dist_setup(args.gpus)
+    ctx = vn.Context.get(local)
+    k, T0, B = SPEC["k"], SPEC["prompt"], SPEC["B"]
+    tk, dk = delta_kwargs(), S.draft_kwargs()
+    target = vn.VerseNexLM(dtype="bf16", device=f"cuda:{local}", **tk)
+    S.load_random(target, tk, seed=0)
+    draft = vn.VerseNexLM(dtype="bf16", device=f"cuda:{local}", **dk)
+    S.load_random(draft, dk, seed=1)
+    warm = max(args.warmup, 3)
+    eng = _spec_engine(vn, target, draft, B, args, warm)
+    ctx.sync()
+    t_pre = time.perf_counter()
+    eng.prefill(spec_prompts(B, T0, SPEC["seed"], rank))
+    ctx.sync()
+    t_pre = time.perf_counter() - t_pre
+    for _ in range(warm):
+        eng.step()
+    clocks = ClockSampler(local).start() if rank == 0 else None
+    l0 = ctx.launch_count()
+    reps, committed_rank = _time_engine(eng, ctx, dist, local, args.steps, warm)
+    launches = (ctx.launch_count() - l0) // len(reps) * args.steps // (args.steps + warm)
+    clk = clocks.stop() if clocks else None
+    ms = statistics.median(reps)
+    value = _sum_over_ranks(dist, committed_rank, local) / (ms * 1e-3)
+    ctx_len = int(eng.t_cache.per_seq_lens.mean())
+    # verify + sample step as a replayed graph, then per-kernel shares with events around every launch
+    n_prof = min(args.steps, 16)
+    eng.rewind()
+    for _ in range(warm):
+        eng.step()
+    lens0 = eng.t_cache.per_seq_lens.copy()
+    eng.verify_accept_only(graph=False)
+    eng.verify_accept_only(graph=True)
+    v_reps = []
+    for _ in range(5):
+        eng.t_cache.set_lengths(lens0)
+        eng._len_bound = int(lens0.max())
+        v0, v1 = ctx.event(), ctx.event()
+        v0.record()
+        for _ in range(n_prof):
+            eng.verify_accept_only(graph=True)
+        v1.record()
+        v_reps.append(v0.elapsed_ms(v1) / n_prof)
+    eng.t_cache.set_lengths(lens0)
+    eng._len_bound = int(lens0.max())
+    step_ms = statistics.median(v_reps)
+    ctx.profile(True)
+    for _ in range(n_prof):
+        eng.verify_accept_only()
+    rep = ctx.profile_report()
+    ctx.profile(False)
+    prof_ms = max(sum(v["ms"] for v in rep.values()) / n_prof, 1e-9)
+    # algorithmic bytes: every target weight once + the K / V every module has to read (a module of a context of at
+    # most 1024 keys reads all of it; 40 modules: 3 per vda layer, 1 per gmla / dsa layer; 2 x 512 values per key)
+    params = S.param_count(tk)
+    n_mod = sum(3 if kind == "vda" else 1 for kind in tk["layer_pattern"])
+    nbytes = params * 2 + n_mod * B * min(ctx_len, 1024) * 2 * 512 * 2
+    peak, peak_kind = peaks()
+    achieved = nbytes / (step_ms * 1e-3) / 1e9
+    top = sorted(rep.items(), key=lambda kv: -kv[1]["ms"])
+    roofline = {"bound": "hbm", "kernel": "verify+sample step (all kernels of the target forward and acceptance)",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                "traffic": None, "step_ms": step_ms, "step_ms_repeats": v_reps, "algorithmic_bytes": nbytes,
+                "kernel_share": {n: v["ms"] / n_prof / prof_ms for n, v in top},
+                "kernel_ms_per_step": {n: v["ms"] / n_prof for n, v in top},
+                "kernel_launches_per_step": {n: v["launches"] / n_prof for n, v in top}}
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        tps, secs, rounds = cpu_delta_sample()
+        cpu = {"value": tps, "unit": "tok/s", "cores": blas_threads(), "kind": "port",
+               "sample": f"1 of 32 requests, {rounds} rounds ({secs:.1f} s), full re-forward per round as the "
+                         f"reference does; NumPy restatement (oracle/), fp32, {blas_threads()} BLAS threads"}
+    if rank == 0:
+        print(json.dumps({
+            "metric": "accepted tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": DELTA_WORKLOAD, "requests": B, "l2": "weights (2.7 GB) larger than L2, no flush",
+                       "step": "one speculative round over the batch"},
+            "timing": spread(reps, args.steps), "context_tokens": ctx_len, "target_params": params,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": None, "gpu_launches": launches, "clocks": clk,
+            "accept_rate": float(eng.accept_len.numpy().mean() / k), "prefill_s": t_pre,
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_layer(args):
     """One MoD + one TriSparse layer of the mate shapes (D=1024, 16 heads / 8 KV heads, window 1024, 128 sinks) with a
     small vocabulary: the per-layer kernels of the verify step on a case small enough for a full ncu capture
@@ -1079,7 +1213,7 @@ def main():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="spec", choices=["spec", "accept", "sharded", "tree", "small", "layer"])
+    ap.add_argument("--workload", default="spec", choices=["spec", "accept", "sharded", "tree", "small", "layer", "delta"])
     ap.add_argument("--weak", action="store_true",
                     help="spec workload: 32 requests on every rank (default: the configuration's 32 split over the ranks)")
     ap.add_argument("--no-weak", action="store_true", help="N > 1: skip the extra 32-per-GPU measurement")
@@ -1093,7 +1227,7 @@ def main():
         {"accept": run_reference, "small": run_reference_small}.get(args.workload, run_reference_spec)(args)
     else:
         {"spec": run_spec, "accept": run_accept, "sharded": run_sharded, "tree": run_tree,
-         "small": run_small, "layer": run_layer}[args.workload](args)
+         "small": run_small, "layer": run_layer, "delta": run_delta}[args.workload](args)
 
 
 if __name__ == "__main__":

@@ -133,3 +133,79 @@ def test_delta_layers_bf16_head_dim_64_with_a_long_prompt():
     assert rel_err(l1, want[:, :160]) < 2e-2
     assert rel_err(l2, want[:, 160:]) < 2e-2
     m.check()
+
+
+def hd64_delta_cfg(**over):
+    kw = dict(vocab_size=128, dim=128, n_layer=4, n_head=2, n_kv_head=1, layer_pattern=["vda", "kda", "gmla", "dsa"],
+              window_size=48, num_global_tokens=5, anchor_interval=40, latent_dim=32, use_alibi=False, use_rope=True,
+              max_seq_len=2048, init_std=0.08)
+    kw.update(over)
+    return OM.Config(**kw)
+
+
+def test_delta_tensor_core_routes_around_the_1024_key_switch():
+    """bf16, head_dim 64: the modules run on the tensor-core attention kernel and (up to 256 rows) on the split-K
+    tcgen05 GEMMs.  1100-token prompt (every class beyond its switch), a chain that crosses the switch on top of 1020
+    cached keys, a tree whose nodes lie on both sides of it, and the same steps on the SIMT kernels
+    (VN_ATTN_SIMT=1 at model creation) -- all against the oracle on the bf16-rounded weights."""
+    import os
+    cfg = hd64_delta_cfg()
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=61, gate_std=1.0).items()}
+    rng = np.random.default_rng(7)
+    toks = rng.integers(0, cfg.vocab_size, (1, 1100))
+    # the oracle takes the prompt in the same pieces (a piece is on one side of the switch as a whole: the first four end
+    # at or before 1024 keys, the last one beyond)
+    want_pieces, oc = [], None
+    for lo in range(0, 1100, 220):
+        lg, oc = OM.forward(sd, cfg, toks[:, lo:lo + 220], cache=oc)
+        want_pieces.append(lg)
+    _, oc = OM.forward(sd, cfg, toks[:, :1020])
+    want_chain = OM.forward(sd, cfg, toks[:, 1020:1030], cache=oc)[0]
+    parents = [-1, -1, 0, 0, 1, 2, 2, 5, 7, 8]          # depths 0..5: positions 1020..1025, key counts 1021..1026
+    nodes = rng.integers(0, cfg.vocab_size, (1, len(parents)))
+    want_tree = OM.forward(sd, cfg, nodes, cache=oc, parents=parents)[0]
+    for simt in ("0", "1"):
+        os.environ["VN_ATTN_SIMT"] = simt
+        try:
+            m = build(cfg, sd, "bf16")
+        finally:
+            os.environ.pop("VN_ATTN_SIMT", None)
+        cache = m.new_cache(1, 1200)
+        for i, lo in enumerate(range(0, 1100, 220)):
+            got = m.forward_cached(toks[:, lo:lo + 220], cache).numpy()
+            cache.commit(220, np.full(1, 220, np.int32))
+            assert rel_err(got, want_pieces[i]) < 2e-2, (simt, i)
+        cache.reset()
+        for lo in range(0, 1020, 255):
+            m.forward_cached(toks[:, lo:lo + 255], cache, last_only=True)
+            cache.commit(255, np.full(1, 255, np.int32))
+        assert rel_err(m.forward_cached(toks[:, 1020:1030], cache).numpy(), want_chain) < 2e-2, simt
+        assert rel_err(m.forward_cached(nodes, cache, parents=parents).numpy(), want_tree) < 2e-2, simt
+        m.check()
+
+
+def test_delta_and_trisparse_layers_in_one_model_bf16():
+    """A model that mixes TriSparse, MoD and delta layers (the plane pairs of the cache are then not one per layer),
+    batch 4: decode rows on the tcgen05 route against the oracle, and the engine's greedy stream against generate."""
+    import versenext_b200 as vn
+    # (every expert of a part is selected, top_k = E: the routed output is then continuous in the activations, and bf16
+    # rounding cannot flip a choice between two experts with nearly equal router logits)
+    cfg = hd64_delta_cfg(layer_pattern=["trisparse", "vda", "mod", "gmla"], num_dense_parts=2, num_experts_per_part=2,
+                         top_k=2, window_size=16, anchor_interval=8)
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=71, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    rng = np.random.default_rng(9)
+    toks = rng.integers(0, cfg.vocab_size, (4, 45))
+    want = OM.forward(sd, cfg, toks)[0]
+    cache = m.new_cache(4, 128)
+    l1 = m.forward_cached(toks[:, :40], cache).numpy()
+    cache.commit(40, np.full(4, 40, np.int32))
+    l2 = m.forward_cached(toks[:, 40:], cache).numpy()
+    assert rel_err(l1, want[:, :40]) < 2e-2
+    assert rel_err(l2, want[:, 40:]) < 2e-2
+    d_cfg = hd64_delta_cfg(n_layer=1, layer_pattern=["kda"])
+    d = build(d_cfg, {n: OM.bf16_round(v) for n, v in OM.init_state_dict(d_cfg, seed=72, gate_std=1.0).items()}, "bf16")
+    plain = m.generate(toks[:2, :12], max_new_tokens=20, temperature=0.0)
+    spec = m.generate(toks[:2, :12], max_new_tokens=20, temperature=0.0, draft=d, k=3)
+    np.testing.assert_array_equal(spec, plain)
+    m.check()

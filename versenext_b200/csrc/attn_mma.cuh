@@ -37,6 +37,7 @@ __device__ __forceinline__ long long clock_stamp() {
 
 struct RowInfo {
   bool valid;
+  bool long_row;   // delta modules: this row's key count is beyond alibi_max
   int tq, pos;
   float slope;
   unsigned long long anc;
@@ -98,7 +99,7 @@ __device__ __forceinline__ void attend_block(const AttnArgs& a, const unsigned c
         const RowInfo& r = row[e >> 1];
         bool vis = r.valid && key < hi;
         float sc = c[i][e] * a.scale;
-        if (MODE == 0 || MODE == 2) {
+        if (MODE == 0 || MODE == 2 || MODE == 3) {
           int kpos = key;
           if (key >= len) {
             const int n = key - len;
@@ -106,9 +107,21 @@ __device__ __forceinline__ void attend_block(const AttnArgs& a, const unsigned c
             vis = vis && (a.anc ? ((r.anc >> n) & 1ull) != 0 : n <= r.tq) && kpos <= r.pos;
           }
           if (MODE == 0) vis = vis && (r.pos - kpos) < a.window;
-          else {
+          else if (MODE == 2) {
             sc -= r.slope * (float)(r.pos - kpos);
             if (a.alibi_window > 0) vis = vis && (r.pos - kpos) < a.alibi_window;
+          } else {
+            // KDA: the window and every anchor key in one soft-max (delta_attention.py:678-698).  Beyond alibi_max
+            // keys the reference scores the window slice of the query's chunk and all anchors, concatenated
+            // (:704-768): an anchor inside the slice [k_lo, ..] counts twice, i.e. its score gains ln 2.
+            const bool in_win = (r.pos - kpos) < a.window, anch = (kpos % a.anchor) == 0;
+            if (!r.long_row) vis = vis && (in_win || anch);
+            else {
+              const int k_lo = max(0, (r.pos / a.window) * a.window - a.window + 1);
+              const int mult = ((in_win || (anch && kpos >= k_lo)) ? 1 : 0) + (anch ? 1 : 0);
+              vis = vis && mult > 0;
+              if (mult == 2) sc += 0.6931471806f;
+            }
           }
         }
         c[i][e] = vis ? sc : -CUDART_INF_F;
@@ -151,7 +164,8 @@ __device__ __forceinline__ void attend_block(const AttnArgs& a, const unsigned c
   }
 }
 
-// mode 0: window path (cached keys within the window, appended keys by ancestry), 1: sinks, 2: ALiBi path
+// mode 0: window path (cached keys within the window, appended keys by ancestry), 1: sinks, 2: ALiBi path (with a
+// zero slope: plain causal attention), 3: all keys under the KDA window | anchor mask
 template <int MODE>
 __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* __restrict__ Kb,
                                        const __nv_bfloat16* __restrict__ Vb, long long ks, int lo, int hi, int len,
@@ -251,8 +265,9 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
     row[h].tq = rr % a.Tn;
     const int hrep = rr / a.Tn;
     row[h].pos = len + (depth ? depth[row[h].tq] : row[h].tq);
-    row[h].slope = 1.0f / exp2f((float)(kvh * n_rep + hrep + 1) / (float)a.H);
+    row[h].slope = a.delta ? 0.f : 1.0f / exp2f((float)(kvh * n_rep + hrep + 1) / (float)a.H);
     row[h].anc = a.anc ? a.anc[row[h].tq] : 0ull;
+    row[h].long_row = (a.anc ? row[h].pos + 1 : len + a.Tn) > a.alibi_max;
   }
   // tile-wide key range (all threads compute the same numbers from the tile's rows)
   for (int r = tile0; r < tile0 + 16 && r < R; ++r) {
@@ -273,8 +288,14 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   const int lo_w = max(0, pos_min - a.window + 1);
   const int nblk_w = hi_new > lo_w ? (hi_new - lo_w + 15) >> 4 : 0;
   const int nblk_s = (a.n_sink + 15) >> 4;
+  // which passes this tile runs: TriSparse and DSA take the window and the sinks; GMLA takes the window only for rows
+  // beyond alibi_max keys (a chain is all on one side of the switch, a tree may straddle it); KDA has one pass
+  const bool some_long = len + a.Tn > a.alibi_max;
+  const bool need_ab = a.delta == 0 || a.delta == 1 || (a.delta == 3 && some_long);
+  const bool need_b = a.delta == 0 || a.delta == 1;
   int nw = 1;
-  {
+  if (!need_b) nw = AW;
+  else {
     int best = 1 << 30;
     for (int c = 1; c < AW; ++c) {           // the split whose busier group has the fewest blocks per warp
       const int cost = max((nblk_w + c - 1) / c, (nblk_s + AW - c - 1) / (AW - c));
@@ -285,8 +306,8 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   // This warp's first key blocks go on their way now, under the set-up work below: cached window keys and sink keys
   // do not depend on this call's q | k | v.  A window warp whose first blocks reach into the rows that this very
   // CTA appends below has to wait for them.
-  bool early = true;
-  if (warp < nw) {
+  bool early = need_ab;
+  if (need_ab && warp < nw) {
     const int last = warp + (RING - 2) * nw;                 // its last block of the first batch
     early = lo_w + (min(last, max(nblk_w - 1, 0)) + 1) * 16 <= len;
   }
@@ -391,8 +412,27 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   // final output of this thread after the cross-warp merge: row = tid / 16, dims 4 * (tid % 16) .. +3
   float fin[4] = {0.f, 0.f, 0.f, 0.f};
   const int mrow = tid >> 4, mcol = (tid & 15) * 4;
-  const bool use_c = a.use_alibi &&
-                     (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max);
+  const bool use_c = a.delta == 2 ||
+                     (a.use_alibi &&
+                      (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max));
+  // weight of a pass's result in this thread's output row: the sigmoid gates of TriSparse, or the delta module's
+  // per-head weights on the row's side of the alibi_max switch (path 0 window, 1 sinks, 2 dense / KDA)
+  auto gate_of = [&](int path) -> float {
+    const int r = tile0 + mrow;
+    const int rr = r < R ? r : 0;
+    const int tq = rr % a.Tn, head = kvh * n_rep + rr / a.Tn;
+    const int tk = a.anc ? len + (depth ? depth[tq] : tq) + 1 : len + a.Tn;
+    if (!a.delta) {
+      if (path == 0) return a.g_a;
+      if (path == 1) return a.g_b;
+      // ALiBi path of a tree node is gated by its own T_k (position + 1 <= 1024)
+      if (a.anc && (a.alibi_window > 0 ? min(tk, a.alibi_window) : tk) > a.alibi_max) return 0.f;
+      return a.g_c;
+    }
+    const bool long_row = tk > a.alibi_max;
+    if (path == 2) return (long_row && a.delta != 2) ? 0.f : a.out_w * a.head_w[2 * a.H + head];
+    return a.out_w * a.head_w[((long_row ? 3 : 0) + path) * a.H + head];
+  };
 
   // each warp parks its partial result.  Column n of tile j is output dim 8n + j, so thread (g, t) holds dims
   // 16t .. 16t+15 of rows g and g + 8: four 16-byte chunks per row, chunk c stored at c ^ bit3(c) ^ 2*(row & 1),
@@ -439,42 +479,42 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
 
   if (tr && tid == 0) tr[1] = clock_stamp();     // row setup and Q fragments done
   // ---- window path and sink path side by side
-  {
+  if (need_ab) {
     float o[8][4], m[2], l[2];
     if (warp < nw) attend<0>(a, Kc, Vc, ks, lo_w, hi_new, len, row, qf, depth, warp, nw, lane, ring, o, m, l, early ? 2 : 0);
     else attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf, depth, warp - nw, AW - nw, lane, ring, o, m, l, early ? 2 : 0);
     if (tr && tid == 0) tr[2] = clock_stamp();   // this warp's keys done
     park(o, m, l);
     __syncthreads();
-    merge(0, nw, a.g_a);
-    merge(nw, AW, a.g_b);
+    merge(0, nw, gate_of(0));
+    merge(nw, AW, gate_of(1));
     if (tr && tid == 0) tr[3] = clock_stamp();   // merge done
   }
   if (use_c) {
     __syncthreads();                             // everybody has read the parked tiles
     float o[8][4], m[2], l[2];
     const int lo_c = a.alibi_window > 0 ? max(0, pos_min - a.alibi_window + 1) : 0;
-    attend<2>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, AW, lane, ring, o, m, l);
+    if (a.delta == 2) attend<3>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, AW, lane, ring, o, m, l);
+    else attend<2>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, AW, lane, ring, o, m, l);
     park(o, m, l);
     __syncthreads();
-    // ALiBi path of a tree node is gated by its own T_k (position + 1 <= 1024)
-    float gate = a.g_c;
-    if (a.anc) {
-      const int r = tile0 + mrow;
-      const int tq = r < R ? r % a.Tn : 0;
-      const int tk = len + (depth ? depth[tq] : tq) + 1;
-      if ((a.alibi_window > 0 ? min(tk, a.alibi_window) : tk) > a.alibi_max) gate = 0.f;
-    }
-    merge(0, AW, gate);
+    merge(0, AW, gate_of(2));
   }
   const int r = tile0 + mrow;
   if (r < R) {
     const int tq = r % a.Tn, hrep = r / a.Tn;
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out) + (long long)(b * a.Tn + tq) * a.H * 64 +
-                         (kvh * n_rep + hrep) * 64 + mcol;
-    __nv_bfloat162 v0 = __floats2bfloat162_rn(fin[0], fin[1]), v1 = __floats2bfloat162_rn(fin[2], fin[3]);
-    reinterpret_cast<__nv_bfloat162*>(out)[0] = v0;
-    reinterpret_cast<__nv_bfloat162*>(out)[1] = v1;
+    const long long at = (long long)(b * a.Tn + tq) * a.H * 64 + (kvh * n_rep + hrep) * 64 + mcol;
+    if (a.acc_in) {
+      const float4 p = *reinterpret_cast<const float4*>(a.acc_in + at);
+      fin[0] += p.x; fin[1] += p.y; fin[2] += p.z; fin[3] += p.w;
+    }
+    if (a.acc_out) *reinterpret_cast<float4*>(a.acc_out + at) = make_float4(fin[0], fin[1], fin[2], fin[3]);
+    if (a.out) {
+      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out) + at;
+      __nv_bfloat162 v0 = __floats2bfloat162_rn(fin[0], fin[1]), v1 = __floats2bfloat162_rn(fin[2], fin[3]);
+      reinterpret_cast<__nv_bfloat162*>(out)[0] = v0;
+      reinterpret_cast<__nv_bfloat162*>(out)[1] = v1;
+    }
   }
 }
 
@@ -513,6 +553,7 @@ __global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_prefill_kernel(Attn
     row[h].pos = len + row[h].tq;
     row[h].slope = 0.f;
     row[h].anc = 0ull;
+    row[h].long_row = false;
   }
   const int pos_min = len + tq_min, pos_max = len + tq_max;
   const int P0 = blockIdx.y * pb_per_cta * 16, P1 = min(a.Tn, P0 + pb_per_cta * 16);

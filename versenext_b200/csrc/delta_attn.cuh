@@ -207,3 +207,66 @@ __global__ void __launch_bounds__(256) delta_attn_kernel(DeltaArgs a) {
     }
   }
 }
+
+// ---- GMLA projections on the split-K GEMM: the reductions between the GEMMs ------------------------------------
+// One CTA per new position sums the partial slices of its row (as qkv_finalize_kernel does).
+// stage 1: the row is [q (H hd) | latent (lat)] of the stacked wq | w_kv_down product: q is rotated and written to the
+//          fp32 q buffer (row stride ld_q), the latent goes to lat_out in the storage dtype (the next GEMM's operand).
+// stage 2: the row is [k (n_kv hd) | v (n_kv hd)] rebuilt from the latent: k is rotated, both go to the cache.
+template <typename T>
+__global__ void __launch_bounds__(256) gmla_finalize_kernel(const float* __restrict__ partial, int splits, long long pstride,
+                                                            int ld, int stage, float* __restrict__ q_out, int ld_q,
+                                                            T* __restrict__ lat_out, int lat,
+                                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                            const int* __restrict__ lens, const int* __restrict__ depth,
+                                                            T* __restrict__ kc, T* __restrict__ vc, int Tn, int H, int n_kv,
+                                                            int hd, int max_seq, int use_rope, int rope_rows, int slot_offset) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ float s_row[];   // ld floats
+  const int row = blockIdx.x, b = row / Tn, t = row % Tn;
+  for (int i = threadIdx.x * 4; i < ld; i += blockDim.x * 4) {
+    const float* p = partial + (long long)row * ld + i;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(p + (long long)s * pstride);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(s_row + i) = acc;
+  }
+  __syncthreads();
+  const int len = lens[b] + slot_offset;
+  const int pos = len + (depth ? depth[t] : t);
+  const int slot = len + t;
+  const int half = hd / 2;
+  const int p = pos < rope_rows ? pos : rope_rows - 1;
+  const int heads = stage == 1 ? H : n_kv;
+  for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+    const int head = i / half, j = i % half;
+    const float x1 = s_row[head * hd + j], x2 = s_row[head * hd + half + j];
+    float o1 = x1, o2 = x2;
+    if (use_rope) {
+      const float c = cos_t[(long long)p * half + j], s = sin_t[(long long)p * half + j];
+      o1 = x1 * c + (-x2) * s;
+      o2 = x2 * c + x1 * s;
+    }
+    if (stage == 1) {
+      float* r = q_out + (long long)row * ld_q + head * hd;
+      r[j] = o1;
+      r[half + j] = o2;
+    } else if (slot < max_seq) {
+      T* dst = kc + (((long long)b * max_seq + slot) * n_kv + head) * hd;
+      dst[j] = from_f<T>(o1);
+      dst[half + j] = from_f<T>(o2);
+    }
+  }
+  if (stage == 1) {
+    const float* l = s_row + H * hd;
+    for (int i = threadIdx.x; i < lat; i += blockDim.x) lat_out[(long long)row * lat + i] = from_f<T>(l[i]);
+  } else if (slot < max_seq) {
+    const float* v = s_row + n_kv * hd;
+    T* dst = vc + ((long long)b * max_seq + slot) * n_kv * hd;
+    for (int i = threadIdx.x; i < n_kv * hd; i += blockDim.x) dst[i] = from_f<T>(v[i]);
+  }
+}

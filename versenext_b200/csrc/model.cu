@@ -87,13 +87,15 @@ bool json_str_list(const std::string& s, const char* key, std::vector<std::strin
 // has one, a vda layer one of each
 struct SubAttn {
   int mode = 0;              // 0 dsa, 1 kda, 2 gmla
-  void* wqkv = nullptr;      // dsa, kda: [(H + 2 n_kv) hd, D] (q | k | v); gmla: [H hd, D] (q)
-  void* w_down = nullptr;    // gmla: [latent, D]              w_kv_down
+  void* wqkv = nullptr;      // dsa, kda: [(H + 2 n_kv) hd, D] (q | k | v); gmla: [H hd + latent, D] (wq | w_kv_down)
+  void* w_down = nullptr;    // gmla: the w_kv_down rows of wqkv (not a buffer of its own)
   void* w_up = nullptr;      // gmla: [2 n_kv hd, latent]      w_k_up | w_v_up
   void* sink = nullptr;      // dsa: [n_sink, D] global_tokens.weight, and its K / V (finalize)
   void* sink_k = nullptr;
   void* sink_v = nullptr;
   float* head_gate = nullptr;  // dsa, gmla: device [H] sigmoid(head_gate_logits)
+  std::vector<float> gate_host;  // the same on the host
+  float* head_w = nullptr;     // device [5][H]: per-head weights of the tensor-core kernel's passes (finalize)
   int pair = 0;              // which K / V plane pair of the cache is this module's
 };
 
@@ -178,6 +180,8 @@ struct vn_model {
 
 struct vn_kv {
   vn_model* m = nullptr;
+  vn_ctx* ctx = nullptr;     // the model's context, kept here so that destroying the cache never reads the model (which a
+                             // garbage collector may have destroyed first)
   int max_batch = 0, max_seq = 0;
   std::vector<void*> k, v;   // per layer [max_batch, max_seq, n_kv, hd]
   void** planes_dev = nullptr;  // [2 * n_layer] device array of plane pointers (k0, v0, k1, v1, ...)
@@ -258,8 +262,8 @@ int32_t alloc_weights(vn_model* m) {
         S.mode = modes[first + si];
         S.pair = m->n_pairs++;
         if (S.mode == 2) {
-          TRY(A(&S.wqkv, qd * D * e));
-          TRY(A(&S.w_down, lat * D * e));
+          TRY(A(&S.wqkv, (qd + lat) * D * e));
+          S.w_down = (char*)S.wqkv + qd * D * e;
           TRY(A(&S.w_up, 2 * kvd * lat * e));
         } else {
           TRY(A(&S.wqkv, qkv_rows * D * e));
@@ -270,6 +274,7 @@ int32_t alloc_weights(vn_model* m) {
           TRY(dev_alloc(ctx, &S.sink_v, (size_t)c.n_sink * kvd * e));
         }
         if (S.mode != 1) TRY(A((void**)&S.head_gate, (size_t)c.n_head * 4));
+        TRY(dev_alloc(ctx, (void**)&S.head_w, (size_t)5 * c.n_head * 4));
         L.sub.push_back(S);
       }
     } else {
@@ -386,8 +391,33 @@ int32_t linear(vn_model* m, GemmArgs g) {
 
 // The attention part of a vda / dsa / kda / gmla layer (verse_nex/delta_attention.py): m->h (normalised rows) ->
 // m->attn (head-space output before the layer's projection).  Every module projects on its own, rotates and appends
-// its K / V to its own plane pair, and runs delta_attn_kernel; a vda layer sums its three modules with
+// its K / V to its own plane pair and runs its attention; a vda layer sums its three modules with
 // sigmoid(gate_logits) (:1167-1168) through the fp32 buffer m->mix.
+float delta_mix_weight(const Layer& L, int si) {
+  return L.sub.size() > 1 ? 0.5f * (1.0f + tanhf(0.5f * L.gate_logits[si])) : 1.0f;
+}
+
+// arguments of the tensor-core attention kernel for module `si` of a delta layer (bf16, head_dim 64)
+AttnArgs delta_mma_args(vn_model* m, vn_kv* kv, Layer& L, int si, int Tn, bool tree, int slot_offset) {
+  const Config& c = m->cfg;
+  SubAttn& S = L.sub[si];
+  const int n_sub = (int)L.sub.size();
+  AttnArgs a;
+  a.q = m->qkv; a.ld_q = (c.n_head + 2 * c.n_kv) * c.hd; a.kc = kv->k[S.pair]; a.vc = kv->v[S.pair];
+  a.sink_k = S.sink_k; a.sink_v = S.sink_v;
+  a.out = si + 1 == n_sub ? m->attn : nullptr;
+  a.acc_in = si > 0 ? m->mix : nullptr;
+  a.acc_out = si + 1 < n_sub ? m->mix : nullptr;
+  a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
+  a.Tn = Tn; a.H = c.n_head; a.n_kv = c.n_kv; a.hd = c.hd; a.max_seq = kv->max_seq; a.window = c.window;
+  a.n_sink = S.mode == 0 ? c.n_sink : 0; a.slot_offset = slot_offset;
+  a.use_alibi = 1; a.alibi_max = 1024; a.alibi_window = 0;       // the dense pass and its switch at 1024 keys
+  a.g_a = a.g_b = a.g_c = 0.f;
+  a.scale = 1.0f / sqrtf((float)c.hd);
+  a.delta = S.mode + 1; a.head_w = S.head_w; a.out_w = delta_mix_weight(L, si); a.anchor = c.anchor;
+  return a;
+}
+
 template <typename T>
 int32_t delta_attention(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool tree, int slot_offset) {
   vn_ctx* ctx = m->ctx;
@@ -418,13 +448,18 @@ int32_t delta_attention(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool tr
     VN_LAUNCH(ctx, rope_append_kernel<T>, M, 128, 0, m->qkv, m->rope_cos, m->rope_sin, kv->lens,
               tree ? m->depth_dev : (const int*)nullptr, (T*)kv->k[S.pair], (T*)kv->v[S.pair], Tn, H, n_kv, hd, kv->max_seq,
               c.use_rope, m->rope_rows, slot_offset);
+    AttnArgs am = delta_mma_args(m, kv, L, si, Tn, tree, slot_offset);
+    if (attn_mma_supported(am, c.bf16 != 0) && !m->force_simt_attn) {
+      TRY(launch_attn_mma(ctx, am, B));
+      continue;
+    }
     DeltaArgs a;
     a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[S.pair]; a.vc = kv->v[S.pair]; a.sink_k = S.sink_k; a.sink_v = S.sink_v;
     a.head_gate = S.head_gate;
     a.acc_in = si > 0 ? m->mix : nullptr;
     a.acc_out = si + 1 < n_sub ? m->mix : nullptr;
     a.out = si + 1 == n_sub ? m->attn : nullptr;
-    a.out_w = n_sub > 1 ? 0.5f * (1.0f + tanhf(0.5f * L.gate_logits[si])) : 1.0f;
+    a.out_w = delta_mix_weight(L, si);
     a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
     a.Tn = Tn; a.H = H; a.n_kv = n_kv; a.hd = hd; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink;
     a.slot_offset = slot_offset; a.anchor = c.anchor; a.max_t = 1024; a.mode = S.mode;
@@ -736,6 +771,61 @@ int32_t launch_draft_stack(vn_model* m, vn_kv* kv, const int64_t* tokens, int B,
   return VN_OK;
 }
 
+// The same on the decode / verify route (bf16, head_dim 64, at most 256 rows): every projection is a split-K
+// tcgen05 GEMM; a DSA / KDA module's q | k | v slices are summed, rotated and appended by its attention CTAs (as for a
+// TriSparse layer), a GMLA module goes through its latent (two GEMMs with a reduction kernel behind each).
+bool delta_tc_ok(const vn_model* m, int Tn, bool tree) {
+  const Config& c = m->cfg;
+  return c.hd == 64 && c.latent % 8 == 0 && !m->force_simt_attn && (!tree || Tn <= 64);
+}
+
+int32_t delta_attention_tc(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool tree, int slot_offset) {
+  typedef __nv_bfloat16 T;
+  vn_ctx* ctx = m->ctx;
+  const Config& c = m->cfg;
+  const int M = B * Tn, D = c.dim, H = c.n_head, hd = c.hd, n_kv = c.n_kv, lat = c.latent;
+  const int qd = H * hd, kvd = n_kv * hd, qkv_ld = qd + 2 * kvd;
+  const long long cap = m->cap_rows;
+  static const bool fuse_on = [] { const char* e = getenv("VN_ATTN_FUSE"); return !(e && e[0] == '0'); }();
+  const int* depth = tree ? m->depth_dev : (const int*)nullptr;
+  for (int si = 0; si < (int)L.sub.size(); ++si) {
+    SubAttn& S = L.sub[si];
+    AttnArgs a = delta_mma_args(m, kv, L, si, Tn, tree, slot_offset);
+    T* kc = (T*)kv->k[S.pair];
+    T* vc = (T*)kv->v[S.pair];
+    int sp = 1;
+    GemmArgs g;
+    g.A = m->h; g.lda = D; g.W = S.wqkv; g.ldw = D; g.M = M; g.K = D;
+    if (S.mode != 2) {
+      g.N = qkv_ld; g.tag = "gemm_qkv";
+      TRY(tc_partial(m, g, cap, M, &sp));
+      if (fuse_on && Tn <= 64 && qkv_ld % 4 == 0) {
+        a.partial = m->partial; a.splits = sp; a.pstride = (long long)M * qkv_ld; a.partial_ld = qkv_ld;
+        a.cos_t = m->rope_cos; a.sin_t = m->rope_sin; a.use_rope = c.use_rope; a.rope_rows = m->rope_rows;
+      } else {
+        VN_LAUNCH_PDL_BIT(ctx, 2, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld,
+                          m->qkv, m->rope_cos, m->rope_sin, kv->lens, depth, kc, vc, Tn, H, n_kv, hd, kv->max_seq,
+                          c.use_rope, m->rope_rows, slot_offset);
+      }
+    } else {
+      const int n1 = qd + lat, n2 = 2 * kvd;
+      g.N = n1; g.tag = "gemm_gmla_q_down";
+      TRY(tc_partial(m, g, cap, M, &sp));
+      VN_LAUNCH_PDL_BIT(ctx, 2, gmla_finalize_kernel<T>, M, 256, (size_t)n1 * 4, m->partial, sp, (long long)M * n1, n1, 1,
+                        m->qkv, qkv_ld, (T*)m->lat, lat, m->rope_cos, m->rope_sin, kv->lens, depth, kc, vc, Tn, H, n_kv,
+                        hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
+      g = GemmArgs();
+      g.A = m->lat; g.lda = lat; g.W = S.w_up; g.ldw = lat; g.M = M; g.N = n2; g.K = lat; g.tag = "gemm_gmla_up";
+      TRY(tc_partial(m, g, cap, M, &sp));
+      VN_LAUNCH_PDL_BIT(ctx, 2, gmla_finalize_kernel<T>, M, 256, (size_t)n2 * 4, m->partial, sp, (long long)M * n2, n2, 2,
+                        m->qkv, qkv_ld, (T*)m->lat, lat, m->rope_cos, m->rope_sin, kv->lens, depth, kc, vc, Tn, H, n_kv,
+                        hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
+    }
+    TRY(launch_attn_mma(ctx, a, B));
+  }
+  return VN_OK;
+}
+
 int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn, bool tree, float* out_hidden,
                    float* out_logits, int last_only, int slot_offset) {
   typedef __nv_bfloat16 T;
@@ -776,16 +866,19 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     int sp = 1;
     GemmArgs g;
     // ---- attention block
+    if (is_delta(L.kind)) {
+      TRY(delta_attention_tc(m, kv, L, B, Tn, tree, slot_offset));
+    } else {
     g.A = m->h; g.lda = D; g.W = L.wqkv; g.ldw = D; g.M = M; g.N = qkv_ld; g.K = D; g.tag = "gemm_qkv";
     pick(g, L.q[0], L.qs[0], 0);
     tc_detail::TcRope rope;
     rope.cos_t = m->rope_cos; rope.sin_t = m->rope_sin; rope.lens = kv->lens;
     rope.depth = tree ? m->depth_dev : (const int*)nullptr;
-    rope.kc = kv->k[li]; rope.vc = kv->v[li]; rope.q_out = m->qkv; rope.ldq = qkv_ld;
+    rope.kc = kv->k[m->pair0[li]]; rope.vc = kv->v[m->pair0[li]]; rope.q_out = m->qkv; rope.ldq = qkv_ld;
     rope.Tn = Tn; rope.H = H; rope.n_kv = n_kv; rope.hd = hd; rope.max_seq = kv->max_seq;
     rope.use_rope = c.use_rope; rope.rope_rows = m->rope_rows; rope.slot_offset = slot_offset;
     AttnArgs a;
-    a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[li]; a.vc = kv->v[li]; a.sink_k = L.sink_k; a.sink_v = L.sink_v;
+    a.q = m->qkv; a.ld_q = qkv_ld; a.kc = kv->k[m->pair0[li]]; a.vc = kv->v[m->pair0[li]]; a.sink_k = L.sink_k; a.sink_v = L.sink_v;
     a.out = m->attn; a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
     a.Tn = Tn; a.H = H; a.n_kv = n_kv; a.hd = hd; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink;
     a.use_alibi = c.use_alibi; a.alibi_max = 1024; a.slot_offset = slot_offset;
@@ -808,7 +901,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
       } else {
         VN_LAUNCH_PDL_BIT(ctx, 2, qkv_finalize_kernel<T>, M, 256, (size_t)qkv_ld * 4, m->partial, sp, (long long)M * qkv_ld,
                       m->qkv, m->rope_cos, m->rope_sin, kv->lens, tree ? m->depth_dev : (const int*)nullptr,
-                      (T*)kv->k[li], (T*)kv->v[li], Tn, H, n_kv, hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
+                      (T*)kv->k[m->pair0[li]], (T*)kv->v[m->pair0[li]], Tn, H, n_kv, hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
       }
     }
     if (attn_tc) {
@@ -816,6 +909,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
     } else {
       dim3 grid(ceil_div(H, 8), M);
       VN_LAUNCH(ctx, trisparse_attn_kernel<T>, grid, 256, 0, a);
+    }
     }
     g = GemmArgs();
     g.A = m->attn; g.lda = H * hd; g.W = L.wproj; g.ldw = H * hd; g.M = M; g.N = D; g.K = H * hd; g.tag = "gemm_proj";
@@ -1104,7 +1198,7 @@ int32_t vn_model_destroy(vn_model* m) {
   F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->stack_bar); F(m->row_seg); F(m->sub_seg); F(m->head_q); F(m->head_qs);
   for (auto& L : m->layers) for (int i = 0; i < 6; ++i) { F(L.q[i]); F(L.qs[i]); }
   for (auto& L : m->layers)
-    for (auto& S : L.sub) { F(S.wqkv); F(S.w_down); F(S.w_up); F(S.sink); F(S.sink_k); F(S.sink_v); F(S.head_gate); }
+    for (auto& S : L.sub) { F(S.wqkv); F(S.w_up); F(S.sink); F(S.sink_k); F(S.sink_v); F(S.head_gate); F(S.head_w); }
   F(m->lat); F(m->mix);
   delete m;
   return VN_OK;
@@ -1172,14 +1266,14 @@ int32_t vn_model_load_tensor(vn_model* m, const char* name, const float* data, i
       else if (S->mode != 2 && leaf == "wk.weight") { SHAPE(kvd, D); TRY(upload(m, data, S->wqkv, r, cl, D, 1, qd)); }
       else if (S->mode != 2 && leaf == "wv.weight") { SHAPE(kvd, D); TRY(upload(m, data, S->wqkv, r, cl, D, 1, qd + kvd)); }
       else if (S->mode == 0 && leaf == "global_tokens.weight") { SHAPE(c.n_sink, D); TRY(upload(m, data, S->sink, r, cl, D)); }
-      else if (S->mode == 2 && leaf == "w_kv_down.weight") { SHAPE(lat, D); TRY(upload(m, data, S->w_down, r, cl, D)); }
+      else if (S->mode == 2 && leaf == "w_kv_down.weight") { SHAPE(lat, D); TRY(upload(m, data, S->wqkv, r, cl, D, 1, qd)); }
       else if (S->mode == 2 && leaf == "w_k_up.weight") { SHAPE(kvd, lat); TRY(upload(m, data, S->w_up, r, cl, lat, 1, 0)); }
       else if (S->mode == 2 && leaf == "w_v_up.weight") { SHAPE(kvd, lat); TRY(upload(m, data, S->w_up, r, cl, lat, 1, kvd)); }
       else if (S->mode != 1 && leaf == "head_gate_logits") {
         SHAPE(c.n_head, 1);
-        std::vector<float> gate(c.n_head);
-        for (int i = 0; i < c.n_head; ++i) gate[i] = 0.5f * (1.0f + tanhf(0.5f * data[i]));   // Tensor.sigmoid, tensor.py:824
-        VN_CUDA(ctx, cudaMemcpyAsync(S->head_gate, gate.data(), gate.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+        S->gate_host.resize(c.n_head);
+        for (int i = 0; i < c.n_head; ++i) S->gate_host[i] = 0.5f * (1.0f + tanhf(0.5f * data[i]));   // Tensor.sigmoid, tensor.py:824
+        VN_CUDA(ctx, cudaMemcpyAsync(S->head_gate, S->gate_host.data(), S->gate_host.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
         VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
       }
       else return vn_fail(ctx, VN_ERR_INVALID, "unexpected tensor %s", name);
@@ -1292,6 +1386,22 @@ int32_t vn_model_finalize(vn_model* m) {
   const long long D = c.dim, qd = (long long)c.n_head * c.hd, kvd = (long long)c.n_kv * c.hd;
   const int pm = m->preq_mode;
   TRY(compute_sinks(m, pm));
+  // per-head weights of the tensor-core attention passes for the delta modules (window, sinks, dense up to 1024
+  // keys; window, sinks beyond): DSA g*dense + (1-g)*(window + sinks), beyond 1024 keys window + sinks
+  // (delta_attention.py:559-573); KDA one pass; GMLA gate * dense, beyond 1024 keys gate * window (:918-927)
+  for (auto& L : m->layers)
+    for (auto& S : L.sub) {
+      const int H = c.n_head;
+      std::vector<float> w((size_t)5 * H, 0.f);
+      for (int h = 0; h < H; ++h) {
+        const float g = S.mode == 1 ? 1.f : S.gate_host[h];
+        if (S.mode == 0) { w[h] = 1.f - g; w[H + h] = 1.f - g; w[2 * H + h] = g; w[3 * H + h] = 1.f; w[4 * H + h] = 1.f; }
+        else if (S.mode == 1) w[2 * H + h] = 1.f;
+        else { w[2 * H + h] = g; w[3 * H + h] = g; }
+      }
+      VN_CUDA(ctx, cudaMemcpyAsync(S.head_w, w.data(), w.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+      VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (pm) {
     // linears arrived quantised: the model is now what vn_model_quantize would have left behind
@@ -1595,7 +1705,7 @@ int32_t vn_kv_create(vn_model* m, int32_t max_batch, int32_t max_seq, vn_kv** ou
   VN_CHECK_CTX(ctx);
   VN_REQUIRE(ctx, max_batch >= 1 && max_seq >= 1, "max_batch and max_seq must be positive");
   vn_kv* kv = new vn_kv();
-  kv->m = m; kv->max_batch = max_batch; kv->max_seq = max_seq;
+  kv->m = m; kv->ctx = ctx; kv->max_batch = max_batch; kv->max_seq = max_seq;
   const size_t plane = (size_t)max_batch * max_seq * m->cfg.n_kv * m->cfg.hd * m->esz;
   std::vector<void*> planes;
   for (int i = 0; i < m->n_pairs; ++i) {
@@ -1621,8 +1731,10 @@ int32_t vn_kv_create(vn_model* m, int32_t max_batch, int32_t max_seq, vn_kv** ou
 
 int32_t vn_kv_destroy(vn_kv* kv) {
   if (!kv) return VN_OK;
-  cudaSetDevice(kv->m->ctx->device);
-  cudaStreamSynchronize(kv->m->ctx->stream);
+  if (kv->ctx) {
+    cudaSetDevice(kv->ctx->device);
+    cudaStreamSynchronize(kv->ctx->stream);
+  }
   if (!kv->parent) {
     for (void* p : kv->k) cudaFree(p);
     for (void* p : kv->v) cudaFree(p);
@@ -1641,7 +1753,7 @@ int32_t vn_kv_view(vn_kv* kv, int32_t first, int32_t count, vn_kv** out) {
   if (first < 0 || count < 1 || first + count > kv->max_batch)
     return vn_fail(ctx, VN_ERR_INDEX, "sequences [%d, %d) outside the cache's %d", first, first + count, kv->max_batch);
   vn_kv* v = new vn_kv();
-  v->m = m; v->max_batch = count; v->max_seq = kv->max_seq;
+  v->m = m; v->ctx = ctx; v->max_batch = count; v->max_seq = kv->max_seq;
   v->parent = kv->parent ? kv->parent : kv;
   v->parent_first = kv->parent_first + first;
   const size_t seq_bytes = (size_t)kv->max_seq * m->cfg.n_kv * m->cfg.hd * m->esz;
@@ -1805,7 +1917,7 @@ int32_t vn_model_forward(vn_model* m, vn_kv* kv, const int64_t* tokens_dev, int3
     }
   }
   TRY(ensure_rows(m, B * T));
-  if (m->cfg.bf16 && m->use_tc && !m->has_delta && B * T <= 256 && m->cfg.dim % 8 == 0 && m->cfg.dim <= 2048 &&
+  if (m->cfg.bf16 && m->use_tc && (!m->has_delta || delta_tc_ok(m, T, tree)) && B * T <= 256 && m->cfg.dim % 8 == 0 && m->cfg.dim <= 2048 &&
       tc_detail::encode_fn() != nullptr)
     return forward_tc(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);
   if (m->cfg.bf16) return forward_t<__nv_bfloat16>(m, kv, tokens_dev, B, T, tree, out_hidden_dev, out_logits_dev, last_only, slot_offset);

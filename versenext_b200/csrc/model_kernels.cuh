@@ -181,6 +181,18 @@ struct AttnArgs {
   const float* cos_t = nullptr;
   const float* sin_t = nullptr;
   int use_rope = 0, rope_rows = 0;
+  // Tensor-core kernel only: a module of the delta attention family (verse_nex/delta_attention.py) on the same three
+  // passes.  delta 1 = DSA (window + sinks + dense), 2 = KDA (one pass over all keys with the window | anchor mask),
+  // 3 = GMLA (dense, or the window beyond alibi_max keys); the dense pass is the ALiBi pass without its bias and the
+  // switch at alibi_max keys is the ALiBi path's.  head_w[5][H]: per-head weights of the window, sink and dense
+  // results while the key count is at most alibi_max, then of the window and sink results beyond it; all times out_w.
+  // acc_in / acc_out: fp32 [M, H * 64] running sum over the modules of a vda layer (out is written when non-null).
+  int delta = 0;
+  const float* head_w = nullptr;
+  float out_w = 1.f;
+  int anchor = 1;
+  const float* acc_in = nullptr;
+  float* acc_out = nullptr;
 };
 
 // online-softmax state of one 8-lane group: running max, running sum, 8 output dims per lane
