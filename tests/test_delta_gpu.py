@@ -186,12 +186,14 @@ def test_delta_tensor_core_routes_around_the_1024_key_switch():
 
 def test_delta_and_trisparse_layers_in_one_model_bf16():
     """A model that mixes TriSparse, MoD and delta layers (the plane pairs of the cache are then not one per layer),
-    batch 4: decode rows on the tcgen05 route against the oracle, and the engine's greedy stream against generate."""
+    batch 4: decode rows on the tcgen05 route against the oracle, and the engine's greedy stream against generate.
+    The latent has the default width (n_kv_head * head_dim), so the GMLA module runs with its K | V projections folded
+    through the latent into one matrix."""
     import versenext_b200 as vn
     # (every expert of a part is selected, top_k = E: the routed output is then continuous in the activations, and bf16
     # rounding cannot flip a choice between two experts with nearly equal router logits)
     cfg = hd64_delta_cfg(layer_pattern=["trisparse", "vda", "mod", "gmla"], num_dense_parts=2, num_experts_per_part=2,
-                         top_k=2, window_size=16, anchor_interval=8)
+                         top_k=2, window_size=16, anchor_interval=8, latent_dim=None)
     sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=71, gate_std=1.0).items()}
     m = build(cfg, sd, "bf16")
     rng = np.random.default_rng(9)

@@ -90,6 +90,11 @@ struct SubAttn {
   void* wqkv = nullptr;      // dsa, kda: [(H + 2 n_kv) hd, D] (q | k | v); gmla: [H hd + latent, D] (wq | w_kv_down)
   void* w_down = nullptr;    // gmla: the w_kv_down rows of wqkv (not a buffer of its own)
   void* w_up = nullptr;      // gmla: [2 n_kv hd, latent]      w_k_up | w_v_up
+  // gmla, bf16 models whose latent is not much narrower than K | V: [(H + 2 n_kv) hd, D] = wq | w_k_up w_kv_down |
+  // w_v_up w_kv_down, built by finalize.  K and V are linear in the latent, so the two projections collapse into one
+  // matrix of about the same size (exactly the same at the default latent_dim = n_kv hd) and the module then runs
+  // like a DSA / KDA module: one q | k | v GEMM, no latent buffer, no reduction kernels in between.
+  void* w_abs = nullptr;
   void* sink = nullptr;      // dsa: [n_sink, D] global_tokens.weight, and its K / V (finalize)
   void* sink_k = nullptr;
   void* sink_v = nullptr;
@@ -429,7 +434,10 @@ int32_t delta_attention(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool tr
     SubAttn& S = L.sub[si];
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = S.wqkv; g.ldw = D; g.C = m->qkv; g.ldc = qkv_ld; g.M = M; g.K = D;
-    if (S.mode == 2) {
+    if (S.mode == 2 && S.w_abs) {
+      g.W = S.w_abs; g.N = qkv_ld; g.tag = "gemm_qkv";
+      TRY(linear(m, g));
+    } else if (S.mode == 2) {
       // q; latent = w_kv_down(h) in the storage dtype; k | v = (w_k_up | w_v_up)(latent)   (:893-896)
       g.N = qd; g.tag = "gemm_gmla_q";
       TRY(linear(m, g));
@@ -796,7 +804,8 @@ int32_t delta_attention_tc(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool
     int sp = 1;
     GemmArgs g;
     g.A = m->h; g.lda = D; g.W = S.wqkv; g.ldw = D; g.M = M; g.K = D;
-    if (S.mode != 2) {
+    if (S.mode != 2 || S.w_abs) {
+      if (S.w_abs) g.W = S.w_abs;
       g.N = qkv_ld; g.tag = "gemm_qkv";
       TRY(tc_partial(m, g, cap, M, &sp));
       if (fuse_on && Tn <= 64 && qkv_ld % 4 == 0) {
@@ -1198,7 +1207,7 @@ int32_t vn_model_destroy(vn_model* m) {
   F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->stack_bar); F(m->row_seg); F(m->sub_seg); F(m->head_q); F(m->head_qs);
   for (auto& L : m->layers) for (int i = 0; i < 6; ++i) { F(L.q[i]); F(L.qs[i]); }
   for (auto& L : m->layers)
-    for (auto& S : L.sub) { F(S.wqkv); F(S.w_up); F(S.sink); F(S.sink_k); F(S.sink_v); F(S.head_gate); F(S.head_w); }
+    for (auto& S : L.sub) { F(S.wqkv); F(S.w_up); F(S.sink); F(S.sink_k); F(S.sink_v); F(S.head_gate); F(S.head_w); F(S.w_abs); }
   F(m->lat); F(m->mix);
   delete m;
   return VN_OK;
@@ -1389,6 +1398,23 @@ int32_t vn_model_finalize(vn_model* m) {
   // per-head weights of the tensor-core attention passes for the delta modules (window, sinks, dense up to 1024
   // keys; window, sinks beyond): DSA g*dense + (1-g)*(window + sinks), beyond 1024 keys window + sinks
   // (delta_attention.py:559-573); KDA one pass; GMLA gate * dense, beyond 1024 keys gate * window (:918-927)
+  // GMLA: K | V projections folded through the latent (VN_GMLA_ABSORB=0, read here, keeps the two-step route)
+  {
+    const char* e = getenv("VN_GMLA_ABSORB");
+    const bool absorb_on = !(e && e[0] == '0');
+    const long long lat = c.latent;
+    for (auto& L : m->layers)
+      for (auto& S : L.sub) {
+        if (S.mode != 2 || !c.bf16 || !absorb_on || S.w_abs) continue;
+        if ((double)2 * kvd * D > 1.25 * (double)lat * (D + 2 * kvd)) continue;   // a narrow latent: two small GEMMs read less
+        TRY(dev_alloc(ctx, &S.w_abs, (size_t)(qd + 2 * kvd) * D * m->esz));
+        VN_CUDA(ctx, cudaMemcpyAsync(S.w_abs, S.wqkv, (size_t)qd * D * m->esz, cudaMemcpyDeviceToDevice, ctx->stream));
+        GemmArgs g;       // C[2 kvd, D] = w_up[2 kvd, lat] x w_kv_down[lat, D]: the weight operand is read along its rows
+        g.A = S.w_up; g.lda = lat; g.W = S.w_down; g.ldw = 1; g.ldw_k = D;
+        g.C = (char*)S.w_abs + (size_t)qd * D * m->esz; g.ldc = D; g.M = (int)(2 * kvd); g.N = (int)D; g.K = (int)lat; g.c_bf16 = 1;
+        TRY((launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g)));
+      }
+  }
   for (auto& L : m->layers)
     for (auto& S : L.sub) {
       const int H = c.n_head;
