@@ -237,7 +237,10 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
 // Called by all AW * 32 threads of a CTA; attn_smem: AW * RING * 4096 bytes of shared memory, 128-byte aligned.
 // Everything another kernel -- or, inside a persistent kernel, another CTA -- wrote shortly before is read past L1
 // (cp.async.cg, __ldcg).
+// DELTA: compiled with the delta-attention modules (AttnArgs::delta); the TriSparse instance carries none of that code.
+template <bool DELTA>
 __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, unsigned char* attn_smem, long long* tr) {
+  const int dmode = DELTA ? a.delta : 0;
   // per warp: a ring of RING key blocks; after a path's keys the first 4 KB of the warp's ring hold its
   // partial output (16 rows x 64 dims fp32, 16-byte chunks swizzled) for the merge across warps
   __shared__ float sM[AW][16], sL[AW][16];
@@ -265,9 +268,9 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
     row[h].tq = rr % a.Tn;
     const int hrep = rr / a.Tn;
     row[h].pos = len + (depth ? depth[row[h].tq] : row[h].tq);
-    row[h].slope = a.delta ? 0.f : 1.0f / exp2f((float)(kvh * n_rep + hrep + 1) / (float)a.H);
+    row[h].slope = dmode ? 0.f : 1.0f / exp2f((float)(kvh * n_rep + hrep + 1) / (float)a.H);
     row[h].anc = a.anc ? a.anc[row[h].tq] : 0ull;
-    row[h].long_row = (a.anc ? row[h].pos + 1 : len + a.Tn) > a.alibi_max;
+    row[h].long_row = DELTA && (a.anc ? row[h].pos + 1 : len + a.Tn) > a.alibi_max;
   }
   // tile-wide key range (all threads compute the same numbers from the tile's rows)
   for (int r = tile0; r < tile0 + 16 && r < R; ++r) {
@@ -291,8 +294,8 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   // which passes this tile runs: TriSparse and DSA take the window and the sinks; GMLA takes the window only for rows
   // beyond alibi_max keys (a chain is all on one side of the switch, a tree may straddle it); KDA has one pass
   const bool some_long = len + a.Tn > a.alibi_max;
-  const bool need_ab = a.delta == 0 || a.delta == 1 || (a.delta == 3 && some_long);
-  const bool need_b = a.delta == 0 || a.delta == 1;
+  const bool need_ab = dmode == 0 || dmode == 1 || (dmode == 3 && some_long);
+  const bool need_b = dmode == 0 || dmode == 1;
   int nw = 1;
   if (!need_b) nw = AW;
   else {
@@ -306,6 +309,18 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   // This warp's first key blocks go on their way now, under the set-up work below: cached window keys and sink keys
   // do not depend on this call's q | k | v.  A window warp whose first blocks reach into the rows that this very
   // CTA appends below has to wait for them.
+  const bool use_c = dmode == 2 ||
+                     (a.use_alibi &&
+                      (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max));
+  const int lo_c = a.alibi_window > 0 ? max(0, pos_min - a.alibi_window + 1) : 0;
+  // a module whose only pass is the one over all keys (GMLA up to alibi_max keys, KDA) starts that pass's first
+  // cached blocks here as well
+  bool early_c = false;
+  if (DELTA && !need_ab && use_c) {
+    const int nblk_c = hi_new > lo_c ? (hi_new - lo_c + 15) >> 4 : 0;
+    const int last = warp + (RING - 2) * AW;
+    early_c = lo_c + (min(last, max(nblk_c - 1, 0)) + 1) * 16 <= len;
+  }
   bool early = need_ab;
   if (need_ab && warp < nw) {
     const int last = warp + (RING - 2) * nw;                 // its last block of the first batch
@@ -317,6 +332,12 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
     if (early) {
       if (warp < nw) attend<0>(a, Kc, Vc, ks, lo_w, hi_new, len, row, qf0, depth, warp, nw, lane, ring, o0, m0, l0, 1);
       else attend<1>(a, Ks, Vs, ks, 0, a.n_sink, len, row, qf0, depth, warp - nw, AW - nw, lane, ring, o0, m0, l0, 1);
+    }
+    if constexpr (DELTA) {
+      if (early_c) {
+        if (dmode == 2) attend<3>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf0, depth, warp, AW, lane, ring, o0, m0, l0, 1);
+        else attend<2>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf0, depth, warp, AW, lane, ring, o0, m0, l0, 1);
+      }
     }
   }
 
@@ -412,9 +433,6 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   // final output of this thread after the cross-warp merge: row = tid / 16, dims 4 * (tid % 16) .. +3
   float fin[4] = {0.f, 0.f, 0.f, 0.f};
   const int mrow = tid >> 4, mcol = (tid & 15) * 4;
-  const bool use_c = a.delta == 2 ||
-                     (a.use_alibi &&
-                      (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max));
   // weight of a pass's result in this thread's output row: the sigmoid gates of TriSparse, or the delta module's
   // per-head weights on the row's side of the alibi_max switch (path 0 window, 1 sinks, 2 dense / KDA)
   auto gate_of = [&](int path) -> float {
@@ -422,7 +440,7 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
     const int rr = r < R ? r : 0;
     const int tq = rr % a.Tn, head = kvh * n_rep + rr / a.Tn;
     const int tk = a.anc ? len + (depth ? depth[tq] : tq) + 1 : len + a.Tn;
-    if (!a.delta) {
+    if (!dmode) {
       if (path == 0) return a.g_a;
       if (path == 1) return a.g_b;
       // ALiBi path of a tree node is gated by its own T_k (position + 1 <= 1024)
@@ -430,7 +448,7 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
       return a.g_c;
     }
     const bool long_row = tk > a.alibi_max;
-    if (path == 2) return (long_row && a.delta != 2) ? 0.f : a.out_w * a.head_w[2 * a.H + head];
+    if (path == 2) return (long_row && dmode != 2) ? 0.f : a.out_w * a.head_w[2 * a.H + head];
     return a.out_w * a.head_w[((long_row ? 3 : 0) + path) * a.H + head];
   };
 
@@ -493,9 +511,12 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   if (use_c) {
     __syncthreads();                             // everybody has read the parked tiles
     float o[8][4], m[2], l[2];
-    const int lo_c = a.alibi_window > 0 ? max(0, pos_min - a.alibi_window + 1) : 0;
-    if (a.delta == 2) attend<3>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, AW, lane, ring, o, m, l);
-    else attend<2>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, AW, lane, ring, o, m, l);
+    if constexpr (DELTA) {
+      if (dmode == 2) attend<3>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, AW, lane, ring, o, m, l, early_c ? 2 : 0);
+      else attend<2>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, AW, lane, ring, o, m, l, early_c ? 2 : 0);
+    } else {
+      attend<2>(a, Kc, Vc, ks, lo_c, hi_new, len, row, qf, depth, warp, AW, lane, ring, o, m, l);
+    }
     park(o, m, l);
     __syncthreads();
     merge(0, AW, gate_of(2));
@@ -504,12 +525,12 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   if (r < R) {
     const int tq = r % a.Tn, hrep = r / a.Tn;
     const long long at = (long long)(b * a.Tn + tq) * a.H * 64 + (kvh * n_rep + hrep) * 64 + mcol;
-    if (a.acc_in) {
+    if (DELTA && a.acc_in) {
       const float4 p = *reinterpret_cast<const float4*>(a.acc_in + at);
       fin[0] += p.x; fin[1] += p.y; fin[2] += p.z; fin[3] += p.w;
     }
-    if (a.acc_out) *reinterpret_cast<float4*>(a.acc_out + at) = make_float4(fin[0], fin[1], fin[2], fin[3]);
-    if (a.out) {
+    if (DELTA && a.acc_out) *reinterpret_cast<float4*>(a.acc_out + at) = make_float4(fin[0], fin[1], fin[2], fin[3]);
+    if (!DELTA || a.out) {
       __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out) + at;
       __nv_bfloat162 v0 = __floats2bfloat162_rn(fin[0], fin[1]), v1 = __floats2bfloat162_rn(fin[2], fin[3]);
       reinterpret_cast<__nv_bfloat162*>(out)[0] = v0;
@@ -523,7 +544,14 @@ __global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_mma_kernel(AttnArgs
   long long* tr = a.trace ? a.trace + 8ll * (blockIdx.x + (long long)gridDim.x * blockIdx.y) : nullptr;
   if (tr && threadIdx.x == 0) tr[0] = clock_stamp();
   pdl_trigger();
-  attn_tile(a, blockIdx.x, blockIdx.y, attn_smem_dyn, tr);
+  attn_tile<false>(a, blockIdx.x, blockIdx.y, attn_smem_dyn, tr);
+}
+
+// the same tile with the delta-attention modules compiled in (AttnArgs::delta != 0)
+__global__ void __launch_bounds__(AW * 32, 2) delta_attn_mma_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char attn_smem_dyn[];
+  pdl_trigger();
+  attn_tile<true>(a, blockIdx.x, blockIdx.y, attn_smem_dyn, nullptr);
 }
 
 // ---- prompt attention: the eight warps of a CTA take eight different 16-row tiles of one (sequence, kv head) --
@@ -672,11 +700,18 @@ inline int32_t launch_attn_mma(vn_ctx* ctx, const AttnArgs& a, int B) {
   if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
     VN_CUDA(ctx, cudaFuncSetAttribute(attn_detail::trisparse_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem));
+    VN_CUDA(ctx, cudaFuncSetAttribute(attn_detail::delta_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
     attr_set |= 1ull << (ctx->device & 63);
   }
   // VN_ATTN_PDL=0 (read once): plain launch
   static const bool attn_pdl = [] { const char* e = getenv("VN_ATTN_PDL"); return !(e && e[0] == '0'); }();
   const int level = ((vn_pdl_mask() & 1) || attn_pdl) ? 1 : 2;
+  if (a.delta) {
+    VN_LAUNCH_PDL_LEVEL(ctx, level, "attn_detail::delta_attn_mma_kernel", attn_detail::delta_attn_mma_kernel, grid,
+                        attn_detail::AW * 32, smem, a);
+    return VN_OK;
+  }
   VN_LAUNCH_PDL_LEVEL(ctx, level, "attn_detail::trisparse_attn_mma_kernel", attn_detail::trisparse_attn_mma_kernel, grid,
                       attn_detail::AW * 32, smem, a);
   return VN_OK;
