@@ -966,10 +966,11 @@ def run_layer(args):
     from versenext_b200 import synthetic as S
     world, rank, local, dist = dist_setup(args.gpus)
     ctx = vn.Context.get(local)
-    kw = S.mate_kwargs(vocab_size=8192, n_layer=2, layer_pattern=["mod", "trisparse"], max_seq_len=2048)
+    pattern = args.pattern.split(",")          # default: one MoD + one TriSparse layer; e.g. --pattern vda,gmla
+    kw = S.mate_kwargs(vocab_size=8192, n_layer=len(pattern), layer_pattern=pattern, max_seq_len=2048)
     m = vn.VerseNexLM(dtype="bf16", device=f"cuda:{local}", **kw)
     S.load_random(m, kw, seed=3)
-    B, T0, Tn = 32, 1100, 5
+    B, T0, Tn = 32, args.context, 5
     rng = np.random.default_rng(5)
     cache = m.new_cache(B, T0 + 64)
     for lo in range(0, T0, 220):                       # prefill in pieces of 220 positions
@@ -992,8 +993,8 @@ def run_layer(args):
         print(json.dumps({"metric": "two-layer slice forward", "value": ms, "unit": "ms", "n_gpus": world,
                           "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
                           "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
-                          "config": {"workload": "layer: one MoD + one TriSparse layer of the mate shapes, V=8192, "
-                                                 "32 sequences at context 1100, 5 new rows each (eager launches)"},
+                          "config": {"workload": f"layer: layers {args.pattern} of the mate shapes, V=8192, "
+                                                 f"32 sequences at context {T0}, 5 new rows each (eager launches)"},
                           "gpu_launches": ctx.launch_count() - l0}))
     if dist is not None:
         dist.destroy_process_group()
@@ -1220,6 +1221,8 @@ def main():
     ap.add_argument("--no-sharded", action="store_true", help="N > 1: skip the sharded-head check")
     ap.add_argument("--quant", default=None, choices=["int8", "int4", "int4g128"],
                     help="spec workload: quantise the target's linear weights (not the default benchmark line)")
+    ap.add_argument("--pattern", default="mod,trisparse", help="layer workload: comma-separated layer kinds")
+    ap.add_argument("--context", type=int, default=1100, help="layer workload: cached positions (a multiple of 220)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-sampler", action="store_true", help="spec workload: skip the sampler GB/s measurement")
     args = ap.parse_args()

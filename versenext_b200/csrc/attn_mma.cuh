@@ -259,7 +259,7 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   const int* depth = a.depth ? s_depth : nullptr;
 
   RowInfo row[2];
-  int tq_min = 1 << 30, tq_max = -1, pos_min = 1 << 30;
+  int tq_min = 1 << 30, tq_max = -1, pos_min = 1 << 30, pos_top = -1;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = tile0 + g + 8 * h;
@@ -276,7 +276,7 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   for (int r = tile0; r < tile0 + 16 && r < R; ++r) {
     const int tq = r % a.Tn;
     const int p = len + (depth ? depth[tq] : tq);
-    tq_min = min(tq_min, tq); tq_max = max(tq_max, tq); pos_min = min(pos_min, p);
+    tq_min = min(tq_min, tq); tq_max = max(tq_max, tq); pos_min = min(pos_min, p); pos_top = max(pos_top, p);
   }
   const int hi_new = a.anc ? len + a.Tn : len + tq_max + 1;  // appended slots this tile can see
 
@@ -309,9 +309,13 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   // This warp's first key blocks go on their way now, under the set-up work below: cached window keys and sink keys
   // do not depend on this call's q | k | v.  A window warp whose first blocks reach into the rows that this very
   // CTA appends below has to wait for them.
-  const bool use_c = dmode == 2 ||
-                     (a.use_alibi &&
-                      (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max));
+  // DSA while every row's window still reaches back to the first key: its dense soft-max IS its window soft-max, so
+  // the window result takes both weights and the dense pass is left out
+  const bool c_is_a = DELTA && dmode == 1 && pos_top < a.window;
+  const bool use_c = !c_is_a &&
+                     (dmode == 2 ||
+                      (a.use_alibi &&
+                       (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max)));
   const int lo_c = a.alibi_window > 0 ? max(0, pos_min - a.alibi_window + 1) : 0;
   // a module whose only pass is the one over all keys (GMLA up to alibi_max keys, KDA) starts that pass's first
   // cached blocks here as well
@@ -504,7 +508,7 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
     if (tr && tid == 0) tr[2] = clock_stamp();   // this warp's keys done
     park(o, m, l);
     __syncthreads();
-    merge(0, nw, gate_of(0));
+    merge(0, nw, gate_of(0) + (c_is_a ? gate_of(2) : 0.f));
     merge(nw, AW, gate_of(1));
     if (tr && tid == 0) tr[3] = clock_stamp();   // merge done
   }
