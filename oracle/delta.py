@@ -104,7 +104,7 @@ def kda_multiplicity(pos, key_pos, visible, window, interval):
     return in_slice.astype(np.int64) + (causal & anchor).astype(np.int64)
 
 
-def _geometry(cache_len, T, parents):
+def _geometry(cache_len, T, parents, recurrent=False):
     from .model import tree_depths_and_ancestors
     if parents is None:
         depth = np.arange(T)
@@ -116,19 +116,26 @@ def _geometry(cache_len, T, parents):
     visible = np.zeros((T, cache_len + T), dtype=bool)
     visible[:, :cache_len] = True
     visible[:, cache_len:] = vis_new
-    tk_eff = np.full(T, cache_len + T) if parents is None else (pos + 1)
+    # key count that decides the length switch: the whole call for a chain, a row's own position + 1 for a tree node
+    # and on the one-token route (where every token is a call of its own)
+    tk_eff = np.full(T, cache_len + T) if (parents is None and not recurrent) else (pos + 1)
     return pos, key_pos, visible, tk_eff
 
 
-def sub_attention(sd, cfg, prefix, kind, x, cache, parents, rope):
+def sub_attention(sd, cfg, prefix, kind, x, cache, parents, rope, recurrent=False):
     """One DSA / KDA / GMLA module without its output projection: head-space output [B, T, H*hd] and the new
-    cache {'k', 'v'} (for GMLA the K / V rebuilt from the latents: the same information as the latent cache)."""
+    cache {'k', 'v'} (for GMLA the K / V rebuilt from the latents: the same information as the latent cache).
+
+    recurrent=True restates the classes' `forward_recurrent` (one token per call, :294-375, :998-1085), evaluated
+    for all T positions at once: every row is its own call, so GMLA's switch to the window looks at the row's own key
+    count (:1059), while DSA keeps its dense soft-max (:594-597) and KDA its plain window | anchor mask (:788-799) at
+    any length."""
     from .model import linear, apply_rope
     B, T, D = x.shape
     H, hd, n_kv = cfg.n_head, cfg.head_dim, cfg.n_kv_head
     n_rep = H // n_kv
     Tc = 0 if cache is None else cache["k"].shape[1]
-    pos, key_pos, visible, tk_eff = _geometry(Tc, T, parents)
+    pos, key_pos, visible, tk_eff = _geometry(Tc, T, parents, recurrent)
     q = linear(x, sd[prefix + "wq.weight"]).reshape(B, T, H, hd)
     if kind == "gmla":
         c = linear(x, sd[prefix + "w_kv_down.weight"])
@@ -154,6 +161,8 @@ def sub_attention(sd, cfg, prefix, kind, x, cache, parents, rope):
     dense = visible & (dist >= 0)
     win = dense & (dist < cfg.window_size)
     long_row = (tk_eff > MAX_T)[None, None, :, None]
+    if recurrent and kind != "gmla":
+        long_row = np.zeros_like(long_row)
 
     if kind == "kda":
         I = cfg.anchor_interval
@@ -189,17 +198,18 @@ def sub_attention(sd, cfg, prefix, kind, x, cache, parents, rope):
     return out.astype(F32).transpose(0, 2, 1, 3).reshape(B, T, H * hd), new_cache
 
 
-def attention(sd, cfg, prefix, kind, x, cache, parents, rope):
+def attention(sd, cfg, prefix, kind, x, cache, parents, rope, recurrent=False):
     """The attention module of a block of kind vda / dsa / kda / gmla (`prefix` ends with 'attn.'): output
     [B, T, D] after the projection, and the new cache (nested per sub-module for vda)."""
     from .model import linear
     if kind != "vda":
-        o, c = sub_attention(sd, cfg, prefix, kind, x, cache, parents, rope)
+        o, c = sub_attention(sd, cfg, prefix, kind, x, cache, parents, rope, recurrent)
         return linear(o, sd[prefix + "proj.weight"]), c
     gate = _sigmoid(sd[prefix + "gate_logits"])
     total, new_cache = None, {}
     for i, sub in enumerate(("dsa", "kda", "gmla")):
-        o, c = sub_attention(sd, cfg, prefix + sub + ".", sub, x, None if cache is None else cache[sub], parents, rope)
+        o, c = sub_attention(sd, cfg, prefix + sub + ".", sub, x, None if cache is None else cache[sub], parents, rope,
+                             recurrent)
         new_cache[sub] = c
         total = gate[i] * o if total is None else total + gate[i] * o
     return linear(total.astype(F32), sd[prefix + "proj.weight"]), new_cache

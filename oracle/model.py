@@ -361,7 +361,7 @@ def forward_hidden(sd, cfg: Config, tokens, cache=None, parents=None, recurrent=
         p = f"blocks.{i}."
         if kind in DELTA_KINDS:
             a, c = delta.attention(sd, cfg, p + "attn.", kind, rmsnorm(x, sd[p + "norm1.weight"]),
-                                   None if cache is None else cache[i], parents, rope)
+                                   None if cache is None else cache[i], parents, rope, recurrent)
         else:
             a, c = attention(sd, cfg, p, rmsnorm(x, sd[p + "norm1.weight"]),
                              None if cache is None else cache[i], parents, rope, recurrent)

@@ -441,6 +441,23 @@ def gen_delta():
     # the same model at 1024 tokens is still on the full-matrix routes
     lg = ref_forward(m, cfg, toks[:, :1024])
     out["c_logits_1024"] = lg[:, rows[:11]]
+    # the one-token route of the same model (cometspark.py:737-767 -> forward_recurrent of every class): fed token by
+    # token past 1024 keys.  There DSA keeps its dense soft-max and KDA its plain window | anchor mask (:580-616,
+    # :780-803); only GMLA switches to the window (:1059-1069)
+    T = 1040
+    r_rows = np.array([0, 1, 47, 48, 500, 1023, 1024, 1025, 1039])
+    states, keep = None, []
+    with no_grad():
+        for t in range(T):
+            lg, states = m.forward_recurrent(Tensor(toks[:, t:t + 1]), states)
+            if t in r_rows:
+                keep.append(np.asarray(lg.data)[:, 0])
+    out["c_recurrent_rows"] = r_rows
+    out["c_recurrent_logits"] = np.stack(keep, axis=1).astype(np.float32)
+    # generate with its defaults (greedy on the one-token route, the last prompt token fed twice) on model a
+    cfg, sd = OD.golden_case("a")
+    m = ref_model(cfg, sd)
+    out["a_generate_default"] = m.generate(out["a_tokens"][:, :8], max_new_tokens=24)
     save("delta_reference.npz", **out)
 
 

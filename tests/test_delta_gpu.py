@@ -211,3 +211,31 @@ def test_delta_and_trisparse_layers_in_one_model_bf16():
     spec = m.generate(toks[:2, :12], max_new_tokens=20, temperature=0.0, draft=d, k=3)
     np.testing.assert_array_equal(spec, plain)
     m.check()
+
+
+@pytest.mark.parametrize("dtype,tol", [("f32", 1e-3), ("bf16", 2e-2)])
+def test_delta_one_token_route(golden, dtype, tol):
+    """The reference's one-token route on a delta model: `forward_recurrent` token by token past 1024 keys against the
+    recorded logits, `generate` with its defaults (greedy, last prompt token fed twice) against the recorded stream,
+    and a prompt longer than 1024 tokens taken as one chunk on that route (every row then counts its own keys)."""
+    g = golden("delta_reference.npz")
+    cfg, sd = OD.golden_case("c")
+    if dtype == "bf16":
+        sd = {n: OM.bf16_round(v) for n, v in sd.items()}
+    m = build(cfg, sd, dtype)
+    toks = g["c_tokens"][:, :1040]
+    rows = list(g["c_recurrent_rows"])
+    want = g["c_recurrent_logits"] if dtype == "f32" else OM.forward(sd, cfg, toks, recurrent=True)[0][:, rows]
+    states, got = None, []
+    for t in range(1040):
+        lg, states = m.forward_recurrent(toks[:, t:t + 1], states)
+        if t in rows:
+            got.append(lg.data.numpy()[:, 0])
+    assert rel_err(np.stack(got, axis=1), want) < tol
+    if dtype == "f32":
+        out = m.generate(toks[:, :1030], max_new_tokens=6)
+        np.testing.assert_array_equal(out, OM.generate_greedy_recurrent(sd, cfg, toks[:, :1030], 6))
+        cfg, sd = OD.golden_case("a")
+        m = build(cfg, sd)
+        np.testing.assert_array_equal(m.generate(g["a_tokens"][:, :8], max_new_tokens=24), g["a_generate_default"])
+    m.check()

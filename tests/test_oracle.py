@@ -316,3 +316,16 @@ def test_delta_cache_and_tree_equal_the_whole_sequence_forward():
         seq = np.concatenate([toks[:1, :20], nodes[:, path[::-1]]], axis=1)
         lg, _ = OM.forward(sd, cfg, seq)
         np.testing.assert_allclose(lg_tree[:, i], lg[:, -1], rtol=2e-4, atol=2e-5)
+
+
+def test_delta_one_token_route_against_the_reference(golden):
+    """`forward_recurrent` of the delta classes past 1024 keys (DSA stays dense, KDA keeps its plain mask, only GMLA
+    switches to the window) and `generate` with its defaults on a delta model."""
+    from oracle import delta as OD
+    g = golden("delta_reference.npz")
+    cfg, sd = OD.golden_case("c")
+    got, _ = OM.forward(sd, cfg, g["c_tokens"][:, :1040], recurrent=True)
+    np.testing.assert_allclose(got[:, g["c_recurrent_rows"]], g["c_recurrent_logits"], rtol=2e-4, atol=2e-5)
+    cfg, sd = OD.golden_case("a")
+    out = OM.generate_greedy_recurrent(sd, cfg, g["a_tokens"][:, :8], 24)
+    np.testing.assert_array_equal(out, g["a_generate_default"])

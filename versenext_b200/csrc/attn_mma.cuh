@@ -270,7 +270,7 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
     row[h].pos = len + (depth ? depth[row[h].tq] : row[h].tq);
     row[h].slope = dmode ? 0.f : 1.0f / exp2f((float)(kvh * n_rep + hrep + 1) / (float)a.H);
     row[h].anc = a.anc ? a.anc[row[h].tq] : 0ull;
-    row[h].long_row = DELTA && (a.anc ? row[h].pos + 1 : len + a.Tn) > a.alibi_max;
+    row[h].long_row = DELTA && ((a.anc || a.row_tk) ? row[h].pos + 1 : len + a.Tn) > a.alibi_max;
   }
   // tile-wide key range (all threads compute the same numbers from the tile's rows)
   for (int r = tile0; r < tile0 + 16 && r < R; ++r) {
@@ -315,7 +315,8 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
   const bool use_c = !c_is_a &&
                      (dmode == 2 ||
                       (a.use_alibi &&
-                       (a.anc ? true : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max)));
+                       ((a.anc || (DELTA && a.row_tk)) ? true
+                            : (a.alibi_window > 0 ? min(len + a.Tn, a.alibi_window) : (len + a.Tn)) <= a.alibi_max)));
   const int lo_c = a.alibi_window > 0 ? max(0, pos_min - a.alibi_window + 1) : 0;
   // a module whose only pass is the one over all keys (GMLA up to alibi_max keys, KDA) starts that pass's first
   // cached blocks here as well
@@ -443,7 +444,7 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, uns
     const int r = tile0 + mrow;
     const int rr = r < R ? r : 0;
     const int tq = rr % a.Tn, head = kvh * n_rep + rr / a.Tn;
-    const int tk = a.anc ? len + (depth ? depth[tq] : tq) + 1 : len + a.Tn;
+    const int tk = (a.anc || (DELTA && a.row_tk)) ? len + (depth ? depth[tq] : tq) + 1 : len + a.Tn;
     if (!dmode) {
       if (path == 0) return a.g_a;
       if (path == 1) return a.g_b;

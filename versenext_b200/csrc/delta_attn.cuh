@@ -34,6 +34,7 @@ struct DeltaArgs {
   const unsigned long long* anc;
   int Tn, H, n_kv, hd, max_seq, window, n_sink, slot_offset;
   int anchor, max_t;
+  int row_tk;            // 1: a chain's rows count their own keys (position + 1) for the max_t switch (one-token route)
   int mode;              // 0 dsa, 1 kda, 2 gmla
   float scale;
 };
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(256) delta_attn_kernel(DeltaArgs a) {
   };
   constexpr int ALL = 0x7fffffff;
 
-  const int tk_eff = a.anc ? (pos + 1) : (len + n_new);
+  const int tk_eff = (a.anc || a.row_tk) ? (pos + 1) : (len + n_new);
   const bool long_seq = tk_eff > a.max_t;
   float out[8];
 

@@ -417,6 +417,10 @@ AttnArgs delta_mma_args(vn_model* m, vn_kv* kv, Layer& L, int si, int Tn, bool t
   a.Tn = Tn; a.H = c.n_head; a.n_kv = c.n_kv; a.hd = c.hd; a.max_seq = kv->max_seq; a.window = c.window;
   a.n_sink = S.mode == 0 ? c.n_sink : 0; a.slot_offset = slot_offset;
   a.use_alibi = 1; a.alibi_max = 1024; a.alibi_window = 0;       // the dense pass and its switch at 1024 keys
+  // the one-token route (vn_model_set_recurrent): every row is a call of its own; DSA and KDA have no switch there
+  // (delta_attention.py:594-597, :788-799), GMLA's looks at the row's own key count (:1059)
+  a.row_tk = m->recurrent ? 1 : 0;
+  if (m->recurrent && S.mode != 2) a.alibi_max = 0x7fffffff;
   a.g_a = a.g_b = a.g_c = 0.f;
   a.scale = 1.0f / sqrtf((float)c.hd);
   a.delta = S.mode + 1; a.head_w = S.head_w; a.out_w = delta_mix_weight(L, si); a.anchor = c.anchor;
@@ -470,7 +474,8 @@ int32_t delta_attention(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool tr
     a.out_w = delta_mix_weight(L, si);
     a.lens = kv->lens; a.depth = tree ? m->depth_dev : nullptr; a.anc = tree ? m->anc_dev : nullptr;
     a.Tn = Tn; a.H = H; a.n_kv = n_kv; a.hd = hd; a.max_seq = kv->max_seq; a.window = c.window; a.n_sink = c.n_sink;
-    a.slot_offset = slot_offset; a.anchor = c.anchor; a.max_t = 1024; a.mode = S.mode;
+    a.slot_offset = slot_offset; a.anchor = c.anchor; a.max_t = (m->recurrent && S.mode != 2) ? 0x7fffffff : 1024;
+    a.row_tk = m->recurrent ? 1 : 0; a.mode = S.mode;
     a.scale = 1.0f / sqrtf((float)hd);
     dim3 grid(ceil_div(H, 8), M);
     VN_LAUNCH(ctx, delta_attn_kernel<T>, grid, 256, 0, a);

@@ -188,6 +188,8 @@ struct AttnArgs {
   // results while the key count is at most alibi_max, then of the window and sink results beyond it; all times out_w.
   // acc_in / acc_out: fp32 [M, H * 64] running sum over the modules of a vda layer (out is written when non-null).
   int delta = 0;
+  int row_tk = 0;        // delta: 1 = every row counts its own keys (position + 1) for the alibi_max switch even in a
+                         // chain: the one-token route of the reference, where every token is a call of its own
   const float* head_w = nullptr;
   float out_w = 1.f;
   int anchor = 1;
