@@ -111,8 +111,6 @@ def test_delta_model_generates_and_verifies_like_the_reference(golden):
     toks, _ = tree.generate(prompt, 24)
     np.testing.assert_array_equal(toks[:, :32], g["a_greedy"])
     assert vn.build_verse_delta_pattern(10) == list(g["pattern_10"])
-    with pytest.raises(NotImplementedError):
-        t.quantize("int8")
 
 
 def test_delta_layers_bf16_head_dim_64_with_a_long_prompt():
@@ -238,4 +236,66 @@ def test_delta_one_token_route(golden, dtype, tol):
         cfg, sd = OD.golden_case("a")
         m = build(cfg, sd)
         np.testing.assert_array_equal(m.generate(g["a_tokens"][:, :8], max_new_tokens=24), g["a_generate_default"])
+    m.check()
+
+
+def _dequantised(sd, scheme, names):
+    """The state dict a model computes with after weight-only quantisation of `names` (oracle quantiser)."""
+    from oracle import quant as OQ
+    out = dict(sd)
+    for n in names:
+        w = sd[n]
+        if scheme == "int8":
+            out[n] = OQ.dequant_int8(*OQ.quantize_int8(w))
+        elif scheme == "int4":
+            out[n] = OQ.dequant_int4(*OQ.quantize_int4(w), w.shape[1])
+        else:
+            out[n] = OQ.dequant_int4_g128(*OQ.quantize_int4_g128(w), w.shape[1])
+    return out
+
+
+@pytest.mark.parametrize("scheme", ["int8", "int4", "int4g128"])
+def test_delta_layers_weight_only_quantised(scheme):
+    """The shipped mate preset is delta attention + INT4: every linear of the modules (stacked q|k|v, q|down, k|v up)
+    is quantised like any other -- bytes and scales equal the oracle quantiser's, the forward equals the oracle on the
+    dequantised weights (prompt rows and decode rows), and the same linears loaded in their quantised form give the
+    same forward bit for bit."""
+    from oracle import quant as OQ
+    cfg = hd64_delta_cfg(latent_dim=64, window_size=16, anchor_interval=8)
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=81, gate_std=1.0).items()}
+    names = [n for n, w in sd.items() if w.ndim == 2 and n.endswith(".weight") and "global_tokens" not in n
+             and n != "tok_emb.weight"]
+    m = build(cfg, sd, "bf16")
+    m.quantize(scheme)
+    for n in names + ["head.weight"]:
+        w = sd["tok_emb.weight"] if n == "head.weight" else sd[n]
+        q, s = m.read_quant(n)
+        wq, ws = (OQ.quantize_int8(w) if scheme == "int8" else OQ.quantize_int4(w) if scheme == "int4"
+                  else OQ.quantize_int4_g128(w))
+        np.testing.assert_array_equal(q, wq, err_msg=n)
+        np.testing.assert_array_equal(s.view(np.uint32), np.ascontiguousarray(ws).reshape(s.shape).view(np.uint32), err_msg=n)
+    dq = _dequantised(sd, scheme, names)
+    dq["head.weight"] = _dequantised({"h": sd["tok_emb.weight"]}, scheme, ["h"])["h"]
+    o_cfg = OM.Config(**{**cfg.to_dict(), "tie_weights": False})
+    rng = np.random.default_rng(11)
+    toks = rng.integers(0, cfg.vocab_size, (2, 41))
+    want = OM.forward(dq, o_cfg, toks)[0]
+    cache = m.new_cache(2, 64)
+    l1 = m.forward_cached(toks[:, :36], cache).numpy()
+    cache.commit(36, np.full(2, 36, np.int32))
+    l2 = m.forward_cached(toks[:, 36:], cache).numpy()
+    assert rel_err(l1, want[:, :36]) < 3e-2
+    assert rel_err(l2, want[:, 36:]) < 3e-2
+    if scheme != "int4g128":
+        class QL:                              # what a reference QuantizedLinear exposes (quantize.py:382-440)
+            def __init__(self, w):
+                self.qtype = scheme
+                self.packed, self.scale = (OQ.quantize_int8 if scheme == "int8" else OQ.quantize_int4)(w)
+        comp = {n: (QL(w) if n in names else w) for n, w in sd.items()}
+        comp["head.weight"] = QL(sd["tok_emb.weight"])
+        m2 = build(cfg, comp, "bf16")
+        c2 = m2.new_cache(2, 64)
+        np.testing.assert_array_equal(m2.forward_cached(toks[:, :36], c2).numpy(), l1)
+        c2.commit(36, np.full(2, 36, np.int32))
+        np.testing.assert_array_equal(m2.forward_cached(toks[:, 36:], c2).numpy(), l2)
     m.check()

@@ -95,6 +95,9 @@ struct SubAttn {
   // matrix of about the same size (exactly the same at the default latent_dim = n_kv hd) and the module then runs
   // like a DSA / KDA module: one q | k | v GEMM, no latent buffer, no reduction kernels in between.
   void* w_abs = nullptr;
+  // weight-only quantised copies (the dense buffers are freed once these exist): 0 = wqkv as stacked above, 1 = w_up
+  void* q[2] = {nullptr, nullptr};
+  float* qs[2] = {nullptr, nullptr};
   void* sink = nullptr;      // dsa: [n_sink, D] global_tokens.weight, and its K / V (finalize)
   void* sink_k = nullptr;
   void* sink_v = nullptr;
@@ -236,6 +239,18 @@ int32_t dev_alloc(vn_ctx* ctx, void** p, size_t bytes) {
 }
 
 #define TRY(expr) do { int32_t _s = (expr); if (_s != VN_OK) return _s; } while (0)
+
+// bytes and scales of one row of a quantised matrix (mode 1 int8, 2 int4 per channel, 3 int4 group-128)
+inline size_t q_row_bytes(int mode, long long K) { return (size_t)(mode == 1 ? K : K / 2); }
+inline size_t q_row_scales(int mode, long long K) { return (size_t)(mode == 3 ? (K + 127) / 128 : 1); }
+
+// a delta module's GEMM on the quantised copy: rows row0.. of slot `slot`
+inline void pick_sub(const vn_model* m, GemmArgs& g, const SubAttn& S, int slot, long long row0) {
+  if (!m->qmode) return;
+  g.W = (const unsigned char*)S.q[slot] + (size_t)row0 * q_row_bytes(m->qmode, g.K);
+  g.w_scale = S.qs[slot] + (size_t)row0 * q_row_scales(m->qmode, g.K);
+  g.wq = m->qmode;
+}
 
 int32_t alloc_weights(vn_model* m) {
   vn_ctx* ctx = m->ctx;
@@ -444,17 +459,21 @@ int32_t delta_attention(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool tr
     } else if (S.mode == 2) {
       // q; latent = w_kv_down(h) in the storage dtype; k | v = (w_k_up | w_v_up)(latent)   (:893-896)
       g.N = qd; g.tag = "gemm_gmla_q";
+      pick_sub(m, g, S, 0, 0);
       TRY(linear(m, g));
       g = GemmArgs();
       g.A = m->h; g.lda = D; g.W = S.w_down; g.ldw = D; g.C = m->lat; g.ldc = c.latent; g.M = M; g.N = c.latent; g.K = D;
       g.c_bf16 = c.bf16; g.tag = "gemm_gmla_down";
+      pick_sub(m, g, S, 0, qd);
       TRY(linear(m, g));
       g = GemmArgs();
       g.A = m->lat; g.lda = c.latent; g.W = S.w_up; g.ldw = c.latent; g.C = m->qkv + qd; g.ldc = qkv_ld; g.M = M;
       g.N = 2 * kvd; g.K = c.latent; g.tag = "gemm_gmla_up";
+      pick_sub(m, g, S, 1, 0);
       TRY(linear(m, g));
     } else {
       g.N = qkv_ld; g.tag = "gemm_qkv";
+      pick_sub(m, g, S, 0, 0);
       TRY(linear(m, g));
     }
     VN_LAUNCH(ctx, rope_append_kernel<T>, M, 128, 0, m->qkv, m->rope_cos, m->rope_sin, kv->lens,
@@ -812,6 +831,7 @@ int32_t delta_attention_tc(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool
     if (S.mode != 2 || S.w_abs) {
       if (S.w_abs) g.W = S.w_abs;
       g.N = qkv_ld; g.tag = "gemm_qkv";
+      pick_sub(m, g, S, 0, 0);
       TRY(tc_partial(m, g, cap, M, &sp));
       if (fuse_on && Tn <= 64 && qkv_ld % 4 == 0) {
         a.partial = m->partial; a.splits = sp; a.pstride = (long long)M * qkv_ld; a.partial_ld = qkv_ld;
@@ -824,12 +844,14 @@ int32_t delta_attention_tc(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool
     } else {
       const int n1 = qd + lat, n2 = 2 * kvd;
       g.N = n1; g.tag = "gemm_gmla_q_down";
+      pick_sub(m, g, S, 0, 0);
       TRY(tc_partial(m, g, cap, M, &sp));
       VN_LAUNCH_PDL_BIT(ctx, 2, gmla_finalize_kernel<T>, M, 256, (size_t)n1 * 4, m->partial, sp, (long long)M * n1, n1, 1,
                         m->qkv, qkv_ld, (T*)m->lat, lat, m->rope_cos, m->rope_sin, kv->lens, depth, kc, vc, Tn, H, n_kv,
                         hd, kv->max_seq, c.use_rope, m->rope_rows, slot_offset);
       g = GemmArgs();
       g.A = m->lat; g.lda = lat; g.W = S.w_up; g.ldw = lat; g.M = M; g.N = n2; g.K = lat; g.tag = "gemm_gmla_up";
+      pick_sub(m, g, S, 1, 0);
       TRY(tc_partial(m, g, cap, M, &sp));
       VN_LAUNCH_PDL_BIT(ctx, 2, gmla_finalize_kernel<T>, M, 256, (size_t)n2 * 4, m->partial, sp, (long long)M * n2, n2, 2,
                         m->qkv, qkv_ld, (T*)m->lat, lat, m->rope_cos, m->rope_sin, kv->lens, depth, kc, vc, Tn, H, n_kv,
@@ -1004,6 +1026,7 @@ int32_t forward_tc(vn_model* m, vn_kv* kv, const int64_t* tokens, int B, int Tn,
 // ---- linears addressed by their state_dict name: where their rows live in the stacked / interleaved matrices ----
 struct LinearSlot {
   int layer = -1;        // -1: the LM head
+  int sub = -1;          // >= 0: a module of a delta layer (slot then indexes SubAttn::q / qs: 0 q|k|v or q|down, 1 k|v up)
   int slot = 0;          // index into Layer::q / qs (0 qkv, 1 proj, 2 gate|up, 3 down, 4 expert gate|up, 5 expert down)
   long long base = 0, row_mul = 1, row_off = 0;   // destination row of source row r: base + r * row_mul + row_off
   long long rows = 0, K = 0;                      // shape of the named tensor
@@ -1021,11 +1044,33 @@ bool locate_linear(const vn_model* m, const std::string& n, LinearSlot* o) {
   o->layer = li;
   const int kind = c.kind[li];
   const std::string rest = n.substr(dot + 1);
+  if (is_delta(kind) && rest.rfind("attn.", 0) == 0 && rest != "attn.proj.weight") {
+    std::string leaf = rest.substr(5);
+    int which = 0;
+    if (kind == 2) {
+      const size_t d2 = leaf.find('.');
+      if (d2 == std::string::npos) return false;
+      const std::string sub = leaf.substr(0, d2);
+      which = sub == "dsa" ? 0 : (sub == "kda" ? 1 : (sub == "gmla" ? 2 : -1));
+      if (which < 0) return false;
+      leaf = leaf.substr(d2 + 1);
+    }
+    const int mode = kind == 2 ? which : kind - 3;
+    const long long lat = c.latent;
+    o->sub = which;
+    if (leaf == "wq.weight") { o->slot = 0; o->rows = qd; o->K = D; return true; }
+    if (mode != 2 && leaf == "wk.weight") { o->slot = 0; o->base = qd; o->rows = kvd; o->K = D; return true; }
+    if (mode != 2 && leaf == "wv.weight") { o->slot = 0; o->base = qd + kvd; o->rows = kvd; o->K = D; return true; }
+    if (mode == 2 && leaf == "w_kv_down.weight") { o->slot = 0; o->base = qd; o->rows = lat; o->K = D; return true; }
+    if (mode == 2 && leaf == "w_k_up.weight") { o->slot = 1; o->rows = kvd; o->K = lat; return true; }
+    if (mode == 2 && leaf == "w_v_up.weight") { o->slot = 1; o->base = kvd; o->rows = kvd; o->K = lat; return true; }
+    return false;
+  }
   if (rest == "attn.wq.weight") { o->slot = 0; o->rows = qd; o->K = D; return true; }
   if (rest == "attn.wk.weight") { o->slot = 0; o->base = qd; o->rows = kvd; o->K = D; return true; }
   if (rest == "attn.wv.weight") { o->slot = 0; o->base = qd + kvd; o->rows = kvd; o->K = D; return true; }
   if (rest == "attn.proj.weight") { o->slot = 1; o->rows = D; o->K = qd; return true; }
-  if (kind == 0) {
+  if (kind != 1) {
     if (rest == "ffn.w_gate.weight") { o->slot = 2; o->row_mul = 2; o->rows = c.mlp_hidden; o->K = D; return true; }
     if (rest == "ffn.w_up.weight") { o->slot = 2; o->row_mul = 2; o->row_off = 1; o->rows = c.mlp_hidden; o->K = D; return true; }
     if (rest == "ffn.w_down.weight") { o->slot = 3; o->rows = D; o->K = c.mlp_hidden; return true; }
@@ -1049,8 +1094,34 @@ bool locate_linear(const vn_model* m, const std::string& n, LinearSlot* o) {
   return false;
 }
 
-inline size_t q_row_bytes(int mode, long long K) { return (size_t)(mode == 1 ? K : K / 2); }
-inline size_t q_row_scales(int mode, long long K) { return (size_t)(mode == 3 ? (K + 127) / 128 : 1); }
+// bytes of what stays dense in a quantised model: embedding, norms, router gates, sink tokens, head gates
+uint64_t dense_keep_bytes(const vn_model* m) {
+  const Config& c = m->cfg;
+  const uint64_t D = c.dim;
+  uint64_t keep = (uint64_t)c.vocab * D * m->esz + D * 4;
+  for (auto& L : m->layers) {
+    keep += 2ull * D * 4;
+    if (!is_delta(L.kind)) keep += (uint64_t)c.n_sink * D * m->esz;
+    for (auto& S : L.sub) {
+      if (S.mode == 0) keep += (uint64_t)c.n_sink * D * m->esz;
+      if (S.mode != 1) keep += (uint64_t)c.n_head * 4;
+    }
+    if (L.kind == 1) keep += (uint64_t)(c.P + c.P * c.E) * D * 4;
+  }
+  return keep;
+}
+
+// where the quantised bytes / scales of a located linear live
+void* slot_q(vn_model* m, const LinearSlot& ls) {
+  if (ls.layer < 0) return m->head_q;
+  Layer& L = m->layers[ls.layer];
+  return ls.sub >= 0 ? L.sub[ls.sub].q[ls.slot] : L.q[ls.slot];
+}
+float* slot_qs(vn_model* m, const LinearSlot& ls) {
+  if (ls.layer < 0) return m->head_qs;
+  Layer& L = m->layers[ls.layer];
+  return ls.sub >= 0 ? L.sub[ls.sub].qs[ls.slot] : L.qs[ls.slot];
+}
 
 // buffers for linears that arrive quantised; the dense buffers of those linears are given back
 int32_t alloc_quant(vn_model* m, int mode) {
@@ -1065,10 +1136,16 @@ int32_t alloc_quant(vn_model* m, int mode) {
   VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   auto F = [](void** p) { if (*p) cudaFree(*p); *p = nullptr; };
   for (auto& L : m->layers) {
-    TRY(A(&L.q[0], &L.qs[0], qd + 2 * kvd, D));
+    if (!is_delta(L.kind)) TRY(A(&L.q[0], &L.qs[0], qd + 2 * kvd, D));
+    for (auto& S : L.sub) {
+      TRY(A(&S.q[0], &S.qs[0], S.mode == 2 ? qd + c.latent : qd + 2 * kvd, D));
+      if (S.mode == 2) TRY(A(&S.q[1], &S.qs[1], 2 * kvd, c.latent));
+      F(&S.wqkv); F(&S.w_up);
+      S.w_down = nullptr;
+    }
     TRY(A(&L.q[1], &L.qs[1], D, qd));
     F(&L.wqkv); F(&L.wproj);
-    if (L.kind == 0) {
+    if (L.kind != 1) {
       TRY(A(&L.q[2], &L.qs[2], 2ll * c.mlp_hidden, D));
       TRY(A(&L.q[3], &L.qs[3], D, c.mlp_hidden));
       F(&L.w_gateup); F(&L.w_down);
@@ -1098,8 +1175,18 @@ int32_t compute_sinks(vn_model* m, int mode) {
       if (S.mode != 0) continue;
       for (int which = 0; which < 2; ++which) {
         GemmArgs g;
-        g.A = S.sink; g.lda = D; g.ldw = D; g.W = (char*)S.wqkv + (size_t)(qd + which * kvd) * D * m->esz;
+        g.A = S.sink; g.lda = D; g.ldw = D;
         g.C = which ? S.sink_v : S.sink_k; g.ldc = kvd; g.M = c.n_sink; g.N = (int)kvd; g.K = (int)D; g.c_bf16 = c.bf16;
+        if (mode) {
+          const long long r0 = qd + which * kvd;
+          g.W = (const unsigned char*)S.q[0] + (size_t)r0 * q_row_bytes(mode, D);
+          g.w_scale = S.qs[0] + (size_t)r0 * q_row_scales(mode, D);
+          g.wq = mode;
+          if (!gemm_mma_q_supported(g)) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised GEMM shape K=%d unsupported", g.K);
+          TRY(launch_gemm_mma_q(ctx, g));
+          continue;
+        }
+        g.W = (char*)S.wqkv + (size_t)(qd + which * kvd) * D * m->esz;
         if (c.bf16) TRY((launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g)));
         else TRY((launch_gemm_simt<float, float>(ctx, g)));
       }
@@ -1212,7 +1299,7 @@ int32_t vn_model_destroy(vn_model* m) {
   F(m->anc_dev); F(m->rows_dev); F(m->stage); F(m->hs); F(m->partial); F(m->tc_error); F(m->stack_bar); F(m->row_seg); F(m->sub_seg); F(m->head_q); F(m->head_qs);
   for (auto& L : m->layers) for (int i = 0; i < 6; ++i) { F(L.q[i]); F(L.qs[i]); }
   for (auto& L : m->layers)
-    for (auto& S : L.sub) { F(S.wqkv); F(S.w_up); F(S.sink); F(S.sink_k); F(S.sink_v); F(S.head_gate); F(S.head_w); F(S.w_abs); }
+    for (auto& S : L.sub) { F(S.wqkv); F(S.w_up); F(S.sink); F(S.sink_k); F(S.sink_v); F(S.head_gate); F(S.head_w); F(S.w_abs); F(S.q[0]); F(S.q[1]); F(S.qs[0]); F(S.qs[1]); }
   F(m->lat); F(m->mix);
   delete m;
   return VN_OK;
@@ -1410,7 +1497,7 @@ int32_t vn_model_finalize(vn_model* m) {
     const long long lat = c.latent;
     for (auto& L : m->layers)
       for (auto& S : L.sub) {
-        if (S.mode != 2 || !c.bf16 || !absorb_on || S.w_abs) continue;
+        if (S.mode != 2 || !c.bf16 || !absorb_on || S.w_abs || pm) continue;
         if ((double)2 * kvd * D > 1.25 * (double)lat * (D + 2 * kvd)) continue;   // a narrow latent: two small GEMMs read less
         TRY(dev_alloc(ctx, &S.w_abs, (size_t)(qd + 2 * kvd) * D * m->esz));
         VN_CUDA(ctx, cudaMemcpyAsync(S.w_abs, S.wqkv, (size_t)qd * D * m->esz, cudaMemcpyDeviceToDevice, ctx->stream));
@@ -1439,17 +1526,17 @@ int32_t vn_model_finalize(vn_model* m) {
     uint64_t bytes = 0;
     auto add = [&](long long rows, long long K) { bytes += (uint64_t)rows * (q_row_bytes(pm, K) + q_row_scales(pm, K) * 4); };
     for (auto& L : m->layers) {
-      add(qd + 2 * kvd, D); add(D, qd);
-      if (L.kind == 0) { add(2ll * c.mlp_hidden, D); add(D, c.mlp_hidden); }
+      if (!is_delta(L.kind)) add(qd + 2 * kvd, D);
+      for (auto& S : L.sub) {
+        add(S.mode == 2 ? qd + c.latent : qd + 2 * kvd, D);
+        if (S.mode == 2) add(2 * kvd, c.latent);
+      }
+      add(D, qd);
+      if (L.kind != 1) { add(2ll * c.mlp_hidden, D); add(D, c.mlp_hidden); }
       else { const long long ne = (long long)c.P * c.E; add(ne * 2 * c.expert_hidden, D); add(ne * D, c.expert_hidden); }
     }
     add(c.vocab, D);
-    uint64_t keep = (uint64_t)c.vocab * D * m->esz + (uint64_t)D * 4;
-    for (auto& L : m->layers) {
-      keep += 2ull * D * 4 + (uint64_t)c.n_sink * D * m->esz;
-      if (L.kind == 1) keep += (uint64_t)(c.P + c.P * c.E) * D * 4;
-    }
-    m->param_bytes = keep + bytes;
+    m->param_bytes = dense_keep_bytes(m) + bytes;
     m->qmode = pm;
     { const char* e = getenv("VN_GEMM_TCQ"); if (e && e[0] == '0') m->use_tc = false; }
   }
@@ -1491,7 +1578,6 @@ int32_t vn_model_quantize(vn_model* m, const char* scheme) {
   const std::string s(scheme);
   const int mode = s == "int8" ? 1 : (s == "int4" ? 2 : (s == "int4g128" ? 3 : 0));
   VN_REQUIRE(ctx, mode != 0, "unknown quantisation scheme %s (int8 | int4 | int4g128)", scheme);
-  if (m->has_delta) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "weight-only quantisation of vda / dsa / kda / gmla layers is not built");
   VN_REQUIRE(ctx, m->finalized, "quantise after vn_model_finalize");
   VN_REQUIRE(ctx, m->qmode == 0, "model is already quantised");
   if (!m->cfg.bf16) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "weight-only quantisation needs a bf16 model");
@@ -1501,9 +1587,17 @@ int32_t vn_model_quantize(vn_model* m, const char* scheme) {
   // every Linear of the blocks and the LM head (verse_torch/compress.py:807-822 swaps every Linear and gives
   // the tied head its own quantised copy); the router gates and the embedding table stay dense
   for (auto& L : m->layers) {
-    TRY(quantize_matrix(m, &L.wqkv, qd + 2 * kvd, (int)D, mode, &L.q[0], &L.qs[0], true, &bytes));
+    if (!is_delta(L.kind)) TRY(quantize_matrix(m, &L.wqkv, qd + 2 * kvd, (int)D, mode, &L.q[0], &L.qs[0], true, &bytes));
+    for (auto& S : L.sub) {
+      // a module's stacked projections as they are; a GMLA module goes back to its two projections (the folded
+      // matrix is a product of the dense factors and is dropped)
+      TRY(quantize_matrix(m, &S.wqkv, S.mode == 2 ? qd + c.latent : qd + 2 * kvd, (int)D, mode, &S.q[0], &S.qs[0], true, &bytes));
+      if (S.mode == 2) TRY(quantize_matrix(m, &S.w_up, 2 * kvd, c.latent, mode, &S.q[1], &S.qs[1], true, &bytes));
+      S.w_down = nullptr;
+      if (S.w_abs) { VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); VN_CUDA(ctx, cudaFree(S.w_abs)); S.w_abs = nullptr; }
+    }
     TRY(quantize_matrix(m, &L.wproj, D, (int)qd, mode, &L.q[1], &L.qs[1], true, &bytes));
-    if (L.kind == 0) {
+    if (L.kind != 1) {
       TRY(quantize_matrix(m, &L.w_gateup, 2ll * c.mlp_hidden, (int)D, mode, &L.q[2], &L.qs[2], true, &bytes));
       TRY(quantize_matrix(m, &L.w_down, D, c.mlp_hidden, mode, &L.q[3], &L.qs[3], true, &bytes));
     } else {
@@ -1522,12 +1616,7 @@ int32_t vn_model_quantize(vn_model* m, const char* scheme) {
   // VN_GEMM_TCQ=0 in the environment: keep the quantised mma.sync GEMMs instead of the tcgen05 ones
   { const char* e = getenv("VN_GEMM_TCQ"); if (e && e[0] == '0') m->use_tc = false; }
   // embedding + norms + routers + sinks stay as they were
-  uint64_t keep = (uint64_t)c.vocab * D * m->esz + (uint64_t)D * 4;
-  for (auto& L : m->layers) {
-    keep += 2ull * D * 4 + (uint64_t)c.n_sink * D * m->esz;
-    if (L.kind == 1) keep += (uint64_t)(c.P + c.P * c.E) * D * 4;
-  }
-  m->param_bytes = keep + bytes;
+  m->param_bytes = dense_keep_bytes(m) + bytes;
   return VN_OK;
 }
 
@@ -1568,7 +1657,6 @@ int32_t vn_model_load_quant_tensor(vn_model* m, const char* name, const char* sc
   const int mode = scheme_mode(scheme);
   VN_REQUIRE(ctx, mode != 0, "unknown quantisation scheme %s (int8 | int4 | int4g128)", scheme ? scheme : "(null)");
   if (!m->cfg.bf16) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised linears need a bf16 model");
-  if (m->has_delta) return vn_fail(ctx, VN_ERR_UNSUPPORTED, "quantised linears of vda / dsa / kda / gmla layers are not built");
   VN_REQUIRE(ctx, m->qmode == 0, "the model is already quantised");
   VN_REQUIRE(ctx, m->preq_mode == 0 || m->preq_mode == mode, "%s: one scheme per model (linears so far arrived as scheme %d)", name, m->preq_mode);
   const std::string n(name);
@@ -1584,8 +1672,8 @@ int32_t vn_model_load_quant_tensor(vn_model* m, const char* name, const char* sc
     }
     TRY(alloc_quant(m, mode));
   }
-  unsigned char* q = (unsigned char*)(ls.layer < 0 ? m->head_q : m->layers[ls.layer].q[ls.slot]);
-  float* qs = ls.layer < 0 ? m->head_qs : m->layers[ls.layer].qs[ls.slot];
+  unsigned char* q = (unsigned char*)slot_q(m, ls);
+  float* qs = slot_qs(m, ls);
   const size_t rb = q_row_bytes(mode, K), sb = q_row_scales(mode, K) * 4;
   VN_CUDA(ctx, cudaMemcpy2DAsync(q + (size_t)(ls.base + ls.row_off) * rb, (size_t)ls.row_mul * rb, packed, rb, rb, (size_t)rows,
                                  cudaMemcpyHostToDevice, ctx->stream));
@@ -1611,8 +1699,8 @@ int32_t vn_model_read_quant(vn_model* m, const char* name, void* q_host, size_t 
   VN_REQUIRE(ctx, q_bytes == (size_t)ls.rows * rb && n_scales * 4 == (size_t)ls.rows * sb,
              "%s: buffers of %zu bytes / %zu scales, expected %zu / %zu", name, q_bytes, n_scales,
              (size_t)ls.rows * rb, (size_t)ls.rows * sb / 4);
-  const unsigned char* q = (const unsigned char*)(ls.layer < 0 ? m->head_q : m->layers[ls.layer].q[ls.slot]);
-  const float* qs = ls.layer < 0 ? m->head_qs : m->layers[ls.layer].qs[ls.slot];
+  const unsigned char* q = (const unsigned char*)slot_q(m, ls);
+  const float* qs = slot_qs(m, ls);
   VN_REQUIRE(ctx, q && qs, "%s has no quantised copy", name);
   VN_CUDA(ctx, cudaMemcpy2DAsync(q_host, rb, q + (size_t)(ls.base + ls.row_off) * rb, (size_t)ls.row_mul * rb, rb,
                                  (size_t)ls.rows, cudaMemcpyDeviceToHost, ctx->stream));

@@ -11,7 +11,7 @@ Differences that the device path brings (all additive):
     float32);
   * layers of the delta attention kinds ("vda", "dsa", "kda", "gmla", verse_nex/delta_attention.py) compute the
     whole-sequence forward of those classes on the cache (masks from absolute positions; a GMLA module caches the
-    K / V rebuilt from its latents); weight-only quantisation of such layers is not available;
+    K / V rebuilt from its latents);
   * `new_cache()` returns a `KVCache`; `forward_cached` runs T new positions
     (a chain, or a tree given `parents`) on top of it, which is what
     `SpeculativeDecoder.verify` re-computes from scratch in the reference
@@ -324,8 +324,10 @@ class VerseNexLM:
             return self.vocab_size, D
         if ".experts." in name:
             return {"w_gate": (eh, D), "w_up": (eh, D), "w_down": (D, eh)}[leaf]
+        lat = self.latent_dim or kvd
         table = {"wq": (qd, D), "wk": (kvd, D), "wv": (kvd, D), "proj": (D, qd), "w_gate": (int(hidden), D),
-                 "w_up": (int(hidden), D), "w_down": (D, int(hidden))}
+                 "w_up": (int(hidden), D), "w_down": (D, int(hidden)),
+                 "w_kv_down": (lat, D), "w_k_up": (kvd, lat), "w_v_up": (kvd, lat)}      # GMLA (delta_attention.py:861-863)
         if leaf not in table:
             raise ValueError(f"{name} is not a linear of this model")
         return table[leaf]
