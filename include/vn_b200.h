@@ -379,6 +379,22 @@ int32_t vn_tree_accept_greedy(vn_ctx* ctx, const int64_t* tokens_dev, const int6
                               int32_t B, int32_t T, int32_t depth, int32_t* out_len_dev, int64_t* out_tokens_dev,
                               int32_t* keep_target_dev, int32_t* keep_draft_dev);
 
+/* Stochastic acceptance on a verified tree (temperature > 0; no counterpart in the reference).  The children of a
+ * node are fixed proposals (vn_top_m), so the test is rejection sampling with point-mass proposals applied child after
+ * child: child c with token x is accepted iff u * R < p(x), R = the mass not yet rejected at that row; a rejected x
+ * leaves the support.  Every committed token then has exactly its target probability p(x) -- p = softmax(logits / T)
+ * over the top-k set, read from the rows' kept lists.  Where no child is accepted, or the path is `depth` long, the
+ * row's own token is drawn from p without the rejected children.
+ *   lists_dev: [B * T] records left by vn_sample_lists on the target's logits of all T rows (row 0 = after the last
+ *   committed token, row r = after node row r); tokens_dev [B, T], parent_dev [T] as for vn_tree_accept_greedy; a
+ *   row has at most 8 children.  u_child_dev / u_sample_dev [B, T]: injected uniforms (tests), or both NULL: Philox
+ *   (seed, offset + the device round counter; row b, position = row index, purpose 0 for a child's test, 1 for the
+ *   final draw).  Outputs as vn_tree_accept_greedy. */
+int32_t vn_tree_accept_sample(vn_ctx* ctx, const void* lists_dev, const int64_t* tokens_dev, const int32_t* parent_dev,
+                              int32_t B, int32_t T, int32_t depth, const float* u_child_dev, const float* u_sample_dev,
+                              uint64_t seed, uint32_t offset, int32_t* out_len_dev, int64_t* out_tokens_dev,
+                              int32_t* keep_target_dev, int32_t* keep_draft_dev);
+
 /* Device-side round counter: while set, every Philox offset passed to vn_accept* / vn_sample is
  * incremented by *counter_dev, and vn_spec_advance adds one to it at the end of a round. */
 int32_t vn_set_offset_source(vn_ctx* ctx, const uint32_t* counter_dev);

@@ -146,3 +146,57 @@ def make_cfg2_inputs(batch=64, k=4, vocab=248320, seed=1234):
             pr = softmax64(q[b, i])
             draft[b, i] = _inverse_cdf(pr, float(rng.random()))
     return p, q, draft
+
+
+def tree_accept_stochastic(p_logits, tokens, parent_rows, depth, u_child, u_sample,
+                           temperature: float = 1.0, top_k: int = 0):
+    """Stochastic acceptance on a verified tree whose children are FIXED proposals (the draft's m best tokens at a
+    node, distinct, in order) -- no counterpart in the reference ("parity unpinned"); the rule is rejection sampling
+    with point-mass proposals, applied child after child:
+
+      at a row with target distribution p (softmax of logits / T over the top-k set, as in `softmax64`), remaining
+      mass R = 1: child c with token x is accepted iff u_child[b, c] * R < p(x); otherwise x leaves the support
+      (R -= p(x)) and the next child is tried.  P(first child) = p(x1), P(second) = (1 - p(x1)) * p(x2) / (1 - p(x1))
+      = p(x2), ...: every token is committed with exactly its target probability.  When no child is accepted, or the
+      row has none, the row's token is drawn from p without the rejected children (inverse CDF over ascending token
+      ids with u_sample[b, row]) and the walk ends.
+
+    p_logits [B, T, V]: row 0 = after the last committed token, row r = after node row r; tokens [B, T] (row 0 is
+    the last committed token itself); parent_rows [T]: parent row of every row (-1 for row 0); u_child, u_sample
+    [B, T].  Returns (accept_len [B], tokens [B, depth + 1] padded with -1, path rows [B, depth + 1] padded with 0)."""
+    tokens = np.asarray(tokens)
+    B, T = tokens.shape
+    acc = np.zeros(B, dtype=np.int32)
+    out = np.full((B, depth + 1), -1, dtype=np.int64)
+    path = np.zeros((B, depth + 1), dtype=np.int32)
+    for b in range(B):
+        cur, a = 0, 0
+        while True:
+            p = softmax64(p_logits[b, cur], temperature, top_k)
+            R = np.float64(1.0)
+            removed = []
+            took = -1
+            if a < depth:
+                for c in range(cur + 1, T):
+                    if parent_rows[c] != cur:
+                        continue
+                    x = int(tokens[b, c])
+                    if np.float64(u_child[b, c]) * R < p[x]:
+                        took = c
+                        break
+                    removed.append(x)
+                    R = R - p[x]
+            if took >= 0:
+                out[b, a] = tokens[b, took]
+                a += 1
+                path[b, a] = took
+                cur = took
+                continue
+            r = p.copy()
+            r[removed] = 0.0
+            if r.sum() <= 0.0:
+                r = p
+            out[b, a] = _inverse_cdf(r, float(u_sample[b, cur]))
+            break
+        acc[b] = a
+    return acc, out, path

@@ -81,6 +81,7 @@ PROTOTYPES = {
     "vn_sample": [_p, _p, _i64, _i32, _i32, _f32, _i32, _p, _u64, _u32, _u32, _u32, _p],
     "vn_top_m": [_p, _p, _i64, _i32, _i32, _i32, _p, _i64],
     "vn_tree_accept_greedy": [_p, _p, _p, _p, _i32, _i32, _i32, _p, _p, _p, _p],
+    "vn_tree_accept_sample": [_p, _p, _p, _p, _i32, _i32, _i32, _p, _p, _u64, _u32, _p, _p, _p, _p],
     "vn_draft_propose": [_p, _p, _p, _i32, _i32, _f32, _i32, _u64, _u32, _p, _p, _p],
     "vn_sample_lists": [_p, _p, _i64, _i32, _i32, _f32, _i32, _p, _u64, _u32, _u32, _u32, _p, _p],
     "vn_topk_row_bytes": [],

@@ -1091,6 +1091,126 @@ accept_topk_decide_kernel(DecideArgs da) {
 }
 
 
+// ---- stochastic acceptance on a verified tree with FIXED proposals -------------------------------------------
+// The children of a node are given tokens (the draft's best ones, distinct, in order), so the test is rejection
+// sampling with point-mass proposals, child after child: at a row with target distribution p (its kept list) and
+// remaining mass R = 1, child c with token x is accepted iff u * R < p(x); otherwise x leaves the support
+// (R -= p(x)) and the next child is tried -- the first child is taken with probability p(x1), the second with
+// (1 - p(x1)) * p(x2) / (1 - p(x1)) = p(x2), and so on: every committed token has exactly its target probability.
+// Where no child is accepted (or the row has none, or the path is `depth` long) the row's token is drawn from p
+// without the rejected children: inverse CDF over ascending token ids, float64 sums, as in topk_decide_seq.
+// One warp per sequence.  Row 0 = after the last committed token, row r = after node row r; outputs as
+// tree_accept_greedy_kernel's (engine.cu).  A row may have at most TREE_CHILD_MAX children.
+constexpr int TREE_CHILD_MAX = 8;
+
+struct TreeSampleArgs {
+  const TopkRow* rows;       // [B * T] kept lists of the target rows
+  const long long* tokens;   // [B, T]
+  const int* parent;         // [T] parent row (-1 for row 0)
+  const float* u_child;      // [B, T] injected uniforms of the child tests, or null: Philox (row b, position c, purpose 0)
+  const float* u_sample;     // [B, T] injected uniforms of the final draw, or null: Philox (row b, position row, purpose 1)
+  uint64_t seed;
+  uint32_t offset_host;
+  const unsigned* offset_dev;
+  int B, T, depth;
+  int* out_len;
+  long long* out_tok;        // [B, depth + 1]
+  int* keep_t;               // [B, depth + 1]
+  int* keep_d;
+};
+
+__global__ void __launch_bounds__(128) tree_accept_sample_kernel(TreeSampleArgs ta) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b >= ta.B) return;
+  const int T = ta.T, depth = ta.depth;
+  const uint32_t offset = ta.offset_host + (ta.offset_dev ? *ta.offset_dev : 0u);
+  const long long* tok = ta.tokens + (long long)b * T;
+  long long* ot = ta.out_tok + (long long)b * (depth + 1);
+  int* kt = ta.keep_t + (long long)b * (depth + 1);
+  int* kd = ta.keep_d + (long long)b * (depth + 1);
+  for (int i = lane; i <= depth; i += 32) { ot[i] = -1; kt[i] = 0; kd[i] = (i == 1) ? 1 : 0; }
+  __syncwarp();
+  int cur = 0, a = 0;
+  for (;;) {
+    const TopkRow* rp = ta.rows + (long long)b * T + cur;
+    ListView P;
+    P.tok = rp->tok; P.val = rp->val; P.n = rp->n;
+    float mp; double sp;
+    list_stats(P, lane, mp, sp);
+    double R = 1.0;
+    int removed[TREE_CHILD_MAX];
+    int n_removed = 0, took = -1;
+    long long took_tok = -1;
+    if (a < depth) {
+      for (int c = cur + 1; c < T; ++c) {
+        if (ta.parent[c] != cur) continue;
+        const long long x = tok[c];
+        const float v = list_value(P, lane, (int)x);
+        const double px = v == -CUDART_INF_F ? 0.0 : (double)expf(v - mp) / sp;
+        const float u = ta.u_child ? ta.u_child[(long long)b * T + c] : philox_uniform(ta.seed, offset, b, c, 0);
+        if ((double)u * R < px) { took = c; took_tok = x; break; }
+        if (n_removed < TREE_CHILD_MAX) removed[n_removed++] = (int)x;
+        R -= px;
+      }
+    }
+    if (took >= 0) {
+      if (lane == 0) {
+        ot[a] = took_tok;
+        kt[a + 1] = took;
+        if (a + 2 <= depth) kd[a + 2] = took + 1;
+      }
+      cur = took;
+      ++a;
+      continue;
+    }
+    const float u = ta.u_sample ? ta.u_sample[(long long)b * T + cur] : philox_uniform(ta.seed, offset, b, cur, 1);
+    const int nchunk = (P.n + 31) >> 5;
+    for (int pass = 0; pass < 2; ++pass) {
+      // pass 0: p without the rejected children; pass 1, only when nothing is left of it: p itself
+      auto weight = [&](int i) -> double {
+        if (i >= P.n) return 0.0;
+        const int t = P.tok[i];
+        if (pass == 0)
+          for (int r = 0; r < n_removed; ++r)
+            if (removed[r] == t) return 0.0;
+        return (double)expf(P.val[i] - mp) / sp;
+      };
+      double Z = 0.0;
+      for (int c = 0; c < nchunk; ++c) Z += weight(c * 32 + lane);
+      Z = warp_sum(Z);
+      if (!(Z > 0.0)) continue;
+      const double target = (double)u * Z;
+      double run = 0.0;
+      int pick = -1, last_nz = -1;
+      for (int c = 0; c < nchunk && pick < 0; ++c) {
+        const int i = c * 32 + lane;
+        const double w = weight(i);
+        double cum = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const double up = __shfl_up_sync(0xffffffffu, cum, o);
+          if (lane >= o) cum += up;
+        }
+        cum += run;
+        const unsigned hit = __ballot_sync(0xffffffffu, i < P.n && cum > target);
+        const unsigned nz = __ballot_sync(0xffffffffu, i < P.n && w > 0.0);
+        if (nz) last_nz = c * 32 + (31 - __clz(nz));
+        if (hit) pick = c * 32 + (__ffs(hit) - 1);
+        run = __shfl_sync(0xffffffffu, cum, 31);
+      }
+      if (pick < 0) pick = last_nz;
+      if (lane == 0 && pick >= 0) ot[a] = P.tok[pick];
+      break;
+    }
+    break;
+  }
+  if (lane == 0 && ta.out_len) ta.out_len[b] = a;
+}
+
+
 // ---- fused LM head: bound, finish ---------------------------------------------------------------------------
 // One CTA per target row.  Every thread takes the maximum of its share of the row's first nb logits; the k-th
 // largest of those per-thread maxima is a lower bound of the k-th largest of the subset (they are k distinct
@@ -1906,6 +2026,23 @@ int32_t vn_sample_lists(vn_ctx* ctx, const float* logits_dev, int64_t row_stride
 }
 
 size_t vn_topk_row_bytes(void) { return vn_topk_row_bytes_impl(); }
+
+int32_t vn_tree_accept_sample(vn_ctx* ctx, const void* lists_dev, const int64_t* tokens_dev, const int32_t* parent_dev,
+                              int32_t B, int32_t T, int32_t depth, const float* u_child_dev, const float* u_sample_dev,
+                              uint64_t seed, uint32_t offset, int32_t* out_len_dev, int64_t* out_tokens_dev,
+                              int32_t* keep_target_dev, int32_t* keep_draft_dev) {
+  VN_CHECK_CTX(ctx);
+  VN_REQUIRE(ctx, lists_dev && tokens_dev && parent_dev && out_tokens_dev && keep_target_dev && keep_draft_dev && B >= 1 &&
+             T >= 1 && T <= 64 && depth >= 1 && depth < T, "vn_tree_accept_sample: bad arguments");
+  VN_REQUIRE(ctx, (u_child_dev == nullptr) == (u_sample_dev == nullptr), "inject both uniform arrays or neither");
+  TreeSampleArgs ta;
+  ta.rows = (const TopkRow*)lists_dev; ta.tokens = (const long long*)tokens_dev; ta.parent = parent_dev;
+  ta.u_child = u_child_dev; ta.u_sample = u_sample_dev; ta.seed = seed; ta.offset_host = offset; ta.offset_dev = ctx->offset_src;
+  ta.B = B; ta.T = T; ta.depth = depth; ta.out_len = out_len_dev; ta.out_tok = (long long*)out_tokens_dev;
+  ta.keep_t = keep_target_dev; ta.keep_d = keep_draft_dev;
+  VN_LAUNCH_PDL(ctx, tree_accept_sample_kernel, ceil_div(B, 4), 128, 0, ta);
+  return VN_OK;
+}
 
 }  // extern "C"
 

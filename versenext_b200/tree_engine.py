@@ -1,4 +1,4 @@
-"""Speculative decoding with TREE proposals (greedy rule).
+"""Speculative decoding with TREE proposals (greedy rule, or stochastic with `temperature > 0`).
 
 A round: the draft model expands a fixed tree under every request's last committed token -- the children of a node
 are the draft's m most likely next tokens there, m = the node's number of children -- the target scores all nodes
@@ -6,6 +6,13 @@ in one forward (ancestor bit mask, `parents=` of `vn_model_forward`), and `vn_tr
 root along the children that carry the target's own arg-max.  The committed tokens are by construction the target's
 greedy continuation: the stream equals `VerseNexLM.generate(..., temperature=0)` of the target alone, whatever the
 draft and the tree (what the reference's greedy rule guarantees for a chain, speculative.py:280-287).
+
+With `temperature > 0` (and `0 < top_k < vocab`) the walk is stochastic: the children of a node are still the draft's
+m best tokens, i.e. FIXED proposals, so a child is tested by rejection sampling with a point-mass proposal -- child
+with token x accepted iff u * R < p(x), R the target mass not yet rejected at that node -- and where no child passes
+the node's token is drawn from the target's distribution without the rejected children (`vn_tree_accept_sample`).
+Every committed token then has exactly the probability the target alone (softmax(logits / T) over its top-k set)
+gives it.
 
 Everything stays on the device (tokens, arg-max, path, cache commits), so after the first, eager round the launch
 sequence is replayed from a CUDA graph like the chain engine's (the draft's per-level trees are the first nodes of one
@@ -29,7 +36,7 @@ from .model import _ptr
 
 class TreeSpecEngine(SpecEngine):
     def __init__(self, target, draft, parents: Sequence[int], max_batch: int, max_seq: int,
-                 max_new_tokens: int = 4096, graph: bool = True):
+                 max_new_tokens: int = 4096, graph: bool = True, temperature: float = 0.0, top_k: int = 0, seed: int = 0):
         parents = [int(p) for p in parents]
         n = len(parents)
         if n < 1 or n > 63:
@@ -50,9 +57,12 @@ class TreeSpecEngine(SpecEngine):
             if len(ks) > 8:
                 raise ValueError("at most 8 children per node")
         D = max(depth)
-        super().__init__(target, draft, max_batch, max_seq, k=D, temperature=0.0, top_k=0, seed=0, bonus=True,
+        super().__init__(target, draft, max_batch, max_seq, k=D, temperature=0.0, top_k=0, seed=int(seed), bonus=True,
                          max_new_tokens=max_new_tokens, graph=graph)
         ctx, B, V = self.ctx, self.B, self.V
+        self.tree_temperature, self.tree_top_k = float(temperature), int(top_k or 0)
+        if self.tree_temperature > 0 and not (0 < self.tree_top_k < V):
+            raise ValueError("stochastic tree acceptance works on the top-k lists: 0 < top_k < vocab_size is needed")
         self.parents, self.depth, self.kids, self.n_nodes, self.D = parents, depth, kids, n, D
         self.T = n + 1                                   # verify rows per request: last committed token + the nodes
         self.n_verify = self.T                           # what a round appends to the target cache before the commit
@@ -67,6 +77,9 @@ class TreeSpecEngine(SpecEngine):
         self.keep_t = ctx.zeros((B, D + 1), np.int32)
         self.keep_d = ctx.zeros((B, D + 1), np.int32)
         self.parent_rows = ctx.from_numpy(np.array([-1] + [p + 1 for p in parents], np.int32))
+        if self.tree_temperature > 0:     # kept top-k lists of all target rows, and the (unused) per-row draws
+            self.p_lists = ctx.empty((B * self.T * self.row_bytes,), np.uint8)
+            self.row_draw = ctx.zeros((B * self.T,), np.int64)
         self.q_logits = None                             # the chain engine's proposal buffers are not used
         self.step_tokens = self.draft_tokens = None
         # per level: the tokens of the nodes known so far (depth <= level), a fixed buffer so that a graph can hold it
@@ -74,6 +87,14 @@ class TreeSpecEngine(SpecEngine):
 
     # -- one round -----------------------------------------------------------------
     def _issue_round(self, draft_part: bool = True):
+        ctx, lib = self.ctx, self.ctx.lib
+        ctx._check(lib.vn_set_offset_source(ctx.handle, _ptr(self.round_dev)))     # fresh Philox numbers every round
+        try:
+            self._issue_tree_round(draft_part)
+        finally:
+            ctx._check(lib.vn_set_offset_source(ctx.handle, None))
+
+    def _issue_tree_round(self, draft_part: bool = True):
         ctx, lib, B, V, n, T, D = self.ctx, self.ctx.lib, self.B, self.V, self.n_nodes, self.T, self.D
         i64 = 8
         if draft_part:
@@ -102,11 +123,19 @@ class TreeSpecEngine(SpecEngine):
                                   n * i64, n * i64, B))
         self.target.forward_cached(self.verify_tokens, self.t_cache, parents=[-1] + [p + 1 for p in self.parents],
                                    out_logits=self.p_logits)
-        ctx._check(lib.vn_sample(ctx.handle, _ptr(self.p_logits), V, B * T, V, 0.0, 0, None, 0, 0, 0, 0,
-                                 _ptr(self.target_arg)))
-        ctx._check(lib.vn_tree_accept_greedy(ctx.handle, _ptr(self.verify_tokens), _ptr(self.target_arg),
-                                             _ptr(self.parent_rows), B, T, D, _ptr(self.accept_len), _ptr(self.out_tokens),
-                                             _ptr(self.keep_t), _ptr(self.keep_d)))
+        if self.tree_temperature > 0:
+            ctx._check(lib.vn_sample_lists(ctx.handle, _ptr(self.p_logits), V, B * T, V, self.tree_temperature,
+                                           self.tree_top_k, None, self.seed, 0, 0, 7, _ptr(self.row_draw), _ptr(self.p_lists)))
+            ctx._check(lib.vn_tree_accept_sample(ctx.handle, _ptr(self.p_lists), _ptr(self.verify_tokens),
+                                                 _ptr(self.parent_rows), B, T, D, None, None, self.seed, 0,
+                                                 _ptr(self.accept_len), _ptr(self.out_tokens), _ptr(self.keep_t),
+                                                 _ptr(self.keep_d)))
+        else:
+            ctx._check(lib.vn_sample(ctx.handle, _ptr(self.p_logits), V, B * T, V, 0.0, 0, None, 0, 0, 0, 0,
+                                     _ptr(self.target_arg)))
+            ctx._check(lib.vn_tree_accept_greedy(ctx.handle, _ptr(self.verify_tokens), _ptr(self.target_arg),
+                                                 _ptr(self.parent_rows), B, T, D, _ptr(self.accept_len),
+                                                 _ptr(self.out_tokens), _ptr(self.keep_t), _ptr(self.keep_d)))
         ctx._check(lib.vn_spec_advance(ctx.handle, _ptr(self.out_tokens), B, D, _ptr(self.pair), _ptr(self.history),
                                        self.cap, _ptr(self.count), _ptr(self.n_commit)))
         # both caches keep (accepted + 1) of the entries appended this round: the accepted path, compacted in place
