@@ -877,6 +877,8 @@ def run_delta(args):
     tk, dk = delta_kwargs(), S.draft_kwargs()
     target = vn.VerseNexLM(dtype="bf16", device=f"cuda:{local}", **tk)
     S.load_random(target, tk, seed=0)
+    if args.quant:                       # the shipped preset's weight-only INT4 (or INT8) on the same layers
+        target.quantize(args.quant)
     draft = vn.VerseNexLM(dtype="bf16", device=f"cuda:{local}", **dk)
     S.load_random(draft, dk, seed=1)
     warm = max(args.warmup, 3)
@@ -928,6 +930,8 @@ def run_delta(args):
     params = S.param_count(tk)
     n_mod = sum(3 if kind == "vda" else 1 for kind in tk["layer_pattern"])
     nbytes = params * 2 + n_mod * B * min(ctx_len, 1024) * 2 * 512 * 2
+    if args.quant:                       # streamed weights: what the quantised model holds, minus the embedding table
+        nbytes += target.param_bytes() - 248320 * 1024 * 2 - params * 2
     peak, peak_kind = peaks()
     achieved = nbytes / (step_ms * 1e-3) / 1e9
     top = sorted(rep.items(), key=lambda kv: -kv[1]["ms"])
@@ -948,7 +952,8 @@ def run_delta(args):
             "metric": "accepted tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": DELTA_WORKLOAD, "requests": B, "l2": "weights (2.7 GB) larger than L2, no flush",
+            "config": {"workload": DELTA_WORKLOAD + (f", target weights {args.quant}" if args.quant else ""), "requests": B,
+                       "l2": "weights and K / V read per step (2.7 GB dense) larger than L2, no flush",
                        "step": "one speculative round over the batch"},
             "timing": spread(reps, args.steps), "context_tokens": ctx_len, "target_params": params,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": None, "gpu_launches": launches, "clocks": clk,
