@@ -773,6 +773,25 @@ def run_tree(args):
                        "accepted_tok_s": committed * world / (t_ms * args.steps * 1e-3),
                        "what": "TreeSpecEngine round: draft tree expansion (3 levels) + target forward over 17 rows per "
                                "request + greedy path acceptance + cache commits, B = 8, context 2048"}
+        # the same round with the stochastic walk (T = 0.8, top-k 50: top-k lists of all 136 target rows + rejection
+        # sampling with fixed proposals)
+        del eng
+        eng = vn.TreeSpecEngine(target, draft, parents, max_batch=B, max_seq=T0 + rounds * 4 + 64,
+                                max_new_tokens=rounds * 4, temperature=0.8, top_k=50, seed=3)
+        eng.prefill(prompt)
+        for _ in range(warm):
+            eng.step()
+        c0 = int(eng.counts().sum())
+        e0, e1 = ctx.event(), ctx.event()
+        e0.record()
+        for _ in range(args.steps):
+            eng.step()
+        e1.record()
+        barrier_sync(dist, ctx)
+        t_ms = max_over_ranks(dist, e0.elapsed_ms(e1), local) / args.steps
+        committed = int(eng.counts().sum()) - c0
+        tree_engine["stochastic"] = {"ms_per_round": t_ms, "tokens_per_round_per_request": committed / (args.steps * B),
+                                     "temperature": 0.8, "top_k": 50}
     if rank == 0:
         print(json.dumps({
             "metric": "verified tree nodes/s", "value": B * n * world * args.steps / (ms * 1e-3), "unit": "nodes/s",
