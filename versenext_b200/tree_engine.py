@@ -19,7 +19,7 @@ sequence is replayed from a CUDA graph like the chain engine's (the draft's per-
 tree, whose masks a model uploads once).
 
 `parents` describes the tree in breadth-first order: parents[i] = index of node i's parent, -1 for the first level;
-depth never decreases along the list and the children of a node are consecutive.  BASELINE configuration 3's tree is
+depth never decreases along the list and the children of a node are consecutive.  The benchmark's 16-node tree is
 `[-1, -1, -1, -1, 0, 0, 1, 1, 4, 4, 5, 5, 6, 6, 7, 7]` (4 roots, two of them expanded twice over, depth 3).
 """
 
