@@ -209,6 +209,14 @@ def test_delta_and_trisparse_layers_in_one_model_bf16():
     spec = m.generate(toks[:2, :12], max_new_tokens=20, temperature=0.0, draft=d, k=3)
     np.testing.assert_array_equal(spec, plain)
     m.check()
+    # a tensor loaded again after the first finalize: what finalize derives from it (the folded GMLA matrix) follows
+    sd2 = dict(sd)
+    name = "blocks.3.attn.w_k_up.weight"
+    sd2[name] = OM.bf16_round(sd[name] * np.float32(-4.0))
+    m.load_tensor(name, sd2[name])
+    got = m(toks[:, :20]).data.numpy()
+    assert rel_err(got, OM.forward(sd2, cfg, toks[:, :20])[0]) < 2e-2
+    assert rel_err(got, want[:, :20]) > 4e-2            # and differs from what the old tensor gave
 
 
 @pytest.mark.parametrize("dtype,tol", [("f32", 1e-3), ("bf16", 2e-2)])

@@ -1497,9 +1497,10 @@ int32_t vn_model_finalize(vn_model* m) {
     const long long lat = c.latent;
     for (auto& L : m->layers)
       for (auto& S : L.sub) {
-        if (S.mode != 2 || !c.bf16 || !absorb_on || S.w_abs || pm) continue;
+        if (S.mode != 2 || !c.bf16 || !absorb_on || pm) continue;
         if ((double)2 * kvd * D > 1.25 * (double)lat * (D + 2 * kvd)) continue;   // a narrow latent: two small GEMMs read less
-        TRY(dev_alloc(ctx, &S.w_abs, (size_t)(qd + 2 * kvd) * D * m->esz));
+        // (built again on every finalize: tensors may have been loaded anew since the last one)
+        if (!S.w_abs) TRY(dev_alloc(ctx, &S.w_abs, (size_t)(qd + 2 * kvd) * D * m->esz));
         VN_CUDA(ctx, cudaMemcpyAsync(S.w_abs, S.wqkv, (size_t)qd * D * m->esz, cudaMemcpyDeviceToDevice, ctx->stream));
         GemmArgs g;       // C[2 kvd, D] = w_up[2 kvd, lat] x w_kv_down[lat, D]: the weight operand is read along its rows
         g.A = S.w_up; g.lda = lat; g.W = S.w_down; g.ldw = 1; g.ldw_k = D;
