@@ -402,6 +402,21 @@ def gen_vn():
     for f in ("model_tiny_st.vn", "model_tiny_npz.vn"):
         print(f"wrote {f}: {os.path.getsize(os.path.join(HERE, f)) / 1024:.1f} KiB")
     save("vn_reference.npz", **out)
+    # a model of delta attention layers through the same writer (names like blocks.0.attn.gmla.w_kv_down.weight,
+    # anchor_interval / latent_dim in config.yml)
+    from oracle import delta as OD
+    # (the writer takes window_size / use_alibi / ... from block 0's attention, cometspark.py:1238-1243, which only a
+    # TriSparse block has, and does not store anchor_interval / latent_dim: block 0 is TriSparse, those two keep
+    # their defaults)
+    cfg = OM.Config(vocab_size=64, dim=32, n_layer=3, n_head=2, n_kv_head=1, layer_pattern=["trisparse", "vda", "dsa"],
+                    window_size=8, num_global_tokens=3, use_alibi=False, use_rope=True, max_seq_len=64, init_std=0.2)
+    sd = OM.init_state_dict(cfg, seed=302, gate_std=1.0)
+    m = ref_model(cfg, sd)
+    toks = np.random.default_rng(302).integers(0, 64, (2, 21)).astype(np.int64)
+    out = {"tokens": toks, "logits": ref_forward(m, cfg, toks)}       # the weights are init_state_dict(cfg, seed=302)
+    m.save_vn(os.path.join(HERE, "model_tiny_delta.vn"))
+    print(f"wrote model_tiny_delta.vn: {os.path.getsize(os.path.join(HERE, 'model_tiny_delta.vn')) / 1024:.1f} KiB")
+    save("vn_delta_reference.npz", **out)
 
 
 # ---------------------------------------------------------------------------

@@ -65,3 +65,41 @@ def test_from_pretrained_matches_the_reference_forward(golden, name, tmp_path):
         vn.VerseNexLM.from_pretrained(str(tmp_path / "empty"))
     with pytest.raises(ValueError):
         vn.VerseNexLM.from_pretrained(str(tmp_path / "model.pt"))
+
+
+def _delta_vn_case():
+    from oracle import model as OM
+    cfg = OM.Config(vocab_size=64, dim=32, n_layer=3, n_head=2, n_kv_head=1, layer_pattern=["trisparse", "vda", "dsa"],
+                    window_size=8, num_global_tokens=3, use_alibi=False, use_rope=True, max_seq_len=64, init_std=0.2)
+    return cfg, OM.init_state_dict(cfg, seed=302, gate_std=1.0)
+
+
+def test_reader_on_a_file_with_delta_attention_layers(golden):
+    """A model with vda / dsa layers written by the reference's writer: names of the modules' tensors, layer kinds in
+    config.yml (the writer stores neither anchor_interval nor latent_dim: they come back as the defaults), and the
+    oracle's forward on what was read."""
+    from oracle import model as OM
+    g = golden("vn_delta_reference.npz")
+    cfg, sd = _delta_vn_case()
+    with VNFileReader(os.path.join(GOLDEN, "model_tiny_delta.vn")) as r:
+        r.read_meta()
+        conf = r.read_config()
+        got = r.read_weights()
+    assert conf["layer_pattern"] == ["trisparse", "vda", "dsa"] and "anchor_interval" not in conf
+    want = {n: w for n, w in sd.items() if not (n == "head.weight" and cfg.tie_weights)}
+    assert set(got) - {"head.weight"} == set(want) - {"head.weight"}
+    for n in ("blocks.1.attn.gmla.w_kv_down.weight", "blocks.1.attn.dsa.global_tokens.weight",
+              "blocks.1.attn.kda.wk.weight", "blocks.1.attn.gate_logits", "blocks.2.attn.head_gate_logits"):
+        np.testing.assert_array_equal(got[n], sd[n], err_msg=n)
+    lg, _ = OM.forward(sd, cfg, g["tokens"])
+    np.testing.assert_allclose(lg, g["logits"], rtol=2e-4, atol=2e-5)
+
+
+@pytest.mark.gpu
+def test_from_pretrained_with_delta_attention_layers(golden):
+    import versenext_b200 as vn
+    g = golden("vn_delta_reference.npz")
+    m = vn.VerseNexLM.from_pretrained(os.path.join(GOLDEN, "model_tiny_delta.vn"))
+    assert m.layer_pattern == ["trisparse", "vda", "dsa"] and m.anchor_interval == 128
+    got = np.asarray(m(g["tokens"]).data)
+    assert float(np.max(np.abs(got - g["logits"])) / np.max(np.abs(g["logits"]))) < 1e-3
