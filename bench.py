@@ -652,7 +652,9 @@ def run_reference_spec(args):
         return
     budget = 150.0
     warm = max(args.warmup, 0)
-    tps, secs, rounds = cpu_spec_sample(max_seconds=budget, rounds=max(1, args.steps), warmup=min(warm, 3))
+    delta = args.workload == "delta"            # the delta-attention target: same round, other target model
+    sampler = cpu_delta_sample if delta else cpu_spec_sample
+    tps, secs, rounds = sampler(max_seconds=budget, rounds=max(1, args.steps), warmup=min(warm, 3))
     threads = blas_threads()
     sample = (f"1 of the 32 requests per step, {rounds} rounds run inside a {budget:.0f} s budget ({min(warm, 3)} untimed "
               f"warm-up rounds); full re-forward of [context, draft] per round as the reference does; NumPy restatement "
@@ -662,7 +664,8 @@ def run_reference_spec(args):
         "impl": "reference", "metric": "accepted tok/s", "value": tps, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": rounds, "warmup": warm, "ms_per_step": secs / max(rounds, 1) * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": spec_config(args.quant),
+        "config": ({"workload": DELTA_WORKLOAD, "requests": SPEC["B"], "step": "one speculative round over the batch"}
+                   if delta else spec_config(args.quant)),
         "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
