@@ -110,6 +110,8 @@ struct SubAttn {
 struct Layer {
   int kind = 0;
   std::vector<SubAttn> sub;  // delta kinds only
+  void* w_vda = nullptr;     // vda, dense bf16: the three modules' q|k|v matrices (GMLA's folded one) stacked into
+                             // [3 (H + 2 n_kv) hd, D], so that the decode route projects all three with one GEMM
   float* norm1 = nullptr;
   float* norm2 = nullptr;
   float gate_logits[3] = {0.f, 0.f, 0.f};
@@ -820,6 +822,21 @@ int32_t delta_attention_tc(vn_model* m, vn_kv* kv, Layer& L, int B, int Tn, bool
   const long long cap = m->cap_rows;
   static const bool fuse_on = [] { const char* e = getenv("VN_ATTN_FUSE"); return !(e && e[0] == '0'); }();
   const int* depth = tree ? m->depth_dev : (const int*)nullptr;
+  if (L.w_vda && !m->qmode && fuse_on && Tn <= 64 && qkv_ld % 4 == 0) {
+    // one GEMM for the three modules' q | k | v; every module's attention CTAs reduce their own column block
+    int sp = 1;
+    GemmArgs g;
+    g.A = m->h; g.lda = D; g.W = L.w_vda; g.ldw = D; g.M = M; g.N = 3 * qkv_ld; g.K = D; g.tag = "gemm_qkv";
+    TRY(tc_partial(m, g, cap, M, &sp));
+    for (int si = 0; si < 3; ++si) {
+      AttnArgs a = delta_mma_args(m, kv, L, si, Tn, tree, slot_offset);
+      a.partial = m->partial + (size_t)si * qkv_ld; a.splits = sp; a.pstride = (long long)M * 3 * qkv_ld;
+      a.partial_ld = 3 * qkv_ld;
+      a.cos_t = m->rope_cos; a.sin_t = m->rope_sin; a.use_rope = c.use_rope; a.rope_rows = m->rope_rows;
+      TRY(launch_attn_mma(ctx, a, B));
+    }
+    return VN_OK;
+  }
   for (int si = 0; si < (int)L.sub.size(); ++si) {
     SubAttn& S = L.sub[si];
     AttnArgs a = delta_mma_args(m, kv, L, si, Tn, tree, slot_offset);
@@ -1300,6 +1317,7 @@ int32_t vn_model_destroy(vn_model* m) {
   for (auto& L : m->layers) for (int i = 0; i < 6; ++i) { F(L.q[i]); F(L.qs[i]); }
   for (auto& L : m->layers)
     for (auto& S : L.sub) { F(S.wqkv); F(S.w_up); F(S.sink); F(S.sink_k); F(S.sink_v); F(S.head_gate); F(S.head_w); F(S.w_abs); F(S.q[0]); F(S.q[1]); F(S.qs[0]); F(S.qs[1]); }
+  for (auto& L : m->layers) F(L.w_vda);
   F(m->lat); F(m->mix);
   delete m;
   return VN_OK;
@@ -1508,6 +1526,19 @@ int32_t vn_model_finalize(vn_model* m) {
         TRY((launch_gemm_simt<__nv_bfloat16, __nv_bfloat16>(ctx, g)));
       }
   }
+  // a vda layer's three projections as one matrix (VN_VDA_STACK=0 keeps three GEMMs)
+  {
+    const char* e = getenv("VN_VDA_STACK");
+    const bool stack_on = !(e && e[0] == '0');
+    const size_t one = (size_t)(qd + 2 * kvd) * D * m->esz;
+    for (auto& L : m->layers) {
+      if (L.kind != 2 || !c.bf16 || pm || !stack_on || !L.sub[2].w_abs) continue;
+      if (!L.w_vda) TRY(dev_alloc(ctx, &L.w_vda, 3 * one));
+      for (int si = 0; si < 3; ++si)
+        VN_CUDA(ctx, cudaMemcpyAsync((char*)L.w_vda + si * one, si == 2 ? L.sub[2].w_abs : L.sub[si].wqkv, one,
+                                     cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+  }
   for (auto& L : m->layers)
     for (auto& S : L.sub) {
       const int H = c.n_head;
@@ -1597,6 +1628,7 @@ int32_t vn_model_quantize(vn_model* m, const char* scheme) {
       S.w_down = nullptr;
       if (S.w_abs) { VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); VN_CUDA(ctx, cudaFree(S.w_abs)); S.w_abs = nullptr; }
     }
+    if (L.w_vda) { VN_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); VN_CUDA(ctx, cudaFree(L.w_vda)); L.w_vda = nullptr; }
     TRY(quantize_matrix(m, &L.wproj, D, (int)qd, mode, &L.q[1], &L.qs[1], true, &bytes));
     if (L.kind != 1) {
       TRY(quantize_matrix(m, &L.w_gateup, 2ll * c.mlp_hidden, (int)D, mode, &L.q[2], &L.qs[2], true, &bytes));
