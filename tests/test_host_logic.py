@@ -1,6 +1,7 @@
 """Host-side logic of the drop-in classes that needs no GPU (a recording stand-in replaces the device context)."""
 
 import numpy as np
+import pytest
 
 import versenext_b200.speculative as S
 
@@ -76,3 +77,22 @@ def test_head_weight_of_the_wrong_shape_is_rejected():
     dec.draft_heads[0].weight = S.Tensor(np.zeros((15, 8), np.float32))
     with pytest.raises(ValueError):
         dec._weights()
+
+
+def test_delta_layer_pattern_and_synthetic_shapes(golden):
+    """`build_verse_delta_pattern` of the package against the lists recorded from the reference, and the synthetic
+    weight generator's tensor names and shapes for delta layers against the oracle's (= the reference's state_dict)."""
+    import versenext_b200 as vn
+    from versenext_b200 import synthetic
+    from oracle import delta as OD
+    from oracle import model as OM
+    g = golden("delta_reference.npz")
+    for n in (1, 5, 6, 9, 10, 14):
+        assert vn.build_verse_delta_pattern(n) == list(g[f"pattern_{n}"])
+    with pytest.raises(ValueError):
+        vn.build_verse_delta_pattern(0)
+    for tag in "abc":
+        cfg, _ = OD.golden_case(tag)
+        got = dict(synthetic._shapes(cfg.to_dict()))
+        want = {n: tuple(s) for n, s in OM.param_shapes(cfg).items() if not (n == "head.weight" and cfg.tie_weights)}
+        assert got == want
