@@ -307,3 +307,33 @@ def test_delta_layers_weight_only_quantised(scheme):
         c2.commit(36, np.full(2, 36, np.int32))
         np.testing.assert_array_equal(m2.forward_cached(toks[:, 36:], c2).numpy(), l2)
     m.check()
+
+
+def test_delta_one_token_route_on_the_tensor_core_kernels():
+    """bf16, head_dim 64: the one-token route's rule (every row counts its own keys; no switch for DSA / KDA) on the
+    tensor-core attention tile -- a 1030-token prompt taken as one chunk on that route, then single tokens."""
+    cfg = hd64_delta_cfg()
+    sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=91, gate_std=1.0).items()}
+    m = build(cfg, sd, "bf16")
+    rng = np.random.default_rng(13)
+    toks = rng.integers(0, cfg.vocab_size, (1, 1040))
+    want, oc = OM.forward(sd, cfg, toks[:, :1030], recurrent=True)
+    cache = m.new_cache(1, 1100)
+    m._set_recurrent(True)
+    try:
+        got = m.forward_cached(toks[:, :1030], cache).numpy()
+        cache.commit(1030, np.full(1, 1030, np.int32))
+        sel = [0, 1, 47, 48, 500, 1000, 1023, 1024, 1025, 1029]
+        assert rel_err(got[:, sel], want[:, sel]) < 2e-2
+        for t in range(1030, 1040):
+            lg = m.forward_cached(toks[:, t:t + 1], cache).numpy()
+            cache.commit(1, np.ones(1, np.int32))
+            w, oc = OM.forward(sd, cfg, toks[:, t:t + 1], cache=oc, recurrent=True)
+            assert rel_err(lg, w) < 2e-2, t
+    finally:
+        m._set_recurrent(False)
+    # the whole-sequence rule gives something else beyond the switch (GMLA rows below 1024 keys differ)
+    cache.reset()
+    other = m.forward_cached(toks[:, :1030], cache).numpy()
+    assert rel_err(other[:, [500]], want[:, [500]]) > 3e-2
+    m.check()
