@@ -113,10 +113,11 @@ def test_delta_model_generates_and_verifies_like_the_reference(golden):
     assert vn.build_verse_delta_pattern(10) == list(g["pattern_10"])
 
 
-def test_delta_layers_bf16_head_dim_64_with_a_long_prompt():
+@pytest.mark.parametrize("n_kv", [2, 4, 1])
+def test_delta_layers_bf16_head_dim_64_with_a_long_prompt(n_kv):
     """head_dim 64, bf16, 320 prompt rows (the projections then run as 256-row segments on the tcgen05 kernel) and a
-    decode step on the cache."""
-    cfg = OM.Config(vocab_size=128, dim=256, n_layer=2, n_head=4, n_kv_head=2, layer_pattern=["vda", "dsa"],
+    decode step on the cache; grouped-query (2 heads per KV head), multi-head and multi-query layouts."""
+    cfg = OM.Config(vocab_size=128, dim=256, n_layer=2, n_head=4, n_kv_head=n_kv, layer_pattern=["vda", "dsa"],
                     window_size=32, num_global_tokens=8, anchor_interval=16, latent_dim=64, use_alibi=False,
                     use_rope=True, max_seq_len=256, init_std=0.05)
     sd = {n: OM.bf16_round(v) for n, v in OM.init_state_dict(cfg, seed=51, gate_std=1.0).items()}
