@@ -219,7 +219,10 @@ int32_t vn_philox_uniform(vn_ctx* ctx, uint64_t seed, uint32_t offset, int32_t B
 
 /* ---- target / draft model (verse_nex/cometspark.py:294-698) ------------ */
 /* config_json: the keyword arguments of CometSparkNexLM.__init__ (cometspark.py:334-364)
- * plus "embedding_scale" (spark/src/base_model.py:161) and "dtype": "f32" | "bf16". */
+ * plus "embedding_scale" (spark/src/base_model.py:161) and "dtype": "f32" | "bf16".
+ * "layer_pattern" takes every kind of VerseNexBlock.VALID_KINDS (cometspark.py:110): "trisparse", "mod", and the
+ * delta attention kinds "vda", "dsa", "kda", "gmla" (verse_nex/delta_attention.py; "anchor_interval", "latent_dim").
+ * A delta layer computes the whole-sequence forward of its class on the cache (masks from absolute positions). */
 int32_t vn_model_create(vn_ctx* ctx, const char* config_json, vn_model** out);
 int32_t vn_model_destroy(vn_model* m);
 /* name: dotted state_dict name (verse_torch/vnnn.py:235-252); data: host fp32, C order */
@@ -282,8 +285,10 @@ int32_t vn_model_probe_wait(vn_model* m, int64_t* waited_cycles);
  * Returns VN_OK when both are clear, VN_ERR_INDEX for a bad token, VN_ERR_TIMEOUT for a timeout. */
 int32_t vn_model_status(vn_model* m, int32_t* bad_token, int32_t* wait_timeout);
 
-/* KV cache: per layer K and V of shape [max_batch, max_seq, n_kv_head, head_dim]
- * with per-sequence lengths (verse_nex/kv_cache_parallel.py:42-283). */
+/* KV cache: per attention module K and V of shape [max_batch, max_seq, n_kv_head, head_dim]
+ * with per-sequence lengths (verse_nex/kv_cache_parallel.py:42-283).  One K / V pair per layer, three (DSA, KDA,
+ * GMLA) for a "vda" layer; vn_kv_read's `layer` counts these pairs.  A GMLA module caches the K / V rebuilt from
+ * its latents. */
 int32_t vn_kv_create(vn_model* m, int32_t max_batch, int32_t max_seq, vn_kv** out);
 int32_t vn_kv_destroy(vn_kv* kv);
 /* A second handle on sequences [first, first + count) of a cache: forwards, commits, resets and length calls on it
