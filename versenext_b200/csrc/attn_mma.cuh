@@ -237,10 +237,12 @@ __device__ __forceinline__ void attend(const AttnArgs& a, const __nv_bfloat16* _
 // Called by all AW * 32 threads of a CTA; attn_smem: AW * RING * 4096 bytes of shared memory, 128-byte aligned.
 // Everything another kernel -- or, inside a persistent kernel, another CTA -- wrote shortly before is read past L1
 // (cp.async.cg, __ldcg).
-// DELTA: compiled with the delta-attention modules (AttnArgs::delta); the TriSparse instance carries none of that code.
-template <bool DELTA>
+// DM: 0 = TriSparse; 1 / 2 / 3 = compiled for that delta-attention module (AttnArgs::delta: DSA / KDA / GMLA), each
+// instance carrying only its own passes.
+template <int DM>
 __device__ __forceinline__ void attn_tile(const AttnArgs& a, int bx, int by, unsigned char* attn_smem, long long* tr) {
-  const int dmode = DELTA ? a.delta : 0;
+  constexpr bool DELTA = DM != 0;
+  constexpr int dmode = DM;
   // per warp: a ring of RING key blocks; after a path's keys the first 4 KB of the warp's ring hold its
   // partial output (16 rows x 64 dims fp32, 16-byte chunks swizzled) for the merge across warps
   __shared__ float sM[AW][16], sL[AW][16];
@@ -549,14 +551,15 @@ __global__ void __launch_bounds__(AW * 32, 2) trisparse_attn_mma_kernel(AttnArgs
   long long* tr = a.trace ? a.trace + 8ll * (blockIdx.x + (long long)gridDim.x * blockIdx.y) : nullptr;
   if (tr && threadIdx.x == 0) tr[0] = clock_stamp();
   pdl_trigger();
-  attn_tile<false>(a, blockIdx.x, blockIdx.y, attn_smem_dyn, tr);
+  attn_tile<0>(a, blockIdx.x, blockIdx.y, attn_smem_dyn, tr);
 }
 
-// the same tile with the delta-attention modules compiled in (AttnArgs::delta != 0)
+// the same tile compiled for one delta-attention module (DM = AttnArgs::delta: 1 DSA, 2 KDA, 3 GMLA)
+template <int DM>
 __global__ void __launch_bounds__(AW * 32, 2) delta_attn_mma_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char attn_smem_dyn[];
   pdl_trigger();
-  attn_tile<true>(a, blockIdx.x, blockIdx.y, attn_smem_dyn, nullptr);
+  attn_tile<DM>(a, blockIdx.x, blockIdx.y, attn_smem_dyn, nullptr);
 }
 
 // ---- prompt attention: the eight warps of a CTA take eight different 16-row tiles of one (sequence, kv head) --
@@ -705,15 +708,29 @@ inline int32_t launch_attn_mma(vn_ctx* ctx, const AttnArgs& a, int B) {
   if (!((attr_set >> (ctx->device & 63)) & 1ull)) {
     VN_CUDA(ctx, cudaFuncSetAttribute(attn_detail::trisparse_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem));
-    VN_CUDA(ctx, cudaFuncSetAttribute(attn_detail::delta_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    VN_CUDA(ctx, cudaFuncSetAttribute(attn_detail::delta_attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+    VN_CUDA(ctx, cudaFuncSetAttribute(attn_detail::delta_attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+    VN_CUDA(ctx, cudaFuncSetAttribute(attn_detail::delta_attn_mma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem));
     attr_set |= 1ull << (ctx->device & 63);
   }
   // VN_ATTN_PDL=0 (read once): plain launch
   static const bool attn_pdl = [] { const char* e = getenv("VN_ATTN_PDL"); return !(e && e[0] == '0'); }();
   const int level = ((vn_pdl_mask() & 1) || attn_pdl) ? 1 : 2;
-  if (a.delta) {
-    VN_LAUNCH_PDL_LEVEL(ctx, level, "attn_detail::delta_attn_mma_kernel", attn_detail::delta_attn_mma_kernel, grid,
+  if (a.delta == 1) {
+    VN_LAUNCH_PDL_LEVEL(ctx, level, "attn_detail::delta_attn_mma_kernel<dsa>", attn_detail::delta_attn_mma_kernel<1>, grid,
+                        attn_detail::AW * 32, smem, a);
+    return VN_OK;
+  }
+  if (a.delta == 2) {
+    VN_LAUNCH_PDL_LEVEL(ctx, level, "attn_detail::delta_attn_mma_kernel<kda>", attn_detail::delta_attn_mma_kernel<2>, grid,
+                        attn_detail::AW * 32, smem, a);
+    return VN_OK;
+  }
+  if (a.delta == 3) {
+    VN_LAUNCH_PDL_LEVEL(ctx, level, "attn_detail::delta_attn_mma_kernel<gmla>", attn_detail::delta_attn_mma_kernel<3>, grid,
                         attn_detail::AW * 32, smem, a);
     return VN_OK;
   }

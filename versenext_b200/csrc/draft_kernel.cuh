@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(DT, 1) draft_layers_kernel(Args a) {
       t.use_alibi = a.use_alibi; t.alibi_max = 1024; t.alibi_window = a.alibi_window;
       t.g_a = L.g_a; t.g_b = L.g_b; t.g_c = L.g_c; t.scale = rsqrtf((float)hd);
       for (int it = cta; it < n_items; it += n_cta) {
-        attn_detail::attn_tile<false>(t, it / tiles, it % tiles, dsm, nullptr);
+        attn_detail::attn_tile<0>(t, it / tiles, it % tiles, dsm, nullptr);
         __syncthreads();
       }
     }
